@@ -1,0 +1,331 @@
+// The exported C ABI (include/b200tile.h): argument validation, configuration selection and
+// forwarding to the per-kernel launchers.  Nothing here allocates, frees or synchronises on a
+// launch path, so launches can be captured into CUDA graphs.
+#include "../../include/b200tile.h"
+
+#include <stdlib.h>
+#include <string.h>
+
+#include "host_common.h"
+
+// per-kernel launchers (defined next to their kernels)
+int b200_gemm_tc_dispatch(int dtype, int b_kmajor, int config, const void* A, const void* B,
+                          void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                          int group_m, int max_ctas, cudaStream_t stream);
+int b200_gemm_f32_dispatch(const float* A, const float* B, float* C, int batch, int M, int N,
+                           int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sa, int64_t sb,
+                           int64_t sc, int accumulate, cudaStream_t stream);
+
+using b200h::set_error;
+
+static_assert(B200TILE_ERR_INVALID == B200_ERR_INVALID && B200TILE_ERR_ALIGN == B200_ERR_ALIGN &&
+                  B200TILE_ERR_UNSUPPORTED == B200_ERR_UNSUPPORTED &&
+                  B200TILE_ERR_CUDA == B200_ERR_CUDA && B200TILE_ERR_DEVICE == B200_ERR_DEVICE,
+              "public and internal status codes must agree");
+
+extern "C" {
+
+int b200tile_abi_version(void) { return B200TILE_ABI_VERSION; }
+
+const char* b200tile_last_error(void) { return b200h::last_error(); }
+
+int b200tile_init(int device_ordinal) {
+  B200_CUDA_CHECK(cudaSetDevice(device_ordinal));
+  B200_CUDA_CHECK(cudaFree(0));  // materialise the primary context on this thread
+  return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+}
+
+int b200tile_num_sms(void) {
+  const b200h::DeviceInfo* di = b200h::device_info();
+  return di ? di->sm_count : -1;
+}
+
+int b200tile_status(void* cu_stream, b200tile_status_t* out) {
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200TILE_ERR_CUDA;
+  if (!out) return set_error(B200TILE_ERR_INVALID, "status: out is null");
+  cudaStream_t s = static_cast<cudaStream_t>(cu_stream);
+  uint32_t w[4] = {0, 0, 0, 0};
+  B200_CUDA_CHECK(cudaMemcpyAsync(w, di->status, sizeof(w), cudaMemcpyDeviceToHost, s));
+  B200_CUDA_CHECK(cudaStreamSynchronize(s));
+  out->code = w[0];
+  out->block = w[1];
+  out->site = w[2];
+  out->aux = w[3];
+  if (w[0] != 0)
+    return set_error(B200TILE_ERR_DEVICE,
+                     "device status %u recorded by block %u at wait site %u (aux %u)", w[0], w[1],
+                     w[2], w[3]);
+  return B200TILE_OK;
+}
+
+int b200tile_status_reset(void* cu_stream) {
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200TILE_ERR_CUDA;
+  B200_CUDA_CHECK(
+      cudaMemsetAsync(di->status, 0, 4 * sizeof(uint32_t), static_cast<cudaStream_t>(cu_stream)));
+  return B200TILE_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Configuration tables
+// ---------------------------------------------------------------------------
+static const b200tile_config kGemmTcConfigs[] = {
+    /* id  bm   bn   bk stages cga occ */
+    {0, 128, 256, 64, 4, 1, 1},
+    {1, 128, 128, 64, 6, 1, 1},
+};
+static const b200tile_config kGemmF32Configs[] = {
+    {0, 64, 64, 16, 1, 1, 1},
+};
+
+static bool is_gemm_name(const char* k) {
+  return !strcmp(k, "gemm") || !strcmp(k, "gemm_acc") || !strcmp(k, "gemm_persistent") ||
+         !strcmp(k, "batch_matmul") || !strcmp(k, "gemm_static");
+}
+
+int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_config* out, int cap) {
+  if (!kernel || !dtype) return 0;
+  const b200tile_config* tab = nullptr;
+  int n = 0;
+  if (is_gemm_name(kernel)) {
+    if (!strcmp(dtype, "f32")) {
+      tab = kGemmF32Configs;
+      n = (int)(sizeof(kGemmF32Configs) / sizeof(kGemmF32Configs[0]));
+    } else if (!strcmp(dtype, "bf16") || !strcmp(dtype, "f16")) {
+      tab = kGemmTcConfigs;
+      n = (int)(sizeof(kGemmTcConfigs) / sizeof(kGemmTcConfigs[0]));
+    }
+  }
+  for (int i = 0; i < n && i < cap && out; ++i) out[i] = tab[i];
+  return n;
+}
+
+// ---------------------------------------------------------------------------
+// Typed GEMM entry point
+// ---------------------------------------------------------------------------
+int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b, void* c,
+                  int batch, int m, int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
+                  int64_t stride_a, int64_t stride_b, int64_t stride_c, int accumulate, int config,
+                  int group_size_m, int num_programs, void* cu_stream) {
+  if (!dtype) return set_error(B200TILE_ERR_INVALID, "gemm: dtype is null");
+  if (!a || !b || !c) return set_error(B200TILE_ERR_INVALID, "gemm: null tensor pointer");
+  if (m <= 0 || n <= 0 || k <= 0 || batch <= 0)
+    return set_error(B200TILE_ERR_INVALID,
+                     "gemm: Shape dimensions must be positive (batch %d, m %d, n %d, k %d)", batch,
+                     m, n, k);
+  const int64_t b_cols = b_layout ? k : n;
+  if (lda < k || ldb < b_cols || ldc < n)
+    return set_error(B200TILE_ERR_INVALID, "gemm: leading dimension smaller than the row length");
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  if (group_size_m <= 0) group_size_m = 8;
+
+  if (!strcmp(dtype, "f32")) {
+    if (b_layout != 0)
+      return set_error(B200TILE_ERR_UNSUPPORTED, "gemm(f32): only B[K,N] is provided");
+    if (config > 0)
+      return set_error(B200TILE_ERR_UNSUPPORTED, "gemm(f32): unknown config %d", config);
+    return b200_gemm_f32_dispatch(static_cast<const float*>(a), static_cast<const float*>(b),
+                                  static_cast<float*>(c), batch, m, n, k, lda, ldb, ldc, stride_a,
+                                  stride_b, stride_c, accumulate, stream);
+  }
+  int dt;
+  if (!strcmp(dtype, "bf16"))
+    dt = 0;
+  else if (!strcmp(dtype, "f16"))
+    dt = 1;
+  else
+    return set_error(B200TILE_ERR_UNSUPPORTED, "gemm: unsupported element type '%s'", dtype);
+  if (accumulate)
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "gemm(%s): accumulate-into-C is only provided for f32", dtype);
+  if (config < 0) config = (n <= 128 || ((int64_t)((m + 127) / 128) * ((n + 255) / 256) < 96)) ? 1 : 0;
+  for (int bi = 0; bi < batch; ++bi) {
+    const char* ab = static_cast<const char*>(a) + (int64_t)bi * stride_a * 2;
+    const char* bb = static_cast<const char*>(b) + (int64_t)bi * stride_b * 2;
+    char* cb = static_cast<char*>(c) + (int64_t)bi * stride_c * 2;
+    int rc = b200_gemm_tc_dispatch(dt, b_layout ? 1 : 0, config, ab, bb, cb, m, n, k, lda, ldb,
+                                   ldc, group_size_m, num_programs, stream);
+    if (rc) return rc;
+  }
+  return B200TILE_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Reference-shaped generic launch
+// ---------------------------------------------------------------------------
+namespace {
+
+struct ParamReader {
+  const void* const* p;
+  int n, pos;
+  bool ok;
+  uint64_t u64() {
+    if (pos >= n || !p[pos]) { ok = false; return 0; }
+    return *static_cast<const uint64_t*>(p[pos++]);
+  }
+  int32_t i32() {
+    if (pos >= n || !p[pos]) { ok = false; return 0; }
+    return *static_cast<const int32_t*>(p[pos++]);
+  }
+  float f32() {
+    if (pos >= n || !p[pos]) { ok = false; return 0; }
+    return *static_cast<const float*>(p[pos++]);
+  }
+};
+
+struct TensorArg {
+  uint64_t ptr;
+  int rank;
+  int32_t dim[3], stride[3], pdim[3], pstride[3];
+};
+
+void read_tensor(ParamReader& r, int rank, bool is_mut, TensorArg& t) {
+  t.rank = rank;
+  t.ptr = r.u64();
+  for (int i = 0; i < rank; ++i) t.dim[i] = r.i32();
+  for (int i = 0; i < rank; ++i) t.stride[i] = r.i32();
+  if (is_mut) {
+    for (int i = 0; i < rank; ++i) t.pdim[i] = r.i32();
+    for (int i = 0; i < rank; ++i) t.pstride[i] = r.i32();
+  }
+}
+
+bool parse_int(const char* s, long* out) {
+  if (!s || !*s) return false;
+  char* end = nullptr;
+  long v = strtol(s, &end, 10);
+  if (*end != '\0') return false;
+  *out = v;
+  return true;
+}
+
+// Maps (BM, BN, BK, CompileOptions) onto a precompiled GEMM configuration id.
+int select_gemm_config(const char* dtype, long bm, long bn, long bk,
+                       const b200tile_compile_options* opts, int* config) {
+  if (opts) {
+    if (opts->num_cta_in_cga > 1)
+      return set_error(B200TILE_ERR_UNSUPPORTED,
+                       "gemm: num_cta_in_cga=%d has no precompiled configuration",
+                       opts->num_cta_in_cga);
+    if (opts->occupancy > 1)
+      return set_error(B200TILE_ERR_UNSUPPORTED,
+                       "gemm: occupancy=%d has no precompiled configuration", opts->occupancy);
+  }
+  if (!strcmp(dtype, "f32")) {
+    *config = 0;  // the exact-fp32 kernel produces identical results for every tile shape
+    return B200TILE_OK;
+  }
+  if (bm == 128 && bn == 256 && bk == 64) { *config = 0; return B200TILE_OK; }
+  if (bm == 128 && bn == 128 && bk == 64) { *config = 1; return B200TILE_OK; }
+  return set_error(B200TILE_ERR_UNSUPPORTED,
+                   "gemm(%s): tile (%ld,%ld,%ld) has no precompiled configuration", dtype, bm, bn,
+                   bk);
+}
+
+int launch_gemm_generic(const char* kernel, const char* const* generics, int n_generics,
+                        const b200tile_compile_options* opts, const void* const* params,
+                        int n_params, const unsigned grid[3], void* stream, bool launch) {
+  const bool batched = !strcmp(kernel, "batch_matmul");
+  const bool persistent = !strcmp(kernel, "gemm_persistent");
+  if (n_generics < 4)
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "%s: expected generics [T, BM, BN, BK, ...], got %d entries", kernel,
+                     n_generics);
+  const char* dtype = generics[0];
+  long bm, bn, bk;
+  if (!parse_int(generics[1], &bm) || !parse_int(generics[2], &bn) || !parse_int(generics[3], &bk))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: tile-size generics must be integers", kernel);
+  if (strcmp(dtype, "f32") && strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  int config = 0;
+  if (int rc = select_gemm_config(dtype, bm, bn, bk, opts, &config)) return rc;
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+
+  const int rank = batched ? 3 : 2;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg z, x, y;
+  read_tensor(r, rank, true, z);
+  read_tensor(r, rank, false, x);
+  read_tensor(r, rank, false, y);
+  if (!r.ok)
+    return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short (%d values)", kernel,
+                     n_params);
+  const int o = batched ? 1 : 0;  // offset of the matrix axes
+  const int M = z.dim[o], N = z.dim[o + 1], K = x.dim[o + 1];
+  if (x.dim[o] != M || y.dim[o] != K || y.dim[o + 1] != N)
+    return set_error(B200TILE_ERR_INVALID,
+                     "%s: shapes do not compose: z[%d,%d] x[%d,%d] y[%d,%d]", kernel, M, N,
+                     x.dim[o], x.dim[o + 1], y.dim[o], y.dim[o + 1]);
+  if (z.stride[o + 1] != 1 || x.stride[o + 1] != 1 || y.stride[o + 1] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: the last axis of every tensor must be contiguous",
+                     kernel);
+  if (z.pdim[o] != bm || z.pdim[o + 1] != bn)
+    return set_error(B200TILE_ERR_INVALID,
+                     "%s: output partition (%d,%d) does not match the tile generics (%ld,%ld)",
+                     kernel, z.pdim[o], z.pdim[o + 1], bm, bn);
+  const unsigned tiles_m = (unsigned)((M + bm - 1) / bm), tiles_n = (unsigned)((N + bn - 1) / bn);
+  int batch = 1;
+  int num_programs = 0;
+  if (batched) {
+    batch = z.dim[0];
+    if (x.dim[0] != batch || y.dim[0] != batch)
+      return set_error(B200TILE_ERR_INVALID, "batch_matmul: batch extents differ");
+    if (grid[0] != (unsigned)batch || grid[1] != tiles_m || grid[2] != tiles_n)
+      return set_error(B200TILE_ERR_INVALID,
+                       "launch grid (%u, %u, %u) does not match the inferred partition grid "
+                       "(%d, %u, %u)",
+                       grid[0], grid[1], grid[2], batch, tiles_m, tiles_n);
+  } else if (persistent) {
+    if (grid[0] == 0 || grid[1] != 1 || grid[2] != 1 || grid[0] > tiles_m * tiles_n)
+      return set_error(B200TILE_ERR_INVALID,
+                       "mapped partition num_tile_blocks cannot exceed the streamed logical tile "
+                       "count. (grid (%u, %u, %u), tiles %u)",
+                       grid[0], grid[1], grid[2], tiles_m * tiles_n);
+    num_programs = (int)grid[0];
+  } else {
+    if (grid[0] != tiles_m || grid[1] != tiles_n || grid[2] != 1)
+      return set_error(B200TILE_ERR_INVALID,
+                       "launch grid (%u, %u, %u) does not match the inferred partition grid "
+                       "(%u, %u, 1)",
+                       grid[0], grid[1], grid[2], tiles_m, tiles_n);
+  }
+  // The paper and persistent kernels start each tile from zero (main.rs:85,121).  The example
+  // `gemm` loads z as the initial accumulator (cutile-examples/examples/gemm.rs:28); a launcher
+  // for that body binds the name "gemm_acc".
+  const int accumulate = !strcmp(kernel, "gemm_acc") ? 1 : 0;
+  long group_m = 8;
+  if (persistent && n_generics >= 6) {
+    long map_m;
+    if (parse_int(generics[4], &map_m) && map_m > 0) group_m = map_m;
+  }
+  return b200tile_gemm(dtype, 0, reinterpret_cast<const void*>(x.ptr),
+                       reinterpret_cast<const void*>(y.ptr), reinterpret_cast<void*>(z.ptr), batch,
+                       M, N, K, x.stride[o], y.stride[o], z.stride[o], batched ? x.stride[0] : 0,
+                       batched ? y.stride[0] : 0, batched ? z.stride[0] : 0, accumulate, config,
+                       (int)group_m, num_programs, stream);
+}
+
+}  // namespace
+
+int b200tile_launch(const char* kernel, const char* const* generics, int n_generics,
+                    const b200tile_compile_options* opts, const void* const* params, int n_params,
+                    const unsigned grid[3], void* cu_stream) {
+  if (!kernel) return set_error(B200TILE_ERR_INVALID, "launch: kernel name is null");
+  if (!params || !grid) return set_error(B200TILE_ERR_INVALID, "launch: null params or grid");
+  if (is_gemm_name(kernel))
+    return launch_gemm_generic(kernel, generics, n_generics, opts, params, n_params, grid,
+                               cu_stream, true);
+  return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
+}
+
+int b200tile_prepare(const char* kernel, const char* const* generics, int n_generics,
+                     const b200tile_compile_options* opts) {
+  if (!kernel) return set_error(B200TILE_ERR_INVALID, "prepare: kernel name is null");
+  if (is_gemm_name(kernel))
+    return launch_gemm_generic(kernel, generics, n_generics, opts, nullptr, 0, nullptr, nullptr,
+                               false);
+  return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
+}
+
+}  // extern "C"

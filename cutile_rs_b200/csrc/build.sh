@@ -1,0 +1,20 @@
+#!/usr/bin/env bash
+# Builds libb200tile.so (sm_100a machine code only) next to this script's package.
+set -euo pipefail
+here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
+out="${here}/../libb200tile.so"
+NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
+FLAGS=(-std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a
+       -Xcompiler -fPIC -Xcompiler -fvisibility=hidden ${B200_NVCC_EXTRA:-})
+objs=()
+for src in host_common gemm_tc gemm_f32 abi; do
+  obj="${here}/_${src}.o"
+  if [[ ! -f "${obj}" || "${here}/${src}.cu" -nt "${obj}" || "${here}/sm100_ptx.cuh" -nt "${obj}" \
+        || "${here}/host_common.h" -nt "${obj}" || "${here}/../../include/b200tile.h" -nt "${obj}" ]]; then
+    "${NVCC}" "${FLAGS[@]}" -c "${here}/${src}.cu" -o "${obj}" &
+  fi
+  objs+=("${obj}")
+done
+wait
+"${NVCC}" -shared -o "${out}" "${objs[@]}" -lcuda 2>/dev/null || "${NVCC}" -shared -o "${out}" "${objs[@]}"
+echo "built ${out}"

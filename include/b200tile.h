@@ -1,0 +1,137 @@
+/* b200tile -- C ABI of the sm_100a dense-contraction kernels.
+ *
+ * This is the boundary a cuTile-Rust launcher binds instead of JIT-compiling the kernel body
+ * and calling cuLaunchKernel itself.  Every entry point takes plain pointers and sizes, never
+ * allocates or synchronises inside a launch call (so launches may be recorded into a CUDA graph,
+ * the contract of `GraphNode`, cuda-async/src/cuda_graph.rs:303-324), borrows device memory only
+ * for the duration of the stream-ordered work, returns 0 on success and a small positive code
+ * otherwise, and never throws or aborts.  All functions may be called from many threads.
+ *
+ * The library contains machine code for sm_100a only; there is no CPU or other-GPU fallback.
+ */
+#ifndef B200TILE_H_
+#define B200TILE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200TILE_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define B200TILE_API __attribute__((visibility("default")))
+#else
+#define B200TILE_API
+#endif
+
+/* Return codes. */
+#define B200TILE_OK 0
+#define B200TILE_ERR_INVALID 1     /* argument violates a kernel precondition            */
+#define B200TILE_ERR_UNSUPPORTED 2 /* unknown kernel / generics / config combination     */
+#define B200TILE_ERR_CUDA 3        /* a CUDA call failed                                 */
+#define B200TILE_ERR_DEVICE 4      /* the device status record holds an error            */
+#define B200TILE_ERR_ALIGN 5       /* pointer or pitch violates TMA's 16-byte rules      */
+
+/* Mirrors `CompileOptions` (cutile-compiler/src/hints.rs:94-126).  A field of -1 means
+ * "not set".  The options select among the fixed, precompiled kernel configurations. */
+typedef struct b200tile_compile_options {
+  int occupancy;
+  int num_cta_in_cga;
+  int max_divisibility;
+  int num_worker_warps_per_cta;
+} b200tile_compile_options;
+
+/* One precompiled configuration, as enumerated for the autotuner (replaces the open-ended
+ * tile-size generics of the JIT, cutile/src/tune.rs:53-121). */
+typedef struct b200tile_config {
+  int id;
+  int bm, bn, bk;
+  int stages;
+  int num_cta_in_cga;
+  int occupancy;
+} b200tile_config;
+
+/* Device status record written by bounded waits inside the kernels. */
+typedef struct b200tile_status_t {
+  uint32_t code;  /* 0 = ok, 1 = a wait gave up */
+  uint32_t block; /* blockIdx.x of the CTA that recorded it */
+  uint32_t site;  /* which wait */
+  uint32_t aux;
+} b200tile_status_t;
+
+/* ---- library management ------------------------------------------------------------------ */
+
+/* Replaces nothing in the reference; lets a binding check it was built against this header. */
+B200TILE_API int b200tile_abi_version(void);
+
+/* Binds the device's primary context to the calling thread and resolves per-device state
+ * (SM count, status record).  Counterpart of `Device::new` + `bind_to_thread`
+ * (cuda-core/src/runtime.rs:126-140,229-237).  Call once per device before capturing graphs. */
+B200TILE_API int b200tile_init(int device_ordinal);
+
+/* Text of the last error on the calling thread.  Counterpart of the `Display` text of
+ * `Error::KernelLaunch` / `DeviceError` (cutile/src/error.rs:42-55). */
+B200TILE_API const char* b200tile_last_error(void);
+
+/* Number of SMs of the current device; what `persistent_num_programs` needs
+ * (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:796-811). */
+B200TILE_API int b200tile_num_sms(void);
+
+/* Reads (synchronising `stream`) or clears the device status record. */
+B200TILE_API int b200tile_status(void* cu_stream, b200tile_status_t* out);
+B200TILE_API int b200tile_status_reset(void* cu_stream);
+
+/* Lists the precompiled configurations of `kernel` for element type `dtype`; returns how many
+ * exist (may exceed `cap`).  Feeds `Autotuner::configs` (cutile/src/tune.rs:312-410). */
+B200TILE_API int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_config* out, int cap);
+
+/* ---- reference-shaped generic launch ----------------------------------------------------- */
+
+/* Drop-in for the two calls the macro-generated launcher makes per launch: `jit_compile` and
+ * `AsyncKernelLaunch::execute` (cutile-macro/src/kernel_launcher_generator.rs:911-923,958-975;
+ * cuda-async/src/launch.rs:91-113).
+ *   kernel    entry name without the `_entry` suffix: "gemm", "gemm_persistent", "batch_matmul"
+ *   generics  the launcher's `Vec<String>` (dtype names from cuda-core/src/dtype.rs:147-168,
+ *             integers in decimal)
+ *   params    the reference's flattened kernel parameter array, one pointer per value, in
+ *             signature order: per `&Tensor`: ptr(u64), dims(i32...), strides(i32...); per
+ *             `&mut Tensor`: the same plus partition dims and partition strides
+ *             (cutile-compiler/src/kernel_entry_generator.rs:176-201; cutile/src/tensor.rs:
+ *             1723-1739,2006-2016); scalars by value
+ *   grid      the launcher's inferred grid; validated against the output partition
+ * An unsupported combination returns B200TILE_ERR_UNSUPPORTED (the autotuner turns that into
+ * `TrialState::Invalid`, cutile/src/tune.rs:503-514). */
+B200TILE_API int b200tile_launch(const char* kernel, const char* const* generics, int n_generics,
+                    const b200tile_compile_options* opts, const void* const* params, int n_params,
+                    const unsigned grid[3], void* cu_stream);
+
+/* Warm-up without launching: the `.compile()` path (cutile-macro/src/_module.rs:852-866).
+ * Sets function attributes so the first real launch has no lazy cost. */
+B200TILE_API int b200tile_prepare(const char* kernel, const char* const* generics, int n_generics,
+                     const b200tile_compile_options* opts);
+
+/* ---- typed entry points (what b200tile_launch forwards to) ------------------------------- */
+
+/* C[b] (+)= A[b] * B[b], row-major, leading dimensions and batch strides in ELEMENTS.
+ * Replaces the kernels `gemm` (cutile-examples/examples/gemm.rs:20-36, cutile-benchmarks/
+ * benches/gemm.rs:20-41), `gemm_persistent` (cutile-benchmarks/paper/sec5_exp1_safety_overhead/
+ * rust/gemm/src/main.rs:98-132) and `batch_matmul` (cutile-examples/examples/batch_matmul.rs:
+ * 17-43).
+ *   dtype       "f32" (exact fp32, bit-identical to the reference's cpu_gemm), "bf16", "f16"
+ *               (tensor cores, fp32 accumulation, output rounded to the input type)
+ *   b_layout    0: B is [K,N] (reference GEMM), 1: B is [N,K] (reference linear_tile, "NT")
+ *   accumulate  0: C = A*B, 1: C = C + A*B (the `load_tile_mut` form; f32 only)
+ *   config      id from b200tile_query_configs, or -1 for the default
+ *   group_size_m  grouped-M tile order (main.rs:53-66); <=0 selects 8
+ *   num_programs  persistent grid size; <=0 selects min(SMs, tiles) */
+B200TILE_API int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b, void* c,
+                  int batch, int m, int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
+                  int64_t stride_a, int64_t stride_b, int64_t stride_c, int accumulate, int config,
+                  int group_size_m, int num_programs, void* cu_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200TILE_H_ */
