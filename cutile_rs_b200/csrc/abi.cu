@@ -16,6 +16,12 @@ int b200_gemm_f32_dispatch(const float* A, const float* B, float* C, int batch, 
                            int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sa, int64_t sb,
                            int64_t sc, int accumulate, cudaStream_t stream);
 
+int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k, const void* v,
+                           void* o, int batch, int heads, int heads_kv, int q_len, int kv_len,
+                           const int64_t* qs, const int64_t* ks, const int64_t* vs,
+                           const int64_t* os, float qk_scale, int causal, int input_pos,
+                           cudaStream_t stream);
+
 using b200h::set_error;
 
 static_assert(B200TILE_ERR_INVALID == B200_ERR_INVALID && B200TILE_ERR_ALIGN == B200_ERR_ALIGN &&
@@ -97,6 +103,12 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
       n = (int)(sizeof(kGemmTcConfigs) / sizeof(kGemmTcConfigs[0]));
     }
   }
+  static const b200tile_config kFmhaConfigs[] = {{0, 128, 128, 0, 2, 1, 1}};
+  if ((!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal")) &&
+      (!strcmp(dtype, "bf16") || !strcmp(dtype, "f16"))) {
+    tab = kFmhaConfigs;
+    n = 1;
+  }
   for (int i = 0; i < n && i < cap && out; ++i) out[i] = tab[i];
   return n;
 }
@@ -151,6 +163,37 @@ int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b,
   return B200TILE_OK;
 }
 
+
+// ---------------------------------------------------------------------------
+// Typed attention entry point
+// ---------------------------------------------------------------------------
+int b200tile_fmha_fwd(const char* dtype, const void* q, const void* k, const void* v, void* out,
+                      int batch, int heads, int heads_kv, int q_len, int kv_len, int head_dim,
+                      const int64_t q_strides[2], const int64_t k_strides[2],
+                      const int64_t v_strides[2], const int64_t o_strides[2], float qk_scale,
+                      int causal, int input_pos, void* cu_stream) {
+  if (!dtype) return set_error(B200TILE_ERR_INVALID, "fmha: dtype is null");
+  if (!q || !k || !v || !out) return set_error(B200TILE_ERR_INVALID, "fmha: null tensor pointer");
+  if (!q_strides || !k_strides || !v_strides || !o_strides)
+    return set_error(B200TILE_ERR_INVALID, "fmha: null stride array");
+  if (batch <= 0 || heads <= 0 || heads_kv <= 0 || q_len <= 0 || kv_len <= 0)
+    return set_error(B200TILE_ERR_INVALID, "fmha: Shape dimensions must be positive");
+  if (heads % heads_kv != 0)
+    return set_error(B200TILE_ERR_INVALID, "fmha: heads (%d) must be a multiple of heads_kv (%d)",
+                     heads, heads_kv);
+  if (input_pos < 0) return set_error(B200TILE_ERR_INVALID, "fmha: input_pos must be >= 0");
+  int dt;
+  if (!strcmp(dtype, "bf16"))
+    dt = 0;
+  else if (!strcmp(dtype, "f16"))
+    dt = 1;
+  else
+    return set_error(B200TILE_ERR_UNSUPPORTED, "fmha: unsupported element type '%s'", dtype);
+  return b200_fmha_fwd_dispatch(dt, head_dim, q, k, v, out, batch, heads, heads_kv, q_len, kv_len,
+                                q_strides, k_strides, v_strides, o_strides, qk_scale,
+                                causal ? 1 : 0, input_pos, static_cast<cudaStream_t>(cu_stream));
+}
+
 // ---------------------------------------------------------------------------
 // Reference-shaped generic launch
 // ---------------------------------------------------------------------------
@@ -177,7 +220,7 @@ struct ParamReader {
 struct TensorArg {
   uint64_t ptr;
   int rank;
-  int32_t dim[3], stride[3], pdim[3], pstride[3];
+  int32_t dim[4], stride[4], pdim[4], pstride[4];
 };
 
 void read_tensor(ParamReader& r, int rank, bool is_mut, TensorArg& t) {
@@ -306,6 +349,127 @@ int launch_gemm_generic(const char* kernel, const char* const* generics, int n_g
                        (int)group_m, num_programs, stream);
 }
 
+// Splits an optional leading element-type generic from the integer generics.
+int split_generics(const char* const* generics, int n, const char* dflt, const char** dtype,
+                   long* ints, int max_ints, int* n_ints) {
+  int start = 0;
+  *dtype = dflt;
+  long tmp;
+  if (n > 0 && generics[0] && !parse_int(generics[0], &tmp)) {
+    *dtype = generics[0];
+    start = 1;
+  }
+  *n_ints = 0;
+  for (int i = start; i < n; ++i) {
+    if (*n_ints >= max_ints || !parse_int(generics[i], &ints[*n_ints])) return 1;
+    ++*n_ints;
+  }
+  return 0;
+}
+
+// "fmha": (out[b*h,m,d] partition [1,BM,D], q, k, v (b,h,m,d), qk_scale f32, input_pos i32,
+//          query_group_size i32), generics [T?, BM, BN, D, H, CAUSAL, EVEN_K]
+//          (cutile-examples/examples/flash_attention_causal.rs:19-45), grid (b*h, m/BM, 1).
+// "fmha_prefill_causal": (q [q_len,heads,D], k, v [kv_heads,kv_len,D], out partition [BM,1,D],
+//          qk_scale f32, query_group_size i32, kv_len i32, query_start i32),
+//          generics [T?, BM, BN, D, CAUSAL, EVEN_K, LATENCY] (cutile-kernels/src/attention.rs:
+//          242-262), grid (q_len/BM, heads, 1).
+int launch_fmha_generic(const char* kernel, const char* const* generics, int n_generics,
+                        const b200tile_compile_options* opts, const void* const* params,
+                        int n_params, const unsigned grid[3], void* stream, bool launch) {
+  (void)opts;
+  const bool prefill = !strcmp(kernel, "fmha_prefill_causal");
+  const char* dtype;
+  long g[8];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 8, &ng) || ng < (prefill ? 4 : 5))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  const long BM = g[0], BN = g[1], D = g[2];
+  const long causal = prefill ? g[3] : g[4];
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  if (BM != 128 || BN != 128 || (D != 64 && D != 128))
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "%s: tile (BM %ld, BN %ld, D %ld) has no precompiled configuration "
+                     "(BM=BN=128, D in {64,128})",
+                     kernel, BM, BN, D);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg q, k, v, o;
+  if (prefill) {
+    read_tensor(r, 3, false, q);
+    read_tensor(r, 3, false, k);
+    read_tensor(r, 3, false, v);
+    read_tensor(r, 3, true, o);
+    const float scale = r.f32();
+    const int group = r.i32();
+    const int kv_len = r.i32();
+    const int query_start = r.i32();
+    if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+    const int q_len = q.dim[0], heads = q.dim[1];
+    const int heads_kv = k.dim[0];
+    if (q.dim[2] != D || k.dim[2] != D || v.dim[2] != D || o.dim[2] != D || q.stride[2] != 1 ||
+        k.stride[2] != 1 || v.stride[2] != 1 || o.stride[2] != 1)
+      return set_error(B200TILE_ERR_INVALID, "%s: head dimension must equal D and be contiguous",
+                       kernel);
+    if (group <= 0 || heads != heads_kv * group || kv_len > k.dim[1] || kv_len <= 0)
+      return set_error(B200TILE_ERR_INVALID, "%s: inconsistent heads / kv_len", kernel);
+    if (o.pdim[0] != BM || o.pdim[1] != 1 || o.pdim[2] != D)
+      return set_error(B200TILE_ERR_INVALID, "%s: output partition must be [BM, 1, D]", kernel);
+    if (grid[0] != (unsigned)((q_len + BM - 1) / BM) || grid[1] != (unsigned)heads || grid[2] != 1)
+      return set_error(B200TILE_ERR_INVALID,
+                       "launch grid (%u, %u, %u) does not match the inferred partition grid "
+                       "(%ld, %d, 1)",
+                       grid[0], grid[1], grid[2], (long)((q_len + BM - 1) / BM), heads);
+    const int64_t qs[2] = {q.stride[1], q.stride[0]}, ks[2] = {k.stride[0], k.stride[1]};
+    const int64_t vs[2] = {v.stride[0], v.stride[1]}, os[2] = {o.stride[1], o.stride[0]};
+    return b200tile_fmha_fwd(dtype, reinterpret_cast<const void*>(q.ptr),
+                             reinterpret_cast<const void*>(k.ptr),
+                             reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr),
+                             1, heads, heads_kv, q_len, kv_len, (int)D, qs, ks, vs, os, scale,
+                             causal != 0, query_start, stream);
+  }
+  read_tensor(r, 3, true, o);
+  read_tensor(r, 4, false, q);
+  read_tensor(r, 4, false, k);
+  read_tensor(r, 4, false, v);
+  const float scale = r.f32();
+  const int input_pos = r.i32();
+  const int group = r.i32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int b = q.dim[0], heads = q.dim[1], m = q.dim[2], heads_kv = k.dim[1], kv_len = k.dim[2];
+  if (q.dim[3] != D || k.dim[3] != D || v.dim[3] != D || o.dim[2] != D || q.stride[3] != 1 ||
+      k.stride[3] != 1 || v.stride[3] != 1 || o.stride[2] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: head dimension must equal D and be contiguous",
+                     kernel);
+  if (o.dim[0] != b * heads || o.dim[1] != m || k.dim[0] != b || v.dim[0] != b ||
+      v.dim[1] != heads_kv || v.dim[2] != kv_len || group <= 0 || heads != heads_kv * group)
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  if (ng >= 4 && g[3] != heads)
+    return set_error(B200TILE_ERR_INVALID, "%s: generic H=%ld but q has %d heads", kernel, g[3],
+                     heads);
+  // (batch, head) must collapse to one stride for every tensor
+  if ((int64_t)q.stride[0] != (int64_t)q.stride[1] * heads ||
+      (int64_t)k.stride[0] != (int64_t)k.stride[1] * heads_kv ||
+      (int64_t)v.stride[0] != (int64_t)v.stride[1] * heads_kv)
+    return set_error(B200TILE_ERR_INVALID,
+                     "%s: batch and head axes must be laid out back to back", kernel);
+  if (o.pdim[0] != 1 || o.pdim[1] != BM || o.pdim[2] != D)
+    return set_error(B200TILE_ERR_INVALID, "%s: output partition must be [1, BM, D]", kernel);
+  if (grid[0] != (unsigned)(b * heads) || grid[1] != (unsigned)((m + BM - 1) / BM) || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid "
+                     "(%d, %ld, 1)",
+                     grid[0], grid[1], grid[2], b * heads, (long)((m + BM - 1) / BM));
+  const int64_t qs[2] = {q.stride[1], q.stride[2]}, ks[2] = {k.stride[1], k.stride[2]};
+  const int64_t vs[2] = {v.stride[1], v.stride[2]}, os[2] = {o.stride[0], o.stride[1]};
+  return b200tile_fmha_fwd(dtype, reinterpret_cast<const void*>(q.ptr),
+                           reinterpret_cast<const void*>(k.ptr),
+                           reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr), b,
+                           heads, heads_kv, m, kv_len, (int)D, qs, ks, vs, os, scale, causal != 0,
+                           input_pos, stream);
+}
+
 }  // namespace
 
 int b200tile_launch(const char* kernel, const char* const* generics, int n_generics,
@@ -316,6 +480,9 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
   if (is_gemm_name(kernel))
     return launch_gemm_generic(kernel, generics, n_generics, opts, params, n_params, grid,
                                cu_stream, true);
+  if (!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal"))
+    return launch_fmha_generic(kernel, generics, n_generics, opts, params, n_params, grid,
+                               cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -324,6 +491,9 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
   if (!kernel) return set_error(B200TILE_ERR_INVALID, "prepare: kernel name is null");
   if (is_gemm_name(kernel))
     return launch_gemm_generic(kernel, generics, n_generics, opts, nullptr, 0, nullptr, nullptr,
+                               false);
+  if (!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal"))
+    return launch_fmha_generic(kernel, generics, n_generics, opts, nullptr, 0, nullptr, nullptr,
                                false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }

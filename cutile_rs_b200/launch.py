@@ -1,0 +1,257 @@
+"""Kernel launchers: the Python mirror of the macro-generated launcher structs.
+
+A launcher is a lazy operation (the ``DeviceOp`` idea, cuda-async/src/device_operation.rs:185-385):
+building it validates nothing and touches no device; ``.sync()/.sync_on()/.async_on()`` run the
+generated ``execute`` sequence (cutile-macro/src/kernel_launcher_generator.rs:819-987) -- resolve
+generics, infer and validate the grid, marshal the flattened parameter array -- and then make ONE
+call into the C ABI (``b200tile_launch``) where the reference would JIT-compile and call
+``cuLaunchKernel``.  Outputs come back in signature order, the same objects that went in
+(:670-687).
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_char_p, c_float, c_int32, c_uint, c_uint64, c_void_p
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple, Union
+
+import torch
+
+from . import _lib
+from .tensor import (Grid, GridBound, KernelLaunchError, MappedLaunchPartition, Partition, Tensor,
+                     infer_launch_grid)
+
+
+@dataclass
+class CompileOptions:
+    """``CompileOptions`` (cutile-compiler/src/hints.rs:94-126); ``None`` = not set."""
+    occupancy: Optional[int] = None
+    num_cta_in_cga: Optional[int] = None
+    max_divisibility: Optional[int] = None
+    num_worker_warps_per_cta: Optional[int] = None
+
+    def to_c(self) -> _lib.CompileOptionsC:
+        f = lambda v: -1 if v is None else int(v)
+        return _lib.CompileOptionsC(f(self.occupancy), f(self.num_cta_in_cga),
+                                    f(self.max_divisibility), f(self.num_worker_warps_per_cta))
+
+
+Output = Union[Partition, MappedLaunchPartition]
+Arg = Union[Partition, MappedLaunchPartition, Tensor, int, float]
+
+
+class _ParamArray:
+    """Owns the C values behind a ``void*[]`` kernel parameter array."""
+
+    def __init__(self):
+        self._keep = []
+
+    def push(self, kind: str, value) -> None:
+        ctype = {"u64": c_uint64, "i32": c_int32, "f32": c_float}[kind]
+        self._keep.append(ctype(value))
+
+    def as_c(self):
+        arr = (c_void_p * len(self._keep))()
+        for i, v in enumerate(self._keep):
+            arr[i] = ctypes.cast(ctypes.pointer(v), c_void_p)
+        return arr, len(self._keep)
+
+
+class KernelLauncher:
+    """One kernel invocation being built (``TileKernel`` trait, cutile/src/tile_kernel.rs:1036-1106)."""
+
+    kernel_name = ""
+
+    def __init__(self, args: Sequence[Arg]):
+        self.args = list(args)
+        self._generics: Optional[List[str]] = None
+        self._grid: Grid = (0, 0, 0)
+        self._opts: Optional[CompileOptions] = None
+        self._compile_only = False
+
+    # ---- builder methods (cutile-macro/src/_module.rs:901-923) ----
+    def generics(self, generics: Sequence[str]) -> "KernelLauncher":
+        self._generics = [str(g) for g in generics]
+        return self
+
+    def grid(self, grid: Grid) -> "KernelLauncher":
+        self._grid = tuple(int(g) for g in grid)
+        return self
+
+    const_grid = grid
+
+    def compile_options(self, opts: CompileOptions) -> "KernelLauncher":
+        self._opts = opts
+        return self
+
+    # ---- to be provided per kernel ----
+    def infer_generics(self) -> List[str]:
+        raise KernelLaunchError(f"{self.kernel_name}: generics must be given explicitly")
+
+    # ---- execution ----
+    def _resolved_generics(self) -> List[str]:
+        return self._generics if self._generics is not None else self.infer_generics()
+
+    def _bounds(self) -> List[GridBound]:
+        return [a.grid_bound() for a in self.args if isinstance(a, (Partition, MappedLaunchPartition))]
+
+    def _marshal(self) -> _ParamArray:
+        pa = _ParamArray()
+        for a in self.args:
+            if isinstance(a, (Partition, MappedLaunchPartition, Tensor)):
+                for kind, v in a.kernel_args():
+                    pa.push(kind, v)
+            elif isinstance(a, bool):
+                pa.push("i32", int(a))
+            elif isinstance(a, int):
+                pa.push("i32", a)
+            elif isinstance(a, float):
+                pa.push("f32", a)
+            else:
+                raise KernelLaunchError(f"{self.kernel_name}: unsupported argument {type(a)}")
+        return pa
+
+    def compile(self) -> "KernelLauncher":
+        """Warm-up without launching (the ``.compile()`` path, cutile-macro/src/_module.rs:852-866)."""
+        lib = _lib.load()
+        gens = self._resolved_generics()
+        garr = (c_char_p * len(gens))(*[g.encode() for g in gens])
+        opts = self._opts.to_c() if self._opts else None
+        rc = lib.b200tile_prepare(self.kernel_name.encode(), garr, len(gens),
+                                  ctypes.byref(opts) if opts else None)
+        if rc:
+            raise KernelLaunchError(lib.b200tile_last_error().decode())
+        return self
+
+    def execute(self, stream: torch.cuda.Stream) -> Tuple:
+        """Enqueues the kernel on ``stream`` without synchronising."""
+        lib = _lib.load()
+        gens = self._resolved_generics()
+        grid = infer_launch_grid(self._grid, self._bounds())
+        pa = self._marshal()
+        params, n_params = pa.as_c()
+        garr = (c_char_p * len(gens))(*[g.encode() for g in gens])
+        cgrid = (c_uint * 3)(*grid)
+        opts = self._opts.to_c() if self._opts else None
+        rc = lib.b200tile_launch(self.kernel_name.encode(), garr, len(gens),
+                                 ctypes.byref(opts) if opts else None, params, n_params, cgrid,
+                                 c_void_p(stream.cuda_stream))
+        if rc:
+            raise KernelLaunchError(lib.b200tile_last_error().decode())
+        return self._recover()
+
+    def _recover(self) -> Tuple:
+        # a mapped output is returned as its plain partition (cutile/src/tensor.rs:1945-1956)
+        return tuple(a.partition if isinstance(a, MappedLaunchPartition) else a for a in self.args)
+
+    def sync_on(self, stream: torch.cuda.Stream) -> Tuple:
+        out = self.execute(stream)
+        stream.synchronize()
+        return out
+
+    def sync(self) -> Tuple:
+        return self.sync_on(torch.cuda.current_stream())
+
+    def async_on(self, stream: torch.cuda.Stream) -> Tuple:
+        """Enqueue only; the caller orders later work on the same stream (``unsafe async_on``)."""
+        return self.execute(stream)
+
+    def graph_on(self, stream: torch.cuda.Stream) -> "CudaGraph":
+        return CudaGraph.capture(self, stream)
+
+
+class CudaGraph:
+    """Capture once, replay many times (cuda-async/src/cuda_graph.rs:61-137,179-208)."""
+
+    def __init__(self, graph: torch.cuda.CUDAGraph, output: Tuple, stream: torch.cuda.Stream):
+        self._graph = graph
+        self._output = output
+        self._stream = stream
+
+    @staticmethod
+    def capture(op: KernelLauncher, stream: torch.cuda.Stream) -> "CudaGraph":
+        _lib.load()
+        g = torch.cuda.CUDAGraph()
+        stream.synchronize()
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="relaxed"):
+            out = op.execute(torch.cuda.current_stream())
+        return CudaGraph(g, out, stream)
+
+    @staticmethod
+    def scope(stream: torch.cuda.Stream, record) -> "CudaGraph":
+        """``CudaGraph::scope(&stream, |s| s.record(op))`` (cuda_graph.rs:400-505): ``record`` gets a
+        function that enqueues launchers into the capture."""
+        _lib.load()
+        g = torch.cuda.CUDAGraph()
+        outs = []
+        stream.synchronize()
+        with torch.cuda.graph(g, stream=stream, capture_error_mode="relaxed"):
+            cur = torch.cuda.current_stream()
+            record(lambda op: outs.append(op.execute(cur)) or outs[-1])
+        return CudaGraph(g, tuple(outs), stream)
+
+    def launch(self) -> "CudaGraph":
+        self._graph.replay()
+        return self
+
+    def sync(self) -> "CudaGraph":
+        torch.cuda.current_stream().synchronize()
+        return self
+
+    def take_output(self) -> Tuple:
+        return self._output
+
+
+# ---------------------------------------------------------------------------------------------
+# Concrete launchers
+# ---------------------------------------------------------------------------------------------
+class _GemmLauncher(KernelLauncher):
+    """z[M,N] = x[M,K] . y[K,N]  (generics [T, BM, BN, BK, ...])."""
+
+    def infer_generics(self) -> List[str]:
+        z = self.args[0]
+        bm, bn = z.partition_shape[-2], z.partition_shape[-1]
+        return [z.dtype_str(), str(bm), str(bn), "64" if z.dtype_str() != "f32" else "16"]
+
+
+class Gemm(_GemmLauncher):
+    kernel_name = "gemm"
+
+
+class GemmAcc(_GemmLauncher):
+    kernel_name = "gemm_acc"
+
+
+class GemmPersistent(_GemmLauncher):
+    kernel_name = "gemm_persistent"
+
+    def infer_generics(self) -> List[str]:
+        z = self.args[0]
+        base = super().infer_generics()
+        ms = z.map_shape if isinstance(z, MappedLaunchPartition) else [8, 1]
+        return base + [str(ms[0]), str(ms[1] if len(ms) > 1 else 1)]
+
+
+class BatchMatmul(_GemmLauncher):
+    kernel_name = "batch_matmul"
+
+
+def gemm(z: Output, x: Tensor, y: Tensor, k: Optional[int] = None) -> Gemm:
+    """Non-persistent form: one [BM,BN] tile per tile-block, accumulator starts at zero
+    (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:74-96)."""
+    return Gemm([z, x, y] + ([int(k)] if k is not None else []))
+
+
+def gemm_acc(z: Output, x: Tensor, y: Tensor) -> GemmAcc:
+    """z += x . y, z loaded as the initial accumulator (cutile-examples/examples/gemm.rs:20-36)."""
+    return GemmAcc([z, x, y])
+
+
+def gemm_persistent(z: MappedLaunchPartition, x: Tensor, y: Tensor) -> GemmPersistent:
+    """Persistent mapped form (main.rs:98-132; cutile-examples/examples/persistent_gemm.rs:26-58)."""
+    return GemmPersistent([z, x, y])
+
+
+def batch_matmul(z: Output, x: Tensor, y: Tensor) -> BatchMatmul:
+    """Per-batch GEMM, grid (batch, M/BM, N/BN) (cutile-examples/examples/batch_matmul.rs:17-43)."""
+    return BatchMatmul([z, x, y])

@@ -92,7 +92,8 @@ B200TILE_API int b200tile_query_configs(const char* kernel, const char* dtype, b
 /* Drop-in for the two calls the macro-generated launcher makes per launch: `jit_compile` and
  * `AsyncKernelLaunch::execute` (cutile-macro/src/kernel_launcher_generator.rs:911-923,958-975;
  * cuda-async/src/launch.rs:91-113).
- *   kernel    entry name without the `_entry` suffix: "gemm", "gemm_persistent", "batch_matmul"
+ *   kernel    entry name without the `_entry` suffix: "gemm", "gemm_acc", "gemm_persistent",
+ *             "batch_matmul", "fmha", "fmha_prefill_causal"
  *   generics  the launcher's `Vec<String>` (dtype names from cuda-core/src/dtype.rs:147-168,
  *             integers in decimal)
  *   params    the reference's flattened kernel parameter array, one pointer per value, in
@@ -130,6 +131,26 @@ B200TILE_API int b200tile_gemm(const char* dtype, int b_layout, const void* a, c
                   int batch, int m, int n, int k, int64_t lda, int64_t ldb, int64_t ldc,
                   int64_t stride_a, int64_t stride_b, int64_t stride_c, int accumulate, int config,
                   int group_size_m, int num_programs, void* cu_stream);
+
+/* out = softmax(qk_scale * Q K^T + mask) V, one query tile per tile-block, online softmax with
+ * fp32 statistics, probabilities rounded to the 16-bit input type before P.V.
+ * Replaces `fmha_prefill_causal` (cutile-kernels/src/attention.rs:232-392), the benchmark kernels
+ * `fmha` (cutile-benchmarks/benches/fmha.rs:20-146, fmha_causal.rs:20-136) and the example
+ * kernels (cutile-examples/examples/flash_attention.rs:20-136, flash_attention_causal.rs:19-134).
+ *   dtype      "bf16" or "f16" (tensor cores; head_dim 64 or 128)
+ *   q          query tensor; element (b, h, i, d) at q + (b*heads + h)*q_strides[0] +
+ *              i*q_strides[1] + d  -- covers both (b,h,s,d) and [q_len, heads, D] layouts
+ *   k, v       same addressing with heads_kv; kv head = h / (heads / heads_kv) (GQA)
+ *   out        same addressing as q
+ *   causal     0/1; key j is visible to query i iff j <= i + input_pos (the diagonal included,
+ *              attention.rs:348; flash_attention_causal.rs:176)
+ * Strides are in ELEMENTS; the head vector is contiguous. */
+B200TILE_API int b200tile_fmha_fwd(const char* dtype, const void* q, const void* k, const void* v,
+                                   void* out, int batch, int heads, int heads_kv, int q_len,
+                                   int kv_len, int head_dim, const int64_t q_strides[2],
+                                   const int64_t k_strides[2], const int64_t v_strides[2],
+                                   const int64_t o_strides[2], float qk_scale, int causal,
+                                   int input_pos, void* cu_stream);
 
 #ifdef __cplusplus
 }

@@ -18,11 +18,45 @@
 #include <stdlib.h>
 #include <string.h>
 
-#if defined(_OPENMP)
-#include <omp.h>
-#endif
+#include <pthread.h>
+#include <unistd.h>
 
 #define ORACLE_API __attribute__((visibility("default")))
+
+/* Minimal static-schedule parallel-for over [0, count) on POSIX threads. */
+typedef void (*oracle_range_fn)(void* ctx, int64_t begin, int64_t end);
+typedef struct { oracle_range_fn fn; void* ctx; int64_t begin, end; } oracle_task;
+static void* oracle_task_main(void* p) {
+  oracle_task* t = (oracle_task*)p;
+  t->fn(t->ctx, t->begin, t->end);
+  return NULL;
+}
+ORACLE_API int oracle_max_threads(void) {
+  long n = sysconf(_SC_NPROCESSORS_ONLN);
+  return n < 1 ? 1 : (n > 256 ? 256 : (int)n);
+}
+static int oracle_parallel_for(oracle_range_fn fn, void* ctx, int64_t count, int threads) {
+  if (threads <= 0) threads = oracle_max_threads();
+  if (threads > 256) threads = 256;
+  if ((int64_t)threads > count) threads = count > 0 ? (int)count : 1;
+  if (threads <= 1) { fn(ctx, 0, count); return 1; }
+  pthread_t tid[256];
+  oracle_task task[256];
+  int started = 0;
+  for (int t = 0; t < threads; ++t) {
+    task[t].fn = fn; task[t].ctx = ctx;
+    task[t].begin = count * t / threads; task[t].end = count * (t + 1) / threads;
+    if (t == threads - 1 || pthread_create(&tid[t], NULL, oracle_task_main, &task[t]) != 0) {
+      /* last chunk (or a failed create) runs on the calling thread */
+      task[t].end = count;
+      fn(ctx, task[t].begin, task[t].end);
+      break;
+    }
+    ++started;
+  }
+  for (int t = 0; t < started; ++t) pthread_join(tid[t], NULL);
+  return started + 1;
+}
 
 /* ------------------------------------------------------------------------------------------
  * GEMM: cutile-examples/examples/persistent_gemm.rs:140-152 (`cpu_gemm`)
@@ -49,24 +83,16 @@ ORACLE_API void oracle_cpu_gemm(const float* x, const float* y, float* z, int64_
 
 /* Same arithmetic, rows spread over `threads` host threads (each output element is still one
  * sequential ascending-k sum, so results are bit-identical to the single-thread form). */
+typedef struct { const float *x, *y; float* z; int64_t m, n, k, row0; float alpha; } gemm_ctx;
+static void gemm_range(void* p, int64_t b, int64_t e) {
+  gemm_ctx* c = (gemm_ctx*)p;
+  oracle_cpu_gemm_rows(c->x, c->y, c->z, c->m, c->n, c->k, c->row0 + b, c->row0 + e);
+}
 ORACLE_API int oracle_cpu_gemm_rows_mt(const float* x, const float* y, float* z, int64_t m,
                                        int64_t n, int64_t k, int64_t row0, int64_t row1,
                                        int threads) {
-  int used = 1;
-#if defined(_OPENMP)
-  if (threads > 0) omp_set_num_threads(threads);
-#pragma omp parallel
-  {
-#pragma omp single
-    used = omp_get_num_threads();
-#pragma omp for schedule(static)
-    for (int64_t row = row0; row < row1; ++row) oracle_cpu_gemm_rows(x, y, z, m, n, k, row, row + 1);
-  }
-#else
-  (void)threads;
-  oracle_cpu_gemm_rows(x, y, z, m, n, k, row0, row1);
-#endif
-  return used;
+  gemm_ctx c = {x, y, z, m, n, k, row0, 1.0f};
+  return oracle_parallel_for(gemm_range, &c, row1 - row0, threads);
 }
 
 /* "NT" form used by the block-scaled linear kernels (cutile-examples/examples/nvfp4.rs:20-33:
@@ -84,25 +110,15 @@ ORACLE_API void oracle_cpu_gemm_nt_rows(const float* x, const float* y, float* z
   }
 }
 
+static void gemm_nt_range(void* p, int64_t b, int64_t e) {
+  gemm_ctx* c = (gemm_ctx*)p;
+  oracle_cpu_gemm_nt_rows(c->x, c->y, c->z, c->m, c->n, c->k, c->alpha, c->row0 + b, c->row0 + e);
+}
 ORACLE_API int oracle_cpu_gemm_nt_rows_mt(const float* x, const float* y, float* z, int64_t m,
                                           int64_t n, int64_t k, float alpha, int64_t row0,
                                           int64_t row1, int threads) {
-  int used = 1;
-#if defined(_OPENMP)
-  if (threads > 0) omp_set_num_threads(threads);
-#pragma omp parallel
-  {
-#pragma omp single
-    used = omp_get_num_threads();
-#pragma omp for schedule(static)
-    for (int64_t row = row0; row < row1; ++row)
-      oracle_cpu_gemm_nt_rows(x, y, z, m, n, k, alpha, row, row + 1);
-  }
-#else
-  (void)threads;
-  oracle_cpu_gemm_nt_rows(x, y, z, m, n, k, alpha, row0, row1);
-#endif
-  return used;
+  gemm_ctx c = {x, y, z, m, n, k, row0, alpha};
+  return oracle_parallel_for(gemm_nt_range, &c, row1 - row0, threads);
 }
 
 /* ------------------------------------------------------------------------------------------
@@ -148,41 +164,30 @@ static void fmha_one_row(const float* q, const float* k, const float* v, float* 
   }
 }
 
+typedef struct {
+  const float *q, *k, *v; float* out;
+  int64_t hsz, hkv, m, dsz, input_pos, group, bh0, i0, rows; float qk_scale; int causal;
+} fmha_ctx;
+static void fmha_range(void* p, int64_t b, int64_t e) {
+  fmha_ctx* c = (fmha_ctx*)p;
+  float* scores = (float*)malloc(sizeof(float) * (size_t)c->m);
+  if (!scores) return;
+  for (int64_t w = b; w < e; ++w) {
+    const int64_t bh = c->bh0 + w / c->rows, i = c->i0 + w % c->rows;
+    fmha_one_row(c->q, c->k, c->v, c->out, scores, bh / c->hsz, bh % c->hsz, i, c->hsz, c->hkv,
+                 c->m, c->dsz, c->qk_scale, c->input_pos, c->group, c->causal);
+  }
+  free(scores);
+}
 ORACLE_API int oracle_fmha_ref_cpu_slab(const float* q, const float* k, const float* v, float* out,
                                         int64_t bsz, int64_t hsz, int64_t hkv, int64_t m,
                                         int64_t dsz, float qk_scale, int64_t input_pos,
                                         int64_t query_group_size, int causal, int64_t bh0,
                                         int64_t bh1, int64_t i0, int64_t i1, int threads) {
   (void)bsz;
-  int used = 1;
-  const int64_t rows = i1 - i0;
-  const int64_t work = (bh1 - bh0) * rows;
-#if defined(_OPENMP)
-  if (threads > 0) omp_set_num_threads(threads);
-#pragma omp parallel
-  {
-#pragma omp single
-    used = omp_get_num_threads();
-    float* scores = (float*)malloc(sizeof(float) * (size_t)m);
-#pragma omp for schedule(static)
-    for (int64_t w = 0; w < work; ++w) {
-      const int64_t bh = bh0 + w / rows, i = i0 + w % rows;
-      fmha_one_row(q, k, v, out, scores, bh / hsz, bh % hsz, i, hsz, hkv, m, dsz, qk_scale,
-                   input_pos, query_group_size, causal);
-    }
-    free(scores);
-  }
-#else
-  (void)threads;
-  float* scores = (float*)malloc(sizeof(float) * (size_t)m);
-  for (int64_t w = 0; w < work; ++w) {
-    const int64_t bh = bh0 + w / rows, i = i0 + w % rows;
-    fmha_one_row(q, k, v, out, scores, bh / hsz, bh % hsz, i, hsz, hkv, m, dsz, qk_scale, input_pos,
-                 query_group_size, causal);
-  }
-  free(scores);
-#endif
-  return used;
+  fmha_ctx c = {q, k, v, out, hsz, hkv, m, dsz, input_pos, query_group_size, bh0, i0, i1 - i0,
+                qk_scale, causal};
+  return oracle_parallel_for(fmha_range, &c, (bh1 - bh0) * (i1 - i0), threads);
 }
 
 ORACLE_API void oracle_fmha_ref_cpu(const float* q, const float* k, const float* v, float* out,
@@ -390,12 +395,4 @@ ORACLE_API void oracle_swizzled_bid(int tile_id, int num_bid_m, int num_bid_n, i
   const int actual = remaining_m < group_size_m ? remaining_m : group_size_m;
   *bid_m = first_bid_m + (tile_id % actual);
   *bid_n = (tile_id % num_bid_in_group) / actual;
-}
-
-ORACLE_API int oracle_max_threads(void) {
-#if defined(_OPENMP)
-  return omp_get_max_threads();
-#else
-  return 1;
-#endif
 }

@@ -1,0 +1,215 @@
+"""TEST INFRASTRUCTURE -- ctypes/numpy front end of ``oracle/oracle.c`` (the CPU restatement of
+the reference's host-side checks).  Only tests, the smoke check and the benchmark's CPU-baseline /
+reference arms may import this module; the product package never does.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from ctypes import POINTER, c_float, c_int, c_int64, c_uint8, c_uint16, c_uint32, c_void_p
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "liboracle.so")
+_lib = None
+
+
+def build(force: bool = False) -> str:
+    """Compiles oracle.c with the committed Makefile (gcc only)."""
+    src = os.path.join(_HERE, "oracle.c")
+    if force or not os.path.exists(LIB_PATH) or os.path.getmtime(src) > os.path.getmtime(LIB_PATH):
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return LIB_PATH
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            build()
+        L = ctypes.CDLL(LIB_PATH)
+        fp, u8p, u16p = POINTER(c_float), POINTER(c_uint8), POINTER(c_uint16)
+        i64 = c_int64
+        sig = {
+            "oracle_cpu_gemm": (None, [fp, fp, fp, i64, i64, i64]),
+            "oracle_cpu_gemm_rows": (None, [fp, fp, fp, i64, i64, i64, i64, i64]),
+            "oracle_cpu_gemm_rows_mt": (c_int, [fp, fp, fp, i64, i64, i64, i64, i64, c_int]),
+            "oracle_cpu_gemm_nt_rows": (None, [fp, fp, fp, i64, i64, i64, c_float, i64, i64]),
+            "oracle_cpu_gemm_nt_rows_mt": (c_int, [fp, fp, fp, i64, i64, i64, c_float, i64, i64, c_int]),
+            "oracle_fmha_ref_cpu": (None, [fp, fp, fp, fp, i64, i64, i64, i64, i64, c_float, i64, i64, c_int]),
+            "oracle_fmha_ref_cpu_slab": (c_int, [fp, fp, fp, fp, i64, i64, i64, i64, i64, c_float, i64,
+                                                 i64, c_int, i64, i64, i64, i64, c_int]),
+            "oracle_f32_to_bf16": (c_uint16, [c_float]),
+            "oracle_bf16_to_f32": (c_float, [c_uint16]),
+            "oracle_f32_to_bf16_array": (None, [fp, u16p, i64]),
+            "oracle_bf16_to_f32_array": (None, [u16p, fp, i64]),
+            "oracle_e4m3_to_f32": (c_float, [c_uint8]),
+            "oracle_f32_to_e4m3": (c_uint8, [c_float]),
+            "oracle_e5m2_to_f32": (c_float, [c_uint8]),
+            "oracle_e8m0_to_f32": (c_float, [c_uint8]),
+            "oracle_e2m1_to_f32": (c_float, [c_uint8]),
+            "oracle_f32_to_e2m1": (c_uint8, [c_float]),
+            "oracle_pack_e2m1x2": (c_uint8, [c_uint8, c_uint8]),
+            "oracle_quant_fp8_block": (None, [fp, i64, i64, i64, i64, u8p, fp]),
+            "oracle_dequant_fp8_block": (None, [u8p, fp, i64, i64, i64, i64, fp]),
+            "oracle_quant_nvfp4": (c_float, [fp, i64, i64, u8p, u8p]),
+            "oracle_dequant_nvfp4": (None, [u8p, u8p, i64, i64, fp]),
+            "oracle_persistent_num_programs": (c_uint32, [i64, i64, c_int, c_int, c_int, c_int, c_int]),
+            "oracle_swizzled_bid": (None, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
+            "oracle_max_threads": (c_int, []),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a: np.ndarray, ct):
+    return a.ctypes.data_as(POINTER(ct))
+
+
+def max_threads() -> int:
+    return int(lib().oracle_max_threads())
+
+
+# ---- GEMM -------------------------------------------------------------------------------
+def cpu_gemm(x, y, rows=None, threads: int = 1) -> np.ndarray:
+    """z = x[M,K] . y[K,N]; `rows=(r0,r1)` computes only that slab (other rows stay zero)."""
+    x, y = _f32(x), _f32(y)
+    m, k = x.shape
+    k2, n = y.shape
+    assert k == k2
+    z = np.zeros((m, n), dtype=np.float32)
+    r0, r1 = rows if rows is not None else (0, m)
+    lib().oracle_cpu_gemm_rows_mt(_p(x, c_float), _p(y, c_float), _p(z, c_float), m, n, k, r0, r1,
+                                  threads)
+    return z
+
+
+def cpu_gemm_nt(x, y, alpha: float = 1.0, rows=None, threads: int = 1) -> np.ndarray:
+    """z = alpha * x[M,K] . y[N,K]^T."""
+    x, y = _f32(x), _f32(y)
+    m, k = x.shape
+    n, k2 = y.shape
+    assert k == k2
+    z = np.zeros((m, n), dtype=np.float32)
+    r0, r1 = rows if rows is not None else (0, m)
+    lib().oracle_cpu_gemm_nt_rows_mt(_p(x, c_float), _p(y, c_float), _p(z, c_float), m, n, k,
+                                     alpha, r0, r1, threads)
+    return z
+
+
+# ---- attention --------------------------------------------------------------------------
+def fmha_ref_cpu(q, k, v, qk_scale: float, input_pos: int = 0, query_group_size: int = 1,
+                 causal: bool = False, bh=None, rows=None, threads: int = 1) -> np.ndarray:
+    """q (b,h,m,d), k/v (b,hkv,m,d) -> out (b,h,m,d); slabs outside (bh, rows) stay zero."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    b, h, m, d = q.shape
+    hkv = k.shape[1]
+    out = np.zeros_like(q)
+    bh0, bh1 = bh if bh is not None else (0, b * h)
+    i0, i1 = rows if rows is not None else (0, m)
+    lib().oracle_fmha_ref_cpu_slab(_p(q, c_float), _p(k, c_float), _p(v, c_float),
+                                   _p(out, c_float), b, h, hkv, m, d, qk_scale, input_pos,
+                                   query_group_size, int(causal), bh0, bh1, i0, i1, threads)
+    return out
+
+
+# ---- codecs -----------------------------------------------------------------------------
+def f32_to_bf16_bits(a) -> np.ndarray:
+    a = _f32(a)
+    out = np.empty(a.shape, dtype=np.uint16)
+    lib().oracle_f32_to_bf16_array(_p(a, c_float), _p(out, c_uint16), a.size)
+    return out
+
+
+def bf16_bits_to_f32(bits) -> np.ndarray:
+    bits = np.ascontiguousarray(bits, dtype=np.uint16)
+    out = np.empty(bits.shape, dtype=np.float32)
+    lib().oracle_bf16_to_f32_array(_p(bits, c_uint16), _p(out, c_float), bits.size)
+    return out
+
+
+def round_bf16(a) -> np.ndarray:
+    return bf16_bits_to_f32(f32_to_bf16_bits(a))
+
+
+def e4m3_table() -> np.ndarray:
+    return np.array([lib().oracle_e4m3_to_f32(i) for i in range(256)], dtype=np.float32)
+
+
+def e2m1_table() -> np.ndarray:
+    return np.array([lib().oracle_e2m1_to_f32(i) for i in range(16)], dtype=np.float32)
+
+
+def quant_fp8_block(x, block_r: int, block_c: int):
+    x = _f32(x)
+    r, c = x.shape
+    q = np.empty((r, c), dtype=np.uint8)
+    s = np.empty((-(-r // block_r), -(-c // block_c)), dtype=np.float32)
+    lib().oracle_quant_fp8_block(_p(x, c_float), r, c, block_r, block_c, _p(q, c_uint8),
+                                 _p(s, c_float))
+    return q, s
+
+
+def dequant_fp8_block(q, s, block_r: int, block_c: int) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    s = _f32(s)
+    r, c = q.shape
+    out = np.empty((r, c), dtype=np.float32)
+    lib().oracle_dequant_fp8_block(_p(q, c_uint8), _p(s, c_float), r, c, block_r, block_c,
+                                   _p(out, c_float))
+    return out
+
+
+def quant_nvfp4(x):
+    """-> (packed [R, C/2] u8, scales [R, C/16] u8 (e4m3 bits), global scale g)."""
+    x = _f32(x)
+    r, c = x.shape
+    assert c % 16 == 0
+    packed = np.empty((r, c // 2), dtype=np.uint8)
+    scales = np.empty((r, c // 16), dtype=np.uint8)
+    g = lib().oracle_quant_nvfp4(_p(x, c_float), r, c, _p(packed, c_uint8), _p(scales, c_uint8))
+    return packed, scales, float(g)
+
+
+def dequant_nvfp4(packed, scales) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    r, c2 = packed.shape
+    out = np.empty((r, c2 * 2), dtype=np.float32)
+    lib().oracle_dequant_nvfp4(_p(packed, c_uint8), _p(scales, c_uint8), r, c2 * 2,
+                               _p(out, c_float))
+    return out
+
+
+# ---- scheduling -------------------------------------------------------------------------
+def persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy) -> int:
+    return int(lib().oracle_persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy))
+
+
+def swizzled_bid(tile_id, num_bid_m, num_bid_n, group_size_m):
+    a, b = c_int(), c_int()
+    lib().oracle_swizzled_bid(tile_id, num_bid_m, num_bid_n, group_size_m, ctypes.byref(a),
+                              ctypes.byref(b))
+    return a.value, b.value
+
+
+# ---- error metrics ----------------------------------------------------------------------
+def rel_frobenius(got, ref) -> float:
+    got = np.asarray(got, dtype=np.float64)
+    ref = np.asarray(ref, dtype=np.float64)
+    return float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30))
+
+
+def max_abs(got, ref) -> float:
+    return float(np.max(np.abs(np.asarray(got, dtype=np.float64) - np.asarray(ref, dtype=np.float64))))
