@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction hot path on N B200s of one node.
+
+Headline workload (BASELINE config 1): bf16 GEMM M=N=K=8192, A[M,K] and B[K,N] ~ N(0,1)/sqrt(K)
+rounded to bf16, fp32 accumulation, bf16 output.  A "step" is one GEMM launch.  With N>1 GPUs the
+weight columns are split (rank r owns B[:, r*N/G:(r+1)*N/G] and the matching columns of C, A is
+replicated), so the total work is fixed ("strong" scaling) and no data-path collective runs.
+
+`value` is the whole-job TFLOP/s with operands resident in HBM; `e2e` is the same metric through
+the public launcher API with HOST buffers (pinned host -> device copies of A and B and a
+device -> host read of C inside the timed region).  `roofline` compares the kernel with the
+measured cuBLAS bf16 peak of this pool; `cpu_baseline` times the CPU oracle (a port of the
+reference's `cpu_gemm`) on a bounded slab.  `extra` reports FMHA forward (BASELINE config 2,
+8 x 32 x 4096 x 128, sharded by batch x head) measured the same way.
+
+`--impl reference` times the reference's own CPU implementation of the path (the oracle port of
+`cpu_gemm`; the reference's GPU path needs a Rust toolchain and NVIDIA's `tileiras`, neither of
+which exists here) on all host threads, each step a bounded row slab of the same GEMM.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "TFLOP/s (GEMM 8192^3 bf16, fp32 accumulate)"
+M = N = K = 8192
+FALLBACK_BF16_TFLOPS = 1590.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tc_kernel launch at 8192^3, from the ncu
+# capture summarised in profiles/gemm_bf16_8192.md (None until a capture exists).
+GEMM_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            d = json.load(fh)
+        return float(d["bf16_tflops"]), float(d.get("hbm_gbs", 0.0)), "measured"
+    except (OSError, ValueError, KeyError):
+        return FALLBACK_BF16_TFLOPS, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.monotonic(), line.strip()))
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for _, l in self.lines]
+        for line in rows:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU arms (the only place besides tests/smoke where the oracle runs)
+# ------------------------------------------------------------------------------------------
+def _cpu_slab_inputs(rows: int):
+    import torch
+    from cutile_rs_b200 import workloads
+    g = torch.Generator().manual_seed(workloads.SEED_BASE + 1)
+    s = 1.0 / math.sqrt(K)
+    a = (torch.randn(rows, K, generator=g) * s).to(torch.bfloat16).float().numpy()
+    b = (torch.randn(K, N, generator=g) * s).to(torch.bfloat16).float().numpy()
+    return a, b
+
+
+def cpu_gemm_rate(target_seconds: float, threads: int):
+    """Times the oracle's cpu_gemm on a row slab of the 8192^3 problem sized to ~target_seconds."""
+    from oracle import oracle
+    threads = threads or oracle.max_threads()
+    a, b = _cpu_slab_inputs(max(threads, 8) * 8)
+    probe_rows = max(threads, 8)
+    t0 = time.perf_counter()
+    oracle.cpu_gemm(a[:probe_rows], b, threads=threads)
+    per_row = (time.perf_counter() - t0) / probe_rows
+    rows = int(min(max(target_seconds / max(per_row, 1e-9), probe_rows), a.shape[0]))
+    rows -= rows % max(threads, 1) if rows >= threads else 0
+    rows = max(rows, 1)
+    t0 = time.perf_counter()
+    oracle.cpu_gemm(a[:rows], b, threads=threads)
+    dt = time.perf_counter() - t0
+    return {"tflops": 2.0 * rows * N * K / dt / 1e12, "rows": rows, "seconds": dt, "threads": threads}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    from oracle import oracle
+    threads = oracle.max_threads()
+    steps, warmup = args.steps, args.warmup
+    budget = 150.0 / max(steps + warmup, 1)
+    a, b = _cpu_slab_inputs(max(threads, 8) * 4)
+    probe_rows = max(threads, 8)
+    t0 = time.perf_counter()
+    oracle.cpu_gemm(a[:probe_rows], b, threads=threads)
+    per_row = (time.perf_counter() - t0) / probe_rows
+    rows = int(min(max(budget / max(per_row, 1e-9), 1), a.shape[0]))
+    if rows >= threads:
+        rows -= rows % threads
+    for _ in range(warmup):
+        oracle.cpu_gemm(a[:rows], b, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.cpu_gemm(a[:rows], b, threads=threads)
+    dt = time.perf_counter() - t0
+    tflops = 2.0 * rows * N * K * steps / dt / 1e12
+    sample = f"rows [0,{rows}) of the 8192^3 bf16-rounded GEMM per step, naive f32 triple loop"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warmup, "ms_per_step": dt / steps * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "gemm_bf16_8192x8192x8192", "layout": "A[M,K] B[K,N] row-major",
+                   "note": "reference's host-side cpu_gemm (oracle port) on host cores; the "
+                           "reference's GPU path cannot be built here (no Rust toolchain, no tileiras)"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+# ------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    from cutile_rs_b200 import _lib, api, launch, sharding, workloads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; the product has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    _lib.check(lib.b200tile_init(local_rank))
+    stream = torch.cuda.current_stream()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- operands: A replicated, B and C column-sharded; generated once, outside timing ----
+    n0, n1 = sharding.split_range(N, world, rank, 256)
+    a_host, b_host = workloads.gemm_bf16_inputs(M, N, K)
+    b_host = b_host[:, n0:n1].contiguous()
+    n_local = n1 - n0
+    x = api.copy_host_to_device(a_host)
+    y = api.copy_host_to_device(b_host)
+    z = api.zeros([M, n_local], "bf16")
+    # the reference's published configuration: tile 256x256x64 on CTA pairs (num_cta_in_cga = 2)
+    bm, bn = 256, 256
+    generics = ["bf16", str(bm), str(bn), "64"]
+    opts = launch.CompileOptions(num_cta_in_cga=2, occupancy=1)
+
+    def step():
+        launch.gemm(z.partition([bm, bn]), x, y).generics(generics).compile_options(opts).async_on(stream)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    barrier()
+    t_begin = time.monotonic()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    t_end = time.monotonic()
+    total_ms = sharding.max_over_ranks(e0.elapsed_time(e1), dev)
+    clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
+    ms_per_step = total_ms / args.steps
+    flops = workloads.gemm_flops(M, N, K)
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    _lib.check(lib.b200tile_status(stream.cuda_stream, __import__("ctypes").byref(_lib.StatusC())))
+
+    # ---- end to end through the public API with host buffers ----
+    a_pin, b_pin = api.pin(a_host), api.pin(b_host)
+    c_pin = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
+    e2e_steps = max(min(args.steps, 5), 1)
+
+    def e2e_step():
+        xa = api.copy_host_to_device(a_pin, stream=stream)
+        yb = api.copy_host_to_device(b_pin, stream=stream)
+        (zz, _, _) = launch.gemm(z.partition([bm, bn]), xa, yb).generics(generics) \
+            .compile_options(opts).async_on(stream)
+        c_pin.copy_(zz.unpartition().storage, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = sharding.max_over_ranks(e0.elapsed_time(e1), dev) / e2e_steps
+    e2e_value = flops / (e2e_ms * 1e-3) / 1e12
+    h2d = (a_pin.numel() + b_pin.numel()) * 2 * world
+    d2h = c_pin.numel() * 2 * world
+
+    # ---- FMHA forward (config 2), sharded by batch x head, reported as `extra` ----
+    extra = {}
+    if not args.no_fmha:
+        import ctypes
+        B_, H_, S_, D_ = 8, 32, 4096, 128
+        p0, p1 = sharding.split_range(B_ * H_, world, rank, 1)
+        nb = p1 - p0
+        g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 2 + rank)
+        q = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
+        kk = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
+        v = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
+        o = torch.empty_like(q)
+        I2 = ctypes.c_int64 * 2
+        st = I2(S_ * D_, D_)
+        for causal in (False, True):
+            def fstep():
+                _lib.check(lib.b200tile_fmha_fwd(b"bf16", q.data_ptr(), kk.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                                 1, nb, nb, S_, S_, D_, st, st, st, st, 1.0 / math.sqrt(D_),
+                                                 int(causal), 0, stream.cuda_stream))
+            for _ in range(3):
+                fstep()
+            barrier()
+            e0.record(stream)
+            iters = 10
+            for _ in range(iters):
+                fstep()
+            e1.record(stream)
+            barrier()
+            fms = sharding.max_over_ranks(e0.elapsed_time(e1), dev) / iters
+            ftf = workloads.fmha_flops(B_, H_, S_, D_, causal) / (fms * 1e-3) / 1e12
+            extra["fmha_fwd_causal" if causal else "fmha_fwd_noncausal"] = {
+                "tflops": ftf, "tflops_per_gpu": ftf / world, "ms": fms,
+                "config": f"bf16 b{B_} h{H_} s{S_} d{D_}, (b*h) split over {world} GPU(s)"}
+        del q, kk, v, o
+
+    peak, hbm_peak, peak_src = measured_peaks()
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            r = cpu_gemm_rate(12.0, 0)
+            cpu = {"value": r["tflops"], "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
+                   "sample": f"rows [0,{r['rows']}) of the same 8192^3 GEMM ({r['seconds']:.1f} s), "
+                             "oracle port of the reference's cpu_gemm"}
+        per_gpu = value / world
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "gemm_bf16_8192x8192x8192", "layout": "A[M,K] B[K,N] row-major, fp32 acc",
+                       "tile": f"{bm}x{bn}x64 per CTA pair (cta_group::2), 6-stage TMA ring, persistent, grouped-M 8",
+                       "parallelism": f"N-split x{world}" if world > 1 else "single GPU",
+                       "l2": "operands 403 MB per step exceed the 126 MB L2; no flush between steps"},
+            "per_gpu_tflops": per_gpu,
+            "pct_of_nominal_peak_2250": 100.0 * per_gpu / 2250.0,
+            "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
+                         "frac": per_gpu / peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
+                         "peak_source": f"{peak_src} cuBLAS bf16 burst"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+            "gpu_launches": args.steps * world,
+            "clocks": clocks,
+            "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-fmha", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world == 1:
+        # convenience: re-launch under torchrun so that `python bench.py --gpus N` works by itself
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", "29531", os.path.abspath(__file__)] + sys.argv[1:]
+        return subprocess.call(cmd)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -12,6 +12,9 @@
 int b200_gemm_tc_dispatch(int dtype, int b_kmajor, int config, const void* A, const void* B,
                           void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                           int group_m, int max_ctas, cudaStream_t stream);
+int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* B, void* C, int M,
+                            int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int group_m,
+                            int max_ctas, cudaStream_t stream);
 int b200_gemm_f32_dispatch(const float* A, const float* B, float* C, int batch, int M, int N,
                            int K, int64_t lda, int64_t ldb, int64_t ldc, int64_t sa, int64_t sb,
                            int64_t sc, int accumulate, cudaStream_t stream);
@@ -80,6 +83,7 @@ static const b200tile_config kGemmTcConfigs[] = {
     /* id  bm   bn   bk stages cga occ */
     {0, 128, 256, 64, 4, 1, 1},
     {1, 128, 128, 64, 6, 1, 1},
+    {2, 256, 256, 64, 6, 2, 1},
 };
 static const b200tile_config kGemmF32Configs[] = {
     {0, 64, 64, 16, 1, 1, 1},
@@ -111,6 +115,19 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
   }
   for (int i = 0; i < n && i < cap && out; ++i) out[i] = tab[i];
   return n;
+}
+
+// Default configuration: the one with the least (waves x per-SM tile work / relative speed).
+// Relative speeds are the measured ratios of the three kernels at 8192^3.
+static int default_gemm_config(int m, int n) {
+  const b200h::DeviceInfo* di = b200h::device_info();
+  const int64_t sms = di ? di->sm_count : 148;
+  auto cdiv = [](int64_t a, int64_t b) { return (a + b - 1) / b; };
+  const double cost0 = (double)cdiv(cdiv(m, 128) * cdiv(n, 256), sms) * 1.0 / 0.92;
+  const double cost1 = (double)cdiv(cdiv(m, 128) * cdiv(n, 128), sms) * 0.5 / 0.72;
+  const double cost2 = (double)cdiv(cdiv(m, 256) * cdiv(n, 256), sms / 2) * 1.0 / 1.0;
+  if (cost2 <= cost0 && cost2 <= cost1) return 2;
+  return cost0 <= cost1 ? 0 : 1;
 }
 
 // ---------------------------------------------------------------------------
@@ -151,13 +168,16 @@ int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b,
   if (accumulate)
     return set_error(B200TILE_ERR_UNSUPPORTED,
                      "gemm(%s): accumulate-into-C is only provided for f32", dtype);
-  if (config < 0) config = (n <= 128 || ((int64_t)((m + 127) / 128) * ((n + 255) / 256) < 96)) ? 1 : 0;
+  if (config < 0) config = default_gemm_config(m, n);
   for (int bi = 0; bi < batch; ++bi) {
     const char* ab = static_cast<const char*>(a) + (int64_t)bi * stride_a * 2;
     const char* bb = static_cast<const char*>(b) + (int64_t)bi * stride_b * 2;
     char* cb = static_cast<char*>(c) + (int64_t)bi * stride_c * 2;
-    int rc = b200_gemm_tc_dispatch(dt, b_layout ? 1 : 0, config, ab, bb, cb, m, n, k, lda, ldb,
-                                   ldc, group_size_m, num_programs, stream);
+    int rc = config == 2
+                 ? b200_gemm_pair_dispatch(dt, b_layout ? 1 : 0, ab, bb, cb, m, n, k, lda, ldb, ldc,
+                                           group_size_m, num_programs, stream)
+                 : b200_gemm_tc_dispatch(dt, b_layout ? 1 : 0, config, ab, bb, cb, m, n, k, lda,
+                                         ldb, ldc, group_size_m, num_programs, stream);
     if (rc) return rc;
   }
   return B200TILE_OK;
@@ -246,11 +266,11 @@ bool parse_int(const char* s, long* out) {
 // Maps (BM, BN, BK, CompileOptions) onto a precompiled GEMM configuration id.
 int select_gemm_config(const char* dtype, long bm, long bn, long bk,
                        const b200tile_compile_options* opts, int* config) {
+  const int cga = (opts && opts->num_cta_in_cga > 0) ? opts->num_cta_in_cga : 0;
   if (opts) {
-    if (opts->num_cta_in_cga > 1)
+    if (cga > 2)
       return set_error(B200TILE_ERR_UNSUPPORTED,
-                       "gemm: num_cta_in_cga=%d has no precompiled configuration",
-                       opts->num_cta_in_cga);
+                       "gemm: num_cta_in_cga=%d has no precompiled configuration", cga);
     if (opts->occupancy > 1)
       return set_error(B200TILE_ERR_UNSUPPORTED,
                        "gemm: occupancy=%d has no precompiled configuration", opts->occupancy);
@@ -259,8 +279,9 @@ int select_gemm_config(const char* dtype, long bm, long bn, long bk,
     *config = 0;  // the exact-fp32 kernel produces identical results for every tile shape
     return B200TILE_OK;
   }
-  if (bm == 128 && bn == 256 && bk == 64) { *config = 0; return B200TILE_OK; }
-  if (bm == 128 && bn == 128 && bk == 64) { *config = 1; return B200TILE_OK; }
+  if (bm == 256 && bn == 256 && bk == 64 && cga != 1) { *config = 2; return B200TILE_OK; }
+  if (bm == 128 && bn == 256 && bk == 64 && cga != 2) { *config = 0; return B200TILE_OK; }
+  if (bm == 128 && bn == 128 && bk == 64 && cga != 2) { *config = 1; return B200TILE_OK; }
   return set_error(B200TILE_ERR_UNSUPPORTED,
                    "gemm(%s): tile (%ld,%ld,%ld) has no precompiled configuration", dtype, bm, bn,
                    bk);

@@ -76,18 +76,23 @@ struct WaitCtx {
   uint32_t* status;               // global memory, 4 words
 };
 
-#ifndef B200_WAIT_LIMIT
-#define B200_WAIT_LIMIT (1u << 24)
+#ifndef B200_WAIT_LIMIT_CYCLES
+#define B200_WAIT_LIMIT_CYCLES (1ll << 32)  // about two seconds of SM clock
 #endif
 
-// Bounded wait.  Returns true when the phase completed, false when the wait
-// gave up (limit reached or another thread of the CTA already aborted).
+// Bounded wait.  Returns true when the phase completed, false when the wait gave up (time limit
+// reached, or another thread of the CTA already aborted).  On expiry the first waiter records
+// {code, block, site, parity} in the status record; the kernel then unwinds normally.
 __device__ __forceinline__ bool mbar_wait(const WaitCtx& ctx, uint32_t bar, uint32_t parity,
                                           uint32_t site) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t it = 0; it < B200_WAIT_LIMIT; ++it) {
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 0xFF) == 0xFF && *ctx.abort_flag) return false;
+    if ((it & 0x3F) == 0x3F) {
+      if (*ctx.abort_flag) return false;
+      if (clock64() - t0 > B200_WAIT_LIMIT_CYCLES) break;
+    }
   }
   *ctx.abort_flag = 1;
   if (atomicCAS(ctx.status, 0u, (uint32_t)ST_WAIT_TIMEOUT) == 0u) {
@@ -268,6 +273,32 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t saddr, uint32_t cta_rank) 
   uint32_t r;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(cta_rank));
   return r;
+}
+
+// ------------------------------ CTA pairs (cta_group::2) ---------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;"
+               ::: "memory");
+}
+// TMA load issued by either CTA of a pair: the data lands in the ISSUING CTA's shared memory,
+// the transaction bytes are counted on `bar_cluster_addr`, which may be the partner's barrier.
+// One destination CTA per load.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* desc,
+                                                 uint32_t bar_cluster_addr, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(desc), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];"
+               ::"r"(bar_cluster_addr) : "memory");
 }
 
 __device__ __forceinline__ void tmem_wait_ld() {

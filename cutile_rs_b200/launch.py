@@ -255,3 +255,51 @@ def gemm_persistent(z: MappedLaunchPartition, x: Tensor, y: Tensor) -> GemmPersi
 def batch_matmul(z: Output, x: Tensor, y: Tensor) -> BatchMatmul:
     """Per-batch GEMM, grid (batch, M/BM, N/BN) (cutile-examples/examples/batch_matmul.rs:17-43)."""
     return BatchMatmul([z, x, y])
+
+
+class Fmha(KernelLauncher):
+    """out (b*h, m, d) partition [1, BM, D]; q (b,h,m,d); k, v (b,hkv,n,d)."""
+    kernel_name = "fmha"
+
+    def __init__(self, args, causal: bool):
+        super().__init__(args)
+        self._causal = bool(causal)
+
+    def infer_generics(self) -> List[str]:
+        out, q, k = self.args[0], self.args[1], self.args[2]
+        bm, d = out.partition_shape[1], out.partition_shape[2]
+        even_k = int(k.shape[2] % 128 == 0)
+        return [out.dtype_str(), str(bm), "128", str(d), str(q.shape[1]), str(int(self._causal)),
+                str(even_k)]
+
+
+class FmhaPrefillCausal(KernelLauncher):
+    """q [q_len, heads, D]; k, v [kv_heads, kv_len, D]; out partition [BM, 1, D]."""
+    kernel_name = "fmha_prefill_causal"
+
+    def __init__(self, args, causal: bool):
+        super().__init__(args)
+        self._causal = bool(causal)
+
+    def infer_generics(self) -> List[str]:
+        out, k = self.args[3], self.args[1]
+        bm, d = out.partition_shape[0], out.partition_shape[2]
+        kv_len = self.args[6]
+        return [out.dtype_str(), str(bm), "128", str(d), str(int(self._causal)),
+                str(int(kv_len % 128 == 0)), "2"]
+
+
+def fmha(out: Output, q: Tensor, k: Tensor, v: Tensor, qk_scale: float, input_pos: int = 0,
+         query_group_size: int = 1, causal: bool = False) -> Fmha:
+    """Attention forward in the (b,h,m,d) layout of the examples and benchmarks
+    (cutile-examples/examples/flash_attention_causal.rs:19-45; cutile-benchmarks/benches/
+    fmha.rs:20-37).  ``causal`` only seeds the inferred CAUSAL generic."""
+    return Fmha([out, q, k, v, float(qk_scale), int(input_pos), int(query_group_size)], causal)
+
+
+def fmha_prefill_causal(q: Tensor, k: Tensor, v: Tensor, out: Output, qk_scale: float,
+                        query_group_size: int, kv_len: int, query_start: int = 0,
+                        causal: bool = True) -> FmhaPrefillCausal:
+    """Prefill attention in the serving layout (cutile-kernels/src/attention.rs:242-262)."""
+    return FmhaPrefillCausal([q, k, v, out, float(qk_scale), int(query_group_size), int(kv_len),
+                              int(query_start)], causal)

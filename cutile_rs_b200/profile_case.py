@@ -1,0 +1,79 @@
+"""Runs one kernel a few times on a small case, for profiler captures and quick timing.
+
+    python -m cutile_rs_b200.profile_case gemm --m 4096 --n 4096 --k 8192 --iters 3
+    python -m cutile_rs_b200.profile_case fmha --batch 1 --heads 16 --seq 4096 --causal 0 --iters 3
+
+The default sizes keep the operands above the 126 MB L2 (so DRAM counters mean something) and the
+device footprint far below a few GB (so a multi-pass capture ends by itself).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "fmha"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--config", type=int, default=-1)
+    ap.add_argument("--layout", type=int, default=0)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--causal", type=int, default=0)
+    ap.add_argument("--iters", type=int, default=3)
+    args = ap.parse_args()
+
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    _lib.check(lib.b200tile_init(0))
+    stream = torch.cuda.current_stream()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.kernel == "gemm":
+        m, n, k = args.m, args.n, args.k
+        a = (torch.randn(m, k, device="cuda", generator=g) / math.sqrt(k)).bfloat16()
+        b = (torch.randn((n, k) if args.layout else (k, n), device="cuda", generator=g) / math.sqrt(k)).bfloat16()
+        c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+
+        def run():
+            _lib.check(lib.b200tile_gemm(b"bf16", args.layout, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n,
+                                         k, k, b.stride(0), n, 0, 0, 0, 0, args.config, 0, 0, stream.cuda_stream))
+        flops = 2.0 * m * n * k
+    else:
+        bsz, h, s, d = args.batch, args.heads, args.seq, args.head_dim
+        q = torch.randn(bsz * h, s, d, device="cuda", generator=g).bfloat16()
+        kk = torch.randn(bsz * h, s, d, device="cuda", generator=g).bfloat16()
+        v = torch.randn(bsz * h, s, d, device="cuda", generator=g).bfloat16()
+        o = torch.empty_like(q)
+        st = (ctypes.c_int64 * 2)(s * d, d)
+
+        def run():
+            _lib.check(lib.b200tile_fmha_fwd(b"bf16", q.data_ptr(), kk.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                             bsz, h, h, s, s, d, st, st, st, st, 1.0 / math.sqrt(d),
+                                             args.causal, 0, stream.cuda_stream))
+        flops = 4.0 * s * s * d * h * bsz / (2 if args.causal else 1)
+    run()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(args.iters):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.iters
+    status = _lib.StatusC()
+    _lib.check(lib.b200tile_status(stream.cuda_stream, ctypes.byref(status)))
+    print(f"{args.kernel}: {ms:.4f} ms/launch, {flops / ms / 1e9:.1f} TFLOP/s")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,129 @@
+"""Attention-forward parity on a B200 against the CPU oracle (`fmha_ref_cpu` restated)."""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from cutile_rs_b200 import _lib, api, launch, workloads  # noqa: E402
+
+ATTN_TOL = 2e-2   # max-abs error on attention outputs
+I64x2 = ctypes.c_int64 * 2
+
+
+def _stream():
+    return torch.cuda.current_stream()
+
+
+def _fmha(lib, q, k, v, causal, input_pos=0):
+    b, h, s, d = q.shape
+    hkv, skv = k.shape[1], k.shape[2]
+    o = torch.full((b * h, s, d), float("nan"), dtype=q.dtype, device="cuda")
+    dt = b"bf16" if q.dtype == torch.bfloat16 else b"f16"
+    _lib.check(lib.b200tile_fmha_fwd(dt, q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, h, hkv, s,
+                                     skv, d, I64x2(s * d, d), I64x2(skv * d, d), I64x2(skv * d, d),
+                                     I64x2(s * d, d), 1.0 / math.sqrt(d), int(causal), input_pos,
+                                     _stream().cuda_stream))
+    torch.cuda.synchronize()
+    st = _lib.StatusC()
+    _lib.check(lib.b200tile_status(_stream().cuda_stream, ctypes.byref(st)))
+    return o
+
+
+@pytest.mark.parametrize("b,h,hkv,s,d,causal", [
+    (1, 1, 1, 256, 128, False), (1, 1, 1, 256, 128, True),
+    (2, 4, 2, 512, 128, True), (1, 2, 2, 384, 128, True), (1, 2, 2, 384, 128, False),
+    (1, 2, 1, 300, 128, False), (1, 2, 1, 300, 128, True), (1, 3, 3, 100, 128, True),
+    (1, 2, 2, 512, 64, False), (2, 2, 2, 320, 64, True),
+])
+def test_bf16_matches_oracle(b200, oracle, b, h, hkv, s, d, causal):
+    q, k, v = workloads.fmha_inputs(b, h, s, d, h_kv=hkv, config_index=100 + s)
+    got = _fmha(b200, q.cuda(), k.cuda(), v.cuda(), causal).float().cpu().numpy()
+    ref = oracle.fmha_ref_cpu(q.float().numpy(), k.float().numpy(), v.float().numpy(), 1.0 / math.sqrt(d),
+                              query_group_size=h // hkv, causal=causal, threads=0)
+    assert not np.isnan(got).any()
+    assert oracle.max_abs(got, ref.reshape(b * h, s, d)) <= ATTN_TOL
+
+
+def test_f16_and_input_pos(b200, oracle):
+    q, k, v = workloads.fmha_inputs(1, 2, 256, 64, config_index=77)
+    q, k, v = q.half(), k.half(), v.half()
+    got = _fmha(b200, q.cuda(), k.cuda(), v.cuda(), True).float().cpu().numpy()
+    ref = oracle.fmha_ref_cpu(q.float().numpy(), k.float().numpy(), v.float().numpy(), 0.125, causal=True)
+    assert oracle.max_abs(got, ref.reshape(2, 256, 64)) <= ATTN_TOL
+    # input_pos shifts the causal frontier: key j visible iff j <= i + input_pos
+    # (cutile-examples/examples/flash_attention_causal.rs:176); here via equal-length q/kv, pos 5
+    q, k, v = workloads.fmha_inputs(1, 2, 256, 128, config_index=78)
+    got = _fmha(b200, q.cuda(), k.cuda(), v.cuda(), True, input_pos=5).float().cpu().numpy()
+    ref = oracle.fmha_ref_cpu(q.float().numpy(), k.float().numpy(), v.float().numpy(), 1 / math.sqrt(128),
+                              input_pos=5, causal=True, threads=0)
+    assert oracle.max_abs(got, ref.reshape(2, 256, 128)) <= ATTN_TOL
+
+
+def test_golden_fixture_shape_family(b200, oracle):
+    # the reference's causal example uses d=32 (no tensor-core configuration): the library must say so
+    I2 = I64x2
+    rc = b200.b200tile_fmha_fwd(b"bf16", 16, 16, 16, 16, 2, 8, 8, 64, 64, 32, I2(2048, 32), I2(2048, 32),
+                                I2(2048, 32), I2(2048, 32), 0.17, 1, 5, _stream().cuda_stream)
+    assert rc == _lib.ERR_UNSUPPORTED and b"head_dim" in b200.b200tile_last_error()
+
+
+def test_properties(b200):
+    torch.manual_seed(1)
+    b, h, s, d = 1, 4, 1024, 128
+    q = torch.randn(b, h, s, d, device="cuda").bfloat16()
+    k = torch.randn(b, h, s, d, device="cuda").bfloat16()
+    # constant V rows -> every output row equals that constant (softmax weights sum to one)
+    v = torch.full((b, h, s, d), 0.75, device="cuda").bfloat16()
+    for causal in (False, True):
+        o = _fmha(b200, q, k, v, causal)
+        assert torch.all((o.float() - 0.75).abs() <= 2 ** -7)
+    # zero queries -> causal running mean of V
+    v = torch.randn(b, h, s, d, device="cuda").bfloat16()
+    o = _fmha(b200, torch.zeros_like(q), k, v, True).float().reshape(b, h, s, d)
+    run = torch.cumsum(v.float(), 2) / torch.arange(1, s + 1, device="cuda")[None, None, :, None]
+    assert (o - run).abs().max() <= ATTN_TOL
+    # permuting the keys (and values with them) leaves non-causal attention unchanged
+    perm = torch.randperm(s, device="cuda")
+    o1 = _fmha(b200, q, k, v, False).float()
+    o2 = _fmha(b200, q, k[:, :, perm].contiguous(), v[:, :, perm].contiguous(), False).float()
+    assert (o1 - o2).abs().max() <= ATTN_TOL
+    # run-to-run determinism
+    assert torch.equal(_fmha(b200, q, k, v, True), _fmha(b200, q, k, v, True))
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_full_size_slab(b200, oracle, causal):
+    # BASELINE config 2 at full size (8 x 32 x 4096 x 128); the oracle checks slabs
+    b, h, s, d = 8, 32, 4096, 128
+    q, k, v = workloads.fmha_inputs(b, h, s, d)
+    o = _fmha(b200, q.cuda(), k.cuda(), v.cuda(), causal).float().cpu().numpy()
+    assert not np.isnan(o).any()
+    for bh, rows in [(0, (0, 8)), (97, (2040, 2056)), (255, (4088, 4096))]:
+        bb, hh = divmod(bh, h)
+        ref = oracle.fmha_ref_cpu(q[bb:bb + 1, hh:hh + 1].float().numpy(), k[bb:bb + 1, hh:hh + 1].float().numpy(),
+                                  v[bb:bb + 1, hh:hh + 1].float().numpy(), 1 / math.sqrt(d), causal=causal,
+                                  rows=rows, threads=0)
+        assert oracle.max_abs(o[bh, rows[0]:rows[1]], ref[0, 0, rows[0]:rows[1]]) <= ATTN_TOL
+
+
+def test_reference_shaped_launchers(b200, oracle):
+    # example/benchmark layout (b,h,m,d), out (b*h, m, d) partition [1, BM, D]
+    b, h, hkv, s, d = 1, 4, 2, 256, 128
+    q, k, v = workloads.fmha_inputs(b, h, s, d, h_kv=hkv, config_index=55)
+    qd, kd, vd = (api.copy_host_to_device(t) for t in (q, k, v))
+    out = api.zeros([b * h, s, d], "bf16").partition([1, 128, d])
+    (out, *_rest) = launch.fmha(out, qd, kd, vd, 1 / math.sqrt(d), 0, h // hkv, causal=True).sync_on(_stream())
+    ref = oracle.fmha_ref_cpu(q.float().numpy(), k.float().numpy(), v.float().numpy(), 1 / math.sqrt(d),
+                              query_group_size=2, causal=True, threads=0).reshape(b * h, s, d)
+    assert oracle.max_abs(out.unpartition().to_host().float().numpy(), ref) <= ATTN_TOL
+    # serving layout: q [q_len, heads, D], k/v [kv_heads, kv_len, D], out partition [BM, 1, D]
+    q2 = api.copy_host_to_device(q[0].permute(1, 0, 2).contiguous())
+    k2, v2 = api.copy_host_to_device(k[0].contiguous()), api.copy_host_to_device(v[0].contiguous())
+    out2 = api.zeros([s, h, d], "bf16").partition([128, 1, d])
+    res = launch.fmha_prefill_causal(q2, k2, v2, out2, 1 / math.sqrt(d), 2, s, 0).sync_on(_stream())
+    got = res[3].unpartition().to_host().float().permute(1, 0, 2).numpy()
+    assert oracle.max_abs(got, ref) <= ATTN_TOL

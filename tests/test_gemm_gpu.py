@@ -1,0 +1,170 @@
+"""GEMM parity on a B200: the CUDA path, called through the C ABI, against the CPU oracle."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from cutile_rs_b200 import _lib, api, launch, workloads  # noqa: E402
+from cutile_rs_b200.tensor import KernelLaunchError  # noqa: E402
+
+BF16_TOL = 1e-2   # relative Frobenius error, bf16 (and f16) against the fp32 oracle
+
+
+def _stream():
+    return torch.cuda.current_stream()
+
+
+def _status_ok(lib):
+    st = _lib.StatusC()
+    _lib.check(lib.b200tile_status(_stream().cuda_stream, ctypes.byref(st)))
+    assert st.code == 0
+
+
+def _gemm(lib, dtype, a, b, layout=0, config=-1, accumulate=0, c=None, num_programs=0, group_m=0):
+    m, k = a.shape
+    n = b.shape[0] if layout else b.shape[1]
+    if c is None:
+        c = torch.full((m, n), float("nan"), dtype=a.dtype, device="cuda")
+    _lib.check(lib.b200tile_gemm(dtype.encode(), layout, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n, k,
+                                 a.stride(0), b.stride(0), c.stride(0), 0, 0, 0, accumulate, config, group_m,
+                                 num_programs, _stream().cuda_stream))
+    torch.cuda.synchronize()
+    return c
+
+
+def test_f32_config0_is_bit_identical_to_oracle(b200, oracle):
+    # BASELINE config 0: f32 512^3, U[-1,1]
+    a, b = workloads.gemm_f32_inputs(512, 512, 512)
+    got = _gemm(b200, "f32", a.cuda(), b.cuda()).cpu().numpy()
+    ref = oracle.cpu_gemm(a.numpy(), b.numpy(), threads=0)
+    assert np.array_equal(got, ref)
+    _status_ok(b200)
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 1, 1), (100, 77, 33), (64, 64, 32), (130, 65, 257)])
+def test_f32_ragged_shapes_bit_identical(b200, oracle, m, n, k):
+    a, b = workloads.gemm_f32_inputs(m, n, k, config_index=10 + m)
+    got = _gemm(b200, "f32", a.cuda(), b.cuda()).cpu().numpy()
+    assert np.array_equal(got, oracle.cpu_gemm(a.numpy(), b.numpy()))
+
+
+def test_f32_known_answers(b200, oracle):
+    # ones x ones == K (cutile/tests/gpu/book_snippets.rs:165-191)
+    ones = torch.ones(64, 64, device="cuda")
+    assert torch.all((_gemm(b200, "f32", ones, ones) - 64.0).abs() < 1e-3)
+    # patterned persistent example (cutile-examples/examples/persistent_gemm.rs:89-94), through the
+    # reference-shaped launcher: 64x64x32, tiles (16,16,8), map [4,1], 4 tile blocks
+    x = torch.tensor([[((r % 7) - 3.0) * 0.25 + (c % 5) * 0.125 for c in range(32)] for r in range(64)])
+    y = torch.tensor([[((r % 3) + 1.0) * 0.2 - (c % 11) * 0.05 for c in range(64)] for r in range(32)])
+    z = api.zeros([64, 64]).partition([16, 16]).map([4, 1], 4)
+    (z, _, _) = launch.gemm_persistent(z, api.copy_host_to_device(x), api.copy_host_to_device(y)) \
+        .generics(["f32", "16", "16", "8", "4", "1"]).sync_on(_stream())
+    got = z.unpartition().to_host().numpy()
+    ref = oracle.cpu_gemm(x.numpy(), y.numpy())
+    assert np.max(np.abs(got - ref)) < 1e-3 and np.array_equal(got, ref)
+
+
+def test_f32_accumulate_and_batch(b200, oracle):
+    a, b = workloads.gemm_f32_inputs(96, 80, 48, config_index=21)
+    c0 = torch.rand(96, 80)
+    got = _gemm(b200, "f32", a.cuda(), b.cuda(), accumulate=1, c=c0.clone().cuda()).cpu().numpy()
+    # accumulator starts from z (cutile-examples/examples/gemm.rs:28), then ascending-k sums
+    ref = c0.numpy().copy()
+    for t in range(48):
+        ref = (ref + (a.numpy()[:, t:t + 1] * b.numpy()[t:t + 1, :]).astype(np.float32)).astype(np.float32)
+    assert np.array_equal(got, ref)
+    # batch_matmul: 4 x 128 x 256 x 64, tiles (64,64,32) (cutile-examples/examples/batch_matmul.rs:52-54)
+    g = torch.Generator().manual_seed(5)
+    xa, yb = torch.rand(4, 128, 64, generator=g), torch.rand(4, 64, 256, generator=g)
+    z = api.zeros([4, 128, 256]).partition([1, 64, 64])
+    (z, _, _) = launch.batch_matmul(z, api.copy_host_to_device(xa), api.copy_host_to_device(yb)) \
+        .generics(["f32", "64", "64", "32"]).sync_on(_stream())
+    got = z.unpartition().to_host().numpy()
+    for i in range(4):
+        assert np.array_equal(got[i], oracle.cpu_gemm(xa[i].numpy(), yb[i].numpy()))
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+@pytest.mark.parametrize("config", [0, 1, 2])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 128), (1024, 768, 512), (200, 328, 136)])
+def test_bf16_matches_oracle(b200, oracle, layout, config, m, n, k):
+    a, b = workloads.gemm_bf16_inputs(m, n, k)
+    bd = b.t().contiguous() if layout else b
+    got = _gemm(b200, "bf16", a.cuda(), bd.cuda(), layout=layout, config=config).float().cpu().numpy()
+    ref = oracle.cpu_gemm(a.float().numpy(), b.float().numpy(), threads=0)
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= BF16_TOL
+    # stronger than the contract: each output is the bf16 rounding of a near-exact fp32 sum
+    assert np.max(np.abs(got - ref)) <= 2.0 ** -7 * np.max(np.abs(ref)) + 1e-6
+    _status_ok(b200)
+
+
+def test_f16_and_known_answer(b200, oracle):
+    g = torch.Generator().manual_seed(3)
+    a = (torch.randn(256, 192, generator=g) / 14).half()
+    b = (torch.randn(192, 384, generator=g) / 14).half()
+    got = _gemm(b200, "f16", a.cuda(), b.cuda()).float().cpu().numpy()
+    assert oracle.rel_frobenius(got, oracle.cpu_gemm(a.float().numpy(), b.float().numpy(), threads=0)) <= BF16_TOL
+    # all-ones f16: every element equals K (sampled +-0.5 in the reference harness, main.rs:977-1024)
+    ones_a = torch.ones(256, 1024, dtype=torch.float16, device="cuda")
+    ones_b = torch.ones(1024, 256, dtype=torch.float16, device="cuda")
+    assert torch.all(_gemm(b200, "f16", ones_a, ones_b) == 1024.0)
+    ones = torch.ones(512, 512, dtype=torch.bfloat16, device="cuda")
+    assert torch.all(_gemm(b200, "bf16", ones, ones) == 512.0)
+
+
+def test_bf16_full_size_slab_and_properties(b200, oracle):
+    # BASELINE config 1 at full size: 8192^3; the oracle checks a 16-row slab, properties the rest
+    m = n = k = 8192
+    a, b = workloads.gemm_bf16_inputs(m, n, k)
+    ad, bd = a.cuda(), b.cuda()
+    c = _gemm(b200, "bf16", ad, bd, config=0)
+    rows = slice(4096 - 8, 4096 + 8)
+    ref = oracle.cpu_gemm(a[rows].float().numpy(), b.float().numpy(), threads=0)
+    assert oracle.rel_frobenius(c[rows].float().cpu().numpy(), ref) <= BF16_TOL
+    # scaling A by 2 is exact in bf16 -> C doubles bit-exactly (linearity)
+    c2 = _gemm(b200, "bf16", ad * 2, bd, config=0)
+    assert torch.equal(c2, c * 2)
+    # determinism and independence from the persistent grid size / tile order
+    c3 = _gemm(b200, "bf16", ad, bd, config=0, num_programs=37, group_m=3)
+    assert torch.equal(c3, c)
+    # different tile shapes (and the CTA-pair kernel) add the same k-slabs in the same order
+    for cfg in (1, 2):
+        assert torch.equal(_gemm(b200, "bf16", ad, bd, config=cfg), c)
+    # checksum of checksums against the fp64 column/row sums: sum(C) = (1^T A)(B 1)
+    lhs = c.double().sum().item()
+    rhs = (ad.double().sum(0) @ bd.double().sum(1)).item()
+    assert abs(lhs - rhs) <= 2e-3 * (ad.double().abs().sum(0) @ bd.double().abs().sum(1)).item() ** 0.5 + 1.0
+    _status_ok(b200)
+
+
+def test_reference_shaped_launcher_and_errors(b200, oracle):
+    a, b = workloads.gemm_bf16_inputs(512, 512, 256)
+    x, y = api.copy_host_to_device(a), api.copy_host_to_device(b)
+    z = api.zeros([512, 512], "bf16").partition([128, 256])
+    (z, x2, y2, _k) = launch.gemm(z, x, y, k=256).sync_on(_stream())      # generics inferred
+    assert x2 is x and y2 is y
+    ref = oracle.cpu_gemm(a.float().numpy(), b.float().numpy(), threads=0)
+    assert oracle.rel_frobenius(z.unpartition().to_host().float().numpy(), ref) <= BF16_TOL
+    # explicit grid that disagrees with the partition is a launch error
+    with pytest.raises(KernelLaunchError, match="does not match the inferred partition grid"):
+        launch.gemm(api.zeros([512, 512], "bf16").partition([128, 256]), x, y).grid((3, 2, 1)).sync_on(_stream())
+    # a tile shape outside the fixed table is reported, not crashed on (TrialState::Invalid path)
+    with pytest.raises(KernelLaunchError, match="no precompiled configuration"):
+        launch.gemm(api.zeros([512, 512], "bf16").partition([64, 64]), x, y).sync_on(_stream())
+    with pytest.raises(KernelLaunchError, match="num_cta_in_cga"):
+        launch.gemm(api.zeros([512, 512], "bf16").partition([128, 256]), x, y) \
+            .compile_options(launch.CompileOptions(num_cta_in_cga=4)).sync_on(_stream())
+    # the reference's published configuration: 256x256x64 tiles on CTA pairs
+    zp = api.zeros([512, 512], "bf16").partition([256, 256])
+    launch.gemm(zp, x, y).compile_options(launch.CompileOptions(num_cta_in_cga=2)).sync_on(_stream())
+    assert oracle.rel_frobenius(zp.unpartition().to_host().float().numpy(), ref) <= BF16_TOL
+    # TMA's 16-byte rule: an odd leading dimension is refused with a clear code
+    bad = torch.zeros(512, 513, dtype=torch.bfloat16, device="cuda")[:, :512]
+    rc = b200.b200tile_gemm(b"bf16", 0, x.cu_deviceptr(), y.cu_deviceptr(), bad.data_ptr(), 1, 512, 512, 256,
+                            256, 512, 513, 0, 0, 0, 0, 0, 0, 0, _stream().cuda_stream)
+    assert rc == _lib.ERR_ALIGN
+    launch.gemm(api.zeros([512, 512], "bf16").partition([128, 256]), x, y).compile()   # warm-up only
