@@ -33,6 +33,23 @@ constexpr int FA_BM = 128;       // query rows per tile
 constexpr int FA_BN = 128;       // key rows per tile
 constexpr int FA_THREADS = 384;  // 12 warps
 constexpr float FA_RESCALE_THRESHOLD = 8.0f;
+// Register budget per role (setmaxnreg): 128 x 56 + 256 x 208 = 60416 <= 65536.
+constexpr int FA_SOFTMAX_REGS = 208;
+constexpr int FA_OTHER_REGS = 56;
+
+template <int N>
+__device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int D>
 struct FmhaSmem {
@@ -152,6 +169,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   auto S_COL = [](int t) { return (uint32_t)(t * 128); };
   auto O_COL = [](int t) { return (uint32_t)(256 + t * 128); };
 
+  if (warp < 4) reg_dealloc<FA_OTHER_REGS>();
   if (warp == 0) {
     // ------------------------------- TMA loader -------------------------------
     if (lane == 0) {
@@ -244,6 +262,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp >= 4) {
     // -------------------------------- softmax ----------------------------------
+    reg_alloc<FA_SOFTMAX_REGS>();
     const int t = (warp - 4) >> 2;
     const int q = warp & 3;
     const int row = q * 32 + lane;          // row inside the tile == TMEM lane
@@ -252,11 +271,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t tS = lane_base + S_COL(t);
     const uint32_t tO = lane_base + O_COL(t);
     const int n_mine = n_kv[t];
+    const float scale = p.scale_log2;
     float m_run = -CUDART_INF_F, l_run = 0.0f;
     bool ok = true;
     for (int j = 0; j < n_mine && ok; ++j) {
       if (!mbar_wait(wctx, bar_s_full + t * 8, j & 1, 30)) { ok = false; break; }
       tc_fence_after_sync();
+      // the whole score row lives in registers: one TMEM read per element
+      uint32_t v[FA_BN];
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c)
+        tmem_ld_32x32b_x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
       // last key column this row may see inside this tile (>= 127: nothing masked)
       int lim = p.kv_len - 1 - j * FA_BN;
       if (p.causal) {
@@ -264,23 +289,21 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         lim = c < lim ? c : lim;
       }
       const bool masked_tile = __any_sync(0xffffffffu, lim < FA_BN - 1);
-
-      // pass 1: row maximum
-      float rmax = -CUDART_INF_F;
-#pragma unroll 1
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tS + c * 32, v);
-        tmem_wait_ld();
-        if (masked_tile) {
+      tmem_wait_ld();
+      if (masked_tile) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i > lim) v[i] = 0xff800000u;  // -inf
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) rmax = fmaxf(rmax, __uint_as_float(v[i]));
+        for (int i = 0; i < FA_BN; ++i)
+          if (i > lim) v[i] = 0xff800000u;  // -inf
       }
-      const float m_tile = rmax * p.scale_log2;
+      // row maximum: four independent chains
+      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(v[i + u]));
+      }
+      const float rmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      const float m_tile = rmax * scale;
       float m_new = fmaxf(m_run, m_tile);
       if (m_new == -CUDART_INF_F) m_new = 0.0f;  // fully masked row: keep exp2 arguments finite
       float alpha = 1.0f;
@@ -289,7 +312,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         m_run = m_new;
       } else if (m_new - m_run > FA_RESCALE_THRESHOLD) {
         need = true;
-        alpha = exp2f(m_run - m_new);
+        alpha = ex2_approx(m_run - m_new);
         l_run *= alpha;
         m_run = m_new;
       }
@@ -305,29 +328,22 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tmem_st_32x32b_x32(tO + c * 32, o);
         }
       }
-      // pass 2: probabilities
+      // probabilities: exp2(s*scale - m); masked entries are exp2(-inf) = 0
       const float neg_m = -m_run;
-      float lsum = 0.0f;
-#pragma unroll 1
+      float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
       for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(tS + c * 32, v);
-        tmem_wait_ld();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float a = exp2f(fmaf(__uint_as_float(v[2 * i]), p.scale_log2, neg_m));
-          float b = exp2f(fmaf(__uint_as_float(v[2 * i + 1]), p.scale_log2, neg_m));
-          if (masked_tile) {
-            if (c * 32 + 2 * i > lim) a = 0.0f;
-            if (c * 32 + 2 * i + 1 > lim) b = 0.0f;
-          }
-          lsum += a + b;
+          const float a = ex2_approx(fmaf(__uint_as_float(v[c * 32 + 2 * i]), scale, neg_m));
+          const float b = ex2_approx(fmaf(__uint_as_float(v[c * 32 + 2 * i + 1]), scale, neg_m));
+          ls[i & 3] += a + b;
           pk[i] = OUT_F16 ? pack_f16x2(a, b) : pack_bf16x2(a, b);
         }
         tmem_st_32x32b_x16(tS + c * 16, pk);
       }
-      l_run += lsum;
+      l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tmem_wait_st();
       tc_fence_before_sync();
       __syncwarp();
