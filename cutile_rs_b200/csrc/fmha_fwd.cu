@@ -51,6 +51,32 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// Packed fp32x2 arithmetic and the three-input maximum halve the instruction count of the softmax
+// inner loops (the softmax warps are issue- and latency-bound, not special-function-bound).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+
 template <int D>
 struct FmhaSmem {
   static constexpr int HALVES = D / 64;                // 128-byte swizzle rows per head vector
@@ -298,9 +324,10 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // row maximum: four independent chains
       float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-      for (int i = 0; i < FA_BN; i += 4) {
+      for (int i = 0; i < FA_BN; i += 8) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) mx[u] = fmaxf(mx[u], __uint_as_float(v[i + u]));
+        for (int u = 0; u < 4; ++u)
+          mx[u] = max3(mx[u], __uint_as_float(v[i + 2 * u]), __uint_as_float(v[i + 2 * u + 1]));
       }
       const float rmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const float m_tile = rmax * scale;
@@ -330,18 +357,28 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       // probabilities: exp2(s*scale - m); masked entries are exp2(-inf) = 0
       const float neg_m = -m_run;
-      float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(neg_m, neg_m);
+      uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed (even, odd) partial sums
 #pragma unroll
       for (int c = 0; c < FA_BN / 32; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float a = ex2_approx(fmaf(__uint_as_float(v[c * 32 + 2 * i]), scale, neg_m));
-          const float b = ex2_approx(fmaf(__uint_as_float(v[c * 32 + 2 * i + 1]), scale, neg_m));
-          ls[i & 3] += a + b;
+          const uint64_t x2 = fma2(pack2(__uint_as_float(v[c * 32 + 2 * i]),
+                                         __uint_as_float(v[c * 32 + 2 * i + 1])), scale2, negm2);
+          float xa, xb;
+          unpack2(x2, xa, xb);
+          const float a = ex2_approx(xa), b = ex2_approx(xb);
+          ls2[i & 3] = add2(ls2[i & 3], pack2(a, b));
           pk[i] = OUT_F16 ? pack_f16x2(a, b) : pack_bf16x2(a, b);
         }
         tmem_st_32x32b_x16(tS + c * 16, pk);
+      }
+      float ls[4];
+      {
+        const uint64_t s01 = add2(ls2[0], ls2[1]), s23 = add2(ls2[2], ls2[3]);
+        unpack2(s01, ls[0], ls[1]);
+        unpack2(s23, ls[2], ls[3]);
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       tmem_wait_st();
