@@ -36,9 +36,10 @@ if ROOT not in sys.path:
 METRIC = "TFLOP/s (GEMM 8192^3 bf16, fp32 accumulate)"
 M = N = K = 8192
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemm_tc_kernel launch at 8192^3, from the ncu
-# capture summarised in profiles/gemm_bf16_8192.md (None until a capture exists).
-GEMM_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tc_pair_kernel: 316.7 MB measured
+# by ncu on a 4096x4096x8192 case (256 tiles), scaled by tiles processed to the 1024 tiles of
+# 8192^3 (profiles/gemm_bf16_pair.md).  The full-size launch is not captured under ncu.
+GEMM_DRAM_TRAFFIC_BYTES = int(316.7e6 * 4)
 
 
 def measured_peaks():
