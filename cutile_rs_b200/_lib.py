@@ -50,6 +50,9 @@ SIGNATURES = {
                                   c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int64),
                                   POINTER(c_int64), POINTER(c_int64), c_float, c_int, c_int,
                                   c_void_p]),
+    "b200tile_linear_fp8_blk128": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p,
+                                           c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64,
+                                           c_int64, c_float, c_void_p]),
 }
 
 _lib = None

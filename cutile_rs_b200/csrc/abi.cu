@@ -25,6 +25,10 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
                            const int64_t* os, float qk_scale, int causal, int input_pos,
                            cudaStream_t stream);
 
+int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const float* xs,
+                               const float* ys, void* z, int M, int N, int K, int64_t ldx, int64_t ldy,
+                               int64_t ldz, int ld_xs, int ld_ys, float alpha, cudaStream_t stream);
+
 using b200h::set_error;
 
 static_assert(B200TILE_ERR_INVALID == B200_ERR_INVALID && B200TILE_ERR_ALIGN == B200_ERR_ALIGN &&
@@ -111,6 +115,11 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
   if ((!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal")) &&
       (!strcmp(dtype, "bf16") || !strcmp(dtype, "f16"))) {
     tab = kFmhaConfigs;
+    n = 1;
+  }
+  static const b200tile_config kFp8Configs[] = {{0, 128, 256, 128, 4, 1, 1}};
+  if (!strcmp(kernel, "linear_tile_fp8_blk128")) {
+    tab = kFp8Configs;
     n = 1;
   }
   for (int i = 0; i < n && i < cap && out; ++i) out[i] = tab[i];
@@ -212,6 +221,32 @@ int b200tile_fmha_fwd(const char* dtype, const void* q, const void* k, const voi
   return b200_fmha_fwd_dispatch(dt, head_dim, q, k, v, out, batch, heads, heads_kv, q_len, kv_len,
                                 q_strides, k_strides, v_strides, o_strides, qk_scale,
                                 causal ? 1 : 0, input_pos, static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---------------------------------------------------------------------------
+// Typed block-scaled fp8 entry point
+// ---------------------------------------------------------------------------
+int b200tile_linear_fp8_blk128(const void* x, const void* y, const float* x_scales,
+                               const float* y_scales, void* z, const char* out_dtype, int m, int n,
+                               int k, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                               int64_t ld_ys, float alpha, void* cu_stream) {
+  if (!x || !y || !x_scales || !y_scales || !z || !out_dtype)
+    return set_error(B200TILE_ERR_INVALID, "linear_fp8_blk128: null argument");
+  if (m <= 0 || n <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_fp8_blk128: Shape dimensions must be positive");
+  if (k % 128 != 0)
+    return set_error(B200TILE_ERR_INVALID,
+                     "linear_fp8_blk128: K (%d) must be a multiple of the 128-element scale block", k);
+  if (ldx < k || ldy < k || ldz < n || ld_xs < k / 128 || ld_ys < k / 128)
+    return set_error(B200TILE_ERR_INVALID, "linear_fp8_blk128: leading dimension too small");
+  int out_f32;
+  if (!strcmp(out_dtype, "f32")) out_f32 = 1;
+  else if (!strcmp(out_dtype, "bf16")) out_f32 = 0;
+  else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_fp8_blk128: unsupported output type '%s'", out_dtype);
+  if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_fp8_blk128: output must be 16-byte aligned with a 16-byte pitch");
+  return b200_gemm_fp8_blk_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz,
+                                    (int)ld_xs, (int)ld_ys, alpha, static_cast<cudaStream_t>(cu_stream));
 }
 
 // ---------------------------------------------------------------------------
@@ -491,6 +526,49 @@ int launch_fmha_generic(const char* kernel, const char* const* generics, int n_g
                            input_pos, stream);
 }
 
+// "linear_tile_fp8_blk128": (z [M,N] partition [BM,BN], x [M,K], y [N,K], x_scales [M,K/128],
+//   y_scales [N/128,K/128], alpha f32) -- the parameter list of the reference's scaled
+//   `linear_tile` (cutile-examples/examples/mxfp8.rs:34-47); generics [T_out?, BM, BN, BK, ...].
+int launch_linear_fp8_generic(const char* kernel, const char* const* generics, int n_generics,
+                              const void* const* params, int n_params, const unsigned grid[3],
+                              void* stream, bool launch) {
+  const char* dtype;
+  long g[8];
+  int ng;
+  if (split_generics(generics, n_generics, "bf16", &dtype, g, 8, &ng) || ng < 3)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (g[0] != 128 || g[1] != 256 || g[2] != 128)
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "%s: tile (%ld,%ld,%ld) has no precompiled configuration (128,256,128)", kernel,
+                     g[0], g[1], g[2]);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg z, x, y, xs, ys;
+  read_tensor(r, 2, true, z);
+  read_tensor(r, 2, false, x);
+  read_tensor(r, 2, false, y);
+  read_tensor(r, 2, false, xs);
+  read_tensor(r, 2, false, ys);
+  const float alpha = r.f32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int M = z.dim[0], N = z.dim[1], K = x.dim[1];
+  if (x.dim[0] != M || y.dim[0] != N || y.dim[1] != K || xs.dim[0] != M || xs.dim[1] * 128 != K ||
+      ys.dim[0] != (N + 127) / 128 || ys.dim[1] * 128 != K)
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  if (z.stride[1] != 1 || x.stride[1] != 1 || y.stride[1] != 1 || xs.stride[1] != 1 || ys.stride[1] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: the last axis of every tensor must be contiguous", kernel);
+  if (z.pdim[0] != g[0] || z.pdim[1] != g[1])
+    return set_error(B200TILE_ERR_INVALID, "%s: output partition does not match the tile generics", kernel);
+  if (grid[0] != (unsigned)((M + g[0] - 1) / g[0]) || grid[1] != (unsigned)((N + g[1] - 1) / g[1]) || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid", grid[0],
+                     grid[1], grid[2]);
+  return b200tile_linear_fp8_blk128(reinterpret_cast<const void*>(x.ptr), reinterpret_cast<const void*>(y.ptr),
+                                    reinterpret_cast<const float*>(xs.ptr), reinterpret_cast<const float*>(ys.ptr),
+                                    reinterpret_cast<void*>(z.ptr), dtype, M, N, K, x.stride[0], y.stride[0],
+                                    z.stride[0], xs.stride[0], ys.stride[0], alpha, stream);
+}
+
 }  // namespace
 
 int b200tile_launch(const char* kernel, const char* const* generics, int n_generics,
@@ -504,6 +582,8 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
   if (!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal"))
     return launch_fmha_generic(kernel, generics, n_generics, opts, params, n_params, grid,
                                cu_stream, true);
+  if (!strcmp(kernel, "linear_tile_fp8_blk128"))
+    return launch_linear_fp8_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -516,6 +596,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
   if (!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal"))
     return launch_fmha_generic(kernel, generics, n_generics, opts, nullptr, 0, nullptr, nullptr,
                                false);
+  if (!strcmp(kernel, "linear_tile_fp8_blk128"))
+    return launch_linear_fp8_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

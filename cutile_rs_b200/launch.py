@@ -303,3 +303,19 @@ def fmha_prefill_causal(q: Tensor, k: Tensor, v: Tensor, out: Output, qk_scale: 
     """Prefill attention in the serving layout (cutile-kernels/src/attention.rs:242-262)."""
     return FmhaPrefillCausal([q, k, v, out, float(qk_scale), int(query_group_size), int(kv_len),
                               int(query_start)], causal)
+
+
+class LinearFp8Blk128(KernelLauncher):
+    """z [M,N] = alpha * x_q [M,K] . y_q [N,K]^T with fp32 scales per 1x128 (x) / 128x128 (y) block."""
+    kernel_name = "linear_tile_fp8_blk128"
+
+    def infer_generics(self) -> List[str]:
+        z = self.args[0]
+        return [z.dtype_str(), str(z.partition_shape[0]), str(z.partition_shape[1]), "128", "1"]
+
+
+def linear_tile_fp8_blk128(z: Output, x: Tensor, y: Tensor, x_scales: Tensor, y_scales: Tensor,
+                           alpha: float = 1.0) -> LinearFp8Blk128:
+    """Block-scaled fp8 linear layer; same parameter list as the reference's scaled `linear_tile`
+    (cutile-examples/examples/mxfp8.rs:34-47) with fp32 scales per 128-block."""
+    return LinearFp8Blk128([z, x, y, x_scales, y_scales, float(alpha)])

@@ -93,7 +93,7 @@ B200TILE_API int b200tile_query_configs(const char* kernel, const char* dtype, b
  * `AsyncKernelLaunch::execute` (cutile-macro/src/kernel_launcher_generator.rs:911-923,958-975;
  * cuda-async/src/launch.rs:91-113).
  *   kernel    entry name without the `_entry` suffix: "gemm", "gemm_acc", "gemm_persistent",
- *             "batch_matmul", "fmha", "fmha_prefill_causal"
+ *             "batch_matmul", "fmha", "fmha_prefill_causal", "linear_tile_fp8_blk128"
  *   generics  the launcher's `Vec<String>` (dtype names from cuda-core/src/dtype.rs:147-168,
  *             integers in decimal)
  *   params    the reference's flattened kernel parameter array, one pointer per value, in
@@ -151,6 +151,18 @@ B200TILE_API int b200tile_fmha_fwd(const char* dtype, const void* q, const void*
                                    const int64_t k_strides[2], const int64_t v_strides[2],
                                    const int64_t o_strides[2], float qk_scale, int causal,
                                    int input_pos, void* cu_stream);
+
+/* z[M,N] = alpha * sum over 128-deep k-blocks of  xs[m,kb] * ys[n/128,kb] * (x_q[m,kb] . y_q[n,kb]),
+ * x_q [M,K] and y_q [N,K] in f8e4m3fn (bit convention cuda-core/src/dtype.rs:25-31,223), one fp32
+ * scale per 1x128 block of x (x_scales [M, K/128]) and per 128x128 block of y
+ * (y_scales [ceil(N/128), K/128]).  The reference has no kernel for this scale granularity (its
+ * fp8 path is MXFP8, cutile-examples/examples/mxfp8.rs:34-64); the operand layout ("NT", both
+ * K-major) and the `alpha` epilogue follow that `linear_tile`.
+ *   out_dtype  "bf16" or "f32";  K must be a multiple of 128; leading dimensions in ELEMENTS. */
+B200TILE_API int b200tile_linear_fp8_blk128(const void* x, const void* y, const float* x_scales,
+                                            const float* y_scales, void* z, const char* out_dtype,
+                                            int m, int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
+                                            int64_t ld_xs, int64_t ld_ys, float alpha, void* cu_stream);
 
 #ifdef __cplusplus
 }
