@@ -9,7 +9,7 @@ from __future__ import annotations
 import ctypes
 import os
 from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int64, c_uint, c_uint32,
-                    c_void_p)
+                    c_uint64, c_void_p)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200tile.so")
@@ -53,6 +53,10 @@ SIGNATURES = {
     "b200tile_linear_fp8_blk128": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p,
                                            c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64,
                                            c_int64, c_float, c_void_p]),
+    "b200tile_linear_nvfp4_workspace_bytes": (c_uint64, [c_int, c_int, c_int]),
+    "b200tile_linear_nvfp4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p, c_int,
+                                      c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                                      c_void_p, c_uint64, c_int, c_void_p]),
 }
 
 _lib = None

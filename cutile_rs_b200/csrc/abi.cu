@@ -29,6 +29,11 @@ int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const 
                                const float* ys, void* z, int M, int N, int K, int64_t ldx, int64_t ldy,
                                int64_t ldz, int ld_xs, int ld_ys, float alpha, cudaStream_t stream);
 
+size_t b200_nvfp4_scratch_bytes(int M, int N, int K, int bn);
+int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, const void* xs, const void* ys,
+                             void* z, int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
+
 using b200h::set_error;
 
 static_assert(B200TILE_ERR_INVALID == B200_ERR_INVALID && B200TILE_ERR_ALIGN == B200_ERR_ALIGN &&
@@ -247,6 +252,55 @@ int b200tile_linear_fp8_blk128(const void* x, const void* y, const float* x_scal
     return set_error(B200TILE_ERR_ALIGN, "linear_fp8_blk128: output must be 16-byte aligned with a 16-byte pitch");
   return b200_gemm_fp8_blk_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz,
                                     (int)ld_xs, (int)ld_ys, alpha, static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---------------------------------------------------------------------------
+// Typed NVFP4 entry point
+// ---------------------------------------------------------------------------
+static const int kNvfp4Bn[3] = {128, 192, 256};
+
+uint64_t b200tile_linear_nvfp4_workspace_bytes(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  size_t best = 0;
+  for (int i = 0; i < 3; ++i) {
+    const size_t b = b200_nvfp4_scratch_bytes(m, n, k, kNvfp4Bn[i]);
+    if (b > best) best = b;
+  }
+  return (uint64_t)best;
+}
+
+int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales, const void* y_scales,
+                          void* z, const char* out_dtype, int m, int n, int k, int64_t ldx, int64_t ldy,
+                          int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
+                          uint64_t workspace_bytes, int config, void* cu_stream) {
+  if (!x || !y || !x_scales || !y_scales || !z || !out_dtype)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4: null argument");
+  if (m <= 0 || n <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4: Shape dimensions must be positive");
+  if (k % 64 != 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4: K (%d) must be a multiple of 64", k);
+  if (ldx < k / 2 || ldy < k / 2 || ldz < n || ld_xs < k / 16 || ld_ys < k / 16)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4: leading dimension too small");
+  if (ld_xs % 4 != 0 || ld_ys % 4 != 0 || (reinterpret_cast<uintptr_t>(x_scales) & 3) != 0 ||
+      (reinterpret_cast<uintptr_t>(y_scales) & 3) != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4: scale rows must be 4-byte aligned");
+  int out_f32;
+  if (!strcmp(out_dtype, "f32")) out_f32 = 1;
+  else if (!strcmp(out_dtype, "bf16")) out_f32 = 0;
+  else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_nvfp4: unsupported output type '%s'", out_dtype);
+  if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4: output must be 16-byte aligned with a 16-byte pitch");
+  if (config < -1 || config > 2)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "linear_nvfp4: unknown config %d", config);
+  if (config < 0) config = 1;
+  const int bn = kNvfp4Bn[config];
+  const size_t need = b200_nvfp4_scratch_bytes(m, n, k, bn);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
+    return set_error(B200TILE_ERR_INVALID,
+                     "linear_nvfp4: workspace of %llu bytes (16-byte aligned) required, got %llu",
+                     (unsigned long long)need, (unsigned long long)workspace_bytes);
+  return b200_gemm_nvfp4_dispatch(bn, out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs,
+                                  ld_ys, alpha, workspace, static_cast<cudaStream_t>(cu_stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -1,0 +1,355 @@
+// NVFP4 block-scaled GEMM for sm_100a:
+//   Z[M,N] = alpha * sum_k  x[m,k]*xs[m,k/16] * y[n,k]*ys[n,k/16]
+// x, y: packed f4e2m1fnx2 (two values per byte, low nibble first) [M,K/2], [N,K/2];
+// xs, ys: f8e4m3fn scales, logical row-major [M,K/16], [N,K/16]; fp32 accumulation.
+// Replaces the machine code behind the reference's `linear_tile` + `mmaf_scaled`
+// (cutile-examples/examples/nvfp4.rs:37-76; cutile/src/_core.rs:2288-2313; semantics
+// cutile-book/tutorials/11-nvfp4-inference.md:58-82).
+//
+// The tensor core applies the scales itself (tcgen05.mma kind::mxf4nvf4.block_scale, one UE4M3
+// scale per 16 elements, K = 64 per instruction) but wants them in Tensor Memory in a fixed
+// arrangement: per 128 rows x 4 scale columns a 512-byte block with byte (row%32)*16 + (row/32)*4 +
+// col, copied by tcgen05.cp 32x128b.warpx4.  The row-major scale tensors are therefore re-laid
+// out once per call by a small pre-pass into a SCRATCH buffer, [tile][K/64][chunk][512 B], from
+// which the main kernel fetches whole stages with 1-D bulk copies.
+//
+//   warp 0      TMA producer: A (128 x 128 B), B (BN x 128 B) and both scale blocks per stage
+//   warp 1      issuer: tcgen05.cp of the stage's scales, then 4 block-scaled MMAs (K = 64 each)
+//   warps 2..5  epilogue: tcgen05.ld -> alpha -> bf16/f32 -> global
+#include "host_common.h"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int F4_BM = 128;
+constexpr int F4_BK = 256;            // elements per stage = 128 bytes = one swizzle row
+constexpr int F4_THREADS = 192;
+
+template <int BN>
+struct Fp4Cfg {
+  static constexpr int CHUNKS = (BN + 127) / 128;            // 128-row scale blocks per B tile
+  static constexpr int SF_COLS = 16 + 16 * CHUNKS;           // TMEM columns of one stage's scales
+  static constexpr int NACC = (2 * BN + 2 * SF_COLS <= 512) ? 2 : 1;
+  static constexpr int SF_BASE = NACC * BN;                  // scales sit after the accumulators
+  static constexpr int A_BYTES = F4_BM * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int SFA_BYTES = 4 * 512;
+  static constexpr int SFB_BYTES = 4 * CHUNKS * 512;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGES = (BN <= 128) ? 5 : 4;
+  static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+  static constexpr int TOTAL = OFF_MISC + 16 + 1024;
+};
+
+// ---------------------------------------------------------------------------
+// Pre-pass: row-major scales -> per-tile tcgen05 scale blocks in scratch memory.
+// One thread per 4-byte word of the output.
+// ---------------------------------------------------------------------------
+__global__ void nvfp4_relayout_scales_kernel(const uint8_t* __restrict__ src, int rows, int kq_count,
+                                             int kq_valid, int64_t ld, int tile_rows, int chunks,
+                                             int num_tiles, uint32_t* __restrict__ dst) {
+  const int64_t total = (int64_t)num_tiles * kq_count * chunks * 128;  // words
+  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total;
+       w += (int64_t)gridDim.x * blockDim.x) {
+    const int word = (int)(w & 127);             // word inside the 512-byte block
+    const int64_t blk = w >> 7;
+    const int c = (int)(blk % chunks);
+    const int64_t t_kq = blk / chunks;
+    const int kq = (int)(t_kq % kq_count);
+    const int tile = (int)(t_kq / kq_count);
+    const int r32 = word >> 2, g = word & 3;
+    const int local = c * 128 + g * 32 + r32;
+    const int row = tile * tile_rows + local;
+    uint32_t v = 0;
+    if (local < tile_rows && row < rows && kq < kq_valid)
+      v = *reinterpret_cast<const uint32_t*>(src + (int64_t)row * ld + (int64_t)kq * 4);
+    dst[w] = v;
+  }
+}
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> TMEM lanes 0..31 (4 columns), replicated into all four
+// 32-lane quarters.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_nvfp4_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Block-scaled instruction descriptor: E2M1 operands (code 1 for this kind), UE4M3 scales, K = 64.
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) {
+  return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (0u << 23) | ((M >> 4) << 24);
+}
+
+template <int BN, bool OUT_F32>
+__global__ void __launch_bounds__(F4_THREADS, 1)
+gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                  const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z,
+                  int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
+  using C = Fp4Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_full = base + C::OFF_BAR;
+  const uint32_t bar_empty = bar_full + STAGES * 8;
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;
+  const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + C::OFF_MISC);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  WaitCtx wctx{misc + 1, status};
+  auto stage_a = [&](uint32_t s) { return base + s * C::STAGE_BYTES; };
+  auto stage_b = [&](uint32_t s) { return base + s * C::STAGE_BYTES + C::A_BYTES; };
+  auto stage_sfa = [&](uint32_t s) { return base + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES; };
+  auto stage_sfb = [&](uint32_t s) { return stage_sfa(s) + C::SFA_BYTES; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + b * 8, 1);
+      mbar_init(bar_tempty + b * 8, 4);
+    }
+    misc[1] = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(misc)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = misc[0];
+
+  const int tiles_m = (M + F4_BM - 1) / F4_BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int total_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + F4_BK - 1) / F4_BK;
+  const int kq_count = num_kb * 4;  // 64-element scale blocks along K (scratch is padded to this)
+  auto tile_coords = [&](int tile, int& bm, int& bn) {
+    const int in_group = group_m * tiles_n;
+    const int group = tile / in_group;
+    const int first_m = group * group_m;
+    const int rem = tiles_m - first_m;
+    const int gsz = rem < group_m ? rem : group_m;
+    bm = first_m + (tile % gsz);
+    bn = (tile % in_group) / gsz;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int bm, bn;
+        tile_coords(tile, bm, bn);
+        const uint8_t* sfa_tile = sfa + (int64_t)bm * kq_count * 512;
+        const uint8_t* sfb_tile = sfb + (int64_t)bn * kq_count * (C::CHUNKS * 512);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
+          const uint32_t full = bar_full + stage * 8;
+          mbar_expect_tx(full, C::STAGE_BYTES);
+          tma_load_2d(stage_a(stage), &tmA, full, kb * 128, bm * F4_BM);
+          tma_load_2d(stage_b(stage), &tmB, full, kb * 128, bn * BN);
+          bulk_load_1d(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
+          bulk_load_1d(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_nvfp4(F4_BM, BN);
+      uint32_t stage = 0, phase = 0, it = 0, g = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const uint32_t buf = (C::NACC == 2) ? (it & 1) : 0;
+        const uint32_t par = (C::NACC == 2) ? (((it >> 1) & 1) ^ 1) : ((it & 1) ^ 1);
+        if (!mbar_wait(wctx, bar_tempty + buf * 8, par, 2)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++g) {
+          if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
+          tc_fence_after_sync();
+          // this stage's scales: smem -> TMEM (two alternating TMEM regions)
+          const uint32_t sf_t = tmem_base + C::SF_BASE + (g & 1) * C::SF_COLS;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            tmem_cp_32x128b_warpx4(sf_t + k * 4, make_smem_desc(stage_sfa(stage) + k * 512, 16, 128, 0));
+#pragma unroll
+            for (int c = 0; c < C::CHUNKS; ++c)
+              tmem_cp_32x128b_warpx4(sf_t + 16 + (k * C::CHUNKS + c) * 4,
+                                     make_smem_desc(stage_sfb(stage) + (k * C::CHUNKS + c) * 512, 16, 128, 0));
+          }
+          const uint64_t adesc = make_smem_desc(stage_a(stage), 16, 1024, SWZ_128B);
+          const uint64_t bdesc = make_smem_desc(stage_b(stage), 16, 1024, SWZ_128B);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_nvfp4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, sf_t + k * 4,
+                          sf_t + 16 + k * C::CHUNKS * 4, (kb | k) != 0);
+          umma_commit(bar_empty + stage * 8);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(bar_tfull + buf * 8);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      int bm, bn;
+      tile_coords(tile, bm, bn);
+      const uint32_t buf = (C::NACC == 2) ? (it & 1) : 0;
+      const uint32_t par = (C::NACC == 2) ? ((it >> 1) & 1) : (it & 1);
+      if (!mbar_wait(wctx, bar_tfull + buf * 8, par, 4)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      const int row_g = bm * F4_BM + row;
+      const int col0 = bn * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(t_row + c * 32, v);
+        tmem_wait_ld();
+        const int cc = col0 + c * 32;
+        if (row_g < M && cc < N) {
+          if (OUT_F32) {
+            float* zrow = static_cast<float*>(Z) + (int64_t)row_g * ldz + cc;
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (cc + i + 3 < N)
+                *reinterpret_cast<float4*>(zrow + i) =
+                    make_float4(__uint_as_float(v[i]) * alpha, __uint_as_float(v[i + 1]) * alpha,
+                                __uint_as_float(v[i + 2]) * alpha, __uint_as_float(v[i + 3]) * alpha);
+              else
+                for (int e = 0; e < 4; ++e)
+                  if (cc + i + e < N) zrow[i + e] = __uint_as_float(v[i + e]) * alpha;
+            }
+          } else {
+            uint16_t* zrow = static_cast<uint16_t*>(Z) + (int64_t)row_g * ldz + cc;
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+              if (cc + i + 7 < N) {
+                uint4 w;
+                w.x = pack_bf16x2(__uint_as_float(v[i]) * alpha, __uint_as_float(v[i + 1]) * alpha);
+                w.y = pack_bf16x2(__uint_as_float(v[i + 2]) * alpha, __uint_as_float(v[i + 3]) * alpha);
+                w.z = pack_bf16x2(__uint_as_float(v[i + 4]) * alpha, __uint_as_float(v[i + 5]) * alpha);
+                w.w = pack_bf16x2(__uint_as_float(v[i + 6]) * alpha, __uint_as_float(v[i + 7]) * alpha);
+                *reinterpret_cast<uint4*>(zrow + i) = w;
+              } else {
+                for (int e = 0; e < 8; ++e)
+                  if (cc + i + e < N)
+                    zrow[i + e] = (uint16_t)(pack_bf16x2(__uint_as_float(v[i + e]) * alpha, 0.0f) & 0xFFFF);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + buf * 8);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// Bytes of scratch needed for the re-laid-out scales of an (M, N, K) problem with B tiles of BN rows.
+static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offset) {
+  const size_t kq = (size_t)((K + F4_BK - 1) / F4_BK) * 4;
+  const size_t tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
+  const size_t chunks = (BN + 127) / 128;
+  const size_t a_bytes = tiles_m * kq * 512;
+  if (sfb_offset) *sfb_offset = a_bytes;
+  return a_bytes + tiles_n * kq * chunks * 512;
+}
+
+template <int BN, bool OUT_F32>
+static int launch_nvfp4(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
+                        int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha,
+                        uint8_t* scratch, cudaStream_t stream) {
+  using C = Fp4Cfg<BN>;
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200_ERR_CUDA;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if ((rc = b200h::encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, (uint64_t)K / 2, (uint64_t)M,
+                                  (uint64_t)ldx, 128, F4_BM, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, (uint64_t)K / 2, (uint64_t)N,
+                                  (uint64_t)ldy, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  size_t sfb_off;
+  nvfp4_scratch_layout(M, N, K, BN, &sfb_off);
+  const int kq = ((K + F4_BK - 1) / F4_BK) * 4;
+  const int tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
+  {
+    const int64_t words_a = (int64_t)tiles_m * kq * 128;
+    const int64_t words_b = (int64_t)tiles_n * kq * C::CHUNKS * 128;
+    const int ga = (int)((words_a + 255) / 256 < 4096 ? (words_a + 255) / 256 : 4096);
+    const int gb = (int)((words_b + 255) / 256 < 4096 ? (words_b + 255) / 256 : 4096);
+    nvfp4_relayout_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(xs), M, kq, K / 64, ld_xs, F4_BM,
+                                                         1, tiles_m, reinterpret_cast<uint32_t*>(scratch));
+    nvfp4_relayout_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(ys), N, kq, K / 64, ld_ys, BN,
+                                                         C::CHUNKS, tiles_n,
+                                                         reinterpret_cast<uint32_t*>(scratch + sfb_off));
+  }
+  auto kern = gemm_nvfp4_kernel<BN, OUT_F32>;
+  static bool attr_done[64] = {};
+  if (!attr_done[di->ordinal]) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+    attr_done[di->ordinal] = true;
+  }
+  const int tiles = tiles_m * tiles_n;
+  const int grid = tiles < di->sm_count ? tiles : di->sm_count;
+  kern<<<grid, F4_THREADS, C::TOTAL, stream>>>(tmA, tmB, scratch, scratch + sfb_off, z, M, N, K, ldz, alpha, 8,
+                                               di->status);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace b200
+
+size_t b200_nvfp4_scratch_bytes(int M, int N, int K, int bn) {
+  return b200::nvfp4_scratch_layout(M, N, K, bn, nullptr);
+}
+
+int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, const void* xs, const void* ys,
+                             void* z, int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream) {
+  using namespace b200;
+  uint8_t* s = static_cast<uint8_t*>(scratch);
+#define B200_F4_CASE(BN_, F32_) \
+  return launch_nvfp4<BN_, F32_>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream)
+  if (bn == 128 && out_f32) B200_F4_CASE(128, true);
+  if (bn == 128 && !out_f32) B200_F4_CASE(128, false);
+  if (bn == 192 && out_f32) B200_F4_CASE(192, true);
+  if (bn == 192 && !out_f32) B200_F4_CASE(192, false);
+  if (bn == 256 && out_f32) B200_F4_CASE(256, true);
+  if (bn == 256 && !out_f32) B200_F4_CASE(256, false);
+#undef B200_F4_CASE
+  return b200h::set_error(B200_ERR_UNSUPPORTED, "linear_nvfp4: no kernel for BN = %d", bn);
+}

@@ -319,3 +319,35 @@ def linear_tile_fp8_blk128(z: Output, x: Tensor, y: Tensor, x_scales: Tensor, y_
     """Block-scaled fp8 linear layer; same parameter list as the reference's scaled `linear_tile`
     (cutile-examples/examples/mxfp8.rs:34-47) with fp32 scales per 128-block."""
     return LinearFp8Blk128([z, x, y, x_scales, y_scales, float(alpha)])
+
+
+def linear_nvfp4(z: Tensor, x: Tensor, y: Tensor, x_scales: Tensor, y_scales: Tensor, alpha: float = 1.0,
+                 stream: Optional[torch.cuda.Stream] = None, config: int = -1,
+                 workspace: Optional[torch.Tensor] = None) -> Tensor:
+    """NVFP4 block-scaled linear layer, z = alpha * x . y^T (`linear_tile` of
+    cutile-examples/examples/nvfp4.rs:37-76): x [M,K/2], y [N,K/2] packed f4e2m1fnx2 bytes,
+    scales [M,K/16], [N,K/16] f8e4m3fn bytes in logical row-major order.  The scale re-layout needs
+    device scratch; pass ``workspace`` (uint8, from :func:`nvfp4_workspace`) to keep the call free
+    of allocations, otherwise one is taken from the torch caching allocator."""
+    lib = _lib.load()
+    s = stream or torch.cuda.current_stream()
+    m, n = z.shape
+    k = x.shape[1] * 2
+    need = int(lib.b200tile_linear_nvfp4_workspace_bytes(m, n, k))
+    if workspace is None:
+        with torch.cuda.stream(s):
+            workspace = torch.empty(need, dtype=torch.uint8, device=z.storage.device)
+    rc = lib.b200tile_linear_nvfp4(x.cu_deviceptr(), y.cu_deviceptr(), x_scales.cu_deviceptr(),
+                                   y_scales.cu_deviceptr(), z.cu_deviceptr(), z.dtype.encode(), m, n, k,
+                                   x.strides[0], y.strides[0], z.strides[0], x_scales.strides[0],
+                                   y_scales.strides[0], float(alpha), workspace.data_ptr(),
+                                   workspace.numel(), config, c_void_p(s.cuda_stream))
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+    return z
+
+
+def nvfp4_workspace(m: int, n: int, k: int) -> torch.Tensor:
+    """Scratch buffer large enough for :func:`linear_nvfp4` on an (m, n, k) problem."""
+    need = int(_lib.load().b200tile_linear_nvfp4_workspace_bytes(m, n, k))
+    return torch.empty(need, dtype=torch.uint8, device="cuda")

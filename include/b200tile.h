@@ -164,6 +164,25 @@ B200TILE_API int b200tile_linear_fp8_blk128(const void* x, const void* y, const 
                                             int m, int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
                                             int64_t ld_xs, int64_t ld_ys, float alpha, void* cu_stream);
 
+/* z[M,N] = alpha * sum_k x[m,k]*xs[m,k/16] * y[n,k]*ys[n,k/16]  (NVFP4 block-scaled linear layer).
+ * Replaces `linear_tile` of cutile-examples/examples/nvfp4.rs:37-76 (`mmaf_scaled`,
+ * cutile/src/_core.rs:2288-2313): x, y packed f4e2m1fnx2 [M,K/2], [N,K/2] (low nibble = first
+ * value, cuda-core/src/dtype.rs:60-110); xs, ys f8e4m3fn scales in logical row-major [M,K/16],
+ * [N,K/16] as the example keeps them; alpha carries the folded per-tensor global scales
+ * (cutile-book/tutorials/11-nvfp4-inference.md:147-148).
+ *   out_dtype  "bf16" or "f32";  K must be a multiple of 64; leading dimensions in BYTES of the
+ *              packed / scale rows (ldx, ldy >= K/2; ld_xs, ld_ys >= K/16, multiples of 4)
+ *   workspace  device scratch of at least b200tile_linear_nvfp4_workspace_bytes(m, n, k) bytes,
+ *              16-byte aligned: the scales are re-laid out into it on every call (stream-ordered);
+ *              calls that overlap on the device must not share a workspace
+ *   config     -1 = default, 0/1/2 = B tiles of 128/192/256 rows */
+B200TILE_API uint64_t b200tile_linear_nvfp4_workspace_bytes(int m, int n, int k);
+B200TILE_API int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales,
+                                       const void* y_scales, void* z, const char* out_dtype, int m,
+                                       int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
+                                       int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
+                                       uint64_t workspace_bytes, int config, void* cu_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,87 @@
+"""NVFP4 block-scaled GEMM parity on a B200 against the oracle's fp32 dequantised reference."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from cutile_rs_b200 import _lib, api, launch, quant, workloads  # noqa: E402
+
+FP4_TOL = 3e-2   # relative Frobenius error against the fp32 dequantised reference
+
+
+def _run(xp, yp, xs, ys, m, n, k, out, alpha=1.0, config=-1):
+    z = api.from_torch(torch.full((m, n), float("nan"), device="cuda",
+                                  dtype=torch.float32 if out == "f32" else torch.bfloat16))
+    launch.linear_nvfp4(z, api.from_torch(xp, "f4e2m1fnx2"), api.from_torch(yp, "f4e2m1fnx2"),
+                        api.from_torch(xs), api.from_torch(ys), alpha, config=config)
+    torch.cuda.synchronize()
+    return z.storage
+
+
+@pytest.mark.parametrize("k", [16 * 4, 128])
+def test_reference_known_answers(b200, k):
+    # nibble 0x2 (= 1.0) with E4M3 scale 0x38 (= 1.0): every output equals K
+    # (cutile/tests/tensor_and_matrix_ops.rs:622-682 with K=16; cutile-examples/examples/nvfp4.rs:104-105,
+    # 145-151 with 16 x 16 x 128).  K = 64 is this kernel's smallest K.
+    m = n = 16
+    one = lambda r, c: torch.full((r, c), 0x22, dtype=torch.uint8, device="cuda")
+    sc = lambda r, c: torch.full((r, c), 0x38, dtype=torch.uint8, device="cuda")
+    z = _run(one(m, k // 2), one(n, k // 2), sc(m, k // 16), sc(n, k // 16), m, n, k, "f32")
+    assert torch.all((z - float(k)).abs() <= 1e-3)
+
+
+@pytest.mark.parametrize("config", [0, 1, 2])
+@pytest.mark.parametrize("m,n,k,out", [(128, 256, 64, "f32"), (256, 384, 512, "f32"), (200, 328, 320, "bf16"),
+                                       (16, 512, 1024, "bf16")])
+def test_matches_oracle(b200, oracle, config, m, n, k, out):
+    a, b = workloads.gemm_normal_inputs(m, n, k, config_index=4)
+    xp, xs, ga = quant.quant_nvfp4(a)
+    yp, ys, gb = quant.quant_nvfp4(b)
+    xp_o, xs_o, ga_o = oracle.quant_nvfp4(a.numpy())     # the torch quantiser must agree bit for bit
+    assert np.array_equal(xp.numpy(), xp_o) and np.array_equal(xs.numpy(), xs_o) and abs(ga - ga_o) < 1e-12
+    got = _run(xp.cuda(), yp.cuda(), xs.cuda(), ys.cuda(), m, n, k, out, ga * gb, config).float().cpu().numpy()
+    ref = oracle.cpu_gemm_nt(oracle.dequant_nvfp4(xp.numpy(), xs.numpy()), oracle.dequant_nvfp4(yp.numpy(), ys.numpy()),
+                             alpha=ga * gb, threads=0)
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= (FP4_TOL if out == "bf16" else 1e-5)
+
+
+def test_scale_placement(b200, oracle):
+    # scales that differ per row and per 16-block expose any mistake in the Tensor-Memory scale layout
+    m, n, k = 256, 384, 256
+    g = torch.Generator().manual_seed(9)
+    xp = torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8)
+    yp = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+    xs = (0x30 + torch.randint(0, 24, (m, k // 16), generator=g)).to(torch.uint8)   # 0.5 .. 3.5
+    ys = (0x30 + torch.randint(0, 24, (n, k // 16), generator=g)).to(torch.uint8)
+    got = _run(xp.cuda(), yp.cuda(), xs.cuda(), ys.cuda(), m, n, k, "f32").cpu().numpy()
+    ref = oracle.cpu_gemm_nt(oracle.dequant_nvfp4(xp.numpy(), xs.numpy()), oracle.dequant_nvfp4(yp.numpy(), ys.numpy()),
+                             threads=0)
+    assert oracle.rel_frobenius(got, ref) <= 1e-5
+
+
+def test_full_size_slabs_and_errors(b200, oracle):
+    # BASELINE config 4: M=4096 (and the decode shape M=16), N=14336, K=4096
+    n, k = 14336, 4096
+    g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 4)
+    b = torch.randn(n, k, device="cuda", generator=g)
+    yp, ys, gb = quant.quant_nvfp4(b)
+    for m in (4096, 16):
+        a = torch.randn(m, k, device="cuda", generator=g)
+        xp, xs, ga = quant.quant_nvfp4(a)
+        z = _run(xp, yp, xs, ys, m, n, k, "bf16", ga * gb)
+        rows = slice(0, 8) if m == 16 else slice(2044, 2052)
+        cols = slice(7100, 7228)
+        ref = oracle.cpu_gemm_nt(oracle.dequant_nvfp4(xp[rows].cpu().numpy(), xs[rows].cpu().numpy()),
+                                 oracle.dequant_nvfp4(yp[cols].cpu().numpy(), ys[cols].cpu().numpy()),
+                                 alpha=ga * gb, threads=0)
+        assert oracle.rel_frobenius(z[rows, cols].float().cpu().numpy(), ref) <= FP4_TOL
+        assert not torch.isnan(z.float()).any()
+    lib = b200
+    rc = lib.b200tile_linear_nvfp4(xp.data_ptr(), yp.data_ptr(), xs.data_ptr(), ys.data_ptr(), z.data_ptr(), b"bf16",
+                                   16, n, k, k // 2, k // 2, n, k // 16, k // 16, 1.0, None, 0, -1, None)
+    assert rc == _lib.ERR_INVALID and b"workspace" in lib.b200tile_last_error()
+    rc = lib.b200tile_linear_nvfp4(xp.data_ptr(), yp.data_ptr(), xs.data_ptr(), ys.data_ptr(), z.data_ptr(), b"bf16",
+                                   16, n, 100, 50, 50, n, 8, 8, 1.0, None, 0, -1, None)
+    assert rc == _lib.ERR_INVALID and b"multiple of 64" in lib.b200tile_last_error()
