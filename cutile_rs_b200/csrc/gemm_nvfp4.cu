@@ -16,6 +16,9 @@
 //   warp 0      TMA producer: A (128 x 128 B), B (BN x 128 B) and both scale blocks per stage
 //   warp 1      issuer: tcgen05.cp of the stage's scales, then 4 block-scaled MMAs (K = 64 each)
 //   warps 2..5  epilogue: tcgen05.ld -> alpha -> bf16/f32 -> global
+#include <mutex>
+
+#include "../../include/b200tile.h"
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
@@ -352,4 +355,71 @@ int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, 
   if (bn == 256 && !out_f32) B200_F4_CASE(256, false);
 #undef B200_F4_CASE
   return b200h::set_error(B200_ERR_UNSUPPORTED, "linear_nvfp4: no kernel for BN = %d", bn);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the scale scratch lives inside the library image.
+//
+// Some callers are not in a position to hand over device memory: code running between
+// cudaStreamBeginCapture and EndCapture on a thread that must not touch an allocator, plugins
+// loaded into a host process whose memory pool they may not draw from, and start-up paths that run
+// before the host's allocator exists.  For them the re-laid-out scales go into the fixed array
+// below instead of a caller workspace.  The price: every GPU that loads this library reserves
+// B200TILE_NVFP4_STATIC_SCRATCH_BYTES for as long as the process lives, problems whose scales do
+// not fit are refused, and all calls on one GPU share the one array -- it still holds the previous
+// call's scales when the next call starts (every word a call reads is first rewritten by that
+// call's own pre-pass, so nothing needs clearing), and two calls that overlap on the GPU (different
+// streams, or graph branches) would overwrite each other's scales.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) uint8_t g_nvfp4_static_scratch[B200TILE_NVFP4_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+uint8_t* g_static_ptr[64] = {};
+
+// In host code `g_nvfp4_static_scratch` is only a handle for the runtime, not a device address;
+// the address a kernel can use comes from cudaGetSymbolAddress, once per device, with that
+// device current.
+int nvfp4_static_scratch_ptr(uint8_t** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return b200h::set_error(B200_ERR_CUDA, "linear_nvfp4_static: no usable CUDA device is current");
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_nvfp4_static_scratch);
+    if (e != cudaSuccess || !p)
+      return b200h::set_error(B200_ERR_CUDA, "linear_nvfp4_static: cudaGetSymbolAddress failed: %s",
+                              cudaGetErrorString(e));
+    g_static_ptr[dev] = static_cast<uint8_t*>(p);
+  }
+  *out = g_static_ptr[dev];
+  return B200_OK;
+}
+}  // namespace
+
+extern "C" int b200tile_linear_nvfp4_static(const void* x, const void* y, const void* x_scales,
+                                            const void* y_scales, void* z, const char* out_dtype, int m,
+                                            int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
+                                            int64_t ld_xs, int64_t ld_ys, float alpha, int config,
+                                            void* cu_stream) {
+  if (m <= 0 || n <= 0 || k <= 0)
+    return b200h::set_error(B200_ERR_INVALID, "linear_nvfp4_static: Shape dimensions must be positive");
+  if (config < -1 || config > 2)
+    return b200h::set_error(B200_ERR_UNSUPPORTED, "linear_nvfp4_static: unknown config %d", config);
+  static const int kBn[3] = {128, 192, 256};
+  const int bn = kBn[config < 0 ? 1 : config];
+  const size_t need = b200::nvfp4_scratch_layout(m, n, k, bn, nullptr);
+  if (need > (size_t)B200TILE_NVFP4_STATIC_SCRATCH_BYTES)
+    return b200h::set_error(B200_ERR_INVALID,
+                            "linear_nvfp4_static: the scales of a %d x %d x %d problem need %llu bytes of "
+                            "scratch, the built-in buffer holds %llu; use b200tile_linear_nvfp4 with a "
+                            "caller workspace",
+                            m, n, k, (unsigned long long)need,
+                            (unsigned long long)B200TILE_NVFP4_STATIC_SCRATCH_BYTES);
+  uint8_t* scratch = nullptr;
+  if (int rc = nvfp4_static_scratch_ptr(&scratch)) return rc;
+  return b200tile_linear_nvfp4(x, y, x_scales, y_scales, z, out_dtype, m, n, k, ldx, ldy, ldz, ld_xs, ld_ys,
+                               alpha, scratch, (uint64_t)B200TILE_NVFP4_STATIC_SCRATCH_BYTES, config,
+                               cu_stream);
 }

@@ -183,6 +183,27 @@ B200TILE_API int b200tile_linear_nvfp4(const void* x, const void* y, const void*
                                        int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
                                        uint64_t workspace_bytes, int config, void* cu_stream);
 
+/* Same computation as b200tile_linear_nvfp4, for callers that cannot provide device memory
+ * (no counterpart in the reference, whose launchers always allocate through their own pool):
+ * code that runs while a stream is being captured and must stay away from any allocator, plugins
+ * that may not draw from their host's memory pool, and start-up code that runs before that pool
+ * exists.  The scale scratch is a fixed array inside the library image, so
+ *   - every GPU that loads the library gives up B200TILE_NVFP4_STATIC_SCRATCH_BYTES until exit;
+ *   - a problem whose re-laid-out scales exceed that size is refused with B200TILE_ERR_INVALID
+ *     (the default config needs about (ceil(M/128)*128 + ceil(N/192)*256) * ceil(K/256)*256 / 16
+ *     bytes: 5.9 MB for 4096 x 14336 x 4096);
+ *   - all calls on one GPU share the array: calls that may overlap on the device (different
+ *     streams, parallel graph branches) race on it and must be serialised by the caller;
+ *   - the first call on each device looks the array's address up (no allocation, but a runtime
+ *     query): make that first call before beginning a stream capture.
+ * It performs no cudaMalloc/cudaFree and calls no allocating library routine. */
+#define B200TILE_NVFP4_STATIC_SCRATCH_BYTES (8u << 20)
+B200TILE_API int b200tile_linear_nvfp4_static(const void* x, const void* y, const void* x_scales,
+                                              const void* y_scales, void* z, const char* out_dtype,
+                                              int m, int n, int k, int64_t ldx, int64_t ldy,
+                                              int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha,
+                                              int config, void* cu_stream);
+
 #ifdef __cplusplus
 }
 #endif
