@@ -18,9 +18,13 @@ namespace b200 {
 
 constexpr int P_BM = 128;   // rows per CTA (256 per pair)
 constexpr int P_BN = 256;   // columns per pair (128 loaded per CTA)
-constexpr int P_BK = 64;
+#ifndef B200_PAIR_BK
+#define B200_PAIR_BK 128
+#endif
+constexpr int P_BK = B200_PAIR_BK;  // 128: two 128-byte swizzle rows per stage, 8 MMAs per pair of commits
+constexpr int P_KH = P_BK / 64;  // 64-wide (128-byte) sub-blocks per stage
 constexpr int P_THREADS = 192;
-constexpr int P_STAGES = 6;
+constexpr int P_STAGES = 384 / P_BK;  // 192 KiB of operand ring per CTA
 
 struct PairSmem {
   static constexpr int A_BYTES = P_BM * P_BK * 2;        // 16 KiB
@@ -116,10 +120,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
           const uint32_t full_leader = mapa_u32(bar_full + stage * 8, 0);
           if (leader) mbar_expect_tx(bar_full + stage * 8, 2 * (L::A_BYTES + L::B_BYTES));
-          tma_load_2d_pair(sA + stage * L::A_BYTES, &tmA, full_leader, kb * P_BK, m0);
+          // A (and a K-major B): one [128 rows][128 B] box per 64-wide k sub-block
+#pragma unroll
+          for (int h = 0; h < P_KH; ++h)
+            tma_load_2d_pair(sA + stage * L::A_BYTES + h * (P_BM * 128), &tmA, full_leader,
+                             kb * P_BK + h * 64, m0);
           if (B_KMAJOR) {
-            tma_load_2d_pair(sB + stage * L::B_BYTES, &tmB, full_leader, kb * P_BK, n0);
+#pragma unroll
+            for (int h = 0; h < P_KH; ++h)
+              tma_load_2d_pair(sB + stage * L::B_BYTES + h * ((P_BN / 2) * 128), &tmB, full_leader,
+                               kb * P_BK + h * 64, n0);
           } else {
+            // N-major B: one [P_BK k-rows][64 columns] box per 64-column chunk
 #pragma unroll
             for (int j = 0; j < P_BN / 2 / 64; ++j)
               tma_load_2d_pair(sB + stage * L::B_BYTES + j * (P_BK * 128), &tmB, full_leader,
@@ -148,8 +160,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                        : make_smem_desc(sB + stage * L::B_BYTES, P_BK * 128, 1024, SWZ_128B);
 #pragma unroll
           for (int k = 0; k < P_BK / 16; ++k) {
-            const uint64_t a_k = adesc + (uint64_t)(k * 2);
-            const uint64_t b_k = bdesc + (uint64_t)(B_KMAJOR ? k * 2 : k * 128);
+            // K-major operands: 32 bytes per step inside a 64-wide sub-block, next sub-block one
+            // [rows][128 B] slab further; N-major B: two 8-row groups (2 x 1024 bytes) per step
+            const uint32_t kmaj_a = (uint32_t)((k & 3) * 2 + (k >> 2) * ((P_BM * 128) >> 4));
+            const uint32_t kmaj_b = (uint32_t)((k & 3) * 2 + (k >> 2) * (((P_BN / 2) * 128) >> 4));
+            const uint64_t a_k = adesc + (uint64_t)kmaj_a;
+            const uint64_t b_k = bdesc + (uint64_t)(B_KMAJOR ? kmaj_b : (uint32_t)(k * 128));
             umma_f16_ss_2cta(d_tmem, a_k, b_k, idesc, (kb | k) != 0);
           }
           // free this stage in both CTAs once the MMAs have read it
@@ -236,11 +252,11 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
       OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmA, tmB, tmC;
   int rc;
-  if ((rc = b200h::encode_tmap_2d(&tmA, dt, 2, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, P_BK,
+  if ((rc = b200h::encode_tmap_2d(&tmA, dt, 2, A, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, 64,
                                   P_BM, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   if (B_KMAJOR)
-    rc = b200h::encode_tmap_2d(&tmB, dt, 2, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, P_BK,
+    rc = b200h::encode_tmap_2d(&tmB, dt, 2, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64,
                                P_BN / 2, CU_TENSOR_MAP_SWIZZLE_128B);
   else
     rc = b200h::encode_tmap_2d(&tmB, dt, 2, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64,
