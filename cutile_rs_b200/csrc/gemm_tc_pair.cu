@@ -8,9 +8,17 @@
 // and write 128 accumulator rows into each CTA's Tensor Memory.  Halving the B operand per SM is
 // what relieves shared-memory bandwidth compared with the single-CTA 128x256 tile.
 //
+// When the tile count does not fill the last wave, that wave's tiles are split along K over all
+// pairs (stream-K): a pair that computes the tail of a tile publishes its fp32 partial to global
+// scratch and raises a flag; the pair that computed the head waits (bounded) and adds it.
+//
 //   warp 0      TMA producer (both CTAs); transaction bytes are counted on the leader's barrier
 //   warp 1      MMA issuer (leader CTA only) -- releases a stage in BOTH CTAs with two commits
 //   warps 2..5  epilogue of this CTA's 128 rows x 256 columns
+#include <stdlib.h>
+
+#include <mutex>
+
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
@@ -50,11 +58,75 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
   bn = (tile % in_group) / gsz;
 }
 
+// Work list of one CTA pair.  The first `sk_tiles` tiles are the partial last wave: their
+// (tile, k-block) units are dealt out evenly ("stream-K"), so a pair may get the tail of one
+// tile, whole tiles and the head of another.  The remaining tiles are whole tiles, strided over
+// the pairs.  Every role of the CTA walks the same list.
+struct PairSched {
+  int nkb, sk_tiles, total_tiles, pair, num_pairs, dp_i;
+  long long u, u_end;
+  __device__ void init(int nkb_, int sk_tiles_, int total_tiles_, int pair_, int num_pairs_) {
+    nkb = nkb_; sk_tiles = sk_tiles_; total_tiles = total_tiles_; pair = pair_; num_pairs = num_pairs_;
+    dp_i = 0;
+    const long long units = (long long)sk_tiles * nkb;
+    u = units * pair / num_pairs;
+    u_end = units * (pair + 1) / num_pairs;
+  }
+  // first stream-K unit of pair q (used to find which pairs contribute to a tile)
+  __device__ long long first_unit(int q) const { return (long long)sk_tiles * nkb * q / num_pairs; }
+  __device__ bool next(int& tile, int& kb0, int& kb1) {
+    if (u < u_end) {
+      tile = (int)(u / nkb);
+      kb0 = (int)(u - (long long)tile * nkb);
+      const long long left = u_end - u;
+      kb1 = (left < (long long)(nkb - kb0)) ? kb0 + (int)left : nkb;
+      u += kb1 - kb0;
+      return true;
+    }
+    const int t = sk_tiles + pair + dp_i * num_pairs;
+    if (t >= total_tiles) return false;
+    ++dp_i;
+    tile = t; kb0 = 0; kb1 = nkb;
+    return true;
+  }
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded wait for another CTA's partial tile (status code 2 = ST_FLAG_TIMEOUT on expiry).
+__device__ __forceinline__ bool wait_flag(const WaitCtx& ctx, const uint32_t* flag, uint32_t epoch) {
+  if (ld_acquire_gpu(flag) == epoch) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 0;; ++it) {
+    if (ld_acquire_gpu(flag) == epoch) return true;
+    if ((it & 0x3F) == 0x3F) {
+      if (*ctx.abort_flag) return false;
+      if (clock64() - t0 > B200_WAIT_LIMIT_CYCLES) break;
+    }
+  }
+  *ctx.abort_flag = 1;
+  if (atomicCAS(ctx.status, 0u, 2u) == 0u) {
+    ctx.status[1] = blockIdx.x;
+    ctx.status[2] = 50;
+    ctx.status[3] = epoch;
+  }
+  return false;
+}
+
+constexpr int P_SLOT_FLOATS = P_BM * P_BN;  // fp32 partial of one CTA: 128 rows x 256 columns
+
 template <bool B_KMAJOR, bool OUT_F16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int group_m,
-                    uint32_t idesc, uint32_t* status) {
+                    uint32_t idesc, uint32_t* status, int sk_tiles, float* sk_partials,
+                    uint32_t* sk_flags, uint32_t sk_epoch) {
   using L = PairSmem;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -111,12 +183,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+      PairSched sched;
+      sched.init(num_kb, sk_tiles, total_tiles, pair, num_pairs);
+      int tile, kb0, kb1;
+      while (ok && sched.next(tile, kb0, kb1)) {
         int bm, bn;
         pair_tile_coords(tile, tiles_m, tiles_n, group_m, bm, bn);
         const int m0 = bm * (2 * P_BM) + (int)rank * P_BM;
         const int n0 = bn * P_BN + (int)rank * (P_BN / 2);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
           const uint32_t full_leader = mapa_u32(bar_full + stage * 8, 0);
           if (leader) mbar_expect_tx(bar_full + stage * 8, 2 * (L::A_BYTES + L::B_BYTES));
@@ -146,12 +221,15 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (leader && lane == 0) {
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+      PairSched sched;
+      sched.init(num_kb, sk_tiles, total_tiles, pair, num_pairs);
+      int tile, kb0, kb1;
+      for (; ok && sched.next(tile, kb0, kb1); ++it) {
         const uint32_t buf = it & 1;
         if (!mbar_wait(wctx, bar_tempty + buf * 8, ((it >> 1) & 1) ^ 1, 2)) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * P_BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
           tc_fence_after_sync();
           const uint64_t adesc = make_smem_desc(sA + stage * L::A_BYTES, 16, 1024, SWZ_128B);
@@ -166,7 +244,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t kmaj_b = (uint32_t)((k & 3) * 2 + (k >> 2) * (((P_BN / 2) * 128) >> 4));
             const uint64_t a_k = adesc + (uint64_t)kmaj_a;
             const uint64_t b_k = bdesc + (uint64_t)(B_KMAJOR ? kmaj_b : (uint32_t)(k * 128));
-            umma_f16_ss_2cta(d_tmem, a_k, b_k, idesc, (kb | k) != 0);
+            umma_f16_ss_2cta(d_tmem, a_k, b_k, idesc, (kb != kb0) || (k != 0));
           }
           // free this stage in both CTAs once the MMAs have read it
           umma_commit_2cta(bar_empty + stage * 8);
@@ -186,7 +264,11 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t tempty_leader = mapa_u32(bar_tempty, 0);
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+    PairSched sched;
+    sched.init(num_kb, sk_tiles, total_tiles, pair, num_pairs);
+    int tile, kb0, kb1;
+    const int etid = threadIdx.x - 64;  // 0..127 inside the epilogue warps
+    for (; ok && sched.next(tile, kb0, kb1); ++it) {
       int bm, bn;
       pair_tile_coords(tile, tiles_m, tiles_n, group_m, bm, bn);
       const int m0 = bm * (2 * P_BM) + (int)rank * P_BM, n0 = bn * P_BN;
@@ -194,6 +276,41 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!mbar_wait(wctx, bar_tfull + buf * 8, (it >> 1) & 1, 4)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * P_BN;
+      const int row = q * 32 + lane;
+      if (kb0 > 0) {
+        // ---- tail/middle segment of a stream-K tile: publish the fp32 partial, column-major so
+        // that the 32 lanes of a warp write 128 contiguous bytes ----
+        float* slot = sk_partials + (size_t)blockIdx.x * P_SLOT_FLOATS;
+#pragma unroll 1
+        for (int c = 0; c < P_BN / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) slot[(c * 32 + i) * P_BM + row] = __uint_as_float(v[i]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_addr(tempty_leader + buf * 8);
+        __threadfence();
+        named_bar_sync(1, 128);
+        if (etid == 0) st_release_gpu(sk_flags + blockIdx.x, sk_epoch);
+        continue;
+      }
+      // ---- head segment (or a whole tile): owner of the output.  For a stream-K head, the pairs
+      // that follow hold the rest of the k range; wait for each and add its partial. ----
+      int q_first = 0, q_last = -1;
+      if (kb1 < num_kb) {
+        q_first = pair + 1;
+        q_last = pair;
+        const long long tile_end = (long long)(tile + 1) * num_kb;
+        while (q_last + 1 < num_pairs && sched.first_unit(q_last + 1) < tile_end) ++q_last;
+        for (int qq = q_first; qq <= q_last && ok; ++qq) {
+          if (sched.first_unit(qq) == sched.first_unit(qq + 1)) continue;  // that pair got no units
+          ok = wait_flag(wctx, sk_flags + (2 * qq + (int)rank), sk_epoch);
+        }
+        if (!ok) break;
+      }
 #pragma unroll 1
       for (int c = 0; c < P_BN / 64; ++c) {
         uint32_t v0[32], v1[32];
@@ -202,20 +319,29 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         tmem_wait_ld();
+        for (int qq = q_first; qq <= q_last; ++qq) {
+          if (sched.first_unit(qq) == sched.first_unit(qq + 1)) continue;
+          const float* part = sk_partials + (size_t)(2 * qq + (int)rank) * P_SLOT_FLOATS + row;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v0[i] = __float_as_uint(__uint_as_float(v0[i]) + __ldcg(part + (c * 64 + i) * P_BM));
+            v1[i] = __float_as_uint(__uint_as_float(v1[i]) + __ldcg(part + (c * 64 + 32 + i) * P_BM));
+          }
+        }
         const uint32_t sbuf = sCw + (c & 1) * L::C_WARP_BYTES;
         const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const uint32_t* src = (j < 4) ? &v0[j * 8] : &v1[(j - 4) * 8];
-          uint32_t p[4];
+          uint32_t pk[4];
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float lo = __uint_as_float(src[2 * e]), hi = __uint_as_float(src[2 * e + 1]);
-            p[e] = OUT_F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+            pk[e] = OUT_F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
           }
           const uint32_t dst = row_addr + ((uint32_t)(j ^ (lane & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(p[0]),
-                       "r"(p[1]), "r"(p[2]), "r"(p[3])
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]),
+                       "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                        : "memory");
         }
         fence_proxy_async_smem();
@@ -240,6 +366,65 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     tmem_dealloc_2cta(tmem_base, 512);
   }
 }
+
+// ---------------------------------------------------------------------------
+// Stream-K scratch: one fp32 partial slot (128 x 256) and one flag per CTA, per (device, stream).
+// Allocated on the first launch that needs it (never while that stream is capturing: the
+// allocation then fails and the launch falls back to whole tiles), kept until process exit.
+// ---------------------------------------------------------------------------
+namespace {
+struct SkScratch {
+  cudaStream_t stream;
+  float* partials;
+  uint32_t* flags;
+  uint32_t epoch;
+  bool used;
+};
+constexpr int kSkPerDevice = 4;
+SkScratch g_sk[64][kSkPerDevice];
+std::mutex g_sk_mu;
+
+SkScratch* sk_scratch_for(int dev, int slots, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(g_sk_mu);
+  for (int i = 0; i < kSkPerDevice; ++i)
+    if (g_sk[dev][i].used && g_sk[dev][i].stream == stream) return &g_sk[dev][i];
+  for (int i = 0; i < kSkPerDevice; ++i) {
+    SkScratch& e = g_sk[dev][i];
+    if (e.used) continue;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    void *p = nullptr, *f = nullptr;
+    if (cudaMalloc(&p, (size_t)slots * P_SLOT_FLOATS * sizeof(float)) != cudaSuccess) {
+      cudaGetLastError();
+      return nullptr;
+    }
+    if (cudaMalloc(&f, (size_t)slots * sizeof(uint32_t)) != cudaSuccess ||
+        cudaMemset(f, 0, (size_t)slots * sizeof(uint32_t)) != cudaSuccess) {
+      cudaGetLastError();
+      cudaFree(p);
+      return nullptr;
+    }
+    e.stream = stream;
+    e.partials = static_cast<float*>(p);
+    e.flags = static_cast<uint32_t*>(f);
+    e.epoch = 0;
+    e.used = true;
+    return &e;
+  }
+  return nullptr;  // more concurrent streams than scratch sets: whole tiles only
+}
+
+bool streamk_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("B200TILE_STREAMK");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+}  // namespace
 
 template <bool B_KMAJOR, bool OUT_F16>
 static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
@@ -273,13 +458,32 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
     attr_done[di->ordinal] = true;
   }
   const int tiles = ((M + 2 * P_BM - 1) / (2 * P_BM)) * ((N + P_BN - 1) / P_BN);
-  int pairs = di->sm_count / 2;
+  const int all_pairs = di->sm_count / 2;
+  int pairs = all_pairs;
   if (tiles < pairs) pairs = tiles;
   if (max_ctas > 0 && pairs > (max_ctas + 1) / 2) pairs = (max_ctas + 1) / 2;
+  // Partial last wave: when whole tiles would leave more than 5 % of the SM-time idle, deal the
+  // k-blocks of the remainder tiles out evenly over all pairs (an explicit grid size keeps the
+  // plain whole-tile schedule).
+  int sk_tiles = 0;
+  SkScratch* sk = nullptr;
+  const int num_kb = (K + P_BK - 1) / P_BK;
+  if (max_ctas <= 0 && streamk_enabled() && tiles > all_pairs && tiles % all_pairs != 0 && num_kb >= 4) {
+    const int waves = (tiles + all_pairs - 1) / all_pairs;
+    if ((double)tiles / ((double)waves * all_pairs) < 0.95) {
+      sk = sk_scratch_for(di->ordinal, 2 * all_pairs, stream);
+      if (sk) {
+        sk_tiles = tiles % all_pairs;
+        pairs = all_pairs;
+        ++sk->epoch;
+      }
+    }
+  }
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
   const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, 2 * P_BM, P_BN);
   kern<<<pairs * 2, P_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, group_m, idesc,
-                                                   di->status);
+                                                   di->status, sk_tiles, sk ? sk->partials : nullptr,
+                                                   sk ? sk->flags : nullptr, sk ? sk->epoch : 0u);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -168,3 +168,22 @@ def test_reference_shaped_launcher_and_errors(b200, oracle):
                             256, 512, 513, 0, 0, 0, 0, 0, 0, 0, _stream().cuda_stream)
     assert rc == _lib.ERR_ALIGN
     launch.gemm(api.zeros([512, 512], "bf16").partition([128, 256]), x, y).compile()   # warm-up only
+
+
+def test_streamk_remainder_wave(b200, oracle):
+    # 8192 x 1024 (the 8-GPU N-split shard) is 128 tiles on 74 CTA pairs: the 54 tiles of the partial
+    # second wave are split along K over all pairs and fixed up through global scratch
+    m, n, k = 8192, 1024, 2048
+    a, b = workloads.gemm_bf16_inputs(m, n, k, config_index=31)
+    ad, bd = a.cuda(), b.cuda()
+    c_sk = _gemm(b200, "bf16", ad, bd, config=2)
+    c_sk2 = _gemm(b200, "bf16", ad, bd, config=2)
+    assert torch.equal(c_sk, c_sk2)                                   # deterministic fix-up order
+    c_whole = _gemm(b200, "bf16", ad, bd, config=2, num_programs=148)   # explicit grid: whole tiles only
+    ref = oracle.cpu_gemm(a[:64].float().numpy(), b.float().numpy(), threads=0)
+    assert oracle.rel_frobenius(c_sk[:64].float().cpu().numpy(), ref) <= BF16_TOL
+    # split-K partial sums differ from one long sum only by fp32 rounding: at most one bf16 ulp apart
+    diff = (c_sk.float() - c_whole.float()).abs().max().item()
+    assert diff <= 2.0 ** -7 * c_whole.float().abs().max().item()
+    assert not torch.isnan(c_sk.float()).any()
+    _status_ok(b200)
