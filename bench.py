@@ -304,6 +304,62 @@ def run_gpu_arm(args):
                 "config": f"bf16 b{B_} h{H_} s{S_} d{D_}, (b*h) split over {world} GPU(s)"}
         del q, kk, v, o
 
+        # ---- block-scaled GEMMs (configs 3 and 4), weight rows (N) split over the ranks ----
+        from cutile_rs_b200 import quant
+
+        def timed(fn, iters=10):
+            for _ in range(3):
+                fn()
+            barrier()
+            e0.record(stream)
+            for _ in range(iters):
+                fn()
+            e1.record(stream)
+            barrier()
+            return sharding.max_over_ranks(e0.elapsed_time(e1), dev) / iters
+
+        g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 3)
+        m8, n8, k8 = 8192, 28672, 8192
+        r0, r1 = sharding.split_range(n8, world, rank, 256)
+        xq, xs = quant.quant_fp8_block(torch.randn(m8, k8, device=dev, generator=g), 1, 128)
+        yq, ys = quant.quant_fp8_block(torch.randn(r1 - r0, k8, device=dev, generator=g), 128, 128)
+        z8 = torch.empty(m8, r1 - r0, dtype=torch.bfloat16, device=dev)
+
+        def f8step():
+            _lib.check(lib.b200tile_linear_fp8_blk128(xq.data_ptr(), yq.data_ptr(), xs.data_ptr(), ys.data_ptr(),
+                                                      z8.data_ptr(), b"bf16", m8, r1 - r0, k8, k8, k8, r1 - r0,
+                                                      k8 // 128, k8 // 128, 1.0, stream.cuda_stream))
+        ms8 = timed(f8step, 5)
+        tf8 = workloads.gemm_flops(m8, n8, k8) / (ms8 * 1e-3) / 1e12
+        extra["gemm_fp8_blk128"] = {"tflops": tf8, "tflops_per_gpu": tf8 / world, "ms": ms8,
+                                    "pct_of_nominal_fp8_peak_4500": 100.0 * tf8 / world / 4500.0,
+                                    "config": f"e4m3 M{m8} N{n8} K{k8}, fp32 scales 1x128 / 128x128, bf16 out, "
+                                              f"N split over {world} GPU(s)"}
+        del xq, xs, yq, ys, z8
+        n4, k4 = 14336, 4096
+        r0, r1 = sharding.split_range(n4, world, rank, 256)
+        yp, ysc, gy = quant.quant_nvfp4(torch.randn(r1 - r0, k4, device=dev, generator=g))
+        for m4 in (4096, 16):
+            xp, xsc, gx = quant.quant_nvfp4(torch.randn(m4, k4, device=dev, generator=g))
+            z4 = torch.empty(m4, r1 - r0, dtype=torch.bfloat16, device=dev)
+            wsb = lib.b200tile_linear_nvfp4_workspace_bytes(m4, r1 - r0, k4)
+            ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+
+            def f4step():
+                _lib.check(lib.b200tile_linear_nvfp4(xp.data_ptr(), yp.data_ptr(), xsc.data_ptr(), ysc.data_ptr(),
+                                                     z4.data_ptr(), b"bf16", m4, r1 - r0, k4, k4 // 2, k4 // 2,
+                                                     r1 - r0, k4 // 16, k4 // 16, gx * gy, ws.data_ptr(), wsb, -1,
+                                                     stream.cuda_stream))
+            ms4 = timed(f4step, 10)
+            tf4 = workloads.gemm_flops(m4, n4, k4) / (ms4 * 1e-3) / 1e12
+            nbytes = (m4 * k4 // 2 + m4 * k4 // 16 + n4 * k4 // 2 + n4 * k4 // 16 + m4 * n4 * 2)
+            extra[f"gemm_nvfp4_m{m4}"] = {"tflops": tf4, "tflops_per_gpu": tf4 / world, "ms": ms4,
+                                          "pct_of_nominal_fp4_peak_9000": 100.0 * tf4 / world / 9000.0,
+                                          "algorithmic_gbs": nbytes / (ms4 * 1e-3) / 1e9,
+                                          "config": f"NVFP4 M{m4} N{n4} K{k4}, e4m3 scale per 16, bf16 out, "
+                                                    f"N split over {world} GPU(s); includes the per-call scale "
+                                                    "re-layout pre-pass"}
+
     peak, hbm_peak, peak_src = measured_peaks()
     if rank == 0:
         cpu = None
