@@ -34,6 +34,11 @@ int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, 
                              void* z, int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                              int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
 
+size_t b200_mxfp8_scratch_bytes(int M, int N, int K);
+int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
+                             int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
+
 using b200h::set_error;
 
 static_assert(B200TILE_ERR_INVALID == B200_ERR_INVALID && B200TILE_ERR_ALIGN == B200_ERR_ALIGN &&
@@ -301,6 +306,44 @@ int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales, co
                      (unsigned long long)need, (unsigned long long)workspace_bytes);
   return b200_gemm_nvfp4_dispatch(bn, out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs,
                                   ld_ys, alpha, workspace, static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---------------------------------------------------------------------------
+// Typed MXFP8 entry point
+// ---------------------------------------------------------------------------
+uint64_t b200tile_linear_mxfp8_workspace_bytes(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  return (uint64_t)b200_mxfp8_scratch_bytes(m, n, k);
+}
+
+int b200tile_linear_mxfp8(const void* x, const void* y, const void* x_scales, const void* y_scales,
+                          void* z, const char* out_dtype, int m, int n, int k, int64_t ldx, int64_t ldy,
+                          int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
+                          uint64_t workspace_bytes, void* cu_stream) {
+  if (!x || !y || !x_scales || !y_scales || !z || !out_dtype)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp8: null argument");
+  if (m <= 0 || n <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp8: Shape dimensions must be positive");
+  if (k % 128 != 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp8: K (%d) must be a multiple of 128", k);
+  if (ldx < k || ldy < k || ldz < n || ld_xs < k / 32 || ld_ys < k / 32)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp8: leading dimension too small");
+  if (ld_xs % 4 != 0 || ld_ys % 4 != 0 || (reinterpret_cast<uintptr_t>(x_scales) & 3) != 0 ||
+      (reinterpret_cast<uintptr_t>(y_scales) & 3) != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_mxfp8: scale rows must be 4-byte aligned");
+  int out_f32;
+  if (!strcmp(out_dtype, "f32")) out_f32 = 1;
+  else if (!strcmp(out_dtype, "bf16")) out_f32 = 0;
+  else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_mxfp8: unsupported output type '%s'", out_dtype);
+  if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_mxfp8: output must be 16-byte aligned with a 16-byte pitch");
+  const size_t need = b200_mxfp8_scratch_bytes(m, n, k);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
+    return set_error(B200TILE_ERR_INVALID,
+                     "linear_mxfp8: workspace of %llu bytes (16-byte aligned) required, got %llu",
+                     (unsigned long long)need, (unsigned long long)workspace_bytes);
+  return b200_gemm_mxfp8_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs, ld_ys,
+                                  alpha, workspace, static_cast<cudaStream_t>(cu_stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -25,20 +25,26 @@
 namespace b200 {
 
 constexpr int F4_BM = 128;
-constexpr int F4_BK = 256;            // elements per stage = 128 bytes = one swizzle row
 constexpr int F4_THREADS = 192;
 
-template <int BN>
+// FP4 = true : NVFP4 (packed e2m1, UE4M3 scale per 16, K = 64 per MMA, 256 elements per stage)
+// FP4 = false: MXFP8 (e4m3, UE8M0 scale per 32, K = 32 per MMA, 128 elements per stage)
+// Either way a stage is 128 bytes per row and 4 MMAs; a 512-byte scale block holds 128 rows x 4
+// scale bytes: one MMA's scales for NVFP4, the whole stage's (one byte per MMA) for MXFP8.
+template <int BN, bool FP4 = true>
 struct Fp4Cfg {
   static constexpr int CHUNKS = (BN + 127) / 128;            // 128-row scale blocks per B tile
-  static constexpr int SF_COLS = 16 + 16 * CHUNKS;           // TMEM columns of one stage's scales
+  static constexpr int KQ_PER_STAGE = FP4 ? 4 : 1;           // scale blocks along K per stage
+  static constexpr int SF_COLS = 4 * KQ_PER_STAGE * (1 + CHUNKS);  // TMEM columns of a stage's scales
   static constexpr int NACC = (2 * BN + 2 * SF_COLS <= 512) ? 2 : 1;
   static constexpr int SF_BASE = NACC * BN;                  // scales sit after the accumulators
   static constexpr int A_BYTES = F4_BM * 128;
   static constexpr int B_BYTES = BN * 128;
-  static constexpr int SFA_BYTES = 4 * 512;
-  static constexpr int SFB_BYTES = 4 * CHUNKS * 512;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int SFA_BYTES = KQ_PER_STAGE * 512;
+  static constexpr int SFB_BYTES = KQ_PER_STAGE * CHUNKS * 512;
+  static constexpr int SFB_COL0 = 4 * KQ_PER_STAGE;          // first TMEM column of the B scales
+  static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;  // bytes landed per stage
+  static constexpr int STAGE_BYTES = (STAGE_TX + 1023) / 1024 * 1024;         // 1024-aligned stride
   static constexpr int STAGES = (BN <= 128) ? 5 : 4;
   static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
@@ -90,18 +96,33 @@ __device__ __forceinline__ void umma_nvfp4_ss(uint32_t d_tmem, uint64_t adesc, u
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_mxfp8_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// MXFP8 descriptor: E4M3 operands (code 0), UE8M0 scales (bit 23); `sf_byte` picks which of the four
+// scale bytes of the TMEM word this K = 32 step uses (A: bits [29,31), B: bits [4,6)).
+__host__ __device__ constexpr uint32_t make_idesc_mxfp8(uint32_t M, uint32_t N, uint32_t sf_byte) {
+  return (sf_byte << 4) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (sf_byte << 29);
+}
 // Block-scaled instruction descriptor: E2M1 operands (code 1 for this kind), UE4M3 scales, K = 64.
 __host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) {
   return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (0u << 23) | ((M >> 4) << 24);
 }
 
-template <int BN, bool OUT_F32>
+template <int BN, bool OUT_F32, bool FP4>
 __global__ void __launch_bounds__(F4_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z,
                   int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
-  using C = Fp4Cfg<BN>;
+  using C = Fp4Cfg<BN, FP4>;
   constexpr int STAGES = C::STAGES;
+  constexpr int STAGE_ELEMS = FP4 ? 256 : 128;  // K elements per 128-byte row
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -143,8 +164,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const int tiles_m = (M + F4_BM - 1) / F4_BM;
   const int tiles_n = (N + BN - 1) / BN;
   const int total_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + F4_BK - 1) / F4_BK;
-  const int kq_count = num_kb * 4;  // 64-element scale blocks along K (scratch is padded to this)
+  const int num_kb = (K + STAGE_ELEMS - 1) / STAGE_ELEMS;
+  const int kq_count = num_kb * C::KQ_PER_STAGE;  // scale blocks along K (scratch is padded to this)
   auto tile_coords = [&](int tile, int& bm, int& bn) {
     const int in_group = group_m * tiles_n;
     const int group = tile / in_group;
@@ -167,7 +188,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
           const uint32_t full = bar_full + stage * 8;
-          mbar_expect_tx(full, C::STAGE_BYTES);
+          mbar_expect_tx(full, C::STAGE_TX);
           tma_load_2d(stage_a(stage), &tmA, full, kb * 128, bm * F4_BM);
           tma_load_2d(stage_b(stage), &tmB, full, kb * 128, bn * BN);
           bulk_load_1d(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
@@ -178,7 +199,6 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_nvfp4(F4_BM, BN);
       uint32_t stage = 0, phase = 0, it = 0, g = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
@@ -193,19 +213,25 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           // this stage's scales: smem -> TMEM (two alternating TMEM regions)
           const uint32_t sf_t = tmem_base + C::SF_BASE + (g & 1) * C::SF_COLS;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < C::KQ_PER_STAGE; ++k) {
             tmem_cp_32x128b_warpx4(sf_t + k * 4, make_smem_desc(stage_sfa(stage) + k * 512, 16, 128, 0));
 #pragma unroll
             for (int c = 0; c < C::CHUNKS; ++c)
-              tmem_cp_32x128b_warpx4(sf_t + 16 + (k * C::CHUNKS + c) * 4,
+              tmem_cp_32x128b_warpx4(sf_t + C::SFB_COL0 + (k * C::CHUNKS + c) * 4,
                                      make_smem_desc(stage_sfb(stage) + (k * C::CHUNKS + c) * 512, 16, 128, 0));
           }
           const uint64_t adesc = make_smem_desc(stage_a(stage), 16, 1024, SWZ_128B);
           const uint64_t bdesc = make_smem_desc(stage_b(stage), 16, 1024, SWZ_128B);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_nvfp4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, sf_t + k * 4,
-                          sf_t + 16 + k * C::CHUNKS * 4, (kb | k) != 0);
+          for (int k = 0; k < 4; ++k) {
+            if (FP4)
+              umma_nvfp4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                            make_idesc_nvfp4(F4_BM, BN), sf_t + k * 4, sf_t + C::SFB_COL0 + k * C::CHUNKS * 4,
+                            (kb | k) != 0);
+            else
+              umma_mxfp8_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                            make_idesc_mxfp8(F4_BM, BN, (uint32_t)k), sf_t, sf_t + C::SFB_COL0, (kb | k) != 0);
+          }
           umma_commit(bar_empty + stage * 8);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -281,8 +307,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 // Bytes of scratch needed for the re-laid-out scales of an (M, N, K) problem with B tiles of BN rows.
-static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offset) {
-  const size_t kq = (size_t)((K + F4_BK - 1) / F4_BK) * 4;
+static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offset, bool fp4 = true) {
+  const size_t kq = fp4 ? (size_t)((K + 255) / 256) * 4 : (size_t)((K + 127) / 128);
   const size_t tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
   const size_t chunks = (BN + 127) / 128;
   const size_t a_bytes = tiles_m * kq * 512;
@@ -290,37 +316,39 @@ static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offs
   return a_bytes + tiles_n * kq * chunks * 512;
 }
 
-template <int BN, bool OUT_F32>
+template <int BN, bool OUT_F32, bool FP4 = true>
 static int launch_nvfp4(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
                         int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha,
                         uint8_t* scratch, cudaStream_t stream) {
-  using C = Fp4Cfg<BN>;
+  using C = Fp4Cfg<BN, FP4>;
   const b200h::DeviceInfo* di = b200h::device_info();
+  const uint64_t row_bytes = FP4 ? (uint64_t)K / 2 : (uint64_t)K;
   if (!di) return B200_ERR_CUDA;
   CUtensorMap tmA, tmB;
   int rc;
-  if ((rc = b200h::encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, (uint64_t)K / 2, (uint64_t)M,
+  if ((rc = b200h::encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, row_bytes, (uint64_t)M,
                                   (uint64_t)ldx, 128, F4_BM, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, (uint64_t)K / 2, (uint64_t)N,
+  if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, row_bytes, (uint64_t)N,
                                   (uint64_t)ldy, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   size_t sfb_off;
-  nvfp4_scratch_layout(M, N, K, BN, &sfb_off);
-  const int kq = ((K + F4_BK - 1) / F4_BK) * 4;
+  nvfp4_scratch_layout(M, N, K, BN, &sfb_off, FP4);
+  const int kq = FP4 ? ((K + 255) / 256) * 4 : (K + 127) / 128;
+  const int kq_valid = FP4 ? K / 64 : K / 128;
   const int tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
   {
     const int64_t words_a = (int64_t)tiles_m * kq * 128;
     const int64_t words_b = (int64_t)tiles_n * kq * C::CHUNKS * 128;
     const int ga = (int)((words_a + 255) / 256 < 4096 ? (words_a + 255) / 256 : 4096);
     const int gb = (int)((words_b + 255) / 256 < 4096 ? (words_b + 255) / 256 : 4096);
-    nvfp4_relayout_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(xs), M, kq, K / 64, ld_xs, F4_BM,
+    nvfp4_relayout_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(xs), M, kq, kq_valid, ld_xs, F4_BM,
                                                          1, tiles_m, reinterpret_cast<uint32_t*>(scratch));
-    nvfp4_relayout_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(ys), N, kq, K / 64, ld_ys, BN,
+    nvfp4_relayout_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, BN,
                                                          C::CHUNKS, tiles_n,
                                                          reinterpret_cast<uint32_t*>(scratch + sfb_off));
   }
-  auto kern = gemm_nvfp4_kernel<BN, OUT_F32>;
+  auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4>;
   static bool attr_done[64] = {};
   if (!attr_done[di->ordinal]) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
@@ -338,6 +366,21 @@ static int launch_nvfp4(const void* x, const void* y, const void* xs, const void
 
 size_t b200_nvfp4_scratch_bytes(int M, int N, int K, int bn) {
   return b200::nvfp4_scratch_layout(M, N, K, bn, nullptr);
+}
+
+size_t b200_mxfp8_scratch_bytes(int M, int N, int K) {
+  return b200::nvfp4_scratch_layout(M, N, K, 224, nullptr, false);
+}
+
+// MXFP8: B tiles of 224 rows -- the widest that keeps two accumulators plus the scales in TMEM
+int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
+                             int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream) {
+  using namespace b200;
+  uint8_t* s = static_cast<uint8_t*>(scratch);
+  if (out_f32)
+    return launch_nvfp4<224, true, false>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
+  return launch_nvfp4<224, false, false>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
 }
 
 int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, const void* xs, const void* ys,

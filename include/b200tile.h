@@ -183,6 +183,20 @@ B200TILE_API int b200tile_linear_nvfp4(const void* x, const void* y, const void*
                                        int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
                                        uint64_t workspace_bytes, int config, void* cu_stream);
 
+/* z[M,N] = alpha * sum_k x[m,k]*xs[m,k/32] * y[n,k]*ys[n,k/32]  (MXFP8 block-scaled linear layer).
+ * Replaces `linear_tile` of cutile-examples/examples/mxfp8.rs:34-64 (`mmaf_scaled` with
+ * f8e8m0fnu scales, cutile/tests/tensor_and_matrix_ops.rs:266-283): x [M,K], y [N,K] f8e4m3fn;
+ * xs [M,K/32], ys [N,K/32] f8e8m0fnu in logical row-major order.
+ *   out_dtype  "bf16" or "f32";  K must be a multiple of 128; leading dimensions in BYTES
+ *   workspace  at least b200tile_linear_mxfp8_workspace_bytes(m, n, k) bytes, 16-byte aligned
+ *              (scale re-layout, as for b200tile_linear_nvfp4) */
+B200TILE_API uint64_t b200tile_linear_mxfp8_workspace_bytes(int m, int n, int k);
+B200TILE_API int b200tile_linear_mxfp8(const void* x, const void* y, const void* x_scales,
+                                       const void* y_scales, void* z, const char* out_dtype, int m,
+                                       int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
+                                       int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
+                                       uint64_t workspace_bytes, void* cu_stream);
+
 /* Same computation as b200tile_linear_nvfp4, for callers that cannot provide device memory
  * (no counterpart in the reference, whose launchers always allocate through their own pool):
  * code that runs while a stream is being captured and must stay away from any allocator, plugins

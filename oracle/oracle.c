@@ -367,6 +367,38 @@ ORACLE_API void oracle_dequant_nvfp4(const uint8_t* packed, const uint8_t* scale
     }
 }
 
+/* MXFP8 (cutile-examples/examples/mxfp8.rs:25-33): e4m3 values with one f8e8m0fnu scale per 32
+ * contiguous K elements, scales row-major [rows, cols/32].  The scale is the smallest power of two
+ * with blockmax/scale <= 448 (exponent byte 127 = 1.0 for an all-zero block); q = e4m3_rne(x/scale). */
+ORACLE_API void oracle_quant_mxfp8(const float* x, int64_t rows, int64_t cols, uint8_t* q, uint8_t* scales) {
+  const int64_t nb = cols / 32;
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t b = 0; b < nb; ++b) {
+      const float* xb = x + r * cols + b * 32;
+      float amax = 0.0f;
+      for (int i = 0; i < 32; ++i) amax = fmaxf(amax, fabsf(xb[i]));
+      int e = 0;
+      if (amax > 0.0f) {
+        int fe;
+        const float fm = frexpf(amax / 448.0f, &fe);   /* amax/448 = fm * 2^fe, fm in [0.5, 1) */
+        e = (fm == 0.5f) ? fe - 1 : fe;                /* ceil(log2(amax/448)) */
+        if (e < -127) e = -127;
+        if (e > 127) e = 127;
+      }
+      scales[r * nb + b] = (uint8_t)(e + 127);
+      const float s = ldexpf(1.0f, e);
+      for (int i = 0; i < 32; ++i) q[r * cols + b * 32 + i] = oracle_f32_to_e4m3(xb[i] / s);
+    }
+}
+
+ORACLE_API void oracle_dequant_mxfp8(const uint8_t* q, const uint8_t* scales, int64_t rows, int64_t cols,
+                                     float* out) {
+  const int64_t nb = cols / 32;
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t c = 0; c < cols; ++c)
+      out[r * cols + c] = oracle_e4m3_to_f32(q[r * cols + c]) * oracle_e8m0_to_f32(scales[r * nb + c / 32]);
+}
+
 /* mmaf_scaled semantics (cutile-book/tutorials/11-nvfp4-inference.md:58-82), NT layout:
  *   z[i,j] = alpha * sum_k  x[i,k]*xs[i,k/V] * y[j,k]*ys[j,k/V]
  * computed here from already-dequantised operands via oracle_cpu_gemm_nt_rows. */

@@ -57,6 +57,8 @@ def lib() -> ctypes.CDLL:
             "oracle_dequant_fp8_block": (None, [u8p, fp, i64, i64, i64, i64, fp]),
             "oracle_quant_nvfp4": (c_float, [fp, i64, i64, u8p, u8p]),
             "oracle_dequant_nvfp4": (None, [u8p, u8p, i64, i64, fp]),
+            "oracle_quant_mxfp8": (None, [fp, i64, i64, u8p, u8p]),
+            "oracle_dequant_mxfp8": (None, [u8p, u8p, i64, i64, fp]),
             "oracle_persistent_num_programs": (c_uint32, [i64, i64, c_int, c_int, c_int, c_int, c_int]),
             "oracle_swizzled_bid": (None, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
             "oracle_max_threads": (c_int, []),
@@ -189,6 +191,26 @@ def dequant_nvfp4(packed, scales) -> np.ndarray:
     out = np.empty((r, c2 * 2), dtype=np.float32)
     lib().oracle_dequant_nvfp4(_p(packed, c_uint8), _p(scales, c_uint8), r, c2 * 2,
                                _p(out, c_float))
+    return out
+
+
+def quant_mxfp8(x):
+    """-> (q [R, C] u8 e4m3 bits, scales [R, C/32] u8 e8m0 bits)."""
+    x = _f32(x)
+    r, c = x.shape
+    assert c % 32 == 0
+    q = np.empty((r, c), dtype=np.uint8)
+    s = np.empty((r, c // 32), dtype=np.uint8)
+    lib().oracle_quant_mxfp8(_p(x, c_float), r, c, _p(q, c_uint8), _p(s, c_uint8))
+    return q, s
+
+
+def dequant_mxfp8(q, s) -> np.ndarray:
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    s = np.ascontiguousarray(s, dtype=np.uint8)
+    r, c = q.shape
+    out = np.empty((r, c), dtype=np.float32)
+    lib().oracle_dequant_mxfp8(_p(q, c_uint8), _p(s, c_uint8), r, c, _p(out, c_float))
     return out
 
 
