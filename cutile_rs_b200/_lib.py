@@ -50,6 +50,16 @@ SIGNATURES = {
                                   c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int64),
                                   POINTER(c_int64), POINTER(c_int64), c_float, c_int, c_int,
                                   c_void_p]),
+    "b200tile_fmha_fwd_dynpos": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                         c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int64),
+                                         POINTER(c_int64), POINTER(c_int64), c_float, c_int, c_void_p,
+                                         c_void_p]),
+    "b200tile_fmha_decode_gqa_split": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                               c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                               c_float, POINTER(c_int64), POINTER(c_int64), POINTER(c_int64),
+                                               POINTER(c_int64), c_int64, POINTER(c_int64), c_void_p]),
+    "b200tile_splitk_reduce_merge": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                             POINTER(c_int64), c_int64, POINTER(c_int64), c_void_p]),
     "b200tile_linear_fp8_blk128": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p,
                                            c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64,
                                            c_int64, c_float, c_void_p]),

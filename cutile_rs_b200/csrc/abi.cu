@@ -23,7 +23,7 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
                            void* o, int batch, int heads, int heads_kv, int q_len, int kv_len,
                            const int64_t* qs, const int64_t* ks, const int64_t* vs,
                            const int64_t* os, float qk_scale, int causal, int input_pos,
-                           cudaStream_t stream);
+                           const uint32_t* pos_ptr, cudaStream_t stream);
 
 int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const float* xs,
                                const float* ys, void* z, int M, int N, int K, int64_t ldx, int64_t ldy,
@@ -38,6 +38,12 @@ size_t b200_mxfp8_scratch_bytes(int M, int N, int K);
 int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
                              int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                              int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
+
+int b200_fmha_decode_dispatch(int dtype, int head_dim, const void* q, const void* k, const void* v, void* att,
+                              float* lse, void* out, const uint32_t* pos, int kv_heads, int group, int kv_cap,
+                              int bn, int splits, float qk_scale, const int64_t* strides, cudaStream_t stream);
+int b200_splitk_merge_dispatch(int dtype, int head_dim, const void* att, const float* lse, void* out, int kv_heads,
+                               int group, int splits, const int64_t* strides, cudaStream_t stream);
 
 using b200h::set_error;
 
@@ -206,11 +212,11 @@ int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b,
 // ---------------------------------------------------------------------------
 // Typed attention entry point
 // ---------------------------------------------------------------------------
-int b200tile_fmha_fwd(const char* dtype, const void* q, const void* k, const void* v, void* out,
-                      int batch, int heads, int heads_kv, int q_len, int kv_len, int head_dim,
-                      const int64_t q_strides[2], const int64_t k_strides[2],
-                      const int64_t v_strides[2], const int64_t o_strides[2], float qk_scale,
-                      int causal, int input_pos, void* cu_stream) {
+static int fmha_fwd_common(const char* dtype, const void* q, const void* k, const void* v, void* out,
+                           int batch, int heads, int heads_kv, int q_len, int kv_len, int head_dim,
+                           const int64_t q_strides[2], const int64_t k_strides[2],
+                           const int64_t v_strides[2], const int64_t o_strides[2], float qk_scale,
+                           int causal, int input_pos, const uint32_t* pos_ptr, void* cu_stream) {
   if (!dtype) return set_error(B200TILE_ERR_INVALID, "fmha: dtype is null");
   if (!q || !k || !v || !out) return set_error(B200TILE_ERR_INVALID, "fmha: null tensor pointer");
   if (!q_strides || !k_strides || !v_strides || !o_strides)
@@ -230,7 +236,86 @@ int b200tile_fmha_fwd(const char* dtype, const void* q, const void* k, const voi
     return set_error(B200TILE_ERR_UNSUPPORTED, "fmha: unsupported element type '%s'", dtype);
   return b200_fmha_fwd_dispatch(dt, head_dim, q, k, v, out, batch, heads, heads_kv, q_len, kv_len,
                                 q_strides, k_strides, v_strides, o_strides, qk_scale,
-                                causal ? 1 : 0, input_pos, static_cast<cudaStream_t>(cu_stream));
+                                causal ? 1 : 0, input_pos, pos_ptr, static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_fmha_fwd(const char* dtype, const void* q, const void* k, const void* v, void* out,
+                      int batch, int heads, int heads_kv, int q_len, int kv_len, int head_dim,
+                      const int64_t q_strides[2], const int64_t k_strides[2],
+                      const int64_t v_strides[2], const int64_t o_strides[2], float qk_scale,
+                      int causal, int input_pos, void* cu_stream) {
+  return fmha_fwd_common(dtype, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, head_dim, q_strides,
+                         k_strides, v_strides, o_strides, qk_scale, causal, input_pos, nullptr, cu_stream);
+}
+
+int b200tile_fmha_fwd_dynpos(const char* dtype, const void* q, const void* k, const void* v, void* out,
+                             int batch, int heads, int heads_kv, int q_len, int kv_len, int head_dim,
+                             const int64_t q_strides[2], const int64_t k_strides[2],
+                             const int64_t v_strides[2], const int64_t o_strides[2], float qk_scale,
+                             int causal, const void* position_start, void* cu_stream) {
+  if (!position_start) return set_error(B200TILE_ERR_INVALID, "fmha_dynpos: position_start is null");
+  if ((reinterpret_cast<uintptr_t>(position_start) & 3) != 0)
+    return set_error(B200TILE_ERR_ALIGN, "fmha_dynpos: position_start must be 4-byte aligned");
+  return fmha_fwd_common(dtype, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, head_dim, q_strides,
+                         k_strides, v_strides, o_strides, qk_scale, causal, 0,
+                         static_cast<const uint32_t*>(position_start), cu_stream);
+}
+
+// ---------------------------------------------------------------------------
+// Typed decode-attention entry points
+// ---------------------------------------------------------------------------
+static int decode_dtype(const char* dtype, const char* who, int* dt) {
+  if (!dtype) return set_error(B200TILE_ERR_INVALID, "%s: dtype is null", who);
+  if (!strcmp(dtype, "bf16")) *dt = 0;
+  else if (!strcmp(dtype, "f16")) *dt = 1;
+  else return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", who, dtype);
+  return B200TILE_OK;
+}
+
+int b200tile_fmha_decode_gqa_split(const char* dtype, const void* q, const void* k, const void* v,
+                                   void* att_partial, float* lse_partial, void* out,
+                                   const void* position_start, int kv_heads, int group, int head_dim,
+                                   int kv_capacity, int bn, int num_kv_splits, float qk_scale,
+                                   const int64_t q_strides[2], const int64_t k_strides[2],
+                                   const int64_t v_strides[2], const int64_t att_strides[2],
+                                   int64_t lse_head_stride, const int64_t out_strides[2], void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "fmha_decode_gqa_split", &dt)) return rc;
+  if (!q || !k || !v || !att_partial || !lse_partial || !position_start || !q_strides || !k_strides ||
+      !v_strides || !att_strides || (out && !out_strides))
+    return set_error(B200TILE_ERR_INVALID, "fmha_decode_gqa_split: null argument");
+  if (kv_heads <= 0 || group <= 0 || kv_capacity <= 0 || bn <= 0 || num_kv_splits <= 0)
+    return set_error(B200TILE_ERR_INVALID, "fmha_decode_gqa_split: Shape dimensions must be positive");
+  if (group > 16)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "fmha_decode_gqa_split: GROUP=%d exceeds 16", group);
+  if (num_kv_splits > 65535)
+    return set_error(B200TILE_ERR_INVALID, "fmha_decode_gqa_split: too many splits");
+  const uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
+                       reinterpret_cast<uintptr_t>(v);
+  if ((al & 15) != 0 || (k_strides[0] % 8) || (k_strides[1] % 8) || (v_strides[0] % 8) || (v_strides[1] % 8) ||
+      (q_strides[0] % 2) || (q_strides[1] % 2))
+    return set_error(B200TILE_ERR_ALIGN, "fmha_decode_gqa_split: q/k/v rows must be 16-byte aligned");
+  const int64_t strides[11] = {q_strides[0], q_strides[1], k_strides[0], k_strides[1], v_strides[0], v_strides[1],
+                               att_strides[0], att_strides[1], lse_head_stride, out ? out_strides[0] : 0,
+                               out ? out_strides[1] : 0};
+  return b200_fmha_decode_dispatch(dt, head_dim, q, k, v, att_partial, lse_partial, out,
+                                   static_cast<const uint32_t*>(position_start), kv_heads, group, kv_capacity, bn,
+                                   num_kv_splits, qk_scale, strides, static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_splitk_reduce_merge(const char* dtype, const void* att_partial, const float* lse_partial, void* out,
+                                 int kv_heads, int group, int head_dim, int num_kv_splits,
+                                 const int64_t att_strides[2], int64_t lse_head_stride,
+                                 const int64_t out_strides[2], void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "splitk_reduce_merge", &dt)) return rc;
+  if (!att_partial || !lse_partial || !out || !att_strides || !out_strides)
+    return set_error(B200TILE_ERR_INVALID, "splitk_reduce_merge: null argument");
+  if (kv_heads <= 0 || group <= 0 || head_dim <= 0 || num_kv_splits <= 0)
+    return set_error(B200TILE_ERR_INVALID, "splitk_reduce_merge: Shape dimensions must be positive");
+  const int64_t strides[5] = {att_strides[0], att_strides[1], lse_head_stride, out_strides[0], out_strides[1]};
+  return b200_splitk_merge_dispatch(dt, head_dim, att_partial, lse_partial, out, kv_heads, group, num_kv_splits,
+                                    strides, static_cast<cudaStream_t>(cu_stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -99,6 +99,7 @@ struct FmhaParams {
   int bh_total;      // batch * heads
   int heads, heads_kv, group;
   int causal, input_pos;
+  const uint32_t* pos_ptr;  // when non-null the causal offset is read from device memory
   int head_group;    // (batch*head) problems scheduled together for L2 reuse of K/V
   float scale_log2;  // qk_scale * log2(e)
 };
@@ -147,6 +148,9 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     bh = chunk * p.head_group + (r - qp * gsz);
     if (p.causal) qp = p.num_q_pairs - 1 - qp;
   }
+  // decode-style callers keep the position of the first query in device memory
+  // (cutile-kernels/src/attention.rs:621-625: `position_start: &Tensor<u32, {[1]}>`)
+  const int input_pos = p.pos_ptr ? (int)__ldg(p.pos_ptr) : p.input_pos;
   const int kv_bh = (bh / p.heads) * p.heads_kv + (bh % p.heads) / p.group;
   const int n_total = (p.kv_len + FA_BN - 1) / FA_BN;
   int q0[2], n_kv[2];
@@ -156,7 +160,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (q0[t] >= p.q_len) {
       n_kv[t] = 0;
     } else if (p.causal) {
-      const int last = (q0[t] + FA_BM - 1 + p.input_pos) / FA_BN + 1;
+      const int last = (q0[t] + FA_BM - 1 + input_pos) / FA_BN + 1;
       n_kv[t] = last < n_total ? last : n_total;
     } else {
       n_kv[t] = n_total;
@@ -311,7 +315,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // last key column this row may see inside this tile (>= 127: nothing masked)
       int lim = p.kv_len - 1 - j * FA_BN;
       if (p.causal) {
-        const int c = row_g + p.input_pos - j * FA_BN;
+        const int c = row_g + input_pos - j * FA_BN;
         lim = c < lim ? c : lim;
       }
       const bool masked_tile = __any_sync(0xffffffffu, lim < FA_BN - 1);
@@ -441,7 +445,7 @@ template <int D, bool OUT_F16>
 static int launch_fmha(const void* q, const void* k, const void* v, void* o, int batch, int heads,
                        int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                        const int64_t* vs, const int64_t* os, float qk_scale, int causal,
-                       int input_pos, cudaStream_t stream) {
+                       int input_pos, const uint32_t* pos_ptr, cudaStream_t stream) {
   using L = FmhaSmem<D>;
   const b200h::DeviceInfo* di = b200h::device_info();
   if (!di) return B200_ERR_CUDA;
@@ -480,6 +484,7 @@ static int launch_fmha(const void* q, const void* k, const void* v, void* o, int
   p.group = heads / heads_kv;
   p.causal = causal;
   p.input_pos = input_pos;
+  p.pos_ptr = pos_ptr;
   p.head_group = 8;
   p.scale_log2 = qk_scale * 1.4426950408889634f;
   const long long ctas = (long long)p.num_q_pairs * p.bh_total;
@@ -497,11 +502,11 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
                            void* o, int batch, int heads, int heads_kv, int q_len, int kv_len,
                            const int64_t* qs, const int64_t* ks, const int64_t* vs,
                            const int64_t* os, float qk_scale, int causal, int input_pos,
-                           cudaStream_t stream) {
+                           const uint32_t* pos_ptr, cudaStream_t stream) {
   using namespace b200;
 #define B200_FA_CASE(D_, F16_)                                                                 \
   return launch_fmha<D_, F16_>(q, k, v, o, batch, heads, heads_kv, q_len, kv_len, qs, ks, vs, \
-                               os, qk_scale, causal, input_pos, stream)
+                               os, qk_scale, causal, input_pos, pos_ptr, stream)
   if (head_dim == 128 && dtype == 0) B200_FA_CASE(128, false);
   if (head_dim == 128 && dtype == 1) B200_FA_CASE(128, true);
   if (head_dim == 64 && dtype == 0) B200_FA_CASE(64, false);

@@ -351,3 +351,46 @@ def nvfp4_workspace(m: int, n: int, k: int) -> torch.Tensor:
     """Scratch buffer large enough for :func:`linear_nvfp4` on an (m, n, k) problem."""
     need = int(_lib.load().b200tile_linear_nvfp4_workspace_bytes(m, n, k))
     return torch.empty(need, dtype=torch.uint8, device="cuda")
+
+
+def _i64x2(a, b):
+    return (ctypes.c_int64 * 2)(int(a), int(b))
+
+
+def fmha_decode_gqa_split(q: Tensor, k: Tensor, v: Tensor, att_partial: Tensor, lse_partial: Tensor,
+                          position_start: Tensor, qk_scale: float, bn: int, num_kv_splits: int,
+                          out: Optional[Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
+    """Split-KV GQA decode attention (`fmha_decode_gqa_split`, cutile-kernels/src/attention.rs:727-901):
+    q [kv_heads, GROUP, D], k/v [kv_heads, kv_capacity, D], scratch att_partial
+    [kv_heads, NUM_KV_SPLITS*GROUP, D] and lse_partial [kv_heads, NUM_KV_SPLITS*GROUP] (f32),
+    position_start a device u32[1].  With ``out`` [kv_heads, GROUP, D] the merge
+    (`splitk_reduce_merge`, :907-1015) runs right behind the split pass on the same stream."""
+    lib = _lib.load()
+    s = stream or torch.cuda.current_stream()
+    heads, group, d = q.shape
+    rc = lib.b200tile_fmha_decode_gqa_split(
+        q.dtype.encode(), q.cu_deviceptr(), k.cu_deviceptr(), v.cu_deviceptr(), att_partial.cu_deviceptr(),
+        lse_partial.cu_deviceptr(), out.cu_deviceptr() if out is not None else None,
+        position_start.cu_deviceptr(), heads, group, d, k.shape[1], int(bn), int(num_kv_splits), float(qk_scale),
+        _i64x2(q.strides[0], q.strides[1]), _i64x2(k.strides[0], k.strides[1]), _i64x2(v.strides[0], v.strides[1]),
+        _i64x2(att_partial.strides[0], att_partial.strides[1]), lse_partial.strides[0],
+        _i64x2(out.strides[0], out.strides[1]) if out is not None else None, c_void_p(s.cuda_stream))
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+    return (att_partial, lse_partial) if out is None else (att_partial, lse_partial, out)
+
+
+def splitk_reduce_merge(att_partial: Tensor, lse_partial: Tensor, out: Tensor, num_kv_splits: int,
+                        stream: Optional[torch.cuda.Stream] = None) -> Tensor:
+    """Merge of split-KV partials (`splitk_reduce_merge`, cutile-kernels/src/attention.rs:907-1015)."""
+    lib = _lib.load()
+    s = stream or torch.cuda.current_stream()
+    heads, group, d = out.shape
+    rc = lib.b200tile_splitk_reduce_merge(out.dtype.encode(), att_partial.cu_deviceptr(), lse_partial.cu_deviceptr(),
+                                          out.cu_deviceptr(), heads, group, d, int(num_kv_splits),
+                                          _i64x2(att_partial.strides[0], att_partial.strides[1]),
+                                          lse_partial.strides[0], _i64x2(out.strides[0], out.strides[1]),
+                                          c_void_p(s.cuda_stream))
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+    return out

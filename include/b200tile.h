@@ -152,6 +152,49 @@ B200TILE_API int b200tile_fmha_fwd(const char* dtype, const void* q, const void*
                                    const int64_t o_strides[2], float qk_scale, int causal,
                                    int input_pos, void* cu_stream);
 
+/* b200tile_fmha_fwd with the causal offset read from DEVICE memory at kernel time, so that a
+ * captured graph can be replayed while the decode position advances.  Replaces the
+ * dynamic-position kernels `fmha_causal` and `flash_attn_causal_seq_dynpos_f16`
+ * (cutile-kernels/src/attention.rs:588-721, 118-226: `position_start: &Tensor<u32, {[1]}>`).
+ * `position_start` points to one u32 = position of query row 0; key j is visible to query i iff
+ * j <= i + *position_start and j < kv_len. */
+B200TILE_API int b200tile_fmha_fwd_dynpos(const char* dtype, const void* q, const void* k, const void* v,
+                                          void* out, int batch, int heads, int heads_kv, int q_len,
+                                          int kv_len, int head_dim, const int64_t q_strides[2],
+                                          const int64_t k_strides[2], const int64_t v_strides[2],
+                                          const int64_t o_strides[2], float qk_scale, int causal,
+                                          const void* position_start, void* cu_stream);
+
+/* Split-KV grouped-query decode attention (one query token per head) and its merge.
+ * Replaces `fmha_decode_gqa_split` and `splitk_reduce_merge`
+ * (cutile-kernels/src/attention.rs:727-901, 907-1015).
+ *   q            [kv_heads, group, D]                 one token, `group` query heads per K/V head
+ *   k, v         [kv_heads, kv_capacity, D]           the KV cache
+ *   att_partial  [kv_heads, num_kv_splits*group, D]   scratch, same element type (split-major)
+ *   lse_partial  [kv_heads, num_kv_splits*group]      scratch, fp32, log2 domain (m + log2 l)
+ *   out          [kv_heads, group, D], or NULL to run the split pass only
+ *   position_start  DEVICE pointer to one u32: keys [0, *position_start + 1) are attended
+ *   bn           key-tile size that defines the split boundaries: split s covers tiles
+ *                [s*ceil(T/S), min((s+1)*ceil(T/S), T)) of T = ceil(s_kv/bn) tiles (attention.rs:774-780)
+ * Strides in ELEMENTS: {head stride, row stride} per tensor; head vectors contiguous; group <= 16;
+ * D in {64, 128}; dtype "bf16" or "f16".  An empty split yields att = 0, lse = -1e30. */
+B200TILE_API int b200tile_fmha_decode_gqa_split(const char* dtype, const void* q, const void* k, const void* v,
+                                                void* att_partial, float* lse_partial, void* out,
+                                                const void* position_start, int kv_heads, int group,
+                                                int head_dim, int kv_capacity, int bn, int num_kv_splits,
+                                                float qk_scale, const int64_t q_strides[2],
+                                                const int64_t k_strides[2], const int64_t v_strides[2],
+                                                const int64_t att_strides[2], int64_t lse_head_stride,
+                                                const int64_t out_strides[2], void* cu_stream);
+
+/* The merge alone (attention.rs:907-1015): out[h,g,:] = sum_s w_s * att_partial[h, s*group+g, :],
+ * w_s = exp2(lse_s - max_s lse) / max(sum_s exp2(lse_s - max), 1e-8). */
+B200TILE_API int b200tile_splitk_reduce_merge(const char* dtype, const void* att_partial, const float* lse_partial,
+                                              void* out, int kv_heads, int group, int head_dim,
+                                              int num_kv_splits, const int64_t att_strides[2],
+                                              int64_t lse_head_stride, const int64_t out_strides[2],
+                                              void* cu_stream);
+
 /* z[M,N] = alpha * sum over 128-deep k-blocks of  xs[m,kb] * ys[n/128,kb] * (x_q[m,kb] . y_q[n,kb]),
  * x_q [M,K] and y_q [N,K] in f8e4m3fn (bit convention cuda-core/src/dtype.rs:25-31,223), one fp32
  * scale per 1x128 block of x (x_scales [M, K/128]) and per 128x128 block of y

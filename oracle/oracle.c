@@ -428,3 +428,99 @@ ORACLE_API void oracle_swizzled_bid(int tile_id, int num_bid_m, int num_bid_n, i
   *bid_m = first_bid_m + (tile_id % actual);
   *bid_n = (tile_id % num_bid_in_group) / actual;
 }
+
+/* ------------------------------------------------------------------------------------------
+ * Split-KV GQA decode attention: cutile-kernels/src/attention.rs:727-901 (`fmha_decode_gqa_split`)
+ * and :907-1015 (`splitk_reduce_merge`), restated tile by tile.  Inputs are floats that already
+ * hold 16-bit-representable values; `is_f16` selects how P and the outputs are rounded.
+ *   q [kv_heads, group, D]; k, v [kv_heads, kv_cap, D]; att [kv_heads, splits*group, D];
+ *   lse [kv_heads, splits*group]; s_kv = position_start + 1.
+ * ------------------------------------------------------------------------------------------ */
+static float round16(float x, int is_f16) {
+  if (is_f16) return (float)(_Float16)x;
+  return oracle_bf16_to_f32(oracle_f32_to_bf16(x));
+}
+
+ORACLE_API void oracle_fmha_decode_gqa_split(const float* q, const float* k, const float* v, float* att,
+                                             float* lse, int64_t kv_heads, int64_t group, int64_t D,
+                                             int64_t kv_cap, int64_t s_kv, int64_t bn, int64_t splits,
+                                             float qk_scale, int is_f16) {
+  const float scale_log2 = qk_scale / logf(2.0f);               /* :760-764 */
+  const int64_t tiles = (s_kv + bn - 1) / bn;                    /* :767 */
+  const int64_t tps = (tiles + splits - 1) / splits;             /* :768 */
+  float* qk = (float*)malloc(sizeof(float) * (size_t)(bn * group));
+  float* l_i = (float*)malloc(sizeof(float) * (size_t)(bn * group));
+  float* acc = (float*)malloc(sizeof(float) * (size_t)(D * group));
+  float* m_i = (float*)malloc(sizeof(float) * (size_t)group);
+  for (int64_t h = 0; h < kv_heads; ++h)
+    for (int64_t sp = 0; sp < splits; ++sp) {
+      const int64_t start = sp * tps;
+      int64_t end = start + tps;
+      if (end > tiles) end = tiles;                              /* :769-771 */
+      for (int64_t g = 0; g < group; ++g) m_i[g] = -1.0e30f;     /* :786-789 */
+      for (int64_t i = 0; i < bn * group; ++i) l_i[i] = 1.0f;    /* :790 */
+      for (int64_t i = 0; i < D * group; ++i) acc[i] = 0.0f;     /* :791 */
+      for (int64_t j = start; j < end; ++j) {
+        for (int64_t n = 0; n < bn; ++n)
+          for (int64_t g = 0; g < group; ++g) {
+            const int64_t key = j * bn + n;
+            float dot = 0.0f;
+            if (key < kv_cap)                                    /* out-of-range tile rows load as zero */
+              for (int64_t d = 0; d < D; ++d)
+                dot += k[(h * kv_cap + key) * D + d] * q[(h * group + g) * D + d];
+            if (j == tiles - 1 && key >= s_kv) dot += -1.0e30f;  /* :832-838 */
+            qk[n * group + g] = dot * scale_log2;                /* :843 */
+          }
+        for (int64_t g = 0; g < group; ++g) {
+          float mx = -INFINITY;
+          for (int64_t n = 0; n < bn; ++n) mx = fmaxf(mx, qk[n * group + g]);
+          const float m_ij = fmaxf(m_i[g], mx);                  /* :847 */
+          const float alpha = exp2f(m_i[g] - m_ij);              /* :854 */
+          for (int64_t n = 0; n < bn; ++n) {
+            const float p = exp2f(qk[n * group + g] - m_ij);     /* :848-850 */
+            l_i[n * group + g] = l_i[n * group + g] * alpha + p; /* :857 */
+            qk[n * group + g] = round16(p, is_f16);              /* :878 */
+          }
+          for (int64_t d = 0; d < D; ++d) acc[d * group + g] *= alpha;   /* :859 */
+          m_i[g] = m_ij;
+        }
+        for (int64_t d = 0; d < D; ++d)                          /* :879 acc += v^T p */
+          for (int64_t g = 0; g < group; ++g) {
+            float a = acc[d * group + g];
+            for (int64_t n = 0; n < bn; ++n) {
+              const int64_t key = j * bn + n;
+              if (key < kv_cap) a += v[(h * kv_cap + key) * D + d] * qk[n * group + g];
+            }
+            acc[d * group + g] = a;
+          }
+      }
+      for (int64_t g = 0; g < group; ++g) {
+        float l_sum = 0.0f;
+        for (int64_t n = 0; n < bn; ++n) l_sum += l_i[n * group + g];    /* :888-889 */
+        const float l_safe = fmaxf(l_sum, 1.0e-8f);                      /* :891-892 */
+        for (int64_t d = 0; d < D; ++d)
+          att[((h * splits + sp) * group + g) * D + d] = round16(acc[d * group + g] / l_safe, is_f16);
+        lse[(h * splits + sp) * group + g] = m_i[g] + log2f(l_safe);     /* :905 */
+      }
+    }
+  free(qk); free(l_i); free(acc); free(m_i);
+}
+
+ORACLE_API void oracle_splitk_reduce_merge(const float* att, const float* lse, float* out, int64_t kv_heads,
+                                           int64_t group, int64_t D, int64_t splits, int is_f16) {
+  for (int64_t h = 0; h < kv_heads; ++h)
+    for (int64_t g = 0; g < group; ++g) {
+      float mx = -INFINITY;
+      for (int64_t s = 0; s < splits; ++s) mx = fmaxf(mx, lse[(h * splits + s) * group + g]);   /* :975 */
+      float sum = 0.0f;
+      for (int64_t s = 0; s < splits; ++s) sum += exp2f(lse[(h * splits + s) * group + g] - mx);
+      const float safe = fmaxf(sum, 1.0e-8f);                                                    /* :983-984 */
+      for (int64_t d = 0; d < D; ++d) {
+        float o = 0.0f;
+        for (int64_t s = 0; s < splits; ++s)
+          o += att[((h * splits + s) * group + g) * D + d] *
+               (exp2f(lse[(h * splits + s) * group + g] - mx) / safe);                           /* :985-1009 */
+        out[(h * group + g) * D + d] = round16(o, is_f16);
+      }
+    }
+}

@@ -59,6 +59,8 @@ def lib() -> ctypes.CDLL:
             "oracle_dequant_nvfp4": (None, [u8p, u8p, i64, i64, fp]),
             "oracle_quant_mxfp8": (None, [fp, i64, i64, u8p, u8p]),
             "oracle_dequant_mxfp8": (None, [u8p, u8p, i64, i64, fp]),
+            "oracle_fmha_decode_gqa_split": (None, [fp, fp, fp, fp, fp, i64, i64, i64, i64, i64, i64, i64, c_float, c_int]),
+            "oracle_splitk_reduce_merge": (None, [fp, fp, fp, i64, i64, i64, i64, c_int]),
             "oracle_persistent_num_programs": (c_uint32, [i64, i64, c_int, c_int, c_int, c_int, c_int]),
             "oracle_swizzled_bid": (None, [c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int)]),
             "oracle_max_threads": (c_int, []),
@@ -123,6 +125,28 @@ def fmha_ref_cpu(q, k, v, qk_scale: float, input_pos: int = 0, query_group_size:
     lib().oracle_fmha_ref_cpu_slab(_p(q, c_float), _p(k, c_float), _p(v, c_float),
                                    _p(out, c_float), b, h, hkv, m, d, qk_scale, input_pos,
                                    query_group_size, int(causal), bh0, bh1, i0, i1, threads)
+    return out
+
+
+def fmha_decode_gqa_split(q, k, v, s_kv: int, bn: int, splits: int, qk_scale: float, is_f16: bool = False):
+    """q [H,G,D], k/v [H,cap,D] -> (att [H, splits*G, D], lse [H, splits*G])."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    h, g, d = q.shape
+    cap = k.shape[1]
+    att = np.zeros((h, splits * g, d), dtype=np.float32)
+    lse = np.zeros((h, splits * g), dtype=np.float32)
+    lib().oracle_fmha_decode_gqa_split(_p(q, c_float), _p(k, c_float), _p(v, c_float), _p(att, c_float),
+                                       _p(lse, c_float), h, g, d, cap, s_kv, bn, splits, qk_scale, int(is_f16))
+    return att, lse
+
+
+def splitk_reduce_merge(att, lse, group: int, is_f16: bool = False) -> np.ndarray:
+    att, lse = _f32(att), _f32(lse)
+    h, sg, d = att.shape
+    splits = sg // group
+    out = np.zeros((h, group, d), dtype=np.float32)
+    lib().oracle_splitk_reduce_merge(_p(att, c_float), _p(lse, c_float), _p(out, c_float), h, group, d, splits,
+                                     int(is_f16))
     return out
 
 

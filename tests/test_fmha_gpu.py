@@ -127,3 +127,22 @@ def test_reference_shaped_launchers(b200, oracle):
     res = launch.fmha_prefill_causal(q2, k2, v2, out2, 1 / math.sqrt(d), 2, s, 0).sync_on(_stream())
     got = res[3].unpartition().to_host().float().permute(1, 0, 2).numpy()
     assert oracle.max_abs(got, ref) <= ATTN_TOL
+
+
+def test_device_side_position_equals_host_side(b200):
+    """`fmha_prefill_gqa` takes its causal offset from a device scalar
+    (cutile-kernels/src/attention.rs:533-540); the result must be the one the host-side
+    `input_pos` gives, bit for bit, and must follow the scalar without a new launch set-up."""
+    b, h, hkv, s, d = 1, 4, 2, 384, 128
+    q, k, v = (t.cuda() for t in workloads.fmha_inputs(b, h, s, d, h_kv=hkv, config_index=91))
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for p in (0, 7, 130):
+        want = _fmha(b200, q, k, v, True, input_pos=p)
+        pos.fill_(p)
+        got = torch.full((b * h, s, d), float("nan"), dtype=q.dtype, device="cuda")
+        _lib.check(b200.b200tile_fmha_fwd_dynpos(b"bf16", q.data_ptr(), k.data_ptr(), v.data_ptr(), got.data_ptr(),
+                                                  b, h, hkv, s, s, d, I64x2(s * d, d), I64x2(s * d, d),
+                                                  I64x2(s * d, d), I64x2(s * d, d), 1.0 / math.sqrt(d), 1,
+                                                  pos.data_ptr(), _stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert torch.equal(got, want)
