@@ -360,6 +360,43 @@ def run_gpu_arm(args):
                                                     f"N split over {world} GPU(s); includes the per-call scale "
                                                     "re-layout pre-pass"}
 
+        del xp, xsc, yp, ysc, z4, ws
+
+        # ---- split-KV GQA decode attention + merge: K/V heads split over the ranks ----
+        HKV, GRP, SKV, DD = 8, 4, 65536, 128
+        h0, h1 = sharding.split_range(HKV, world, rank, 1)
+        hl = h1 - h0
+        if hl > 0:
+            ns = max(1, lib.b200tile_num_sms() // hl)
+            nbuf = 4   # rotate K/V sets (268 MB each at 8 heads) so that no launch finds its keys in L2
+            qd = torch.randn(hl, GRP, DD, generator=g, device=dev).bfloat16()
+            kds = [torch.randn(hl, SKV, DD, generator=g, device=dev).bfloat16() for _ in range(nbuf)]
+            vds = [torch.randn(hl, SKV, DD, generator=g, device=dev).bfloat16() for _ in range(nbuf)]
+            attp = torch.empty(hl, ns * GRP, DD, dtype=torch.bfloat16, device=dev)
+            lsep = torch.empty(hl, ns * GRP, dtype=torch.float32, device=dev)
+            od = torch.empty_like(qd)
+            posd = torch.tensor([SKV - 1], dtype=torch.int32, device=dev)
+            turn = [0]
+
+            def dstep():
+                i = turn[0] = (turn[0] + 1) % nbuf
+                _lib.check(lib.b200tile_fmha_decode_gqa_split(
+                    b"bf16", qd.data_ptr(), kds[i].data_ptr(), vds[i].data_ptr(), attp.data_ptr(), lsep.data_ptr(),
+                    od.data_ptr(), posd.data_ptr(), hl, GRP, DD, SKV, 128, ns, 1.0 / math.sqrt(DD), I2(GRP * DD, DD),
+                    I2(SKV * DD, DD), I2(SKV * DD, DD), I2(ns * GRP * DD, DD), ns * GRP, I2(GRP * DD, DD),
+                    stream.cuda_stream))
+            msd = timed(dstep, 20)
+        else:
+            barrier(); barrier()
+            msd = sharding.max_over_ranks(0.0, dev)
+        kv_bytes = 2 * HKV * SKV * DD * 2
+        gbs = kv_bytes / (msd * 1e-3) / 1e9
+        extra["fmha_decode_gqa_split_merge"] = {
+            "gbs": gbs, "gbs_per_gpu": gbs / world, "us": msd * 1e3,
+            "frac_of_measured_hbm": gbs / world / measured_peaks()[1],
+            "config": f"bf16 kv_heads {HKV} group {GRP} D {DD} s_kv {SKV}, BN 128, splits = SMs / local heads, "
+                      f"split pass + merge per step, kv heads split over {world} GPU(s), K/V sets rotated (inputs > L2)"}
+
     peak, hbm_peak, peak_src = measured_peaks()
     if rank == 0:
         cpu = None

@@ -5,6 +5,7 @@
 
 #include <stdlib.h>
 #include <string.h>
+#include <cuda_fp16.h>
 
 #include "host_common.h"
 
@@ -128,7 +129,8 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
     }
   }
   static const b200tile_config kFmhaConfigs[] = {{0, 128, 128, 0, 2, 1, 1}};
-  if ((!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal")) &&
+  if ((!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal") ||
+       !strcmp(kernel, "fmha_prefill_gqa") || !strcmp(kernel, "fmha_causal")) &&
       (!strcmp(dtype, "bf16") || !strcmp(dtype, "f16"))) {
     tab = kFmhaConfigs;
     n = 1;
@@ -295,6 +297,9 @@ int b200tile_fmha_decode_gqa_split(const char* dtype, const void* q, const void*
   if ((al & 15) != 0 || (k_strides[0] % 8) || (k_strides[1] % 8) || (v_strides[0] % 8) || (v_strides[1] % 8) ||
       (q_strides[0] % 2) || (q_strides[1] % 2))
     return set_error(B200TILE_ERR_ALIGN, "fmha_decode_gqa_split: q/k/v rows must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(att_partial) & 3) || (att_strides[0] % 2) || (att_strides[1] % 2) ||
+      (out && ((reinterpret_cast<uintptr_t>(out) & 3) || (out_strides[0] % 2) || (out_strides[1] % 2))))
+    return set_error(B200TILE_ERR_ALIGN, "fmha_decode_gqa_split: att_partial/out rows must be 4-byte aligned");
   const int64_t strides[11] = {q_strides[0], q_strides[1], k_strides[0], k_strides[1], v_strides[0], v_strides[1],
                                att_strides[0], att_strides[1], lse_head_stride, out ? out_strides[0] : 0,
                                out ? out_strides[1] : 0};
@@ -313,6 +318,9 @@ int b200tile_splitk_reduce_merge(const char* dtype, const void* att_partial, con
     return set_error(B200TILE_ERR_INVALID, "splitk_reduce_merge: null argument");
   if (kv_heads <= 0 || group <= 0 || head_dim <= 0 || num_kv_splits <= 0)
     return set_error(B200TILE_ERR_INVALID, "splitk_reduce_merge: Shape dimensions must be positive");
+  if ((reinterpret_cast<uintptr_t>(att_partial) & 3) || (att_strides[0] % 2) || (att_strides[1] % 2) ||
+      (reinterpret_cast<uintptr_t>(out) & 3) || (out_strides[0] % 2) || (out_strides[1] % 2))
+    return set_error(B200TILE_ERR_ALIGN, "splitk_reduce_merge: att_partial/out rows must be 4-byte aligned");
   const int64_t strides[5] = {att_strides[0], att_strides[1], lse_head_stride, out_strides[0], out_strides[1]};
   return b200_splitk_merge_dispatch(dt, head_dim, att_partial, lse_partial, out, kv_heads, group, num_kv_splits,
                                     strides, static_cast<cudaStream_t>(cu_stream));
@@ -451,6 +459,13 @@ struct ParamReader {
   float f32() {
     if (pos >= n || !p[pos]) { ok = false; return 0; }
     return *static_cast<const float*>(p[pos++]);
+  }
+  // an f16 scalar parameter (two bytes), widened exactly
+  float f16() {
+    if (pos >= n || !p[pos]) { ok = false; return 0; }
+    __half_raw raw;
+    raw.x = *static_cast<const uint16_t*>(p[pos++]);
+    return __half2float(__half(raw));
   }
 };
 
@@ -751,6 +766,162 @@ int launch_linear_fp8_generic(const char* kernel, const char* const* generics, i
                                     z.stride[0], xs.stride[0], ys.stride[0], alpha, stream);
 }
 
+// Serving attention kernels of cutile-kernels/src/attention.rs in their own parameter order.
+// "fmha_prefill_gqa" (:398-582): (q [q_len,q_heads,D], k, v [kv_heads,kv_len,D], out partition
+//    [BM,GROUP,D], qk_scale f32, query_group_size i32, kv_len i32, query_start i32), generics
+//    [T?, BM, BN, D, GROUP, M_EFF, CAUSAL, EVEN_K, LATENCY], grid (q_len/BM, q_heads/GROUP, 1).
+// "fmha_causal" (:588-721): (q [m,h,D], k, v [hkv,n,D], out partition [BM,1,D], qk_scale f16,
+//    query_group_size i32, position_start u32[1]), generics [T?, BM, BN, D, CAUSAL, EVEN_K],
+//    grid (m/BM, h, 1).
+int launch_fmha_serving_generic(const char* kernel, const char* const* generics, int n_generics,
+                                const void* const* params, int n_params, const unsigned grid[3],
+                                void* stream, bool launch) {
+  const bool gqa = !strcmp(kernel, "fmha_prefill_gqa");
+  const char* dtype;
+  long g[9];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 9, &ng) || ng < (gqa ? 6 : 4))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  const long BM = g[0], BN = g[1], D = g[2];
+  const long GROUP = gqa ? g[3] : 1;
+  const long causal = gqa ? g[5] : g[3];
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  if (BM <= 0 || BN <= 0 || GROUP <= 0 || (D != 64 && D != 128))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: D=%ld has no precompiled configuration (64, 128)",
+                     kernel, D);
+  if (gqa && g[4] != BM * GROUP)
+    return set_error(B200TILE_ERR_INVALID, "%s: M_EFF=%ld must equal BM*GROUP=%ld", kernel, g[4],
+                     BM * GROUP);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg q, k, v, o, pos;
+  read_tensor(r, 3, false, q);
+  read_tensor(r, 3, false, k);
+  read_tensor(r, 3, false, v);
+  read_tensor(r, 3, true, o);
+  const float scale = gqa ? r.f32() : r.f16();
+  const int group = r.i32();
+  int kv_len = 0, query_start = 0;
+  if (gqa) {
+    kv_len = r.i32();
+    query_start = r.i32();
+  } else {
+    read_tensor(r, 1, false, pos);
+    kv_len = k.dim[1];
+  }
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int q_len = q.dim[0], heads = q.dim[1], heads_kv = k.dim[0];
+  if (q.dim[2] != D || k.dim[2] != D || v.dim[2] != D || o.dim[2] != D || q.stride[2] != 1 ||
+      k.stride[2] != 1 || v.stride[2] != 1 || o.stride[2] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: head dimension must equal D and be contiguous", kernel);
+  if (group <= 0 || heads != heads_kv * group || kv_len > k.dim[1] || kv_len <= 0 || group % GROUP)
+    return set_error(B200TILE_ERR_INVALID, "%s: inconsistent heads / GROUP / kv_len", kernel);
+  if (o.pdim[0] != BM || o.pdim[1] != GROUP || o.pdim[2] != D)
+    return set_error(B200TILE_ERR_INVALID, "%s: output partition must be [BM, %ld, D]", kernel, GROUP);
+  if (grid[0] != (unsigned)((q_len + BM - 1) / BM) || grid[1] != (unsigned)(heads / GROUP) || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid (%ld, %ld, 1)",
+                     grid[0], grid[1], grid[2], (long)((q_len + BM - 1) / BM), (long)(heads / GROUP));
+  const int64_t qs[2] = {q.stride[1], q.stride[0]}, ks[2] = {k.stride[0], k.stride[1]};
+  const int64_t vs[2] = {v.stride[0], v.stride[1]}, os[2] = {o.stride[1], o.stride[0]};
+  if (gqa)
+    return b200tile_fmha_fwd(dtype, reinterpret_cast<const void*>(q.ptr), reinterpret_cast<const void*>(k.ptr),
+                             reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr), 1, heads,
+                             heads_kv, q_len, kv_len, (int)D, qs, ks, vs, os, scale, causal != 0, query_start,
+                             stream);
+  if (pos.dim[0] < 1) return set_error(B200TILE_ERR_INVALID, "%s: position_start must hold one u32", kernel);
+  return b200tile_fmha_fwd_dynpos(dtype, reinterpret_cast<const void*>(q.ptr), reinterpret_cast<const void*>(k.ptr),
+                                  reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr), 1, heads,
+                                  heads_kv, q_len, kv_len, (int)D, qs, ks, vs, os, scale, causal != 0,
+                                  reinterpret_cast<const void*>(pos.ptr), stream);
+}
+
+// "fmha_decode_gqa_split" (:727-901): (q [kv_heads,GROUP,D], k, v [kv_heads,cap,D], att_out partition
+//    [1,GROUP,D] of [kv_heads,NUM_KV_SPLITS*GROUP,D], lse_out partition [1,GROUP] of
+//    [kv_heads,NUM_KV_SPLITS*GROUP], qk_scale f16, position_start u32[1]), generics
+//    [T?, GROUP, BN, D, NUM_KV_SPLITS, LATENCY], grid (kv_heads, NUM_KV_SPLITS, 1).
+// "splitk_reduce_merge" (:907-1015): (att_partial [kv_heads,NS_GROUP,D], lse_partial [kv_heads,NS_GROUP],
+//    out partition [1,GROUP,CHUNK_D]), generics [T?, GROUP, D, CHUNK_D, NUM_KV_SPLITS, NS_GROUP, LATENCY],
+//    grid (kv_heads, 1, D/CHUNK_D).
+int launch_decode_generic(const char* kernel, const char* const* generics, int n_generics,
+                          const void* const* params, int n_params, const unsigned grid[3], void* stream,
+                          bool launch) {
+  const bool merge = !strcmp(kernel, "splitk_reduce_merge");
+  const char* dtype;
+  long g[8];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 8, &ng) || ng < (merge ? 5 : 4))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  const long GROUP = g[0];
+  const long D = merge ? g[1] : g[2];
+  const long NS = g[3];
+  if (D != 64 && D != 128)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: D=%ld has no precompiled configuration (64, 128)",
+                     kernel, D);
+  if (GROUP <= 0 || GROUP > 16 || NS <= 0)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: GROUP must be 1..16 and NUM_KV_SPLITS positive", kernel);
+  if (merge && (g[4] != NS * GROUP || g[2] <= 0 || D % g[2]))
+    return set_error(B200TILE_ERR_INVALID, "%s: NS_GROUP must equal NUM_KV_SPLITS*GROUP and CHUNK_D divide D",
+                     kernel);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  if (merge) {
+    TensorArg att, lse, o;
+    read_tensor(r, 3, false, att);
+    read_tensor(r, 2, false, lse);
+    read_tensor(r, 3, true, o);
+    if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+    const int heads = o.dim[0];
+    if (att.dim[0] != heads || att.dim[1] != NS * GROUP || att.dim[2] != D || lse.dim[0] != heads ||
+        lse.dim[1] != NS * GROUP || o.dim[1] != GROUP || o.dim[2] != D || att.stride[2] != 1 ||
+        lse.stride[1] != 1 || o.stride[2] != 1)
+      return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+    if (o.pdim[0] != 1 || o.pdim[1] != GROUP || o.pdim[2] != g[2])
+      return set_error(B200TILE_ERR_INVALID, "%s: output partition must be [1, GROUP, CHUNK_D]", kernel);
+    if (grid[0] != (unsigned)heads || grid[1] != 1 || grid[2] != (unsigned)(D / g[2]))
+      return set_error(B200TILE_ERR_INVALID,
+                       "launch grid (%u, %u, %u) does not match the inferred partition grid (%d, 1, %ld)",
+                       grid[0], grid[1], grid[2], heads, (long)(D / g[2]));
+    const int64_t as[2] = {att.stride[0], att.stride[1]}, os[2] = {o.stride[0], o.stride[1]};
+    return b200tile_splitk_reduce_merge(dtype, reinterpret_cast<const void*>(att.ptr),
+                                        reinterpret_cast<const float*>(lse.ptr), reinterpret_cast<void*>(o.ptr),
+                                        heads, (int)GROUP, (int)D, (int)NS, as, lse.stride[0], os, stream);
+  }
+  TensorArg q, k, v, att, lse, pos;
+  read_tensor(r, 3, false, q);
+  read_tensor(r, 3, false, k);
+  read_tensor(r, 3, false, v);
+  read_tensor(r, 3, true, att);
+  read_tensor(r, 2, true, lse);
+  const float scale = r.f16();
+  read_tensor(r, 1, false, pos);
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int heads = q.dim[0];
+  if (q.dim[1] != GROUP || q.dim[2] != D || k.dim[0] != heads || v.dim[0] != heads || k.dim[2] != D ||
+      v.dim[2] != D || v.dim[1] != k.dim[1] || att.dim[0] != heads || att.dim[1] != NS * GROUP ||
+      att.dim[2] != D || lse.dim[0] != heads || lse.dim[1] != NS * GROUP || pos.dim[0] < 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  if (q.stride[2] != 1 || k.stride[2] != 1 || v.stride[2] != 1 || att.stride[2] != 1 || lse.stride[1] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: the last axis of every tensor must be contiguous", kernel);
+  if (att.pdim[0] != 1 || att.pdim[1] != GROUP || att.pdim[2] != D || lse.pdim[0] != 1 || lse.pdim[1] != GROUP)
+    return set_error(B200TILE_ERR_INVALID, "%s: output partitions must be [1, GROUP, D] and [1, GROUP]", kernel);
+  if (grid[0] != (unsigned)heads || grid[1] != (unsigned)NS || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid (%d, %ld, 1)",
+                     grid[0], grid[1], grid[2], heads, NS);
+  const int64_t qs[2] = {q.stride[0], q.stride[1]}, ks[2] = {k.stride[0], k.stride[1]};
+  const int64_t vs[2] = {v.stride[0], v.stride[1]}, as[2] = {att.stride[0], att.stride[1]};
+  return b200tile_fmha_decode_gqa_split(dtype, reinterpret_cast<const void*>(q.ptr),
+                                        reinterpret_cast<const void*>(k.ptr), reinterpret_cast<const void*>(v.ptr),
+                                        reinterpret_cast<void*>(att.ptr), reinterpret_cast<float*>(lse.ptr),
+                                        nullptr, reinterpret_cast<const void*>(pos.ptr), heads, (int)GROUP, (int)D,
+                                        k.dim[1], (int)g[1], (int)NS, scale, qs, ks, vs, as, lse.stride[0], nullptr,
+                                        stream);
+}
+
 }  // namespace
 
 int b200tile_launch(const char* kernel, const char* const* generics, int n_generics,
@@ -766,6 +937,10 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
                                cu_stream, true);
   if (!strcmp(kernel, "linear_tile_fp8_blk128"))
     return launch_linear_fp8_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "fmha_prefill_gqa") || !strcmp(kernel, "fmha_causal"))
+    return launch_fmha_serving_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "fmha_decode_gqa_split") || !strcmp(kernel, "splitk_reduce_merge"))
+    return launch_decode_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -780,6 +955,10 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
                                false);
   if (!strcmp(kernel, "linear_tile_fp8_blk128"))
     return launch_linear_fp8_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "fmha_prefill_gqa") || !strcmp(kernel, "fmha_causal"))
+    return launch_fmha_serving_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "fmha_decode_gqa_split") || !strcmp(kernel, "splitk_reduce_merge"))
+    return launch_decode_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

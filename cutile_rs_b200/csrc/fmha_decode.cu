@@ -7,30 +7,20 @@
 // merge weights the partials by exp2(lse - max lse).
 //
 // The path is HBM-bound (every K/V byte is read once, ~GROUP FLOP per byte), so the design goal is
-// bytes in flight, not tensor throughput: one CTA per (kv head, split), four warps, each warp
-// streaming 16-key steps through its own 4-deep cp.async ring (32 KiB per warp, 128 KiB per CTA)
-// and running a register-resident online softmax with warp-level mma.sync m16n8k16 (queries padded
-// to 16 rows).  tcgen05 would add latency and nothing else here.
+// bytes in flight per SM at the lowest instruction cost, not tensor throughput: one CTA per
+// (kv head, split); every warp owns a private ring of K/V stages filled by TMA (tiled loads with
+// the 128-byte swizzle, one elected lane issues them, completion on a per-stage mbarrier) and runs a
+// register-resident online softmax with warp-level mma.sync m16n8k16 (queries padded to 16 rows)
+// fed by conflict-free ldmatrix reads.  tcgen05 would add latency and nothing else here.
 #include <math_constants.h>
 
 #include "host_common.h"
+#include "sm100_ptx.cuh"
 
 namespace b200 {
 
-constexpr int DEC_WARPS = 4;
-constexpr int DEC_STAGES = 4;
-constexpr int DEC_STEP = 16;  // keys per warp step
-
 __device__ __forceinline__ uint32_t dec_smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -75,27 +65,56 @@ __device__ __forceinline__ float dec_ex2(float x) {
 
 struct DecodeParams {
   const void* q;    // [kv_heads, group, D]
-  const void* k;    // [kv_heads, kv_cap, D]
-  const void* v;
   void* att;        // [kv_heads, splits*group, D]
   float* lse;       // [kv_heads, splits*group]
   const uint32_t* pos;
-  int64_t q_head_stride, q_row_stride, k_head_stride, k_row_stride, v_head_stride, v_row_stride;
+  int64_t q_head_stride, q_row_stride;
   int64_t att_head_stride, att_row_stride, lse_head_stride;
   int group, kv_cap, bn, splits;
   float scale_log2;
 };
 
-template <int D, bool F16>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
-fmha_decode_split_kernel(const DecodeParams p) {
-  constexpr int ROW_BYTES = D * 2;
-  constexpr int CHUNKS = ROW_BYTES / 16;                 // 16-byte chunks per key row
-  constexpr int TILE_BYTES = DEC_STEP * ROW_BYTES;       // one 16-key K (or V) tile
-  constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-  extern __shared__ __align__(128) uint8_t smem[];
+// WARPS warps per CTA, STEP keys per warp step, STAGES ring slots per warp.
+template <int D, int WARPS, int STEP, int STAGES>
+struct DecodeCfg {
+  static constexpr int HALVES = D / 64;               // 128-byte (64-element) column blocks per row
+  static constexpr int SUB = STEP * 128;               // one TMA box: STEP keys x 128 bytes
+  static constexpr int TILE = HALVES * SUB;            // K (or V) tile of one step
+  static constexpr int STAGE = 2 * TILE;
+  static constexpr int RING = STAGES * STAGE;          // per warp
+  static constexpr int BAR_OFF = WARPS * RING;         // mbarriers behind the rings
+  static constexpr int SMEM = BAR_OFF + WARPS * STAGES * 8 + 16 + 1024;  // + abort flag + alignment slack
+  static_assert(SUB % 1024 == 0, "TMA boxes must start on swizzle-atom boundaries");
+  static_assert(WARPS * 16 * D * 4 + WARPS * 32 * 4 <= BAR_OFF, "the cross-warp merge reuses the rings");
+};
+
+template <int D, bool F16, int WARPS, int STEP, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+fmha_decode_split_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                         const DecodeParams p, uint32_t* status) {
+  using C = DecodeCfg<D, WARPS, STEP, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x, split = blockIdx.y;
+  // the merge kernel may be scheduled now; it waits for this grid to finish before it reads
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (lane == 0) {
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+
+  const uint32_t ring = dec_smem_u32(smem) + warp * C::RING;
+  const uint32_t bars = dec_smem_u32(smem) + C::BAR_OFF + warp * STAGES * 8;
+  volatile uint32_t* abort_flag = reinterpret_cast<volatile uint32_t*>(smem + C::BAR_OFF + WARPS * STAGES * 8);
+  WaitCtx wctx{abort_flag, status};
+  if (threadIdx.x == 0) *abort_flag = 0;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) mbar_init(bars + s * 8, 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
 
   // key range of this split: whole BN-key tiles (attention.rs:767-780)
   const int s_kv_raw = (int)__ldg(p.pos) + 1;
@@ -106,13 +125,30 @@ fmha_decode_split_kernel(const DecodeParams p) {
   int key_end = (split * tps + tps) * p.bn;
   if (key_end > s_kv) key_end = s_kv;
   const int n_keys = key_end - key_begin;
-  const int n_steps = n_keys > 0 ? (n_keys + DEC_STEP - 1) / DEC_STEP : 0;
+  const int n_steps = n_keys > 0 ? (n_keys + STEP - 1) / STEP : 0;
+  // this warp takes steps warp, warp + WARPS, ...
+  const int my_steps = n_steps > warp ? (n_steps - warp + WARPS - 1) / WARPS : 0;
 
-  const uint16_t* qh = static_cast<const uint16_t*>(p.q) + (int64_t)head * p.q_head_stride;
-  const uint8_t* kh = static_cast<const uint8_t*>(p.k) + (int64_t)head * p.k_head_stride * 2;
-  const uint8_t* vh = static_cast<const uint8_t*>(p.v) + (int64_t)head * p.v_head_stride * 2;
+  // keys past the cache end read as zero (TMA fill) and are masked; nothing is clamped
+  auto issue_step = [&](int it) {
+    const int stage = it % STAGES;
+    const int key0 = key_begin + (warp + it * WARPS) * STEP;
+    const uint32_t dst = ring + stage * C::STAGE, bar = bars + stage * 8;
+    mbar_expect_tx(bar, C::STAGE);
+#pragma unroll
+    for (int h = 0; h < C::HALVES; ++h) {
+      tma_load_3d(dst + h * C::SUB, &tmK, bar, h * 64, key0, head);
+      tma_load_3d(dst + C::TILE + h * C::SUB, &tmV, bar, h * 64, key0, head);
+    }
+  };
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s)
+      if (s < my_steps) issue_step(s);
+  }
 
   // ---- Q as the A operand: 16 rows (query heads of the group, zero beyond) x D ----
+  const uint16_t* qh = static_cast<const uint16_t*>(p.q) + (int64_t)head * p.q_head_stride;
   const int r0 = lane >> 2, r1 = r0 + 8, kq = (lane & 3) * 2;
   uint32_t qa[D / 16][4];
 #pragma unroll
@@ -124,67 +160,52 @@ fmha_decode_split_kernel(const DecodeParams p) {
     qa[ks][3] = r1 < p.group ? *reinterpret_cast<const uint32_t*>(qh + (int64_t)r1 * p.q_row_stride + c1) : 0u;
   }
 
-  uint8_t* my_ring = smem + warp * (DEC_STAGES * STAGE_BYTES);
-  const uint32_t ring = dec_smem_u32(my_ring);
-  auto issue_step = [&](int step, int stage) {
-    // 16 keys x CHUNKS chunks for K and for V; lanes take consecutive 16-byte chunks
-    const int key0 = key_begin + step * DEC_STEP;
+  // per-lane ldmatrix offsets inside a box: row*128 + ((chunk ^ row) << 4), chunk = j*2 + bit
+  const int mid = lane >> 3, row = lane & 7;
+  uint32_t offk[4], offv[4];
 #pragma unroll
-    for (int i = lane; i < DEC_STEP * CHUNKS; i += 32) {
-      const int row = i / CHUNKS, ch = i % CHUNKS;
-      int key = key0 + row;
-      if (key >= p.kv_cap) key = p.kv_cap - 1;  // stay inside the cache; such keys are masked
-      const uint32_t dst = ring + stage * STAGE_BYTES + row * ROW_BYTES + ((ch ^ (row & 7)) << 4);
-      cp_async16(dst, kh + (int64_t)key * p.k_row_stride * 2 + ch * 16);
-      cp_async16(dst + TILE_BYTES, vh + (int64_t)key * p.v_row_stride * 2 + ch * 16);
-    }
-  };
+  for (int j = 0; j < 4; ++j) {
+    offk[j] = ((mid >> 1) * 8 + row) * 128 + (((j * 2 + (mid & 1)) ^ row) << 4);   // keys by mid>>1, chunk by mid&1
+    offv[j] = ((mid & 1) * 8 + row) * 128 + (((j * 2 + (mid >> 1)) ^ row) << 4);   // keys by mid&1, chunk by mid>>1
+  }
 
   float m_run[2] = {-CUDART_INF_F, -CUDART_INF_F}, l_run[2] = {0.0f, 0.0f};
   float o[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
 
-  // steps warp, warp + 4, ... ; prologue fills STAGES-1 slots
-  const int my_steps = n_steps > warp ? (n_steps - warp + DEC_WARPS - 1) / DEC_WARPS : 0;
-#pragma unroll
-  for (int s = 0; s < DEC_STAGES - 1; ++s) {
-    if (s < my_steps) issue_step(warp + s * DEC_WARPS, s);
-    cp_async_commit();
-  }
+  bool alive = true;
   for (int it = 0; it < my_steps; ++it) {
-    const int stage = it % DEC_STAGES;
-    const int pre = it + DEC_STAGES - 1;
-    if (pre < my_steps) issue_step(warp + pre * DEC_WARPS, pre % DEC_STAGES);
-    cp_async_commit();
-    cp_async_wait<DEC_STAGES - 1>();
-    __syncwarp();
-    const uint32_t sK = ring + stage * STAGE_BYTES, sV = sK + TILE_BYTES;
-    const int key0 = key_begin + (warp + it * DEC_WARPS) * DEC_STEP;
+    const int stage = it % STAGES;
+    if (!mbar_wait(wctx, bars + stage * 8, (uint32_t)(it / STAGES) & 1u, 70u + (uint32_t)stage)) {
+      alive = false;
+      break;
+    }
+    const uint32_t sK = ring + stage * C::STAGE, sV = sK + C::TILE;
+    const int key0 = key_begin + (warp + it * WARPS) * STEP;
 
-    // S[16 q x 16 keys] = Q K^T
-    float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-    {
-      const int mid = lane >> 3, row = lane & 7;
-      const int key = (mid >> 1) * 8 + row;
+    // S[16 q x STEP keys] = Q K^T
+    float s[STEP / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < STEP / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+    for (int kb = 0; kb < STEP / 16; ++kb)
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
-        const int ch = ks * 2 + (mid & 1);
-        uint32_t kb[4];
-        ldsm_x4(sK + key * ROW_BYTES + ((ch ^ (key & 7)) << 4), kb);
-        mma16816<F16>(s[0], qa[ks], kb[0], kb[1]);
-        mma16816<F16>(s[1], qa[ks], kb[2], kb[3]);
+        uint32_t kf[4];
+        ldsm_x4(sK + (ks >> 2) * C::SUB + kb * 2048 + offk[ks & 3], kf);
+        mma16816<F16>(s[kb * 2], qa[ks], kf[0], kf[1]);
+        mma16816<F16>(s[kb * 2 + 1], qa[ks], kf[2], kf[3]);
       }
-    }
-    // scale, mask keys past the end of the range, online softmax per query row
+    // scale, mask keys past the end of the range (last step only), online softmax per query row
+    const bool ragged = key0 + STEP > key_end;
     float tmax[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt)
+    for (int nt = 0; nt < STEP / 8; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int key = key0 + nt * 8 + kq + (e & 1);
         float x = s[nt][e] * p.scale_log2;
-        if (key >= key_end) x = -CUDART_INF_F;
+        if (ragged && key0 + nt * 8 + kq + (e & 1) >= key_end) x = -CUDART_INF_F;
         s[nt][e] = x;
         tmax[e >> 1] = fmaxf(tmax[e >> 1], x);
       }
@@ -199,7 +220,7 @@ fmha_decode_split_kernel(const DecodeParams p) {
       m_run[h] = m_new;
       float sum = 0.0f;
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
+      for (int nt = 0; nt < STEP / 8; ++nt) {
         const float a = dec_ex2(s[nt][2 * h] - m_use), b = dec_ex2(s[nt][2 * h + 1] - m_use);
         s[nt][2 * h] = a;
         s[nt][2 * h + 1] = b;
@@ -207,35 +228,36 @@ fmha_decode_split_kernel(const DecodeParams p) {
       }
       l_run[h] = l_run[h] * alpha[h] + sum;
     }
-    // P (16 q x 16 keys, rounded to the 16-bit type: attention.rs:866-868) as the A operand
-    uint32_t pa[4];
-    pa[0] = pack16<F16>(s[0][0], s[0][1]);
-    pa[1] = pack16<F16>(s[0][2], s[0][3]);
-    pa[2] = pack16<F16>(s[1][0], s[1][1]);
-    pa[3] = pack16<F16>(s[1][2], s[1][3]);
-    // O = O * alpha + P V
-    {
-      const int mid = lane >> 3, row = lane & 7;
-      const int key = (mid & 1) * 8 + row;
+    // O *= alpha, skipped while no row of the warp raised its running maximum
+    if (!__all_sync(0xffffffffu, alpha[0] == 1.0f && alpha[1] == 1.0f)) {
 #pragma unroll
-      for (int c = 0; c < D / 16; ++c) {
-        const int ch = c * 2 + (mid >> 1);
-        uint32_t vb[4];
-        ldsm_x4_trans(sV + key * ROW_BYTES + ((ch ^ (key & 7)) << 4), vb);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          float (&acc)[4] = o[c * 2 + half];
-          acc[0] *= alpha[0];
-          acc[1] *= alpha[0];
-          acc[2] *= alpha[1];
-          acc[3] *= alpha[1];
-          mma16816<F16>(acc, pa, vb[half * 2], vb[half * 2 + 1]);
-        }
+      for (int i = 0; i < D / 8; ++i) {
+        o[i][0] *= alpha[0];
+        o[i][1] *= alpha[0];
+        o[i][2] *= alpha[1];
+        o[i][3] *= alpha[1];
       }
     }
-    __syncwarp();
+    // O += P V, P (16 q x 16 keys per k-step) rounded to the 16-bit type (attention.rs:866-868)
+#pragma unroll
+    for (int kb = 0; kb < STEP / 16; ++kb) {
+      uint32_t pa[4];
+      pa[0] = pack16<F16>(s[kb * 2][0], s[kb * 2][1]);
+      pa[1] = pack16<F16>(s[kb * 2][2], s[kb * 2][3]);
+      pa[2] = pack16<F16>(s[kb * 2 + 1][0], s[kb * 2 + 1][1]);
+      pa[3] = pack16<F16>(s[kb * 2 + 1][2], s[kb * 2 + 1][3]);
+#pragma unroll
+      for (int c = 0; c < D / 16; ++c) {
+        uint32_t vf[4];
+        ldsm_x4_trans(sV + (c >> 2) * C::SUB + kb * 2048 + offv[c & 3], vf);
+        mma16816<F16>(o[c * 2], pa, vf[0], vf[1]);
+        mma16816<F16>(o[c * 2 + 1], pa, vf[2], vf[3]);
+      }
+    }
+    __syncwarp();  // every lane is done reading the slot before it is refilled
+    if (lane == 0 && it + STAGES < my_steps) issue_step(it + STAGES);
   }
-  cp_async_wait<0>();
+  (void)alive;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -243,10 +265,10 @@ fmha_decode_split_kernel(const DecodeParams p) {
   }
   __syncthreads();  // every warp is done with its ring: reuse shared memory for the merge
 
-  // ---- combine the four warps' (m, l, O) ----
+  // ---- combine the warps' (m, l, O) ----
   float* sm_m = reinterpret_cast<float*>(smem);                 // [warps][16]
-  float* sm_l = sm_m + DEC_WARPS * 16;                          // [warps][16]
-  float* sm_o = sm_l + DEC_WARPS * 16;                          // [warps][16][D]
+  float* sm_l = sm_m + WARPS * 16;                              // [warps][16]
+  float* sm_o = sm_l + WARPS * 16;                              // [warps][16][D]
   if ((lane & 3) == 0) {
     sm_m[warp * 16 + r0] = m_run[0];
     sm_m[warp * 16 + r1] = m_run[1];
@@ -256,85 +278,168 @@ fmha_decode_split_kernel(const DecodeParams p) {
 #pragma unroll
   for (int nt = 0; nt < D / 8; ++nt) {
     float* base = sm_o + (warp * 16) * D + nt * 8 + kq;
-    base[r0 * D] = o[nt][0];
-    base[r0 * D + 1] = o[nt][1];
-    base[r1 * D] = o[nt][2];
-    base[r1 * D + 1] = o[nt][3];
+    if (r0 < p.group) *reinterpret_cast<float2*>(base + r0 * D) = make_float2(o[nt][0], o[nt][1]);
+    if (r1 < p.group) *reinterpret_cast<float2*>(base + r1 * D) = make_float2(o[nt][2], o[nt][3]);
   }
   __syncthreads();
   uint16_t* att = static_cast<uint16_t*>(p.att) + (int64_t)head * p.att_head_stride +
                   (int64_t)(split * p.group) * p.att_row_stride;
   float* lse = p.lse + (int64_t)head * p.lse_head_stride + split * p.group;
-  for (int idx = threadIdx.x; idx < p.group * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx % D;
+  for (int idx = threadIdx.x; idx < p.group * (D / 2); idx += blockDim.x) {
+    const int g = idx / (D / 2), d = (idx % (D / 2)) * 2;
     float m_all = -CUDART_INF_F;
 #pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) m_all = fmaxf(m_all, sm_m[w * 16 + g]);
-    float l_all = 0.0f, acc = 0.0f;
+    for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, sm_m[w * 16 + g]);
+    float l_all = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
     if (m_all != -CUDART_INF_F) {
 #pragma unroll
-      for (int w = 0; w < DEC_WARPS; ++w) {
+      for (int w = 0; w < WARPS; ++w) {
         const float wgt = dec_ex2(sm_m[w * 16 + g] - m_all);
+        const float2 ov = *reinterpret_cast<const float2*>(sm_o + (w * 16 + g) * D + d);
         l_all += sm_l[w * 16 + g] * wgt;
-        acc += sm_o[(w * 16 + g) * D + d] * wgt;
+        acc0 += ov.x * wgt;
+        acc1 += ov.y * wgt;
       }
     }
     // an empty split contributes nothing: att = 0, lse = -1e30 (attention.rs:790-795 start values)
     const float l_safe = fmaxf(l_all, 1e-8f);
-    const float val = m_all == -CUDART_INF_F ? 0.0f : acc / l_safe;
-    att[(int64_t)g * p.att_row_stride + d] = (uint16_t)(pack16<F16>(val, 0.0f) & 0xFFFF);
-    if (d == 0) lse[g] = m_all == -CUDART_INF_F ? -1.0e30f : m_all + log2f(l_safe);
+    const bool empty = m_all == -CUDART_INF_F;
+    *reinterpret_cast<uint32_t*>(att + (int64_t)g * p.att_row_stride + d) =
+        empty ? 0u : pack16<F16>(acc0 / l_safe, acc1 / l_safe);
+    if (d == 0) lse[g] = empty ? -1.0e30f : m_all + log2f(l_safe);
   }
 }
 
-// out[head][g][d] = sum_s w_s att[head][s*group+g][d],  w_s = exp2(lse_s - max) / max(sum, 1e-8)
-template <bool F16>
-__global__ void splitk_reduce_merge_kernel(const void* att, const float* lse, void* out, int group, int D,
-                                           int splits, int64_t att_head_stride, int64_t att_row_stride,
-                                           int64_t lse_head_stride, int64_t out_head_stride,
-                                           int64_t out_row_stride) {
-  const int head = blockIdx.x;
+// out[head][g][d] = sum_s w_s att[head][s*group+g][d],  w_s = exp2(lse_s - max) / max(sum, 1e-8).
+// One CTA per (kv head, query head of the group): 128 threads = (D/VEC column lanes) x (split lanes);
+// every split lane walks its share of the splits with VEC-element loads, shared memory adds the lanes.
+template <bool F16, int VEC>
+__global__ void __launch_bounds__(128)
+splitk_reduce_merge_kernel(const void* att, const float* lse, void* out, int group, int D, int splits,
+                           int64_t att_head_stride, int64_t att_row_stride, int64_t lse_head_stride,
+                           int64_t out_head_stride, int64_t out_row_stride) {
+  __shared__ float s_red[4];
+  __shared__ float s_acc[128 * VEC];   // [split lanes][D]
+  __shared__ float s_w[128];
+  // when launched as a programmatic dependent of the split pass: wait until its results are visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int head = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
   const uint16_t* a = static_cast<const uint16_t*>(att) + (int64_t)head * att_head_stride;
-  const float* l = lse + (int64_t)head * lse_head_stride;
-  uint16_t* o = static_cast<uint16_t*>(out) + (int64_t)head * out_head_stride;
-  for (int idx = threadIdx.x; idx < group * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx % D;
-    float mx = -CUDART_INF_F;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, l[s * group + g]);
-    float sum = 0.0f, acc = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-      const float w = exp2f(l[s * group + g] - mx);
-      sum += w;
-      acc += w * unpack16<F16>(a[(int64_t)(s * group + g) * att_row_stride + d]);
+  const float* l = lse + (int64_t)head * lse_head_stride + g;
+  float mx = -CUDART_INF_F;
+  for (int s = tid; s < splits; s += 128) mx = fmaxf(mx, l[s * group]);
+#pragma unroll
+  for (int off = 16; off; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  if ((tid & 31) == 0) s_red[tid >> 5] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+
+  const int col_lanes = D / VEC, split_lanes = 128 / col_lanes;
+  const int cl = tid % col_lanes, sl = tid / col_lanes;
+  float acc[VEC], wsum = 0.0f;
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0.0f;
+  for (int s = sl; s < splits; s += split_lanes) {
+    const float w = exp2f(l[s * group] - mx);
+    const uint16_t* src = a + (int64_t)(s * group + g) * att_row_stride + cl * VEC;
+    uint32_t raw[VEC / 2];
+    if (VEC == 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(src);
+      raw[0] = v.x; raw[1] = v.y; raw[VEC / 2 - 2] = v.z; raw[VEC / 2 - 1] = v.w;
+    } else {
+      raw[0] = *reinterpret_cast<const uint32_t*>(src);
     }
-    const float val = acc / fmaxf(sum, 1e-8f);
-    o[(int64_t)g * out_row_stride + d] = (uint16_t)(pack16<F16>(val, 0.0f) & 0xFFFF);
+#pragma unroll
+    for (int j = 0; j < VEC / 2; ++j) {
+      acc[2 * j] += w * unpack16<F16>((uint16_t)(raw[j] & 0xFFFF));
+      acc[2 * j + 1] += w * unpack16<F16>((uint16_t)(raw[j] >> 16));
+    }
+    wsum += w;
+  }
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) s_acc[sl * D + cl * VEC + j] = acc[j];
+  if (cl == 0) s_w[sl] = wsum;
+  __syncthreads();
+  if (tid < D / 2) {
+    float v0 = 0.0f, v1 = 0.0f, wt = 0.0f;
+    for (int i = 0; i < split_lanes; ++i) {
+      v0 += s_acc[i * D + 2 * tid];
+      v1 += s_acc[i * D + 2 * tid + 1];
+      wt += s_w[i];
+    }
+    const float inv = 1.0f / fmaxf(wt, 1e-8f);
+    uint16_t* o = static_cast<uint16_t*>(out) + (int64_t)head * out_head_stride + (int64_t)g * out_row_stride;
+    *reinterpret_cast<uint32_t*>(o + 2 * tid) = pack16<F16>(v0 * inv, v1 * inv);
   }
 }
 
-template <int D, bool F16>
-static int launch_decode(const DecodeParams& p, int kv_heads, void* out, int64_t out_head_stride,
-                         int64_t out_row_stride, cudaStream_t stream) {
+template <bool F16>
+static int launch_merge(const void* att, const float* lse, void* out, int kv_heads, int group, int D, int splits,
+                        int64_t att_head_stride, int64_t att_row_stride, int64_t lse_head_stride,
+                        int64_t out_head_stride, int64_t out_row_stride, bool dependent, cudaStream_t stream) {
+  const bool vec8 = (reinterpret_cast<uintptr_t>(att) % 16 == 0) && att_head_stride % 8 == 0 && att_row_stride % 8 == 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kv_heads, group);
+  cfg.blockDim = dim3(128);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dependent ? 1 : 0;
+  if (vec8)
+    B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, splitk_reduce_merge_kernel<F16, 8>, att, lse, out, group, D, splits,
+                                       att_head_stride, att_row_stride, lse_head_stride, out_head_stride,
+                                       out_row_stride));
+  else
+    B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, splitk_reduce_merge_kernel<F16, 2>, att, lse, out, group, D, splits,
+                                       att_head_stride, att_row_stride, lse_head_stride, out_head_stride,
+                                       out_row_stride));
+  return B200_OK;
+}
+
+struct DecodeHostArgs {
+  const void* k;
+  const void* v;
+  int64_t k_head_stride, k_row_stride, v_head_stride, v_row_stride;
+  int kv_heads;
+  void* out;
+  int64_t out_head_stride, out_row_stride;
+};
+
+template <int D, bool F16, int WARPS, int STEP, int STAGES>
+static int launch_decode_variant(const DecodeParams& p, const DecodeHostArgs& h, cudaStream_t stream) {
+  using C = DecodeCfg<D, WARPS, STEP, STAGES>;
   const b200h::DeviceInfo* di = b200h::device_info();
   if (!di) return B200_ERR_CUDA;
-  constexpr int SMEM = DEC_WARPS * DEC_STAGES * 2 * DEC_STEP * D * 2;
-  static_assert(SMEM >= (int)((DEC_WARPS * 32 + DEC_WARPS * 16 * D) * sizeof(float)), "merge area must fit");
-  auto kern = fmha_decode_split_kernel<D, F16>;
+  const CUtensorMapDataType dt = F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tmK, tmV;
+  int rc;
+  if ((rc = b200h::encode_tmap_3d(&tmK, dt, 2, h.k, D, p.kv_cap, h.kv_heads, h.k_row_stride * 2, h.k_head_stride * 2,
+                                  64, STEP, 1, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_3d(&tmV, dt, 2, h.v, D, p.kv_cap, h.kv_heads, h.v_row_stride * 2, h.v_head_stride * 2,
+                                  64, STEP, 1, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  auto kern = fmha_decode_split_kernel<D, F16, WARPS, STEP, STAGES>;
   static bool attr_done[64] = {};
   if (!attr_done[di->ordinal]) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
     attr_done[di->ordinal] = true;
   }
-  kern<<<dim3(kv_heads, p.splits), DEC_WARPS * 32, SMEM, stream>>>(p);
+  kern<<<dim3(h.kv_heads, p.splits), WARPS * 32, C::SMEM, stream>>>(tmK, tmV, p, di->status);
   B200_CUDA_CHECK(cudaGetLastError());
-  if (out) {
-    splitk_reduce_merge_kernel<F16><<<kv_heads, 128, 0, stream>>>(p.att, p.lse, out, p.group, D, p.splits,
-                                                                 p.att_head_stride, p.att_row_stride,
-                                                                 p.lse_head_stride, out_head_stride,
-                                                                 out_row_stride);
-    B200_CUDA_CHECK(cudaGetLastError());
-  }
+  if (h.out)
+    return launch_merge<F16>(p.att, p.lse, h.out, h.kv_heads, p.group, D, p.splits, p.att_head_stride,
+                             p.att_row_stride, p.lse_head_stride, h.out_head_stride, h.out_row_stride, true, stream);
   return B200_OK;
+}
+
+// Eight warps of 16-key steps with three ring slots each (192 KiB of K/V in flight per SM for
+// D = 128) measured best among {4 warps x 32 keys x 3, 8 x 16 x 3, 4 x 16 x 6}.
+template <int D, bool F16>
+static int launch_decode(const DecodeParams& p, const DecodeHostArgs& h, cudaStream_t stream) {
+  return launch_decode_variant<D, F16, 8, 16, 3>(p, h, stream);
 }
 
 }  // namespace b200
@@ -345,15 +450,19 @@ int b200_fmha_decode_dispatch(int dtype, int head_dim, const void* q, const void
                               int bn, int splits, float qk_scale, const int64_t* strides, cudaStream_t stream) {
   using namespace b200;
   DecodeParams p;
-  p.q = q; p.k = k; p.v = v; p.att = att; p.lse = lse; p.pos = pos;
+  p.q = q; p.att = att; p.lse = lse; p.pos = pos;
   p.q_head_stride = strides[0]; p.q_row_stride = strides[1];
-  p.k_head_stride = strides[2]; p.k_row_stride = strides[3];
-  p.v_head_stride = strides[4]; p.v_row_stride = strides[5];
   p.att_head_stride = strides[6]; p.att_row_stride = strides[7];
   p.lse_head_stride = strides[8];
   p.group = group; p.kv_cap = kv_cap; p.bn = bn; p.splits = splits;
   p.scale_log2 = qk_scale * 1.4426950408889634f;
-#define B200_DEC_CASE(D_, F16_) return launch_decode<D_, F16_>(p, kv_heads, out, strides[9], strides[10], stream)
+  DecodeHostArgs h;
+  h.k = k; h.v = v;
+  h.k_head_stride = strides[2]; h.k_row_stride = strides[3];
+  h.v_head_stride = strides[4]; h.v_row_stride = strides[5];
+  h.kv_heads = kv_heads; h.out = out;
+  h.out_head_stride = strides[9]; h.out_row_stride = strides[10];
+#define B200_DEC_CASE(D_, F16_) return launch_decode<D_, F16_>(p, h, stream)
   if (head_dim == 128 && dtype == 0) B200_DEC_CASE(128, false);
   if (head_dim == 128 && dtype == 1) B200_DEC_CASE(128, true);
   if (head_dim == 64 && dtype == 0) B200_DEC_CASE(64, false);
@@ -367,12 +476,11 @@ int b200_splitk_merge_dispatch(int dtype, int head_dim, const void* att, const f
                                int group, int splits, const int64_t* strides, cudaStream_t stream) {
   using namespace b200;
   if (!b200h::device_info()) return B200_ERR_CUDA;
-  if (dtype)
-    splitk_reduce_merge_kernel<true><<<kv_heads, 128, 0, stream>>>(att, lse, out, group, head_dim, splits, strides[0],
-                                                                  strides[1], strides[2], strides[3], strides[4]);
-  else
-    splitk_reduce_merge_kernel<false><<<kv_heads, 128, 0, stream>>>(att, lse, out, group, head_dim, splits, strides[0],
-                                                                   strides[1], strides[2], strides[3], strides[4]);
-  B200_CUDA_CHECK(cudaGetLastError());
-  return B200_OK;
+  if (head_dim != 64 && head_dim != 128)
+    return b200h::set_error(B200_ERR_UNSUPPORTED, "splitk_reduce_merge: head_dim %d (64 and 128 are provided)",
+                            head_dim);
+  return dtype ? launch_merge<true>(att, lse, out, kv_heads, group, head_dim, splits, strides[0], strides[1],
+                                    strides[2], strides[3], strides[4], false, stream)
+               : launch_merge<false>(att, lse, out, kv_heads, group, head_dim, splits, strides[0], strides[1],
+                                     strides[2], strides[3], strides[4], false, stream);
 }

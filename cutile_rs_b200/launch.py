@@ -11,6 +11,7 @@ call into the C ABI (``b200tile_launch``) where the reference would JIT-compile 
 from __future__ import annotations
 
 import ctypes
+import struct
 from ctypes import c_char_p, c_float, c_int32, c_uint, c_uint64, c_void_p
 from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple, Union
@@ -36,6 +37,11 @@ class CompileOptions:
                                     f(self.max_divisibility), f(self.num_worker_warps_per_cta))
 
 
+class F16(float):
+    """A scalar kernel parameter of type f16 (the `qk_scale: f16` of the decode kernels,
+    cutile-kernels/src/attention.rs:610,754): two bytes in the parameter array."""
+
+
 Output = Union[Partition, MappedLaunchPartition]
 Arg = Union[Partition, MappedLaunchPartition, Tensor, int, float]
 
@@ -47,6 +53,9 @@ class _ParamArray:
         self._keep = []
 
     def push(self, kind: str, value) -> None:
+        if kind == "f16":
+            self._keep.append(ctypes.c_uint16(struct.unpack("<H", struct.pack("<e", value))[0]))
+            return
         ctype = {"u64": c_uint64, "i32": c_int32, "f32": c_float}[kind]
         self._keep.append(ctype(value))
 
@@ -105,6 +114,8 @@ class KernelLauncher:
                 pa.push("i32", int(a))
             elif isinstance(a, int):
                 pa.push("i32", a)
+            elif isinstance(a, F16):
+                pa.push("f16", float(a))
             elif isinstance(a, float):
                 pa.push("f32", a)
             else:
@@ -357,10 +368,10 @@ def _i64x2(a, b):
     return (ctypes.c_int64 * 2)(int(a), int(b))
 
 
-def fmha_decode_gqa_split(q: Tensor, k: Tensor, v: Tensor, att_partial: Tensor, lse_partial: Tensor,
-                          position_start: Tensor, qk_scale: float, bn: int, num_kv_splits: int,
-                          out: Optional[Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
-    """Split-KV GQA decode attention (`fmha_decode_gqa_split`, cutile-kernels/src/attention.rs:727-901):
+def decode_attention(q: Tensor, k: Tensor, v: Tensor, att_partial: Tensor, lse_partial: Tensor,
+                     position_start: Tensor, qk_scale: float, bn: int, num_kv_splits: int,
+                     out: Optional[Tensor] = None, stream: Optional[torch.cuda.Stream] = None):
+    """Typed call: split-KV GQA decode attention (`fmha_decode_gqa_split`, cutile-kernels/src/attention.rs:727-901):
     q [kv_heads, GROUP, D], k/v [kv_heads, kv_capacity, D], scratch att_partial
     [kv_heads, NUM_KV_SPLITS*GROUP, D] and lse_partial [kv_heads, NUM_KV_SPLITS*GROUP] (f32),
     position_start a device u32[1].  With ``out`` [kv_heads, GROUP, D] the merge
@@ -380,9 +391,9 @@ def fmha_decode_gqa_split(q: Tensor, k: Tensor, v: Tensor, att_partial: Tensor, 
     return (att_partial, lse_partial) if out is None else (att_partial, lse_partial, out)
 
 
-def splitk_reduce_merge(att_partial: Tensor, lse_partial: Tensor, out: Tensor, num_kv_splits: int,
-                        stream: Optional[torch.cuda.Stream] = None) -> Tensor:
-    """Merge of split-KV partials (`splitk_reduce_merge`, cutile-kernels/src/attention.rs:907-1015)."""
+def decode_merge(att_partial: Tensor, lse_partial: Tensor, out: Tensor, num_kv_splits: int,
+                 stream: Optional[torch.cuda.Stream] = None) -> Tensor:
+    """Typed call: merge of split-KV partials (`splitk_reduce_merge`, cutile-kernels/src/attention.rs:907-1015)."""
     lib = _lib.load()
     s = stream or torch.cuda.current_stream()
     heads, group, d = out.shape
@@ -394,3 +405,88 @@ def splitk_reduce_merge(att_partial: Tensor, lse_partial: Tensor, out: Tensor, n
     if rc:
         raise KernelLaunchError(lib.b200tile_last_error().decode())
     return out
+
+
+class FmhaPrefillGqa(KernelLauncher):
+    """q [q_len, q_heads, D]; k, v [kv_heads, kv_len, D]; out partition [BM, GROUP, D]."""
+    kernel_name = "fmha_prefill_gqa"
+
+    def __init__(self, args, causal: bool):
+        super().__init__(args)
+        self._causal = bool(causal)
+
+    def infer_generics(self) -> List[str]:
+        out = self.args[3]
+        bm, group, d = out.partition_shape
+        kv_len = self.args[6]
+        return [out.dtype_str(), str(bm), "128", str(d), str(group), str(bm * group), str(int(self._causal)),
+                str(int(kv_len % 128 == 0)), "2"]
+
+
+def fmha_prefill_gqa(q: Tensor, k: Tensor, v: Tensor, out: Output, qk_scale: float, query_group_size: int,
+                     kv_len: int, query_start: int = 0, causal: bool = True) -> FmhaPrefillGqa:
+    """GQA prefill attention with GROUP query heads per tile-block
+    (cutile-kernels/src/attention.rs:398-440)."""
+    return FmhaPrefillGqa([q, k, v, out, float(qk_scale), int(query_group_size), int(kv_len), int(query_start)],
+                          causal)
+
+
+class FmhaCausal(KernelLauncher):
+    """q [m, h, D]; k, v [hkv, n, D]; out partition [BM, 1, D]; the causal offset is a device u32[1]."""
+    kernel_name = "fmha_causal"
+
+    def __init__(self, args, causal: bool):
+        super().__init__(args)
+        self._causal = bool(causal)
+
+    def infer_generics(self) -> List[str]:
+        out, k = self.args[3], self.args[1]
+        return [out.dtype_str(), str(out.partition_shape[0]), "128", str(out.partition_shape[2]),
+                str(int(self._causal)), str(int(k.shape[1] % 128 == 0))]
+
+
+def fmha_causal(q: Tensor, k: Tensor, v: Tensor, out: Output, qk_scale: float, query_group_size: int,
+                position_start: Tensor, causal: bool = True) -> FmhaCausal:
+    """Dynamic-position causal attention (cutile-kernels/src/attention.rs:588-613)."""
+    return FmhaCausal([q, k, v, out, F16(qk_scale), int(query_group_size), position_start], causal)
+
+
+class FmhaDecodeGqaSplit(KernelLauncher):
+    """Partial pass of split-KV decode; generics [T, GROUP, BN, D, NUM_KV_SPLITS, LATENCY]."""
+    kernel_name = "fmha_decode_gqa_split"
+
+    def __init__(self, args, bn: int):
+        super().__init__(args)
+        self._bn = int(bn)
+
+    def infer_generics(self) -> List[str]:
+        q, att = self.args[0], self.args[3]
+        group, d = att.partition_shape[1], att.partition_shape[2]
+        whole = att.partition.object if isinstance(att, MappedLaunchPartition) else att.object
+        return [q.dtype_str(), str(group), str(self._bn), str(d), str(whole.shape[1] // group), "2"]
+
+
+def fmha_decode_gqa_split(q: Tensor, k: Tensor, v: Tensor, att_out: Output, lse_out: Output, qk_scale: float,
+                          position_start: Tensor, bn: int = 128) -> FmhaDecodeGqaSplit:
+    """`fmha_decode_gqa_split` (cutile-kernels/src/attention.rs:738-757): att_out is the [1, GROUP, D]
+    partition of [kv_heads, NUM_KV_SPLITS*GROUP, D], lse_out the [1, GROUP] partition of
+    [kv_heads, NUM_KV_SPLITS*GROUP]; the grid (kv_heads, NUM_KV_SPLITS, 1) follows from them."""
+    return FmhaDecodeGqaSplit([q, k, v, att_out, lse_out, F16(qk_scale), position_start], bn)
+
+
+class SplitkReduceMerge(KernelLauncher):
+    """Generics [T, GROUP, D, CHUNK_D, NUM_KV_SPLITS, NS_GROUP, LATENCY]."""
+    kernel_name = "splitk_reduce_merge"
+
+    def infer_generics(self) -> List[str]:
+        att, out = self.args[0], self.args[2]
+        group, chunk = out.partition_shape[1], out.partition_shape[2]
+        ns_group = att.shape[1]
+        return [att.dtype_str(), str(group), str(att.shape[2]), str(chunk), str(ns_group // group),
+                str(ns_group), "2"]
+
+
+def splitk_reduce_merge(att_partial: Tensor, lse_partial: Tensor, out: Output) -> SplitkReduceMerge:
+    """`splitk_reduce_merge` (cutile-kernels/src/attention.rs:921-939); out is the [1, GROUP, CHUNK_D]
+    partition of [kv_heads, GROUP, D]."""
+    return SplitkReduceMerge([att_partial, lse_partial, out])

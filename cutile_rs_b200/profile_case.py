@@ -2,6 +2,7 @@
 
     python -m cutile_rs_b200.profile_case gemm --m 4096 --n 4096 --k 8192 --iters 3
     python -m cutile_rs_b200.profile_case fmha --batch 1 --heads 16 --seq 4096 --causal 0 --iters 3
+    python -m cutile_rs_b200.profile_case decode --heads 8 --group 4 --seq 65536 --splits 18 --iters 3
 
 The default sizes keep the operands above the 126 MB L2 (so DRAM counters mean something) and the
 device footprint far below a few GB (so a multi-pass capture ends by itself).
@@ -19,7 +20,7 @@ from . import _lib
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "fmha"])
+    ap.add_argument("kernel", choices=["gemm", "fmha", "decode"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=8192)
@@ -30,6 +31,9 @@ def main() -> None:
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--causal", type=int, default=0)
+    ap.add_argument("--group", type=int, default=4)
+    ap.add_argument("--splits", type=int, default=18)
+    ap.add_argument("--bn", type=int, default=128)
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
 
@@ -49,6 +53,24 @@ def main() -> None:
             _lib.check(lib.b200tile_gemm(b"bf16", args.layout, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n,
                                          k, k, b.stride(0), n, 0, 0, 0, 0, args.config, 0, 0, stream.cuda_stream))
         flops = 2.0 * m * n * k
+    elif args.kernel == "decode":
+        h, grp, s, d, ns = args.heads, args.group, args.seq, args.head_dim, args.splits
+        q = torch.randn(h, grp, d, device="cuda", generator=g).bfloat16()
+        kk = torch.randn(h, s, d, device="cuda", generator=g).bfloat16()
+        v = torch.randn(h, s, d, device="cuda", generator=g).bfloat16()
+        att = torch.empty(h, ns * grp, d, dtype=torch.bfloat16, device="cuda")
+        lse = torch.empty(h, ns * grp, dtype=torch.float32, device="cuda")
+        o = torch.empty_like(q)
+        pos = torch.tensor([s - 1], dtype=torch.int32, device="cuda")
+        i2 = ctypes.c_int64 * 2
+
+        def run():
+            _lib.check(lib.b200tile_fmha_decode_gqa_split(
+                b"bf16", q.data_ptr(), kk.data_ptr(), v.data_ptr(), att.data_ptr(), lse.data_ptr(), o.data_ptr(),
+                pos.data_ptr(), h, grp, d, s, args.bn, ns, 1.0 / math.sqrt(d), i2(grp * d, d), i2(s * d, d),
+                i2(s * d, d), i2(ns * grp * d, d), ns * grp, i2(grp * d, d), stream.cuda_stream))
+        flops = 4.0 * s * d * h * grp
+        print(f"decode: K+V bytes per launch {2 * h * s * d * 2}")
     else:
         bsz, h, s, d = args.batch, args.heads, args.seq, args.head_dim
         q = torch.randn(bsz * h, s, d, device="cuda", generator=g).bfloat16()

@@ -27,7 +27,7 @@ def _run(q, k, v, pos, bn, splits, merge=True):
     lse = api.from_torch(torch.full((heads, splits * group), float("nan"), dtype=torch.float32, device="cuda"))
     out = api.zeros([heads, group, d], name) if merge else None
     p = api.from_torch(torch.tensor([pos], dtype=torch.int32, device="cuda"))
-    launch.fmha_decode_gqa_split(api.copy_host_to_device(q), api.copy_host_to_device(k), api.copy_host_to_device(v),
+    launch.decode_attention(api.copy_host_to_device(q), api.copy_host_to_device(k), api.copy_host_to_device(v),
                                  att, lse, p, 1.0 / math.sqrt(d), bn, splits, out=out)
     torch.cuda.synchronize()
     return att.storage, lse.storage, (out.storage if merge else None)
@@ -66,7 +66,7 @@ def test_merge_alone_and_position_is_read_on_device(b200, oracle):
     q, k, v = _setup(heads, group, d, cap, torch.bfloat16, seed=5)
     att, lse, _ = _run(q, k, v, 600, bn, splits, merge=False)
     out = api.zeros([heads, group, d], "bf16")
-    launch.splitk_reduce_merge(api.from_torch(att), api.from_torch(lse), out, splits)
+    launch.decode_merge(api.from_torch(att), api.from_torch(lse), out, splits)
     torch.cuda.synchronize()
     ref = oracle.splitk_reduce_merge(att.float().cpu().numpy(), lse.cpu().numpy(), group, False)
     assert oracle.max_abs(out.storage.float().cpu().numpy(), ref) <= 2.0 ** -7
@@ -77,11 +77,11 @@ def test_merge_alone_and_position_is_read_on_device(b200, oracle):
     out_t = api.zeros([heads, group, d], "bf16")
     pos = api.from_torch(torch.tensor([99], dtype=torch.int32, device="cuda"))
     stream = torch.cuda.Stream()
-    launch.fmha_decode_gqa_split(qd, kd, vd, att_t, lse_t, pos, 1 / math.sqrt(d), bn, splits, out=out_t, stream=stream)
+    launch.decode_attention(qd, kd, vd, att_t, lse_t, pos, 1 / math.sqrt(d), bn, splits, out=out_t, stream=stream)
     stream.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=stream):
-        launch.fmha_decode_gqa_split(qd, kd, vd, att_t, lse_t, pos, 1 / math.sqrt(d), bn, splits, out=out_t,
+        launch.decode_attention(qd, kd, vd, att_t, lse_t, pos, 1 / math.sqrt(d), bn, splits, out=out_t,
                                      stream=torch.cuda.current_stream())
     for p in (99, 600, 1023):
         pos.storage.fill_(p)
@@ -90,3 +90,47 @@ def test_merge_alone_and_position_is_read_on_device(b200, oracle):
         sc = torch.einsum("hgd,hnd->hgn", q.float(), k.float()[:, :p + 1]) / math.sqrt(d)
         dense = torch.einsum("hgn,hnd->hgd", torch.softmax(sc, -1), v.float()[:, :p + 1])
         assert (out_t.storage.float().cpu() - dense).abs().max().item() <= ATTN_TOL
+
+
+def test_reference_shaped_launchers(b200, oracle):
+    """The serving kernels under their reference names, parameter order and inferred grids
+    (cutile-kernels/src/attention.rs:398-440, 588-613, 738-757, 921-939)."""
+    heads_kv, group, d, cap, pos, bn, splits = 2, 4, 128, 640, 500, 64, 5
+    q, k, v = _setup(heads_kv, group, d, cap, torch.float16, seed=3)
+    qd, kd, vd = (api.copy_host_to_device(t) for t in (q, k, v))
+    att = api.zeros([heads_kv, splits * group, d], "f16")
+    lse = api.from_torch(torch.zeros(heads_kv, splits * group, device="cuda"))
+    out = api.zeros([heads_kv, group, d], "f16")
+    p = api.from_torch(torch.tensor([pos], dtype=torch.int32, device="cuda"))
+    scale = 1.0 / math.sqrt(d)
+    launch.fmha_decode_gqa_split(qd, kd, vd, att.partition([1, group, d]), lse.partition([1, group]), scale, p,
+                                 bn=bn).sync()
+    launch.splitk_reduce_merge(att, lse, out.partition([1, group, 32])).sync()
+    scale16 = float(np.float16(scale))        # the kernel parameter is an f16 scalar
+    att_o, lse_o = oracle.fmha_decode_gqa_split(q.float().numpy(), k.float().numpy(), v.float().numpy(), pos + 1, bn,
+                                                splits, scale16, True)
+    assert oracle.max_abs(att.storage.float().cpu().numpy(), att_o) <= ATTN_TOL
+    assert oracle.max_abs(out.storage.float().cpu().numpy(), oracle.splitk_reduce_merge(att_o, lse_o, group, True)) \
+        <= ATTN_TOL
+    with pytest.raises(Exception, match="grid"):
+        launch.fmha_decode_gqa_split(qd, kd, vd, att.partition([1, group, d]), lse.partition([1, group]), scale, p,
+                                     bn=bn).grid((heads_kv, splits + 1, 1)).sync()
+
+    # prefill with GROUP query heads per tile-block, and the dynamic-position kernel, [q_len, heads, D]
+    q_len, heads = 200, heads_kv * group
+    g = torch.Generator().manual_seed(9)
+    qp = torch.randn(q_len, heads, d, generator=g).half()
+    kp = torch.randn(heads_kv, q_len, d, generator=g).half()   # equal lengths: the reference CPU attention's shape
+    vp = torch.randn(heads_kv, q_len, d, generator=g).half()
+    qpd, kpd, vpd = (api.copy_host_to_device(t) for t in (qp, kp, vp))
+    ref = oracle.fmha_ref_cpu(qp.permute(1, 0, 2)[None].float().numpy(), kp[None].float().numpy(),
+                              vp[None].float().numpy(), scale16, input_pos=40, query_group_size=group, causal=True)
+    ref = ref.reshape(heads, q_len, d).transpose(1, 0, 2)
+    o1 = api.zeros([q_len, heads, d], "f16")
+    launch.fmha_prefill_gqa(qpd, kpd, vpd, o1.partition([32, group, d]), scale16, group, q_len,
+                            query_start=40).sync()
+    assert oracle.max_abs(o1.storage.float().cpu().numpy(), ref) <= ATTN_TOL
+    o2 = api.zeros([q_len, heads, d], "f16")
+    p40 = api.from_torch(torch.tensor([40], dtype=torch.int32, device="cuda"))
+    launch.fmha_causal(qpd, kpd, vpd, o2.partition([128, 1, d]), scale, group, p40).sync()
+    assert oracle.max_abs(o2.storage.float().cpu().numpy(), ref) <= ATTN_TOL
