@@ -46,6 +46,8 @@ SIGNATURES = {
     "b200tile_gemm": (c_int, [c_char_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int,
                               c_int, c_int, c_int, c_void_p]),
+    "b200tile_gemm_host": (c_int, [c_char_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_int, c_int, c_int, c_int, c_void_p]),
     "b200tile_fmha_fwd": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, POINTER(c_int64), POINTER(c_int64),
                                   POINTER(c_int64), POINTER(c_int64), c_float, c_int, c_int,

@@ -66,3 +66,35 @@ def copy_host_vec_to_device(host: torch.Tensor, dtype: Optional[str] = None) -> 
 def from_torch(t: torch.Tensor, dtype: Optional[str] = None) -> Tensor:
     """Borrow a foreign allocation (``Tensor::from_foreign``, cutile/src/tensor.rs:839-907)."""
     return Tensor.from_torch(t, dtype)
+
+
+class HostGemm:
+    """C = A.B for operands that live in HOST memory, as one upload / multiply / download pipeline
+    (`b200tile_gemm_host`).  The device staging buffers are allocated once here and reused by
+    every call; the host operands should be page-locked (:func:`pin`)."""
+
+    def __init__(self, m: int, n: int, k: int, dtype: str = "bf16", b_layout: int = 0, slab_rows: int = 0):
+        from . import _lib
+        self._lib = _lib.load()
+        self._check = _lib.check
+        self.m, self.n, self.k, self.dtype, self.b_layout, self.slab_rows = m, n, k, dtype, int(b_layout), slab_rows
+        td = _NAME_TO_TORCH[dtype]
+        self.a_dev = torch.empty((m, k), dtype=td, device=_device())
+        self.b_dev = torch.empty((n, k) if b_layout else (k, n), dtype=td, device=_device())
+        self.c_dev = torch.empty((m, n), dtype=td, device=_device())
+
+    def __call__(self, a_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor,
+                 stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """Queues the pipeline; ``c_host`` is complete once ``stream`` has been synchronised."""
+        if tuple(a_host.shape) != (self.m, self.k) or tuple(c_host.shape) != (self.m, self.n) or \
+                tuple(b_host.shape) != tuple(self.b_dev.shape):
+            raise ValueError("HostGemm: operand shapes do not match the planned problem")
+        for t in (a_host, b_host, c_host):
+            if t.device.type != "cpu" or not t.is_contiguous() or t.dtype != self.a_dev.dtype:
+                raise ValueError("HostGemm: operands must be contiguous host tensors of the planned type")
+        s = stream or torch.cuda.current_stream()
+        self._check(self._lib.b200tile_gemm_host(self.dtype.encode(), self.b_layout, a_host.data_ptr(),
+                                                  b_host.data_ptr(), c_host.data_ptr(), self.a_dev.data_ptr(),
+                                                  self.b_dev.data_ptr(), self.c_dev.data_ptr(), self.m, self.n,
+                                                  self.k, self.slab_rows, s.cuda_stream))
+        return c_host

@@ -132,6 +132,22 @@ B200TILE_API int b200tile_gemm(const char* dtype, int b_layout, const void* a, c
                   int64_t stride_a, int64_t stride_b, int64_t stride_c, int accumulate, int config,
                   int group_size_m, int num_programs, void* cu_stream);
 
+/* C = A*B with all three operands in HOST memory (page-locked for full speed), as one pipeline:
+ * B is uploaded first, A follows in slabs of `slab_rows` rows (<= 0 selects 512; rounded up to a
+ * multiple of 256), every slab is multiplied by b200tile_gemm as soon as it has arrived and its
+ * rows of C are downloaded while the next slab is still on its way.  Replaces the reference
+ * user's serial sequence `copy_host_vec_to_device` x2 (cutile/src/api.rs:422) -> kernel launch ->
+ * `copy_device_to_host_vec` (api.rs:371).
+ *   a_host [m,k], b_host ([k,n] for b_layout 0, [n,k] for 1), c_host [m,n]: dense row-major
+ *   a_dev, b_dev, c_dev: device staging buffers of the same sizes, provided by the caller
+ * Ordered after everything already queued on `cu_stream`; when the call returns, the work is
+ * queued and `cu_stream` ends after the last download, so synchronising it completes the call.
+ * Two internal streams and their events are created on first use per device; not usable inside
+ * a stream capture (B200TILE_ERR_UNSUPPORTED). */
+B200TILE_API int b200tile_gemm_host(const char* dtype, int b_layout, const void* a_host, const void* b_host,
+                                    void* c_host, void* a_dev, void* b_dev, void* c_dev, int m, int n, int k,
+                                    int slab_rows, void* cu_stream);
+
 /* out = softmax(qk_scale * Q K^T + mask) V, one query tile per tile-block, online softmax with
  * fp32 statistics, probabilities rounded to the 16-bit input type before P.V.
  * Replaces `fmha_prefill_causal` (cutile-kernels/src/attention.rs:232-392), the benchmark kernels

@@ -187,3 +187,32 @@ def test_streamk_remainder_wave(b200, oracle):
     assert diff <= 2.0 ** -7 * c_whole.float().abs().max().item()
     assert not torch.isnan(c_sk.float()).any()
     _status_ok(b200)
+
+
+@pytest.mark.parametrize("dtype,m,n,k,layout,slab", [("bf16", 1300, 512, 768, 0, 256), ("bf16", 1024, 768, 512, 1, 0),
+                                                      ("f32", 300, 256, 128, 0, 256)])
+def test_host_operand_pipeline(b200, oracle, dtype, m, n, k, layout, slab):
+    """Upload / multiply / download pipeline over host operands: same result as the device-resident
+    call (bit for bit: the slabs run the same kernel on the same rows), twice in a row on one stream."""
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    g = torch.Generator().manual_seed(m + n)
+    a = (torch.randn(m, k, generator=g) / 8).to(td).pin_memory()
+    b = (torch.randn((n, k) if layout else (k, n), generator=g) / 8).to(td).pin_memory()
+    c = torch.full((m, n), float("nan"), dtype=td).pin_memory()
+    plan = api.HostGemm(m, n, k, dtype, layout, slab)
+    stream = torch.cuda.current_stream()
+    plan(a, b, c, stream)
+    stream.synchronize()
+    first = c.clone()
+    a2 = (a.float() * 0.5).to(td).pin_memory()
+    plan(a2, b, c, stream)         # staging buffers reused while nothing of the first call is pending
+    stream.synchronize()
+    bm = b.float().t() if layout else b.float()
+    if dtype == "f32":
+        ref = oracle.cpu_gemm(a.numpy(), b.numpy())
+        assert np.array_equal(first.numpy(), ref)
+    else:
+        ref = (a.float() @ bm).numpy()
+        assert oracle.rel_frobenius(first.float().numpy(), ref) <= 1e-2
+        assert oracle.rel_frobenius(c.float().numpy(), 0.5 * ref) <= 1e-2
+    assert not torch.isnan(c.float()).any()
