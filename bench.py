@@ -250,7 +250,7 @@ def run_gpu_arm(args):
     c_pin = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(min(args.steps, 5), 1)
 
-    # one call of the public API per step: B up, A up in 512-row slabs, each slab multiplied on arrival and
+    # one call of the public API per step: B up, A up in 1024-row slabs, each slab multiplied on arrival and
     # its C rows sent back while the next slab is in flight (uploads, MMA and downloads on three streams)
     host_gemm = api.HostGemm(M, n_local, K, "bf16")
 
@@ -437,9 +437,9 @@ def run_gpu_arm(args):
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "api": "api.HostGemm (b200tile_gemm_host): pinned host A, B, C; pipelined in 512-row slabs",
+                    "api": "api.HostGemm (b200tile_gemm_host): pinned host A, B, C; pipelined in 1024-row slabs",
                     "serial_copy_launch_copy_ms": e2e_serial_ms,
-                    "gpu_launches_per_step": -(-M // 512)},
+                    "gpu_launches_per_step": -(-M // 1024)},
             "gpu_launches": args.steps * world,
             "clocks": clocks,
             "extra": extra,

@@ -66,7 +66,7 @@ extern "C" int b200tile_gemm_host(const char* dtype, int b_layout, const void* a
   B200_CUDA_CHECK(cudaStreamIsCapturing(s, &cap));
   if (cap != cudaStreamCaptureStatusNone)
     return set_error(B200_ERR_UNSUPPORTED, "gemm_host: not available inside a stream capture");
-  if (slab_rows <= 0) slab_rows = 512;
+  if (slab_rows <= 0) slab_rows = 1024;
   slab_rows = (slab_rows + 255) / 256 * 256;
   int slabs = (m + slab_rows - 1) / slab_rows;
   if (slabs > kMaxSlabs) {

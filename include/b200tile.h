@@ -133,7 +133,7 @@ B200TILE_API int b200tile_gemm(const char* dtype, int b_layout, const void* a, c
                   int group_size_m, int num_programs, void* cu_stream);
 
 /* C = A*B with all three operands in HOST memory (page-locked for full speed), as one pipeline:
- * B is uploaded first, A follows in slabs of `slab_rows` rows (<= 0 selects 512; rounded up to a
+ * B is uploaded first, A follows in slabs of `slab_rows` rows (<= 0 selects 1024; rounded up to a
  * multiple of 256), every slab is multiplied by b200tile_gemm as soon as it has arrived and its
  * rows of C are downloaded while the next slab is still on its way.  Replaces the reference
  * user's serial sequence `copy_host_vec_to_device` x2 (cutile/src/api.rs:422) -> kernel launch ->
