@@ -43,6 +43,10 @@ int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const vo
 int b200_fmha_decode_dispatch(int dtype, int head_dim, const void* q, const void* k, const void* v, void* att,
                               float* lse, void* out, const uint32_t* pos, int kv_heads, int group, int kv_cap,
                               int bn, int splits, float qk_scale, const int64_t* strides, cudaStream_t stream);
+size_t b200_grouped_workspace_bytes(int groups);
+int b200_gemm_grouped_dispatch(int dtype, int bn, const int64_t* a_ptrs, const int64_t* b_ptrs, const int64_t* c_ptrs,
+                               const int32_t* a_metas, const int32_t* b_metas, const int32_t* c_metas, int groups,
+                               void* workspace, cudaStream_t stream);
 int b200_splitk_merge_dispatch(int dtype, int head_dim, const void* att, const float* lse, void* out, int kv_heads,
                                int group, int splits, const int64_t* strides, cudaStream_t stream);
 
@@ -324,6 +328,53 @@ int b200tile_splitk_reduce_merge(const char* dtype, const void* att_partial, con
   const int64_t strides[5] = {att_strides[0], att_strides[1], lse_head_stride, out_strides[0], out_strides[1]};
   return b200_splitk_merge_dispatch(dt, head_dim, att_partial, lse_partial, out, kv_heads, group, num_kv_splits,
                                     strides, static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---------------------------------------------------------------------------
+// Grouped GEMM over device-side pointer / extent tables
+// ---------------------------------------------------------------------------
+uint64_t b200tile_group_gemm_workspace_bytes(int num_groups) { return b200_grouped_workspace_bytes(num_groups); }
+
+int b200tile_group_gemm(const char* dtype, const int64_t* a_ptrs, const int64_t* b_ptrs, const int64_t* c_ptrs,
+                        const int32_t* a_metas, const int32_t* b_metas, const int32_t* c_metas, int num_groups,
+                        int bn, void* workspace, uint64_t workspace_bytes, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "group_gemm", &dt)) return rc;
+  if (num_groups < 0) return set_error(B200TILE_ERR_INVALID, "group_gemm: num_groups must not be negative");
+  if (num_groups == 0) return B200TILE_OK;
+  if (!a_ptrs || !b_ptrs || !c_ptrs || !a_metas || !b_metas || !c_metas)
+    return set_error(B200TILE_ERR_INVALID, "group_gemm: null table pointer");
+  if (bn <= 0) bn = 256;
+  cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
+  const size_t need = b200_grouped_workspace_bytes(num_groups);
+  if (!workspace) {
+    // library-owned workspace, one per device, grown on demand (never inside a stream capture)
+    static void* pool[64] = {};
+    static size_t pool_bytes[64] = {};
+    const b200h::DeviceInfo* di = b200h::device_info();
+    if (!di) return B200TILE_ERR_CUDA;
+    if (pool_bytes[di->ordinal] < need) {
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      B200_CUDA_CHECK(cudaStreamIsCapturing(stream, &cap));
+      if (cap != cudaStreamCaptureStatusNone)
+        return set_error(B200TILE_ERR_INVALID,
+                         "group_gemm: pass a workspace of %llu bytes when capturing (the library cannot allocate)",
+                         (unsigned long long)need);
+      B200_CUDA_CHECK(cudaDeviceSynchronize());  // earlier launches may still read the old block
+      if (pool[di->ordinal]) B200_CUDA_CHECK(cudaFree(pool[di->ordinal]));
+      pool[di->ordinal] = nullptr;
+      pool_bytes[di->ordinal] = 0;
+      const size_t grow = need < (64u << 10) ? (64u << 10) : need * 2;
+      B200_CUDA_CHECK(cudaMalloc(&pool[di->ordinal], grow));
+      pool_bytes[di->ordinal] = grow;
+    }
+    workspace = pool[di->ordinal];
+  } else if ((reinterpret_cast<uintptr_t>(workspace) & 127) != 0 || workspace_bytes < need) {
+    return set_error(B200TILE_ERR_INVALID, "group_gemm: workspace of %llu bytes (128-byte aligned) required, got %llu",
+                     (unsigned long long)need, (unsigned long long)workspace_bytes);
+  }
+  return b200_gemm_grouped_dispatch(dt, bn, a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas, c_metas, num_groups, workspace,
+                                    stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -922,6 +973,45 @@ int launch_decode_generic(const char* kernel, const char* const* generics, int n
                                         stream);
 }
 
+// "group_gemm_f16_nt_desc" (cutile-kernels/src/experimental/moe.rs:66-85): (a_ptrs, b_ptrs, c_ptrs i64[G],
+//    a_metas, b_metas, c_metas i32[G,8], num_groups i32), generics [T?, BM, BN, BK, NUM_SM], grid (NUM_SM,1,1).
+int launch_group_gemm_generic(const char* kernel, const char* const* generics, int n_generics,
+                              const void* const* params, int n_params, void* stream, bool launch) {
+  const char* dtype;
+  long g[8];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 8, &ng) || ng < 3)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (g[0] != 128 || (g[1] != 128 && g[1] != 256) || g[2] != 64)
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "%s: tile (%ld,%ld,%ld) has no precompiled configuration ((128,128,64), (128,256,64))", kernel,
+                     g[0], g[1], g[2]);
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg ap, bp, cp, am, bmeta, cm;
+  read_tensor(r, 1, false, ap);
+  read_tensor(r, 1, false, bp);
+  read_tensor(r, 1, false, cp);
+  read_tensor(r, 2, false, am);
+  read_tensor(r, 2, false, bmeta);
+  read_tensor(r, 2, false, cm);
+  const int groups = r.i32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  if (groups < 0 || ap.dim[0] < groups || bp.dim[0] < groups || cp.dim[0] < groups || am.dim[0] < groups ||
+      bmeta.dim[0] < groups || cm.dim[0] < groups || am.dim[1] != 8 || bmeta.dim[1] != 8 || cm.dim[1] != 8)
+    return set_error(B200TILE_ERR_INVALID, "%s: tables must hold num_groups entries ([G] pointers, [G,8] extents)",
+                     kernel);
+  if (ap.stride[0] != 1 || bp.stride[0] != 1 || cp.stride[0] != 1 || am.stride[0] != 8 || am.stride[1] != 1 ||
+      bmeta.stride[0] != 8 || bmeta.stride[1] != 1 || cm.stride[0] != 8 || cm.stride[1] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: tables must be dense", kernel);
+  return b200tile_group_gemm(dtype, reinterpret_cast<const int64_t*>(ap.ptr), reinterpret_cast<const int64_t*>(bp.ptr),
+                             reinterpret_cast<const int64_t*>(cp.ptr), reinterpret_cast<const int32_t*>(am.ptr),
+                             reinterpret_cast<const int32_t*>(bmeta.ptr), reinterpret_cast<const int32_t*>(cm.ptr),
+                             groups, (int)g[1], nullptr, 0, stream);
+}
+
 }  // namespace
 
 int b200tile_launch(const char* kernel, const char* const* generics, int n_generics,
@@ -941,6 +1031,8 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
     return launch_fmha_serving_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   if (!strcmp(kernel, "fmha_decode_gqa_split") || !strcmp(kernel, "splitk_reduce_merge"))
     return launch_decode_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "group_gemm_f16_nt_desc"))
+    return launch_group_gemm_generic(kernel, generics, n_generics, params, n_params, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -959,6 +1051,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
     return launch_fmha_serving_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   if (!strcmp(kernel, "fmha_decode_gqa_split") || !strcmp(kernel, "splitk_reduce_merge"))
     return launch_decode_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "group_gemm_f16_nt_desc"))
+    return launch_group_gemm_generic(kernel, generics, n_generics, nullptr, 0, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

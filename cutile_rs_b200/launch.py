@@ -490,3 +490,44 @@ def splitk_reduce_merge(att_partial: Tensor, lse_partial: Tensor, out: Output) -
     """`splitk_reduce_merge` (cutile-kernels/src/attention.rs:921-939); out is the [1, GROUP, CHUNK_D]
     partition of [kv_heads, GROUP, D]."""
     return SplitkReduceMerge([att_partial, lse_partial, out])
+
+
+class GroupGemmF16NtDesc(KernelLauncher):
+    """Generics [T, BM, BN, BK, NUM_SM]; the grid is (NUM_SM, 1, 1) as in the reference launcher."""
+    kernel_name = "group_gemm_f16_nt_desc"
+
+    def __init__(self, args, dtype: str, bn: int):
+        super().__init__(args)
+        self._dtype, self._bn = dtype, int(bn)
+
+    def infer_generics(self) -> List[str]:
+        return [self._dtype, "128", str(self._bn), "64", str(_lib.load().b200tile_num_sms())]
+
+    def _bounds(self) -> List[GridBound]:
+        return []
+
+
+def group_gemm_f16_nt_desc(a_ptrs: Tensor, b_ptrs: Tensor, c_ptrs: Tensor, a_metas: Tensor, b_metas: Tensor,
+                           c_metas: Tensor, num_groups: int, dtype: str = "f16", bn: int = 256) -> GroupGemmF16NtDesc:
+    """Persistent grouped GEMM over expert descriptor tables (cutile-kernels/src/experimental/moe.rs:
+    66-85): i64 pointer arrays [G] and i32 extent tables [G, 8] = {rows, cols, row stride, ...}, all on
+    the device.  The launch grid defaults to one tile-block per SM."""
+    la = GroupGemmF16NtDesc([a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas, c_metas, int(num_groups)], dtype, bn)
+    return la.grid((_lib.load().b200tile_num_sms(), 1, 1))
+
+
+def group_gemm_tables(a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Tensor],
+                      c_list: Sequence[torch.Tensor]):
+    """Builds the six device tables of :func:`group_gemm_f16_nt_desc` from lists of 2-D device tensors
+    (the host-side bucketing step of the reference's MoE example)."""
+    def tables(ts):
+        ptrs = torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64)
+        metas = torch.zeros(len(ts), 8, dtype=torch.int32)
+        for i, t in enumerate(ts):
+            if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+                raise KernelLaunchError("group_gemm: operands must be 2-D with a contiguous last axis")
+            metas[i, 0], metas[i, 1], metas[i, 2] = t.shape[0], t.shape[1], t.stride(0)
+        dev = ts[0].device
+        return Tensor(ptrs.to(dev)), Tensor(metas.to(dev))
+    (ap, am), (bp, bm), (cp, cm) = tables(a_list), tables(b_list), tables(c_list)
+    return ap, bp, cp, am, bm, cm

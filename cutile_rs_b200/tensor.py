@@ -34,6 +34,7 @@ _TORCH_TO_NAME = {
     torch.bfloat16: "bf16",
     torch.uint8: "u8",
     torch.int32: "i32",
+    torch.int64: "i64",
 }
 for _name, _attr in (("f8e4m3fn", "float8_e4m3fn"), ("f8e5m2", "float8_e5m2"),
                      ("f8e8m0fnu", "float8_e8m0fnu")):

@@ -148,6 +148,25 @@ B200TILE_API int b200tile_gemm_host(const char* dtype, int b_layout, const void*
                                     void* c_host, void* a_dev, void* b_dev, void* c_dev, int m, int n, int k,
                                     int slab_rows, void* cu_stream);
 
+/* Persistent grouped GEMM over device-side tables (MoE expert batches): for g in [0, num_groups)
+ * C_g [m_g, n_g] = A_g [m_g, k_g] * B_g [k_g, n_g], row-major 16-bit operands, fp32 accumulation.
+ * Replaces `group_gemm_f16_nt_desc` (cutile-kernels/src/experimental/moe.rs:66-128).
+ *   a_ptrs, b_ptrs, c_ptrs   DEVICE arrays of num_groups i64 addresses (16-byte aligned tensors)
+ *   a_metas, b_metas, c_metas DEVICE tables [num_groups, 8] of i32: {rows, cols, row stride in
+ *                            elements (a multiple of 8), 5 unused}, moe.rs:27-63; m_g and k_g are
+ *                            taken from a_metas, n_g from b_metas, the row stride of C from c_metas
+ *   bn          B tile width: 128 or 256 (<= 0 selects 256); BM = 128, BK = 64
+ *   workspace   DEVICE scratch of b200tile_group_gemm_workspace_bytes(num_groups) bytes, 128-byte
+ *               aligned (TMA descriptors built on the device plus the tile prefix sums); NULL lets
+ *               the library keep one such block per device (allocated on first use, never inside a
+ *               stream capture; calls that overlap on one device must then bring their own)
+ * Groups with m, n = 0 are skipped; k = 0 stores zeros.  Nothing is read back to the host. */
+B200TILE_API uint64_t b200tile_group_gemm_workspace_bytes(int num_groups);
+B200TILE_API int b200tile_group_gemm(const char* dtype, const int64_t* a_ptrs, const int64_t* b_ptrs,
+                                     const int64_t* c_ptrs, const int32_t* a_metas, const int32_t* b_metas,
+                                     const int32_t* c_metas, int num_groups, int bn, void* workspace,
+                                     uint64_t workspace_bytes, void* cu_stream);
+
 /* out = softmax(qk_scale * Q K^T + mask) V, one query tile per tile-block, online softmax with
  * fp32 statistics, probabilities rounded to the 16-bit input type before P.V.
  * Replaces `fmha_prefill_causal` (cutile-kernels/src/attention.rs:232-392), the benchmark kernels

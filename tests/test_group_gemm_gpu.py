@@ -1,0 +1,93 @@
+"""Grouped (MoE) GEMM over device-side pointer / extent tables against the CPU oracle GEMM."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from cutile_rs_b200 import _lib, api, launch  # noqa: E402
+
+GEMM_TOL = 1e-2   # relative Frobenius error of a 16-bit GEMM with fp32 accumulation
+
+
+def _groups(shapes, dtype, seed, pad=0):
+    g = torch.Generator().manual_seed(seed)
+    a, b, c = [], [], []
+    for (m, n, k) in shapes:
+        # padded row strides exercise the {rows, cols, stride} extent records
+        fa = torch.zeros(max(m, 1), k + pad, dtype=dtype)
+        fa[:, :k] = (torch.randn(max(m, 1), k, generator=g) / 4).to(dtype)
+        fb = torch.zeros(max(k, 1), n + pad, dtype=dtype)
+        fb[:, :n] = (torch.randn(max(k, 1), n, generator=g) / 4).to(dtype)
+        a.append(fa.cuda()[:m, :k])
+        b.append(fb.cuda()[:k, :n])
+        c.append(torch.full((max(m, 1), n + pad), float("nan"), dtype=dtype, device="cuda")[:m, :n])
+    return a, b, c
+
+
+def _check(oracle, a, b, c):
+    for ai, bi, ci in zip(a, b, c):
+        if ai.shape[0] == 0:
+            continue
+        got = ci.float().cpu().numpy()
+        assert not np.isnan(got).any()
+        if ai.shape[1] == 0:
+            assert not got.any()
+            continue
+        ref = oracle.cpu_gemm(ai.float().cpu().numpy(), bi.float().cpu().numpy(), threads=0)
+        assert oracle.rel_frobenius(got, ref) <= GEMM_TOL
+
+
+@pytest.mark.parametrize("dtype,bn", [(torch.bfloat16, 256), (torch.float16, 128)])
+def test_groups_of_many_shapes(b200, oracle, dtype, bn):
+    shapes = [(128, 256, 64), (16, 512, 128), (300, 272, 192), (0, 256, 64), (48, 16, 80), (1024, 768, 256),
+              (128, 256, 64), (64, 1024, 512)]
+    a, b, c = _groups(shapes, dtype, seed=17, pad=8)
+    tabs = launch.group_gemm_tables(a, b, c)
+    name = "bf16" if dtype == torch.bfloat16 else "f16"
+    launch.group_gemm_f16_nt_desc(*tabs, len(shapes), dtype=name, bn=bn).sync()
+    _check(oracle, a, b, c)
+    st = _lib.StatusC()
+    _lib.check(b200.b200tile_status(torch.cuda.current_stream().cuda_stream, st))
+    assert st.code == 0
+
+
+def test_typed_entry_with_caller_workspace_and_graph(b200, oracle):
+    """Many small experts (more groups than one prepare pass of 256), a caller workspace, and a
+    captured graph replayed after the token counts changed on the device."""
+    rng = np.random.default_rng(3)
+    shapes = [(int(rng.integers(1, 5)) * 16, 256, 128) for _ in range(300)]
+    a, b, c = _groups(shapes, torch.bfloat16, seed=5)
+    ap, bp, cp, am, bm, cm = launch.group_gemm_tables(a, b, c)
+    need = b200.b200tile_group_gemm_workspace_bytes(len(shapes))
+    ws = torch.empty(need + 128, dtype=torch.uint8, device="cuda")
+    wp = (ws.data_ptr() + 127) // 128 * 128
+    stream = torch.cuda.Stream()
+
+    def run(s):
+        _lib.check(b200.b200tile_group_gemm(b"bf16", ap.cu_deviceptr(), bp.cu_deviceptr(), cp.cu_deviceptr(),
+                                            am.cu_deviceptr(), bm.cu_deviceptr(), cm.cu_deviceptr(), len(shapes), 256,
+                                            wp, need, s.cuda_stream))
+    torch.cuda.synchronize()
+    run(stream)
+    stream.synchronize()
+    _check(oracle, a, b, c)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        run(torch.cuda.current_stream())
+    # halve every expert's row count on the device only; rows past the new count must stay untouched
+    for ci in c:
+        ci.fill_(7.0)
+    am.storage[:, 0] //= 2
+    g.replay()
+    torch.cuda.synchronize()
+    for (m, n, k), ai, bi, ci in zip(shapes, a, b, c):
+        h = m // 2
+        if h:
+            ref = oracle.cpu_gemm(ai[:h].float().cpu().numpy(), bi.float().cpu().numpy())
+            assert oracle.rel_frobenius(ci[:h].float().cpu().numpy(), ref) <= GEMM_TOL
+        assert (ci[h:] == 7.0).all()
+    with pytest.raises(_lib.B200TileError, match="workspace"):
+        _lib.check(b200.b200tile_group_gemm(b"bf16", ap.cu_deviceptr(), bp.cu_deviceptr(), cp.cu_deviceptr(),
+                                            am.cu_deviceptr(), bm.cu_deviceptr(), cm.cu_deviceptr(), len(shapes), 256,
+                                            wp, need - 1, stream.cuda_stream))
