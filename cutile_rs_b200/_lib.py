@@ -12,7 +12,8 @@ from ctypes import (POINTER, Structure, c_char_p, c_float, c_int, c_int64, c_uin
                     c_uint64, c_void_p)
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200tile.so")
+# B200TILE_LIB selects another build of the same library (the diagnostic trace build)
+LIB_PATH = os.environ.get("B200TILE_LIB") or os.path.join(_HERE, "libb200tile.so")
 
 OK, ERR_INVALID, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE, ERR_ALIGN = range(6)
 

@@ -26,6 +26,17 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
                            const int64_t* os, float qk_scale, int causal, int input_pos,
                            const uint32_t* pos_ptr, cudaStream_t stream);
 
+int b200_fmha_fwd_pair_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
+                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
+                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
+                                const uint32_t* pos_ptr, cudaStream_t stream);
+
+#ifdef B200TILE_TRACE
+int b200_trace_read_gemm_pair(long long* out);
+int b200_trace_read_fmha(long long* out);
+int b200_trace_read_fmha_pair(long long* out);
+#endif
+
 int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const float* xs,
                                const float* ys, void* z, int M, int N, int K, int64_t ldx, int64_t ldy,
                                int64_t ldz, int ld_xs, int ld_ys, float alpha, cudaStream_t stream);
@@ -132,12 +143,12 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
       n = (int)(sizeof(kGemmTcConfigs) / sizeof(kGemmTcConfigs[0]));
     }
   }
-  static const b200tile_config kFmhaConfigs[] = {{0, 128, 128, 0, 2, 1, 1}};
+  static const b200tile_config kFmhaConfigs[] = {{0, 128, 128, 0, 2, 1, 1}, {1, 128, 128, 0, 4, 2, 1}};
   if ((!strcmp(kernel, "fmha") || !strcmp(kernel, "fmha_prefill_causal") ||
        !strcmp(kernel, "fmha_prefill_gqa") || !strcmp(kernel, "fmha_causal")) &&
       (!strcmp(dtype, "bf16") || !strcmp(dtype, "f16"))) {
     tab = kFmhaConfigs;
-    n = 1;
+    n = 2;
   }
   static const b200tile_config kFp8Configs[] = {{0, 128, 256, 128, 4, 1, 1}};
   if (!strcmp(kernel, "linear_tile_fp8_blk128")) {
@@ -222,7 +233,8 @@ static int fmha_fwd_common(const char* dtype, const void* q, const void* k, cons
                            int batch, int heads, int heads_kv, int q_len, int kv_len, int head_dim,
                            const int64_t q_strides[2], const int64_t k_strides[2],
                            const int64_t v_strides[2], const int64_t o_strides[2], float qk_scale,
-                           int causal, int input_pos, const uint32_t* pos_ptr, void* cu_stream) {
+                           int causal, int input_pos, const uint32_t* pos_ptr, void* cu_stream,
+                           int cluster = 0) {
   if (!dtype) return set_error(B200TILE_ERR_INVALID, "fmha: dtype is null");
   if (!q || !k || !v || !out) return set_error(B200TILE_ERR_INVALID, "fmha: null tensor pointer");
   if (!q_strides || !k_strides || !v_strides || !o_strides)
@@ -240,6 +252,17 @@ static int fmha_fwd_common(const char* dtype, const void* q, const void* k, cons
     dt = 1;
   else
     return set_error(B200TILE_ERR_UNSUPPORTED, "fmha: unsupported element type '%s'", dtype);
+  // Two configurations for head_dim 128: one CTA per 256 query rows (default, the faster one as
+  // measured) and a CTA pair per 512 rows with cta_group::2 MMAs, chosen with
+  // CompileOptions::num_cta_in_cga = 2 on the generic launch or B200TILE_FMHA_PAIR=1.
+  static const bool env_pair = [] {
+    const char* e = getenv("B200TILE_FMHA_PAIR");
+    return e && e[0] == '1';
+  }();
+  if (head_dim == 128 && (cluster == 2 || (cluster == 0 && env_pair)))
+    return b200_fmha_fwd_pair_dispatch(dt, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, q_strides,
+                                       k_strides, v_strides, o_strides, qk_scale, causal ? 1 : 0, input_pos,
+                                       pos_ptr, static_cast<cudaStream_t>(cu_stream));
   return b200_fmha_fwd_dispatch(dt, head_dim, q, k, v, out, batch, heads, heads_kv, q_len, kv_len,
                                 q_strides, k_strides, v_strides, o_strides, qk_scale,
                                 causal ? 1 : 0, input_pos, pos_ptr, static_cast<cudaStream_t>(cu_stream));
@@ -681,7 +704,9 @@ int split_generics(const char* const* generics, int n, const char* dflt, const c
 int launch_fmha_generic(const char* kernel, const char* const* generics, int n_generics,
                         const b200tile_compile_options* opts, const void* const* params,
                         int n_params, const unsigned grid[3], void* stream, bool launch) {
-  (void)opts;
+  const int cga = (opts && opts->num_cta_in_cga > 0) ? opts->num_cta_in_cga : 0;
+  if (cga > 2)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: num_cta_in_cga=%d has no precompiled configuration", kernel, cga);
   const bool prefill = !strcmp(kernel, "fmha_prefill_causal");
   const char* dtype;
   long g[8];
@@ -727,11 +752,11 @@ int launch_fmha_generic(const char* kernel, const char* const* generics, int n_g
                        grid[0], grid[1], grid[2], (long)((q_len + BM - 1) / BM), heads);
     const int64_t qs[2] = {q.stride[1], q.stride[0]}, ks[2] = {k.stride[0], k.stride[1]};
     const int64_t vs[2] = {v.stride[0], v.stride[1]}, os[2] = {o.stride[1], o.stride[0]};
-    return b200tile_fmha_fwd(dtype, reinterpret_cast<const void*>(q.ptr),
-                             reinterpret_cast<const void*>(k.ptr),
-                             reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr),
-                             1, heads, heads_kv, q_len, kv_len, (int)D, qs, ks, vs, os, scale,
-                             causal != 0, query_start, stream);
+    return fmha_fwd_common(dtype, reinterpret_cast<const void*>(q.ptr),
+                           reinterpret_cast<const void*>(k.ptr),
+                           reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr),
+                           1, heads, heads_kv, q_len, kv_len, (int)D, qs, ks, vs, os, scale,
+                           causal != 0, query_start, nullptr, stream, cga);
   }
   read_tensor(r, 3, true, o);
   read_tensor(r, 4, false, q);
@@ -767,11 +792,11 @@ int launch_fmha_generic(const char* kernel, const char* const* generics, int n_g
                      grid[0], grid[1], grid[2], b * heads, (long)((m + BM - 1) / BM));
   const int64_t qs[2] = {q.stride[1], q.stride[2]}, ks[2] = {k.stride[1], k.stride[2]};
   const int64_t vs[2] = {v.stride[1], v.stride[2]}, os[2] = {o.stride[0], o.stride[1]};
-  return b200tile_fmha_fwd(dtype, reinterpret_cast<const void*>(q.ptr),
-                           reinterpret_cast<const void*>(k.ptr),
-                           reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr), b,
-                           heads, heads_kv, m, kv_len, (int)D, qs, ks, vs, os, scale, causal != 0,
-                           input_pos, stream);
+  return fmha_fwd_common(dtype, reinterpret_cast<const void*>(q.ptr),
+                         reinterpret_cast<const void*>(k.ptr),
+                         reinterpret_cast<const void*>(v.ptr), reinterpret_cast<void*>(o.ptr), b,
+                         heads, heads_kv, m, kv_len, (int)D, qs, ks, vs, os, scale, causal != 0,
+                         input_pos, nullptr, stream, cga);
 }
 
 // "linear_tile_fp8_blk128": (z [M,N] partition [BM,BN], x [M,K], y [N,K], x_scales [M,K/128],
@@ -1055,5 +1080,18 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
     return launch_group_gemm_generic(kernel, generics, n_generics, nullptr, 0, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
+
+#ifdef B200TILE_TRACE
+// Diagnostic builds only: copies the cycle counters of one traced kernel ("gemm_pair", "fmha",
+// "fmha_pair") into out[16]; see csrc/trace.cuh.
+B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
+  if (!which || !out) return B200TILE_ERR_INVALID;
+  for (int i = 0; i < 16; ++i) out[i] = 0;
+  if (!strcmp(which, "gemm_pair")) return b200_trace_read_gemm_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "fmha")) return b200_trace_read_fmha(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "fmha_pair")) return b200_trace_read_fmha_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  return B200TILE_ERR_UNSUPPORTED;
+}
+#endif
 
 }  // extern "C"

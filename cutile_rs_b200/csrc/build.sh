@@ -2,15 +2,18 @@
 # Builds libb200tile.so (sm_100a machine code only) next to this script's package.
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
-out="${here}/../libb200tile.so"
+# B200_VARIANT=name builds a second library (libb200tile_name.so, objects _x.name.o) next to the
+# product one, e.g. the diagnostic build: B200_VARIANT=trace B200_NVCC_EXTRA=-DB200TILE_TRACE
+variant="${B200_VARIANT:-}"
+out="${here}/../libb200tile${variant:+_${variant}}.so"
 NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
 FLAGS=(-std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a
        -Xcompiler -fPIC -Xcompiler -fvisibility=hidden ${B200_NVCC_EXTRA:-})
 objs=()
-for src in host_common gemm_tc gemm_tc_pair gemm_f32 gemm_fp8_blk gemm_nvfp4 fmha_fwd fmha_decode gemm_host gemm_grouped abi; do
-  obj="${here}/_${src}.o"
+for src in host_common gemm_tc gemm_tc_pair gemm_f32 gemm_fp8_blk gemm_nvfp4 fmha_fwd fmha_fwd_pair fmha_decode gemm_host gemm_grouped abi; do
+  obj="${here}/_${src}${variant:+.${variant}}.o"
   if [[ ! -f "${obj}" || "${here}/${src}.cu" -nt "${obj}" || "${here}/sm100_ptx.cuh" -nt "${obj}" \
-        || "${here}/host_common.h" -nt "${obj}" || "${here}/../../include/b200tile.h" -nt "${obj}" ]]; then
+        || "${here}/host_common.h" -nt "${obj}" || "${here}/fmha_common.cuh" -nt "${obj}" || "${here}/trace.cuh" -nt "${obj}" || "${here}/../../include/b200tile.h" -nt "${obj}" ]]; then
     "${NVCC}" "${FLAGS[@]}" -c "${here}/${src}.cu" -o "${obj}" &
   fi
   objs+=("${obj}")

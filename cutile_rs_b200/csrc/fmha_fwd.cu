@@ -25,57 +25,18 @@
 #include <math_constants.h>
 
 #include "host_common.h"
+#include "fmha_common.cuh"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
 
 namespace b200 {
 
-constexpr int FA_BM = 128;       // query rows per tile
-constexpr int FA_BN = 128;       // key rows per tile
-constexpr int FA_THREADS = 384;  // 12 warps
-constexpr float FA_RESCALE_THRESHOLD = 8.0f;
-// Register budget per role (setmaxnreg): 128 x 56 + 256 x 208 = 60416 <= 65536.
-constexpr int FA_SOFTMAX_REGS = 208;
-constexpr int FA_OTHER_REGS = 56;
-
-template <int N>
-__device__ __forceinline__ void reg_alloc() {
-  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
-}
-template <int N>
-__device__ __forceinline__ void reg_dealloc() {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
-}
-__device__ __forceinline__ float ex2_approx(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-// Packed fp32x2 arithmetic and the three-input maximum halve the instruction count of the softmax
-// inner loops (the softmax warps are issue- and latency-bound, not special-function-bound).
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
+#ifdef B200TILE_TRACE
+// One CTA: MMA thread [0] K/V waits, [1] P waits, [2] P.V issue, [3] Q.K issue, [4] S commits,
+// [5] stage-release commits, [6] key tiles, [7] total cycles; softmax lane 0 of tile 0 from [8]:
+// S wait, TMEM load, max and rescale, exp2 loop, store wait, hand-off, key tiles, total.
+__device__ long long g_trace_fmha[16];
+#endif
 
 template <int D>
 struct FmhaSmem {
@@ -91,17 +52,6 @@ struct FmhaSmem {
   static constexpr int NUM_BARS = 2 + 4 * KV_STAGES + 6;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
-};
-
-struct FmhaParams {
-  int q_len, kv_len;
-  int num_q_pairs;   // ceil(q_len / 256)
-  int bh_total;      // batch * heads
-  int heads, heads_kv, group;
-  int causal, input_pos;
-  const uint32_t* pos_ptr;  // when non-null the causal offset is read from device memory
-  int head_group;    // (batch*head) problems scheduled together for L2 reuse of K/V
-  float scale_log2;  // qk_scale * log2(e)
 };
 
 template <int D, bool OUT_F16>
@@ -254,6 +204,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       };
       bool ok = true;
+      B200_TR_DECL(7);
       // prologue: S_t(0) = Q_t K(0)^T
       ok = mbar_wait(wctx, bar_k_full + 0, 0, 20);
 #pragma unroll
@@ -269,26 +220,40 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t vs = j % STAGES, vph = (j / STAGES) & 1;
         const uint32_t ks = (j + 1) % STAGES, kph = ((j + 1) / STAGES) & 1;
         const bool have_next = j + 1 < n_max;
+        B200_TR_COUNT(6);
+        B200_TR_BEGIN();
         if (!mbar_wait(wctx, bar_v_full + vs * 8, vph, 22)) { ok = false; break; }
         if (have_next && !mbar_wait(wctx, bar_k_full + ks * 8, kph, 23)) { ok = false; break; }
         tc_fence_after_sync();
+        B200_TR_END(0);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < n_kv[t]) {
+            B200_TR_BEGIN();
             if (!mbar_wait(wctx, bar_p_full + t * 8, j & 1, 24)) { ok = false; break; }
             tc_fence_after_sync();
+            B200_TR_END(1);
+            B200_TR_BEGIN();
             issue_pv(t, sV + vs * TILE, j > 0);
+            B200_TR_END(2);
             if (j == n_kv[t] - 1) umma_commit(bar_o_done + t * 8);
           }
           if (j + 1 < n_kv[t]) {
+            B200_TR_BEGIN();
             issue_qk(t, sK + ks * TILE);
+            B200_TR_END(3);
+            B200_TR_BEGIN();
             umma_commit(bar_s_full + t * 8);
+            B200_TR_END(4);
           }
         }
         if (!ok) break;
+        B200_TR_BEGIN();
         umma_commit(bar_v_empty + vs * 8);
         if (have_next) umma_commit(bar_k_empty + ks * 8);
+        B200_TR_END(5);
       }
+      B200_TR_FLUSH(g_trace_fmha, 7, blockIdx.x == 7);
     }
   } else if (warp >= 4) {
     // -------------------------------- softmax ----------------------------------
@@ -304,9 +269,14 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const float scale = p.scale_log2;
     float m_run = -CUDART_INF_F, l_run = 0.0f;
     bool ok = true;
+    B200_TR_DECL(7);
     for (int j = 0; j < n_mine && ok; ++j) {
+      B200_TR_COUNT(6);
+      B200_TR_BEGIN();
       if (!mbar_wait(wctx, bar_s_full + t * 8, j & 1, 30)) { ok = false; break; }
       tc_fence_after_sync();
+      B200_TR_END(0);
+      B200_TR_BEGIN();
       // the whole score row lives in registers: one TMEM read per element
       uint32_t v[FA_BN];
 #pragma unroll
@@ -320,6 +290,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       const bool masked_tile = __any_sync(0xffffffffu, lim < FA_BN - 1);
       tmem_wait_ld();
+      B200_TR_END(1);
+      B200_TR_BEGIN();
       if (masked_tile) {
 #pragma unroll
         for (int i = 0; i < FA_BN; ++i)
@@ -360,6 +332,8 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       // probabilities: exp2(s*scale - m); masked entries are exp2(-inf) = 0
+      B200_TR_END(2);
+      B200_TR_BEGIN();
       const float neg_m = -m_run;
       const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(neg_m, neg_m);
       uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed (even, odd) partial sums
@@ -385,11 +359,17 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         unpack2(s23, ls[2], ls[3]);
       }
       l_run += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      B200_TR_END(3);
+      B200_TR_BEGIN();
       tmem_wait_st();
+      B200_TR_END(4);
+      B200_TR_BEGIN();
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_p_full + t * 8);
+      B200_TR_END(5);
     }
+    B200_TR_FLUSH(g_trace_fmha + 8, 7, blockIdx.x == 7 && warp == 4 && lane == 0);
     // ------------------------------- epilogue ----------------------------------
     if (n_mine > 0 && ok) {
       if (mbar_wait(wctx, bar_o_done + t * 8, 0, 31)) {
@@ -515,3 +495,9 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
   return b200h::set_error(B200_ERR_UNSUPPORTED,
                           "fmha: no kernel for head_dim %d (64 and 128 are provided)", head_dim);
 }
+
+#ifdef B200TILE_TRACE
+int b200_trace_read_fmha(long long* out) {
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fmha, 16 * sizeof(long long)) != cudaSuccess;
+}
+#endif

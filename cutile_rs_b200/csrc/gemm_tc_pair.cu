@@ -21,8 +21,15 @@
 
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
 
 namespace b200 {
+
+#ifdef B200TILE_TRACE
+// MMA thread of pair 10: [0] accumulator-buffer waits, [1] stage-full waits, [2] MMA issue,
+// [3] commits, [4] stages, [5] tiles, [6] total cycles
+__device__ long long g_trace_gemm_pair[8];
+#endif
 
 constexpr int P_BM = 128;   // rows per CTA (256 per pair)
 constexpr int P_BN = 256;   // columns per pair (128 loaded per CTA)
@@ -224,14 +231,22 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       PairSched sched;
       sched.init(num_kb, sk_tiles, total_tiles, pair, num_pairs);
       int tile, kb0, kb1;
+      B200_TR_DECL(6);
       for (; ok && sched.next(tile, kb0, kb1); ++it) {
         const uint32_t buf = it & 1;
+        B200_TR_BEGIN();
         if (!mbar_wait(wctx, bar_tempty + buf * 8, ((it >> 1) & 1) ^ 1, 2)) { ok = false; break; }
+        B200_TR_END(0);
+        B200_TR_COUNT(5);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * P_BN;
         for (int kb = kb0; kb < kb1; ++kb) {
+          B200_TR_BEGIN();
           if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
           tc_fence_after_sync();
+          B200_TR_END(1);
+          B200_TR_COUNT(4);
+          B200_TR_BEGIN();
           const uint64_t adesc = make_smem_desc(sA + stage * L::A_BYTES, 16, 1024, SWZ_128B);
           const uint64_t bdesc =
               B_KMAJOR ? make_smem_desc(sB + stage * L::B_BYTES, 16, 1024, SWZ_128B)
@@ -246,9 +261,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint64_t b_k = bdesc + (uint64_t)(B_KMAJOR ? kmaj_b : (uint32_t)(k * 128));
             umma_f16_ss_2cta(d_tmem, a_k, b_k, idesc, (kb != kb0) || (k != 0));
           }
+          B200_TR_END(2);
+          B200_TR_BEGIN();
           // free this stage in both CTAs once the MMAs have read it
           umma_commit_2cta(bar_empty + stage * 8);
           umma_commit_2cta(mapa_u32(bar_empty + stage * 8, 1));
+          B200_TR_END(3);
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) {
@@ -256,6 +274,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           umma_commit_2cta(mapa_u32(bar_tfull + buf * 8, 1));
         }
       }
+      B200_TR_FLUSH(g_trace_gemm_pair, 6, blockIdx.x == 20);
     }
   } else {
     // -------------------------------- epilogue ---------------------------------
@@ -502,3 +521,9 @@ int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* 
     return launch_gemm_pair<true, false>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
   return launch_gemm_pair<true, true>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
 }
+
+#ifdef B200TILE_TRACE
+int b200_trace_read_gemm_pair(long long* out) {
+  return cudaMemcpyFromSymbol(out, b200::g_trace_gemm_pair, 7 * sizeof(long long)) != cudaSuccess;
+}
+#endif

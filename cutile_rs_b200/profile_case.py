@@ -4,6 +4,13 @@
     python -m cutile_rs_b200.profile_case fmha --batch 1 --heads 16 --seq 4096 --causal 0 --iters 3
     python -m cutile_rs_b200.profile_case decode --heads 8 --group 4 --seq 65536 --splits 18 --iters 3
 
+With the diagnostic build (B200_VARIANT=trace B200_NVCC_EXTRA=-DB200TILE_TRACE csrc/build.sh) and
+B200TILE_LIB=cutile_rs_b200/libb200tile_trace.so, ``--trace`` prints where the MMA-issuing thread
+(and one softmax lane) of one CTA spent its cycles:
+
+    B200TILE_LIB=cutile_rs_b200/libb200tile_trace.so python -m cutile_rs_b200.profile_case gemm \
+        --m 8192 --n 8192 --k 8192 --config 2 --iters 5 --trace
+
 The default sizes keep the operands above the 126 MB L2 (so DRAM counters mean something) and the
 device footprint far below a few GB (so a multi-pass capture ends by itself).
 """
@@ -35,7 +42,12 @@ def main() -> None:
     ap.add_argument("--splits", type=int, default=18)
     ap.add_argument("--bn", type=int, default=128)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--pair", type=int, default=0, help="fmha: 1 = the CTA-pair configuration")
+    ap.add_argument("--trace", action="store_true", help="print the cycle counters of a trace build")
     args = ap.parse_args()
+    if args.pair:
+        import os
+        os.environ["B200TILE_FMHA_PAIR"] = "1"
 
     torch.cuda.set_device(0)
     lib = _lib.load()
@@ -95,6 +107,32 @@ def main() -> None:
     status = _lib.StatusC()
     _lib.check(lib.b200tile_status(stream.cuda_stream, ctypes.byref(status)))
     print(f"{args.kernel}: {ms:.4f} ms/launch, {flops / ms / 1e9:.1f} TFLOP/s")
+    if args.trace:
+        _print_trace(lib, args)
+
+
+def _print_trace(lib, args) -> None:
+    if not hasattr(lib, "b200tile_trace_read"):
+        raise SystemExit("--trace needs the diagnostic build (see the module docstring)")
+    out = (ctypes.c_longlong * 16)()
+    which = {"gemm": b"gemm_pair", "fmha": b"fmha_pair" if args.pair else b"fmha"}.get(args.kernel)
+    if which is None or lib.b200tile_trace_read(which, out):
+        raise SystemExit("no trace for this kernel")
+    v = list(out)
+    if args.kernel == "gemm":
+        stages, tiles = max(v[4], 1), max(v[5], 1)
+        print(f"MMA thread of one CTA pair, per 128-deep stage (8 MMAs 256x256x16 = 1024 tensor cycles): "
+              f"wait full {v[1] / stages:.0f}, issue {v[2] / stages:.0f}, commits {v[3] / stages:.0f}; "
+              f"accumulator waits {v[0] / tiles:.0f} per tile; total {v[6] / stages:.0f} cycles per stage "
+              f"({stages} stages, {tiles} tiles)")
+    else:
+        n, m = max(v[6], 1), max(v[14], 1)
+        names = ["K/V waits", "P waits", "P.V issue", "Q.K issue", "S commits", "release commits"]
+        print("MMA thread per key tile (both query tiles): " +
+              ", ".join(f"{nm} {v[i] / n:.0f}" for i, nm in enumerate(names)) + f"; total {v[7] / n:.0f} ({n} key tiles)")
+        names = ["S wait", "TMEM load", "max+rescale", "exp2 loop", "store wait", "hand-off"]
+        print("softmax lane per key tile: " + ", ".join(f"{nm} {v[8 + i] / m:.0f}" for i, nm in enumerate(names)) +
+              f"; total {v[15] / m:.0f}")
 
 
 if __name__ == "__main__":

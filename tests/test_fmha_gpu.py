@@ -146,3 +146,27 @@ def test_device_side_position_equals_host_side(b200):
                                                   pos.data_ptr(), _stream().cuda_stream))
         torch.cuda.synchronize()
         assert torch.equal(got, want)
+
+
+@pytest.mark.parametrize("s,causal", [(640, True), (300, False), (1024, True)])
+def test_cta_pair_configuration(b200, oracle, s, causal):
+    """`CompileOptions(num_cta_in_cga=2)` selects the kernel that shares every K/V tile between the two
+    CTAs of a cluster (512 query rows per cluster); ragged lengths leave query tiles of the cluster
+    partly or wholly past the end."""
+    b, h, hkv, d = 1, 4, 2, 128
+    q, k, v = workloads.fmha_inputs(b, h, s, d, h_kv=hkv, config_index=300 + s)
+    qd, kd, vd = (api.copy_host_to_device(t) for t in (q, k, v))
+    out = api.zeros([b * h, s, d], "bf16").partition([1, 128, d])
+    (out, *_rest) = launch.fmha(out, qd, kd, vd, 1 / math.sqrt(d), 0, h // hkv, causal=causal) \
+        .compile_options(launch.CompileOptions(num_cta_in_cga=2)).sync_on(_stream())
+    ref = oracle.fmha_ref_cpu(q.float().numpy(), k.float().numpy(), v.float().numpy(), 1 / math.sqrt(d),
+                              query_group_size=2, causal=causal, threads=0).reshape(b * h, s, d)
+    got = out.unpartition().to_host().float().numpy()
+    assert not np.isnan(got).any()
+    assert oracle.max_abs(got, ref) <= ATTN_TOL
+    st = _lib.StatusC()
+    _lib.check(b200.b200tile_status(_stream().cuda_stream, ctypes.byref(st)))
+    assert st.code == 0
+    with pytest.raises(Exception, match="num_cta_in_cga"):
+        launch.fmha(out, qd, kd, vd, 1 / math.sqrt(d), 0, h // hkv, causal=causal) \
+            .compile_options(launch.CompileOptions(num_cta_in_cga=4)).sync_on(_stream())
