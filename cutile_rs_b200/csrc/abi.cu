@@ -1083,10 +1083,10 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
 
 #ifdef B200TILE_TRACE
 // Diagnostic builds only: copies the cycle counters of one traced kernel ("gemm_pair", "fmha",
-// "fmha_pair") into out[16]; see csrc/trace.cuh.
+// "fmha_pair") into out[20]; see csrc/trace.cuh.
 B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!which || !out) return B200TILE_ERR_INVALID;
-  for (int i = 0; i < 16; ++i) out[i] = 0;
+  for (int i = 0; i < 20; ++i) out[i] = 0;
   if (!strcmp(which, "gemm_pair")) return b200_trace_read_gemm_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha")) return b200_trace_read_fmha(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha_pair")) return b200_trace_read_fmha_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;

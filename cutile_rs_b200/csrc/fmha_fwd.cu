@@ -33,9 +33,9 @@ namespace b200 {
 
 #ifdef B200TILE_TRACE
 // One CTA: MMA thread [0] K/V waits, [1] P waits, [2] P.V issue, [3] Q.K issue, [4] S commits,
-// [5] stage-release commits, [6] key tiles, [7] total cycles; softmax lane 0 of tile 0 from [8]:
+// [5] stage-release commits, [6] key tiles, [7] total cycles; [8] the same span in ns; softmax lane 0 of tile 0 from [10]:
 // S wait, TMEM load, max and rescale, exp2 loop, store wait, hand-off, key tiles, total.
-__device__ long long g_trace_fmha[16];
+__device__ long long g_trace_fmha[20];
 #endif
 
 template <int D>
@@ -369,7 +369,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (lane == 0) mbar_arrive(bar_p_full + t * 8);
       B200_TR_END(5);
     }
-    B200_TR_FLUSH(g_trace_fmha + 8, 7, blockIdx.x == 7 && warp == 4 && lane == 0);
+    B200_TR_FLUSH(g_trace_fmha + 10, 7, blockIdx.x == 7 && warp == 4 && lane == 0);
     // ------------------------------- epilogue ----------------------------------
     if (n_mine > 0 && ok) {
       if (mbar_wait(wctx, bar_o_done + t * 8, 0, 31)) {
@@ -498,6 +498,6 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
 
 #ifdef B200TILE_TRACE
 int b200_trace_read_fmha(long long* out) {
-  return cudaMemcpyFromSymbol(out, b200::g_trace_fmha, 16 * sizeof(long long)) != cudaSuccess;
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fmha, 20 * sizeof(long long)) != cudaSuccess;
 }
 #endif

@@ -24,9 +24,9 @@ namespace b200 {
 
 #ifdef B200TILE_TRACE
 // One CTA: MMA thread [0] K/V waits, [1] P waits, [2] P.V issue, [3] Q.K issue, [4] S commits,
-// [5] stage-release commits, [6] key tiles, [7] total cycles; softmax lane 0 of tile 0 from [8]:
+// [5] stage-release commits, [6] key tiles, [7] total cycles; [8] the same span in ns; softmax lane 0 of tile 0 from [10]:
 // S wait, TMEM load, max and rescale, exp2 loop, store wait, hand-off, key tiles, total.
-__device__ long long g_trace_fmha_pair[16];
+__device__ long long g_trace_fmha_pair[20];
 #endif
 
 struct FmhaPairSmem {
@@ -363,7 +363,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (lane == 0) mbar_arrive_cluster_addr(p_full_leader);
       B200_TR_END(5);
     }
-    B200_TR_FLUSH(g_trace_fmha_pair + 8, 7, blockIdx.x == 14 && warp == 4 && lane == 0);
+    B200_TR_FLUSH(g_trace_fmha_pair + 10, 7, blockIdx.x == 14 && warp == 4 && lane == 0);
     // ------------------------------- epilogue ----------------------------------
     if (n_mine > 0 && ok) {
       if (mbar_wait(wctx, bar_o_done + t * 8, 0, 31)) {
@@ -488,6 +488,6 @@ int b200_fmha_fwd_pair_dispatch(int dtype, const void* q, const void* k, const v
 
 #ifdef B200TILE_TRACE
 int b200_trace_read_fmha_pair(long long* out) {
-  return cudaMemcpyFromSymbol(out, b200::g_trace_fmha_pair, 16 * sizeof(long long)) != cudaSuccess;
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fmha_pair, 20 * sizeof(long long)) != cudaSuccess;
 }
 #endif

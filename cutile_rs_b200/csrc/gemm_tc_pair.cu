@@ -27,7 +27,7 @@ namespace b200 {
 
 #ifdef B200TILE_TRACE
 // MMA thread of pair 10: [0] accumulator-buffer waits, [1] stage-full waits, [2] MMA issue,
-// [3] commits, [4] stages, [5] tiles, [6] total cycles
+// [3] commits, [4] stages, [5] tiles, [6] total cycles, [7] the same span in ns
 __device__ long long g_trace_gemm_pair[8];
 #endif
 
@@ -524,6 +524,6 @@ int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* 
 
 #ifdef B200TILE_TRACE
 int b200_trace_read_gemm_pair(long long* out) {
-  return cudaMemcpyFromSymbol(out, b200::g_trace_gemm_pair, 7 * sizeof(long long)) != cudaSuccess;
+  return cudaMemcpyFromSymbol(out, b200::g_trace_gemm_pair, 8 * sizeof(long long)) != cudaSuccess;
 }
 #endif

@@ -114,7 +114,7 @@ def main() -> None:
 def _print_trace(lib, args) -> None:
     if not hasattr(lib, "b200tile_trace_read"):
         raise SystemExit("--trace needs the diagnostic build (see the module docstring)")
-    out = (ctypes.c_longlong * 16)()
+    out = (ctypes.c_longlong * 20)()
     which = {"gemm": b"gemm_pair", "fmha": b"fmha_pair" if args.pair else b"fmha"}.get(args.kernel)
     if which is None or lib.b200tile_trace_read(which, out):
         raise SystemExit("no trace for this kernel")
@@ -124,15 +124,15 @@ def _print_trace(lib, args) -> None:
         print(f"MMA thread of one CTA pair, per 128-deep stage (8 MMAs 256x256x16 = 1024 tensor cycles): "
               f"wait full {v[1] / stages:.0f}, issue {v[2] / stages:.0f}, commits {v[3] / stages:.0f}; "
               f"accumulator waits {v[0] / tiles:.0f} per tile; total {v[6] / stages:.0f} cycles per stage "
-              f"({stages} stages, {tiles} tiles)")
+              f"({stages} stages, {tiles} tiles); SM clock inside the kernel {1e3 * v[6] / max(v[7], 1):.0f} MHz")
     else:
-        n, m = max(v[6], 1), max(v[14], 1)
+        n, m = max(v[6], 1), max(v[16], 1)
         names = ["K/V waits", "P waits", "P.V issue", "Q.K issue", "S commits", "release commits"]
         print("MMA thread per key tile (both query tiles): " +
-              ", ".join(f"{nm} {v[i] / n:.0f}" for i, nm in enumerate(names)) + f"; total {v[7] / n:.0f} ({n} key tiles)")
+              ", ".join(f"{nm} {v[i] / n:.0f}" for i, nm in enumerate(names)) + f"; total {v[7] / n:.0f} ({n} key tiles); SM clock inside the kernel {1e3 * v[7] / max(v[8], 1):.0f} MHz")
         names = ["S wait", "TMEM load", "max+rescale", "exp2 loop", "store wait", "hand-off"]
-        print("softmax lane per key tile: " + ", ".join(f"{nm} {v[8 + i] / m:.0f}" for i, nm in enumerate(names)) +
-              f"; total {v[15] / m:.0f}")
+        print("softmax lane per key tile: " + ", ".join(f"{nm} {v[10 + i] / m:.0f}" for i, nm in enumerate(names)) +
+              f"; total {v[17] / m:.0f}")
 
 
 if __name__ == "__main__":
