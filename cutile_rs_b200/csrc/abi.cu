@@ -54,6 +54,8 @@ int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const vo
 int b200_fmha_decode_dispatch(int dtype, int head_dim, const void* q, const void* k, const void* v, void* att,
                               float* lse, void* out, const uint32_t* pos, int kv_heads, int group, int kv_cap,
                               int bn, int splits, float qk_scale, const int64_t* strides, cudaStream_t stream);
+int b200_gemm_swiglu_dispatch(int dtype, const void* X, const void* W, void* O, int M, int I, int K, int64_t ldx,
+                              int64_t ldw, int64_t ldo, cudaStream_t stream);
 size_t b200_grouped_workspace_bytes(int groups);
 int b200_gemm_grouped_dispatch(int dtype, int bn, const int64_t* a_ptrs, const int64_t* b_ptrs, const int64_t* c_ptrs,
                                const int32_t* a_metas, const int32_t* b_metas, const int32_t* c_metas, int groups,
@@ -351,6 +353,26 @@ int b200tile_splitk_reduce_merge(const char* dtype, const void* att_partial, con
   const int64_t strides[5] = {att_strides[0], att_strides[1], lse_head_stride, out_strides[0], out_strides[1]};
   return b200_splitk_merge_dispatch(dt, head_dim, att_partial, lse_partial, out, kv_heads, group, num_kv_splits,
                                     strides, static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---------------------------------------------------------------------------
+// Linear layer with the SwiGLU pointwise step fused into its epilogue
+// ---------------------------------------------------------------------------
+int b200tile_linear_swiglu(const char* dtype, const void* x, const void* w_gate_up, void* out, int m, int inter,
+                           int k, int64_t ldx, int64_t ldw, int64_t ldo, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "linear_swiglu", &dt)) return rc;
+  if (!x || !w_gate_up || !out) return set_error(B200TILE_ERR_INVALID, "linear_swiglu: null tensor pointer");
+  if (m <= 0 || inter <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_swiglu: Shape dimensions must be positive");
+  if (ldx < k || ldw < k || ldo < inter)
+    return set_error(B200TILE_ERR_INVALID, "linear_swiglu: a leading dimension is smaller than its row");
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w_gate_up) |
+                       reinterpret_cast<uintptr_t>(out);
+  if ((al & 15) != 0 || (ldx % 8) || (ldw % 8) || (ldo % 8))
+    return set_error(B200TILE_ERR_ALIGN, "linear_swiglu: base pointers and row pitches must be 16-byte aligned");
+  return b200_gemm_swiglu_dispatch(dt, x, w_gate_up, out, m, inter, k, ldx, ldw, ldo,
+                                   static_cast<cudaStream_t>(cu_stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -48,14 +48,38 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   bn = (tile % in_group) / gsz;
 }
 
+// silu(gate) * up on values that first pass through the 16-bit type, as they would between the GEMM
+// and the pointwise kernel: y = gate / (1 + exp(-gate)) * up in fp32 (pointwise.rs:66-74).
+template <bool OUT_F16>
+__device__ __forceinline__ float swiglu_16bit(float gate, float up) {
+  const uint32_t packed = OUT_F16 ? pack_f16x2(gate, up) : pack_bf16x2(gate, up);
+  float g, u;
+  if (OUT_F16) {
+    asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %2; cvt.f32.f16 %0, lo; cvt.f32.f16 %1, hi;}"
+        : "=f"(g), "=f"(u) : "r"(packed));
+  } else {
+    g = __uint_as_float(packed << 16);
+    u = __uint_as_float(packed & 0xffff0000u);
+  }
+  const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+  return sig * g * u;
+}
+
 // B_KMAJOR = false: B is [K,N] row-major (the reference GEMM layout; N-major operand)
 // B_KMAJOR = true : B is [N,K] row-major (the reference `linear_tile` layout; K-major operand)
 // OUT_F16 selects f16 instead of bf16 for the 16-bit output pack.
-template <int BN, bool B_KMAJOR, bool OUT_F16>
+// SWIGLU (BN = 256, K-major B only): B is [2N, K] = N gate rows followed by N up rows; a tile takes 128
+// rows of each as one 256-row operand, so accumulator columns [0,128) hold x.gate^T and [128,256)
+// x.up^T for the same 128 output columns, and the epilogue stores silu(gate) * up -- the GEMM and
+// `silu_mul_2d_f16` (cutile-kernels/src/pointwise.rs:50-77) in one pass, with gate and up rounded to
+// the 16-bit type in between exactly as the two-kernel sequence does.
+template <int BN, bool B_KMAJOR, bool OUT_F16, bool SWIGLU = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int group_m,
                uint32_t idesc, uint32_t* status) {
+  static_assert(!SWIGLU || (BN == 256 && B_KMAJOR), "the fused SwiGLU epilogue pairs two 128-row K-major B blocks");
+  constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;   // output columns per tile
   using L = GemmSmem<BN>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -101,7 +125,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = misc[0];
 
   const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
-  const int tiles_n = (N + BN - 1) / BN;
+  const int tiles_n = (N + BN_OUT - 1) / BN_OUT;
   const int total_tiles = tiles_m * tiles_n;
   const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
 
@@ -113,13 +137,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int bm, bn;
         tile_coords(tile, tiles_m, tiles_n, group_m, bm, bn);
-        const int m0 = bm * GEMM_BM, n0 = bn * BN;
+        const int m0 = bm * GEMM_BM, n0 = bn * BN_OUT;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
           const uint32_t full = bar_full + stage * 8;
           mbar_expect_tx(full, L::A_BYTES + L::B_BYTES);
           tma_load_2d(sA + stage * L::A_BYTES, &tmA, full, kb * GEMM_BK, m0);
-          if (B_KMAJOR) {
+          if (SWIGLU) {
+            // 128 gate rows, then the 128 up rows that belong to the same output columns
+            tma_load_2d(sB + stage * L::B_BYTES, &tmB, full, kb * GEMM_BK, n0);
+            tma_load_2d(sB + stage * L::B_BYTES + BN_OUT * 128, &tmB, full, kb * GEMM_BK, N + n0);
+          } else if (B_KMAJOR) {
             tma_load_2d(sB + stage * L::B_BYTES, &tmB, full, kb * GEMM_BK, n0);
           } else {
 #pragma unroll
@@ -172,16 +200,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       int bm, bn;
       tile_coords(tile, tiles_m, tiles_n, group_m, bm, bn);
-      const int m0 = bm * GEMM_BM, n0 = bn * BN;
+      const int m0 = bm * GEMM_BM, n0 = bn * BN_OUT;
       const uint32_t buf = it & 1;
       if (!mbar_wait(wctx, bar_tfull + buf * 8, (it >> 1) & 1, 4)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
 #pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
+      for (int c = 0; c < BN_OUT / 64; ++c) {
         uint32_t v0[32], v1[32];
         tmem_ld_32x32b_x32(t_row + c * 64, v0);
         tmem_ld_32x32b_x32(t_row + c * 64 + 32, v1);
+        if (SWIGLU) {
+          uint32_t u0[32], u1[32];
+          tmem_ld_32x32b_x32(t_row + BN_OUT + c * 64, u0);
+          tmem_ld_32x32b_x32(t_row + BN_OUT + c * 64 + 32, u1);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v0[i] = __float_as_uint(swiglu_16bit<OUT_F16>(__uint_as_float(v0[i]), __uint_as_float(u0[i])));
+            v1[i] = __float_as_uint(swiglu_16bit<OUT_F16>(__uint_as_float(v1[i]), __uint_as_float(u1[i])));
+          }
+        }
         // staging buffer (c & 1): the store issued two chunks ago must have drained it
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
@@ -271,6 +310,40 @@ static int launch_gemm_tc(const void* A, const void* B, void* C, int M, int N, i
   return B200_OK;
 }
 
+// out[M, I] = silu(x . w[0:I]^T) * (x . w[I:2I]^T), x [M,K], w [2I,K] (gate rows, then up rows)
+template <bool OUT_F16>
+static int launch_gemm_swiglu(const void* X, const void* W, void* O, int M, int I, int K, int64_t ldx, int64_t ldw,
+                              int64_t ldo, cudaStream_t stream) {
+  using L = GemmSmem<256>;
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200_ERR_CUDA;
+  const CUtensorMapDataType dt = OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = b200h::encode_tmap_2d(&tmA, dt, 2, X, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, GEMM_BK, GEMM_BM,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_2d(&tmB, dt, 2, W, (uint64_t)K, (uint64_t)2 * I, (uint64_t)ldw * 2, GEMM_BK, 128,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_2d(&tmC, dt, 2, O, (uint64_t)I, (uint64_t)M, (uint64_t)ldo * 2, 64, 32,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  auto kern = gemm_tc_kernel<256, true, OUT_F16, true>;
+  static bool attr_done[64] = {};
+  if (!attr_done[di->ordinal]) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    attr_done[di->ordinal] = true;
+  }
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((I + 127) / 128);
+  const int grid = tiles < di->sm_count ? tiles : di->sm_count;
+  const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
+  const uint32_t idesc = make_idesc(fmt, fmt, 0, 0, GEMM_BM, 256);
+  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, I, K, 8, idesc, di->status);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
 }  // namespace b200
 
 // dtype: 0 = bf16, 1 = f16.  b_kmajor: 0 = B[K,N] row-major, 1 = B[N,K] row-major.
@@ -296,4 +369,12 @@ int b200_gemm_tc_dispatch(int dtype, int b_kmajor, int config, const void* A, co
 #undef B200_GEMM_CASE
   return b200h::set_error(B200_ERR_UNSUPPORTED, "gemm: no kernel for dtype %d / config %d", dtype,
                           config);
+}
+
+// dtype: 0 = bf16, 1 = f16.
+int b200_gemm_swiglu_dispatch(int dtype, const void* X, const void* W, void* O, int M, int I, int K, int64_t ldx,
+                              int64_t ldw, int64_t ldo, cudaStream_t stream) {
+  using namespace b200;
+  return dtype ? launch_gemm_swiglu<true>(X, W, O, M, I, K, ldx, ldw, ldo, stream)
+               : launch_gemm_swiglu<false>(X, W, O, M, I, K, ldx, ldw, ldo, stream);
 }

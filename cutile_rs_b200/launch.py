@@ -531,3 +531,20 @@ def group_gemm_tables(a_list: Sequence[torch.Tensor], b_list: Sequence[torch.Ten
         return Tensor(ptrs.to(dev)), Tensor(metas.to(dev))
     (ap, am), (bp, bm), (cp, cm) = tables(a_list), tables(b_list), tables(c_list)
     return ap, bp, cp, am, bm, cm
+
+
+def linear_swiglu(out: Tensor, x: Tensor, w_gate_up: Tensor, stream: Optional[torch.cuda.Stream] = None) -> Tensor:
+    """out [M, I] = silu(x . w[:I]^T) * (x . w[I:]^T) in one kernel: the NT linear layer and
+    `silu_mul_2d_f16` (cutile-kernels/src/pointwise.rs:50-77) fused; x [M, K], w_gate_up [2I, K]."""
+    lib = _lib.load()
+    s = stream or torch.cuda.current_stream()
+    m, inter = out.shape
+    k = x.shape[1]
+    if tuple(w_gate_up.shape) != (2 * inter, k) or x.shape[0] != m:
+        raise KernelLaunchError("linear_swiglu: expected x [M,K], w_gate_up [2I,K], out [M,I]")
+    rc = lib.b200tile_linear_swiglu(out.dtype_str().encode(), x.cu_deviceptr(), w_gate_up.cu_deviceptr(),
+                                    out.cu_deviceptr(), m, inter, k, x.strides[0], w_gate_up.strides[0],
+                                    out.strides[0], c_void_p(s.cuda_stream))
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+    return out

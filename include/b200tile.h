@@ -148,6 +148,17 @@ B200TILE_API int b200tile_gemm_host(const char* dtype, int b_layout, const void*
                                     void* c_host, void* a_dev, void* b_dev, void* c_dev, int m, int n, int k,
                                     int slab_rows, void* cu_stream);
 
+/* out[m, inter] = silu(x . w[0:inter]^T) * (x . w[inter:2*inter]^T): the gate/up projection of a
+ * SwiGLU feed-forward block with the pointwise step in the GEMM epilogue.  Replaces the sequence
+ * "NT linear layer into [m, 2*inter], then `silu_mul_2d_f16`" (cutile-kernels/src/pointwise.rs:
+ * 50-77); gate and up are rounded to the 16-bit type before the pointwise step, as that sequence
+ * does, so the result differs from it only by the exp implementation.
+ *   dtype      "bf16" or "f16"
+ *   x          [m, k], row pitch ldx;  w_gate_up [2*inter, k] (gate rows first), row pitch ldw
+ *   out        [m, inter], row pitch ldo.  Pitches in elements, multiples of 8; pointers 16-byte aligned. */
+B200TILE_API int b200tile_linear_swiglu(const char* dtype, const void* x, const void* w_gate_up, void* out, int m,
+                                        int inter, int k, int64_t ldx, int64_t ldw, int64_t ldo, void* cu_stream);
+
 /* Persistent grouped GEMM over device-side tables (MoE expert batches): for g in [0, num_groups)
  * C_g [m_g, n_g] = A_g [m_g, k_g] * B_g [k_g, n_g], row-major 16-bit operands, fp32 accumulation.
  * Replaces `group_gemm_f16_nt_desc` (cutile-kernels/src/experimental/moe.rs:66-128).

@@ -239,6 +239,16 @@ def dequant_mxfp8(q, s) -> np.ndarray:
 
 
 # ---- scheduling -------------------------------------------------------------------------
+def silu_mul(gate, up, is_f16: bool = False) -> np.ndarray:
+    """`silu_mul_2d_f16` (cutile-kernels/src/pointwise.rs:63-75): 16-bit inputs widened to f32,
+    sigmoid = 1 / (1 + exp(-gate)), y = sigmoid * gate * up, rounded to the 16-bit type."""
+    g, u = _f32(gate), _f32(up)
+    one = np.float32(1.0)
+    sig = one / (one + np.exp(-g, dtype=np.float32))
+    y = (sig * g * u).astype(np.float32)
+    return y.astype(np.float16).astype(np.float32) if is_f16 else round_bf16(y)
+
+
 def persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy) -> int:
     return int(lib().oracle_persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy))
 

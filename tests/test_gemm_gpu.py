@@ -216,3 +216,27 @@ def test_host_operand_pipeline(b200, oracle, dtype, m, n, k, layout, slab):
         assert oracle.rel_frobenius(first.float().numpy(), ref) <= 1e-2
         assert oracle.rel_frobenius(c.float().numpy(), 0.5 * ref) <= 1e-2
     assert not torch.isnan(c.float()).any()
+
+
+@pytest.mark.parametrize("dtype,m,inter,k", [(torch.bfloat16, 300, 384, 320), (torch.float16, 128, 200, 256),
+                                             (torch.bfloat16, 1024, 1024, 512)])
+def test_linear_with_fused_swiglu(b200, oracle, dtype, m, inter, k):
+    """silu(x.Wg^T) * (x.Wu^T) from one kernel against the reference's two-step restatement: GEMM
+    outputs rounded to the 16-bit type, then `silu_mul_2d_f16` in fp32 (pointwise.rs:63-75)."""
+    g = torch.Generator().manual_seed(inter + k)
+    x = (torch.randn(m, k, generator=g) / 4).to(dtype)
+    w = (torch.randn(2 * inter, k, generator=g) / 4).to(dtype)
+    name = "bf16" if dtype == torch.bfloat16 else "f16"
+    out = api.from_torch(torch.full((m, inter), float("nan"), dtype=dtype, device="cuda"))
+    launch.linear_swiglu(out, api.copy_host_to_device(x), api.copy_host_to_device(w))
+    torch.cuda.synchronize()
+    is_f16 = dtype == torch.float16
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if is_f16 else oracle.round_bf16
+    gate = rnd(oracle.cpu_gemm_nt(x.float().numpy(), w[:inter].float().numpy(), threads=0))
+    up = rnd(oracle.cpu_gemm_nt(x.float().numpy(), w[inter:].float().numpy(), threads=0))
+    ref = oracle.silu_mul(gate, up, is_f16)
+    got = out.storage.float().cpu().numpy()
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= 1e-2
+    # element-wise: one rounding step of the output type plus the effect of a last-bit difference in gate/up
+    assert np.max(np.abs(got - ref) / (np.abs(ref) + 1e-2)) <= 0.05
