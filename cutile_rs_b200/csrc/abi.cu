@@ -35,6 +35,7 @@ int b200_fmha_fwd_pair_dispatch(int dtype, const void* q, const void* k, const v
 int b200_trace_read_gemm_pair(long long* out);
 int b200_trace_read_fmha(long long* out);
 int b200_trace_read_fmha_pair(long long* out);
+int b200_trace_read_fp4(long long* out);
 #endif
 
 int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const float* xs,
@@ -1112,6 +1113,7 @@ B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!strcmp(which, "gemm_pair")) return b200_trace_read_gemm_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha")) return b200_trace_read_fmha(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha_pair")) return b200_trace_read_fmha_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "block_scaled")) return b200_trace_read_fp4(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   return B200TILE_ERR_UNSUPPORTED;
 }
 #endif

@@ -8,24 +8,32 @@
 //
 // The tensor core applies the scales itself (tcgen05.mma kind::mxf4nvf4.block_scale, one UE4M3
 // scale per 16 elements, K = 64 per instruction) but wants them in Tensor Memory in a fixed
-// arrangement: per 128 rows x 4 scale columns a 512-byte block with byte (row%32)*16 + (row/32)*4 +
-// col, copied by tcgen05.cp 32x128b.warpx4.  The row-major scale tensors are therefore re-laid
-// out once per call by a small pre-pass into a SCRATCH buffer, [tile][K/64][chunk][512 B], from
-// which the main kernel fetches whole stages with 1-D bulk copies.
+// arrangement: per 128 rows x 4 scale columns, lane (row % 32) of every 32-lane quadrant holds the
+// four scale bytes of rows l, l+32, l+64, l+96 in four consecutive columns -- as a 512-byte block,
+// byte (row%32)*16 + (row/32)*4 + col.  The row-major scale tensors are therefore re-laid out once
+// per call by a small pre-pass into a SCRATCH buffer, [tile][K/64][chunk][512 B], from which the
+// main kernel fetches whole stages with 1-D bulk copies.
 //
 //   warp 0      TMA producer: A (128 x 128 B), B (BN x 128 B) and both scale blocks per stage
-//   warp 1      issuer: tcgen05.cp of the stage's scales, then 4 block-scaled MMAs (K = 64 each)
+//   warp 1      issuer: 4 block-scaled MMAs (K = 64 each) per stage, nothing else on its queue
 //   warps 2..5  epilogue: tcgen05.ld -> alpha -> bf16/f32 -> global
+//   warps 6..9  scale writers: shared memory -> Tensor Memory with tcgen05.st, one warp per quadrant
 #include <mutex>
 
 #include "../../include/b200tile.h"
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
 
 namespace b200 {
 
+#ifdef B200TILE_TRACE
+// MMA thread of CTA 5: [0] accumulator waits, [1] unused, [2] stage + scale ready waits, [3] MMA issue, [4] commits, [5] stages, [6] total cycles, [7] the same span in ns
+__device__ long long g_trace_fp4[8];
+#endif
+
 constexpr int F4_BM = 128;
-constexpr int F4_THREADS = 192;
+constexpr int F4_THREADS = 320;  // TMA, MMA, 4 epilogue warps, 4 scale-writer warps
 
 // FP4 = true : NVFP4 (packed e2m1, UE4M3 scale per 16, K = 64 per MMA, 256 elements per stage)
 // FP4 = false: MXFP8 (e4m3, UE8M0 scale per 32, K = 32 per MMA, 128 elements per stage)
@@ -35,19 +43,30 @@ template <int BN, bool FP4 = true>
 struct Fp4Cfg {
   static constexpr int CHUNKS = (BN + 127) / 128;            // 128-row scale blocks per B tile
   static constexpr int KQ_PER_STAGE = FP4 ? 4 : 1;           // scale blocks along K per stage
-  static constexpr int SF_COLS = 4 * KQ_PER_STAGE * (1 + CHUNKS);  // TMEM columns of a stage's scales
-  static constexpr int NACC = (2 * BN + 2 * SF_COLS <= 512) ? 2 : 1;
+  static constexpr int STAGES_ = (BN <= 128) ? 5 : 4;
+  // Scales travel to Tensor Memory in REGIONS of RK scale blocks along K (half a stage for NVFP4, a
+  // whole one for MXFP8); the columns left beside the accumulators form a ring of NREG regions so
+  // that the writers run ahead of the MMAs.  NREG < STAGES * HALVES keeps a writer's wait on a
+  // stage's `empty` barrier within one phase of that barrier.
+  static constexpr int RK = FP4 ? 2 : 1;
+  static constexpr int HALVES = KQ_PER_STAGE / RK;           // regions per stage
+  static constexpr int MMAS_PER_REGION = 4 / HALVES;
+  static constexpr int REGION_COLS = 4 * RK * (1 + CHUNKS);
+  static constexpr int NACC = (2 * BN + 2 * REGION_COLS <= 512) ? 2 : 1;
   static constexpr int SF_BASE = NACC * BN;                  // scales sit after the accumulators
+  static constexpr int NREG_FIT = (512 - NACC * BN) / REGION_COLS;
+  static constexpr int NREG = NREG_FIT < STAGES_ * HALVES - 1 ? NREG_FIT : STAGES_ * HALVES - 1;
+  static_assert(NREG >= 2, "at least two scale regions");
   static constexpr int A_BYTES = F4_BM * 128;
   static constexpr int B_BYTES = BN * 128;
   static constexpr int SFA_BYTES = KQ_PER_STAGE * 512;
   static constexpr int SFB_BYTES = KQ_PER_STAGE * CHUNKS * 512;
-  static constexpr int SFB_COL0 = 4 * KQ_PER_STAGE;          // first TMEM column of the B scales
+  static constexpr int SFB_COL0 = 4 * RK;                    // first column of the B scales inside a region
   static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;  // bytes landed per stage
   static constexpr int STAGE_BYTES = (STAGE_TX + 1023) / 1024 * 1024;         // 1024-aligned stride
-  static constexpr int STAGES = (BN <= 128) ? 5 : 4;
+  static constexpr int STAGES = STAGES_;
   static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 4;
+  static constexpr int NUM_BARS = 2 * STAGES + 4 + NREG;   // + one `ready` barrier per scale region
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
 };
@@ -84,9 +103,6 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
 }
 // 32 rows x 16 bytes of shared memory -> TMEM lanes 0..31 (4 columns), replicated into all four
 // 32-lane quarters.
-__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
 __device__ __forceinline__ void umma_nvfp4_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                               uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
   asm volatile(
@@ -130,6 +146,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t bar_empty = bar_full + STAGES * 8;
   const uint32_t bar_tfull = bar_empty + STAGES * 8;
   const uint32_t bar_tempty = bar_tfull + 2 * 8;
+  const uint32_t bar_sf_ready = bar_tempty + 2 * 8;   // [NREG]: stage landed in shared memory AND the region's scales in TMEM
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + C::OFF_MISC);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wctx{misc + 1, status};
@@ -147,6 +164,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(bar_tfull + b * 8, 1);
       mbar_init(bar_tempty + b * 8, 4);
     }
+    for (int r = 0; r < C::NREG; ++r) mbar_init(bar_sf_ready + r * 8, 4);   // one arrival per scale-writer warp
     misc[1] = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -199,43 +217,109 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0, it = 0, g = 0;
+      uint32_t stage = 0, phase = 0, it = 0, g = 0, reg = 0, reg_par = 0;
       bool ok = true;
+      B200_TR_DECL(6);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
         const uint32_t buf = (C::NACC == 2) ? (it & 1) : 0;
         const uint32_t par = (C::NACC == 2) ? (((it >> 1) & 1) ^ 1) : ((it & 1) ^ 1);
+        B200_TR_BEGIN();
         if (!mbar_wait(wctx, bar_tempty + buf * 8, par, 2)) { ok = false; break; }
+        B200_TR_END(0);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb, ++g) {
-          if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
-          tc_fence_after_sync();
-          // this stage's scales: smem -> TMEM (two alternating TMEM regions)
-          const uint32_t sf_t = tmem_base + C::SF_BASE + (g & 1) * C::SF_COLS;
-#pragma unroll
-          for (int k = 0; k < C::KQ_PER_STAGE; ++k) {
-            tmem_cp_32x128b_warpx4(sf_t + k * 4, make_smem_desc(stage_sfa(stage) + k * 512, 16, 128, 0));
-#pragma unroll
-            for (int c = 0; c < C::CHUNKS; ++c)
-              tmem_cp_32x128b_warpx4(sf_t + C::SFB_COL0 + (k * C::CHUNKS + c) * 4,
-                                     make_smem_desc(stage_sfb(stage) + (k * C::CHUNKS + c) * 512, 16, 128, 0));
-          }
+          B200_TR_COUNT(5);
           const uint64_t adesc = make_smem_desc(stage_a(stage), 16, 1024, SWZ_128B);
           const uint64_t bdesc = make_smem_desc(stage_b(stage), 16, 1024, SWZ_128B);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            if (FP4)
-              umma_nvfp4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
-                            make_idesc_nvfp4(F4_BM, BN), sf_t + k * 4, sf_t + C::SFB_COL0 + k * C::CHUNKS * 4,
-                            (kb | k) != 0);
-            else
-              umma_mxfp8_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
-                            make_idesc_mxfp8(F4_BM, BN, (uint32_t)k), sf_t, sf_t + C::SFB_COL0, (kb | k) != 0);
+          for (int h = 0; h < C::HALVES; ++h) {
+            B200_TR_BEGIN();
+            // the scale writers arrive only after the stage's TMA bytes have landed, so this wait
+            // covers the operands in shared memory and the region's scales in Tensor Memory
+            const uint32_t sf_t = tmem_base + C::SF_BASE + reg * C::REGION_COLS;
+            if (!mbar_wait(wctx, bar_sf_ready + reg * 8, reg_par, 6)) { ok = false; break; }
+            tc_fence_after_sync();
+            B200_TR_END(2);
+            B200_TR_BEGIN();
+#pragma unroll
+            for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
+              const int k = h * C::MMAS_PER_REGION + kk;
+              if (FP4)
+                umma_nvfp4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                              make_idesc_nvfp4(F4_BM, BN), sf_t + kk * 4, sf_t + C::SFB_COL0 + kk * C::CHUNKS * 4,
+                              (kb | k) != 0);
+              else
+                umma_mxfp8_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                              make_idesc_mxfp8(F4_BM, BN, (uint32_t)k), sf_t, sf_t + C::SFB_COL0, (kb | k) != 0);
+            }
+            B200_TR_END(3);
+            if (++reg == C::NREG) { reg = 0; reg_par ^= 1; }
           }
-          umma_commit(bar_empty + stage * 8);
+          if (!ok) break;
+          B200_TR_BEGIN();
+          umma_commit(bar_empty + stage * 8);   // frees the smem stage and, later, the TMEM scale regions it used
+          B200_TR_END(4);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok) umma_commit(bar_tfull + buf * 8);
+      }
+      B200_TR_FLUSH(g_trace_fp4, 6, blockIdx.x == 5);
+    }
+  } else if (warp >= 6) {
+    // ---- scale writers: four warps, one per 32-lane quadrant of Tensor Memory ----
+    // Lane l of every quadrant must hold bytes [16 l, 16 l + 16) of each 512-byte scale block (the
+    // scales of rows l, l+32, l+64, l+96): what tcgen05.cp 32x128b.warpx4 would broadcast.  Written
+    // with tcgen05.st instead, they stay off the tensor core's instruction queue, where each such
+    // copy was measured at ~56 cycles with 12 of them per 4 MMAs.
+    const int q = warp & 3;
+    constexpr int NBLK = C::RK * (1 + C::CHUNKS);   // 512-byte blocks per region, A's first
+    uint32_t stage = 0, phase = 0, g = 0, u = 0, reg = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+        if (!mbar_wait(wctx, bar_full + stage * 8, phase, 5)) { ok = false; break; }
+        // all stores of the stage first, one completion wait, then one arrival per region: the store
+        // completion latency (a few hundred cycles while MMAs stream) is paid once per stage
+        const uint32_t reg0 = reg;
+#pragma unroll
+        for (int h = 0; h < C::HALVES; ++h, ++u) {
+          // region `reg` was last read by the MMAs of unit u - NREG; their stage's commit is `empty`
+          if (u >= (uint32_t)C::NREG) {
+            const uint32_t gp = (u - C::NREG) / C::HALVES;
+            if (!mbar_wait(wctx, bar_empty + (gp % STAGES) * 8, (gp / STAGES) & 1, 7)) { ok = false; break; }
+          }
+          tc_fence_after_sync();
+          const uint32_t dst = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_BASE + reg * C::REGION_COLS;
+          const uint32_t src_a = stage_sfa(stage) + (h * C::RK) * 512 + lane * 16;
+          const uint32_t src_b = stage_sfb(stage) + (h * C::RK) * C::CHUNKS * 512 + lane * 16;
+          // region layout: RK blocks of A scales, then RK x CHUNKS blocks of B scales; gathered in
+          // registers and stored as one or two wide column runs (each tcgen05.st costs its issuer
+          // tens of cycles while MMAs stream, whatever its width)
+          uint32_t regs[NBLK * 4];
+#pragma unroll
+          for (int b = 0; b < NBLK; ++b) {
+            const uint32_t src = b < C::RK ? src_a + b * 512 : src_b + (b - C::RK) * 512;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(regs[4 * b]), "=r"(regs[4 * b + 1]), "=r"(regs[4 * b + 2]), "=r"(regs[4 * b + 3])
+                         : "r"(src));
+          }
+          tmem_st_cols<NBLK * 4>(dst, regs);
+          if (++reg == (uint32_t)C::NREG) reg = 0;
+        }
+        if (!ok) break;
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          uint32_t r = reg0;
+#pragma unroll
+          for (int h = 0; h < C::HALVES; ++h) {
+            mbar_arrive(bar_sf_ready + r * 8);
+            if (++r == (uint32_t)C::NREG) r = 0;
+          }
+        }
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
       }
     }
   } else {
@@ -466,3 +550,9 @@ extern "C" int b200tile_linear_nvfp4_static(const void* x, const void* y, const 
                                alpha, scratch, (uint64_t)B200TILE_NVFP4_STATIC_SCRATCH_BYTES, config,
                                cu_stream);
 }
+
+#ifdef B200TILE_TRACE
+int b200_trace_read_fp4(long long* out) {
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fp4, 8 * sizeof(long long)) != cudaSuccess;
+}
+#endif

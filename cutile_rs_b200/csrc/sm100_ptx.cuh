@@ -352,6 +352,17 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32b_x4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2,
+                                                  uint32_t r3) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};"
+               ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
 __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
@@ -383,6 +394,35 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+
+// Stores NCOLS (a multiple of 4) consecutive columns of this thread's lane from registers, with as few
+// tcgen05.st instructions as the x32 / x16 / x8 / x4 shapes allow.
+template <int NCOLS>
+__device__ __forceinline__ void tmem_st_cols(uint32_t taddr, const uint32_t (&r)[NCOLS]) {
+  static_assert(NCOLS % 4 == 0 && NCOLS <= 64, "column runs of 4..64");
+  int done = 0;
+  if constexpr (NCOLS >= 32) {
+    tmem_st_32x32b_x32(taddr, *reinterpret_cast<const uint32_t(*)[32]>(&r[0]));
+    done = 32;
+    if constexpr (NCOLS == 64) {
+      tmem_st_32x32b_x32(taddr + 32, *reinterpret_cast<const uint32_t(*)[32]>(&r[32]));
+      done = 64;
+    }
+  }
+  constexpr int REM = NCOLS % 32;
+  if constexpr (REM >= 16) {
+    tmem_st_32x32b_x16(taddr + done, *reinterpret_cast<const uint32_t(*)[16]>(&r[NCOLS - REM]));
+    done += 16;
+  }
+  if constexpr (REM % 16 >= 8) {
+    tmem_st_32x32b_x8(taddr + done, &r[NCOLS - (REM % 16)]);
+    done += 8;
+  }
+  if constexpr (REM % 8 >= 4) {
+    const uint32_t* t = &r[NCOLS - 4];
+    tmem_st_32x32b_x4(taddr + done, t[0], t[1], t[2], t[3]);
+  }
 }
 
 }  // namespace b200

@@ -3,6 +3,7 @@
     python -m cutile_rs_b200.profile_case gemm --m 4096 --n 4096 --k 8192 --iters 3
     python -m cutile_rs_b200.profile_case fmha --batch 1 --heads 16 --seq 4096 --causal 0 --iters 3
     python -m cutile_rs_b200.profile_case decode --heads 8 --group 4 --seq 65536 --splits 18 --iters 3
+    python -m cutile_rs_b200.profile_case nvfp4 --m 4096 --n 14336 --k 4096 --iters 3
 
 With the diagnostic build (B200_VARIANT=trace B200_NVCC_EXTRA=-DB200TILE_TRACE csrc/build.sh) and
 B200TILE_LIB=cutile_rs_b200/libb200tile_trace.so, ``--trace`` prints where the MMA-issuing thread
@@ -27,7 +28,7 @@ from . import _lib
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "fmha", "decode"])
+    ap.add_argument("kernel", choices=["gemm", "fmha", "decode", "nvfp4"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=8192)
@@ -64,6 +65,21 @@ def main() -> None:
         def run():
             _lib.check(lib.b200tile_gemm(b"bf16", args.layout, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n,
                                          k, k, b.stride(0), n, 0, 0, 0, 0, args.config, 0, 0, stream.cuda_stream))
+        flops = 2.0 * m * n * k
+    elif args.kernel == "nvfp4":
+        m, n, k = args.m, args.n, args.k
+        xp = torch.randint(0, 256, (m, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+        yp = torch.randint(0, 256, (n, k // 2), dtype=torch.uint8, device="cuda", generator=g)
+        xs = torch.full((m, k // 16), 0x38, dtype=torch.uint8, device="cuda")    # e4m3 1.0
+        ys = torch.full((n, k // 16), 0x38, dtype=torch.uint8, device="cuda")
+        z = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        wsb = lib.b200tile_linear_nvfp4_workspace_bytes(m, n, k)
+        ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+
+        def run():
+            _lib.check(lib.b200tile_linear_nvfp4(xp.data_ptr(), yp.data_ptr(), xs.data_ptr(), ys.data_ptr(),
+                                                 z.data_ptr(), b"bf16", m, n, k, k // 2, k // 2, n, k // 16, k // 16,
+                                                 1.0, ws.data_ptr(), wsb, args.config, stream.cuda_stream))
         flops = 2.0 * m * n * k
     elif args.kernel == "decode":
         h, grp, s, d, ns = args.heads, args.group, args.seq, args.head_dim, args.splits
@@ -115,10 +131,17 @@ def _print_trace(lib, args) -> None:
     if not hasattr(lib, "b200tile_trace_read"):
         raise SystemExit("--trace needs the diagnostic build (see the module docstring)")
     out = (ctypes.c_longlong * 20)()
-    which = {"gemm": b"gemm_pair", "fmha": b"fmha_pair" if args.pair else b"fmha"}.get(args.kernel)
+    which = {"gemm": b"gemm_pair", "fmha": b"fmha_pair" if args.pair else b"fmha",
+             "nvfp4": b"block_scaled"}.get(args.kernel)
     if which is None or lib.b200tile_trace_read(which, out):
         raise SystemExit("no trace for this kernel")
     v = list(out)
+    if args.kernel == "nvfp4":
+        n = max(v[5], 1)
+        print(f"MMA thread of one CTA per stage (4 block-scaled MMAs): stage + scale waits {v[2] / n:.0f}, "
+              f"MMA issue {v[3] / n:.0f}, commit {v[4] / n:.0f}; total {v[6] / n:.0f} cycles per stage ({n} stages); "
+              f"SM clock inside the kernel {1e3 * v[6] / max(v[7], 1):.0f} MHz")
+        return
     if args.kernel == "gemm":
         stages, tiles = max(v[4], 1), max(v[5], 1)
         print(f"MMA thread of one CTA pair, per 128-deep stage (8 MMAs 256x256x16 = 1024 tensor cycles): "
