@@ -45,7 +45,8 @@ int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const 
 size_t b200_nvfp4_scratch_bytes(int M, int N, int K, int bn);
 int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, const void* xs, const void* ys,
                              void* z, int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
-                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
+                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream, int b_scales_prepared);
+int b200_nvfp4_prepare_b_scales(const void* ys, int N, int K, int64_t ld_ys, int bn, void* out, cudaStream_t stream);
 
 size_t b200_mxfp8_scratch_bytes(int M, int N, int K);
 int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
@@ -495,7 +496,60 @@ int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales, co
                      "linear_nvfp4: workspace of %llu bytes (16-byte aligned) required, got %llu",
                      (unsigned long long)need, (unsigned long long)workspace_bytes);
   return b200_gemm_nvfp4_dispatch(bn, out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs,
-                                  ld_ys, alpha, workspace, static_cast<cudaStream_t>(cu_stream));
+                                  ld_ys, alpha, workspace, static_cast<cudaStream_t>(cu_stream), 0);
+}
+
+// Weight scales laid out once (inference weights do not change): no per-call pre-pass, no workspace.
+uint64_t b200tile_nvfp4_weight_scales_bytes(int n, int k, int config) {
+  if (n <= 0 || k <= 0 || config < 0 || config > 2) return 0;
+  return (uint64_t)b200_nvfp4_scratch_bytes(1, n, k, kNvfp4Bn[config]);
+}
+
+int b200tile_nvfp4_prepare_weight_scales(const void* y_scales, int n, int k, int64_t ld_ys, int config,
+                                         void* prepared, uint64_t prepared_bytes, void* cu_stream) {
+  if (!y_scales || !prepared) return set_error(B200TILE_ERR_INVALID, "nvfp4_prepare_weight_scales: null argument");
+  if (n <= 0 || k <= 0 || k % 64 != 0)
+    return set_error(B200TILE_ERR_INVALID, "nvfp4_prepare_weight_scales: n, k must be positive and K a multiple of 64");
+  if (config < 0 || config > 2)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "nvfp4_prepare_weight_scales: config must be 0, 1 or 2 (got %d)", config);
+  if (ld_ys < k / 16 || ld_ys % 4 != 0 || (reinterpret_cast<uintptr_t>(y_scales) & 3) != 0)
+    return set_error(B200TILE_ERR_ALIGN, "nvfp4_prepare_weight_scales: scale rows must be 4-byte aligned");
+  const uint64_t need = b200tile_nvfp4_weight_scales_bytes(n, k, config);
+  if ((reinterpret_cast<uintptr_t>(prepared) & 15) != 0 || prepared_bytes < need)
+    return set_error(B200TILE_ERR_INVALID,
+                     "nvfp4_prepare_weight_scales: buffer of %llu bytes (16-byte aligned) required, got %llu",
+                     (unsigned long long)need, (unsigned long long)prepared_bytes);
+  return b200_nvfp4_prepare_b_scales(y_scales, n, k, ld_ys, kNvfp4Bn[config], prepared,
+                                     static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_linear_nvfp4_prepared(const void* x, const void* y, const void* x_scales,
+                                   const void* y_scales_prepared, void* z, const char* out_dtype, int m, int n,
+                                   int k, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, float alpha,
+                                   int config, void* cu_stream) {
+  if (!x || !y || !x_scales || !y_scales_prepared || !z || !out_dtype)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4_prepared: null argument");
+  if (m <= 0 || n <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4_prepared: Shape dimensions must be positive");
+  if (k % 64 != 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4_prepared: K (%d) must be a multiple of 64", k);
+  if (ldx < k / 2 || ldy < k / 2 || ldz < n || ld_xs < k / 16)
+    return set_error(B200TILE_ERR_INVALID, "linear_nvfp4_prepared: leading dimension too small");
+  if (ld_xs % 4 != 0 || (reinterpret_cast<uintptr_t>(x_scales) & 3) != 0 ||
+      (reinterpret_cast<uintptr_t>(y_scales_prepared) & 15) != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4_prepared: scale rows must be 4-byte aligned");
+  int out_f32;
+  if (!strcmp(out_dtype, "f32")) out_f32 = 1;
+  else if (!strcmp(out_dtype, "bf16")) out_f32 = 0;
+  else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_nvfp4_prepared: unsupported output type '%s'", out_dtype);
+  if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4_prepared: output must be 16-byte aligned with a 16-byte pitch");
+  if (config < 0 || config > 2)
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "linear_nvfp4_prepared: config must be the one the scales were prepared for (0, 1 or 2)");
+  return b200_gemm_nvfp4_dispatch(kNvfp4Bn[config], out_f32, x, y, x_scales, nullptr, z, m, n, k, ldx, ldy, ldz,
+                                  ld_xs, 0, alpha, const_cast<void*>(y_scales_prepared),
+                                  static_cast<cudaStream_t>(cu_stream), 1);
 }
 
 // ---------------------------------------------------------------------------

@@ -39,7 +39,9 @@ constexpr int F4_THREADS = 320;  // TMA, MMA, 4 epilogue warps, 4 scale-writer w
 // FP4 = false: MXFP8 (e4m3, UE8M0 scale per 32, K = 32 per MMA, 128 elements per stage)
 // Either way a stage is 128 bytes per row and 4 MMAs; a 512-byte scale block holds 128 rows x 4
 // scale bytes: one MMA's scales for NVFP4, the whole stage's (one byte per MMA) for MXFP8.
-template <int BN, bool FP4 = true>
+// A_DIRECT: A's scales are read in place by the writer warps (no pre-pass, no scratch: decode-sized M
+// and the prepared-weights entry); otherwise they come re-laid-out from scratch with the stage's TMA.
+template <int BN, bool FP4 = true, bool A_DIRECT = false>
 struct Fp4Cfg {
   static constexpr int CHUNKS = (BN + 127) / 128;            // 128-row scale blocks per B tile
   static constexpr int KQ_PER_STAGE = FP4 ? 4 : 1;           // scale blocks along K per stage
@@ -59,7 +61,7 @@ struct Fp4Cfg {
   static_assert(NREG >= 2, "at least two scale regions");
   static constexpr int A_BYTES = F4_BM * 128;
   static constexpr int B_BYTES = BN * 128;
-  static constexpr int SFA_BYTES = KQ_PER_STAGE * 512;
+  static constexpr int SFA_BYTES = A_DIRECT ? 0 : KQ_PER_STAGE * 512;
   static constexpr int SFB_BYTES = KQ_PER_STAGE * CHUNKS * 512;
   static constexpr int SFB_COL0 = 4 * RK;                    // first column of the B scales inside a region
   static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;  // bytes landed per stage
@@ -68,7 +70,9 @@ struct Fp4Cfg {
   static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4 + NREG;   // + one `ready` barrier per scale region
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
-  static constexpr int TOTAL = OFF_MISC + 16 + 1024;
+  static constexpr int XROW_BYTES = 4 * KQ_PER_STAGE;          // one row's A scales for one stage
+  static constexpr int OFF_XBUF = (OFF_MISC + 16 + 15) / 16 * 16;   // [2][128 rows][XROW_BYTES]
+  static constexpr int TOTAL = OFF_XBUF + 2 * F4_BM * XROW_BYTES + 1024;
 };
 
 // ---------------------------------------------------------------------------
@@ -131,12 +135,13 @@ __host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) 
   return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (0u << 23) | ((M >> 4) << 24);
 }
 
-template <int BN, bool OUT_F32, bool FP4>
+template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT>
 __global__ void __launch_bounds__(F4_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z,
+                  const uint8_t* __restrict__ xs, int64_t ld_xs, int kq_valid, const uint8_t* __restrict__ sfa,
+                  const uint8_t* __restrict__ sfb, void* __restrict__ Z,
                   int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
-  using C = Fp4Cfg<BN, FP4>;
+  using C = Fp4Cfg<BN, FP4, A_DIRECT>;
   constexpr int STAGES = C::STAGES;
   constexpr int STAGE_ELEMS = FP4 ? 256 : 128;  // K elements per 128-byte row
   extern __shared__ uint8_t smem_raw[];
@@ -201,7 +206,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int bm, bn;
         tile_coords(tile, bm, bn);
-        const uint8_t* sfa_tile = sfa + (int64_t)bm * kq_count * 512;
+        const uint8_t* sfa_tile = A_DIRECT ? nullptr : sfa + (int64_t)bm * kq_count * 512;
         const uint8_t* sfb_tile = sfb + (int64_t)bn * kq_count * (C::CHUNKS * 512);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
@@ -209,7 +214,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           mbar_expect_tx(full, C::STAGE_TX);
           tma_load_2d(stage_a(stage), &tmA, full, kb * 128, bm * F4_BM);
           tma_load_2d(stage_b(stage), &tmB, full, kb * 128, bn * BN);
-          bulk_load_1d(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
+          if (!A_DIRECT)
+            bulk_load_1d(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
           bulk_load_1d(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -274,10 +280,57 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     // copy was measured at ~56 cycles with 12 of them per 4 MMAs.
     const int q = warp & 3;
     constexpr int NBLK = C::RK * (1 + C::CHUNKS);   // 512-byte blocks per region, A's first
+    // A's scales come straight from the row-major tensor, no pre-pass: writer thread t = 32 q + lane
+    // fetches row t's scale bytes of a stage (16 for NVFP4, 4 for MXFP8, one load, issued a stage
+    // ahead), the four warps swap them through a small shared buffer, and lane l then picks up rows
+    // l, l+32, l+64, l+96 -- the words its Tensor-Memory lane must hold.
+    constexpr int AW = C::KQ_PER_STAGE * 4;     // A-scale words per lane and stage
+    constexpr int XW = C::KQ_PER_STAGE;         // words per row and stage
+    const uint32_t xbuf = base + C::OFF_XBUF;
+    auto load_row_scales = [&](int tile, int kb, uint32_t (&dst)[XW]) {
+      int bm, bn;
+      tile_coords(tile, bm, bn);
+      const int row = bm * F4_BM + q * 32 + lane;
+      const int kq0 = kb * C::KQ_PER_STAGE;
+#pragma unroll
+      for (int k = 0; k < XW; ++k) dst[k] = 0u;
+      if (row < M) {
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(xs + (int64_t)row * ld_xs) + kq0;
+        if (XW == 4 && kq0 + 3 < kq_valid && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+          dst[0] = v.x; dst[1] = v.y; dst[XW - 2] = v.z; dst[XW - 1] = v.w;
+        } else {
+#pragma unroll
+          for (int k = 0; k < XW; ++k)
+            if (kq0 + k < kq_valid) dst[k] = __ldg(src + k);
+        }
+      }
+    };
     uint32_t stage = 0, phase = 0, g = 0, u = 0, reg = 0;
     bool ok = true;
+    uint32_t x_next[XW];
+    if (A_DIRECT && (int)blockIdx.x < total_tiles) load_row_scales(blockIdx.x, 0, x_next);
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+        uint32_t a_cur[AW];
+        if (A_DIRECT) {
+          // publish this stage's row words, fetch the next stage's, then gather the four rows of the lane
+          const uint32_t xb = xbuf + (g & 1) * (F4_BM * C::XROW_BYTES);
+#pragma unroll
+          for (int k = 0; k < XW; ++k)
+            asm volatile("st.shared.b32 [%0], %1;" ::"r"(xb + (q * 32 + lane) * C::XROW_BYTES + k * 4), "r"(x_next[k])
+                         : "memory");
+          const int nkb = kb + 1 < num_kb ? kb + 1 : 0;
+          const int ntile = kb + 1 < num_kb ? tile : tile + (int)gridDim.x;
+          if (ntile < total_tiles) load_row_scales(ntile, nkb, x_next);
+          named_bar_sync(1, 128);   // the four writer warps only
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int k = 0; k < XW; ++k)
+              asm volatile("ld.shared.b32 %0, [%1];" : "=r"(a_cur[k * 4 + j])
+                           : "r"(xb + (lane + 32 * j) * C::XROW_BYTES + k * 4));
+        }
         if (!mbar_wait(wctx, bar_full + stage * 8, phase, 5)) { ok = false; break; }
         // all stores of the stage first, one completion wait, then one arrival per region: the store
         // completion latency (a few hundred cycles while MMAs stream) is paid once per stage
@@ -291,18 +344,27 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
           tc_fence_after_sync();
           const uint32_t dst = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_BASE + reg * C::REGION_COLS;
-          const uint32_t src_a = stage_sfa(stage) + (h * C::RK) * 512 + lane * 16;
           const uint32_t src_b = stage_sfb(stage) + (h * C::RK) * C::CHUNKS * 512 + lane * 16;
           // region layout: RK blocks of A scales, then RK x CHUNKS blocks of B scales; gathered in
           // registers and stored as one or two wide column runs (each tcgen05.st costs its issuer
           // tens of cycles while MMAs stream, whatever its width)
           uint32_t regs[NBLK * 4];
+          if (A_DIRECT) {
 #pragma unroll
-          for (int b = 0; b < NBLK; ++b) {
-            const uint32_t src = b < C::RK ? src_a + b * 512 : src_b + (b - C::RK) * 512;
+            for (int i = 0; i < C::RK * 4; ++i) regs[i] = a_cur[h * C::RK * 4 + i];
+          } else {
+            const uint32_t src_a = stage_sfa(stage) + (h * C::RK) * 512 + lane * 16;
+#pragma unroll
+            for (int b = 0; b < C::RK; ++b)
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(regs[4 * b]), "=r"(regs[4 * b + 1]), "=r"(regs[4 * b + 2]), "=r"(regs[4 * b + 3])
+                           : "r"(src_a + b * 512));
+          }
+#pragma unroll
+          for (int b = C::RK; b < NBLK; ++b) {
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(regs[4 * b]), "=r"(regs[4 * b + 1]), "=r"(regs[4 * b + 2]), "=r"(regs[4 * b + 3])
-                         : "r"(src));
+                         : "r"(src_b + (b - C::RK) * 512));
           }
           tmem_st_cols<NBLK * 4>(dst, regs);
           if (++reg == (uint32_t)C::NREG) reg = 0;
@@ -390,21 +452,24 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   }
 }
 
-// Bytes of scratch needed for the re-laid-out scales of an (M, N, K) problem with B tiles of BN rows.
+// Bytes of scratch needed for the re-laid-out B (weight) scales of an (M, N, K) problem with B tiles of BN rows.
 static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offset, bool fp4 = true) {
   const size_t kq = fp4 ? (size_t)((K + 255) / 256) * 4 : (size_t)((K + 127) / 128);
   const size_t tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
   const size_t chunks = (BN + 127) / 128;
-  const size_t a_bytes = tiles_m * kq * 512;
+  // decode-sized M reads A's scales in place (no scratch for them)
+  const size_t a_bytes = M <= F4_BM ? 0 : tiles_m * kq * 512;
   if (sfb_offset) *sfb_offset = a_bytes;
   return a_bytes + tiles_n * kq * chunks * 512;
 }
 
-template <int BN, bool OUT_F32, bool FP4 = true>
-static int launch_nvfp4(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
-                        int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha,
-                        uint8_t* scratch, cudaStream_t stream) {
-  using C = Fp4Cfg<BN, FP4>;
+// b_scales_prepared: `scratch` IS the tile layout of the B scales (written once by the caller); A's
+// scales are then read in place whatever M is, so that the call needs no workspace at all.
+template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT>
+static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
+                             int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys,
+                             float alpha, uint8_t* scratch, cudaStream_t stream, bool b_scales_prepared) {
+  using C = Fp4Cfg<BN, FP4, A_DIRECT>;
   const b200h::DeviceInfo* di = b200h::device_info();
   const uint64_t row_bytes = FP4 ? (uint64_t)K / 2 : (uint64_t)K;
   if (!di) return B200_ERR_CUDA;
@@ -416,23 +481,25 @@ static int launch_nvfp4(const void* x, const void* y, const void* xs, const void
   if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, row_bytes, (uint64_t)N,
                                   (uint64_t)ldy, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  size_t sfb_off;
-  nvfp4_scratch_layout(M, N, K, BN, &sfb_off, FP4);
   const int kq = FP4 ? ((K + 255) / 256) * 4 : (K + 127) / 128;
   const int kq_valid = FP4 ? K / 64 : K / 128;
   const int tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
-  {
+  const size_t sfb_off = A_DIRECT ? 0 : (size_t)tiles_m * kq * 512;
+  if (!A_DIRECT) {
     const int64_t words_a = (int64_t)tiles_m * kq * 128;
-    const int64_t words_b = (int64_t)tiles_n * kq * C::CHUNKS * 128;
     const int ga = (int)((words_a + 255) / 256 < 4096 ? (words_a + 255) / 256 : 4096);
-    const int gb = (int)((words_b + 255) / 256 < 4096 ? (words_b + 255) / 256 : 4096);
     nvfp4_relayout_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(xs), M, kq, kq_valid, ld_xs, F4_BM,
                                                          1, tiles_m, reinterpret_cast<uint32_t*>(scratch));
+  }
+  if (!b_scales_prepared) {
+    const int64_t words_b = (int64_t)tiles_n * kq * C::CHUNKS * 128;
+    const int gb = (int)((words_b + 255) / 256 < 4096 ? (words_b + 255) / 256 : 4096);
     nvfp4_relayout_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, BN,
                                                          C::CHUNKS, tiles_n,
                                                          reinterpret_cast<uint32_t*>(scratch + sfb_off));
   }
-  auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4>;
+  B200_CUDA_CHECK(cudaGetLastError());
+  auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4, A_DIRECT>;
   static bool attr_done[64] = {};
   if (!attr_done[di->ordinal]) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
@@ -440,13 +507,38 @@ static int launch_nvfp4(const void* x, const void* y, const void* xs, const void
   }
   const int tiles = tiles_m * tiles_n;
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;
-  kern<<<grid, F4_THREADS, C::TOTAL, stream>>>(tmA, tmB, scratch, scratch + sfb_off, z, M, N, K, ldz, alpha, 8,
-                                               di->status);
+  kern<<<grid, F4_THREADS, C::TOTAL, stream>>>(tmA, tmB, static_cast<const uint8_t*>(xs), ld_xs, kq_valid, scratch,
+                                               scratch + sfb_off, z, M, N, K, ldz, alpha, 8, di->status);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
 
+template <int BN, bool OUT_F32, bool FP4 = true>
+static int launch_nvfp4(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
+                        int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha,
+                        uint8_t* scratch, cudaStream_t stream, bool b_scales_prepared = false) {
+  // same rule as nvfp4_scratch_layout: one tile row of A, or prepared weights => A's scales in place
+  if (M <= F4_BM || b_scales_prepared)
+    return launch_nvfp4_impl<BN, OUT_F32, FP4, true>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha,
+                                                     scratch, stream, b_scales_prepared);
+  return launch_nvfp4_impl<BN, OUT_F32, FP4, false>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha,
+                                                    scratch, stream, false);
+}
+
 }  // namespace b200
+
+// Writes the tile layout of the B (weight) scales for B tiles of `bn` rows into `out`.
+int b200_nvfp4_prepare_b_scales(const void* ys, int N, int K, int64_t ld_ys, int bn, void* out, cudaStream_t stream) {
+  using namespace b200;
+  const int kq = ((K + 255) / 256) * 4, kq_valid = K / 64;
+  const int tiles_n = (N + bn - 1) / bn, chunks = (bn + 127) / 128;
+  const int64_t words_b = (int64_t)tiles_n * kq * chunks * 128;
+  const int gb = (int)((words_b + 255) / 256 < 4096 ? (words_b + 255) / 256 : 4096);
+  nvfp4_relayout_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, bn,
+                                                       chunks, tiles_n, static_cast<uint32_t*>(out));
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
 
 size_t b200_nvfp4_scratch_bytes(int M, int N, int K, int bn) {
   return b200::nvfp4_scratch_layout(M, N, K, bn, nullptr);
@@ -469,11 +561,12 @@ int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const vo
 
 int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, const void* xs, const void* ys,
                              void* z, int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
-                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream) {
+                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream, int b_scales_prepared) {
   using namespace b200;
   uint8_t* s = static_cast<uint8_t*>(scratch);
-#define B200_F4_CASE(BN_, F32_) \
-  return launch_nvfp4<BN_, F32_>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream)
+#define B200_F4_CASE(BN_, F32_)                                                                            \
+  return launch_nvfp4<BN_, F32_>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream, \
+                                 b_scales_prepared != 0)
   if (bn == 128 && out_f32) B200_F4_CASE(128, true);
   if (bn == 128 && !out_f32) B200_F4_CASE(128, false);
   if (bn == 192 && out_f32) B200_F4_CASE(192, true);

@@ -548,3 +548,36 @@ def linear_swiglu(out: Tensor, x: Tensor, w_gate_up: Tensor, stream: Optional[to
     if rc:
         raise KernelLaunchError(lib.b200tile_last_error().decode())
     return out
+
+
+def nvfp4_prepare_weight_scales(y_scales: Tensor, n: int, k: int, config: int = 0,
+                                stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+    """Brings weight scales [N, K/16] into the kernel's tile layout once (``b200tile_nvfp4_prepare_weight_scales``);
+    the returned uint8 buffer goes to :func:`linear_nvfp4_prepared` with the same ``config``."""
+    lib = _lib.load()
+    s = stream or torch.cuda.current_stream()
+    need = int(lib.b200tile_nvfp4_weight_scales_bytes(n, k, config))
+    with torch.cuda.stream(s):
+        buf = torch.empty(need, dtype=torch.uint8, device=y_scales.storage.device)
+    rc = lib.b200tile_nvfp4_prepare_weight_scales(y_scales.cu_deviceptr(), n, k, y_scales.strides[0], config,
+                                                  buf.data_ptr(), need, c_void_p(s.cuda_stream))
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+    return buf
+
+
+def linear_nvfp4_prepared(z: Tensor, x: Tensor, y: Tensor, x_scales: Tensor, y_scales_prepared: torch.Tensor,
+                          alpha: float = 1.0, config: int = 0, stream: Optional[torch.cuda.Stream] = None) -> Tensor:
+    """NVFP4 linear layer on weight scales prepared by :func:`nvfp4_prepare_weight_scales`: one kernel, no
+    workspace; otherwise the operands of :func:`linear_nvfp4`."""
+    lib = _lib.load()
+    s = stream or torch.cuda.current_stream()
+    m, n = z.shape
+    k = x.shape[1] * 2
+    rc = lib.b200tile_linear_nvfp4_prepared(x.cu_deviceptr(), y.cu_deviceptr(), x_scales.cu_deviceptr(),
+                                            y_scales_prepared.data_ptr(), z.cu_deviceptr(), z.dtype_str().encode(),
+                                            m, n, k, x.strides[0], y.strides[0], z.strides[0], x_scales.strides[0],
+                                            float(alpha), config, c_void_p(s.cuda_stream))
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+    return z

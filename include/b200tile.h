@@ -286,6 +286,22 @@ B200TILE_API int b200tile_linear_mxfp8(const void* x, const void* y, const void*
                                        int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
                                        uint64_t workspace_bytes, void* cu_stream);
 
+/* NVFP4 linear layer with the weight scales laid out ahead of time.  Inference weights do not
+ * change, so their scales can be brought into the kernel's tile layout once
+ * (b200tile_nvfp4_prepare_weight_scales, for one `config` = B tile of 128 / 192 / 256 rows); every
+ * later call then runs a single kernel and needs no workspace (the activation scales are read in
+ * place).  Same operands and semantics as b200tile_linear_nvfp4 otherwise; config 0 suits decode
+ * (m <= 128: most tile-blocks), config 1 large m.  No reference counterpart: the reference passes
+ * logically row-major scales on every call (cutile-examples/examples/nvfp4.rs:37-76). */
+B200TILE_API uint64_t b200tile_nvfp4_weight_scales_bytes(int n, int k, int config);
+B200TILE_API int b200tile_nvfp4_prepare_weight_scales(const void* y_scales, int n, int k, int64_t ld_ys,
+                                                      int config, void* prepared, uint64_t prepared_bytes,
+                                                      void* cu_stream);
+B200TILE_API int b200tile_linear_nvfp4_prepared(const void* x, const void* y, const void* x_scales,
+                                                const void* y_scales_prepared, void* z, const char* out_dtype,
+                                                int m, int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
+                                                int64_t ld_xs, float alpha, int config, void* cu_stream);
+
 /* Same computation as b200tile_linear_nvfp4, for callers that cannot provide device memory
  * (no counterpart in the reference, whose launchers always allocate through their own pool):
  * code that runs while a stream is being captured and must stay away from any allocator, plugins

@@ -85,3 +85,22 @@ def test_full_size_slabs_and_errors(b200, oracle):
     rc = lib.b200tile_linear_nvfp4(xp.data_ptr(), yp.data_ptr(), xs.data_ptr(), ys.data_ptr(), z.data_ptr(), b"bf16",
                                    16, n, 100, 50, 50, n, 8, 8, 1.0, None, 0, -1, None)
     assert rc == _lib.ERR_INVALID and b"multiple of 64" in lib.b200tile_last_error()
+
+
+@pytest.mark.parametrize("config,m,n,k", [(0, 16, 512, 1024), (1, 200, 328, 320), (2, 256, 384, 512)])
+def test_prepared_weight_scales_give_the_same_bits(b200, config, m, n, k):
+    """Weight scales laid out once, then a workspace-free call: bit-identical to the call that lays
+    them out itself (same kernel, same scale bytes in Tensor Memory)."""
+    a, b = workloads.gemm_normal_inputs(m, n, k, config_index=9)
+    xp, xs, ga = quant.quant_nvfp4(a)
+    yp, ys, gb = quant.quant_nvfp4(b)
+    want = _run(xp.cuda(), yp.cuda(), xs.cuda(), ys.cuda(), m, n, k, "f32", ga * gb, config=config)
+    xt, yt = api.from_torch(xp.cuda(), "f4e2m1fnx2"), api.from_torch(yp.cuda(), "f4e2m1fnx2")
+    prepared = launch.nvfp4_prepare_weight_scales(api.from_torch(ys.cuda()), n, k, config)
+    z = api.from_torch(torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32))
+    for _ in range(2):   # the prepared buffer is read-only: a second call gives the same result
+        launch.linear_nvfp4_prepared(z, xt, yt, api.from_torch(xs.cuda()), prepared, ga * gb, config)
+        torch.cuda.synchronize()
+        assert torch.equal(z.storage, want)
+    with pytest.raises(Exception, match="config"):
+        launch.linear_nvfp4_prepared(z, xt, yt, api.from_torch(xs.cuda()), prepared, ga * gb, config=-1)
