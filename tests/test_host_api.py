@@ -2,6 +2,7 @@
 import json
 import os
 
+import numpy as np
 import pytest
 import torch
 
@@ -197,3 +198,35 @@ def test_measurement_quantiles():
     assert m.median_ms() == 2.5 and m.min_ms() == 1.0 and m.mean_ms() == 2.5 and m.reps() == 4
     assert m.quantile_ms(0.0) == 1.0 and m.quantile_ms(1.0) == 4.0
     assert BenchOptions().clear_l2 and BenchOptions().min_reps == 5
+
+
+def test_serving_attention_launchers_infer_reference_generics():
+    """Generic strings and grids of the serving kernels as the reference's launchers would produce them
+    (cutile-kernels/src/attention.rs:398-440, 588-613, 738-757, 921-939); no device needed."""
+    from cutile_rs_b200 import launch
+    f16 = torch.float16
+    heads_kv, group, d, cap, ns = 2, 4, 128, 640, 5
+    q = Tensor(torch.zeros(heads_kv, group, d, dtype=f16))
+    k = Tensor(torch.zeros(heads_kv, cap, d, dtype=f16))
+    att = Tensor(torch.zeros(heads_kv, ns * group, d, dtype=f16))
+    lse = Tensor(torch.zeros(heads_kv, ns * group))
+    pos = Tensor(torch.zeros(1, dtype=torch.int32))
+    la = launch.fmha_decode_gqa_split(q, k, k, att.partition([1, group, d]), lse.partition([1, group]), 0.088, pos,
+                                      bn=64)
+    assert la.infer_generics() == ["f16", "4", "64", "128", "5", "2"]
+    assert infer_launch_grid((0, 0, 0), la._bounds()) == (heads_kv, ns, 1)
+    out = Tensor(torch.zeros(heads_kv, group, d, dtype=f16))
+    lm = launch.splitk_reduce_merge(att, lse, out.partition([1, group, 32]))
+    assert lm.infer_generics() == ["f16", "4", "128", "32", "5", "20", "2"]
+    assert infer_launch_grid((0, 0, 0), lm._bounds()) == (heads_kv, 1, 4)
+    qp = Tensor(torch.zeros(200, heads_kv * group, d, dtype=f16))
+    op = Tensor(torch.zeros(200, heads_kv * group, d, dtype=f16))
+    lg = launch.fmha_prefill_gqa(qp, k, k, op.partition([32, group, d]), 0.088, group, 200)
+    assert lg.infer_generics() == ["f16", "32", "128", "128", "4", "128", "1", "0", "2"]
+    assert infer_launch_grid((0, 0, 0), lg._bounds()) == (7, heads_kv, 1)
+    lc = launch.fmha_causal(qp, k, k, op.partition([128, 1, d]), 0.088, group, pos)
+    assert lc.infer_generics() == ["f16", "128", "128", "128", "1", "1"]
+    # the f16 scalar parameter is marshalled as two bytes holding the rounded half
+    pa = launch._ParamArray()
+    pa.push("f16", 0.088)
+    assert pa._keep[0].value == int(np.float16(0.088).view(np.uint16))
