@@ -399,6 +399,24 @@ def run_gpu_arm(args):
                                     "pct_of_nominal_fp8_peak_4500": 100.0 * tf8 / world / 4500.0,
                                     "config": f"e4m3 M{m8} N{n8} K{k8}, fp32 scales 1x128 / 128x128, bf16 out, "
                                               f"N split over {world} GPU(s)"}
+        # the same shape with the hardware's own fp8 block scaling (MXFP8: e8m0 scale per 32 elements), the
+        # reference's fp8 path (cutile-examples/examples/mxfp8.rs:34-64): no promotion pass on CUDA cores
+        xm, xms = quant.quant_mxfp8(torch.randn(m8, k8, device=dev, generator=g))
+        ym, yms = quant.quant_mxfp8(torch.randn(r1 - r0, k8, device=dev, generator=g))
+        wsm = lib.b200tile_linear_mxfp8_workspace_bytes(m8, r1 - r0, k8)
+        wsb8 = torch.empty(wsm, dtype=torch.uint8, device=dev)
+
+        def mx8step():
+            _lib.check(lib.b200tile_linear_mxfp8(xm.data_ptr(), ym.data_ptr(), xms.data_ptr(), yms.data_ptr(),
+                                                 z8.data_ptr(), b"bf16", m8, r1 - r0, k8, k8, k8, r1 - r0, k8 // 32,
+                                                 k8 // 32, 1.0, wsb8.data_ptr(), wsm, stream.cuda_stream))
+        msm = timed(mx8step, 5)
+        tfm = workloads.gemm_flops(m8, n8, k8) / (msm * 1e-3) / 1e12
+        extra["gemm_mxfp8"] = {"tflops": tfm, "tflops_per_gpu": tfm / world, "ms": msm,
+                               "pct_of_nominal_fp8_peak_4500": 100.0 * tfm / world / 4500.0,
+                               "config": f"MXFP8 (e4m3, e8m0 scale per 32) M{m8} N{n8} K{k8}, bf16 out, N split over "
+                                         f"{world} GPU(s); includes the per-call scale re-layout"}
+        del xm, xms, ym, yms, wsb8
         del xq, xs, yq, ys, z8
         n4, k4 = 14336, 4096
         r0, r1 = sharding.split_range(n4, world, rank, 256)
