@@ -574,7 +574,7 @@ def run_gpu_arm(args):
                          "peak_sustained": SUSTAINED_BF16_TFLOPS,
                          "frac_of_sustained": (per_gpu / SUSTAINED_BF16_TFLOPS) if SUSTAINED_BF16_TFLOPS else None,
                          "note": "the MMA-issuing thread measures 1048 cycles per 1024 tensor-pipe cycles of work "
-                                 "(profiles/gemm_bf16_pair.md); the SM clock under the 1 kW cap sets the rest"},
+                                 "(cycle accounting of the diagnostic trace build); the SM clock under the 1 kW cap sets the rest"},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
