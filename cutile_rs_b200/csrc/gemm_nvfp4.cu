@@ -17,7 +17,8 @@
 //   warp 0      TMA producer: A (128 x 128 B), B (BN x 128 B) and both scale blocks per stage
 //   warp 1      issuer: 4 block-scaled MMAs (K = 64 each) per stage, nothing else on its queue
 //   warps 2..5  epilogue: tcgen05.ld -> alpha -> bf16/f32 -> global
-//   warps 6..9  scale writers: shared memory -> Tensor Memory with tcgen05.st, one warp per quadrant
+//   warps 6..13 scale writers: shared memory -> Tensor Memory with tcgen05.st, one warp per quadrant,
+//               two sets of four taking alternate stages
 #include <mutex>
 
 #include "../../include/b200tile.h"
@@ -30,10 +31,13 @@ namespace b200 {
 #ifdef B200TILE_TRACE
 // MMA thread of CTA 5: [0] accumulator waits, [1] unused, [2] stage + scale ready waits, [3] MMA issue, [4] commits, [5] stages, [6] total cycles, [7] the same span in ns
 __device__ long long g_trace_fp4[8];
+// writer warp 6 of the same CTA: [0] stage-full waits, [1] region waits + loads + store issue, [2] store
+// completion wait, [3] hand-off, [4] stages, [5] total cycles
+__device__ long long g_trace_fp4_writer[8];
 #endif
 
 constexpr int F4_BM = 128;
-constexpr int F4_THREADS = 320;  // TMA, MMA, 4 epilogue warps, 4 scale-writer warps
+constexpr int F4_THREADS = 448;  // TMA, MMA, 4 epilogue warps, two sets of 4 scale-writer warps
 
 // FP4 = true : NVFP4 (packed e2m1, UE4M3 scale per 16, K = 64 per MMA, 256 elements per stage)
 // FP4 = false: MXFP8 (e4m3, UE8M0 scale per 32, K = 32 per MMA, 128 elements per stage)
@@ -72,7 +76,7 @@ struct Fp4Cfg {
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int XROW_BYTES = 4 * KQ_PER_STAGE;          // one row's A scales for one stage
   static constexpr int OFF_XBUF = (OFF_MISC + 16 + 15) / 16 * 16;   // [2][128 rows][XROW_BYTES]
-  static constexpr int TOTAL = OFF_XBUF + 2 * F4_BM * XROW_BYTES + 1024;
+  static constexpr int TOTAL = OFF_XBUF + 4 * F4_BM * XROW_BYTES + 1024;   // two buffers per writer set
 };
 
 // ---------------------------------------------------------------------------
@@ -306,24 +310,43 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
       }
     };
+    // Two sets of four warps take alternate stages: a set's tcgen05.st stream for one stage (issue
+    // plus the wait for the region) was measured at ~650 cycles, longer than the MMA thread needs for
+    // the stage's four MMAs, so one set alone was the pipeline's slowest member.
+    const uint32_t set = (uint32_t)(warp - 6) >> 2;
+    int tile = blockIdx.x, kb = 0;                      // position of the stage this set handles next
     uint32_t stage = 0, phase = 0, g = 0, u = 0, reg = 0;
+    auto next_stage = [&](int& t_, int& kb_) {
+      if (++kb_ == num_kb) { kb_ = 0; t_ += (int)gridDim.x; }
+    };
+    auto advance = [&]() {                              // ring / region bookkeeping of one stage
+      next_stage(tile, kb);
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      u += C::HALVES;
+      reg = (reg + C::HALVES) % C::NREG;
+      ++g;
+    };
+    if (set == 1) advance();
     bool ok = true;
+    B200_TR_DECL(5);
     uint32_t x_next[XW];
-    if (A_DIRECT && (int)blockIdx.x < total_tiles) load_row_scales(blockIdx.x, 0, x_next);
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb && ok; ++kb, ++g) {
+    if (A_DIRECT && tile < total_tiles) load_row_scales(tile, kb, x_next);
+    while (tile < total_tiles && ok) {
+      {
         uint32_t a_cur[AW];
         if (A_DIRECT) {
-          // publish this stage's row words, fetch the next stage's, then gather the four rows of the lane
-          const uint32_t xb = xbuf + (g & 1) * (F4_BM * C::XROW_BYTES);
+          // publish this stage's row words, fetch those of the set's next stage, then gather the four
+          // rows of the lane; two buffers per set so that a fast warp cannot overwrite a slow one's rows
+          const uint32_t xb = xbuf + (set * 2 + ((g >> 1) & 1)) * (F4_BM * C::XROW_BYTES);
 #pragma unroll
           for (int k = 0; k < XW; ++k)
             asm volatile("st.shared.b32 [%0], %1;" ::"r"(xb + (q * 32 + lane) * C::XROW_BYTES + k * 4), "r"(x_next[k])
                          : "memory");
-          const int nkb = kb + 1 < num_kb ? kb + 1 : 0;
-          const int ntile = kb + 1 < num_kb ? tile : tile + (int)gridDim.x;
-          if (ntile < total_tiles) load_row_scales(ntile, nkb, x_next);
-          named_bar_sync(1, 128);   // the four writer warps only
+          int nt = tile, nkb = kb;
+          next_stage(nt, nkb);
+          next_stage(nt, nkb);
+          if (nt < total_tiles) load_row_scales(nt, nkb, x_next);
+          named_bar_sync(1 + set, 128);   // the four warps of this set only
 #pragma unroll
           for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -331,23 +354,25 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
               asm volatile("ld.shared.b32 %0, [%1];" : "=r"(a_cur[k * 4 + j])
                            : "r"(xb + (lane + 32 * j) * C::XROW_BYTES + k * 4));
         }
+        B200_TR_COUNT(4);
+        B200_TR_BEGIN();
         if (!mbar_wait(wctx, bar_full + stage * 8, phase, 5)) { ok = false; break; }
-        // all stores of the stage first, one completion wait, then one arrival per region: the store
-        // completion latency (a few hundred cycles while MMAs stream) is paid once per stage
-        const uint32_t reg0 = reg;
+        B200_TR_END(0);
+        B200_TR_BEGIN();
+        // all stores of the stage first, one completion wait, then one arrival per region
 #pragma unroll
-        for (int h = 0; h < C::HALVES; ++h, ++u) {
-          // region `reg` was last read by the MMAs of unit u - NREG; their stage's commit is `empty`
-          if (u >= (uint32_t)C::NREG) {
-            const uint32_t gp = (u - C::NREG) / C::HALVES;
+        for (int h = 0; h < C::HALVES; ++h) {
+          const uint32_t uu = u + h, rr = (reg + h) % C::NREG;
+          // region rr was last read by the MMAs of unit uu - NREG; their stage's commit is `empty`
+          if (uu >= (uint32_t)C::NREG) {
+            const uint32_t gp = (uu - C::NREG) / C::HALVES;
             if (!mbar_wait(wctx, bar_empty + (gp % STAGES) * 8, (gp / STAGES) & 1, 7)) { ok = false; break; }
           }
           tc_fence_after_sync();
-          const uint32_t dst = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_BASE + reg * C::REGION_COLS;
+          const uint32_t dst = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_BASE + rr * C::REGION_COLS;
           const uint32_t src_b = stage_sfb(stage) + (h * C::RK) * C::CHUNKS * 512 + lane * 16;
           // region layout: RK blocks of A scales, then RK x CHUNKS blocks of B scales; gathered in
-          // registers and stored as one or two wide column runs (each tcgen05.st costs its issuer
-          // tens of cycles while MMAs stream, whatever its width)
+          // registers and stored as one or two wide column runs
           uint32_t regs[NBLK * 4];
           if (A_DIRECT) {
 #pragma unroll
@@ -367,23 +392,25 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                          : "r"(src_b + (b - C::RK) * 512));
           }
           tmem_st_cols<NBLK * 4>(dst, regs);
-          if (++reg == (uint32_t)C::NREG) reg = 0;
         }
         if (!ok) break;
+        B200_TR_END(1);
+        B200_TR_BEGIN();
         tmem_wait_st();
+        B200_TR_END(2);
+        B200_TR_BEGIN();
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-          uint32_t r = reg0;
 #pragma unroll
-          for (int h = 0; h < C::HALVES; ++h) {
-            mbar_arrive(bar_sf_ready + r * 8);
-            if (++r == (uint32_t)C::NREG) r = 0;
-          }
+          for (int h = 0; h < C::HALVES; ++h) mbar_arrive(bar_sf_ready + ((reg + h) % C::NREG) * 8);
         }
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        B200_TR_END(3);
       }
+      advance();
+      advance();
     }
+    B200_TR_FLUSH(g_trace_fp4_writer, 5, blockIdx.x == 5 && warp == 6 && lane == 0);
   } else {
     const int q = warp & 3;
     const int row = q * 32 + lane;
@@ -646,6 +673,7 @@ extern "C" int b200tile_linear_nvfp4_static(const void* x, const void* y, const 
 
 #ifdef B200TILE_TRACE
 int b200_trace_read_fp4(long long* out) {
-  return cudaMemcpyFromSymbol(out, b200::g_trace_fp4, 8 * sizeof(long long)) != cudaSuccess;
+  if (cudaMemcpyFromSymbol(out, b200::g_trace_fp4, 8 * sizeof(long long)) != cudaSuccess) return 1;
+  return cudaMemcpyFromSymbol(out + 10, b200::g_trace_fp4_writer, 7 * sizeof(long long)) != cudaSuccess;
 }
 #endif

@@ -141,6 +141,9 @@ def _print_trace(lib, args) -> None:
         print(f"MMA thread of one CTA per stage (4 block-scaled MMAs): stage + scale waits {v[2] / n:.0f}, "
               f"MMA issue {v[3] / n:.0f}, commit {v[4] / n:.0f}; total {v[6] / n:.0f} cycles per stage ({n} stages); "
               f"SM clock inside the kernel {1e3 * v[6] / max(v[7], 1):.0f} MHz")
+        w = max(v[14], 1)
+        print(f"scale-writer warp per stage: stage-full wait {v[10] / w:.0f}, region wait + loads + store issue "
+              f"{v[11] / w:.0f}, store completion {v[12] / w:.0f}, hand-off {v[13] / w:.0f}; total {v[15] / w:.0f}")
         return
     if args.kernel == "gemm":
         stages, tiles = max(v[4], 1), max(v[5], 1)
