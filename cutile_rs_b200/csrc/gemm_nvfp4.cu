@@ -34,6 +34,8 @@ __device__ long long g_trace_fp4[8];
 // writer warp 6 of the same CTA: [0] stage-full waits, [1] region waits + loads + store issue, [2] store
 // completion wait, [3] hand-off, [4] stages, [5] total cycles
 __device__ long long g_trace_fp4_writer[8];
+// TMA producer thread of the same CTA: [0] stage-empty waits, [1] issue of the stage's copies, [2] stages, [3] total
+__device__ long long g_trace_fp4_producer[8];
 #endif
 
 constexpr int F4_BM = 128;
@@ -207,13 +209,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      B200_TR_DECL(3);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int bm, bn;
         tile_coords(tile, bm, bn);
         const uint8_t* sfa_tile = A_DIRECT ? nullptr : sfa + (int64_t)bm * kq_count * 512;
         const uint8_t* sfb_tile = sfb + (int64_t)bn * kq_count * (C::CHUNKS * 512);
         for (int kb = 0; kb < num_kb; ++kb) {
+          B200_TR_COUNT(2);
+          B200_TR_BEGIN();
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
+          B200_TR_END(0);
+          B200_TR_BEGIN();
           const uint32_t full = bar_full + stage * 8;
           mbar_expect_tx(full, C::STAGE_TX);
           tma_load_2d(stage_a(stage), &tmA, full, kb * 128, bm * F4_BM);
@@ -221,9 +228,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           if (!A_DIRECT)
             bulk_load_1d(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
           bulk_load_1d(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+          B200_TR_END(1);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+      B200_TR_FLUSH(g_trace_fp4_producer, 3, blockIdx.x == 5);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -674,6 +683,7 @@ extern "C" int b200tile_linear_nvfp4_static(const void* x, const void* y, const 
 #ifdef B200TILE_TRACE
 int b200_trace_read_fp4(long long* out) {
   if (cudaMemcpyFromSymbol(out, b200::g_trace_fp4, 8 * sizeof(long long)) != cudaSuccess) return 1;
-  return cudaMemcpyFromSymbol(out + 10, b200::g_trace_fp4_writer, 7 * sizeof(long long)) != cudaSuccess;
+  if (cudaMemcpyFromSymbol(out + 10, b200::g_trace_fp4_writer, 7 * sizeof(long long)) != cudaSuccess) return 1;
+  return cudaMemcpyFromSymbol(out + 17, b200::g_trace_fp4_producer, 3 * sizeof(long long)) != cudaSuccess;
 }
 #endif

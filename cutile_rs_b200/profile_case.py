@@ -144,6 +144,8 @@ def _print_trace(lib, args) -> None:
         w = max(v[14], 1)
         print(f"scale-writer warp per stage: stage-full wait {v[10] / w:.0f}, region wait + loads + store issue "
               f"{v[11] / w:.0f}, store completion {v[12] / w:.0f}, hand-off {v[13] / w:.0f}; total {v[15] / w:.0f}")
+        pn = max(v[19], 1)
+        print(f"TMA producer per stage: stage-empty wait {v[17] / pn:.0f}, issue of the copies {v[18] / pn:.0f}")
         return
     if args.kernel == "gemm":
         stages, tiles = max(v[4], 1), max(v[5], 1)
