@@ -30,8 +30,13 @@ int b200_fmha_fwd_pair_dispatch(int dtype, const void* q, const void* k, const v
                                 int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                                 const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
                                 const uint32_t* pos_ptr, cudaStream_t stream);
+int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
+                               int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
+                               const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
+                               const uint32_t* pos_ptr, cudaStream_t stream);
 
 #ifdef B200TILE_TRACE
+int b200_trace_read_fmha_alt(long long* out);
 int b200_trace_read_gemm_pair(long long* out);
 int b200_trace_read_fmha(long long* out);
 int b200_trace_read_fmha_pair(long long* out);
@@ -259,11 +264,15 @@ static int fmha_fwd_common(const char* dtype, const void* q, const void* k, cons
   // Two configurations for head_dim 128: one CTA per 256 query rows (default, the faster one as
   // measured) and a CTA pair per 512 rows with cta_group::2 MMAs, chosen with
   // CompileOptions::num_cta_in_cga = 2 on the generic launch or B200TILE_FMHA_PAIR=1.
-  static const bool env_pair = [] {
+  static const int env_pair = [] {
     const char* e = getenv("B200TILE_FMHA_PAIR");
-    return e && e[0] == '1';
+    return e ? e[0] - '0' : 0;
   }();
-  if (head_dim == 128 && (cluster == 2 || (cluster == 0 && env_pair)))
+  if (head_dim == 128 && cluster == 0 && env_pair == 2)
+    return b200_fmha_fwd_alt_dispatch(dt, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, q_strides,
+                                      k_strides, v_strides, o_strides, qk_scale, causal ? 1 : 0, input_pos,
+                                      pos_ptr, static_cast<cudaStream_t>(cu_stream));
+  if (head_dim == 128 && (cluster == 2 || (cluster == 0 && env_pair == 1)))
     return b200_fmha_fwd_pair_dispatch(dt, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, q_strides,
                                        k_strides, v_strides, o_strides, qk_scale, causal ? 1 : 0, input_pos,
                                        pos_ptr, static_cast<cudaStream_t>(cu_stream));
@@ -1167,6 +1176,7 @@ B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!strcmp(which, "gemm_pair")) return b200_trace_read_gemm_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha")) return b200_trace_read_fmha(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha_pair")) return b200_trace_read_fmha_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "fmha_alt")) return b200_trace_read_fmha_alt(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "block_scaled")) return b200_trace_read_fp4(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   return B200TILE_ERR_UNSUPPORTED;
 }

@@ -1,0 +1,554 @@
+// Attention forward for head_dim 128 with the softmax taken off the tensor-core chain.
+//
+// fmha_fwd.cu keeps S and P of a query tile in the same Tensor Memory columns, so per key tile the
+// chain softmax -> P.V -> next Q.K^T runs in series and two query tiles per CTA only half hide it.
+// Here a CTA owns ONE 128-row query tile and THREE S buffers (3 x 128 + 128 columns of O fill the
+// 512-column Tensor Memory): S(j+2) is computed while the softmax of tiles j and j+1 is running,
+// and two softmax warpgroups take the key tiles alternately (warpgroup w: tiles j = w, w+2, ...),
+// so the special-function unit, not a dependency chain, sets the pace.
+//
+// With one query tile per CTA the Q.K^T MMAs would need twice the shared-memory operand bandwidth
+// per flop, so the CTAs work in pairs (cta_group::2): one thread of the leader issues M = 256 MMAs
+// covering the query tile of each CTA, and each CTA loads and feeds only 64 of the 128 keys
+// (S = Q K^T) and 64 of the 128 value columns (O += P V) of every K/V tile.
+//
+// The two warpgroups share one running reference maximum per row: a thread decides the reference
+// for its tile from the row maximum and the reference its partner thread (same row, other
+// warpgroup) published for the previous tile, publishes it, and only then does the expensive part.
+// The accumulator O is rescaled in place only when the reference moves by more than 2^8 (rare
+// after the first tiles); each warpgroup keeps its own partial row sum relative to the reference it
+// last saw and the two are merged once at the end.  Numerics are those of fmha_fwd.cu.
+#include "fmha_common.cuh"
+#include "host_common.h"
+#include "sm100_ptx.cuh"
+#include "trace.cuh"
+
+namespace b200 {
+
+#ifdef B200TILE_TRACE
+// One CTA: the P.V thread's [0] V waits, [1] P waits, [2] P.V issue, [5] stage-release commits,
+// [6] key tiles, [7] total cycles; the Q.K thread's [3] K waits, [4] waits for a free S buffer; [8] the same span in ns; softmax lane 0
+// of warpgroup 0 from [10]: S wait, TMEM load, max + reference hand-off, exp2 loop, store wait, P hand-off,
+// key tiles, total.
+__device__ long long g_trace_fmha_alt[20];
+#endif
+
+struct FmhaAltSmem {
+  static constexpr int D = 128;
+  static constexpr int NBUF = 2;                        // S buffers and P buffers in Tensor Memory
+  static constexpr int HALF_BYTES = 128 * 128;          // 128 rows x 128 bytes (one 64-wide column block)
+  static constexpr int TILE_BYTES = 2 * HALF_BYTES;     // the 128 x 128 Q tile
+  static constexpr int K_HALF = 64 * 128;               // this CTA's 64 keys, one column block
+  static constexpr int K_BYTES = 2 * K_HALF;            // 64 keys x 128 dims
+  static constexpr int V_BYTES = 128 * 128;             // 128 keys x this CTA's 64 value columns
+  // K is consumed two key tiles before V: separate rings, each released as early as possible
+  static constexpr int K_STAGES = 6;
+  static constexpr int V_STAGES = 5;
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_K = OFF_Q + TILE_BYTES;
+  static constexpr int OFF_V = OFF_K + K_STAGES * K_BYTES;
+  static constexpr int OFF_BAR = OFF_V + V_STAGES * V_BYTES;
+  // q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[NBUF], s_free[NBUF], p_full[NBUF], m_pub[2][4]
+  static constexpr int NUM_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 3 * NBUF + 8;
+  static constexpr int OFF_MREF = OFF_BAR + NUM_BARS * 8;       // float[128] shared reference maximum
+  static constexpr int OFF_LSUM = OFF_MREF + 128 * 4;           // float[2][128] partial sums, float[2][128] their references
+  static constexpr int OFF_MISC = OFF_LSUM + 4 * 128 * 4;
+  static constexpr int TOTAL = OFF_MISC + 16 + 1024;
+};
+
+template <bool OUT_F16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FA_THREADS, 1)
+fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                    const FmhaParams p, uint32_t* status) {
+  using L = FmhaAltSmem;
+  constexpr int D = L::D;
+  constexpr int KST = L::K_STAGES;
+  constexpr int VST = L::V_STAGES;
+  constexpr int NBUF = L::NBUF;
+  constexpr uint32_t HALF = L::HALF_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+
+  const uint32_t sQ = base + L::OFF_Q;
+  const uint32_t sK = base + L::OFF_K;
+  const uint32_t sV = base + L::OFF_V;
+  const uint32_t bar_q_full = base + L::OFF_BAR;            // leader
+  const uint32_t bar_k_full = bar_q_full + 8;               // leader
+  const uint32_t bar_k_empty = bar_k_full + KST * 8;        // each CTA
+  const uint32_t bar_v_full = bar_k_empty + KST * 8;        // leader
+  const uint32_t bar_v_empty = bar_v_full + VST * 8;        // each CTA; also "P.V of that key tile has retired"
+  const uint32_t bar_s_full = bar_v_empty + VST * 8;        // each CTA
+  const uint32_t bar_s_free = bar_s_full + NBUF * 8;        // leader, 8 arrivals: S buffer read into registers
+  const uint32_t bar_p_full = bar_s_free + NBUF * 8;        // leader, 8 arrivals
+  const uint32_t bar_m_pub = bar_p_full + NBUF * 8;         // each CTA: [warpgroup][quadrant]
+  float* m_ref = reinterpret_cast<float*>(gen_base + L::OFF_MREF);
+  float* l_part_sm = reinterpret_cast<float*>(gen_base + L::OFF_LSUM);
+  float* m_part_sm = l_part_sm + 256;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + L::OFF_MISC);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  WaitCtx wctx{misc + 1, status};
+
+  // ---- work item of the cluster: 256 query rows of one (batch, head); longest causal rows first ----
+  int qpair, bh;
+  {
+    const int idx = blockIdx.x >> 1;
+    const int per_chunk = p.num_q_pairs * p.head_group;
+    const int chunk = idx / per_chunk;
+    const int r = idx - chunk * per_chunk;
+    const int left = p.bh_total - chunk * p.head_group;
+    const int gsz = left < p.head_group ? left : p.head_group;
+    qpair = r / gsz;
+    bh = chunk * p.head_group + (r - qpair * gsz);
+    if (p.causal) qpair = p.num_q_pairs - 1 - qpair;
+  }
+  const int input_pos = p.pos_ptr ? (int)__ldg(p.pos_ptr) : p.input_pos;
+  const int kv_bh = (bh / p.heads) * p.heads_kv + (bh % p.heads) / p.group;
+  const int n_total = (p.kv_len + FA_BN - 1) / FA_BN;
+  const int q0 = (qpair * 2 + (int)rank) * FA_BM;   // this CTA's tile
+  // both CTAs walk the same key tiles: the count is that of the pair's last row
+  int n_kv = n_total;
+  if (p.causal) {
+    const int last = (qpair * 2 * FA_BM + 2 * FA_BM - 1 + input_pos) / FA_BN + 1;
+    n_kv = last < n_total ? last : n_total;
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar_q_full, 1);
+    for (int s = 0; s < KST; ++s) {
+      mbar_init(bar_k_full + s * 8, 1);
+      mbar_init(bar_k_empty + s * 8, 1);
+    }
+    for (int s = 0; s < VST; ++s) {
+      mbar_init(bar_v_full + s * 8, 1);
+      mbar_init(bar_v_empty + s * 8, 1);
+    }
+    for (int i = 0; i < NBUF; ++i) {
+      mbar_init(bar_s_full + i * 8, 1);
+      mbar_init(bar_s_free + i * 8, 8);   // four softmax warps from each CTA
+      mbar_init(bar_p_full + i * 8, 8);
+    }
+    for (int i = 0; i < 8; ++i) mbar_init(bar_m_pub + i * 8, 1);
+    misc[1] = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmO);
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(misc)), 512);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = misc[0];
+  // Tensor Memory columns: S[2] (fp32, 128 each), P[2] (16-bit pairs, 64 each), O (fp32, 128)
+  auto S_COL = [](int b) { return (uint32_t)(b * 128); };
+  auto P_COL = [](int b) { return (uint32_t)(256 + b * 64); };
+  constexpr uint32_t O_COL = 384;
+
+  if (warp < 4) reg_dealloc<80>();   // 128 x 80 + 256 x 208 registers
+  if (warp == 0) {
+    // ---------------------------- TMA loader: Q and K ----------------------------
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t q_full_l = mapa_u32(bar_q_full, 0);
+      const uint32_t k_full_l = mapa_u32(bar_k_full, 0);
+      if (leader) mbar_expect_tx(bar_q_full, 2 * L::TILE_BYTES);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) tma_load_3d_pair(sQ + h * HALF, &tmQ, q_full_l, h * 64, q0, bh);
+      uint32_t stage = 0, phase = 0;
+      for (int j = 0; j < n_kv; ++j) {
+        if (!mbar_wait(wctx, bar_k_empty + stage * 8, phase ^ 1, 10)) break;
+        const uint32_t k_dst = sK + stage * L::K_BYTES;
+        if (leader) mbar_expect_tx(bar_k_full + stage * 8, 2 * L::K_BYTES);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          tma_load_3d_pair(k_dst + h * L::K_HALF, &tmK, k_full_l + stage * 8, h * 64,
+                           j * FA_BN + (int)rank * 64, kv_bh);
+        if (++stage == KST) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------- TMA loader: V -------------------------------
+    if (lane == 0 && n_kv > 0) {
+      const uint32_t v_full_l = mapa_u32(bar_v_full, 0);
+      uint32_t stage = 0, phase = 0;
+      for (int j = 0; j < n_kv; ++j) {
+        if (!mbar_wait(wctx, bar_v_empty + stage * 8, phase ^ 1, 11)) break;
+        if (leader) mbar_expect_tx(bar_v_full + stage * 8, 2 * L::V_BYTES);
+        tma_load_3d_pair(sV + stage * L::V_BYTES, &tmV, v_full_l + stage * 8, (int)rank * 64, j * FA_BN, kv_bh);
+        if (++stage == VST) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------- S = Q K^T issuer (leader CTA only), runs ahead of the softmax -------------
+    // The two kinds of MMA come from two threads: issuing one tcgen05.mma costs the issuing thread
+    // about as long as a 256x128x16 MMA keeps the tensor pipe busy, so one thread alone cannot
+    // keep the pipe fed once waits and commits are added.
+    if (leader && lane == 0 && n_kv > 0) {
+      constexpr uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
+      constexpr uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, 2 * FA_BM, FA_BN);
+      const uint32_t s_full_peer = mapa_u32(bar_s_full, 1);
+      const uint32_t k_empty_peer = mapa_u32(bar_k_empty, 1);
+      bool ok = mbar_wait(wctx, bar_q_full, 0, 21);
+      uint32_t ks = 0, kph = 0, sb = 0;
+#ifdef B200TILE_TRACE
+      long long qk_wait_k = 0, qk_wait_s = 0;
+#endif
+      for (int j = 0; j < n_kv && ok; ++j) {
+#ifdef B200TILE_TRACE
+        const long long c0 = clock64();
+#endif
+        if (!mbar_wait(wctx, bar_k_full + ks * 8, kph, 20)) break;
+#ifdef B200TILE_TRACE
+        const long long c1 = clock64();
+        qk_wait_k += c1 - c0;
+#endif
+        if (j >= NBUF) {
+          // the softmax warps of both CTAs have read S(j - NBUF) out of buffer sb
+          if (!mbar_wait(wctx, bar_s_free + sb * 8, (uint32_t)((j - NBUF) / NBUF) & 1u, 23)) break;
+        }
+#ifdef B200TILE_TRACE
+        qk_wait_s += clock64() - c1;
+#endif
+        tc_fence_after_sync();
+        const uint32_t k_addr = sK + ks * L::K_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint64_t a = make_smem_desc(sQ + (kk / 4) * HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
+          const uint64_t bd = make_smem_desc(k_addr + (kk / 4) * L::K_HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
+          umma_f16_ss_2cta(tmem_base + S_COL(sb), a, bd, idesc_qk, kk != 0);
+        }
+        umma_commit_2cta(bar_s_full + sb * 8);
+        umma_commit_2cta(s_full_peer + sb * 8);
+        umma_commit_2cta(bar_k_empty + ks * 8);
+        umma_commit_2cta(k_empty_peer + ks * 8);
+        if (++ks == KST) { ks = 0; kph ^= 1; }
+        if (++sb == NBUF) sb = 0;
+      }
+#ifdef B200TILE_TRACE
+      misc[2] = (uint32_t)qk_wait_k;   // read by the P.V thread, which finishes later
+      misc[3] = (uint32_t)qk_wait_s;
+#endif
+    }
+  } else if (warp == 2) {
+    // ------------------------- O += P V issuer (leader CTA only) -------------------------
+    if (leader && lane == 0 && n_kv > 0) {
+      constexpr uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
+      constexpr uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, 2 * FA_BM, D);
+      const uint32_t v_empty_peer = mapa_u32(bar_v_empty, 1);
+      bool ok = true;
+      B200_TR_DECL(7);
+      uint32_t vs = 0, vph = 0, pb = 0, pph = 0;
+      for (int j = 0; j < n_kv && ok; ++j) {
+        B200_TR_COUNT(6);
+        B200_TR_BEGIN();
+        if (!mbar_wait(wctx, bar_v_full + vs * 8, vph, 22)) { ok = false; break; }
+        B200_TR_END(0);
+        B200_TR_BEGIN();
+        if (!mbar_wait(wctx, bar_p_full + pb * 8, pph, 24)) { ok = false; break; }
+        tc_fence_after_sync();
+        B200_TR_END(1);
+        B200_TR_BEGIN();
+        const uint32_t v_addr = sV + vs * L::V_BYTES;
+#pragma unroll
+        for (int kk = 0; kk < FA_BN / 16; ++kk) {
+          // V is the N-major B operand; each CTA holds one 64-column block, 16 key rows per step
+          const uint64_t bd = make_smem_desc(v_addr + kk * 2048, HALF, 1024, SWZ_128B);
+          umma_f16_ts_2cta(tmem_base + O_COL, tmem_base + P_COL(pb) + kk * 8, bd, idesc_pv, j > 0 || kk != 0);
+        }
+        B200_TR_END(2);
+        // V(j) is free in both CTAs; the same signal tells the softmax warps that O holds key tile j
+        B200_TR_BEGIN();
+        umma_commit_2cta(bar_v_empty + vs * 8);
+        umma_commit_2cta(v_empty_peer + vs * 8);
+        B200_TR_END(5);
+        if (++vs == VST) { vs = 0; vph ^= 1; }
+        if (++pb == NBUF) { pb = 0; pph ^= 1; }
+      }
+#ifdef B200TILE_TRACE
+      tr_[3] = misc[2];
+      tr_[4] = misc[3];
+#endif
+      B200_TR_FLUSH(g_trace_fmha_alt, 7, blockIdx.x == 14);
+    }
+  } else if (warp >= 4) {
+    // -------------------------------- softmax ----------------------------------
+    reg_alloc<FA_SOFTMAX_REGS>();
+    const int w = (warp - 4) >> 2;          // warpgroup: key tiles j = w, w + 2, ...
+    const int q = warp & 3;
+    const int row = q * 32 + lane;          // row inside the tile == TMEM lane
+    const int row_g = q0 + row;             // query position
+    const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    const uint32_t tO = lane_base + O_COL;
+    const uint32_t my_pub = bar_m_pub + (uint32_t)(w * 4 + q) * 8;
+    const uint32_t other_pub = bar_m_pub + (uint32_t)((1 - w) * 4 + q) * 8;
+    const float scale = p.scale_log2;
+    float m_seen = -CUDART_INF_F, l_part = 0.0f;   // this warpgroup's row sum, relative to m_seen
+    bool ok = true;
+    B200_TR_DECL(7);
+    for (int j = w; j < n_kv && ok; j += 2) {
+      const int b = j % NBUF;
+      const uint32_t tS = lane_base + S_COL(b);
+      const uint32_t tP = lane_base + P_COL(b);
+      B200_TR_COUNT(6);
+      B200_TR_BEGIN();
+      if (!mbar_wait(wctx, bar_s_full + b * 8, (uint32_t)(j / NBUF) & 1u, 30)) { ok = false; break; }
+      tc_fence_after_sync();
+      B200_TR_END(0);
+      B200_TR_BEGIN();
+      // the whole score row lives in registers: one TMEM read per element
+      uint32_t v[FA_BN];
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c)
+        tmem_ld_32x32b_x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+      // last key column this row may see inside this tile (>= 127: nothing masked)
+      int lim = p.kv_len - 1 - j * FA_BN;
+      if (p.causal) {
+        const int c = row_g + input_pos - j * FA_BN;
+        lim = c < lim ? c : lim;
+      }
+      const bool masked_tile = __any_sync(0xffffffffu, lim < FA_BN - 1);
+      tmem_wait_ld();
+      // the scores are in registers: the buffer can take S(j + 2) while this tile is worked on
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_s_free + b * 8, 0));
+      B200_TR_END(1);
+      B200_TR_BEGIN();
+      if (masked_tile) {
+#pragma unroll
+        for (int i = 0; i < FA_BN; ++i)
+          if (i > lim) v[i] = 0xff800000u;  // -inf
+      }
+      // row maximum: four independent chains
+      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int i = 0; i < FA_BN; i += 8) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          mx[u] = max3(mx[u], __uint_as_float(v[i + 2 * u]), __uint_as_float(v[i + 2 * u + 1]));
+      }
+      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale;
+      // reference maximum of this tile: the partner's reference unless the row maximum outgrew it
+      float m_new, alpha = 1.0f;
+      bool need = false;
+      if (j == 0) {
+        m_new = m_tile == -CUDART_INF_F ? 0.0f : m_tile;  // fully masked row: keep exp2 arguments finite
+      } else {
+        if (!mbar_wait(wctx, other_pub, (uint32_t)((j - 1) >> 1) & 1u, 32)) { ok = false; break; }
+        const float m_old = m_ref[row];
+        m_new = m_old;
+        if (m_tile - m_old > FA_RESCALE_THRESHOLD) {
+          need = true;
+          m_new = m_tile;
+          alpha = ex2_approx(m_old - m_new);
+        }
+      }
+      m_ref[row] = m_new;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(my_pub);
+      if (m_new != m_seen) {
+        l_part *= ex2_approx(m_seen - m_new);
+        m_seen = m_new;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, need)) {
+        // O must hold key tile j-1 before it is rescaled; P.V of tile j cannot start before this
+        // warp has handed over P(j), and the partner's rescale for tile j+1 waits for that P.V
+        const int jp = j - 1;
+        if (!mbar_wait(wctx, bar_v_empty + (jp % VST) * 8, (uint32_t)(jp / VST) & 1u, 33)) { ok = false; break; }
+        tc_fence_after_sync();
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tO + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x32(tO + c * 32, o);
+        }
+      }
+      // probabilities: exp2(s*scale - m); masked entries are exp2(-inf) = 0
+      B200_TR_END(2);
+      B200_TR_BEGIN();
+      if (j >= NBUF) {
+        // P(j - 2) must have been consumed before its buffer is overwritten
+        const int jp = j - NBUF;
+        if (!mbar_wait(wctx, bar_v_empty + (jp % VST) * 8, (uint32_t)(jp / VST) & 1u, 34)) { ok = false; break; }
+        tc_fence_after_sync();
+      }
+      const float neg_m = -m_new;
+      const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(neg_m, neg_m);
+      uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed (even, odd) partial sums
+#pragma unroll
+      for (int c = 0; c < FA_BN / 32; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint64_t x2 = fma2(pack2(__uint_as_float(v[c * 32 + 2 * i]),
+                                         __uint_as_float(v[c * 32 + 2 * i + 1])), scale2, negm2);
+          float xa, xb;
+          unpack2(x2, xa, xb);
+          const float a = ex2_approx(xa), bb = ex2_approx(xb);
+          ls2[i & 3] = add2(ls2[i & 3], pack2(a, bb));
+          pk[i] = OUT_F16 ? pack_f16x2(a, bb) : pack_bf16x2(a, bb);
+        }
+        tmem_st_32x32b_x16(tP + c * 16, pk);
+      }
+      float ls[4];
+      {
+        const uint64_t s01 = add2(ls2[0], ls2[1]), s23 = add2(ls2[2], ls2[3]);
+        unpack2(s01, ls[0], ls[1]);
+        unpack2(s23, ls[2], ls[3]);
+      }
+      l_part += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+      B200_TR_END(3);
+      B200_TR_BEGIN();
+      tmem_wait_st();
+      B200_TR_END(4);
+      B200_TR_BEGIN();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_p_full + b * 8, 0));
+      B200_TR_END(5);
+    }
+    B200_TR_FLUSH(g_trace_fmha_alt + 10, 7, blockIdx.x == 14 && warp == 4 && lane == 0);
+    // ------------------------------- epilogue ----------------------------------
+    // merge the two warpgroups' row sums under the final reference
+    l_part_sm[w * 128 + row] = l_part;
+    m_part_sm[w * 128 + row] = m_seen;
+    named_bar_sync(1, 256);
+    if (n_kv > 0 && ok) {
+      const int jl = n_kv - 1;
+      if (mbar_wait(wctx, bar_v_empty + (jl % VST) * 8, (uint32_t)(jl / VST) & 1u, 31)) {
+        tc_fence_after_sync();
+        const float m_fin = m_ref[row];
+        const float l_run = l_part_sm[row] * ex2_approx(m_part_sm[row] - m_fin) +
+                            l_part_sm[128 + row] * ex2_approx(m_part_sm[128 + row] - m_fin);
+        const float inv_l = 1.0f / fmaxf(l_run, 1e-8f);  // attention.rs:385-390
+        // Q's shared memory is free now (all S MMAs retired): warpgroup w stages value columns
+        // [64w, 64w + 64) there and each warp stores its 32 rows
+        const uint32_t half_base = sQ + (uint32_t)w * HALF + (uint32_t)row * 128;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tO + w * 64 + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint32_t wd[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const float lo = __uint_as_float(o[e * 8 + 2 * x]) * inv_l;
+              const float hi = __uint_as_float(o[e * 8 + 2 * x + 1]) * inv_l;
+              wd[x] = OUT_F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
+            }
+            const uint32_t chunk = (uint32_t)(c * 4 + e);
+            const uint32_t dst = half_base + ((chunk ^ (uint32_t)(lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(wd[0]),
+                         "r"(wd[1]), "r"(wd[2]), "r"(wd[3])
+                         : "memory");
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && q0 + q * 32 < p.q_len) {   // the pair may reach past the last query row
+          tma_store_3d(&tmO, sQ + (uint32_t)w * HALF + (uint32_t)(q * 32) * 128, w * 64, q0 + q * 32, bh);
+          tma_store_commit();
+          tma_store_wait_all<0>();
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while its partner may still signal its barriers
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_2cta(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host launch
+// ---------------------------------------------------------------------------
+template <bool OUT_F16>
+static int launch_fmha_alt(const void* q, const void* k, const void* v, void* o, int batch, int heads, int heads_kv,
+                           int q_len, int kv_len, const int64_t* qs, const int64_t* ks, const int64_t* vs,
+                           const int64_t* os, float qk_scale, int causal, int input_pos, const uint32_t* pos_ptr,
+                           cudaStream_t stream) {
+  using L = FmhaAltSmem;
+  constexpr int D = L::D;
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200_ERR_CUDA;
+  const CUtensorMapDataType dt = OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tmQ, tmK, tmV, tmO;
+  int rc;
+  const uint64_t bh = (uint64_t)batch * heads, bhkv = (uint64_t)batch * heads_kv;
+  if ((rc = b200h::encode_tmap_3d(&tmQ, dt, 2, q, D, q_len, bh, qs[1] * 2, qs[0] * 2, 64, FA_BM, 1,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  // K arrives as 64-key boxes (one per CTA of the pair), V as 128 keys x one 64-column block
+  if ((rc = b200h::encode_tmap_3d(&tmK, dt, 2, k, D, kv_len, bhkv, ks[1] * 2, ks[0] * 2, 64, 64, 1,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_3d(&tmV, dt, 2, v, D, kv_len, bhkv, vs[1] * 2, vs[0] * 2, 64, FA_BN, 1,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_3d(&tmO, dt, 2, o, D, q_len, bh, os[1] * 2, os[0] * 2, 64, 32, 1,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  auto kern = fmha_fwd_alt_kernel<OUT_F16>;
+  static bool attr_done[64] = {};
+  if (!attr_done[di->ordinal]) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    attr_done[di->ordinal] = true;
+  }
+  FmhaParams p;
+  p.q_len = q_len;
+  p.kv_len = kv_len;
+  p.num_q_pairs = (q_len + 2 * FA_BM - 1) / (2 * FA_BM);   // 256-row pairs per (batch, head)
+  p.bh_total = (int)bh;
+  p.heads = heads;
+  p.heads_kv = heads_kv;
+  p.group = heads / heads_kv;
+  p.causal = causal;
+  p.input_pos = input_pos;
+  p.pos_ptr = pos_ptr;
+  p.head_group = 8;
+  p.scale_log2 = qk_scale * 1.4426950408889634f;
+  const long long ctas = 2ll * p.num_q_pairs * p.bh_total;
+  if (ctas > 0x7fffffffLL) return b200h::set_error(B200_ERR_INVALID, "fmha: grid too large");
+  kern<<<(unsigned)ctas, FA_THREADS, L::TOTAL, stream>>>(tmQ, tmK, tmV, tmO, p, di->status);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+}  // namespace b200
+
+// dtype: 0 = bf16, 1 = f16; head_dim 128 only.  Same argument meaning as b200_fmha_fwd_dispatch.
+int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
+                               int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
+                               const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
+                               const uint32_t* pos_ptr, cudaStream_t stream) {
+  using namespace b200;
+  return dtype ? launch_fmha_alt<true>(q, k, v, o, batch, heads, heads_kv, q_len, kv_len, qs, ks, vs, os, qk_scale,
+                                       causal, input_pos, pos_ptr, stream)
+               : launch_fmha_alt<false>(q, k, v, o, batch, heads, heads_kv, q_len, kv_len, qs, ks, vs, os, qk_scale,
+                                        causal, input_pos, pos_ptr, stream);
+}
+
+#ifdef B200TILE_TRACE
+int b200_trace_read_fmha_alt(long long* out) {
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fmha_alt, 20 * sizeof(long long)) != cudaSuccess;
+}
+#endif

@@ -360,7 +360,7 @@ fmha_fwd_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       B200_TR_BEGIN();
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_addr(p_full_leader);
+      if (lane == 0) mbar_arrive_cluster_addr_cta_release(p_full_leader);
       B200_TR_END(5);
     }
     B200_TR_FLUSH(g_trace_fmha_pair + 10, 7, blockIdx.x == 14 && warp == 4 && lane == 0);

@@ -314,6 +314,12 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* desc,
       ::"r"(dst), "l"(desc), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+// The same with CTA-scope release: enough when what the waiter consumes is ordered by other means
+// (Tensor Memory contents behind tcgen05 fences); the cluster-scope release above costs several
+// hundred cycles per call.
+__device__ __forceinline__ void mbar_arrive_cluster_addr_cta_release(uint32_t bar_cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster_addr(uint32_t bar_cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];"
                ::"r"(bar_cluster_addr) : "memory");

@@ -48,7 +48,7 @@ def main() -> None:
     args = ap.parse_args()
     if args.pair:
         import os
-        os.environ["B200TILE_FMHA_PAIR"] = "1"
+        os.environ["B200TILE_FMHA_PAIR"] = str(args.pair)
 
     torch.cuda.set_device(0)
     lib = _lib.load()
@@ -131,7 +131,7 @@ def _print_trace(lib, args) -> None:
     if not hasattr(lib, "b200tile_trace_read"):
         raise SystemExit("--trace needs the diagnostic build (see the module docstring)")
     out = (ctypes.c_longlong * 20)()
-    which = {"gemm": b"gemm_pair", "fmha": b"fmha_pair" if args.pair else b"fmha",
+    which = {"gemm": b"gemm_pair", "fmha": {0: b"fmha", 1: b"fmha_pair", 2: b"fmha_alt"}[args.pair],
              "nvfp4": b"block_scaled"}.get(args.kernel)
     if which is None or lib.b200tile_trace_read(which, out):
         raise SystemExit("no trace for this kernel")
@@ -156,6 +156,8 @@ def _print_trace(lib, args) -> None:
     else:
         n, m = max(v[6], 1), max(v[16], 1)
         names = ["K/V waits", "P waits", "P.V issue", "Q.K issue", "S commits", "release commits"]
+        if args.pair == 2:
+            names = ["V waits", "P waits", "P.V issue", "K waits (Q.K thread)", "free-S waits (Q.K thread)", "release commits"]
         print("MMA thread per key tile (both query tiles): " +
               ", ".join(f"{nm} {v[i] / n:.0f}" for i, nm in enumerate(names)) + f"; total {v[7] / n:.0f} ({n} key tiles); SM clock inside the kernel {1e3 * v[7] / max(v[8], 1):.0f} MHz")
         names = ["S wait", "TMEM load", "max+rescale", "exp2 loop", "store wait", "hand-off"]
