@@ -2,22 +2,30 @@
 //
 // fmha_fwd.cu keeps S and P of a query tile in the same Tensor Memory columns, so per key tile the
 // chain softmax -> P.V -> next Q.K^T runs in series and two query tiles per CTA only half hide it.
-// Here a CTA owns ONE 128-row query tile and THREE S buffers (3 x 128 + 128 columns of O fill the
-// 512-column Tensor Memory): S(j+2) is computed while the softmax of tiles j and j+1 is running,
-// and two softmax warpgroups take the key tiles alternately (warpgroup w: tiles j = w, w+2, ...),
-// so the special-function unit, not a dependency chain, sets the pace.
+// Here a CTA owns ONE 128-row query tile at a time, two S buffers and two separate P buffers
+// (2 x 128 + 2 x 64 + 128 columns of O fill the 512-column Tensor Memory).  An S buffer is free
+// again as soon as the softmax has read it into registers, so S(j+2) is computed while the softmax
+// of tiles j and j+1 is running; two softmax warpgroups take the key tiles alternately, and the
+// Q.K^T and P.V MMAs are issued by two different threads (issuing one tcgen05.mma costs the issuing
+// thread about as long as the MMA keeps the tensor pipe busy, so one thread with its waits and
+// commits cannot keep the pipe fed).
 //
 // With one query tile per CTA the Q.K^T MMAs would need twice the shared-memory operand bandwidth
-// per flop, so the CTAs work in pairs (cta_group::2): one thread of the leader issues M = 256 MMAs
-// covering the query tile of each CTA, and each CTA loads and feeds only 64 of the 128 keys
-// (S = Q K^T) and 64 of the 128 value columns (O += P V) of every K/V tile.
+// per flop, so the CTAs work in pairs (cta_group::2): the leader issues M = 256 MMAs covering the
+// query tile of each CTA, and each CTA loads and feeds only 64 of the 128 keys (S = Q K^T) and 64
+// of the 128 value columns (O += P V) of every K/V tile.
+//
+// The kernel is persistent: a CTA pair walks a strided list of (256 query rows, batch*head) items,
+// all barriers and rings run on across items, Q is double-buffered, and the only thing one item
+// waits for from the previous one is the drained accumulator.  Pipeline fill and drain, which cost
+// as much as five key tiles per item, are hidden that way.
 //
 // The two warpgroups share one running reference maximum per row: a thread decides the reference
 // for its tile from the row maximum and the reference its partner thread (same row, other
 // warpgroup) published for the previous tile, publishes it, and only then does the expensive part.
 // The accumulator O is rescaled in place only when the reference moves by more than 2^8 (rare
 // after the first tiles); each warpgroup keeps its own partial row sum relative to the reference it
-// last saw and the two are merged once at the end.  Numerics are those of fmha_fwd.cu.
+// last saw and the two are merged at the end of the item.  Numerics are those of fmha_fwd.cu.
 #include "fmha_common.cuh"
 #include "host_common.h"
 #include "sm100_ptx.cuh"
@@ -27,45 +35,70 @@ namespace b200 {
 
 #ifdef B200TILE_TRACE
 // One CTA: the P.V thread's [0] V waits, [1] P waits, [2] P.V issue, [5] stage-release commits,
-// [6] key tiles, [7] total cycles; the Q.K thread's [3] K waits, [4] waits for a free S buffer; [8] the same span in ns; softmax lane 0
-// of warpgroup 0 from [10]: S wait, TMEM load, max + reference hand-off, exp2 loop, store wait, P hand-off,
-// key tiles, total.
+// [6] key tiles, [7] total cycles; the Q.K thread's [3] K waits, [4] waits for a free S buffer;
+// [8] the total span in ns; softmax lane 0 of warpgroup 0 from [10]: S wait, TMEM load, max +
+// reference hand-off, exp2 loop, store wait, P hand-off, key tiles, total.
 __device__ long long g_trace_fmha_alt[20];
 #endif
 
 struct FmhaAltSmem {
   static constexpr int D = 128;
-  static constexpr int NBUF = 2;                        // S buffers and P buffers in Tensor Memory
   static constexpr int HALF_BYTES = 128 * 128;          // 128 rows x 128 bytes (one 64-wide column block)
-  static constexpr int TILE_BYTES = 2 * HALF_BYTES;     // the 128 x 128 Q tile
+  static constexpr int TILE_BYTES = 2 * HALF_BYTES;     // a 128 x 128 Q tile
   static constexpr int K_HALF = 64 * 128;               // this CTA's 64 keys, one column block
   static constexpr int K_BYTES = 2 * K_HALF;            // 64 keys x 128 dims
   static constexpr int V_BYTES = 128 * 128;             // 128 keys x this CTA's 64 value columns
   // K is consumed two key tiles before V: separate rings, each released as early as possible
-  static constexpr int K_STAGES = 6;
-  static constexpr int V_STAGES = 5;
-  static constexpr int OFF_Q = 0;
-  static constexpr int OFF_K = OFF_Q + TILE_BYTES;
+  static constexpr int K_STAGES = 5;
+  static constexpr int V_STAGES = 4;
+  static constexpr int OFF_Q = 0;                       // two Q tiles: this item's and the next one's
+  static constexpr int OFF_K = OFF_Q + 2 * TILE_BYTES;
   static constexpr int OFF_V = OFF_K + K_STAGES * K_BYTES;
   static constexpr int OFF_BAR = OFF_V + V_STAGES * V_BYTES;
-  // q_full, k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[NBUF], s_free[NBUF], p_full[NBUF], m_pub[2][4]
-  static constexpr int NUM_BARS = 1 + 2 * K_STAGES + 2 * V_STAGES + 3 * NBUF + 8;
+  // q_full[2], q_empty[2], k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], s_free[2],
+  // p_full[2], o_free, m_pub[2][4]
+  static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 6 + 1 + 8;
   static constexpr int OFF_MREF = OFF_BAR + NUM_BARS * 8;       // float[128] shared reference maximum
   static constexpr int OFF_LSUM = OFF_MREF + 128 * 4;           // float[2][128] partial sums, float[2][128] their references
   static constexpr int OFF_MISC = OFF_LSUM + 4 * 128 * 4;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
 };
 
+// One work item of a CTA pair.
+struct AltItem {
+  int bh, kv_bh, q0, n_kv;
+};
+
+__device__ __forceinline__ AltItem alt_item(const FmhaParams& p, int idx, int rank, int input_pos, int n_total) {
+  const int per_chunk = p.num_q_pairs * p.head_group;
+  const int chunk = idx / per_chunk;
+  const int r = idx - chunk * per_chunk;
+  const int left = p.bh_total - chunk * p.head_group;
+  const int gsz = left < p.head_group ? left : p.head_group;
+  int qpair = r / gsz;
+  AltItem it;
+  it.bh = chunk * p.head_group + (r - qpair * gsz);
+  if (p.causal) qpair = p.num_q_pairs - 1 - qpair;   // long rows first
+  it.kv_bh = (it.bh / p.heads) * p.heads_kv + (it.bh % p.heads) / p.group;
+  it.q0 = (qpair * 2 + rank) * FA_BM;
+  // both CTAs walk the same key tiles: the count is that of the pair's last row
+  it.n_kv = n_total;
+  if (p.causal) {
+    const int last = (qpair * 2 * FA_BM + 2 * FA_BM - 1 + input_pos) / FA_BN + 1;
+    it.n_kv = last < n_total ? last : n_total;
+  }
+  return it;
+}
+
 template <bool OUT_F16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FA_THREADS, 1)
 fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
-                    const FmhaParams p, uint32_t* status) {
+                    const __grid_constant__ CUtensorMap tmV, uint16_t* __restrict__ out, long long o_stride_bh,
+                    long long o_stride_row, const FmhaParams p, uint32_t* status) {
   using L = FmhaAltSmem;
   constexpr int D = L::D;
   constexpr int KST = L::K_STAGES;
   constexpr int VST = L::V_STAGES;
-  constexpr int NBUF = L::NBUF;
   constexpr uint32_t HALF = L::HALF_BYTES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -74,15 +107,17 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t sQ = base + L::OFF_Q;
   const uint32_t sK = base + L::OFF_K;
   const uint32_t sV = base + L::OFF_V;
-  const uint32_t bar_q_full = base + L::OFF_BAR;            // leader
-  const uint32_t bar_k_full = bar_q_full + 8;               // leader
+  const uint32_t bar_q_full = base + L::OFF_BAR;            // leader [2]
+  const uint32_t bar_q_empty = bar_q_full + 2 * 8;          // each CTA [2]
+  const uint32_t bar_k_full = bar_q_empty + 2 * 8;          // leader
   const uint32_t bar_k_empty = bar_k_full + KST * 8;        // each CTA
   const uint32_t bar_v_full = bar_k_empty + KST * 8;        // leader
   const uint32_t bar_v_empty = bar_v_full + VST * 8;        // each CTA; also "P.V of that key tile has retired"
-  const uint32_t bar_s_full = bar_v_empty + VST * 8;        // each CTA
-  const uint32_t bar_s_free = bar_s_full + NBUF * 8;        // leader, 8 arrivals: S buffer read into registers
-  const uint32_t bar_p_full = bar_s_free + NBUF * 8;        // leader, 8 arrivals
-  const uint32_t bar_m_pub = bar_p_full + NBUF * 8;         // each CTA: [warpgroup][quadrant]
+  const uint32_t bar_s_full = bar_v_empty + VST * 8;        // each CTA [2]
+  const uint32_t bar_s_free = bar_s_full + 2 * 8;           // leader [2], 8 arrivals: S buffer read into registers
+  const uint32_t bar_p_full = bar_s_free + 2 * 8;           // leader [2], 8 arrivals
+  const uint32_t bar_o_free = bar_p_full + 2 * 8;           // leader, 16 arrivals: O read out of Tensor Memory
+  const uint32_t bar_m_pub = bar_o_free + 8;                // each CTA: [warpgroup][quadrant]
   float* m_ref = reinterpret_cast<float*>(gen_base + L::OFF_MREF);
   float* l_part_sm = reinterpret_cast<float*>(gen_base + L::OFF_LSUM);
   float* m_part_sm = l_part_sm + 256;
@@ -94,32 +129,20 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const bool leader = rank == 0;
   WaitCtx wctx{misc + 1, status};
 
-  // ---- work item of the cluster: 256 query rows of one (batch, head); longest causal rows first ----
-  int qpair, bh;
-  {
-    const int idx = blockIdx.x >> 1;
-    const int per_chunk = p.num_q_pairs * p.head_group;
-    const int chunk = idx / per_chunk;
-    const int r = idx - chunk * per_chunk;
-    const int left = p.bh_total - chunk * p.head_group;
-    const int gsz = left < p.head_group ? left : p.head_group;
-    qpair = r / gsz;
-    bh = chunk * p.head_group + (r - qpair * gsz);
-    if (p.causal) qpair = p.num_q_pairs - 1 - qpair;
-  }
   const int input_pos = p.pos_ptr ? (int)__ldg(p.pos_ptr) : p.input_pos;
-  const int kv_bh = (bh / p.heads) * p.heads_kv + (bh % p.heads) / p.group;
   const int n_total = (p.kv_len + FA_BN - 1) / FA_BN;
-  const int q0 = (qpair * 2 + (int)rank) * FA_BM;   // this CTA's tile
-  // both CTAs walk the same key tiles: the count is that of the pair's last row
-  int n_kv = n_total;
-  if (p.causal) {
-    const int last = (qpair * 2 * FA_BM + 2 * FA_BM - 1 + input_pos) / FA_BN + 1;
-    n_kv = last < n_total ? last : n_total;
-  }
+  const int total_items = p.num_q_pairs * p.bh_total;
+  const int first_item = blockIdx.x >> 1;
+  const int item_stride = gridDim.x >> 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_q_full + i * 8, 1);
+      mbar_init(bar_q_empty + i * 8, 1);
+      mbar_init(bar_s_full + i * 8, 1);
+      mbar_init(bar_s_free + i * 8, 8);   // four softmax warps from each CTA
+      mbar_init(bar_p_full + i * 8, 8);
+    }
     for (int s = 0; s < KST; ++s) {
       mbar_init(bar_k_full + s * 8, 1);
       mbar_init(bar_k_empty + s * 8, 1);
@@ -128,18 +151,13 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(bar_v_full + s * 8, 1);
       mbar_init(bar_v_empty + s * 8, 1);
     }
-    for (int i = 0; i < NBUF; ++i) {
-      mbar_init(bar_s_full + i * 8, 1);
-      mbar_init(bar_s_free + i * 8, 8);   // four softmax warps from each CTA
-      mbar_init(bar_p_full + i * 8, 8);
-    }
+    mbar_init(bar_o_free, 16);            // eight softmax warps from each CTA
     for (int i = 0; i < 8; ++i) mbar_init(bar_m_pub + i * 8, 1);
     misc[1] = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
     tma_prefetch_desc(&tmV);
-    tma_prefetch_desc(&tmO);
   }
   if (warp == 1) {
     tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(misc)), 512);
@@ -151,88 +169,110 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = misc[0];
   // Tensor Memory columns: S[2] (fp32, 128 each), P[2] (16-bit pairs, 64 each), O (fp32, 128)
-  auto S_COL = [](int b) { return (uint32_t)(b * 128); };
-  auto P_COL = [](int b) { return (uint32_t)(256 + b * 64); };
+  auto S_COL = [](uint32_t b) { return b * 128u; };
+  auto P_COL = [](uint32_t b) { return 256u + b * 64u; };
   constexpr uint32_t O_COL = 384;
 
   if (warp < 4) reg_dealloc<80>();   // 128 x 80 + 256 x 208 registers
   if (warp == 0) {
     // ---------------------------- TMA loader: Q and K ----------------------------
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0) {
       const uint32_t q_full_l = mapa_u32(bar_q_full, 0);
       const uint32_t k_full_l = mapa_u32(bar_k_full, 0);
-      if (leader) mbar_expect_tx(bar_q_full, 2 * L::TILE_BYTES);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) tma_load_3d_pair(sQ + h * HALF, &tmQ, q_full_l, h * 64, q0, bh);
-      uint32_t stage = 0, phase = 0;
-      for (int j = 0; j < n_kv; ++j) {
-        if (!mbar_wait(wctx, bar_k_empty + stage * 8, phase ^ 1, 10)) break;
-        const uint32_t k_dst = sK + stage * L::K_BYTES;
-        if (leader) mbar_expect_tx(bar_k_full + stage * 8, 2 * L::K_BYTES);
+      uint32_t stage = 0, phase = 0, n_item = 0;
+      bool ok = true;
+      for (int idx = first_item; idx < total_items && ok; idx += item_stride) {
+        const AltItem it = alt_item(p, idx, (int)rank, input_pos, n_total);
+        if (it.n_kv <= 0) continue;
+        const uint32_t qb = n_item & 1, qph = (n_item >> 1) & 1;
+        ++n_item;
+        if (!mbar_wait(wctx, bar_q_empty + qb * 8, qph ^ 1, 12)) break;
+        if (leader) mbar_expect_tx(bar_q_full + qb * 8, 2 * L::TILE_BYTES);
 #pragma unroll
         for (int h = 0; h < 2; ++h)
-          tma_load_3d_pair(k_dst + h * L::K_HALF, &tmK, k_full_l + stage * 8, h * 64,
-                           j * FA_BN + (int)rank * 64, kv_bh);
-        if (++stage == KST) { stage = 0; phase ^= 1; }
+          tma_load_3d_pair(sQ + qb * L::TILE_BYTES + h * HALF, &tmQ, q_full_l + qb * 8, h * 64, it.q0, it.bh);
+        for (int j = 0; j < it.n_kv; ++j) {
+          if (!mbar_wait(wctx, bar_k_empty + stage * 8, phase ^ 1, 10)) { ok = false; break; }
+          const uint32_t k_dst = sK + stage * L::K_BYTES;
+          if (leader) mbar_expect_tx(bar_k_full + stage * 8, 2 * L::K_BYTES);
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            tma_load_3d_pair(k_dst + h * L::K_HALF, &tmK, k_full_l + stage * 8, h * 64,
+                             j * FA_BN + (int)rank * 64, it.kv_bh);
+          if (++stage == KST) { stage = 0; phase ^= 1; }
+        }
       }
     }
   } else if (warp == 3) {
     // ------------------------------- TMA loader: V -------------------------------
-    if (lane == 0 && n_kv > 0) {
+    if (lane == 0) {
       const uint32_t v_full_l = mapa_u32(bar_v_full, 0);
       uint32_t stage = 0, phase = 0;
-      for (int j = 0; j < n_kv; ++j) {
-        if (!mbar_wait(wctx, bar_v_empty + stage * 8, phase ^ 1, 11)) break;
-        if (leader) mbar_expect_tx(bar_v_full + stage * 8, 2 * L::V_BYTES);
-        tma_load_3d_pair(sV + stage * L::V_BYTES, &tmV, v_full_l + stage * 8, (int)rank * 64, j * FA_BN, kv_bh);
-        if (++stage == VST) { stage = 0; phase ^= 1; }
+      bool ok = true;
+      for (int idx = first_item; idx < total_items && ok; idx += item_stride) {
+        const AltItem it = alt_item(p, idx, (int)rank, input_pos, n_total);
+        for (int j = 0; j < it.n_kv; ++j) {
+          if (!mbar_wait(wctx, bar_v_empty + stage * 8, phase ^ 1, 11)) { ok = false; break; }
+          if (leader) mbar_expect_tx(bar_v_full + stage * 8, 2 * L::V_BYTES);
+          tma_load_3d_pair(sV + stage * L::V_BYTES, &tmV, v_full_l + stage * 8, (int)rank * 64, j * FA_BN, it.kv_bh);
+          if (++stage == VST) { stage = 0; phase ^= 1; }
+        }
       }
     }
   } else if (warp == 1) {
     // ------------- S = Q K^T issuer (leader CTA only), runs ahead of the softmax -------------
-    // The two kinds of MMA come from two threads: issuing one tcgen05.mma costs the issuing thread
-    // about as long as a 256x128x16 MMA keeps the tensor pipe busy, so one thread alone cannot
-    // keep the pipe fed once waits and commits are added.
-    if (leader && lane == 0 && n_kv > 0) {
+    if (leader && lane == 0) {
       constexpr uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
       constexpr uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, 2 * FA_BM, FA_BN);
       const uint32_t s_full_peer = mapa_u32(bar_s_full, 1);
       const uint32_t k_empty_peer = mapa_u32(bar_k_empty, 1);
-      bool ok = mbar_wait(wctx, bar_q_full, 0, 21);
-      uint32_t ks = 0, kph = 0, sb = 0;
+      const uint32_t q_empty_peer = mapa_u32(bar_q_empty, 1);
+      uint32_t ks = 0, kph = 0, g = 0, n_item = 0;   // g: key tiles issued so far, over all items
+      bool ok = true;
 #ifdef B200TILE_TRACE
       long long qk_wait_k = 0, qk_wait_s = 0;
 #endif
-      for (int j = 0; j < n_kv && ok; ++j) {
+      for (int idx = first_item; idx < total_items && ok; idx += item_stride) {
+        const AltItem it = alt_item(p, idx, 0, input_pos, n_total);
+        if (it.n_kv <= 0) continue;
+        const uint32_t qb = n_item & 1, qph = (n_item >> 1) & 1;
+        ++n_item;
+        if (!mbar_wait(wctx, bar_q_full + qb * 8, qph, 21)) break;
+        const uint32_t q_addr = sQ + qb * L::TILE_BYTES;
+        for (int j = 0; j < it.n_kv; ++j, ++g) {
+          const uint32_t sb = g & 1;
 #ifdef B200TILE_TRACE
-        const long long c0 = clock64();
+          const long long c0 = clock64();
 #endif
-        if (!mbar_wait(wctx, bar_k_full + ks * 8, kph, 20)) break;
+          if (!mbar_wait(wctx, bar_k_full + ks * 8, kph, 20)) { ok = false; break; }
 #ifdef B200TILE_TRACE
-        const long long c1 = clock64();
-        qk_wait_k += c1 - c0;
+          const long long c1 = clock64();
+          qk_wait_k += c1 - c0;
 #endif
-        if (j >= NBUF) {
-          // the softmax warps of both CTAs have read S(j - NBUF) out of buffer sb
-          if (!mbar_wait(wctx, bar_s_free + sb * 8, (uint32_t)((j - NBUF) / NBUF) & 1u, 23)) break;
-        }
+          if (g >= 2) {
+            // the softmax warps of both CTAs have read S(g - 2) out of buffer sb
+            if (!mbar_wait(wctx, bar_s_free + sb * 8, ((g >> 1) - 1) & 1u, 23)) { ok = false; break; }
+          }
 #ifdef B200TILE_TRACE
-        qk_wait_s += clock64() - c1;
+          qk_wait_s += clock64() - c1;
 #endif
-        tc_fence_after_sync();
-        const uint32_t k_addr = sK + ks * L::K_BYTES;
+          tc_fence_after_sync();
+          const uint32_t k_addr = sK + ks * L::K_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint64_t a = make_smem_desc(sQ + (kk / 4) * HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
-          const uint64_t bd = make_smem_desc(k_addr + (kk / 4) * L::K_HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
-          umma_f16_ss_2cta(tmem_base + S_COL(sb), a, bd, idesc_qk, kk != 0);
+          for (int kk = 0; kk < D / 16; ++kk) {
+            const uint64_t a = make_smem_desc(q_addr + (kk / 4) * HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
+            const uint64_t bd = make_smem_desc(k_addr + (kk / 4) * L::K_HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
+            umma_f16_ss_2cta(tmem_base + S_COL(sb), a, bd, idesc_qk, kk != 0);
+          }
+          umma_commit_2cta(bar_s_full + sb * 8);
+          umma_commit_2cta(s_full_peer + sb * 8);
+          umma_commit_2cta(bar_k_empty + ks * 8);
+          umma_commit_2cta(k_empty_peer + ks * 8);
+          if (++ks == KST) { ks = 0; kph ^= 1; }
         }
-        umma_commit_2cta(bar_s_full + sb * 8);
-        umma_commit_2cta(s_full_peer + sb * 8);
-        umma_commit_2cta(bar_k_empty + ks * 8);
-        umma_commit_2cta(k_empty_peer + ks * 8);
-        if (++ks == KST) { ks = 0; kph ^= 1; }
-        if (++sb == NBUF) sb = 0;
+        // every Q.K^T of the item has been issued: its Q tile is free once they retire
+        umma_commit_2cta(bar_q_empty + qb * 8);
+        umma_commit_2cta(q_empty_peer + qb * 8);
       }
 #ifdef B200TILE_TRACE
       misc[2] = (uint32_t)qk_wait_k;   // read by the P.V thread, which finishes later
@@ -241,38 +281,45 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 2) {
     // ------------------------- O += P V issuer (leader CTA only) -------------------------
-    if (leader && lane == 0 && n_kv > 0) {
+    if (leader && lane == 0) {
       constexpr uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
       constexpr uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, 2 * FA_BM, D);
       const uint32_t v_empty_peer = mapa_u32(bar_v_empty, 1);
       bool ok = true;
       B200_TR_DECL(7);
-      uint32_t vs = 0, vph = 0, pb = 0, pph = 0;
-      for (int j = 0; j < n_kv && ok; ++j) {
-        B200_TR_COUNT(6);
-        B200_TR_BEGIN();
-        if (!mbar_wait(wctx, bar_v_full + vs * 8, vph, 22)) { ok = false; break; }
-        B200_TR_END(0);
-        B200_TR_BEGIN();
-        if (!mbar_wait(wctx, bar_p_full + pb * 8, pph, 24)) { ok = false; break; }
-        tc_fence_after_sync();
-        B200_TR_END(1);
-        B200_TR_BEGIN();
-        const uint32_t v_addr = sV + vs * L::V_BYTES;
+      uint32_t vs = 0, vph = 0, g = 0, n_item = 0;
+      for (int idx = first_item; idx < total_items && ok; idx += item_stride) {
+        const AltItem it = alt_item(p, idx, 0, input_pos, n_total);
+        if (it.n_kv <= 0) continue;
+        // the previous item's accumulator has been read out by all softmax warps of both CTAs
+        if (n_item > 0 && !mbar_wait(wctx, bar_o_free, (n_item - 1) & 1u, 25)) break;
+        ++n_item;
+        for (int j = 0; j < it.n_kv; ++j, ++g) {
+          const uint32_t pb = g & 1, pph = (g >> 1) & 1;
+          B200_TR_COUNT(6);
+          B200_TR_BEGIN();
+          if (!mbar_wait(wctx, bar_v_full + vs * 8, vph, 22)) { ok = false; break; }
+          B200_TR_END(0);
+          B200_TR_BEGIN();
+          if (!mbar_wait(wctx, bar_p_full + pb * 8, pph, 24)) { ok = false; break; }
+          tc_fence_after_sync();
+          B200_TR_END(1);
+          B200_TR_BEGIN();
+          const uint32_t v_addr = sV + vs * L::V_BYTES;
 #pragma unroll
-        for (int kk = 0; kk < FA_BN / 16; ++kk) {
-          // V is the N-major B operand; each CTA holds one 64-column block, 16 key rows per step
-          const uint64_t bd = make_smem_desc(v_addr + kk * 2048, HALF, 1024, SWZ_128B);
-          umma_f16_ts_2cta(tmem_base + O_COL, tmem_base + P_COL(pb) + kk * 8, bd, idesc_pv, j > 0 || kk != 0);
+          for (int kk = 0; kk < FA_BN / 16; ++kk) {
+            // V is the N-major B operand; each CTA holds one 64-column block, 16 key rows per step
+            const uint64_t bd = make_smem_desc(v_addr + kk * 2048, HALF, 1024, SWZ_128B);
+            umma_f16_ts_2cta(tmem_base + O_COL, tmem_base + P_COL(pb) + kk * 8, bd, idesc_pv, j > 0 || kk != 0);
+          }
+          B200_TR_END(2);
+          // V(g) is free in both CTAs; the same signal tells the softmax warps that O holds key tile g
+          B200_TR_BEGIN();
+          umma_commit_2cta(bar_v_empty + vs * 8);
+          umma_commit_2cta(v_empty_peer + vs * 8);
+          B200_TR_END(5);
+          if (++vs == VST) { vs = 0; vph ^= 1; }
         }
-        B200_TR_END(2);
-        // V(j) is free in both CTAs; the same signal tells the softmax warps that O holds key tile j
-        B200_TR_BEGIN();
-        umma_commit_2cta(bar_v_empty + vs * 8);
-        umma_commit_2cta(v_empty_peer + vs * 8);
-        B200_TR_END(5);
-        if (++vs == VST) { vs = 0; vph ^= 1; }
-        if (++pb == NBUF) { pb = 0; pph ^= 1; }
       }
 #ifdef B200TILE_TRACE
       tr_[3] = misc[2];
@@ -283,167 +330,176 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp >= 4) {
     // -------------------------------- softmax ----------------------------------
     reg_alloc<FA_SOFTMAX_REGS>();
-    const int w = (warp - 4) >> 2;          // warpgroup: key tiles j = w, w + 2, ...
+    const uint32_t w = (uint32_t)(warp - 4) >> 2;   // warpgroup: key tiles with (running index & 1) == w
     const int q = warp & 3;
-    const int row = q * 32 + lane;          // row inside the tile == TMEM lane
-    const int row_g = q0 + row;             // query position
+    const int row = q * 32 + lane;                  // row inside the tile == TMEM lane
     const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+    const uint32_t tS = lane_base + S_COL(w);
+    const uint32_t tP = lane_base + P_COL(w);
     const uint32_t tO = lane_base + O_COL;
-    const uint32_t my_pub = bar_m_pub + (uint32_t)(w * 4 + q) * 8;
-    const uint32_t other_pub = bar_m_pub + (uint32_t)((1 - w) * 4 + q) * 8;
+    const uint32_t my_pub = bar_m_pub + (w * 4 + (uint32_t)q) * 8;
+    const uint32_t other_pub = bar_m_pub + ((1 - w) * 4 + (uint32_t)q) * 8;
+    const uint32_t s_free_l = mapa_u32(bar_s_free + w * 8, 0);
+    const uint32_t p_full_l = mapa_u32(bar_p_full + w * 8, 0);
+    const uint32_t o_free_l = mapa_u32(bar_o_free, 0);
     const float scale = p.scale_log2;
-    float m_seen = -CUDART_INF_F, l_part = 0.0f;   // this warpgroup's row sum, relative to m_seen
     bool ok = true;
+    uint32_t g0 = 0;                                // key tiles of the items before this one
     B200_TR_DECL(7);
-    for (int j = w; j < n_kv && ok; j += 2) {
-      const int b = j % NBUF;
-      const uint32_t tS = lane_base + S_COL(b);
-      const uint32_t tP = lane_base + P_COL(b);
-      B200_TR_COUNT(6);
-      B200_TR_BEGIN();
-      if (!mbar_wait(wctx, bar_s_full + b * 8, (uint32_t)(j / NBUF) & 1u, 30)) { ok = false; break; }
-      tc_fence_after_sync();
-      B200_TR_END(0);
-      B200_TR_BEGIN();
-      // the whole score row lives in registers: one TMEM read per element
-      uint32_t v[FA_BN];
-#pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c)
-        tmem_ld_32x32b_x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
-      // last key column this row may see inside this tile (>= 127: nothing masked)
-      int lim = p.kv_len - 1 - j * FA_BN;
-      if (p.causal) {
-        const int c = row_g + input_pos - j * FA_BN;
-        lim = c < lim ? c : lim;
-      }
-      const bool masked_tile = __any_sync(0xffffffffu, lim < FA_BN - 1);
-      tmem_wait_ld();
-      // the scores are in registers: the buffer can take S(j + 2) while this tile is worked on
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_s_free + b * 8, 0));
-      B200_TR_END(1);
-      B200_TR_BEGIN();
-      if (masked_tile) {
-#pragma unroll
-        for (int i = 0; i < FA_BN; ++i)
-          if (i > lim) v[i] = 0xff800000u;  // -inf
-      }
-      // row maximum: four independent chains
-      float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-      for (int i = 0; i < FA_BN; i += 8) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u)
-          mx[u] = max3(mx[u], __uint_as_float(v[i + 2 * u]), __uint_as_float(v[i + 2 * u + 1]));
-      }
-      const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale;
-      // reference maximum of this tile: the partner's reference unless the row maximum outgrew it
-      float m_new, alpha = 1.0f;
-      bool need = false;
-      if (j == 0) {
-        m_new = m_tile == -CUDART_INF_F ? 0.0f : m_tile;  // fully masked row: keep exp2 arguments finite
-      } else {
-        if (!mbar_wait(wctx, other_pub, (uint32_t)((j - 1) >> 1) & 1u, 32)) { ok = false; break; }
-        const float m_old = m_ref[row];
-        m_new = m_old;
-        if (m_tile - m_old > FA_RESCALE_THRESHOLD) {
-          need = true;
-          m_new = m_tile;
-          alpha = ex2_approx(m_old - m_new);
-        }
-      }
-      m_ref[row] = m_new;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(my_pub);
-      if (m_new != m_seen) {
-        l_part *= ex2_approx(m_seen - m_new);
-        m_seen = m_new;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, need)) {
-        // O must hold key tile j-1 before it is rescaled; P.V of tile j cannot start before this
-        // warp has handed over P(j), and the partner's rescale for tile j+1 waits for that P.V
-        const int jp = j - 1;
-        if (!mbar_wait(wctx, bar_v_empty + (jp % VST) * 8, (uint32_t)(jp / VST) & 1u, 33)) { ok = false; break; }
+    for (int idx = first_item; idx < total_items; idx += item_stride) {
+      const AltItem it = alt_item(p, idx, (int)rank, input_pos, n_total);
+      if (it.n_kv <= 0) continue;
+      const int row_g = it.q0 + row;                // query position
+      float m_seen = -CUDART_INF_F, l_part = 0.0f;  // this warpgroup's row sum, relative to m_seen
+      for (int j = (int)((g0 ^ w) & 1u); j < it.n_kv && ok; j += 2) {
+        const uint32_t g = g0 + (uint32_t)j;
+        B200_TR_COUNT(6);
+        B200_TR_BEGIN();
+        if (!mbar_wait(wctx, bar_s_full + w * 8, (g >> 1) & 1u, 30)) { ok = false; break; }
         tc_fence_after_sync();
+        B200_TR_END(0);
+        B200_TR_BEGIN();
+        // the whole score row lives in registers: one TMEM read per element
+        uint32_t v[FA_BN];
+#pragma unroll
+        for (int c = 0; c < FA_BN / 32; ++c)
+          tmem_ld_32x32b_x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+        // last key column this row may see inside this tile (>= 127: nothing masked)
+        int lim = p.kv_len - 1 - j * FA_BN;
+        if (p.causal) {
+          const int c = row_g + input_pos - j * FA_BN;
+          lim = c < lim ? c : lim;
+        }
+        const bool masked_tile = __any_sync(0xffffffffu, lim < FA_BN - 1);
+        tmem_wait_ld();
+        // the scores are in registers: the buffer can take S(g + 2) while this tile is worked on
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_addr_cta_release(s_free_l);
+        B200_TR_END(1);
+        B200_TR_BEGIN();
+        if (masked_tile) {
+#pragma unroll
+          for (int i = 0; i < FA_BN; ++i)
+            if (i > lim) v[i] = 0xff800000u;  // -inf
+        }
+        // row maximum: four independent chains
+        float mx[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+        for (int i = 0; i < FA_BN; i += 8) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            mx[u] = max3(mx[u], __uint_as_float(v[i + 2 * u]), __uint_as_float(v[i + 2 * u + 1]));
+        }
+        const float m_tile = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale;
+        // reference maximum of this tile: the partner's reference unless the row maximum outgrew it
+        float m_new, alpha = 1.0f;
+        bool need = false;
+        if (j == 0) {
+          m_new = m_tile == -CUDART_INF_F ? 0.0f : m_tile;  // fully masked row: keep exp2 arguments finite
+        } else {
+          if (!mbar_wait(wctx, other_pub, ((g - 1) >> 1) & 1u, 32)) { ok = false; break; }
+          const float m_old = m_ref[row];
+          m_new = m_old;
+          if (m_tile - m_old > FA_RESCALE_THRESHOLD) {
+            need = true;
+            m_new = m_tile;
+            alpha = ex2_approx(m_old - m_new);
+          }
+        }
+        m_ref[row] = m_new;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(my_pub);
+        if (m_new != m_seen) {
+          l_part *= ex2_approx(m_seen - m_new);
+          m_seen = m_new;
+        }
+        if (j > 0 && __any_sync(0xffffffffu, need)) {
+          // O must hold key tile g-1 before it is rescaled; P.V of tile g cannot start before this
+          // warp has handed over P(g), and the partner's rescale for tile g+1 waits for that P.V
+          const uint32_t gp = g - 1;
+          if (!mbar_wait(wctx, bar_v_empty + (gp % VST) * 8, (gp / VST) & 1u, 33)) { ok = false; break; }
+          tc_fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(tO + c * 32, o);
-          tmem_wait_ld();
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tO + c * 32, o);
+            tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32b_x32(tO + c * 32, o);
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x32(tO + c * 32, o);
+          }
         }
-      }
-      // probabilities: exp2(s*scale - m); masked entries are exp2(-inf) = 0
-      B200_TR_END(2);
-      B200_TR_BEGIN();
-      if (j >= NBUF) {
-        // P(j - 2) must have been consumed before its buffer is overwritten
-        const int jp = j - NBUF;
-        if (!mbar_wait(wctx, bar_v_empty + (jp % VST) * 8, (uint32_t)(jp / VST) & 1u, 34)) { ok = false; break; }
-        tc_fence_after_sync();
-      }
-      const float neg_m = -m_new;
-      const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(neg_m, neg_m);
-      uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed (even, odd) partial sums
-#pragma unroll
-      for (int c = 0; c < FA_BN / 32; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const uint64_t x2 = fma2(pack2(__uint_as_float(v[c * 32 + 2 * i]),
-                                         __uint_as_float(v[c * 32 + 2 * i + 1])), scale2, negm2);
-          float xa, xb;
-          unpack2(x2, xa, xb);
-          const float a = ex2_approx(xa), bb = ex2_approx(xb);
-          ls2[i & 3] = add2(ls2[i & 3], pack2(a, bb));
-          pk[i] = OUT_F16 ? pack_f16x2(a, bb) : pack_bf16x2(a, bb);
+        B200_TR_END(2);
+        B200_TR_BEGIN();
+        if (g >= 2) {
+          // P(g - 2) must have been consumed before its buffer is overwritten
+          const uint32_t gp = g - 2;
+          if (!mbar_wait(wctx, bar_v_empty + (gp % VST) * 8, (gp / VST) & 1u, 34)) { ok = false; break; }
+          tc_fence_after_sync();
         }
-        tmem_st_32x32b_x16(tP + c * 16, pk);
-      }
-      float ls[4];
-      {
-        const uint64_t s01 = add2(ls2[0], ls2[1]), s23 = add2(ls2[2], ls2[3]);
-        unpack2(s01, ls[0], ls[1]);
-        unpack2(s23, ls[2], ls[3]);
-      }
-      l_part += (ls[0] + ls[1]) + (ls[2] + ls[3]);
-      B200_TR_END(3);
-      B200_TR_BEGIN();
-      tmem_wait_st();
-      B200_TR_END(4);
-      B200_TR_BEGIN();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_p_full + b * 8, 0));
-      B200_TR_END(5);
-    }
-    B200_TR_FLUSH(g_trace_fmha_alt + 10, 7, blockIdx.x == 14 && warp == 4 && lane == 0);
-    // ------------------------------- epilogue ----------------------------------
-    // merge the two warpgroups' row sums under the final reference
-    l_part_sm[w * 128 + row] = l_part;
-    m_part_sm[w * 128 + row] = m_seen;
-    named_bar_sync(1, 256);
-    if (n_kv > 0 && ok) {
-      const int jl = n_kv - 1;
-      if (mbar_wait(wctx, bar_v_empty + (jl % VST) * 8, (uint32_t)(jl / VST) & 1u, 31)) {
-        tc_fence_after_sync();
-        const float m_fin = m_ref[row];
-        const float l_run = l_part_sm[row] * ex2_approx(m_part_sm[row] - m_fin) +
-                            l_part_sm[128 + row] * ex2_approx(m_part_sm[128 + row] - m_fin);
-        const float inv_l = 1.0f / fmaxf(l_run, 1e-8f);  // attention.rs:385-390
-        // Q's shared memory is free now (all S MMAs retired): warpgroup w stages value columns
-        // [64w, 64w + 64) there and each warp stores its 32 rows
-        const uint32_t half_base = sQ + (uint32_t)w * HALF + (uint32_t)row * 128;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(tO + w * 64 + c * 32, o);
-          tmem_wait_ld();
+        // probabilities: exp2(s*scale - m); masked entries are exp2(-inf) = 0
+        const float neg_m = -m_new;
+        const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(neg_m, neg_m);
+        uint64_t ls2[4] = {0ull, 0ull, 0ull, 0ull};  // four packed (even, odd) partial sums
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
+        for (int c = 0; c < FA_BN / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const uint64_t x2 = fma2(pack2(__uint_as_float(v[c * 32 + 2 * i]),
+                                           __uint_as_float(v[c * 32 + 2 * i + 1])), scale2, negm2);
+            float xa, xb;
+            unpack2(x2, xa, xb);
+            const float a = ex2_approx(xa), bb = ex2_approx(xb);
+            ls2[i & 3] = add2(ls2[i & 3], pack2(a, bb));
+            pk[i] = OUT_F16 ? pack_f16x2(a, bb) : pack_bf16x2(a, bb);
+          }
+          tmem_st_32x32b_x16(tP + c * 16, pk);
+        }
+        float ls[4];
+        {
+          const uint64_t s01 = add2(ls2[0], ls2[1]), s23 = add2(ls2[2], ls2[3]);
+          unpack2(s01, ls[0], ls[1]);
+          unpack2(s23, ls[2], ls[3]);
+        }
+        l_part += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        B200_TR_END(3);
+        B200_TR_BEGIN();
+        tmem_wait_st();
+        B200_TR_END(4);
+        B200_TR_BEGIN();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_addr_cta_release(p_full_l);
+        B200_TR_END(5);
+      }
+      // ---- end of the item: merge the two warpgroups' row sums under the final reference ----
+      l_part_sm[w * 128 + row] = l_part;
+      m_part_sm[w * 128 + row] = m_seen;
+      named_bar_sync(1, 256);
+      const float m_fin = m_ref[row];
+      const float l_run = l_part_sm[row] * ex2_approx(m_part_sm[row] - m_fin) +
+                          l_part_sm[128 + row] * ex2_approx(m_part_sm[128 + row] - m_fin);
+      named_bar_sync(1, 256);   // the next item may overwrite the reference and the partial sums
+      const uint32_t g_last = g0 + (uint32_t)it.n_kv - 1;
+      g0 += (uint32_t)it.n_kv;
+      if (ok && mbar_wait(wctx, bar_v_empty + (g_last % VST) * 8, (g_last / VST) & 1u, 31)) {
+        tc_fence_after_sync();
+        // warpgroup w takes value columns [64w, 64w + 64) of its 32 rows per warp
+        uint32_t o[64];
+        tmem_ld_32x32b_x32(tO + w * 64, *reinterpret_cast<uint32_t(*)[32]>(&o[0]));
+        tmem_ld_32x32b_x32(tO + w * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&o[32]));
+        tmem_wait_ld();
+        // the accumulator is in registers: the next item's first P.V may overwrite it
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_addr_cta_release(o_free_l);
+        if (row_g < p.q_len) {
+          const float inv_l = 1.0f / fmaxf(l_run, 1e-8f);  // attention.rs:385-390
+          uint16_t* dst = out + (long long)it.bh * o_stride_bh + (long long)row_g * o_stride_row + w * 64;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
             uint32_t wd[4];
 #pragma unroll
             for (int x = 0; x < 4; ++x) {
@@ -451,22 +507,14 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               const float hi = __uint_as_float(o[e * 8 + 2 * x + 1]) * inv_l;
               wd[x] = OUT_F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
             }
-            const uint32_t chunk = (uint32_t)(c * 4 + e);
-            const uint32_t dst = half_base + ((chunk ^ (uint32_t)(lane & 7)) << 4);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(wd[0]),
-                         "r"(wd[1]), "r"(wd[2]), "r"(wd[3])
-                         : "memory");
+            *reinterpret_cast<uint4*>(dst + e * 8) = make_uint4(wd[0], wd[1], wd[2], wd[3]);
           }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0 && q0 + q * 32 < p.q_len) {   // the pair may reach past the last query row
-          tma_store_3d(&tmO, sQ + (uint32_t)w * HALF + (uint32_t)(q * 32) * 128, w * 64, q0 + q * 32, bh);
-          tma_store_commit();
-          tma_store_wait_all<0>();
-        }
+      } else {
+        ok = false;
       }
     }
+    B200_TR_FLUSH(g_trace_fmha_alt + 10, 7, blockIdx.x == 14 && warp == 4 && lane == 0);
   }
 
   tc_fence_before_sync();
@@ -491,7 +539,7 @@ static int launch_fmha_alt(const void* q, const void* k, const void* v, void* o,
   const b200h::DeviceInfo* di = b200h::device_info();
   if (!di) return B200_ERR_CUDA;
   const CUtensorMapDataType dt = OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  CUtensorMap tmQ, tmK, tmV, tmO;
+  CUtensorMap tmQ, tmK, tmV;
   int rc;
   const uint64_t bh = (uint64_t)batch * heads, bhkv = (uint64_t)batch * heads_kv;
   if ((rc = b200h::encode_tmap_3d(&tmQ, dt, 2, q, D, q_len, bh, qs[1] * 2, qs[0] * 2, 64, FA_BM, 1,
@@ -504,9 +552,9 @@ static int launch_fmha_alt(const void* q, const void* k, const void* v, void* o,
   if ((rc = b200h::encode_tmap_3d(&tmV, dt, 2, v, D, kv_len, bhkv, vs[1] * 2, vs[0] * 2, 64, FA_BN, 1,
                                   CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  if ((rc = b200h::encode_tmap_3d(&tmO, dt, 2, o, D, q_len, bh, os[1] * 2, os[0] * 2, 64, 32, 1,
-                                  CU_TENSOR_MAP_SWIZZLE_128B)))
-    return rc;
+  // the output is written with 16-byte stores straight from registers
+  if ((reinterpret_cast<uintptr_t>(o) & 15) || (os[0] & 7) || (os[1] & 7))
+    return b200h::set_error(B200_ERR_ALIGN, "fmha: output base and pitches must be multiples of 16 bytes");
   auto kern = fmha_fwd_alt_kernel<OUT_F16>;
   static bool attr_done[64] = {};
   if (!attr_done[di->ordinal]) {
@@ -526,9 +574,13 @@ static int launch_fmha_alt(const void* q, const void* k, const void* v, void* o,
   p.pos_ptr = pos_ptr;
   p.head_group = 8;
   p.scale_log2 = qk_scale * 1.4426950408889634f;
-  const long long ctas = 2ll * p.num_q_pairs * p.bh_total;
-  if (ctas > 0x7fffffffLL) return b200h::set_error(B200_ERR_INVALID, "fmha: grid too large");
-  kern<<<(unsigned)ctas, FA_THREADS, L::TOTAL, stream>>>(tmQ, tmK, tmV, tmO, p, di->status);
+  const long long items = (long long)p.num_q_pairs * p.bh_total;
+  if (items > 0x3fffffffLL) return b200h::set_error(B200_ERR_INVALID, "fmha: grid too large");
+  // one CTA pair per two SMs, each walking items pair, pair + pairs, ...
+  const long long pairs = items < di->sm_count / 2 ? items : di->sm_count / 2;
+  if (pairs <= 0) return B200_OK;
+  kern<<<(unsigned)(2 * pairs), FA_THREADS, L::TOTAL, stream>>>(tmQ, tmK, tmV, static_cast<uint16_t*>(o),
+                                                                (long long)os[0], (long long)os[1], p, di->status);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
