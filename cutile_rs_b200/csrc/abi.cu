@@ -26,10 +26,6 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
                            const int64_t* os, float qk_scale, int causal, int input_pos,
                            const uint32_t* pos_ptr, cudaStream_t stream);
 
-int b200_fmha_fwd_pair_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
-                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
-                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
-                                const uint32_t* pos_ptr, cudaStream_t stream);
 int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
@@ -37,9 +33,9 @@ int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const vo
 
 #ifdef B200TILE_TRACE
 int b200_trace_read_fmha_alt(long long* out);
+int b200_trace_read_fmha_alt_t(long long* out);
 int b200_trace_read_gemm_pair(long long* out);
 int b200_trace_read_fmha(long long* out);
-int b200_trace_read_fmha_pair(long long* out);
 int b200_trace_read_fp4(long long* out);
 #endif
 
@@ -261,21 +257,18 @@ static int fmha_fwd_common(const char* dtype, const void* q, const void* k, cons
     dt = 1;
   else
     return set_error(B200TILE_ERR_UNSUPPORTED, "fmha: unsupported element type '%s'", dtype);
-  // Two configurations for head_dim 128: one CTA per 256 query rows (default, the faster one as
-  // measured) and a CTA pair per 512 rows with cta_group::2 MMAs, chosen with
-  // CompileOptions::num_cta_in_cga = 2 on the generic launch or B200TILE_FMHA_PAIR=1.
-  static const int env_pair = [] {
+  // Two configurations for head_dim 128: one CTA per 256 query rows with S and P sharing their
+  // Tensor Memory columns (default), and persistent CTA pairs with cta_group::2 MMAs, separate S and
+  // P buffers and two alternating softmax warpgroups, chosen with CompileOptions::num_cta_in_cga = 2
+  // on the generic launch or B200TILE_FMHA_PAIR=1.
+  static const bool env_pair = [] {
     const char* e = getenv("B200TILE_FMHA_PAIR");
-    return e ? e[0] - '0' : 0;
+    return e && e[0] != '0';
   }();
-  if (head_dim == 128 && cluster == 0 && env_pair == 2)
+  if (head_dim == 128 && (cluster == 2 || (cluster == 0 && env_pair)))
     return b200_fmha_fwd_alt_dispatch(dt, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, q_strides,
                                       k_strides, v_strides, o_strides, qk_scale, causal ? 1 : 0, input_pos,
                                       pos_ptr, static_cast<cudaStream_t>(cu_stream));
-  if (head_dim == 128 && (cluster == 2 || (cluster == 0 && env_pair == 1)))
-    return b200_fmha_fwd_pair_dispatch(dt, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, q_strides,
-                                       k_strides, v_strides, o_strides, qk_scale, causal ? 1 : 0, input_pos,
-                                       pos_ptr, static_cast<cudaStream_t>(cu_stream));
   return b200_fmha_fwd_dispatch(dt, head_dim, q, k, v, out, batch, heads, heads_kv, q_len, kv_len,
                                 q_strides, k_strides, v_strides, o_strides, qk_scale,
                                 causal ? 1 : 0, input_pos, pos_ptr, static_cast<cudaStream_t>(cu_stream));
@@ -1169,13 +1162,13 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
 
 #ifdef B200TILE_TRACE
 // Diagnostic builds only: copies the cycle counters of one traced kernel ("gemm_pair", "fmha",
-// "fmha_pair") into out[20]; see csrc/trace.cuh.
+// "fmha_alt", "fmha_alt_t", "block_scaled") into out[20]; see csrc/trace.cuh.
 B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!which || !out) return B200TILE_ERR_INVALID;
   for (int i = 0; i < 20; ++i) out[i] = 0;
   if (!strcmp(which, "gemm_pair")) return b200_trace_read_gemm_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha")) return b200_trace_read_fmha(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
-  if (!strcmp(which, "fmha_pair")) return b200_trace_read_fmha_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "fmha_alt_t")) return b200_trace_read_fmha_alt_t(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha_alt")) return b200_trace_read_fmha_alt(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "block_scaled")) return b200_trace_read_fp4(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   return B200TILE_ERR_UNSUPPORTED;

@@ -39,6 +39,9 @@ namespace b200 {
 // [8] the total span in ns; softmax lane 0 of warpgroup 0 from [10]: S wait, TMEM load, max +
 // reference hand-off, exp2 loop, store wait, P hand-off, key tiles, total.
 __device__ long long g_trace_fmha_alt[20];
+// Time line of the same CTA: for warpgroup 0 then warpgroup 1, (scores loaded, P handed over) of their
+// tiles number 10..14, as SM clock values.
+__device__ long long g_trace_fmha_alt_t[20];
 #endif
 
 struct FmhaAltSmem {
@@ -372,6 +375,10 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         const bool masked_tile = __any_sync(0xffffffffu, lim < FA_BN - 1);
         tmem_wait_ld();
+#ifdef B200TILE_TRACE
+        if (blockIdx.x == 14 && q == 0 && lane == 0 && (g >> 1) >= 10 && (g >> 1) < 15)
+          g_trace_fmha_alt_t[w * 10 + ((g >> 1) - 10) * 2] = clock64();
+#endif
         // the scores are in registers: the buffer can take S(g + 2) while this tile is worked on
         tc_fence_before_sync();
         __syncwarp();
@@ -472,6 +479,10 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster_addr_cta_release(p_full_l);
+#ifdef B200TILE_TRACE
+        if (blockIdx.x == 14 && q == 0 && lane == 0 && (g >> 1) >= 10 && (g >> 1) < 15)
+          g_trace_fmha_alt_t[w * 10 + ((g >> 1) - 10) * 2 + 1] = clock64();
+#endif
         B200_TR_END(5);
       }
       // ---- end of the item: merge the two warpgroups' row sums under the final reference ----
@@ -602,5 +613,8 @@ int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const vo
 #ifdef B200TILE_TRACE
 int b200_trace_read_fmha_alt(long long* out) {
   return cudaMemcpyFromSymbol(out, b200::g_trace_fmha_alt, 20 * sizeof(long long)) != cudaSuccess;
+}
+int b200_trace_read_fmha_alt_t(long long* out) {
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fmha_alt_t, 20 * sizeof(long long)) != cudaSuccess;
 }
 #endif

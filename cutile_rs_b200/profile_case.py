@@ -131,7 +131,7 @@ def _print_trace(lib, args) -> None:
     if not hasattr(lib, "b200tile_trace_read"):
         raise SystemExit("--trace needs the diagnostic build (see the module docstring)")
     out = (ctypes.c_longlong * 20)()
-    which = {"gemm": b"gemm_pair", "fmha": {0: b"fmha", 1: b"fmha_pair", 2: b"fmha_alt"}[args.pair],
+    which = {"gemm": b"gemm_pair", "fmha": b"fmha_alt" if args.pair else b"fmha",
              "nvfp4": b"block_scaled"}.get(args.kernel)
     if which is None or lib.b200tile_trace_read(which, out):
         raise SystemExit("no trace for this kernel")
@@ -156,10 +156,18 @@ def _print_trace(lib, args) -> None:
     else:
         n, m = max(v[6], 1), max(v[16], 1)
         names = ["K/V waits", "P waits", "P.V issue", "Q.K issue", "S commits", "release commits"]
-        if args.pair == 2:
+        if args.pair:
             names = ["V waits", "P waits", "P.V issue", "K waits (Q.K thread)", "free-S waits (Q.K thread)", "release commits"]
         print("MMA thread per key tile (both query tiles): " +
               ", ".join(f"{nm} {v[i] / n:.0f}" for i, nm in enumerate(names)) + f"; total {v[7] / n:.0f} ({n} key tiles); SM clock inside the kernel {1e3 * v[7] / max(v[8], 1):.0f} MHz")
+        if args.pair:
+            t = (ctypes.c_longlong * 20)()
+            if lib.b200tile_trace_read(b"fmha_alt_t", t) == 0:
+                t = list(t)
+                t0 = min(x for x in t if x > 0)
+                for wg in range(2):
+                    print(f"warpgroup {wg} tiles 10..14 (scores loaded, P handed over), cycles: " +
+                          " ".join(f"({t[wg * 10 + 2 * i] - t0}, {t[wg * 10 + 2 * i + 1] - t0})" for i in range(5)))
         names = ["S wait", "TMEM load", "max+rescale", "exp2 loop", "store wait", "hand-off"]
         print("softmax lane per key tile: " + ", ".join(f"{nm} {v[10 + i] / m:.0f}" for i, nm in enumerate(names)) +
               f"; total {v[17] / m:.0f}")

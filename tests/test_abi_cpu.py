@@ -56,7 +56,7 @@ def test_query_configs_lists_the_fixed_table():
     n = lib.b200tile_query_configs(b"gemm", b"bf16", arr, 8)
     assert n >= 2 and (arr[0].bm, arr[0].bn, arr[0].bk) == (128, 256, 64)
     assert lib.b200tile_query_configs(b"gemm", b"f32", arr, 8) == 1
-    assert lib.b200tile_query_configs(b"fmha", b"bf16", arr, 8) == 2   # one CTA per 256 rows; CTA pair per 512 rows
+    assert lib.b200tile_query_configs(b"fmha", b"bf16", arr, 8) == 2   # one CTA per 256 rows; persistent CTA pairs, 256 rows per item
     assert (arr[0].num_cta_in_cga, arr[1].num_cta_in_cga) == (1, 2)
     assert lib.b200tile_query_configs(b"gemm", b"i4", arr, 8) == 0
     assert lib.b200tile_query_configs(b"unknown", b"bf16", arr, 8) == 0

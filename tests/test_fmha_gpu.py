@@ -148,12 +148,15 @@ def test_device_side_position_equals_host_side(b200):
         assert torch.equal(got, want)
 
 
-@pytest.mark.parametrize("s,causal", [(640, True), (300, False), (1024, True)])
-def test_cta_pair_configuration(b200, oracle, s, causal):
-    """`CompileOptions(num_cta_in_cga=2)` selects the kernel that shares every K/V tile between the two
-    CTAs of a cluster (512 query rows per cluster); ragged lengths leave query tiles of the cluster
-    partly or wholly past the end."""
-    b, h, hkv, d = 1, 4, 2, 128
+@pytest.mark.parametrize("b,h,s,causal", [(1, 4, 640, True), (1, 4, 300, False), (1, 4, 1024, True),
+                                          (4, 16, 640, True), (4, 16, 640, False), (2, 32, 1152, True)])
+def test_cta_pair_configuration(b200, oracle, b, h, s, causal):
+    """`CompileOptions(num_cta_in_cga=2)` selects the persistent kernel whose CTA pairs share every K/V
+    tile (256 query rows per work item).  Ragged lengths leave the second CTA's query tile partly or
+    wholly past the end; the larger cases give every pair several items with odd and even key-tile
+    counts, so that the alternating softmax warpgroups, the rings and the accumulator hand-over run on
+    across items."""
+    hkv, d = h // 2, 128
     q, k, v = workloads.fmha_inputs(b, h, s, d, h_kv=hkv, config_index=300 + s)
     qd, kd, vd = (api.copy_host_to_device(t) for t in (q, k, v))
     out = api.zeros([b * h, s, d], "bf16").partition([1, 128, d])
