@@ -366,7 +366,30 @@ def run_gpu_arm(args):
             extra["fmha_fwd_causal" if causal else "fmha_fwd_noncausal"] = {
                 "tflops": ftf, "tflops_per_gpu": ftf / world, "ms": fms,
                 "config": f"bf16 b{B_} h{H_} s{S_} d{D_}, (b*h) split over {world} GPU(s)"}
-        del q, kk, v, o
+        # the same non-causal shape through the generated-launcher mirror with the CTA-pair configuration
+        # (CompileOptions(num_cta_in_cga=2): persistent pairs, alternating softmax warpgroups)
+        qd, kd, vd = (api.from_torch(t_.view(1, nb, S_, D_)) for t_ in (q, kk, v))
+        od = api.from_torch(o).partition([1, 128, D_])
+        fopts = launch.CompileOptions(num_cta_in_cga=2)
+
+        def pstep():
+            nonlocal od
+            (od, *_r) = launch.fmha(od, qd, kd, vd, 1.0 / math.sqrt(D_), 0, 1, causal=False) \
+                .compile_options(fopts).async_on(stream)
+        for _ in range(3):
+            pstep()
+        barrier()
+        e0.record(stream)
+        for _ in range(10):
+            pstep()
+        e1.record(stream)
+        barrier()
+        fms = sharding.max_over_ranks(e0.elapsed_time(e1), dev) / 10
+        ftf = workloads.fmha_flops(B_, H_, S_, D_, False) / (fms * 1e-3) / 1e12
+        extra["fmha_fwd_noncausal_cta_pairs"] = {
+            "tflops": ftf, "tflops_per_gpu": ftf / world, "ms": fms,
+            "config": "same shape, CompileOptions(num_cta_in_cga=2), through the launcher"}
+        del q, kk, v, o, qd, kd, vd, od
 
         # ---- block-scaled GEMMs (configs 3 and 4), weight rows (N) split over the ranks ----
         from cutile_rs_b200 import quant
