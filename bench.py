@@ -572,6 +572,31 @@ def run_gpu_arm(args):
                 "this_kernel_blocks": ours, "cublas_blocks": theirs,
                 "config": "8192^3 bf16, 6 alternating blocks of 16 launches each, CUDA events per block"}
 
+            # ---- the library's fp8 GEMM (cuBLASLt through torch._scaled_mm, one scale per tensor) as a
+            # yardstick for the block-scaled kernels above: it does less (no block scales) on the same
+            # power-capped part
+            try:
+                a8 = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+                b8 = torch.randn(N, K, device=dev).to(torch.float8_e4m3fn).t()
+                one = torch.ones((), device=dev)
+
+                def lib8():
+                    return torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                for _ in range(3):
+                    lib8()
+                torch.cuda.synchronize()
+                e0.record(stream)
+                for _ in range(16):
+                    lib8()
+                e1.record(stream)
+                torch.cuda.synchronize()
+                extra["library_fp8_gemm_yardstick"] = {
+                    "tflops": 2.0 * M * N * K / (e0.elapsed_time(e1) / 16 * 1e-3) / 1e12,
+                    "config": "8192^3 e4m3 x e4m3 -> bf16, per-tensor scales, torch._scaled_mm, 16 launches"}
+                del a8, b8
+            except Exception as exc:  # the private API may differ between torch builds
+                extra["library_fp8_gemm_yardstick"] = {"unavailable": str(exc)[:200]}
+
     peak, hbm_peak, peak_src = measured_peaks()
     if rank == 0:
         cpu = None
