@@ -173,3 +173,21 @@ def test_cta_pair_configuration(b200, oracle, b, h, s, causal):
     with pytest.raises(Exception, match="num_cta_in_cga"):
         launch.fmha(out, qd, kd, vd, 1 / math.sqrt(d), 0, h // hkv, causal=causal) \
             .compile_options(launch.CompileOptions(num_cta_in_cga=4)).sync_on(_stream())
+
+
+def test_every_case_under_the_cta_pair_configuration(b200):
+    """`B200TILE_FMHA_PAIR=1` makes head_dim-128 calls without compile options use the CTA-pair
+    configuration; the variable is read once per process, so the rest of this module (f16, input
+    positions, device-side position, the full-size slab, the properties) is re-run in a child
+    process under it."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, B200TILE_FMHA_PAIR="1")
+    here = os.path.abspath(__file__)
+    r = subprocess.run([sys.executable, "-m", "pytest", here, "-q", "-x", "-m", "gpu", "-k",
+                        "not every_case_under", "-p", "no:cacheprovider"],
+                       env=env, capture_output=True, text=True, timeout=900,
+                       cwd=os.path.dirname(os.path.dirname(here)))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert " passed" in r.stdout
