@@ -518,6 +518,36 @@ def run_gpu_arm(args):
             "config": f"bf16 kv_heads {HKV} group {GRP} D {DD} s_kv {SKV}, BN 128, splits = SMs / local heads, "
                       f"split pass + merge per step, kv heads split over {world} GPU(s), K/V sets rotated (inputs > L2)"}
 
+        # ---- residual add + RMSNorm (HBM-bound neighbour of the linear layers), token rows split over the ranks;
+        # two sets of tensors are alternated so that nothing is served from L2 (2 x 1.07 GB at one GPU)
+        NT, NH = 16384, 8192
+        t0_, t1_ = sharding.split_range(NT, world, rank, 1)
+        nt = t1_ - t0_
+        sets = []
+        for i_ in range(2):
+            g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 11 + i_)
+            sets.append((torch.randn(nt, NH, device=dev, generator=g).half(),
+                         torch.randn(nt, NH, device=dev, generator=g).half(),
+                         torch.empty(nt, NH, device=dev, dtype=torch.float16),
+                         torch.empty(nt, NH, device=dev, dtype=torch.float16)))
+        wn = torch.ones(NH, device=dev, dtype=torch.float16)
+        flip = [0]
+
+        def nstep():
+            r_, x_, o_, ro_ = sets[flip[0] & 1]
+            flip[0] += 1
+            _lib.check(lib.b200tile_add_rms_norm(b"f16", r_.data_ptr(), x_.data_ptr(), wn.data_ptr(), o_.data_ptr(),
+                                                 ro_.data_ptr(), nt, NH, NH, NH, NH, NH, 1e-5, stream.cuda_stream))
+        msn = timed(nstep, 20)
+        nbytes = 4.0 * NT * NH * 2
+        gbn = nbytes / (msn * 1e-3) / 1e9
+        extra["add_rms_norm_f16"] = {
+            "gbs": gbn, "gbs_per_gpu": gbn / world, "us": msn * 1e3,
+            "frac_of_measured_hbm": gbn / world / measured_peaks()[1],
+            "config": f"f16 {NT} tokens x {NH}, read residual + x, write out + residual_out (algorithmic bytes), "
+                      f"token rows split over {world} GPU(s), two tensor sets alternated (inputs > L2)"}
+        del sets
+
         # ---- the reference's published protocol, as far as this library goes: f16 all-ones operands, 5 warm-up
         # launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
         # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322).

@@ -51,6 +51,10 @@ SIGNATURES = {
                                    c_int, c_int, c_int, c_int, c_void_p]),
     "b200tile_linear_swiglu": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int64, c_int64,
                                        c_int64, c_void_p]),
+    "b200tile_rms_norm": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_float,
+                                  c_void_p]),
+    "b200tile_add_rms_norm": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                      c_int64, c_int64, c_int64, c_int64, c_float, c_void_p]),
     "b200tile_group_gemm_workspace_bytes": (c_uint64, [c_int]),
     "b200tile_group_gemm": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                     c_int, c_void_p, c_uint64, c_void_p]),

@@ -26,6 +26,9 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
                            const int64_t* os, float qk_scale, int causal, int input_pos,
                            const uint32_t* pos_ptr, cudaStream_t stream);
 
+int b200_rms_norm_dispatch(int dtype, const void* residual, const void* x, const void* w, void* out,
+                           void* residual_out, int rows, int n, long long ld_res, long long ld_x, long long ld_out,
+                           long long ld_res_out, float eps, cudaStream_t stream);
 int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
@@ -593,6 +596,34 @@ int b200tile_linear_mxfp8(const void* x, const void* y, const void* x_scales, co
 }
 
 // ---------------------------------------------------------------------------
+// Typed normalisation entry points
+// ---------------------------------------------------------------------------
+int b200tile_add_rms_norm(const char* dtype, const void* residual, const void* x, const void* w, void* out,
+                          void* residual_out, int rows, int n, int64_t ld_residual, int64_t ldx, int64_t ldo,
+                          int64_t ld_residual_out, float eps, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "add_rms_norm", &dt)) return rc;
+  if (!residual || !x || !w || !out || !residual_out)
+    return set_error(B200TILE_ERR_INVALID, "add_rms_norm: null argument");
+  if (rows <= 0 || n <= 0) return set_error(B200TILE_ERR_INVALID, "add_rms_norm: Shape dimensions must be positive");
+  if (ld_residual < n || ldx < n || ldo < n || ld_residual_out < n)
+    return set_error(B200TILE_ERR_INVALID, "add_rms_norm: row pitch smaller than the row");
+  return b200_rms_norm_dispatch(dt, residual, x, w, out, residual_out, rows, n, ld_residual, ldx, ldo,
+                                ld_residual_out, eps, static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_rms_norm(const char* dtype, const void* x, const void* w, void* out, int rows, int n, int64_t ldx,
+                      int64_t ldo, float eps, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "rms_norm", &dt)) return rc;
+  if (!x || !w || !out) return set_error(B200TILE_ERR_INVALID, "rms_norm: null argument");
+  if (rows <= 0 || n <= 0) return set_error(B200TILE_ERR_INVALID, "rms_norm: Shape dimensions must be positive");
+  if (ldx < n || ldo < n) return set_error(B200TILE_ERR_INVALID, "rms_norm: row pitch smaller than the row");
+  return b200_rms_norm_dispatch(dt, nullptr, x, w, out, nullptr, rows, n, 0, ldx, ldo, 0, eps,
+                                static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---------------------------------------------------------------------------
 // Reference-shaped generic launch
 // ---------------------------------------------------------------------------
 namespace {
@@ -992,6 +1023,53 @@ int launch_fmha_serving_generic(const char* kernel, const char* const* generics,
                                   reinterpret_cast<const void*>(pos.ptr), stream);
 }
 
+// "rms_norm_f16" (cutile-kernels/src/norms.rs:22-27): (x [rows,N], w [N], out partition [1,N], eps f32);
+// "add_rms_norm_f16" (:77-84): (residual [rows,N], x [rows,N], w [N], out partition [1,N], residual_out
+// partition [1,N], eps f32).  Generics [T?, N, BLOCK_SIZE]; grid (rows, 1, 1).  BLOCK_SIZE only shapes the
+// reference's loop and is ignored here.
+int launch_norm_generic(const char* kernel, const char* const* generics, int n_generics, const void* const* params,
+                        int n_params, const unsigned grid[3], void* stream, bool launch) {
+  const bool add = !strcmp(kernel, "add_rms_norm_f16");
+  const char* dtype;
+  long g[4];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 4, &ng) || ng < 2)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  const long N = g[0];
+  if (N <= 0 || g[1] <= 0) return set_error(B200TILE_ERR_INVALID, "%s: N and BLOCK_SIZE must be positive", kernel);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg res, x, w, o, ro;
+  if (add) read_tensor(r, 2, false, res);
+  read_tensor(r, 2, false, x);
+  read_tensor(r, 1, false, w);
+  read_tensor(r, 2, true, o);
+  if (add) read_tensor(r, 2, true, ro);
+  const float eps = r.f32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int rows = o.dim[0];
+  if (x.dim[0] != rows || x.dim[1] != N || o.dim[1] != N || w.dim[0] != N || x.stride[1] != 1 ||
+      o.stride[1] != 1 || w.stride[0] != 1 ||
+      (add && (res.dim[0] != rows || res.dim[1] != N || ro.dim[0] != rows || ro.dim[1] != N ||
+               res.stride[1] != 1 || ro.stride[1] != 1)))
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  if (o.pdim[0] != 1 || o.pdim[1] != N || (add && (ro.pdim[0] != 1 || ro.pdim[1] != N)))
+    return set_error(B200TILE_ERR_INVALID, "%s: output partition must be [1, N]", kernel);
+  if (grid[0] != (unsigned)rows || grid[1] != 1 || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid (%d, 1, 1)", grid[0],
+                     grid[1], grid[2], rows);
+  if (add)
+    return b200tile_add_rms_norm(dtype, reinterpret_cast<const void*>(res.ptr), reinterpret_cast<const void*>(x.ptr),
+                                 reinterpret_cast<const void*>(w.ptr), reinterpret_cast<void*>(o.ptr),
+                                 reinterpret_cast<void*>(ro.ptr), rows, (int)N, res.stride[0], x.stride[0],
+                                 o.stride[0], ro.stride[0], eps, stream);
+  return b200tile_rms_norm(dtype, reinterpret_cast<const void*>(x.ptr), reinterpret_cast<const void*>(w.ptr),
+                           reinterpret_cast<void*>(o.ptr), rows, (int)N, x.stride[0], o.stride[0], eps, stream);
+}
+
 // "fmha_decode_gqa_split" (:727-901): (q [kv_heads,GROUP,D], k, v [kv_heads,cap,D], att_out partition
 //    [1,GROUP,D] of [kv_heads,NUM_KV_SPLITS*GROUP,D], lse_out partition [1,GROUP] of
 //    [kv_heads,NUM_KV_SPLITS*GROUP], qk_scale f16, position_start u32[1]), generics
@@ -1137,6 +1215,8 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
     return launch_decode_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   if (!strcmp(kernel, "group_gemm_f16_nt_desc"))
     return launch_group_gemm_generic(kernel, generics, n_generics, params, n_params, cu_stream, true);
+  if (!strcmp(kernel, "rms_norm_f16") || !strcmp(kernel, "add_rms_norm_f16"))
+    return launch_norm_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -1157,6 +1237,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
     return launch_decode_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   if (!strcmp(kernel, "group_gemm_f16_nt_desc"))
     return launch_group_gemm_generic(kernel, generics, n_generics, nullptr, 0, nullptr, false);
+  if (!strcmp(kernel, "rms_norm_f16") || !strcmp(kernel, "add_rms_norm_f16"))
+    return launch_norm_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

@@ -492,6 +492,35 @@ def splitk_reduce_merge(att_partial: Tensor, lse_partial: Tensor, out: Output) -
     return SplitkReduceMerge([att_partial, lse_partial, out])
 
 
+class RmsNormF16(KernelLauncher):
+    """Generics [T, N, BLOCK_SIZE]; grid (rows, 1, 1) from the [1, N] output partition."""
+    kernel_name = "rms_norm_f16"
+
+    def __init__(self, args, block_size: int):
+        super().__init__(args)
+        self._block = int(block_size)
+
+    def infer_generics(self) -> List[str]:
+        x = self.args[0]   # x, or the residual of the same shape and type
+        return [x.dtype_str(), str(x.shape[1]), str(self._block)]
+
+
+class AddRmsNormF16(RmsNormF16):
+    kernel_name = "add_rms_norm_f16"
+
+
+def rms_norm_f16(x: Tensor, w: Tensor, out: Output, eps: float, block_size: int = 512) -> RmsNormF16:
+    """`rms_norm_f16` (cutile-kernels/src/norms.rs:22-27): x [rows, N], w [N], out the [1, N] partition of
+    [rows, N]."""
+    return RmsNormF16([x, w, out, float(eps)], block_size)
+
+
+def add_rms_norm_f16(residual: Tensor, x: Tensor, w: Tensor, out: Output, residual_out: Output, eps: float,
+                     block_size: int = 512) -> AddRmsNormF16:
+    """`add_rms_norm_f16` (cutile-kernels/src/norms.rs:77-84): out and residual_out are [1, N] partitions."""
+    return AddRmsNormF16([residual, x, w, out, residual_out, float(eps)], block_size)
+
+
 class GroupGemmF16NtDesc(KernelLauncher):
     """Generics [T, BM, BN, BK, NUM_SM]; the grid is (NUM_SM, 1, 1) as in the reference launcher."""
     kernel_name = "group_gemm_f16_nt_desc"

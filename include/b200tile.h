@@ -159,6 +159,26 @@ B200TILE_API int b200tile_gemm_host(const char* dtype, int b_layout, const void*
 B200TILE_API int b200tile_linear_swiglu(const char* dtype, const void* x, const void* w_gate_up, void* out, int m,
                                         int inter, int k, int64_t ldx, int64_t ldw, int64_t ldo, void* cu_stream);
 
+/* RMSNorm over the last dimension of a [rows, n] 16-bit tensor:
+ *     out = round16((x * rsqrt(mean(x^2) + eps)) * w)
+ * Replaces `rms_norm_f16` (cutile-kernels/src/norms.rs:22-60; also its per-head use `qk_norm_f16`,
+ * :152 ff., when the heads are passed as rows).  Each row is read once (the reference reads it twice).
+ *   dtype   "f16" (the reference's type) or "bf16";  w [n];  pitches ldx / ldo in elements.
+ *   16-byte aligned bases with pitches that are multiples of 8 take the vector path; anything else
+ *   is accepted and runs with scalar accesses. */
+B200TILE_API int b200tile_rms_norm(const char* dtype, const void* x, const void* w, void* out, int rows, int n,
+                                   int64_t ldx, int64_t ldo, float eps, void* cu_stream);
+
+/* Residual add fused with RMSNorm, also writing the updated residual:
+ *     combined = residual + x (fp32);  residual_out = round16(combined);
+ *     out = round16((combined * rsqrt(mean(combined^2) + eps)) * w)
+ * Replaces `add_rms_norm_f16` (cutile-kernels/src/norms.rs:77-137).  `residual_out` may alias
+ * `residual`, and `out` may alias `x` (every element is read before its row is written). */
+B200TILE_API int b200tile_add_rms_norm(const char* dtype, const void* residual, const void* x, const void* w,
+                                       void* out, void* residual_out, int rows, int n, int64_t ld_residual,
+                                       int64_t ldx, int64_t ldo, int64_t ld_residual_out, float eps,
+                                       void* cu_stream);
+
 /* Persistent grouped GEMM over device-side tables (MoE expert batches): for g in [0, num_groups)
  * C_g [m_g, n_g] = A_g [m_g, k_g] * B_g [k_g, n_g], row-major 16-bit operands, fp32 accumulation.
  * Replaces `group_gemm_f16_nt_desc` (cutile-kernels/src/experimental/moe.rs:66-128).

@@ -249,6 +249,30 @@ def silu_mul(gate, up, is_f16: bool = False) -> np.ndarray:
     return y.astype(np.float16).astype(np.float32) if is_f16 else round_bf16(y)
 
 
+def add_rms_norm(residual, x, w, eps: float, block_size: int = 512, is_f16: bool = True):
+    """`add_rms_norm_f16` (cutile-kernels/src/norms.rs:77-137), and with ``residual=None``
+    `rms_norm_f16` (:22-60).  16-bit inputs widened to f32; per row the squares are accumulated
+    lane-wise over tiles of ``block_size`` columns (:100-108; overhang lanes read as zero), the lanes are
+    summed (:109), inv = rsqrt(sum / N + eps) (:112-115), out = combined * inv * w and the updated
+    residual = combined, both rounded to the 16-bit type (:126-134).  numpy's pairwise lane sum stands
+    in for the tile reduction, whose order the compiler chooses.  Returns (out, residual_out or None)."""
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if is_f16 else round_bf16
+    xf, wf = _f32(x), _f32(w)
+    comb = (_f32(residual) + xf).astype(np.float32) if residual is not None else xf
+    rows, n = comb.shape
+    tiles = (n + block_size - 1) // block_size
+    pad = np.zeros((rows, tiles * block_size), dtype=np.float32)
+    pad[:, :n] = comb
+    lanes = np.zeros((rows, block_size), dtype=np.float32)
+    for j in range(tiles):
+        t = pad[:, j * block_size:(j + 1) * block_size]
+        lanes = (lanes + t * t).astype(np.float32)
+    ssum = lanes.sum(axis=1, dtype=np.float32)
+    inv = (np.float32(1.0) / np.sqrt(ssum / np.float32(n) + np.float32(eps), dtype=np.float32)).astype(np.float32)
+    out = rnd(((comb * inv[:, None]).astype(np.float32) * wf[None, :]).astype(np.float32))
+    return out, (rnd(comb) if residual is not None else None)
+
+
 def persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy) -> int:
     return int(lib().oracle_persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy))
 
