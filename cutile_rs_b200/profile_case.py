@@ -4,6 +4,7 @@
     python -m cutile_rs_b200.profile_case fmha --batch 1 --heads 16 --seq 4096 --causal 0 --iters 3
     python -m cutile_rs_b200.profile_case decode --heads 8 --group 4 --seq 65536 --splits 18 --iters 3
     python -m cutile_rs_b200.profile_case nvfp4 --m 4096 --n 14336 --k 4096 --iters 3
+    python -m cutile_rs_b200.profile_case norm --m 8192 --n 8192 --iters 3      # residual add + RMSNorm, rows x N
 
 With the diagnostic build (B200_VARIANT=trace B200_NVCC_EXTRA=-DB200TILE_TRACE csrc/build.sh) and
 B200TILE_LIB=cutile_rs_b200/libb200tile_trace.so, ``--trace`` prints where the MMA-issuing thread
@@ -28,7 +29,7 @@ from . import _lib
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "fmha", "decode", "nvfp4"])
+    ap.add_argument("kernel", choices=["gemm", "fmha", "decode", "nvfp4", "norm"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=8192)
@@ -85,6 +86,17 @@ def main() -> None:
                                                  z.data_ptr(), b"bf16", m, n, k, k // 2, k // 2, n, k // 16, k // 16,
                                                  1.0, ws.data_ptr(), wsb, args.config, stream.cuda_stream))
         flops = 2.0 * m * n * k
+    elif args.kernel == "norm":
+        rows, n = args.m, args.n
+        r = torch.randn(rows, n, device="cuda", generator=g).half()
+        x = torch.randn(rows, n, device="cuda", generator=g).half()
+        w = torch.ones(n, device="cuda", dtype=torch.float16)
+        o, ro = torch.empty_like(x), torch.empty_like(x)
+
+        def run():
+            _lib.check(lib.b200tile_add_rms_norm(b"f16", r.data_ptr(), x.data_ptr(), w.data_ptr(), o.data_ptr(),
+                                                 ro.data_ptr(), rows, n, n, n, n, n, 1e-5, stream.cuda_stream))
+        flops = 4.0 * rows * n * 2     # bytes, reported below as GB/s
     elif args.kernel == "decode":
         h, grp, s, d, ns = args.heads, args.group, args.seq, args.head_dim, args.splits
         q = torch.randn(h, grp, d, device="cuda", generator=g).bfloat16()
@@ -126,7 +138,10 @@ def main() -> None:
     ms = e0.elapsed_time(e1) / args.iters
     status = _lib.StatusC()
     _lib.check(lib.b200tile_status(stream.cuda_stream, ctypes.byref(status)))
-    print(f"{args.kernel}: {ms:.4f} ms/launch, {flops / ms / 1e9:.1f} TFLOP/s")
+    if args.kernel == "norm":
+        print(f"norm: {ms * 1e3:.1f} us/launch, {flops / ms / 1e6:.0f} GB/s of algorithmic bytes")
+    else:
+        print(f"{args.kernel}: {ms:.4f} ms/launch, {flops / ms / 1e9:.1f} TFLOP/s")
     if args.trace:
         _print_trace(lib, args)
 
