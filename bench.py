@@ -548,6 +548,31 @@ def run_gpu_arm(args):
                       f"token rows split over {world} GPU(s), two tensor sets alternated (inputs > L2)"}
         del sets
 
+        # ---- rotary position embedding over [tokens, heads, D]; token rows split over the ranks, two sets alternated
+        RT, RH, RD = 32768, 32, 128
+        t0_, t1_ = sharding.split_range(RT, world, rank, 1)
+        rt = t1_ - t0_
+        rsets = [(torch.randn(rt, RH, RD, device=dev).half(), torch.empty(rt, RH, RD, device=dev, dtype=torch.float16))
+                 for _ in range(2)]
+        inv_f = (1.0 / 10000.0 ** (torch.arange(0, RD, 2, dtype=torch.float32, device=dev) / RD)).contiguous()
+        I2r = ctypes.c_int64 * 2
+        rst = I2r(RH * RD, RD)
+        rflip = [0]
+
+        def rstep():
+            x_, o_ = rsets[rflip[0] & 1]
+            rflip[0] += 1
+            _lib.check(lib.b200tile_rope_seq(b"f16", x_.data_ptr(), inv_f.data_ptr(), o_.data_ptr(), rt, RH, RD, rst, rst,
+                                             t0_, None, stream.cuda_stream))
+        msr = timed(rstep, 20)
+        gbr = 2.0 * RT * RH * RD * 2 / (msr * 1e-3) / 1e9
+        extra["rope_seq_f16"] = {
+            "gbs": gbr, "gbs_per_gpu": gbr / world, "us": msr * 1e3,
+            "frac_of_measured_hbm": gbr / world / measured_peaks()[1],
+            "config": f"f16 {RT} tokens x {RH} heads x {RD}, one read + one write per element, token rows split over "
+                      f"{world} GPU(s), two tensor sets alternated (inputs > L2)"}
+        del rsets
+
         # ---- the reference's published protocol, as far as this library goes: f16 all-ones operands, 5 warm-up
         # launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
         # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322).

@@ -29,6 +29,9 @@ int b200_fmha_fwd_dispatch(int dtype, int head_dim, const void* q, const void* k
 int b200_rms_norm_dispatch(int dtype, const void* residual, const void* x, const void* w, void* out,
                            void* residual_out, int rows, int n, long long ld_res, long long ld_x, long long ld_out,
                            long long ld_res_out, float eps, cudaStream_t stream);
+int b200_rope_seq_dispatch(int dtype, const void* x, const float* inv_freq, void* out, int seq, int heads,
+                           int head_dim, long long xs_seq, long long xs_head, long long os_seq, long long os_head,
+                           int position_start, const uint32_t* pos_ptr, cudaStream_t stream);
 int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
@@ -623,6 +626,22 @@ int b200tile_rms_norm(const char* dtype, const void* x, const void* w, void* out
                                 static_cast<cudaStream_t>(cu_stream));
 }
 
+int b200tile_rope_seq(const char* dtype, const void* x, const float* inv_freq, void* out, int seq, int heads,
+                      int head_dim, const int64_t x_strides[2], const int64_t out_strides[2], int position_start,
+                      const void* position_ptr, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "rope_seq", &dt)) return rc;
+  if (!x || !inv_freq || !out || !x_strides || !out_strides)
+    return set_error(B200TILE_ERR_INVALID, "rope_seq: null argument");
+  if (seq <= 0 || heads <= 0 || head_dim <= 0)
+    return set_error(B200TILE_ERR_INVALID, "rope_seq: Shape dimensions must be positive");
+  if ((reinterpret_cast<uintptr_t>(inv_freq) & 3) || (reinterpret_cast<uintptr_t>(position_ptr) & 3))
+    return set_error(B200TILE_ERR_ALIGN, "rope_seq: inv_freq / position must be 4-byte aligned");
+  return b200_rope_seq_dispatch(dt, x, inv_freq, out, seq, heads, head_dim, x_strides[0], x_strides[1],
+                                out_strides[0], out_strides[1], position_start,
+                                static_cast<const uint32_t*>(position_ptr), static_cast<cudaStream_t>(cu_stream));
+}
+
 // ---------------------------------------------------------------------------
 // Reference-shaped generic launch
 // ---------------------------------------------------------------------------
@@ -1070,6 +1089,47 @@ int launch_norm_generic(const char* kernel, const char* const* generics, int n_g
                            reinterpret_cast<void*>(o.ptr), rows, (int)N, x.stride[0], o.stride[0], eps, stream);
 }
 
+// "rope_seq_f16" (cutile-kernels/src/positional.rs:20-25): (x [seq,heads,D], inv_freq f32 [HALF_D], out partition
+// [1,1,HALF_D], position_start i32); "rope_seq_dynpos_f16" (:74-79): (x, inv_freq, position_start u32[1], out).
+// Generics [T?, D, HALF_D]; grid (seq, heads, 2).
+int launch_rope_generic(const char* kernel, const char* const* generics, int n_generics, const void* const* params,
+                        int n_params, const unsigned grid[3], void* stream, bool launch) {
+  const bool dyn = !strcmp(kernel, "rope_seq_dynpos_f16");
+  const char* dtype;
+  long g[4];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 4, &ng) || ng < 2)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  const long D = g[0], HALF = g[1];
+  if (D <= 0 || HALF * 2 != D) return set_error(B200TILE_ERR_INVALID, "%s: HALF_D must be D / 2", kernel);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg x, f, pos, o;
+  int position_start = 0;
+  read_tensor(r, 3, false, x);
+  read_tensor(r, 1, false, f);
+  if (dyn) read_tensor(r, 1, false, pos);
+  read_tensor(r, 3, true, o);
+  if (!dyn) position_start = r.i32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int seq = x.dim[0], heads = x.dim[1];
+  if (x.dim[2] != D || o.dim[0] != seq || o.dim[1] != heads || o.dim[2] != D || f.dim[0] != HALF ||
+      x.stride[2] != 1 || o.stride[2] != 1 || f.stride[0] != 1 || (dyn && pos.dim[0] < 1))
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  if (o.pdim[0] != 1 || o.pdim[1] != 1 || o.pdim[2] != HALF)
+    return set_error(B200TILE_ERR_INVALID, "%s: output partition must be [1, 1, HALF_D]", kernel);
+  if (grid[0] != (unsigned)seq || grid[1] != (unsigned)heads || grid[2] != 2)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid (%d, %d, 2)", grid[0],
+                     grid[1], grid[2], seq, heads);
+  const int64_t xs[2] = {x.stride[0], x.stride[1]}, os[2] = {o.stride[0], o.stride[1]};
+  return b200tile_rope_seq(dtype, reinterpret_cast<const void*>(x.ptr), reinterpret_cast<const float*>(f.ptr),
+                           reinterpret_cast<void*>(o.ptr), seq, heads, (int)D, xs, os, position_start,
+                           dyn ? reinterpret_cast<const void*>(pos.ptr) : nullptr, stream);
+}
+
 // "fmha_decode_gqa_split" (:727-901): (q [kv_heads,GROUP,D], k, v [kv_heads,cap,D], att_out partition
 //    [1,GROUP,D] of [kv_heads,NUM_KV_SPLITS*GROUP,D], lse_out partition [1,GROUP] of
 //    [kv_heads,NUM_KV_SPLITS*GROUP], qk_scale f16, position_start u32[1]), generics
@@ -1217,6 +1277,8 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
     return launch_group_gemm_generic(kernel, generics, n_generics, params, n_params, cu_stream, true);
   if (!strcmp(kernel, "rms_norm_f16") || !strcmp(kernel, "add_rms_norm_f16"))
     return launch_norm_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "rope_seq_f16") || !strcmp(kernel, "rope_seq_dynpos_f16"))
+    return launch_rope_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -1239,6 +1301,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
     return launch_group_gemm_generic(kernel, generics, n_generics, nullptr, 0, nullptr, false);
   if (!strcmp(kernel, "rms_norm_f16") || !strcmp(kernel, "add_rms_norm_f16"))
     return launch_norm_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "rope_seq_f16") || !strcmp(kernel, "rope_seq_dynpos_f16"))
+    return launch_rope_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

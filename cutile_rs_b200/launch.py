@@ -521,6 +521,31 @@ def add_rms_norm_f16(residual: Tensor, x: Tensor, w: Tensor, out: Output, residu
     return AddRmsNormF16([residual, x, w, out, residual_out, float(eps)], block_size)
 
 
+class RopeSeqF16(KernelLauncher):
+    """Generics [T, D, HALF_D]; grid (seq, heads, 2) from the [1, 1, HALF_D] output partition."""
+    kernel_name = "rope_seq_f16"
+
+    def infer_generics(self) -> List[str]:
+        x = self.args[0]
+        return [x.dtype_str(), str(x.shape[2]), str(x.shape[2] // 2)]
+
+
+class RopeSeqDynposF16(RopeSeqF16):
+    kernel_name = "rope_seq_dynpos_f16"
+
+
+def rope_seq_f16(x: Tensor, inv_freq: Tensor, out: Output, position_start: int) -> RopeSeqF16:
+    """`rope_seq_f16` (cutile-kernels/src/positional.rs:20-25): x [seq, heads, D], inv_freq f32 [D/2], out the
+    [1, 1, D/2] partition of [seq, heads, D]."""
+    return RopeSeqF16([x, inv_freq, out, int(position_start)])
+
+
+def rope_seq_dynpos_f16(x: Tensor, inv_freq: Tensor, position_start: Tensor, out: Output) -> RopeSeqDynposF16:
+    """`rope_seq_dynpos_f16` (cutile-kernels/src/positional.rs:74-79): the position of the first row is a
+    device u32[1] (i64 storage is accepted as in the attention launchers)."""
+    return RopeSeqDynposF16([x, inv_freq, position_start, out])
+
+
 class GroupGemmF16NtDesc(KernelLauncher):
     """Generics [T, BM, BN, BK, NUM_SM]; the grid is (NUM_SM, 1, 1) as in the reference launcher."""
     kernel_name = "group_gemm_f16_nt_desc"

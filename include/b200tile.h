@@ -179,6 +179,20 @@ B200TILE_API int b200tile_add_rms_norm(const char* dtype, const void* residual, 
                                        int64_t ldx, int64_t ldo, int64_t ld_residual_out, float eps,
                                        void* cu_stream);
 
+/* Rotary position embedding, chunked (GPT-NeoX) layout, over x [seq, heads, head_dim]:
+ *     theta = float(position + s) * inv_freq[i],  i in [0, head_dim/2)
+ *     out[s,h,i] = x[s,h,i] cos - x[s,h,i+D/2] sin;   out[s,h,i+D/2] = x[s,h,i+D/2] cos + x[s,h,i] sin
+ * Replaces `rope_seq_f16` and, with a non-null `position_ptr` (device u32[1], read by the kernel, so
+ * that a captured graph can be replayed with a new position), `rope_seq_dynpos_f16`
+ * (cutile-kernels/src/positional.rs:20-62, 74-120).  The angles are evaluated once per position, not
+ * once per (position, head, half).
+ *   dtype "f16" or "bf16"; inv_freq [head_dim/2] f32; strides {seq, head} in elements (innermost 1);
+ *   `out` may alias `x`. */
+B200TILE_API int b200tile_rope_seq(const char* dtype, const void* x, const float* inv_freq, void* out, int seq,
+                                   int heads, int head_dim, const int64_t x_strides[2],
+                                   const int64_t out_strides[2], int position_start, const void* position_ptr,
+                                   void* cu_stream);
+
 /* Persistent grouped GEMM over device-side tables (MoE expert batches): for g in [0, num_groups)
  * C_g [m_g, n_g] = A_g [m_g, k_g] * B_g [k_g, n_g], row-major 16-bit operands, fp32 accumulation.
  * Replaces `group_gemm_f16_nt_desc` (cutile-kernels/src/experimental/moe.rs:66-128).

@@ -273,6 +273,26 @@ def add_rms_norm(residual, x, w, eps: float, block_size: int = 512, is_f16: bool
     return out, (rnd(comb) if residual is not None else None)
 
 
+def rope_seq(x, inv_freq, position_start: int, is_f16: bool = True) -> np.ndarray:
+    """`rope_seq_f16` / `rope_seq_dynpos_f16` (cutile-kernels/src/positional.rs:20-62, 74-120): x
+    [seq, heads, D] in the chunked layout, theta = f32(position_start + s) * inv_freq (:41-44), cos and sin
+    in f32 (:46-47), y_lo = x_lo cos - x_hi sin, y_hi = x_hi cos + x_lo sin with every product and sum
+    rounded to f32 (:49-50), results rounded to the 16-bit type (:51-52).  The angles are formed in f32 as the
+    kernel does and their cos / sin taken in double precision and rounded, i.e. correctly rounded values."""
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if is_f16 else round_bf16
+    xf = _f32(x)
+    seq, heads, d = xf.shape
+    half = d // 2
+    pos = (np.arange(seq, dtype=np.int64) + int(position_start)).astype(np.float32)
+    theta = (pos[:, None] * _f32(inv_freq)[None, :]).astype(np.float32)
+    cs = np.cos(theta.astype(np.float64)).astype(np.float32)[:, None, :]
+    sn = np.sin(theta.astype(np.float64)).astype(np.float32)[:, None, :]
+    lo, hi = xf[:, :, :half], xf[:, :, half:]
+    y_lo = ((lo * cs).astype(np.float32) - (hi * sn).astype(np.float32)).astype(np.float32)
+    y_hi = ((hi * cs).astype(np.float32) + (lo * sn).astype(np.float32)).astype(np.float32)
+    return rnd(np.concatenate([y_lo, y_hi], axis=2))
+
+
 def persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy) -> int:
     return int(lib().oracle_persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy))
 
