@@ -573,6 +573,33 @@ def run_gpu_arm(args):
                       f"{world} GPU(s), two tensor sets alternated (inputs > L2)"}
         del rsets
 
+        # ---- QK norm + rotary embedding + KV-cache write in one pass (prefill block of 16384 tokens, 32 + 8 heads);
+        # token rows split over the ranks; 403 MB of reads and writes per launch at one GPU (> L2)
+        QT, QH, KVH = 16384, 32, 8
+        t0_, t1_ = sharding.split_range(QT, world, rank, 1)
+        qt = t1_ - t0_
+        qq = torch.randn(qt, QH, RD, device=dev).half()
+        qk_ = torch.randn(qt, KVH, RD, device=dev).half()
+        qv = torch.randn(qt, KVH, RD, device=dev).half()
+        qo_ = torch.empty_like(qq)
+        kc_ = torch.empty(KVH, qt, RD, device=dev, dtype=torch.float16)
+        vc_ = torch.empty(KVH, qt, RD, device=dev, dtype=torch.float16)
+        wq_ = torch.ones(RD, device=dev, dtype=torch.float16)
+
+        def qstep():
+            _lib.check(lib.b200tile_qk_norm_rope_kv(b"f16", qq.data_ptr(), qk_.data_ptr(), qv.data_ptr(), wq_.data_ptr(),
+                                                    wq_.data_ptr(), inv_f.data_ptr(), qo_.data_ptr(), kc_.data_ptr(),
+                                                    vc_.data_ptr(), 1e-6, 0, None, qt, QH, KVH, RD, qt, QH * RD,
+                                                    KVH * RD, KVH * RD, QH * RD, stream.cuda_stream))
+        msq = timed(qstep, 20)
+        gbq = 2.0 * QT * (QH + 2 * KVH) * RD * 2 / (msq * 1e-3) / 1e9
+        extra["qk_norm_rope_kv_prefill"] = {
+            "gbs": gbq, "gbs_per_gpu": gbq / world, "us": msq * 1e3,
+            "frac_of_measured_hbm": gbq / world / measured_peaks()[1],
+            "config": f"f16 {QT} tokens, {QH} q heads + {KVH} kv heads x {RD}: read q, k, v; write q_out, k_cache, v_cache; "
+                      f"token rows split over {world} GPU(s)"}
+        del qq, qk_, qv, qo_, kc_, vc_
+
         # ---- the reference's published protocol, as far as this library goes: f16 all-ones operands, 5 warm-up
         # launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
         # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322).

@@ -32,6 +32,11 @@ int b200_rms_norm_dispatch(int dtype, const void* residual, const void* x, const
 int b200_rope_seq_dispatch(int dtype, const void* x, const float* inv_freq, void* out, int seq, int heads,
                            int head_dim, long long xs_seq, long long xs_head, long long os_seq, long long os_head,
                            int position_start, const uint32_t* pos_ptr, cudaStream_t stream);
+int b200_qk_norm_rope_kv_dispatch(int dtype, const void* q, const void* k, const void* v, const void* q_weight,
+                                  const void* k_weight, const float* inv_freq, void* q_out, void* k_cache,
+                                  void* v_cache, float eps, int position_start, const uint32_t* pos_ptr, int seq,
+                                  int q_heads, int kv_heads, int head_dim, int max_seq, long long q_ss,
+                                  long long k_ss, long long v_ss, long long qo_ss, cudaStream_t stream);
 int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
@@ -642,6 +647,29 @@ int b200tile_rope_seq(const char* dtype, const void* x, const float* inv_freq, v
                                 static_cast<const uint32_t*>(position_ptr), static_cast<cudaStream_t>(cu_stream));
 }
 
+int b200tile_qk_norm_rope_kv(const char* dtype, const void* q, const void* k, const void* v, const void* q_weight,
+                             const void* k_weight, const float* inv_freq, void* q_out, void* k_cache, void* v_cache,
+                             float eps, int position_start, const void* position_ptr, int seq_len, int num_q_heads,
+                             int num_kv_heads, int head_dim, int max_seq, int64_t q_seq_stride, int64_t k_seq_stride,
+                             int64_t v_seq_stride, int64_t q_out_seq_stride, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "qk_norm_rope_kv", &dt)) return rc;
+  if (!q || !k || !v || !q_weight || !k_weight || !inv_freq || !q_out || !k_cache || !v_cache)
+    return set_error(B200TILE_ERR_INVALID, "qk_norm_rope_kv: null argument");
+  if (seq_len <= 0 || num_q_heads < 0 || num_kv_heads < 0 || num_q_heads + num_kv_heads <= 0 || head_dim <= 0 ||
+      max_seq <= 0)
+    return set_error(B200TILE_ERR_INVALID, "qk_norm_rope_kv: Shape dimensions must be positive");
+  if (!position_ptr && (position_start < 0 || (int64_t)position_start + seq_len > max_seq))
+    return set_error(B200TILE_ERR_INVALID, "qk_norm_rope_kv: positions [%d, %lld) do not fit the cache of %d rows",
+                     position_start, (long long)position_start + seq_len, max_seq);
+  if ((reinterpret_cast<uintptr_t>(inv_freq) & 3) || (reinterpret_cast<uintptr_t>(position_ptr) & 3))
+    return set_error(B200TILE_ERR_ALIGN, "qk_norm_rope_kv: inv_freq / position must be 4-byte aligned");
+  return b200_qk_norm_rope_kv_dispatch(dt, q, k, v, q_weight, k_weight, inv_freq, q_out, k_cache, v_cache, eps,
+                                       position_start, static_cast<const uint32_t*>(position_ptr), seq_len,
+                                       num_q_heads, num_kv_heads, head_dim, max_seq, q_seq_stride, k_seq_stride,
+                                       v_seq_stride, q_out_seq_stride, static_cast<cudaStream_t>(cu_stream));
+}
+
 // ---------------------------------------------------------------------------
 // Reference-shaped generic launch
 // ---------------------------------------------------------------------------
@@ -1130,6 +1158,66 @@ int launch_rope_generic(const char* kernel, const char* const* generics, int n_g
                            dyn ? reinterpret_cast<const void*>(pos.ptr) : nullptr, stream);
 }
 
+// "qk_norm_rope_kv_prefill_raw_f16" (experimental/fused_transformer.rs:22-43): nine raw pointers (q, k, v,
+// q_weight, k_weight, inv_freq, q_out, k_cache, v_cache), eps f32, position_start, seq_len, num_q_heads,
+// num_kv_heads i32; "qk_norm_rope_kv_decode_raw_f16" (:356-372): seven raw pointers (qkv, q_weight, k_weight,
+// inv_freq, q_out, k_cache, v_cache), position_start u32[1], eps f32, num_q_heads, num_kv_heads i32.
+// Generics [T?, D, HALF_D, MAX_SEQ]; grid (seq_len, num_q_heads + num_kv_heads, 1).
+int launch_qk_rope_generic(const char* kernel, const char* const* generics, int n_generics,
+                           const void* const* params, int n_params, const unsigned grid[3], void* stream,
+                           bool launch) {
+  const bool decode = !strcmp(kernel, "qk_norm_rope_kv_decode_raw_f16");
+  const char* dtype;
+  long g[4];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 4, &ng) || ng < 3)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  const long D = g[0], MAXS = g[2];
+  if (D <= 0 || g[1] * 2 != D || MAXS <= 0)
+    return set_error(B200TILE_ERR_INVALID, "%s: HALF_D must be D / 2 and MAX_SEQ positive", kernel);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  uint64_t ptr[9];
+  TensorArg pos;
+  float eps;
+  int position_start = 0, seq_len = 1, qh, kvh;
+  if (decode) {
+    for (int i = 0; i < 7; ++i) ptr[i] = r.u64();
+    read_tensor(r, 1, false, pos);
+    eps = r.f32();
+  } else {
+    for (int i = 0; i < 9; ++i) ptr[i] = r.u64();
+    eps = r.f32();
+    position_start = r.i32();
+    seq_len = r.i32();
+  }
+  qh = r.i32();
+  kvh = r.i32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  if (qh < 0 || kvh < 0 || seq_len <= 0)
+    return set_error(B200TILE_ERR_INVALID, "%s: Shape dimensions must be positive", kernel);
+  if (grid[0] != (unsigned)seq_len || grid[1] != (unsigned)(qh + kvh) || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid (%d, %d, 1)", grid[0],
+                     grid[1], grid[2], seq_len, qh + kvh);
+  auto vp = [](uint64_t a) { return reinterpret_cast<void*>(a); };
+  if (decode) {
+    // one fused projection row: q heads, then k heads, then v heads
+    const char* qkv = reinterpret_cast<const char*>(ptr[0]);
+    const int64_t row = (int64_t)(qh + 2 * kvh) * D;
+    return b200tile_qk_norm_rope_kv(dtype, qkv, qkv + (int64_t)qh * D * 2, qkv + (int64_t)(qh + kvh) * D * 2,
+                                    vp(ptr[1]), vp(ptr[2]), reinterpret_cast<const float*>(ptr[3]), vp(ptr[4]),
+                                    vp(ptr[5]), vp(ptr[6]), eps, 0, reinterpret_cast<const void*>(pos.ptr), 1, qh, kvh,
+                                    (int)D, (int)MAXS, row, row, row, (int64_t)qh * D, stream);
+  }
+  return b200tile_qk_norm_rope_kv(dtype, vp(ptr[0]), vp(ptr[1]), vp(ptr[2]), vp(ptr[3]), vp(ptr[4]),
+                                  reinterpret_cast<const float*>(ptr[5]), vp(ptr[6]), vp(ptr[7]), vp(ptr[8]), eps,
+                                  position_start, nullptr, seq_len, qh, kvh, (int)D, (int)MAXS, (int64_t)qh * D,
+                                  (int64_t)kvh * D, (int64_t)kvh * D, (int64_t)qh * D, stream);
+}
+
 // "fmha_decode_gqa_split" (:727-901): (q [kv_heads,GROUP,D], k, v [kv_heads,cap,D], att_out partition
 //    [1,GROUP,D] of [kv_heads,NUM_KV_SPLITS*GROUP,D], lse_out partition [1,GROUP] of
 //    [kv_heads,NUM_KV_SPLITS*GROUP], qk_scale f16, position_start u32[1]), generics
@@ -1279,6 +1367,8 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
     return launch_norm_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   if (!strcmp(kernel, "rope_seq_f16") || !strcmp(kernel, "rope_seq_dynpos_f16"))
     return launch_rope_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "qk_norm_rope_kv_prefill_raw_f16") || !strcmp(kernel, "qk_norm_rope_kv_decode_raw_f16"))
+    return launch_qk_rope_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -1303,6 +1393,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
     return launch_norm_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   if (!strcmp(kernel, "rope_seq_f16") || !strcmp(kernel, "rope_seq_dynpos_f16"))
     return launch_rope_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "qk_norm_rope_kv_prefill_raw_f16") || !strcmp(kernel, "qk_norm_rope_kv_decode_raw_f16"))
+    return launch_qk_rope_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

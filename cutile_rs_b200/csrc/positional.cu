@@ -36,6 +36,22 @@ __device__ __forceinline__ uint16_t rope_to_16(float v) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(v));
 }
 
+// Two 16-bit values <-> two floats with the packed conversion instructions.
+template <bool F16>
+__device__ __forceinline__ float2 rope_unpack2(uint32_t w) {
+  if (F16) return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <bool F16>
+__device__ __forceinline__ uint32_t rope_pack2(float a, float b) {
+  if (F16) {
+    const __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 struct RopeParams {
   const uint16_t* x;
   const float* inv_freq;
@@ -135,6 +151,199 @@ int b200_rope_seq_dispatch(int dtype, const void* x, const float* inv_freq, void
     rope_seq_kernel<true><<<(unsigned)seq, ROPE_THREADS, 0, stream>>>(p);
   else
     rope_seq_kernel<false><<<(unsigned)seq, ROPE_THREADS, 0, stream>>>(p);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Per-head RMSNorm of Q and K, rotary embedding, and the KV-cache write, in one pass
+// ---------------------------------------------------------------------------
+// Replaces `qk_norm_rope_kv_prefill_raw_f16` and `qk_norm_rope_kv_decode_raw_f16`
+// (cutile-kernels/src/experimental/fused_transformer.rs:22-344, 356 ff.): for every (position, head)
+//     inv  = rsqrt(sum(x^2) / D + eps);   n = (x * inv) * w        (fp32, not rounded in between)
+//     y_lo = n_lo cos - n_hi sin;  y_hi = n_hi cos + n_lo sin;     theta = float(position + s) * inv_freq
+// Q heads go to q_out [seq, q_heads, D]; K heads to k_cache [kv_heads, MAX_SEQ, D] at row position + s,
+// and the V heads are copied to v_cache beside them.  One CTA per position: the angles are
+// evaluated once, then groups of D/16 lanes take one head each (a 16-byte vector of the low half and
+// one of the high half per lane), reduce the squares with shuffles, and write 16-byte vectors.
+namespace b200 {
+namespace {
+
+struct QkRopeParams {
+  const uint16_t *q, *k, *v, *qw, *kw;
+  const float* inv_freq;
+  uint16_t *q_out, *k_cache, *v_cache;
+  const uint32_t* pos_ptr;
+  int position_start, seq, q_heads, kv_heads, half_d, max_seq;
+  long long q_ss, k_ss, v_ss, qo_ss;   // row (position) strides in elements; heads are D apart
+  float eps;
+};
+
+// Kept out of line so that the argument reduction of sincosf does not set the register count of the
+// streaming part of the kernel.
+__device__ __noinline__ void rope_angles(float pos, const float* __restrict__ inv_freq, int half_d, float* s_cos,
+                                         float* s_sin) {
+  for (int i = threadIdx.x; i < half_d; i += blockDim.x) {
+    float sn, cs;
+    sincosf(__fmul_rn(pos, __ldg(inv_freq + i)), &sn, &cs);
+    s_cos[i] = cs;
+    s_sin[i] = sn;
+  }
+}
+
+template <bool F16>
+__global__ void __launch_bounds__(ROPE_THREADS, 4) qk_norm_rope_kv_kernel(const QkRopeParams p) {
+  __shared__ __align__(16) float s_cos[ROPE_MAX_HALF], s_sin[ROPE_MAX_HALF];
+  const int s = blockIdx.x;
+  const int base = p.pos_ptr ? (int)__ldg(p.pos_ptr) : p.position_start;
+  const int cache_pos = base + s;
+  const int d = 2 * p.half_d;
+  const int lanes = p.half_d / 8;                 // lanes per head: a power of two, 1..32
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sub = lane % lanes;                   // this lane's vector inside each half
+  const int heads_per_warp = 32 / lanes;
+  const int total = p.q_heads + p.kv_heads;       // heads to normalise and rotate
+  const int items = total + p.kv_heads;           // ... and V heads to copy
+  const int step = (blockDim.x / 32) * heads_per_warp;
+  const bool cache_ok = cache_pos >= 0 && cache_pos < p.max_seq;
+
+  // item i: Q head i, K head i - q_heads, or V head i - total.  Source vectors of the low and high half.
+  auto load_item = [&](int i, uint4& qlo, uint4& qhi) {
+    if (i >= items) return;
+    const uint16_t* x;
+    if (i < p.q_heads) x = p.q + (long long)s * p.q_ss + (long long)i * d;
+    else if (i < total) x = p.k + (long long)s * p.k_ss + (long long)(i - p.q_heads) * d;
+    else x = p.v + (long long)s * p.v_ss + (long long)(i - total) * d;
+    qlo = __ldg(reinterpret_cast<const uint4*>(x) + sub);
+    qhi = __ldg(reinterpret_cast<const uint4*>(x + p.half_d) + sub);
+  };
+  // every lane of a warp calls this for every round (the shuffles need all of them)
+  auto finish_item = [&](int i, const uint4& qlo, const uint4& qhi) {
+    const bool rot = i < total;
+    float lo[8], hi[8];
+    float ss = 0.0f;
+    if (rot) {
+      const uint32_t wl[4] = {qlo.x, qlo.y, qlo.z, qlo.w}, wh[4] = {qhi.x, qhi.y, qhi.z, qhi.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 a = rope_unpack2<F16>(wl[e]), b = rope_unpack2<F16>(wh[e]);
+        lo[2 * e] = a.x;
+        lo[2 * e + 1] = a.y;
+        hi[2 * e] = b.x;
+        hi[2 * e + 1] = b.y;
+        ss += a.x * a.x + b.x * b.x;
+        ss += a.y * a.y + b.y * b.y;
+      }
+    }
+    for (int o = lanes >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (i >= items) return;
+    if (!rot) {
+      if (cache_ok) {
+        uint16_t* vc = p.v_cache + ((long long)(i - total) * p.max_seq + cache_pos) * d;
+        reinterpret_cast<uint4*>(vc)[sub] = qlo;
+        reinterpret_cast<uint4*>(vc + p.half_d)[sub] = qhi;
+      }
+      return;
+    }
+    const bool is_q = i < p.q_heads;
+    const float inv = rsqrtf(ss / (float)d + p.eps);
+    const uint16_t* w = is_q ? p.qw : p.kw;
+    const uint4 qwl = __ldg(reinterpret_cast<const uint4*>(w) + sub);
+    const uint4 qwh = __ldg(reinterpret_cast<const uint4*>(w + p.half_d) + sub);
+    const uint32_t wl[4] = {qwl.x, qwl.y, qwl.z, qwl.w}, wh[4] = {qwh.x, qwh.y, qwh.z, qwh.w};
+    const float4 c0 = *reinterpret_cast<const float4*>(s_cos + sub * 8), c1 = *reinterpret_cast<const float4*>(s_cos + sub * 8 + 4);
+    const float4 n0 = *reinterpret_cast<const float4*>(s_sin + sub * 8), n1 = *reinterpret_cast<const float4*>(s_sin + sub * 8 + 4);
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+    uint32_t ylo[4], yhi[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 wa = rope_unpack2<F16>(wl[e]), wb = rope_unpack2<F16>(wh[e]);
+      const float nl0 = (lo[2 * e] * inv) * wa.x, nl1 = (lo[2 * e + 1] * inv) * wa.y;
+      const float nh0 = (hi[2 * e] * inv) * wb.x, nh1 = (hi[2 * e + 1] * inv) * wb.y;
+      // the second product of each line is fused into the sum (one rounding less than the tile program)
+      ylo[e] = rope_pack2<F16>(fmaf(nl0, cs[2 * e], -(nh0 * sn[2 * e])), fmaf(nl1, cs[2 * e + 1], -(nh1 * sn[2 * e + 1])));
+      yhi[e] = rope_pack2<F16>(fmaf(nh0, cs[2 * e], nl0 * sn[2 * e]), fmaf(nh1, cs[2 * e + 1], nl1 * sn[2 * e + 1]));
+    }
+    uint16_t* o;
+    if (is_q) {
+      o = p.q_out + (long long)s * p.qo_ss + (long long)i * d;
+    } else {
+      if (!cache_ok) return;
+      o = p.k_cache + ((long long)(i - p.q_heads) * p.max_seq + cache_pos) * d;
+    }
+    reinterpret_cast<uint4*>(o)[sub] = make_uint4(ylo[0], ylo[1], ylo[2], ylo[3]);
+    reinterpret_cast<uint4*>(o + p.half_d)[sub] = make_uint4(yhi[0], yhi[1], yhi[2], yhi[3]);
+  };
+  // Two rounds per iteration with all four loads issued first; the first iteration's loads go out
+  // before the angles are evaluated, which do not depend on them.  64 bytes in flight per thread
+  // and four CTAs per SM are what it takes to keep HBM busy at one position per CTA.
+  int i0 = warp * heads_per_warp;
+  int ia = i0 + lane / lanes, ib = ia + step;
+  uint4 alo = make_uint4(0, 0, 0, 0), ahi = alo, blo = alo, bhi = alo;
+  load_item(ia, alo, ahi);
+  load_item(ib, blo, bhi);
+  rope_angles((float)cache_pos, p.inv_freq, p.half_d, s_cos, s_sin);
+  __syncthreads();
+  while (i0 < items) {
+    finish_item(ia, alo, ahi);
+    asm volatile("" ::: "memory");   // finish one head before the next: shorter live ranges
+    if (i0 + step < items) finish_item(ib, blo, bhi);   // warp-uniform condition
+    i0 += 2 * step;
+    if (i0 >= items) break;
+    ia = i0 + lane / lanes;
+    ib = ia + step;
+    load_item(ia, alo, ahi);
+    load_item(ib, blo, bhi);
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+int b200_qk_norm_rope_kv_dispatch(int dtype, const void* q, const void* k, const void* v, const void* q_weight,
+                                  const void* k_weight, const float* inv_freq, void* q_out, void* k_cache,
+                                  void* v_cache, float eps, int position_start, const uint32_t* pos_ptr, int seq,
+                                  int q_heads, int kv_heads, int head_dim, int max_seq, long long q_ss,
+                                  long long k_ss, long long v_ss, long long qo_ss, cudaStream_t stream) {
+  using namespace b200;
+  if (!b200h::device_info()) return B200_ERR_CUDA;
+  const int half = head_dim / 2, lanes = half / 8;
+  if (head_dim % 16 || lanes < 1 || lanes > 32 || (lanes & (lanes - 1)))
+    return b200h::set_error(B200_ERR_UNSUPPORTED, "qk_norm_rope_kv: D=%d has no configuration (16, 32, ..., 512)",
+                            head_dim);
+  const uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+                       reinterpret_cast<uintptr_t>(q_weight) | reinterpret_cast<uintptr_t>(k_weight) |
+                       reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
+                       reinterpret_cast<uintptr_t>(v_cache);
+  if ((al & 15) || (q_ss & 7) || (k_ss & 7) || (v_ss & 7) || (qo_ss & 7))
+    return b200h::set_error(B200_ERR_ALIGN, "qk_norm_rope_kv: pointers and row pitches must be multiples of 16 bytes");
+  QkRopeParams p;
+  p.q = static_cast<const uint16_t*>(q);
+  p.k = static_cast<const uint16_t*>(k);
+  p.v = static_cast<const uint16_t*>(v);
+  p.qw = static_cast<const uint16_t*>(q_weight);
+  p.kw = static_cast<const uint16_t*>(k_weight);
+  p.inv_freq = inv_freq;
+  p.q_out = static_cast<uint16_t*>(q_out);
+  p.k_cache = static_cast<uint16_t*>(k_cache);
+  p.v_cache = static_cast<uint16_t*>(v_cache);
+  p.pos_ptr = pos_ptr;
+  p.position_start = position_start;
+  p.seq = seq;
+  p.q_heads = q_heads;
+  p.kv_heads = kv_heads;
+  p.half_d = half;
+  p.max_seq = max_seq;
+  p.q_ss = q_ss;
+  p.k_ss = k_ss;
+  p.v_ss = v_ss;
+  p.qo_ss = qo_ss;
+  p.eps = eps;
+  if (dtype)
+    qk_norm_rope_kv_kernel<true><<<(unsigned)seq, ROPE_THREADS, 0, stream>>>(p);
+  else
+    qk_norm_rope_kv_kernel<false><<<(unsigned)seq, ROPE_THREADS, 0, stream>>>(p);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

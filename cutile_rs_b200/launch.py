@@ -37,6 +37,10 @@ class CompileOptions:
                                     f(self.max_divisibility), f(self.num_worker_warps_per_cta))
 
 
+class DevicePtr(int):
+    """A raw device address passed as a kernel parameter (`*mut T` in the reference's raw-pointer kernels)."""
+
+
 class F16(float):
     """A scalar kernel parameter of type f16 (the `qk_scale: f16` of the decode kernels,
     cutile-kernels/src/attention.rs:610,754): two bytes in the parameter array."""
@@ -110,6 +114,8 @@ class KernelLauncher:
             if isinstance(a, (Partition, MappedLaunchPartition, Tensor)):
                 for kind, v in a.kernel_args():
                     pa.push(kind, v)
+            elif isinstance(a, DevicePtr):
+                pa.push("u64", int(a))
             elif isinstance(a, bool):
                 pa.push("i32", int(a))
             elif isinstance(a, int):
@@ -544,6 +550,39 @@ def rope_seq_dynpos_f16(x: Tensor, inv_freq: Tensor, position_start: Tensor, out
     """`rope_seq_dynpos_f16` (cutile-kernels/src/positional.rs:74-79): the position of the first row is a
     device u32[1] (i64 storage is accepted as in the attention launchers)."""
     return RopeSeqDynposF16([x, inv_freq, position_start, out])
+
+
+class QkNormRopeKvPrefillRawF16(KernelLauncher):
+    """Raw-pointer kernel: generics [T, D, HALF_D, MAX_SEQ] and the grid (seq_len, q_heads + kv_heads, 1) are
+    given by the caller, as in the reference (no partitioned argument to infer them from)."""
+    kernel_name = "qk_norm_rope_kv_prefill_raw_f16"
+
+
+class QkNormRopeKvDecodeRawF16(KernelLauncher):
+    kernel_name = "qk_norm_rope_kv_decode_raw_f16"
+
+
+def qk_norm_rope_kv_prefill_raw_f16(q: Tensor, k: Tensor, v: Tensor, q_weight: Tensor, k_weight: Tensor,
+                                    inv_freq: Tensor, q_out: Tensor, k_cache: Tensor, v_cache: Tensor, eps: float,
+                                    position_start: int) -> QkNormRopeKvPrefillRawF16:
+    """`qk_norm_rope_kv_prefill_raw_f16` (cutile-kernels/src/experimental/fused_transformer.rs:22-43): contiguous
+    q [seq, q_heads, D], k / v [seq, kv_heads, D], caches [kv_heads, MAX_SEQ, D]."""
+    seq, qh, d = q.shape
+    kvh, max_seq = k_cache.shape[0], k_cache.shape[1]
+    ptrs = [DevicePtr(t.cu_deviceptr()) for t in (q, k, v, q_weight, k_weight, inv_freq, q_out, k_cache, v_cache)]
+    op = QkNormRopeKvPrefillRawF16(ptrs + [float(eps), int(position_start), int(seq), int(qh), int(kvh)])
+    return op.generics([q.dtype_str(), d, d // 2, max_seq]).grid((seq, qh + kvh, 1))
+
+
+def qk_norm_rope_kv_decode_raw_f16(qkv: Tensor, q_weight: Tensor, k_weight: Tensor, inv_freq: Tensor, q_out: Tensor,
+                                   k_cache: Tensor, v_cache: Tensor, position_start: Tensor, eps: float,
+                                   num_q_heads: int, num_kv_heads: int) -> QkNormRopeKvDecodeRawF16:
+    """`qk_norm_rope_kv_decode_raw_f16` (fused_transformer.rs:356-372): qkv is one fused projection row,
+    [(q_heads + 2 kv_heads) * D]; the position is a device u32[1]."""
+    d, max_seq = k_cache.shape[2], k_cache.shape[1]
+    ptrs = [DevicePtr(t.cu_deviceptr()) for t in (qkv, q_weight, k_weight, inv_freq, q_out, k_cache, v_cache)]
+    op = QkNormRopeKvDecodeRawF16(ptrs + [position_start, float(eps), int(num_q_heads), int(num_kv_heads)])
+    return op.generics([qkv.dtype_str(), d, d // 2, max_seq]).grid((1, num_q_heads + num_kv_heads, 1))
 
 
 class GroupGemmF16NtDesc(KernelLauncher):

@@ -5,6 +5,7 @@
     python -m cutile_rs_b200.profile_case decode --heads 8 --group 4 --seq 65536 --splits 18 --iters 3
     python -m cutile_rs_b200.profile_case nvfp4 --m 4096 --n 14336 --k 4096 --iters 3
     python -m cutile_rs_b200.profile_case norm --m 8192 --n 8192 --iters 3      # residual add + RMSNorm, rows x N
+    python -m cutile_rs_b200.profile_case qkrope --m 16384 --heads 32 --iters 3 # QK norm + RoPE + KV write, tokens
 
 With the diagnostic build (B200_VARIANT=trace B200_NVCC_EXTRA=-DB200TILE_TRACE csrc/build.sh) and
 B200TILE_LIB=cutile_rs_b200/libb200tile_trace.so, ``--trace`` prints where the MMA-issuing thread
@@ -29,7 +30,7 @@ from . import _lib
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "fmha", "decode", "nvfp4", "norm"])
+    ap.add_argument("kernel", choices=["gemm", "fmha", "decode", "nvfp4", "norm", "qkrope"])
     ap.add_argument("--m", type=int, default=4096)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=8192)
@@ -97,6 +98,23 @@ def main() -> None:
             _lib.check(lib.b200tile_add_rms_norm(b"f16", r.data_ptr(), x.data_ptr(), w.data_ptr(), o.data_ptr(),
                                                  ro.data_ptr(), rows, n, n, n, n, n, 1e-5, stream.cuda_stream))
         flops = 4.0 * rows * n * 2     # bytes, reported below as GB/s
+    elif args.kernel == "qkrope":
+        t, qh, kvh, d = args.m, args.heads, max(args.heads // 4, 1), args.head_dim
+        q = torch.randn(t, qh, d, device="cuda", generator=g).half()
+        k = torch.randn(t, kvh, d, device="cuda", generator=g).half()
+        v = torch.randn(t, kvh, d, device="cuda", generator=g).half()
+        w = torch.ones(d, device="cuda", dtype=torch.float16)
+        f = (1.0 / 10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32, device="cuda") / d)).contiguous()
+        qo = torch.empty_like(q)
+        kc = torch.empty(kvh, t, d, device="cuda", dtype=torch.float16)
+        vc = torch.empty_like(kc)
+
+        def run():
+            _lib.check(lib.b200tile_qk_norm_rope_kv(b"f16", q.data_ptr(), k.data_ptr(), v.data_ptr(), w.data_ptr(),
+                                                    w.data_ptr(), f.data_ptr(), qo.data_ptr(), kc.data_ptr(),
+                                                    vc.data_ptr(), 1e-6, 0, None, t, qh, kvh, d, t, qh * d, kvh * d,
+                                                    kvh * d, qh * d, stream.cuda_stream))
+        flops = 2.0 * t * (qh + 2 * kvh) * d * 2     # bytes
     elif args.kernel == "decode":
         h, grp, s, d, ns = args.heads, args.group, args.seq, args.head_dim, args.splits
         q = torch.randn(h, grp, d, device="cuda", generator=g).bfloat16()
@@ -138,8 +156,8 @@ def main() -> None:
     ms = e0.elapsed_time(e1) / args.iters
     status = _lib.StatusC()
     _lib.check(lib.b200tile_status(stream.cuda_stream, ctypes.byref(status)))
-    if args.kernel == "norm":
-        print(f"norm: {ms * 1e3:.1f} us/launch, {flops / ms / 1e6:.0f} GB/s of algorithmic bytes")
+    if args.kernel in ("norm", "qkrope"):
+        print(f"{args.kernel}: {ms * 1e3:.1f} us/launch, {flops / ms / 1e6:.0f} GB/s of algorithmic bytes")
     else:
         print(f"{args.kernel}: {ms:.4f} ms/launch, {flops / ms / 1e9:.1f} TFLOP/s")
     if args.trace:

@@ -193,6 +193,24 @@ B200TILE_API int b200tile_rope_seq(const char* dtype, const void* x, const float
                                    const int64_t out_strides[2], int position_start, const void* position_ptr,
                                    void* cu_stream);
 
+/* Per-head RMSNorm of Q and K, rotary embedding and the KV-cache write in one pass over a token block:
+ * for every position s and head,  n = (x * rsqrt(mean(x^2) + eps)) * w  (fp32),  then the rotation of
+ * b200tile_rope_seq at position + s.  Q heads are written to q_out [seq, q_heads, D]; K heads to
+ * k_cache [kv_heads, max_seq, D] at row position + s; V heads are copied to v_cache at the same row.
+ * Replaces `qk_norm_rope_kv_prefill_raw_f16` and, with seq_len = 1, q / k / v pointing into one fused
+ * projection row and a device-side position, `qk_norm_rope_kv_decode_raw_f16`
+ * (cutile-kernels/src/experimental/fused_transformer.rs:22-344, 356 ff.).
+ *   q [seq, q_heads, D], k and v [seq, kv_heads, D]: heads D apart, rows *_seq_stride elements apart
+ *   q_weight, k_weight [D]; inv_freq [D/2] f32; D in {16, 32, 64, 128, 256, 512}
+ *   position_ptr: device u32[1] or null (then position_start is used).  Rows that would fall outside
+ *   [0, max_seq) are not written to the caches.  All tensors 16-byte aligned. */
+B200TILE_API int b200tile_qk_norm_rope_kv(const char* dtype, const void* q, const void* k, const void* v,
+                                          const void* q_weight, const void* k_weight, const float* inv_freq,
+                                          void* q_out, void* k_cache, void* v_cache, float eps, int position_start,
+                                          const void* position_ptr, int seq_len, int num_q_heads, int num_kv_heads,
+                                          int head_dim, int max_seq, int64_t q_seq_stride, int64_t k_seq_stride,
+                                          int64_t v_seq_stride, int64_t q_out_seq_stride, void* cu_stream);
+
 /* Persistent grouped GEMM over device-side tables (MoE expert batches): for g in [0, num_groups)
  * C_g [m_g, n_g] = A_g [m_g, k_g] * B_g [k_g, n_g], row-major 16-bit operands, fp32 accumulation.
  * Replaces `group_gemm_f16_nt_desc` (cutile-kernels/src/experimental/moe.rs:66-128).

@@ -293,6 +293,41 @@ def rope_seq(x, inv_freq, position_start: int, is_f16: bool = True) -> np.ndarra
     return rnd(np.concatenate([y_lo, y_hi], axis=2))
 
 
+def qk_norm_rope_kv(q, k, v, q_weight, k_weight, inv_freq, k_cache, v_cache, eps: float, position_start: int,
+                    is_f16: bool = True):
+    """`qk_norm_rope_kv_prefill_raw_f16` (cutile-kernels/src/experimental/fused_transformer.rs:145-344; the decode
+    form :356 ff. is the same arithmetic on one row): per (position, head) the squares of the low and the high
+    half are added lane-wise and summed (:184-186), inv = rsqrt(sum / D + eps) (:187-191), n = x * inv * w in f32
+    (:240-241), then the rotation of `rope_seq` on n (:251-262) and one rounding to the 16-bit type (:263-264).
+    Returns q_out; k_cache / v_cache (float arrays [kv_heads, MAX_SEQ, D]) are updated in place at rows
+    position_start + s."""
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if is_f16 else round_bf16
+    seq = q.shape[0]
+    half = q.shape[2] // 2
+    pos = (np.arange(seq, dtype=np.int64) + int(position_start)).astype(np.float32)
+    theta = (pos[:, None] * _f32(inv_freq)[None, :]).astype(np.float32)
+    cs = np.cos(theta.astype(np.float64)).astype(np.float32)[:, None, :]
+    sn = np.sin(theta.astype(np.float64)).astype(np.float32)[:, None, :]
+
+    def one(x, w):
+        xf, wf = _f32(x), _f32(w)
+        lo, hi = xf[:, :, :half], xf[:, :, half:]
+        ssum = ((lo * lo).astype(np.float32) + (hi * hi).astype(np.float32)).astype(np.float32).sum(axis=2, dtype=np.float32)
+        inv = (np.float32(1.0) / np.sqrt(ssum / np.float32(2 * half) + np.float32(eps), dtype=np.float32))[:, :, None]
+        nlo = ((lo * inv).astype(np.float32) * wf[None, None, :half]).astype(np.float32)
+        nhi = ((hi * inv).astype(np.float32) * wf[None, None, half:]).astype(np.float32)
+        ylo = ((nlo * cs).astype(np.float32) - (nhi * sn).astype(np.float32)).astype(np.float32)
+        yhi = ((nhi * cs).astype(np.float32) + (nlo * sn).astype(np.float32)).astype(np.float32)
+        return rnd(np.concatenate([ylo, yhi], axis=2))
+
+    q_out = one(q, q_weight)
+    k_rot = one(k, k_weight)
+    for s_ in range(seq):
+        k_cache[:, position_start + s_, :] = k_rot[s_]
+        v_cache[:, position_start + s_, :] = _f32(v)[s_]
+    return q_out
+
+
 def persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy) -> int:
     return int(lib().oracle_persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy))
 

@@ -95,3 +95,81 @@ def test_properties_and_errors(b200):
     assert b200.b200tile_rope_seq(b"f16", x.data_ptr(), f.data_ptr(), out.data_ptr(), 4, heads, 127, st, st, 0, None, s) != 0
     assert b"even" in b200.b200tile_last_error()
     assert b200.b200tile_rope_seq(b"f32", x.data_ptr(), f.data_ptr(), out.data_ptr(), 4, heads, d, st, st, 0, None, s) != 0
+
+
+def _qk_case(seq, qh, kvh, d, max_seq, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(seq, qh, d, generator=g).to(dtype)
+    k = (torch.randn(seq, kvh, d, generator=g) * 2.0).to(dtype)
+    v = torch.randn(seq, kvh, d, generator=g).to(dtype)
+    qw = (1.0 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    kw = (1.0 + 0.1 * torch.randn(d, generator=g)).to(dtype)
+    kc = torch.randn(kvh, max_seq, d, generator=g).to(dtype)
+    vc = torch.randn(kvh, max_seq, d, generator=g).to(dtype)
+    return q, k, v, qw, kw, kc, vc
+
+
+@pytest.mark.parametrize("seq,qh,kvh,d,max_seq,pos,dtype", [
+    (40, 32, 8, 128, 256, 100, torch.float16), (7, 5, 3, 64, 64, 0, torch.float16),
+    (3, 4, 4, 256, 16, 13, torch.bfloat16), (9, 2, 1, 16, 32, 5, torch.float16),
+])
+def test_qk_norm_rope_kv_prefill(b200, oracle, seq, qh, kvh, d, max_seq, pos, dtype):
+    q, k, v, qw, kw, kc, vc = _qk_case(seq, qh, kvh, d, max_seq, dtype, seq + d)
+    f = _inv_freq(d)
+    kc_ref, vc_ref = kc.float().numpy().copy(), vc.float().numpy().copy()
+    q_ref = oracle.qk_norm_rope_kv(q.float().numpy(), k.float().numpy(), v.float().numpy(), qw.float().numpy(),
+                                   kw.float().numpy(), f.numpy(), kc_ref, vc_ref, 1e-6, pos,
+                                   is_f16=dtype == torch.float16)
+    dev = [t.cuda() for t in (q, k, v, qw, kw, kc, vc)]
+    qd, kd, vd, qwd, kwd, kcd, vcd = dev
+    fd = f.cuda()
+    qo = torch.empty_like(qd)
+    name = b"f16" if dtype == torch.float16 else b"bf16"
+    _lib.check(b200.b200tile_qk_norm_rope_kv(name, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), qwd.data_ptr(),
+                                             kwd.data_ptr(), fd.data_ptr(), qo.data_ptr(), kcd.data_ptr(),
+                                             vcd.data_ptr(), 1e-6, pos, None, seq, qh, kvh, d, max_seq, qh * d,
+                                             kvh * d, kvh * d, qh * d, _stream().cuda_stream))
+    torch.cuda.synchronize()
+    ulp = 2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7
+    _close(qo.float().cpu().numpy(), q_ref, 2 * ulp)
+    _close(kcd.float().cpu().numpy(), kc_ref, 2 * ulp)
+    # V rows are copies; rows outside [pos, pos + seq) keep their old contents bit for bit
+    assert np.array_equal(vcd.float().cpu().numpy(), vc_ref)
+    untouched = np.ones(max_seq, dtype=bool)
+    untouched[pos:pos + seq] = False
+    assert np.array_equal(kcd.float().cpu().numpy()[:, untouched], kc.float().numpy()[:, untouched])
+
+
+def test_qk_norm_rope_kv_launchers(b200, oracle):
+    """The raw-pointer launchers of the reference: prefill over a token block, then one decode step from a fused
+    projection row with the position on the device; both leave the caches as the oracle's."""
+    seq, qh, kvh, d, max_seq = 12, 8, 2, 128, 64
+    q, k, v, qw, kw, kc, vc = _qk_case(seq, qh, kvh, d, max_seq, torch.float16, 99)
+    f = _inv_freq(d)
+    kc_ref, vc_ref = kc.float().numpy().copy(), vc.float().numpy().copy()
+    q_ref = oracle.qk_norm_rope_kv(q.float().numpy(), k.float().numpy(), v.float().numpy(), qw.float().numpy(),
+                                   kw.float().numpy(), f.numpy(), kc_ref, vc_ref, 1e-6, 0)
+    t = [api.copy_host_to_device(x) for x in (q, k, v, qw, kw, f, kc, vc)]
+    qd, kd, vd, qwd, kwd, fd, kcd, vcd = t
+    qo = api.zeros([seq, qh, d], "f16")
+    launch.qk_norm_rope_kv_prefill_raw_f16(qd, kd, vd, qwd, kwd, fd, qo, kcd, vcd, 1e-6, 0).sync_on(_stream())
+    _close(qo.to_host().float().numpy(), q_ref, 2.0 ** -9)
+    # decode: token `seq`, q / k / v taken from one row
+    g = torch.Generator().manual_seed(7)
+    row = torch.randn((qh + 2 * kvh) * d, generator=g).half()
+    q1 = row[:qh * d].reshape(1, qh, d)
+    k1 = row[qh * d:(qh + kvh) * d].reshape(1, kvh, d)
+    v1 = row[(qh + kvh) * d:].reshape(1, kvh, d)
+    q1_ref = oracle.qk_norm_rope_kv(q1.float().numpy(), k1.float().numpy(), v1.float().numpy(), qw.float().numpy(),
+                                    kw.float().numpy(), f.numpy(), kc_ref, vc_ref, 1e-6, seq)
+    rowd = api.copy_host_to_device(row)
+    q1o = api.zeros([qh, d], "f16")
+    p = api.from_torch(torch.tensor([seq], dtype=torch.int32, device="cuda"))
+    launch.qk_norm_rope_kv_decode_raw_f16(rowd, qwd, kwd, fd, q1o, kcd, vcd, p, 1e-6, qh, kvh).sync_on(_stream())
+    _close(q1o.to_host().float().numpy().reshape(1, qh, d), q1_ref, 2.0 ** -9)
+    _close(kcd.to_host().float().numpy(), kc_ref, 2.0 ** -9)
+    assert np.array_equal(vcd.to_host().float().numpy(), vc_ref)
+    # a block that does not fit the cache is refused on the host
+    with pytest.raises(Exception, match="do not fit"):
+        launch.qk_norm_rope_kv_prefill_raw_f16(qd, kd, vd, qwd, kwd, fd, qo, kcd, vcd, 1e-6, max_seq - 3) \
+            .sync_on(_stream())
