@@ -600,6 +600,31 @@ def run_gpu_arm(args):
                       f"token rows split over {world} GPU(s)"}
         del qq, qk_, qv, qo_, kc_, vc_
 
+        # ---- LM head fused with the block argmax (decode: one hidden vector against the vocabulary matrix), the
+        # vocabulary rows split over the ranks; 1.05 GB of weights at one GPU (> L2), read once
+        LV, LK = 128256, 4096
+        v0_, v1_ = sharding.split_range(LV, world, rank, 64)
+        lv = v1_ - v0_
+        lw = (torch.randn(lv, LK, device=dev) / 64).half()
+        lh = torch.randn(LK, device=dev).half()
+        lbm = torch.empty((lv + 63) // 64, device=dev, dtype=torch.float32)
+        lbi = torch.empty((lv + 63) // 64, device=dev, dtype=torch.int32)
+        ltok = torch.empty(1, device=dev, dtype=torch.int32)
+
+        def lstep():
+            _lib.check(lib.b200tile_lm_head_argmax_blocks(b"f16", lw.data_ptr(), lh.data_ptr(), lbm.data_ptr(),
+                                                          lbi.data_ptr(), lv, LK, LK, stream.cuda_stream))
+            _lib.check(lib.b200tile_argmax_reduce_blocks(lbm.data_ptr(), lbi.data_ptr(), ltok.data_ptr(),
+                                                         (lv + 63) // 64, stream.cuda_stream))
+        msl = timed(lstep, 20)
+        gbl = 2.0 * LV * LK / (msl * 1e-3) / 1e9
+        extra["lm_head_argmax_f16"] = {
+            "gbs": gbl, "gbs_per_gpu": gbl / world, "us": msl * 1e3,
+            "frac_of_measured_hbm": gbl / world / measured_peaks()[1],
+            "config": f"f16 vocabulary {LV} x hidden {LK}: fused matrix-vector product + block argmax, then the reduction "
+                      f"over blocks (two launches per step); vocabulary rows split over {world} GPU(s)"}
+        del lw
+
         # ---- the reference's published protocol, as far as this library goes: f16 all-ones operands, 5 warm-up
         # launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
         # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322).

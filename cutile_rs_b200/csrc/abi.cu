@@ -37,6 +37,12 @@ int b200_qk_norm_rope_kv_dispatch(int dtype, const void* q, const void* k, const
                                   void* v_cache, float eps, int position_start, const uint32_t* pos_ptr, int seq,
                                   int q_heads, int kv_heads, int head_dim, int max_seq, long long q_ss,
                                   long long k_ss, long long v_ss, long long qo_ss, cudaStream_t stream);
+int b200_argmax_blocks_dispatch(int dtype, const void* logits, float* block_max, uint32_t* block_idx, int len,
+                                int block_size, cudaStream_t stream);
+int b200_lm_head_argmax_blocks_dispatch(int dtype, const void* weights, const void* hidden, float* block_max,
+                                        uint32_t* block_idx, int vocab, int k, long long ldw, cudaStream_t stream);
+int b200_argmax_reduce_blocks_dispatch(const float* block_max, const uint32_t* block_idx, uint32_t* out,
+                                       int num_blocks, cudaStream_t stream);
 int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
@@ -670,6 +676,38 @@ int b200tile_qk_norm_rope_kv(const char* dtype, const void* q, const void* k, co
                                        v_seq_stride, q_out_seq_stride, static_cast<cudaStream_t>(cu_stream));
 }
 
+int b200tile_argmax_blocks(const char* dtype, const void* logits, float* block_max, uint32_t* block_idx, int len,
+                           int block_size, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "argmax_blocks", &dt)) return rc;
+  if (!logits || !block_max || !block_idx) return set_error(B200TILE_ERR_INVALID, "argmax_blocks: null argument");
+  if (len <= 0 || block_size <= 0)
+    return set_error(B200TILE_ERR_INVALID, "argmax_blocks: Shape dimensions must be positive");
+  return b200_argmax_blocks_dispatch(dt, logits, block_max, block_idx, len, block_size,
+                                     static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_lm_head_argmax_blocks(const char* dtype, const void* weights, const void* hidden, float* block_max,
+                                   uint32_t* block_idx, int vocab, int k, int64_t ldw, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "lm_head_argmax_blocks", &dt)) return rc;
+  if (!weights || !hidden || !block_max || !block_idx)
+    return set_error(B200TILE_ERR_INVALID, "lm_head_argmax_blocks: null argument");
+  if (vocab <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "lm_head_argmax_blocks: Shape dimensions must be positive");
+  if (ldw < k) return set_error(B200TILE_ERR_INVALID, "lm_head_argmax_blocks: row pitch smaller than the row");
+  return b200_lm_head_argmax_blocks_dispatch(dt, weights, hidden, block_max, block_idx, vocab, k, ldw,
+                                             static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_argmax_reduce_blocks(const float* block_max, const uint32_t* block_idx, uint32_t* out, int num_blocks,
+                                  void* cu_stream) {
+  if (!block_max || !block_idx || !out) return set_error(B200TILE_ERR_INVALID, "argmax_reduce_blocks: null argument");
+  if (num_blocks <= 0) return set_error(B200TILE_ERR_INVALID, "argmax_reduce_blocks: Shape dimensions must be positive");
+  return b200_argmax_reduce_blocks_dispatch(block_max, block_idx, out, num_blocks,
+                                            static_cast<cudaStream_t>(cu_stream));
+}
+
 // ---------------------------------------------------------------------------
 // Reference-shaped generic launch
 // ---------------------------------------------------------------------------
@@ -1218,6 +1256,65 @@ int launch_qk_rope_generic(const char* kernel, const char* const* generics, int 
                                   (int64_t)kvh * D, (int64_t)kvh * D, (int64_t)qh * D, stream);
 }
 
+// "argmax_blocks_f16" (cutile-kernels/src/argmax.rs:20-25): (logits [len], block_max partition [1], block_idx
+//    partition [1], len i32), generics [T?, BLOCK_SIZE], grid (blocks, 1, 1).
+// "lm_head_argmax_blocks_f16" (:88-94): (weights [vocab, K], hidden [1, K], block_max partition [1], block_idx
+//    partition [1], vocab_size i32), generics [T?, K], grid (ceil(vocab / 64), 1, 1).
+// "argmax_reduce_blocks_to_u32" (:162-167): (block_max [n], block_idx [n], out partition [1], num_blocks i32),
+//    generics [BLOCK_SIZE], grid (1, 1, 1).
+int launch_argmax_generic(const char* kernel, const char* const* generics, int n_generics, const void* const* params,
+                          int n_params, const unsigned grid[3], void* stream, bool launch) {
+  const bool fused = !strcmp(kernel, "lm_head_argmax_blocks_f16");
+  const bool reduce = !strcmp(kernel, "argmax_reduce_blocks_to_u32");
+  const char* dtype;
+  long g[2];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 2, &ng) || ng < 1 || g[0] <= 0)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg a, b, bm, bi;
+  read_tensor(r, fused ? 2 : 1, false, a);
+  if (fused) read_tensor(r, 2, false, b);
+  if (reduce) read_tensor(r, 1, false, b);
+  read_tensor(r, 1, true, bm);
+  if (!reduce) read_tensor(r, 1, true, bi);
+  const int count = r.i32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  if (bm.pdim[0] != 1 || bm.stride[0] != 1 || (!reduce && (bi.pdim[0] != 1 || bi.stride[0] != 1)))
+    return set_error(B200TILE_ERR_INVALID, "%s: outputs must be contiguous with partition [1]", kernel);
+  if (reduce) {
+    if (count > a.dim[0] || count > b.dim[0] || a.stride[0] != 1 || b.stride[0] != 1 || count > g[0])
+      return set_error(B200TILE_ERR_INVALID, "%s: num_blocks exceeds the inputs or BLOCK_SIZE", kernel);
+    if (grid[0] != 1 || grid[1] != 1 || grid[2] != 1)
+      return set_error(B200TILE_ERR_INVALID, "launch grid (%u, %u, %u) does not match the inferred partition grid (1, 1, 1)",
+                       grid[0], grid[1], grid[2]);
+    return b200tile_argmax_reduce_blocks(reinterpret_cast<const float*>(a.ptr), reinterpret_cast<const uint32_t*>(b.ptr),
+                                         reinterpret_cast<uint32_t*>(bm.ptr), count, stream);
+  }
+  const long per_block = fused ? 64 : g[0];
+  const long blocks = (count + per_block - 1) / per_block;
+  if (bm.dim[0] < blocks || bi.dim[0] < blocks)
+    return set_error(B200TILE_ERR_INVALID, "%s: block_max / block_idx hold fewer than %ld entries", kernel, blocks);
+  if (grid[0] != (unsigned)blocks || grid[1] != 1 || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid (%ld, 1, 1)", grid[0],
+                     grid[1], grid[2], blocks);
+  if (fused) {
+    if (a.dim[1] != g[0] || b.dim[1] != g[0] || a.stride[1] != 1 || b.stride[1] != 1 || count > a.dim[0])
+      return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+    return b200tile_lm_head_argmax_blocks(dtype, reinterpret_cast<const void*>(a.ptr),
+                                          reinterpret_cast<const void*>(b.ptr), reinterpret_cast<float*>(bm.ptr),
+                                          reinterpret_cast<uint32_t*>(bi.ptr), count, (int)g[0], a.stride[0], stream);
+  }
+  if (a.stride[0] != 1 || count > a.dim[0])
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  return b200tile_argmax_blocks(dtype, reinterpret_cast<const void*>(a.ptr), reinterpret_cast<float*>(bm.ptr),
+                                reinterpret_cast<uint32_t*>(bi.ptr), count, (int)g[0], stream);
+}
+
 // "fmha_decode_gqa_split" (:727-901): (q [kv_heads,GROUP,D], k, v [kv_heads,cap,D], att_out partition
 //    [1,GROUP,D] of [kv_heads,NUM_KV_SPLITS*GROUP,D], lse_out partition [1,GROUP] of
 //    [kv_heads,NUM_KV_SPLITS*GROUP], qk_scale f16, position_start u32[1]), generics
@@ -1369,6 +1466,9 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
     return launch_rope_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   if (!strcmp(kernel, "qk_norm_rope_kv_prefill_raw_f16") || !strcmp(kernel, "qk_norm_rope_kv_decode_raw_f16"))
     return launch_qk_rope_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "argmax_blocks_f16") || !strcmp(kernel, "lm_head_argmax_blocks_f16") ||
+      !strcmp(kernel, "argmax_reduce_blocks_to_u32"))
+    return launch_argmax_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -1395,6 +1495,9 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
     return launch_rope_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   if (!strcmp(kernel, "qk_norm_rope_kv_prefill_raw_f16") || !strcmp(kernel, "qk_norm_rope_kv_decode_raw_f16"))
     return launch_qk_rope_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "argmax_blocks_f16") || !strcmp(kernel, "lm_head_argmax_blocks_f16") ||
+      !strcmp(kernel, "argmax_reduce_blocks_to_u32"))
+    return launch_argmax_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

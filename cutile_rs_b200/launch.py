@@ -585,6 +585,61 @@ def qk_norm_rope_kv_decode_raw_f16(qkv: Tensor, q_weight: Tensor, k_weight: Tens
     return op.generics([qkv.dtype_str(), d, d // 2, max_seq]).grid((1, num_q_heads + num_kv_heads, 1))
 
 
+class ArgmaxBlocksF16(KernelLauncher):
+    """Generics [T, BLOCK_SIZE]; grid (blocks, 1, 1) from the [1] output partitions."""
+    kernel_name = "argmax_blocks_f16"
+
+    def __init__(self, args, block_size: int):
+        super().__init__(args)
+        self._block = int(block_size)
+
+    def infer_generics(self) -> List[str]:
+        return [self.args[0].dtype_str(), str(self._block)]
+
+
+class LmHeadArgmaxBlocksF16(KernelLauncher):
+    """Generics [T, K]; 64 vocabulary rows per block."""
+    kernel_name = "lm_head_argmax_blocks_f16"
+
+    def infer_generics(self) -> List[str]:
+        w = self.args[0]
+        return [w.dtype_str(), str(w.shape[1])]
+
+
+class ArgmaxReduceBlocksToU32(KernelLauncher):
+    """Generic [BLOCK_SIZE] >= num_blocks; one tile block."""
+    kernel_name = "argmax_reduce_blocks_to_u32"
+
+    def __init__(self, args, block_size: int):
+        super().__init__(args)
+        self._block = int(block_size)
+
+    def infer_generics(self) -> List[str]:
+        return [str(self._block)]
+
+
+def argmax_blocks_f16(logits: Tensor, block_max: Output, block_idx: Output, length: int,
+                      block_size: int = 1024) -> ArgmaxBlocksF16:
+    """`argmax_blocks_f16` (cutile-kernels/src/argmax.rs:20-25); block_max (f32) and block_idx (u32 / i32 storage)
+    are [1] partitions of ceil(len / BLOCK_SIZE) entries."""
+    return ArgmaxBlocksF16([logits, block_max, block_idx, int(length)], block_size)
+
+
+def lm_head_argmax_blocks_f16(weights: Tensor, hidden: Tensor, block_max: Output, block_idx: Output,
+                              vocab_size: int) -> LmHeadArgmaxBlocksF16:
+    """`lm_head_argmax_blocks_f16` (cutile-kernels/src/argmax.rs:88-94): weights [vocab, K], hidden [1, K]; outputs
+    are [1] partitions of ceil(vocab / 64) entries."""
+    return LmHeadArgmaxBlocksF16([weights, hidden, block_max, block_idx, int(vocab_size)])
+
+
+def argmax_reduce_blocks_to_u32(block_max: Tensor, block_idx: Tensor, out: Output, num_blocks: int,
+                                block_size: Optional[int] = None) -> ArgmaxReduceBlocksToU32:
+    """`argmax_reduce_blocks_to_u32` (cutile-kernels/src/argmax.rs:162-167); out is the [1] partition of a
+    one-element tensor.  BLOCK_SIZE defaults to the next power of two >= num_blocks."""
+    bs = block_size or max(1, 1 << (int(num_blocks) - 1).bit_length())
+    return ArgmaxReduceBlocksToU32([block_max, block_idx, out, int(num_blocks)], bs)
+
+
 class GroupGemmF16NtDesc(KernelLauncher):
     """Generics [T, BM, BN, BK, NUM_SM]; the grid is (NUM_SM, 1, 1) as in the reference launcher."""
     kernel_name = "group_gemm_f16_nt_desc"

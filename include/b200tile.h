@@ -211,6 +211,23 @@ B200TILE_API int b200tile_qk_norm_rope_kv(const char* dtype, const void* q, cons
                                           int head_dim, int max_seq, int64_t q_seq_stride, int64_t k_seq_stride,
                                           int64_t v_seq_stride, int64_t q_out_seq_stride, void* cu_stream);
 
+/* Greedy-decode token selection (cutile-kernels/src/argmax.rs).  Ties go to the lowest index.
+ * b200tile_argmax_blocks: per block of `block_size` logits the maximum (as f32) and its index;
+ *   replaces `argmax_blocks_f16` (:20-69).  block_max / block_idx hold ceil(len / block_size) entries.
+ * b200tile_lm_head_argmax_blocks: the same over logits = weights [vocab, k] . hidden [k] that are never
+ *   written, 64 vocabulary rows per block; replaces `lm_head_argmax_blocks_f16` (:81-143).  fp32
+ *   products and sums; k <= 16384.  block_max / block_idx hold ceil(vocab / 64) entries.
+ * b200tile_argmax_reduce_blocks: the winning index over the blocks into out[0]; replaces
+ *   `argmax_reduce_blocks_to_u32` (:155-199), for any number of blocks.
+ * dtype "f16" or "bf16"; all pointers are device pointers; ldw is the weights' row pitch in elements. */
+B200TILE_API int b200tile_argmax_blocks(const char* dtype, const void* logits, float* block_max, uint32_t* block_idx,
+                                        int len, int block_size, void* cu_stream);
+B200TILE_API int b200tile_lm_head_argmax_blocks(const char* dtype, const void* weights, const void* hidden,
+                                                float* block_max, uint32_t* block_idx, int vocab, int k,
+                                                int64_t ldw, void* cu_stream);
+B200TILE_API int b200tile_argmax_reduce_blocks(const float* block_max, const uint32_t* block_idx, uint32_t* out,
+                                               int num_blocks, void* cu_stream);
+
 /* Persistent grouped GEMM over device-side tables (MoE expert batches): for g in [0, num_groups)
  * C_g [m_g, n_g] = A_g [m_g, k_g] * B_g [k_g, n_g], row-major 16-bit operands, fp32 accumulation.
  * Replaces `group_gemm_f16_nt_desc` (cutile-kernels/src/experimental/moe.rs:66-128).

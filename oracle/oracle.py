@@ -328,6 +328,38 @@ def qk_norm_rope_kv(q, k, v, q_weight, k_weight, inv_freq, k_cache, v_cache, eps
     return q_out
 
 
+def argmax_blocks(logits, length: int, block_size: int):
+    """`argmax_blocks_f16` (cutile-kernels/src/argmax.rs:27-68): per block the maximum of the logits widened to
+    f32, positions >= len counting as -1e30 (:41-46), and the lowest index that attains it (:52-58)."""
+    x = _f32(logits).reshape(-1)
+    blocks = (length + block_size - 1) // block_size
+    pad = np.full(blocks * block_size, np.float32(-1.0e30), dtype=np.float32)
+    pad[:length] = x[:length]
+    pad = pad.reshape(blocks, block_size)
+    mx = pad.max(axis=1)
+    idx = (pad == mx[:, None]).argmax(axis=1) + np.arange(blocks) * block_size
+    return mx.astype(np.float32), idx.astype(np.uint32)
+
+
+def lm_head_logits(weights, hidden) -> np.ndarray:
+    """The logits of `lm_head_argmax_blocks_f16` (cutile-kernels/src/argmax.rs:103-114): per row, for every
+    32-wide slice of K in order, the f32 products are summed and the partial sum is added to the accumulator."""
+    w, h = _f32(weights), _f32(hidden).reshape(-1)
+    acc = np.zeros(w.shape[0], dtype=np.float32)
+    for kb in range(0, w.shape[1], 32):
+        prod = (w[:, kb:kb + 32] * h[None, kb:kb + 32]).astype(np.float32)
+        acc = (acc + prod.sum(axis=1, dtype=np.float32)).astype(np.float32)
+    return acc
+
+
+def argmax_reduce_blocks(block_max, block_idx, num_blocks: int) -> int:
+    """`argmax_reduce_blocks_to_u32` (cutile-kernels/src/argmax.rs:169-198): the lowest block_idx among the
+    blocks whose maximum equals the overall maximum."""
+    bm = np.asarray(block_max, dtype=np.float32)[:num_blocks]
+    bi = np.asarray(block_idx).astype(np.int64)[:num_blocks]
+    return int(bi[bm == bm.max()].min())
+
+
 def persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy) -> int:
     return int(lib().oracle_persistent_num_programs(m, n, bm, bn, num_sms, num_cta_in_cga, occupancy))
 
