@@ -625,6 +625,26 @@ def run_gpu_arm(args):
                       f"over blocks (two launches per step); vocabulary rows split over {world} GPU(s)"}
         del lw
 
+        # ---- SiLU(gate) * up as a kernel of its own (the unfused SwiGLU step), token rows split over the ranks;
+        # 3 x 235 MB per launch at one GPU (> L2)
+        ST, SI = 8192, 14336
+        t0_, t1_ = sharding.split_range(ST, world, rank, 1)
+        st_ = t1_ - t0_
+        sg = torch.randn(st_, SI, device=dev).half()
+        su = torch.randn(st_, SI, device=dev).half()
+        so = torch.empty_like(sg)
+
+        def sstep():
+            _lib.check(lib.b200tile_silu_mul_2d(b"f16", so.data_ptr(), sg.data_ptr(), su.data_ptr(), st_, SI, SI, SI, SI,
+                                                stream.cuda_stream))
+        mss = timed(sstep, 20)
+        gbs_ = 3.0 * ST * SI * 2 / (mss * 1e-3) / 1e9
+        extra["silu_mul_2d_f16"] = {
+            "gbs": gbs_, "gbs_per_gpu": gbs_ / world, "us": mss * 1e3,
+            "frac_of_measured_hbm": gbs_ / world / measured_peaks()[1],
+            "config": f"f16 {ST} x {SI}: two reads and one write per element, token rows split over {world} GPU(s)"}
+        del sg, su, so
+
         # ---- the reference's published protocol, as far as this library goes: f16 all-ones operands, 5 warm-up
         # launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
         # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322).

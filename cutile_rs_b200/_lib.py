@@ -64,6 +64,10 @@ SIGNATURES = {
     "b200tile_lm_head_argmax_blocks": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64,
                                                c_void_p]),
     "b200tile_argmax_reduce_blocks": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "b200tile_add_2d": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
+                                c_void_p]),
+    "b200tile_silu_mul_2d": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
+                                     c_void_p]),
     "b200tile_group_gemm_workspace_bytes": (c_uint64, [c_int]),
     "b200tile_group_gemm": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                     c_int, c_void_p, c_uint64, c_void_p]),

@@ -43,6 +43,8 @@ int b200_lm_head_argmax_blocks_dispatch(int dtype, const void* weights, const vo
                                         uint32_t* block_idx, int vocab, int k, long long ldw, cudaStream_t stream);
 int b200_argmax_reduce_blocks_dispatch(const float* block_max, const uint32_t* block_idx, uint32_t* out,
                                        int num_blocks, cudaStream_t stream);
+int b200_pointwise_dispatch(int dtype, int op, void* out, const void* a, const void* b, int rows, int cols,
+                            long long ld_out, long long ld_a, long long ld_b, cudaStream_t stream);
 int b200_fmha_fwd_alt_dispatch(int dtype, const void* q, const void* k, const void* v, void* o, int batch, int heads,
                                int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
                                const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
@@ -708,6 +710,28 @@ int b200tile_argmax_reduce_blocks(const float* block_max, const uint32_t* block_
                                             static_cast<cudaStream_t>(cu_stream));
 }
 
+static int pointwise_common(const char* who, int op, const char* dtype, void* out, const void* a, const void* b,
+                            int rows, int cols, int64_t ld_out, int64_t ld_a, int64_t ld_b, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, who, &dt)) return rc;
+  if (!out || !a || !b) return set_error(B200TILE_ERR_INVALID, "%s: null argument", who);
+  if (rows <= 0 || cols <= 0) return set_error(B200TILE_ERR_INVALID, "%s: Shape dimensions must be positive", who);
+  if (ld_out < cols || ld_a < cols || ld_b < cols)
+    return set_error(B200TILE_ERR_INVALID, "%s: row pitch smaller than the row", who);
+  return b200_pointwise_dispatch(dt, op, out, a, b, rows, cols, ld_out, ld_a, ld_b,
+                                 static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_add_2d(const char* dtype, void* out, const void* lhs, const void* rhs, int rows, int cols, int64_t ld_out,
+                    int64_t ld_lhs, int64_t ld_rhs, void* cu_stream) {
+  return pointwise_common("add_2d", 0, dtype, out, lhs, rhs, rows, cols, ld_out, ld_lhs, ld_rhs, cu_stream);
+}
+
+int b200tile_silu_mul_2d(const char* dtype, void* out, const void* gate, const void* up, int rows, int cols,
+                         int64_t ld_out, int64_t ld_gate, int64_t ld_up, void* cu_stream) {
+  return pointwise_common("silu_mul_2d", 1, dtype, out, gate, up, rows, cols, ld_out, ld_gate, ld_up, cu_stream);
+}
+
 // ---------------------------------------------------------------------------
 // Reference-shaped generic launch
 // ---------------------------------------------------------------------------
@@ -1315,6 +1339,42 @@ int launch_argmax_generic(const char* kernel, const char* const* generics, int n
                                 reinterpret_cast<uint32_t*>(bi.ptr), count, (int)g[0], stream);
 }
 
+// "add_2d_f16" / "silu_mul_2d_f16" (cutile-kernels/src/pointwise.rs:20-24, 50-54): (out partition [1, BLOCK_SIZE],
+// lhs [rows, cols], rhs [rows, cols]), generics [T?, BLOCK_SIZE], grid (rows, ceil(cols / BLOCK_SIZE), 1).
+int launch_pointwise_generic(const char* kernel, const char* const* generics, int n_generics,
+                             const void* const* params, int n_params, const unsigned grid[3], void* stream,
+                             bool launch) {
+  const bool silu = !strcmp(kernel, "silu_mul_2d_f16");
+  const char* dtype;
+  long g[2];
+  int ng;
+  if (split_generics(generics, n_generics, "f16", &dtype, g, 2, &ng) || ng < 1 || g[0] <= 0)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
+  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg o, a, b;
+  read_tensor(r, 2, true, o);
+  read_tensor(r, 2, false, a);
+  read_tensor(r, 2, false, b);
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int rows = o.dim[0], cols = o.dim[1];
+  if (a.dim[0] != rows || a.dim[1] != cols || b.dim[0] != rows || b.dim[1] != cols || o.stride[1] != 1 ||
+      a.stride[1] != 1 || b.stride[1] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  if (o.pdim[0] != 1 || o.pdim[1] != g[0])
+    return set_error(B200TILE_ERR_INVALID, "%s: output partition must be [1, BLOCK_SIZE]", kernel);
+  const long cb = (cols + g[0] - 1) / g[0];
+  if (grid[0] != (unsigned)rows || grid[1] != (unsigned)cb || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid (%d, %ld, 1)", grid[0],
+                     grid[1], grid[2], rows, cb);
+  return pointwise_common(silu ? "silu_mul_2d" : "add_2d", silu ? 1 : 0, dtype, reinterpret_cast<void*>(o.ptr),
+                          reinterpret_cast<const void*>(a.ptr), reinterpret_cast<const void*>(b.ptr), rows, cols,
+                          o.stride[0], a.stride[0], b.stride[0], stream);
+}
+
 // "fmha_decode_gqa_split" (:727-901): (q [kv_heads,GROUP,D], k, v [kv_heads,cap,D], att_out partition
 //    [1,GROUP,D] of [kv_heads,NUM_KV_SPLITS*GROUP,D], lse_out partition [1,GROUP] of
 //    [kv_heads,NUM_KV_SPLITS*GROUP], qk_scale f16, position_start u32[1]), generics
@@ -1469,6 +1529,8 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
   if (!strcmp(kernel, "argmax_blocks_f16") || !strcmp(kernel, "lm_head_argmax_blocks_f16") ||
       !strcmp(kernel, "argmax_reduce_blocks_to_u32"))
     return launch_argmax_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "add_2d_f16") || !strcmp(kernel, "silu_mul_2d_f16"))
+    return launch_pointwise_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   return set_error(B200TILE_ERR_UNSUPPORTED, "launch: unknown kernel '%s'", kernel);
 }
 
@@ -1498,6 +1560,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
   if (!strcmp(kernel, "argmax_blocks_f16") || !strcmp(kernel, "lm_head_argmax_blocks_f16") ||
       !strcmp(kernel, "argmax_reduce_blocks_to_u32"))
     return launch_argmax_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "add_2d_f16") || !strcmp(kernel, "silu_mul_2d_f16"))
+    return launch_pointwise_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   return set_error(B200TILE_ERR_UNSUPPORTED, "prepare: unknown kernel '%s'", kernel);
 }
 

@@ -640,6 +640,29 @@ def argmax_reduce_blocks_to_u32(block_max: Tensor, block_idx: Tensor, out: Outpu
     return ArgmaxReduceBlocksToU32([block_max, block_idx, out, int(num_blocks)], bs)
 
 
+class Add2dF16(KernelLauncher):
+    """Generics [T, BLOCK_SIZE]; grid (rows, ceil(cols / BLOCK_SIZE), 1) from the [1, BLOCK_SIZE] output partition."""
+    kernel_name = "add_2d_f16"
+
+    def infer_generics(self) -> List[str]:
+        out = self.args[0]
+        return [out.dtype_str(), str(out.partition_shape[1])]
+
+
+class SiluMul2dF16(Add2dF16):
+    kernel_name = "silu_mul_2d_f16"
+
+
+def add_2d_f16(out: Output, lhs: Tensor, rhs: Tensor) -> Add2dF16:
+    """`add_2d_f16` (cutile-kernels/src/pointwise.rs:20-24): out is the [1, BLOCK_SIZE] partition of [rows, cols]."""
+    return Add2dF16([out, lhs, rhs])
+
+
+def silu_mul_2d_f16(out: Output, gate: Tensor, up: Tensor) -> SiluMul2dF16:
+    """`silu_mul_2d_f16` (cutile-kernels/src/pointwise.rs:50-54)."""
+    return SiluMul2dF16([out, gate, up])
+
+
 class GroupGemmF16NtDesc(KernelLauncher):
     """Generics [T, BM, BN, BK, NUM_SM]; the grid is (NUM_SM, 1, 1) as in the reference launcher."""
     kernel_name = "group_gemm_f16_nt_desc"

@@ -228,6 +228,18 @@ B200TILE_API int b200tile_lm_head_argmax_blocks(const char* dtype, const void* w
 B200TILE_API int b200tile_argmax_reduce_blocks(const float* block_max, const uint32_t* block_idx, uint32_t* out,
                                                int num_blocks, void* cu_stream);
 
+/* Element-wise kernels over [rows, cols] 16-bit tensors (pitches in elements; `out` may alias an input):
+ * b200tile_add_2d:      out = lhs + rhs in the 16-bit type; replaces `add_2d_f16`
+ *                       (cutile-kernels/src/pointwise.rs:20-36).
+ * b200tile_silu_mul_2d: out = round16((gate / (1 + exp(-gate))) * up) through fp32; replaces
+ *                       `silu_mul_2d_f16` (:50-77).  (b200tile_linear_swiglu fuses this step into the
+ *                       gate/up projection.)
+ * 16-byte aligned tensors take the vector path; anything else is accepted and runs with scalar accesses. */
+B200TILE_API int b200tile_add_2d(const char* dtype, void* out, const void* lhs, const void* rhs, int rows, int cols,
+                                 int64_t ld_out, int64_t ld_lhs, int64_t ld_rhs, void* cu_stream);
+B200TILE_API int b200tile_silu_mul_2d(const char* dtype, void* out, const void* gate, const void* up, int rows,
+                                      int cols, int64_t ld_out, int64_t ld_gate, int64_t ld_up, void* cu_stream);
+
 /* Persistent grouped GEMM over device-side tables (MoE expert batches): for g in [0, num_groups)
  * C_g [m_g, n_g] = A_g [m_g, k_g] * B_g [k_g, n_g], row-major 16-bit operands, fp32 accumulation.
  * Replaces `group_gemm_f16_nt_desc` (cutile-kernels/src/experimental/moe.rs:66-128).
