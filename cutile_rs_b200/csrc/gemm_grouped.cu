@@ -6,7 +6,7 @@
 // eight i32 per group ({rows, cols, row stride, ...}, moe.rs:27-63).  Nothing about the groups is
 // known on the host, so the work is split in two launches:
 //
-//   grouped_prepare_kernel   one CTA: tile counts and their prefix sum, and for every group three
+//   grouped_prepare_kernel   CTA 0: tile counts and their prefix sum; every warp of the grid: for one group three
 //                            TMA descriptors made on the device from host-encoded templates
 //                            (`tensormap.replace` in shared memory, published to the workspace with
 //                            `tensormap.cp_fenceproxy`)
@@ -74,39 +74,45 @@ grouped_prepare_kernel(const __grid_constant__ CUtensorMap tplA, const __grid_co
   if (tid == 0) s_carry = 0;
   __syncthreads();
 
-  // ---- extents and the exclusive prefix sum of the tile counts ----
-  for (int g0 = 0; g0 < groups; g0 += GG_PREP_THREADS) {
-    const int g = g0 + tid;
-    int m = 0, n = 0, k = 0, tiles = 0;
-    if (g < groups) {
-      m = a_metas[g * 8 + 0];
-      k = a_metas[g * 8 + 1];
-      n = b_metas[g * 8 + 1];
-      if (m < 0) m = 0;
-      if (n < 0) n = 0;
-      if (k < 0) k = 0;
-      tiles = ((m + GG_BM - 1) / GG_BM) * ((n + BN - 1) / BN);
-    }
-    int scan = tiles;
+  // ---- CTA 0: extents and the exclusive prefix sum of the tile counts ----
+  if (blockIdx.x == 0) {
+    for (int g0 = 0; g0 < groups; g0 += GG_PREP_THREADS) {
+      const int g = g0 + tid;
+      int m = 0, n = 0, k = 0, tiles = 0;
+      if (g < groups) {
+        m = a_metas[g * 8 + 0];
+        k = a_metas[g * 8 + 1];
+        n = b_metas[g * 8 + 1];
+        if (m < 0) m = 0;
+        if (n < 0) n = 0;
+        if (k < 0) k = 0;
+        tiles = ((m + GG_BM - 1) / GG_BM) * ((n + BN - 1) / BN);
+      }
+      int scan = tiles;
 #pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int v = __shfl_up_sync(0xffffffffu, scan, off);
-      if (lane >= off) scan += v;
+      for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, scan, off);
+        if (lane >= off) scan += v;
+      }
+      if (lane == 31) s_warp_sum[warp] = scan;
+      __syncthreads();
+      int before = s_carry;
+      for (int w = 0; w < warp; ++w) before += s_warp_sum[w];
+      if (g < groups) ws.info[g] = make_int4(m, n, k, before + scan - tiles);
+      __syncthreads();
+      if (tid == GG_PREP_THREADS - 1) s_carry = before + scan;
+      __syncthreads();
     }
-    if (lane == 31) s_warp_sum[warp] = scan;
-    __syncthreads();
-    int before = s_carry;
-    for (int w = 0; w < warp; ++w) before += s_warp_sum[w];
-    if (g < groups) ws.info[g] = make_int4(m, n, k, before + scan - tiles);
-    __syncthreads();
-    if (tid == GG_PREP_THREADS - 1) s_carry = before + scan;
-    __syncthreads();
+    if (tid == 0) ws.info[groups] = make_int4(0, 0, 0, s_carry);
   }
-  if (tid == 0) ws.info[groups] = make_int4(0, 0, 0, s_carry);
 
-  // ---- descriptors: warp w builds groups w, w + 8, ... ----
-  const uint32_t sd = smem_u32(&s_desc[warp][0][0]);
-  for (int g = warp; g < groups; g += GG_PREP_THREADS / 32) {
+  // ---- descriptors: every warp of the grid builds ONE group's three records.  A warp's shared-memory
+  // slot is written once and never reused, so nothing can overwrite a record that is still being
+  // copied out (a loop that reused the slot produced corrupt descriptors now and then when there were
+  // more groups than warps). ----
+  const int g = blockIdx.x * (GG_PREP_THREADS / 32) + warp;
+  if (g < groups) {
+    const uint32_t sd = smem_u32(&s_desc[warp][0][0]);
     // templates -> shared memory, four bytes per lane and descriptor
     reinterpret_cast<uint32_t*>(&s_desc[warp][0][0])[lane] = reinterpret_cast<const uint32_t*>(&tplA)[lane];
     reinterpret_cast<uint32_t*>(&s_desc[warp][1][0])[lane] = reinterpret_cast<const uint32_t*>(&tplB)[lane];
@@ -371,9 +377,10 @@ static int launch_grouped(const int64_t* a_ptrs, const int64_t* b_ptrs, const in
   GroupedWs ws;
   ws.desc = static_cast<CUtensorMap*>(workspace);
   ws.info = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + grouped_desc_bytes(groups));
-  grouped_prepare_kernel<BN><<<1, GG_PREP_THREADS, 0, stream>>>(tA, tB, tC, a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas,
+  grouped_prepare_kernel<BN><<<(groups + GG_PREP_THREADS / 32 - 1) / (GG_PREP_THREADS / 32), GG_PREP_THREADS, 0, stream>>>(tA, tB, tC, a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas,
                                                                c_metas, groups, ws);
-  B200_CUDA_CHECK(cudaGetLastError());
+  const cudaError_t after_grouped_prepare_launch = cudaGetLastError();
+  B200_CUDA_CHECK(after_grouped_prepare_launch);
   auto kern = gemm_grouped_kernel<BN, OUT_F16>;
   static bool attr_done[64] = {};
   if (!attr_done[di->ordinal]) {
@@ -384,7 +391,8 @@ static int launch_grouped(const int64_t* a_ptrs, const int64_t* b_ptrs, const in
   const uint32_t idesc = make_idesc(fmt, fmt, 0, 1, GG_BM, BN);
   // the tile count is only known on the device: one CTA per SM, CTAs without a tile leave at once
   kern<<<di->sm_count, GG_THREADS, L::TOTAL, stream>>>(ws, groups, idesc, di->status);
-  B200_CUDA_CHECK(cudaGetLastError());
+  const cudaError_t after_grouped_main_launch = cudaGetLastError();
+  B200_CUDA_CHECK(after_grouped_main_launch);
   return B200_OK;
 }
 
