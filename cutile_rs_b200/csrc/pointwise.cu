@@ -37,7 +37,9 @@ template <bool F16, bool SILU>
 __device__ __forceinline__ uint16_t pw_op(uint16_t a, uint16_t b) {
   const float fa = pw_to_f32<F16>(a), fb = pw_to_f32<F16>(b);
   if (!SILU) return pw_to_16<F16>(__fadd_rn(fa, fb));   // the fp32 sum of two 16-bit values is exact: one rounding
-  const float sig = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-fa)));
+  // fast exp and reciprocal: their error (a few units in the last place of fp32) is far below the
+  // rounding of the 16-bit result, and the full-precision forms made the kernel instruction-bound
+  const float sig = __fdividef(1.0f, 1.0f + __expf(-fa));
   return pw_to_16<F16>(__fmul_rn(__fmul_rn(sig, fa), fb));
 }
 template <bool F16, bool SILU>
