@@ -287,6 +287,8 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
     const uint32_t sCw = sC + q * (2 * L::C_WARP_BYTES);
     GroupCursor cur(ws.info, groups);
     uint32_t it = 0;
+    uint32_t nst = 0;   // stores committed by this warp: picks the staging buffer, so that `wait_read<1>` below
+                        // always frees the buffer about to be written, whatever number of chunks a tile stored
     bool ok = true, first = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       const bool moved = cur.seek(tile);
@@ -306,7 +308,7 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       const bool rows_live = m0 + q * 32 < cur.cur.x;
 #pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
+      for (int c = 0; rows_live && c < BN / 64; ++c) {   // a warp whose rows lie past m stages and stores nothing
         if (n0 + c * 64 >= cur.cur.y) break;   // columns past n: nothing to store (uniform per warp)
         uint32_t v0[32], v1[32];
         tmem_ld_32x32b_x32(t_row + c * 64, v0);
@@ -314,7 +316,8 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         tmem_wait_ld();
-        const uint32_t sbuf = sCw + (c & 1) * L::C_WARP_BYTES;
+        const uint32_t sbuf = sCw + (nst & 1) * L::C_WARP_BYTES;
+        ++nst;
         const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -333,7 +336,7 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && rows_live) {
+        if (lane == 0) {
           tma_store_2d(dC, sbuf, n0 + c * 64, m0 + q * 32);
           tma_store_commit();
         }
