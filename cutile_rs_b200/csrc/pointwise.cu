@@ -61,9 +61,28 @@ struct PwParams {
   int nv;          // 8-element vectors per row taken by the vector path
 };
 
-template <bool F16, bool SILU>
+// Vector index -> (row, vector within the row).  FLAT: the host folded dense tensors into one row, so no
+// division at all; otherwise a 32-bit division where the count allows it (a 64-bit one costs about as
+// many instructions as the rest of the vector's work).
+template <bool FLAT>
+__device__ __forceinline__ void pw_split(long long e, int nv, bool small, long long& row, int& v) {
+  if (FLAT) {
+    row = 0;
+    v = (int)e;
+  } else if (small) {
+    const uint32_t r = (uint32_t)e / (uint32_t)nv;
+    row = r;
+    v = (int)((uint32_t)e - r * (uint32_t)nv);
+  } else {
+    row = e / nv;
+    v = (int)(e - row * nv);
+  }
+}
+
+template <bool F16, bool SILU, bool FLAT>
 __global__ void __launch_bounds__(PW_THREADS) pointwise_kernel(const PwParams p) {
   const long long total_v = (long long)p.rows * p.nv;
+  const bool small = total_v <= 0x7fffffffLL;
   const long long step = (long long)gridDim.x * PW_THREADS;
   long long i = (long long)blockIdx.x * PW_THREADS + threadIdx.x;
   // four vectors per thread and pass, all loads first
@@ -73,8 +92,9 @@ __global__ void __launch_bounds__(PW_THREADS) pointwise_kernel(const PwParams p)
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const long long e = i + u * step;
-      const long long row = e / p.nv;
-      const int v = (int)(e - row * p.nv);
+      long long row;
+      int v;
+      pw_split<FLAT>(e, p.nv, small, row, v);
       qa[u] = __ldg(reinterpret_cast<const uint4*>(p.a + row * p.ld_a) + v);
       qb[u] = __ldg(reinterpret_cast<const uint4*>(p.b + row * p.ld_b) + v);
       off_o[u] = row * p.ld_out + (long long)v * 8;
@@ -83,8 +103,9 @@ __global__ void __launch_bounds__(PW_THREADS) pointwise_kernel(const PwParams p)
     for (int u = 0; u < 4; ++u) *reinterpret_cast<uint4*>(p.out + off_o[u]) = pw_op8<F16, SILU>(qa[u], qb[u]);
   }
   for (; i < total_v; i += step) {
-    const long long row = i / p.nv;
-    const int v = (int)(i - row * p.nv);
+    long long row;
+    int v;
+    pw_split<FLAT>(i, p.nv, small, row, v);
     const uint4 qa = __ldg(reinterpret_cast<const uint4*>(p.a + row * p.ld_a) + v);
     const uint4 qb = __ldg(reinterpret_cast<const uint4*>(p.b + row * p.ld_b) + v);
     *reinterpret_cast<uint4*>(p.out + row * p.ld_out + (long long)v * 8) = pw_op8<F16, SILU>(qa, qb);
@@ -122,11 +143,23 @@ int b200_pointwise_dispatch(int dtype, int op, void* out, const void* a, const v
   const uintptr_t al = reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b);
   const bool vec = (al & 15) == 0 && !(ld_out & 7) && !(ld_a & 7) && !(ld_b & 7);
   p.nv = vec ? cols / 8 : 0;
-  const long long work = (long long)rows * (p.nv > 0 ? p.nv : cols);
+  // dense tensors whose element count fits the vector index: one long row, no index division in the kernel
+  const bool flat = vec && cols % 8 == 0 && ld_out == cols && ld_a == cols && ld_b == cols &&
+                    (long long)rows * cols / 8 <= 0x7fffffffLL;
+  if (flat) {
+    p.nv = (int)((long long)rows * cols / 8);
+    p.cols = p.nv * 8;
+    p.rows = 1;
+  }
+  const long long work = (long long)p.rows * (p.nv > 0 ? p.nv : p.cols);
   long long ctas = (work + 4 * PW_THREADS - 1) / (4 * PW_THREADS);
   const long long cap = (long long)di->sm_count * 16;
   ctas = ctas < 1 ? 1 : (ctas > cap ? cap : ctas);
-#define B200_PW(F16_, SILU_) pointwise_kernel<F16_, SILU_><<<(unsigned)ctas, PW_THREADS, 0, stream>>>(p)
+#define B200_PW(F16_, SILU_)                                                               \
+  do {                                                                                     \
+    if (flat) pointwise_kernel<F16_, SILU_, true><<<(unsigned)ctas, PW_THREADS, 0, stream>>>(p);  \
+    else pointwise_kernel<F16_, SILU_, false><<<(unsigned)ctas, PW_THREADS, 0, stream>>>(p);      \
+  } while (0)
   if (dtype) {
     if (op) B200_PW(true, true); else B200_PW(true, false);
   } else {

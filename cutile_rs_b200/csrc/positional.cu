@@ -191,8 +191,8 @@ __device__ __noinline__ void rope_angles(float pos, const float* __restrict__ in
   }
 }
 
-template <bool F16>
-__global__ void __launch_bounds__(ROPE_THREADS, 4) qk_norm_rope_kv_kernel(const QkRopeParams p) {
+template <bool F16, int THREADS>
+__global__ void __launch_bounds__(THREADS, 1024 / THREADS) qk_norm_rope_kv_kernel(const QkRopeParams p) {
   __shared__ __align__(16) float s_cos[ROPE_MAX_HALF], s_sin[ROPE_MAX_HALF];
   const int s = blockIdx.x;
   const int base = p.pos_ptr ? (int)__ldg(p.pos_ptr) : p.position_start;
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(ROPE_THREADS, 4) qk_norm_rope_kv_kernel(const 
   };
   // Two rounds per iteration with all four loads issued first; the first iteration's loads go out
   // before the angles are evaluated, which do not depend on them.  64 bytes in flight per thread
-  // and four CTAs per SM are what it takes to keep HBM busy at one position per CTA.
+  // and 1024 resident threads per SM are what it takes to keep HBM busy at one position per CTA.
   int i0 = warp * heads_per_warp;
   int ia = i0 + lane / lanes, ib = ia + step;
   uint4 alo = make_uint4(0, 0, 0, 0), ahi = alo, blo = alo, bhi = alo;
@@ -340,10 +340,17 @@ int b200_qk_norm_rope_kv_dispatch(int dtype, const void* q, const void* k, const
   p.v_ss = v_ss;
   p.qo_ss = qo_ss;
   p.eps = eps;
-  if (dtype)
-    qk_norm_rope_kv_kernel<true><<<(unsigned)seq, ROPE_THREADS, 0, stream>>>(p);
-  else
-    qk_norm_rope_kv_kernel<false><<<(unsigned)seq, ROPE_THREADS, 0, stream>>>(p);
+  // One CTA per position.  Prefill: small CTAs (64 threads, 16 per SM) drift apart, so the loads of some
+  // overlap the arithmetic of others; 256-thread CTAs moved in step and reached 0.6 of the HBM rate where
+  // these reach 0.77.  Few positions (decode): one wide CTA per position finishes its heads in one pass.
+#define B200_QK(T_)                                                                     \
+  do {                                                                                  \
+    if (dtype) qk_norm_rope_kv_kernel<true, T_><<<(unsigned)seq, T_, 0, stream>>>(p);   \
+    else qk_norm_rope_kv_kernel<false, T_><<<(unsigned)seq, T_, 0, stream>>>(p);        \
+  } while (0)
+  if (seq >= 512) B200_QK(64);
+  else B200_QK(256);
+#undef B200_QK
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
