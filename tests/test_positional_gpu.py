@@ -112,6 +112,8 @@ def _qk_case(seq, qh, kvh, d, max_seq, dtype, seed):
 @pytest.mark.parametrize("seq,qh,kvh,d,max_seq,pos,dtype", [
     (40, 32, 8, 128, 256, 100, torch.float16), (7, 5, 3, 64, 64, 0, torch.float16),
     (3, 4, 4, 256, 16, 13, torch.bfloat16), (9, 2, 1, 16, 32, 5, torch.float16),
+    # 512 positions and more take the small-CTA configuration of the kernel
+    (600, 8, 2, 128, 640, 17, torch.float16), (512, 3, 1, 64, 512, 0, torch.bfloat16),
 ])
 def test_qk_norm_rope_kv_prefill(b200, oracle, seq, qh, kvh, d, max_seq, pos, dtype):
     q, k, v, qw, kw, kc, vc = _qk_case(seq, qh, kvh, d, max_seq, dtype, seq + d)
