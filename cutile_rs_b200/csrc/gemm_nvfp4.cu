@@ -47,11 +47,18 @@ constexpr int F4_THREADS = 448;  // TMA, MMA, 4 epilogue warps, two sets of 4 sc
 // scale bytes: one MMA's scales for NVFP4, the whole stage's (one byte per MMA) for MXFP8.
 // A_DIRECT: A's scales are read in place by the writer warps (no pre-pass, no scratch: decode-sized M
 // and the prepared-weights entry); otherwise they come re-laid-out from scratch with the stage's TMA.
-template <int BN, bool FP4 = true, bool A_DIRECT = false>
+// AROWS: rows of the A tile that are loaded (the TMA box).  The MMA always reads 128 rows; with AROWS < 128
+// (decode-sized M) the rows past the box are whatever follows in the stage (the B tile), their scales are
+// zero and their results are never stored, and the shared memory saved buys a ring nearly twice as deep,
+// which is what a call bound by the latency of the weight stream needs.
+template <int BN, bool FP4 = true, bool A_DIRECT = false, int AROWS = 128>
 struct Fp4Cfg {
+  static_assert(AROWS == 128 || (AROWS % 8 == 0 && AROWS * 128 + BN * 128 >= 128 * 128),
+                "a short A tile must be followed by enough of the B tile for the MMA's 128-row read");
   static constexpr int CHUNKS = (BN + 127) / 128;            // 128-row scale blocks per B tile
   static constexpr int KQ_PER_STAGE = FP4 ? 4 : 1;           // scale blocks along K per stage
-  static constexpr int STAGES_ = (BN <= 128) ? 5 : 4;   // 3 instead of 4 measured 9 % slower at BN = 192
+  static constexpr int STAGES_ = AROWS < 128 ? ((BN <= 128) ? 9 : (BN <= 192 ? 6 : 5))
+                                             : ((BN <= 128) ? 5 : 4);   // 3 instead of 4 measured 9 % slower at BN = 192
   // Scales travel to Tensor Memory in REGIONS of RK scale blocks along K (half a stage for NVFP4, a
   // whole one for MXFP8); the columns left beside the accumulators form a ring of NREG regions so
   // that the writers run ahead of the MMAs.  NREG < STAGES * HALVES keeps a writer's wait on a
@@ -65,7 +72,7 @@ struct Fp4Cfg {
   static constexpr int NREG_FIT = (512 - NACC * BN) / REGION_COLS;
   static constexpr int NREG = NREG_FIT < STAGES_ * HALVES - 1 ? NREG_FIT : STAGES_ * HALVES - 1;
   static_assert(NREG >= 2, "at least two scale regions");
-  static constexpr int A_BYTES = F4_BM * 128;
+  static constexpr int A_BYTES = AROWS * 128;
   static constexpr int B_BYTES = BN * 128;
   static constexpr int SFA_BYTES = A_DIRECT ? 0 : KQ_PER_STAGE * 512;
   static constexpr int SFB_BYTES = KQ_PER_STAGE * CHUNKS * 512;
@@ -141,13 +148,13 @@ __host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) 
   return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (0u << 23) | ((M >> 4) << 24);
 }
 
-template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT>
+template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT, int AROWS>
 __global__ void __launch_bounds__(F4_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const uint8_t* __restrict__ xs, int64_t ld_xs, int kq_valid, const uint8_t* __restrict__ sfa,
                   const uint8_t* __restrict__ sfb, void* __restrict__ Z,
                   int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
-  using C = Fp4Cfg<BN, FP4, A_DIRECT>;
+  using C = Fp4Cfg<BN, FP4, A_DIRECT, AROWS>;
   constexpr int STAGES = C::STAGES;
   constexpr int STAGE_ELEMS = FP4 ? 256 : 128;  // K elements per 128-byte row
   extern __shared__ uint8_t smem_raw[];
@@ -501,18 +508,18 @@ static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offs
 
 // b_scales_prepared: `scratch` IS the tile layout of the B scales (written once by the caller); A's
 // scales are then read in place whatever M is, so that the call needs no workspace at all.
-template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT>
+template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT, int AROWS = 128>
 static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
                              int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys,
                              float alpha, uint8_t* scratch, cudaStream_t stream, bool b_scales_prepared) {
-  using C = Fp4Cfg<BN, FP4, A_DIRECT>;
+  using C = Fp4Cfg<BN, FP4, A_DIRECT, AROWS>;
   const b200h::DeviceInfo* di = b200h::device_info();
   const uint64_t row_bytes = FP4 ? (uint64_t)K / 2 : (uint64_t)K;
   if (!di) return B200_ERR_CUDA;
   CUtensorMap tmA, tmB;
   int rc;
   if ((rc = b200h::encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, row_bytes, (uint64_t)M,
-                                  (uint64_t)ldx, 128, F4_BM, CU_TENSOR_MAP_SWIZZLE_128B)))
+                                  (uint64_t)ldx, 128, AROWS, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, row_bytes, (uint64_t)N,
                                   (uint64_t)ldy, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B)))
@@ -535,7 +542,7 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
                                                          reinterpret_cast<uint32_t*>(scratch + sfb_off));
   }
   B200_CUDA_CHECK(cudaGetLastError());
-  auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4, A_DIRECT>;
+  auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4, A_DIRECT, AROWS>;
   static bool attr_done[64] = {};
   if (!attr_done[di->ordinal]) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
@@ -554,6 +561,11 @@ static int launch_nvfp4(const void* x, const void* y, const void* xs, const void
                         int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha,
                         uint8_t* scratch, cudaStream_t stream, bool b_scales_prepared = false) {
   // same rule as nvfp4_scratch_layout: one tile row of A, or prepared weights => A's scales in place
+  if constexpr (FP4 && BN == 128) {
+    if (M <= 32)   // decode: short A tile, deep ring
+      return launch_nvfp4_impl<BN, OUT_F32, FP4, true, 32>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys,
+                                                           alpha, scratch, stream, b_scales_prepared);
+  }
   if (M <= F4_BM || b_scales_prepared)
     return launch_nvfp4_impl<BN, OUT_F32, FP4, true>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha,
                                                      scratch, stream, b_scales_prepared);
