@@ -509,7 +509,9 @@ int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales, co
     return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4: output must be 16-byte aligned with a 16-byte pitch");
   if (config < -1 || config > 2)
     return set_error(B200TILE_ERR_UNSUPPORTED, "linear_nvfp4: unknown config %d", config);
-  if (config < 0) config = 1;
+  // default: 192-row B tiles; decode-sized M takes 128-row tiles (more CTAs for the weight stream, and the
+  // short-A-tile configuration of the kernel exists for that tile only)
+  if (config < 0) config = m <= 32 ? 0 : 1;
   const int bn = kNvfp4Bn[config];
   const size_t need = b200_nvfp4_scratch_bytes(m, n, k, bn);
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)

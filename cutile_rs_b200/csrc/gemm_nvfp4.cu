@@ -676,7 +676,7 @@ extern "C" int b200tile_linear_nvfp4_static(const void* x, const void* y, const 
   if (config < -1 || config > 2)
     return b200h::set_error(B200_ERR_UNSUPPORTED, "linear_nvfp4_static: unknown config %d", config);
   static const int kBn[3] = {128, 192, 256};
-  const int bn = kBn[config < 0 ? 1 : config];
+  const int bn = kBn[config < 0 ? (m <= 32 ? 0 : 1) : config];   // the default of b200tile_linear_nvfp4
   const size_t need = b200::nvfp4_scratch_layout(m, n, k, bn, nullptr);
   if (need > (size_t)B200TILE_NVFP4_STATIC_SCRATCH_BYTES)
     return b200h::set_error(B200_ERR_INVALID,
