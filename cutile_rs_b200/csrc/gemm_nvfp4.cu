@@ -95,23 +95,38 @@ struct Fp4Cfg {
 __global__ void nvfp4_relayout_scales_kernel(const uint8_t* __restrict__ src, int rows, int kq_count,
                                              int kq_valid, int64_t ld, int tile_rows, int chunks,
                                              int num_tiles, uint32_t* __restrict__ dst) {
-  const int64_t total = (int64_t)num_tiles * kq_count * chunks * 128;  // words
-  for (int64_t w = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; w < total;
-       w += (int64_t)gridDim.x * blockDim.x) {
-    const int word = (int)(w & 127);             // word inside the 512-byte block
-    const int64_t blk = w >> 7;
-    const int c = (int)(blk % chunks);
-    const int64_t t_kq = blk / chunks;
-    const int kq = (int)(t_kq % kq_count);
-    const int tile = (int)(t_kq / kq_count);
-    const int r32 = word >> 2, g = word & 3;
-    const int local = c * 128 + g * 32 + r32;
-    const int row = tile * tile_rows + local;
+  // Work item = (tile, group of 8 scale blocks along K, chunk, block of the group, word): the 1024 threads of
+  // a CTA read 32 consecutive bytes of each of 128 rows (whole sectors, shared through L1) and every warp
+  // writes 128 consecutive bytes.  32-bit index arithmetic: the 64-bit divisions of a first version cost
+  // more than the copy itself.
+  const uint32_t kq_groups = (uint32_t)(kq_count + 7) / 8;
+  const uint32_t total = (uint32_t)num_tiles * kq_groups * (uint32_t)chunks * 1024u;   // checked on the host
+  for (uint32_t w = blockIdx.x * blockDim.x + threadIdx.x; w < total; w += gridDim.x * blockDim.x) {
+    const uint32_t word = w & 127u;              // word inside the 512-byte block
+    const uint32_t kq_lo = (w >> 7) & 7u;
+    const uint32_t rest = w >> 10;
+    const uint32_t c = rest % (uint32_t)chunks;
+    const uint32_t t_kg = rest / (uint32_t)chunks;
+    const uint32_t kq = (t_kg % kq_groups) * 8u + kq_lo;
+    const uint32_t tile = t_kg / kq_groups;
+    if (kq >= (uint32_t)kq_count) continue;
+    const int r32 = (int)(word >> 2), g = (int)(word & 3u);
+    const int local = (int)c * 128 + g * 32 + r32;
+    const int row = (int)tile * tile_rows + local;
     uint32_t v = 0;
-    if (local < tile_rows && row < rows && kq < kq_valid)
+    if (local < tile_rows && row < rows && (int)kq < kq_valid)
       v = *reinterpret_cast<const uint32_t*>(src + (int64_t)row * ld + (int64_t)kq * 4);
-    dst[w] = v;
+    dst[((size_t)(tile * (uint32_t)kq_count + kq) * (uint32_t)chunks + c) * 128u + word] = v;
   }
+}
+
+// Launch shape of the pre-pass: 1024-thread CTAs, one per 8 scale blocks along K of a 128-row chunk.
+static inline int nvfp4_relayout_grid(int num_tiles, int kq_count, int chunks) {
+  const long long ctas = (long long)num_tiles * ((kq_count + 7) / 8) * chunks;
+  return (int)(ctas < 1 ? 1 : (ctas > 65535 ? 65535 : ctas));
+}
+static inline bool nvfp4_relayout_fits(int num_tiles, int kq_count, int chunks) {
+  return (long long)num_tiles * ((kq_count + 7) / 8) * chunks * 1024 < 0x7fffffffLL;
 }
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -529,17 +544,17 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
   const int tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
   const size_t sfb_off = A_DIRECT ? 0 : (size_t)tiles_m * kq * 512;
   if (!A_DIRECT) {
-    const int64_t words_a = (int64_t)tiles_m * kq * 128;
-    const int ga = (int)((words_a + 255) / 256 < 4096 ? (words_a + 255) / 256 : 4096);
-    nvfp4_relayout_scales_kernel<<<ga, 256, 0, stream>>>(static_cast<const uint8_t*>(xs), M, kq, kq_valid, ld_xs, F4_BM,
-                                                         1, tiles_m, reinterpret_cast<uint32_t*>(scratch));
+    if (!nvfp4_relayout_fits(tiles_m, kq, 1))
+      return b200h::set_error(B200_ERR_UNSUPPORTED, "block-scaled GEMM: scale tensor of A too large for the pre-pass");
+    nvfp4_relayout_scales_kernel<<<nvfp4_relayout_grid(tiles_m, kq, 1), 1024, 0, stream>>>(
+        static_cast<const uint8_t*>(xs), M, kq, kq_valid, ld_xs, F4_BM, 1, tiles_m, reinterpret_cast<uint32_t*>(scratch));
   }
   if (!b_scales_prepared) {
-    const int64_t words_b = (int64_t)tiles_n * kq * C::CHUNKS * 128;
-    const int gb = (int)((words_b + 255) / 256 < 4096 ? (words_b + 255) / 256 : 4096);
-    nvfp4_relayout_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, BN,
-                                                         C::CHUNKS, tiles_n,
-                                                         reinterpret_cast<uint32_t*>(scratch + sfb_off));
+    if (!nvfp4_relayout_fits(tiles_n, kq, C::CHUNKS))
+      return b200h::set_error(B200_ERR_UNSUPPORTED, "block-scaled GEMM: scale tensor of B too large for the pre-pass");
+    nvfp4_relayout_scales_kernel<<<nvfp4_relayout_grid(tiles_n, kq, C::CHUNKS), 1024, 0, stream>>>(
+        static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, BN, C::CHUNKS, tiles_n,
+        reinterpret_cast<uint32_t*>(scratch + sfb_off));
   }
   B200_CUDA_CHECK(cudaGetLastError());
   auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4, A_DIRECT, AROWS>;
@@ -580,10 +595,10 @@ int b200_nvfp4_prepare_b_scales(const void* ys, int N, int K, int64_t ld_ys, int
   using namespace b200;
   const int kq = ((K + 255) / 256) * 4, kq_valid = K / 64;
   const int tiles_n = (N + bn - 1) / bn, chunks = (bn + 127) / 128;
-  const int64_t words_b = (int64_t)tiles_n * kq * chunks * 128;
-  const int gb = (int)((words_b + 255) / 256 < 4096 ? (words_b + 255) / 256 : 4096);
-  nvfp4_relayout_scales_kernel<<<gb, 256, 0, stream>>>(static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, bn,
-                                                       chunks, tiles_n, static_cast<uint32_t*>(out));
+  if (!nvfp4_relayout_fits(tiles_n, kq, chunks))
+    return b200h::set_error(B200_ERR_UNSUPPORTED, "nvfp4_prepare_weight_scales: scale tensor too large for the pre-pass");
+  nvfp4_relayout_scales_kernel<<<nvfp4_relayout_grid(tiles_n, kq, chunks), 1024, 0, stream>>>(
+      static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, bn, chunks, tiles_n, static_cast<uint32_t*>(out));
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
