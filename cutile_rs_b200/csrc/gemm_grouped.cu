@@ -6,14 +6,28 @@
 // eight i32 per group ({rows, cols, row stride, ...}, moe.rs:27-63).  Nothing about the groups is
 // known on the host, so the work is split in two launches:
 //
-//   grouped_prepare_kernel   CTA 0: tile counts and their prefix sum; every warp of the grid: for one group three
-//                            TMA descriptors made on the device from host-encoded templates
-//                            (`tensormap.replace` in shared memory, published to the workspace with
-//                            `tensormap.cp_fenceproxy`)
-//   gemm_grouped_kernel      the persistent warp-specialised GEMM of gemm_tc.cu (TMA ring ->
-//                            tcgen05.mma into two TMEM accumulators -> TMA-store epilogue) walking
-//                            the concatenated tile list of all groups, tile t of the list going to
-//                            CTA t mod grid like the reference's `tile_idx += NUM_SM`
+//   grouped_prepare_kernel   one CTA: validates every group's pointers and pitches (16-byte rule),
+//                            computes the tile counts and their exclusive prefix sum into the workspace
+//   gemm_grouped_kernel      persistent warp-specialised GEMM walking the concatenated tile list of all
+//                            groups, tile t of the list going to CTA t mod grid like the reference's
+//                            `tile_idx += NUM_SM`
+//
+// No TMA descriptor is involved: with per-group base addresses, extents and pitches that exist only
+// in device memory a descriptor would have to be built on the device for every group.  Instead four
+// producer warps fill the operand ring with 16-byte `cp.async` copies whose addresses are computed
+// from the table entries and checked against the group's extents in the kernel (rows, columns and
+// k past the extents are zero-filled by the copy's source-size operand, never read), writing the
+// same 128-byte-swizzled layout that the tensor core's shared-memory descriptors expect.  The
+// epilogue goes tcgen05.ld -> 16-bit -> swizzled staging -> 16-byte global stores, clipped to
+// [m_g, n_g].  Every address the kernel touches is therefore ptr_g + (row < rows_g) * pitch_g +
+// (col < cols_g).
+//
+//   warps 0..3  producers: cp.async ring, completion handed to the MMA thread through the `full`
+//               barrier after cp.async.wait_group + fence.proxy.async (generic -> async proxy)
+//   warp 4      MMA issuer: tcgen05.mma kind::f16 into two TMEM accumulator buffers
+//   warps 5..8  epilogue
+#include <atomic>
+
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
@@ -21,125 +35,73 @@ namespace b200 {
 
 constexpr int GG_BM = 128;
 constexpr int GG_BK = 64;
-constexpr int GG_THREADS = 192;
+constexpr int GG_PRODUCERS = 128;
+constexpr int GG_THREADS = GG_PRODUCERS + 32 + 128;
 constexpr int GG_PREP_THREADS = 256;
+constexpr int GG_LAG = 2;   // a producer thread hands a stage over after issuing this many later ones
 
-// Workspace layout: descriptors first (128-byte records), then one int4 {m, n, k, first tile} per
-// group and a closing record whose .w is the total tile count.
+enum : uint32_t { ST_BAD_GROUP = 3 };   // status code: a group's pointer or pitch breaks the 16-byte rule
+
+// Workspace: one int4 {m, n, k, first tile} per group and a closing record whose .w is the total
+// tile count.  A group that fails validation gets m = 0 (no tiles, nothing stored).
 struct GroupedWs {
-  CUtensorMap* desc;  // [groups][3]: A, B, C
-  int4* info;         // [groups + 1]
+  int4* info;  // [groups + 1]
 };
-__host__ __device__ inline size_t grouped_desc_bytes(int groups) { return (size_t)groups * 3 * 128; }
-__host__ __device__ inline size_t grouped_ws_bytes(int groups) {
-  return grouped_desc_bytes(groups) + (size_t)(groups + 1) * sizeof(int4);
-}
-
-__device__ __forceinline__ void tmap_replace_addr(uint32_t smem_desc, uint64_t addr) {
-  asm volatile("tensormap.replace.tile.global_address.shared::cta.b1024.b64 [%0], %1;" ::"r"(smem_desc), "l"(addr)
-               : "memory");
-}
-__device__ __forceinline__ void tmap_replace_dims(uint32_t smem_desc, uint32_t dim0, uint32_t dim1) {
-  asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 0, %1;" ::"r"(smem_desc), "r"(dim0)
-               : "memory");
-  asm volatile("tensormap.replace.tile.global_dim.shared::cta.b1024.b32 [%0], 1, %1;" ::"r"(smem_desc), "r"(dim1)
-               : "memory");
-}
-// pitch of dimension 1 in bytes (a multiple of 16)
-__device__ __forceinline__ void tmap_replace_stride(uint32_t smem_desc, uint64_t bytes) {
-  asm volatile("tensormap.replace.tile.global_stride.shared::cta.b1024.b64 [%0], 0, %1;" ::"r"(smem_desc), "l"(bytes)
-               : "memory");
-}
-// whole warp: copies the 128-byte record to global memory and releases it to the tensormap proxy
-__device__ __forceinline__ void tmap_publish(void* gmem_desc, uint32_t smem_desc) {
-  asm volatile(
-      "tensormap.cp_fenceproxy.global.shared::cta.tensormap::generic.release.gpu.sync.aligned [%0], [%1], 128;"
-      ::"l"(gmem_desc), "r"(smem_desc)
-      : "memory");
-}
-__device__ __forceinline__ void tmap_acquire(const void* gmem_desc) {
-  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(gmem_desc) : "memory");
-}
+__host__ __device__ inline size_t grouped_ws_bytes(int groups) { return (size_t)(groups + 1) * sizeof(int4); }
 
 template <int BN>
 __global__ void __launch_bounds__(GG_PREP_THREADS)
-grouped_prepare_kernel(const __grid_constant__ CUtensorMap tplA, const __grid_constant__ CUtensorMap tplB,
-                       const __grid_constant__ CUtensorMap tplC, const int64_t* a_ptrs, const int64_t* b_ptrs,
-                       const int64_t* c_ptrs, const int32_t* a_metas, const int32_t* b_metas,
-                       const int32_t* c_metas, int groups, GroupedWs ws) {
-  __shared__ __align__(128) uint8_t s_desc[GG_PREP_THREADS / 32][3][128];
+grouped_prepare_kernel(const int64_t* a_ptrs, const int64_t* b_ptrs, const int64_t* c_ptrs, const int32_t* a_metas,
+                       const int32_t* b_metas, const int32_t* c_metas, int groups, GroupedWs ws, uint32_t* status) {
   __shared__ int s_warp_sum[GG_PREP_THREADS / 32];
   __shared__ int s_carry;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) s_carry = 0;
   __syncthreads();
-
-  // ---- CTA 0: extents and the exclusive prefix sum of the tile counts ----
-  if (blockIdx.x == 0) {
-    for (int g0 = 0; g0 < groups; g0 += GG_PREP_THREADS) {
-      const int g = g0 + tid;
-      int m = 0, n = 0, k = 0, tiles = 0;
-      if (g < groups) {
-        m = a_metas[g * 8 + 0];
-        k = a_metas[g * 8 + 1];
-        n = b_metas[g * 8 + 1];
-        if (m < 0) m = 0;
-        if (n < 0) n = 0;
-        if (k < 0) k = 0;
-        tiles = ((m + GG_BM - 1) / GG_BM) * ((n + BN - 1) / BN);
+  for (int g0 = 0; g0 < groups; g0 += GG_PREP_THREADS) {
+    const int g = g0 + tid;
+    int m = 0, n = 0, k = 0, tiles = 0;
+    if (g < groups) {
+      m = a_metas[g * 8 + 0];
+      k = a_metas[g * 8 + 1];
+      n = b_metas[g * 8 + 1];
+      if (m < 0) m = 0;
+      if (n < 0) n = 0;
+      if (k < 0) k = 0;
+      const int lda = a_metas[g * 8 + 2], ldb = b_metas[g * 8 + 2], ldc = c_metas[g * 8 + 2];
+      const uint64_t pa = (uint64_t)a_ptrs[g], pb = (uint64_t)b_ptrs[g], pc = (uint64_t)c_ptrs[g];
+      const bool live = m > 0 && n > 0;
+      // 16-byte copies: bases and pitches must be multiples of 16 bytes, pitches must cover a row
+      // (with k = 0 the operands are never read, only C is written)
+      const bool bad_ab = k > 0 && (((pa | pb) & 15) != 0 || pa == 0 || pb == 0 || (lda & 7) || (ldb & 7) || lda < k ||
+                                    ldb < n);
+      const bool bad = live && (bad_ab || (pc & 15) != 0 || pc == 0 || (ldc & 7) || ldc < n);
+      if (bad) {
+        if (atomicCAS(status, 0u, (uint32_t)ST_BAD_GROUP) == 0u) {
+          status[1] = 0;
+          status[2] = (uint32_t)g;   // the offending group
+          status[3] = 0;
+        }
+        m = 0;
       }
-      int scan = tiles;
+      tiles = ((m + GG_BM - 1) / GG_BM) * ((n + BN - 1) / BN);
+    }
+    int scan = tiles;
 #pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, scan, off);
-        if (lane >= off) scan += v;
-      }
-      if (lane == 31) s_warp_sum[warp] = scan;
-      __syncthreads();
-      int before = s_carry;
-      for (int w = 0; w < warp; ++w) before += s_warp_sum[w];
-      if (g < groups) ws.info[g] = make_int4(m, n, k, before + scan - tiles);
-      __syncthreads();
-      if (tid == GG_PREP_THREADS - 1) s_carry = before + scan;
-      __syncthreads();
+    for (int off = 1; off < 32; off <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, scan, off);
+      if (lane >= off) scan += v;
     }
-    if (tid == 0) ws.info[groups] = make_int4(0, 0, 0, s_carry);
+    if (lane == 31) s_warp_sum[warp] = scan;
+    __syncthreads();
+    int before = s_carry;
+    for (int w = 0; w < warp; ++w) before += s_warp_sum[w];
+    if (g < groups) ws.info[g] = make_int4(m, n, k, before + scan - tiles);
+    __syncthreads();
+    if (tid == GG_PREP_THREADS - 1) s_carry = before + scan;
+    __syncthreads();
   }
-
-  // ---- descriptors: every warp of the grid builds ONE group's three records.  A warp's shared-memory
-  // slot is written once and never reused, so nothing can overwrite a record that is still being
-  // copied out (a loop that reused the slot produced corrupt descriptors now and then when there were
-  // more groups than warps). ----
-  const int g = blockIdx.x * (GG_PREP_THREADS / 32) + warp;
-  if (g < groups) {
-    const uint32_t sd = smem_u32(&s_desc[warp][0][0]);
-    // templates -> shared memory, four bytes per lane and descriptor
-    reinterpret_cast<uint32_t*>(&s_desc[warp][0][0])[lane] = reinterpret_cast<const uint32_t*>(&tplA)[lane];
-    reinterpret_cast<uint32_t*>(&s_desc[warp][1][0])[lane] = reinterpret_cast<const uint32_t*>(&tplB)[lane];
-    reinterpret_cast<uint32_t*>(&s_desc[warp][2][0])[lane] = reinterpret_cast<const uint32_t*>(&tplC)[lane];
-    __syncwarp();
-    if (lane == 0) {
-      // extents of an empty group are never used by a copy; keep them legal for the descriptor
-      const uint32_t m = max(a_metas[g * 8 + 0], 1), k = max(a_metas[g * 8 + 1], 1);
-      const uint32_t n = max(b_metas[g * 8 + 1], 1);
-      const uint64_t lda = (uint64_t)max(a_metas[g * 8 + 2], 8), ldb = (uint64_t)max(b_metas[g * 8 + 2], 8);
-      const uint64_t ldc = (uint64_t)max(c_metas[g * 8 + 2], 8);
-      tmap_replace_addr(sd, (uint64_t)a_ptrs[g]);
-      tmap_replace_dims(sd, k, m);
-      tmap_replace_stride(sd, lda * 2);
-      tmap_replace_addr(sd + 128, (uint64_t)b_ptrs[g]);
-      tmap_replace_dims(sd + 128, n, k);
-      tmap_replace_stride(sd + 128, ldb * 2);
-      tmap_replace_addr(sd + 256, (uint64_t)c_ptrs[g]);
-      tmap_replace_dims(sd + 256, n, m);
-      tmap_replace_stride(sd + 256, ldc * 2);
-    }
-    __syncwarp();
-    tmap_publish(&ws.desc[g * 3 + 0], sd);
-    tmap_publish(&ws.desc[g * 3 + 1], sd + 128);
-    tmap_publish(&ws.desc[g * 3 + 2], sd + 256);
-    __syncwarp();
-  }
+  if (tid == 0) ws.info[groups] = make_int4(0, 0, 0, s_carry);
 }
 
 // Cursor over the concatenated tile list: advances to the group that holds `tile`.
@@ -179,12 +141,26 @@ struct GroupedSmem {
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
+  static_assert(GG_LAG < STAGES, "a stage must be handed over before the ring wraps onto it");
 };
+
+// 16-byte asynchronous copy global -> shared; bytes past `src_bytes` (0..16) are written as zeros and
+// not read.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // B is [k, n] row-major (the N-major UMMA operand), as in the reference kernel's `b.partition([BK, BN])`.
 template <int BN, bool OUT_F16>
 __global__ void __launch_bounds__(GG_THREADS, 1)
-gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) {
+gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, const int64_t* c_ptrs,
+                    const int32_t* a_metas, const int32_t* b_metas, const int32_t* c_metas, int groups, uint32_t idesc,
+                    uint32_t* status) {
   using L = GroupedSmem<BN>;
   constexpr int STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -204,7 +180,7 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_full + s * 8, GG_PRODUCERS);
       mbar_init(bar_empty + s * 8, 1);
     }
     for (int b = 0; b < 2; ++b) {
@@ -214,7 +190,7 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
     misc[1] = 0;
     fence_mbar_init();
   }
-  if (warp == 1) {
+  if (warp == 4) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(misc)), 2 * BN);
     tmem_relinquish();
   }
@@ -223,38 +199,92 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
   tc_fence_after_sync();
   const uint32_t tmem_base = misc[0];
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      GroupCursor cur(ws.info, groups);
-      uint32_t stage = 0, phase = 0;
-      bool ok = true, first = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const bool moved = cur.seek(tile);
-        const CUtensorMap* dA = ws.desc + cur.g * 3;
-        const CUtensorMap* dB = dA + 1;
-        if (moved || first) {
-          tmap_acquire(dA);
-          tmap_acquire(dB);
-          first = false;
-        }
-        const int tiles_n = (cur.cur.y + BN - 1) / BN;
-        const int local = tile - cur.cur.w;
-        const int m0 = (local / tiles_n) * GG_BM, n0 = (local % tiles_n) * BN;
-        const int num_kb = (cur.cur.z + GG_BK - 1) / GG_BK;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
-          const uint32_t full = bar_full + stage * 8;
-          mbar_expect_tx(full, L::A_BYTES + L::B_BYTES);
-          tma_load_2d(sA + stage * L::A_BYTES, dA, full, kb * GG_BK, m0);
+  if (warp < 4) {
+    // ------------------------------ producers ------------------------------
+    // Thread t owns 16-byte chunk (t & 7) of rows (t >> 3) + 16 i of every 128-byte-wide operand box, so
+    // the eight threads of a row read 128 contiguous bytes.  A box row r keeps chunk c at byte
+    // r * 128 + ((c ^ (r & 7)) << 4): the 128-byte swizzle; r & 7 does not depend on i.
+    const int t = threadIdx.x;
+    const int ch = t & 7, r0 = t >> 3;
+    const uint32_t soff = (uint32_t)r0 * 128u + (uint32_t)((ch ^ (r0 & 7)) << 4);
+    GroupCursor cur(ws.info, groups);
+    const uint16_t* pa = nullptr;
+    const uint16_t* pb = nullptr;
+    int64_t lda = 0, ldb = 0;
+    uint32_t issued = 0, arrived = 0;   // stages issued / handed over by this thread
+    bool ok = true, first = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      if (cur.seek(tile) || first) {
+        first = false;
+        pa = reinterpret_cast<const uint16_t*>(__ldg(a_ptrs + cur.g));
+        pb = reinterpret_cast<const uint16_t*>(__ldg(b_ptrs + cur.g));
+        lda = __ldg(a_metas + cur.g * 8 + 2);
+        ldb = __ldg(b_metas + cur.g * 8 + 2);
+      }
+      const int m = cur.cur.x, n = cur.cur.y, k = cur.cur.z;
+      const int tiles_n = (n + BN - 1) / BN;
+      const int local = tile - cur.cur.w;
+      const int m0 = (local / tiles_n) * GG_BM, n0 = (local % tiles_n) * BN;
+      const int num_kb = (k + GG_BK - 1) / GG_BK;
+      // A: rows m0 + r0 + 16 i (i < 8); the row mask is fixed for the tile
+      uint32_t a_rows = 0;
 #pragma unroll
-          for (int j = 0; j < BN / 64; ++j)
-            tma_load_2d(sB + stage * L::B_BYTES + j * (GG_BK * 128), dB, full, n0 + j * 64, kb * GG_BK);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      for (int i = 0; i < GG_BM / 16; ++i)
+        if (m0 + r0 + 16 * i < m) a_rows |= 1u << i;
+      const uint16_t* a_src = pa + (int64_t)(m0 + r0) * lda + ch * 8;
+      // B: box j holds columns n0 + 64 j + [0, 64); this thread's chunk starts at column bcol + 64 j
+      const int bcol = n0 + ch * 8;
+      const uint16_t* b_src = pb + bcol;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const uint32_t stage = issued % STAGES;
+        if (!mbar_wait(wctx, bar_empty + stage * 8, ((issued / STAGES) & 1) ^ 1, 1)) { ok = false; break; }
+        const int k0 = kb * GG_BK;
+        // ---- A box: 128 rows x 64 k ----
+        {
+          const int left = (k - k0 - ch * 8) * 2;   // bytes of this chunk inside [0, k)
+          const uint32_t kbytes = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+          const uint32_t dst = sA + stage * L::A_BYTES + soff;
+#pragma unroll
+          for (int i = 0; i < GG_BM / 16; ++i) {
+            const bool live = ((a_rows >> i) & 1u) && kbytes;
+            cp_async_16(dst + i * 2048, live ? (const void*)(a_src + (int64_t)(16 * i) * lda + k0) : (const void*)pa,
+                        live ? kbytes : 0u);
+          }
+        }
+        // ---- B boxes: 64 k rows x 64 columns each ----
+        {
+          const uint32_t dst = sB + stage * L::B_BYTES + soff;
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j) {
+            const int left = (n - bcol - 64 * j) * 2;
+            const uint32_t nbytes = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int kr = k0 + r0 + 16 * i;
+              const bool live = kr < k && nbytes;
+              cp_async_16(dst + j * (GG_BK * 128) + i * 2048,
+                          live ? (const void*)(b_src + (int64_t)kr * ldb + 64 * j) : (const void*)pb, live ? nbytes : 0u);
+            }
+          }
+        }
+        cp_async_commit();
+        ++issued;
+        if (issued - arrived > (uint32_t)GG_LAG) {
+          cp_async_wait<GG_LAG>();
+          fence_proxy_async_smem();
+          mbar_arrive(bar_full + (arrived % STAGES) * 8);
+          ++arrived;
         }
       }
     }
-  } else if (warp == 1) {
+    // hand over what is still in flight (also after a wait that gave up: nothing may stay in flight)
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    while (arrived < issued) {
+      mbar_arrive(bar_full + (arrived % STAGES) * 8);
+      ++arrived;
+    }
+  } else if (warp == 4) {
     // ------------------------------- MMA issuer --------------------------------
     if (lane == 0) {
       GroupCursor cur(ws.info, groups);
@@ -283,22 +313,21 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
     }
   } else {
     // -------------------------------- epilogue ---------------------------------
-    const int q = warp & 3;
+    const int q = warp & 3;   // the TMEM lane quarter this warp may read
     const uint32_t sCw = sC + q * (2 * L::C_WARP_BYTES);
     GroupCursor cur(ws.info, groups);
-    uint32_t it = 0;
-    uint32_t nst = 0;   // stores committed by this warp: picks the staging buffer, so that `wait_read<1>` below
-                        // always frees the buffer about to be written, whatever number of chunks a tile stored
+    uint16_t* pc = nullptr;
+    int64_t ldc = 0;
+    uint32_t it = 0, nst = 0;
     bool ok = true, first = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      const bool moved = cur.seek(tile);
-      const CUtensorMap* dC = ws.desc + cur.g * 3 + 2;
-      if (moved || first) {
-        // stores of the previous group must have read their staging before the descriptor changes hands
-        if (lane == 0) tmap_acquire(dC);
+      if (cur.seek(tile) || first) {
         first = false;
+        pc = reinterpret_cast<uint16_t*>(__ldg(c_ptrs + cur.g));
+        ldc = __ldg(c_metas + cur.g * 8 + 2);
       }
-      const int tiles_n = (cur.cur.y + BN - 1) / BN;
+      const int m = cur.cur.x, n = cur.cur.y;
+      const int tiles_n = (n + BN - 1) / BN;
       const int local = tile - cur.cur.w;
       const int m0 = (local / tiles_n) * GG_BM, n0 = (local % tiles_n) * BN;
       const bool zero = cur.cur.z <= 0;  // k = 0: C = 0 (the accumulator was never written)
@@ -306,15 +335,15 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
       if (!mbar_wait(wctx, bar_tfull + buf * 8, (it >> 1) & 1, 4)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-      const bool rows_live = m0 + q * 32 < cur.cur.x;
+      const int row_base = m0 + q * 32;
+      const bool rows_live = row_base < m;
 #pragma unroll 1
-      for (int c = 0; rows_live && c < BN / 64; ++c) {   // a warp whose rows lie past m stages and stores nothing
-        if (n0 + c * 64 >= cur.cur.y) break;   // columns past n: nothing to store (uniform per warp)
+      for (int c = 0; rows_live && c < BN / 64; ++c) {   // a warp whose rows lie past m stores nothing
+        const int col0 = n0 + c * 64;
+        if (col0 >= n) break;   // columns past n: nothing to store (uniform per warp)
         uint32_t v0[32], v1[32];
         tmem_ld_32x32b_x32(t_row + c * 64, v0);
         tmem_ld_32x32b_x32(t_row + c * 64 + 32, v1);
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
         tmem_wait_ld();
         const uint32_t sbuf = sCw + (nst & 1) * L::C_WARP_BYTES;
         ++nst;
@@ -334,23 +363,41 @@ gemm_grouped_kernel(GroupedWs ws, int groups, uint32_t idesc, uint32_t* status) 
                        "r"(p[3])
                        : "memory");
         }
-        fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-          tma_store_2d(dC, sbuf, n0 + c * 64, m0 + q * 32);
-          tma_store_commit();
+        // rows of 128 bytes leave as eight 16-byte stores by eight neighbouring lanes
+        const int cch = lane & 7;
+        const int col = col0 + cch * 8;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          const int row = r * 4 + (lane >> 3);
+          const int grow = row_base + row;
+          if (grow < m && col < n) {
+            uint4 w;
+            const uint32_t src = sbuf + row * 128 + ((uint32_t)(cch ^ (row & 7)) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(w.x), "=r"(w.y), "=r"(w.z), "=r"(w.w)
+                         : "r"(src)
+                         : "memory");
+            uint16_t* dst = pc + (int64_t)grow * ldc + col;
+            if (col + 8 <= n) {
+              *reinterpret_cast<uint4*>(dst) = w;
+            } else {
+              const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+              for (int e = 0; e < 8 && col + e < n; ++e) dst[e] = (uint16_t)(ww[e >> 1] >> ((e & 1) * 16));
+            }
+          }
         }
+        // the other staging buffer is written next; this one is rewritten two chunks later, after the
+        // __syncwarp() that follows the next chunk's staging
       }
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + buf * 8);
     }
-    if (lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) {
+  if (warp == 4) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 2 * BN);
   }
@@ -366,34 +413,23 @@ static int launch_grouped(const int64_t* a_ptrs, const int64_t* b_ptrs, const in
   using L = GroupedSmem<BN>;
   const b200h::DeviceInfo* di = b200h::device_info();
   if (!di) return B200_ERR_CUDA;
-  const CUtensorMapDataType dt = OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  // Templates carry what is common to every group (element type, box, swizzle); address, extents
-  // and pitch are placeholders that the prepare kernel replaces.
-  CUtensorMap tA, tB, tC;
-  int rc;
-  if ((rc = b200h::encode_tmap_2d(&tA, dt, 2, workspace, 1024, 1024, 2048, GG_BK, GG_BM, CU_TENSOR_MAP_SWIZZLE_128B)))
-    return rc;
-  if ((rc = b200h::encode_tmap_2d(&tB, dt, 2, workspace, 1024, 1024, 2048, 64, GG_BK, CU_TENSOR_MAP_SWIZZLE_128B)))
-    return rc;
-  if ((rc = b200h::encode_tmap_2d(&tC, dt, 2, workspace, 1024, 1024, 2048, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)))
-    return rc;
   GroupedWs ws;
-  ws.desc = static_cast<CUtensorMap*>(workspace);
-  ws.info = reinterpret_cast<int4*>(static_cast<uint8_t*>(workspace) + grouped_desc_bytes(groups));
-  grouped_prepare_kernel<BN><<<(groups + GG_PREP_THREADS / 32 - 1) / (GG_PREP_THREADS / 32), GG_PREP_THREADS, 0, stream>>>(tA, tB, tC, a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas,
-                                                               c_metas, groups, ws);
+  ws.info = static_cast<int4*>(workspace);
+  grouped_prepare_kernel<BN><<<1, GG_PREP_THREADS, 0, stream>>>(a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas, c_metas,
+                                                               groups, ws, di->status);
   const cudaError_t after_grouped_prepare_launch = cudaGetLastError();
   B200_CUDA_CHECK(after_grouped_prepare_launch);
   auto kern = gemm_grouped_kernel<BN, OUT_F16>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static std::atomic<bool> attr_done[64];
+  if (!attr_done[di->ordinal].load(std::memory_order_acquire)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done[di->ordinal].store(true, std::memory_order_release);
   }
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
   const uint32_t idesc = make_idesc(fmt, fmt, 0, 1, GG_BM, BN);
   // the tile count is only known on the device: one CTA per SM, CTAs without a tile leave at once
-  kern<<<di->sm_count, GG_THREADS, L::TOTAL, stream>>>(ws, groups, idesc, di->status);
+  kern<<<di->sm_count, GG_THREADS, L::TOTAL, stream>>>(ws, a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas, c_metas, groups,
+                                                       idesc, di->status);
   const cudaError_t after_grouped_main_launch = cudaGetLastError();
   B200_CUDA_CHECK(after_grouped_main_launch);
   return B200_OK;

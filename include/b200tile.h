@@ -55,9 +55,9 @@ typedef struct b200tile_config {
 
 /* Device status record written by bounded waits inside the kernels. */
 typedef struct b200tile_status_t {
-  uint32_t code;  /* 0 = ok, 1 = a wait gave up */
+  uint32_t code;  /* 0 = ok, 1 = a wait gave up, 3 = a grouped-GEMM group broke the 16-byte rule and was skipped */
   uint32_t block; /* blockIdx.x of the CTA that recorded it */
-  uint32_t site;  /* which wait */
+  uint32_t site;  /* which wait (code 1); index of the offending group (code 3) */
   uint32_t aux;
 } b200tile_status_t;
 
@@ -249,10 +249,14 @@ B200TILE_API int b200tile_silu_mul_2d(const char* dtype, void* out, const void* 
  *                            taken from a_metas, n_g from b_metas, the row stride of C from c_metas
  *   bn          B tile width: 128 or 256 (<= 0 selects 256); BM = 128, BK = 64
  *   workspace   DEVICE scratch of b200tile_group_gemm_workspace_bytes(num_groups) bytes, 128-byte
- *               aligned (TMA descriptors built on the device plus the tile prefix sums); NULL lets
+ *               aligned (the groups' extents and tile prefix sums); NULL lets
  *               the library keep one such block per device (allocated on first use, never inside a
  *               stream capture; calls that overlap on one device must then bring their own)
- * Groups with m, n = 0 are skipped; k = 0 stores zeros.  Nothing is read back to the host. */
+ * Groups with m, n = 0 are skipped; k = 0 stores zeros.  Nothing is read back to the host, so a group
+ * whose addresses or row strides are not multiples of 16 bytes (or whose stride is shorter than its
+ * row) cannot be refused by the call: the kernel skips it, stores nothing for it and records status
+ * code 3 with the group's index (b200tile_status).  The operands are fetched with bounds-checked
+ * 16-byte copies computed from the table entries; no tensor-map descriptor is built on the device. */
 B200TILE_API uint64_t b200tile_group_gemm_workspace_bytes(int num_groups);
 B200TILE_API int b200tile_group_gemm(const char* dtype, const int64_t* a_ptrs, const int64_t* b_ptrs,
                                      const int64_t* c_ptrs, const int32_t* a_metas, const int32_t* b_metas,

@@ -3,14 +3,9 @@ import numpy as np
 import pytest
 import torch
 
-# The whole module stays off the GPU for now: the 300-group case below raised an illegal-address fault in
-# about a quarter of fresh processes and the cause has not been found by reading.  If a device-built
-# descriptor goes wrong now and then independently of the shapes (the one hypothesis that fits everything
-# seen), the two smaller cases are exposed as well, only less often; they passed in every run so far.
-pytestmark = [pytest.mark.gpu, pytest.mark.skip(reason="grouped GEMM kept off the GPU until the cause of an "
-                                                       "intermittent illegal-address fault is found")]
+pytestmark = pytest.mark.gpu
 
-from cutile_rs_b200 import _lib, api, launch  # noqa: E402
+from cutile_rs_b200 import _lib, api, launch
 
 GEMM_TOL = 1e-2   # relative Frobenius error of a 16-bit GEMM with fp32 accumulation
 
@@ -20,13 +15,15 @@ def _groups(shapes, dtype, seed, pad=0):
     a, b, c = [], [], []
     for (m, n, k) in shapes:
         # padded row strides exercise the {rows, cols, stride} extent records
-        fa = torch.zeros(max(m, 1), k + pad, dtype=dtype)
+        # (row strides are multiples of 8 elements: the 16-byte rule of the kernel's copies)
+        lda, ldn = (k + pad + 7) // 8 * 8, (n + pad + 7) // 8 * 8
+        fa = torch.zeros(max(m, 1), lda, dtype=dtype)
         fa[:, :k] = (torch.randn(max(m, 1), k, generator=g) / 4).to(dtype)
-        fb = torch.zeros(max(k, 1), n + pad, dtype=dtype)
+        fb = torch.zeros(max(k, 1), ldn, dtype=dtype)
         fb[:, :n] = (torch.randn(max(k, 1), n, generator=g) / 4).to(dtype)
         a.append(fa.cuda()[:m, :k])
         b.append(fb.cuda()[:k, :n])
-        c.append(torch.full((max(m, 1), n + pad), float("nan"), dtype=dtype, device="cuda")[:m, :n])
+        c.append(torch.full((max(m, 1), ldn), float("nan"), dtype=dtype, device="cuda")[:m, :n])
     return a, b, c
 
 
@@ -77,6 +74,9 @@ def test_typed_entry_with_caller_workspace_and_graph(b200, oracle):
     run(stream)
     stream.synchronize()
     _check(oracle, a, b, c)
+    st = _lib.StatusC()
+    _lib.check(b200.b200tile_status(stream.cuda_stream, st))
+    assert st.code == 0
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=stream):
         run(torch.cuda.current_stream())
@@ -96,3 +96,40 @@ def test_typed_entry_with_caller_workspace_and_graph(b200, oracle):
         _lib.check(b200.b200tile_group_gemm(b"bf16", ap.cu_deviceptr(), bp.cu_deviceptr(), cp.cu_deviceptr(),
                                             am.cu_deviceptr(), bm.cu_deviceptr(), cm.cu_deviceptr(), len(shapes), 256,
                                             wp, need - 1, stream.cuda_stream))
+
+
+def test_ragged_extents_leave_neighbouring_memory_alone(b200, oracle):
+    """Extents that are not multiples of the tile, of 8 elements or of the k slab: rows, columns and k past a
+    group's extents are neither read into the product nor written."""
+    shapes = [(130, 264, 72), (1, 8, 8), (257, 40, 200), (33, 520, 136), (64, 24, 64), (20, 36, 100), (7, 3, 5)]
+    a, b, c = _groups(shapes, torch.float16, seed=23, pad=16)
+    # poison what lies behind every operand's extents: it must not reach the result
+    for t in a + b:
+        base = t._base if t._base is not None else t
+        base[:, t.shape[1]:] = float("nan")
+    tabs = launch.group_gemm_tables(a, b, c)
+    launch.group_gemm_f16_nt_desc(*tabs, len(shapes), dtype="f16", bn=128).sync()
+    _check(oracle, a, b, c)
+    for ci in c:
+        assert torch.isnan(ci._base[:, ci.shape[1]:]).all()      # the padding columns of C keep their NaN fill
+    st = _lib.StatusC()
+    _lib.check(b200.b200tile_status(torch.cuda.current_stream().cuda_stream, st))
+    assert st.code == 0
+
+
+def test_group_that_breaks_the_16_byte_rule_is_skipped_and_reported(b200, oracle):
+    """The tables live on the device, so the call cannot refuse a bad group: the kernel skips it (its C stays
+    untouched), reports it through the status record and computes the other groups."""
+    shapes = [(64, 128, 64), (32, 128, 64), (48, 256, 128)]
+    a, b, c = _groups(shapes, torch.bfloat16, seed=29)
+    ap, bp, cp, am, bm, cm = launch.group_gemm_tables(a, b, c)
+    ap.storage[1] += 2           # group 1: A no longer 16-byte aligned
+    s = torch.cuda.current_stream().cuda_stream
+    _lib.check(b200.b200tile_status_reset(s))
+    launch.group_gemm_f16_nt_desc(ap, bp, cp, am, bm, cm, len(shapes), dtype="bf16", bn=256).sync()
+    st = _lib.StatusC()
+    rc = b200.b200tile_status(s, st)
+    assert rc == 4 and st.code == 3 and st.site == 1
+    _lib.check(b200.b200tile_status_reset(s))
+    assert torch.isnan(c[1]).all()
+    _check(oracle, [a[0], a[2]], [b[0], b[2]], [c[0], c[2]])
