@@ -13,6 +13,7 @@
 int b200_gemm_tc_dispatch(int dtype, int b_kmajor, int config, const void* A, const void* B,
                           void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                           int group_m, int max_ctas, cudaStream_t stream);
+int b200_gemm_pair_reset_scratch(cudaStream_t stream);
 int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* B, void* C, int M,
                             int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int group_m,
                             int max_ctas, cudaStream_t stream);
@@ -133,7 +134,8 @@ int b200tile_status_reset(void* cu_stream) {
   if (!di) return B200TILE_ERR_CUDA;
   B200_CUDA_CHECK(
       cudaMemsetAsync(di->status, 0, 4 * sizeof(uint32_t), static_cast<cudaStream_t>(cu_stream)));
-  return B200TILE_OK;
+  // a launch that gave up may have left stream-K hand-off flags raised
+  return b200_gemm_pair_reset_scratch(static_cast<cudaStream_t>(cu_stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -422,10 +422,10 @@ static int launch_decode_variant(const DecodeParams& p, const DecodeHostArgs& h,
                                   64, STEP, 1, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   auto kern = fmha_decode_split_kernel<D, F16, WARPS, STEP, STAGES>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   kern<<<dim3(h.kv_heads, p.splits), WARPS * 32, C::SMEM, stream>>>(tmK, tmV, p, di->status);
   B200_CUDA_CHECK(cudaGetLastError());

@@ -448,11 +448,11 @@ static int launch_fmha(const void* q, const void* k, const void* v, void* o, int
                                   CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   auto kern = fmha_fwd_kernel<D, OUT_F16>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   FmhaParams p;
   p.q_len = q_len;

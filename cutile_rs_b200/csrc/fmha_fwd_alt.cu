@@ -567,10 +567,10 @@ static int launch_fmha_alt(const void* q, const void* k, const void* v, void* o,
   if ((reinterpret_cast<uintptr_t>(o) & 15) || (os[0] & 7) || (os[1] & 7))
     return b200h::set_error(B200_ERR_ALIGN, "fmha: output base and pitches must be multiples of 16 bytes");
   auto kern = fmha_fwd_alt_kernel<OUT_F16>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   FmhaParams p;
   p.q_len = q_len;

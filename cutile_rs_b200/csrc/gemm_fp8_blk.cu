@@ -240,10 +240,10 @@ static int launch_fp8(const void* x, const void* y, const float* xs, const float
                                   (uint64_t)ldy, F8_BK, F8_BN, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   auto kern = gemm_fp8_blk_kernel<OUT_F32>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   const int tiles = ((M + F8_BM - 1) / F8_BM) * ((N + F8_BN - 1) / F8_BN);
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;

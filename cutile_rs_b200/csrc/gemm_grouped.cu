@@ -420,10 +420,10 @@ static int launch_grouped(const int64_t* a_ptrs, const int64_t* b_ptrs, const in
   const cudaError_t after_grouped_prepare_launch = cudaGetLastError();
   B200_CUDA_CHECK(after_grouped_prepare_launch);
   auto kern = gemm_grouped_kernel<BN, OUT_F16>;
-  static std::atomic<bool> attr_done[64];
-  if (!attr_done[di->ordinal].load(std::memory_order_acquire)) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal].store(true, std::memory_order_release);
+    attr_done.set(di->ordinal);
   }
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
   const uint32_t idesc = make_idesc(fmt, fmt, 0, 1, GG_BM, BN);

@@ -558,10 +558,10 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
   }
   B200_CUDA_CHECK(cudaGetLastError());
   auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4, A_DIRECT, AROWS>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   const int tiles = tiles_m * tiles_n;
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;

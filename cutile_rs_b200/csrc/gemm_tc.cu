@@ -221,7 +221,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             v1[i] = __float_as_uint(swiglu_16bit<OUT_F16>(__uint_as_float(v1[i]), __uint_as_float(u1[i])));
           }
         }
-        // staging buffer (c & 1): the store issued two chunks ago must have drained it
+        // staging buffer (c & 1): the store issued two chunks ago must have drained it.  Chunk parity is a
+        // valid choice only because every tile stores an even number of chunks; a variant with an odd
+        // count must pick the buffer by a count of committed stores instead.
+        static_assert((BN_OUT / 64) % 2 == 0, "chunk-parity staging needs an even number of chunks per tile");
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         tmem_wait_ld();
@@ -293,11 +296,11 @@ static int launch_gemm_tc(const void* A, const void* B, void* C, int M, int N, i
     return rc;
 
   auto kern = gemm_tc_kernel<BN, B_KMAJOR, OUT_F16>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   int grid = tiles < di->sm_count ? tiles : di->sm_count;
@@ -330,10 +333,10 @@ static int launch_gemm_swiglu(const void* X, const void* W, void* O, int M, int 
                                   CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   auto kern = gemm_tc_kernel<256, true, OUT_F16, true>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((I + 127) / 128);
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;

@@ -9,8 +9,13 @@
 // what relieves shared-memory bandwidth compared with the single-CTA 128x256 tile.
 //
 // When the tile count does not fill the last wave, that wave's tiles are split along K over all
-// pairs (stream-K): a pair that computes the tail of a tile publishes its fp32 partial to global
-// scratch and raises a flag; the pair that computed the head waits (bounded) and adds it.
+// pairs (stream-K).  The pair that holds the END of a tile's k range owns its output; a pair whose
+// share stops inside a tile publishes that fp32 partial to global scratch and raises a flag.  Every
+// pair publishes FIRST and only then works as an owner, and an owner only waits (bounded) for pairs
+// with a lower index: a wait never depends on a CTA that has not been dispatched yet or that is
+// itself waiting, so the launch makes progress even when other work shares the GPU.  The owner
+// clears a flag once it has read the partial, which leaves the scratch ready for the next launch
+// (or the next replay of a captured graph) without any host-side state.
 //
 //   warp 0      TMA producer (both CTAs); transaction bytes are counted on the leader's barrier
 //   warp 1      MMA issuer (leader CTA only) -- releases a stage in BOTH CTAs with two commits
@@ -66,27 +71,40 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
 }
 
 // Work list of one CTA pair.  The first `sk_tiles` tiles are the partial last wave: their
-// (tile, k-block) units are dealt out evenly ("stream-K"), so a pair may get the tail of one
-// tile, whole tiles and the head of another.  The remaining tiles are whole tiles, strided over
-// the pairs.  Every role of the CTA walks the same list.
+// (tile, k-block) units are dealt out evenly ("stream-K"), so a pair's share may hold the tail of one
+// tile, whole tiles and the head of another.  A share that stops inside a tile yields that last
+// segment FIRST (kb1 < nkb: a partial to publish), then the segments that reach a tile's end (the
+// pair owns those tiles), then whole tiles strided over the pairs.  Every role of the CTA walks the
+// same list.
 struct PairSched {
   int nkb, sk_tiles, total_tiles, pair, num_pairs, dp_i;
-  long long u, u_end;
+  long long u, u_pub, u_end;
+  bool pub_pending;
   __device__ void init(int nkb_, int sk_tiles_, int total_tiles_, int pair_, int num_pairs_) {
     nkb = nkb_; sk_tiles = sk_tiles_; total_tiles = total_tiles_; pair = pair_; num_pairs = num_pairs_;
     dp_i = 0;
     const long long units = (long long)sk_tiles * nkb;
     u = units * pair / num_pairs;
     u_end = units * (pair + 1) / num_pairs;
+    // the segment to publish starts at the last tile boundary inside the share (or at the share's start)
+    const long long boundary = (u_end / nkb) * nkb;
+    u_pub = (u_end == boundary) ? u_end : (boundary > u ? boundary : u);
+    pub_pending = u_pub < u_end;
   }
   // first stream-K unit of pair q (used to find which pairs contribute to a tile)
   __device__ long long first_unit(int q) const { return (long long)sk_tiles * nkb * q / num_pairs; }
   __device__ bool next(int& tile, int& kb0, int& kb1) {
-    if (u < u_end) {
+    if (pub_pending) {
+      pub_pending = false;
+      tile = (int)(u_pub / nkb);
+      kb0 = (int)(u_pub - (long long)tile * nkb);
+      kb1 = (int)(u_end - (long long)tile * nkb);
+      return true;
+    }
+    if (u < u_pub) {
       tile = (int)(u / nkb);
       kb0 = (int)(u - (long long)tile * nkb);
-      const long long left = u_end - u;
-      kb1 = (left < (long long)(nkb - kb0)) ? kb0 + (int)left : nkb;
+      kb1 = nkb;   // u_pub lies on a tile boundary whenever it is past u
       u += kb1 - kb0;
       return true;
     }
@@ -106,12 +124,12 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 __device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-// Bounded wait for another CTA's partial tile (status code 2 = ST_FLAG_TIMEOUT on expiry).
-__device__ __forceinline__ bool wait_flag(const WaitCtx& ctx, const uint32_t* flag, uint32_t epoch) {
-  if (ld_acquire_gpu(flag) == epoch) return true;
+// Bounded wait for another CTA's partial tile (status code 2 on expiry).
+__device__ __forceinline__ bool wait_flag(const WaitCtx& ctx, const uint32_t* flag) {
+  if (ld_acquire_gpu(flag) != 0u) return true;
   const long long t0 = clock64();
   for (uint32_t it = 0;; ++it) {
-    if (ld_acquire_gpu(flag) == epoch) return true;
+    if (ld_acquire_gpu(flag) != 0u) return true;
     if ((it & 0x3F) == 0x3F) {
       if (*ctx.abort_flag) return false;
       if (clock64() - t0 > B200_WAIT_LIMIT_CYCLES) break;
@@ -121,7 +139,7 @@ __device__ __forceinline__ bool wait_flag(const WaitCtx& ctx, const uint32_t* fl
   if (atomicCAS(ctx.status, 0u, 2u) == 0u) {
     ctx.status[1] = blockIdx.x;
     ctx.status[2] = 50;
-    ctx.status[3] = epoch;
+    ctx.status[3] = 0;
   }
   return false;
 }
@@ -133,7 +151,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int group_m,
                     uint32_t idesc, uint32_t* status, int sk_tiles, float* sk_partials,
-                    uint32_t* sk_flags, uint32_t sk_epoch) {
+                    uint32_t* sk_flags) {
   using L = PairSmem;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -296,9 +314,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * P_BN;
       const int row = q * 32 + lane;
-      if (kb0 > 0) {
-        // ---- tail/middle segment of a stream-K tile: publish the fp32 partial, column-major so
-        // that the 32 lanes of a warp write 128 contiguous bytes ----
+      if (kb1 < num_kb) {
+        // ---- the share stops inside this tile: publish the fp32 partial, column-major so that the
+        // 32 lanes of a warp write 128 contiguous bytes ----
         float* slot = sk_partials + (size_t)blockIdx.x * P_SLOT_FLOATS;
 #pragma unroll 1
         for (int c = 0; c < P_BN / 32; ++c) {
@@ -313,20 +331,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (lane == 0) mbar_arrive_cluster_addr(tempty_leader + buf * 8);
         __threadfence();
         named_bar_sync(1, 128);
-        if (etid == 0) st_release_gpu(sk_flags + blockIdx.x, sk_epoch);
+        if (etid == 0) st_release_gpu(sk_flags + blockIdx.x, 1u);
         continue;
       }
-      // ---- head segment (or a whole tile): owner of the output.  For a stream-K head, the pairs
-      // that follow hold the rest of the k range; wait for each and add its partial. ----
+      // ---- the share reaches the tile's end: owner of the output.  When it starts inside the tile,
+      // the pairs before this one hold the rest of the k range (each published it as the first item
+      // of its list); wait for each and add its partial. ----
       int q_first = 0, q_last = -1;
-      if (kb1 < num_kb) {
-        q_first = pair + 1;
-        q_last = pair;
-        const long long tile_end = (long long)(tile + 1) * num_kb;
-        while (q_last + 1 < num_pairs && sched.first_unit(q_last + 1) < tile_end) ++q_last;
+      if (kb0 > 0) {
+        q_last = pair - 1;
+        q_first = pair;
+        const long long tile_begin = (long long)tile * num_kb;
+        while (q_first > 0 && sched.first_unit(q_first) > tile_begin) --q_first;
         for (int qq = q_first; qq <= q_last && ok; ++qq) {
           if (sched.first_unit(qq) == sched.first_unit(qq + 1)) continue;  // that pair got no units
-          ok = wait_flag(wctx, sk_flags + (2 * qq + (int)rank), sk_epoch);
+          ok = wait_flag(wctx, sk_flags + (2 * qq + (int)rank));
         }
         if (!ok) break;
       }
@@ -347,6 +366,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             v1[i] = __float_as_uint(__uint_as_float(v1[i]) + __ldcg(part + (c * 64 + 32 + i) * P_BM));
           }
         }
+        // staging buffer by chunk parity: valid because every tile stores an EVEN number of chunks (4), so
+        // `wait_group.read 1` above has always drained the buffer chosen here; a variant that can store an
+        // odd number of chunks per tile must count committed stores instead
+        static_assert((P_BN / 64) % 2 == 0, "chunk-parity staging needs an even number of chunks per tile");
         const uint32_t sbuf = sCw + (c & 1) * L::C_WARP_BYTES;
         const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
@@ -373,6 +396,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster_addr(tempty_leader + buf * 8);
+      if (q_last >= q_first) {
+        // every epilogue thread of this CTA has read the partials: clear their flags for the next launch
+        named_bar_sync(1, 128);
+        if (etid == 0)
+          for (int qq = q_first; qq <= q_last; ++qq)
+            if (sched.first_unit(qq) != sched.first_unit(qq + 1)) st_release_gpu(sk_flags + (2 * qq + (int)rank), 0u);
+      }
     }
     if (lane == 0) tma_store_wait_all<0>();
   }
@@ -388,25 +418,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 // ---------------------------------------------------------------------------
 // Stream-K scratch: one fp32 partial slot (128 x 256) and one flag per CTA, per (device, stream).
-// Allocated on the first launch that needs it (never while that stream is capturing: the
-// allocation then fails and the launch falls back to whole tiles), kept until process exit.
+// Streams are told apart by cudaStreamGetId, which is never reused within a process (a handle can be:
+// a destroyed stream's address may come back for a new one).  Allocated on the first launch that needs
+// it (never while that stream is capturing: the launch then falls back to whole tiles), kept until
+// process exit; when all sets of a device are taken, further streams run whole tiles only.  The flags
+// are zero between launches (the kernel clears what it raised), so a launch captured into a graph
+// replays correctly; two launches that share a set must not overlap on the GPU (same-stream order
+// guarantees that; a graph replayed concurrently with eager work of its capture stream does not).
 // ---------------------------------------------------------------------------
 namespace {
 struct SkScratch {
-  cudaStream_t stream;
+  unsigned long long stream_id;
   float* partials;
   uint32_t* flags;
-  uint32_t epoch;
+  int slots;
   bool used;
 };
-constexpr int kSkPerDevice = 4;
+constexpr int kSkPerDevice = 8;
 SkScratch g_sk[64][kSkPerDevice];
 std::mutex g_sk_mu;
 
 SkScratch* sk_scratch_for(int dev, int slots, cudaStream_t stream) {
+  unsigned long long id = 0;
+  if (cudaStreamGetId(stream, &id) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
   std::lock_guard<std::mutex> lk(g_sk_mu);
   for (int i = 0; i < kSkPerDevice; ++i)
-    if (g_sk[dev][i].used && g_sk[dev][i].stream == stream) return &g_sk[dev][i];
+    if (g_sk[dev][i].used && g_sk[dev][i].stream_id == id && g_sk[dev][i].slots >= slots) return &g_sk[dev][i];
   for (int i = 0; i < kSkPerDevice; ++i) {
     SkScratch& e = g_sk[dev][i];
     if (e.used) continue;
@@ -426,14 +466,14 @@ SkScratch* sk_scratch_for(int dev, int slots, cudaStream_t stream) {
       cudaFree(p);
       return nullptr;
     }
-    e.stream = stream;
+    e.stream_id = id;
     e.partials = static_cast<float*>(p);
     e.flags = static_cast<uint32_t*>(f);
-    e.epoch = 0;
+    e.slots = slots;
     e.used = true;
     return &e;
   }
-  return nullptr;  // more concurrent streams than scratch sets: whole tiles only
+  return nullptr;  // more streams than scratch sets: whole tiles only
 }
 
 bool streamk_enabled() {
@@ -470,11 +510,11 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
                                   32, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   auto kern = gemm_tc_pair_kernel<B_KMAJOR, OUT_F16>;
-  static bool attr_done[64] = {};
-  if (!attr_done[di->ordinal]) {
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-    attr_done[di->ordinal] = true;
+    attr_done.set(di->ordinal);
   }
   const int tiles = ((M + 2 * P_BM - 1) / (2 * P_BM)) * ((N + P_BN - 1) / P_BN);
   const int all_pairs = di->sm_count / 2;
@@ -494,7 +534,6 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
       if (sk) {
         sk_tiles = tiles % all_pairs;
         pairs = all_pairs;
-        ++sk->epoch;
       }
     }
   }
@@ -502,7 +541,7 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
   const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, 2 * P_BM, P_BN);
   kern<<<pairs * 2, P_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, group_m, idesc,
                                                    di->status, sk_tiles, sk ? sk->partials : nullptr,
-                                                   sk ? sk->flags : nullptr, sk ? sk->epoch : 0u);
+                                                   sk ? sk->flags : nullptr);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -520,6 +559,21 @@ int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* 
   if (b_kmajor && dtype == 0)
     return launch_gemm_pair<true, false>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
   return launch_gemm_pair<true, true>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
+}
+
+// Clears the stream-K flags of every scratch set of the current device (ordered on `stream`).  A launch
+// that gave up a wait can leave a flag raised; the status reset calls this so that the next launch
+// starts clean.
+int b200_gemm_pair_reset_scratch(cudaStream_t stream) {
+  using namespace b200;
+  int dev = 0;
+  B200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200_OK;
+  std::lock_guard<std::mutex> lk(g_sk_mu);
+  for (int i = 0; i < kSkPerDevice; ++i)
+    if (g_sk[dev][i].used)
+      B200_CUDA_CHECK(cudaMemsetAsync(g_sk[dev][i].flags, 0, (size_t)g_sk[dev][i].slots * sizeof(uint32_t), stream));
+  return B200_OK;
 }
 
 #ifdef B200TILE_TRACE

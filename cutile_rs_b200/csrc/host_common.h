@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 // Status codes returned across the C ABI (see include/b200tile.h).
 #define B200_OK 0
 #define B200_ERR_INVALID 1      // argument violates a kernel precondition
@@ -30,6 +32,14 @@ int encode_tmap_3d(CUtensorMap* out, CUtensorMapDataType dtype, int elem_bytes, 
                    uint64_t dim0, uint64_t dim1, uint64_t dim2, uint64_t stride1_bytes,
                    uint64_t stride2_bytes, uint32_t box0, uint32_t box1, uint32_t box2,
                    CUtensorMapSwizzle swizzle);
+
+// Per-device first-use flag for idempotent set-up (function attributes).  Threads that race may both do
+// the set-up, which is harmless because the calls are idempotent; the flag itself is atomic.
+struct DeviceOnce {
+  std::atomic<bool> done[64];
+  bool test(int dev) const { return done[dev].load(std::memory_order_acquire); }
+  void set(int dev) { done[dev].store(true, std::memory_order_release); }
+};
 
 // Per-device facts, resolved once per device on first use.
 struct DeviceInfo {

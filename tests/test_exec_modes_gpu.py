@@ -9,11 +9,12 @@ pytestmark = pytest.mark.gpu
 from cutile_rs_b200 import api, benching, launch, tune, workloads  # noqa: E402
 
 
-def _ref(a, b):
-    return (a.float().cuda() @ b.float().cuda())
+def _ref(oracle, a, b):
+    """fp32 CPU oracle GEMM of the 16-bit operands, as a device tensor."""
+    return torch.from_numpy(oracle.cpu_gemm(a.float().numpy(), b.float().numpy(), threads=0)).cuda()
 
 
-def test_async_on_two_streams(b200):
+def test_async_on_two_streams(b200, oracle):
     a, b = workloads.gemm_bf16_inputs(512, 512, 512)
     x, y = api.copy_host_to_device(a), api.copy_host_to_device(b)
     torch.cuda.synchronize()
@@ -25,19 +26,19 @@ def test_async_on_two_streams(b200):
     launch.gemm(z2, x, y).async_on(s2)
     s1.synchronize()
     s2.synchronize()
-    ref = _ref(a, b)
+    ref = _ref(oracle, a, b)
     for z in (z1, z2):
         assert (z.unpartition().storage.float() - ref).norm() / ref.norm() <= 1e-2
 
 
-def test_cuda_graph_capture_and_replay(b200):
+def test_cuda_graph_capture_and_replay(b200, oracle):
     a, b = workloads.gemm_bf16_inputs(512, 512, 512)
     x, y = api.copy_host_to_device(a), api.copy_host_to_device(b)
     z = api.zeros([512, 512], "bf16").partition([128, 256])
     torch.cuda.synchronize()
     stream = torch.cuda.Stream()
     graph = launch.gemm(z, x, y).graph_on(stream)        # capture: the kernel is recorded, not run
-    ref = _ref(a, b)
+    ref = _ref(oracle, a, b)
     graph.launch().sync()
     torch.cuda.synchronize()
     assert (z.unpartition().storage.float() - ref).norm() / ref.norm() <= 1e-2
@@ -50,10 +51,10 @@ def test_cuda_graph_capture_and_replay(b200):
     assert out[0] is z
 
 
-def test_do_bench_and_autotuner_on_device(b200, tmp_path):
+def test_do_bench_and_autotuner_on_device(b200, oracle, tmp_path):
     a, b = workloads.gemm_bf16_inputs(1024, 1024, 1024)
     x, y = api.copy_host_to_device(a), api.copy_host_to_device(b)
-    ref = _ref(a, b)
+    ref = _ref(oracle, a, b)
     stream = torch.cuda.current_stream()
 
     def setup(s, config):

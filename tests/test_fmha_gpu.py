@@ -30,6 +30,7 @@ def _fmha(lib, q, k, v, causal, input_pos=0):
     torch.cuda.synchronize()
     st = _lib.StatusC()
     _lib.check(lib.b200tile_status(_stream().cuda_stream, ctypes.byref(st)))
+    assert st.code == 0
     return o
 
 

@@ -189,6 +189,39 @@ def test_streamk_remainder_wave(b200, oracle):
     _status_ok(b200)
 
 
+def test_streamk_launch_replays_from_a_graph(b200, oracle):
+    """A stream-K launch captured after eager launches on the same stream: every replay must do its own
+    hand-off (nothing of the hand-off lives on the host), with inputs that change between replays."""
+    m, n, k = 8192, 1024, 2048
+    a, b = workloads.gemm_bf16_inputs(m, n, k, config_index=33)
+    ad, bd = a.cuda(), b.cuda()
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    stream = torch.cuda.Stream()
+    rows = slice(4096 - 16, 4096 + 16)
+    bf = b.float().numpy()
+
+    def launch_on(s):
+        _lib.check(b200.b200tile_gemm(b"bf16", 0, ad.data_ptr(), bd.data_ptr(), c.data_ptr(), 1, m, n, k,
+                                      ad.stride(0), bd.stride(0), c.stride(0), 0, 0, 0, 0, 2, 0, 0, s.cuda_stream))
+    torch.cuda.synchronize()
+    for _ in range(2):                      # eager warm-up: the stream's scratch exists before the capture
+        launch_on(stream)
+    stream.synchronize()
+    eager = c.clone()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        launch_on(torch.cuda.current_stream())
+    for rep, scale in enumerate((1.0, 0.5, -2.0, 0.25)):
+        ad.copy_((a.float() * scale).to(torch.bfloat16))      # exact scalings: the result scales bit for bit
+        c.fill_(float("nan"))
+        g.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(c, (eager.float() * scale).to(torch.bfloat16)), f"replay {rep}"
+        ref = oracle.cpu_gemm(a[rows].float().numpy() * scale, bf, threads=0)
+        assert oracle.rel_frobenius(c[rows].float().cpu().numpy(), ref) <= BF16_TOL
+    _status_ok(b200)
+
+
 @pytest.mark.parametrize("dtype,m,n,k,layout,slab", [("bf16", 1300, 512, 768, 0, 256), ("bf16", 1024, 768, 512, 1, 0),
                                                       ("f32", 300, 256, 128, 0, 256)])
 def test_host_operand_pipeline(b200, oracle, dtype, m, n, k, layout, slab):
@@ -212,7 +245,7 @@ def test_host_operand_pipeline(b200, oracle, dtype, m, n, k, layout, slab):
         ref = oracle.cpu_gemm(a.numpy(), b.numpy())
         assert np.array_equal(first.numpy(), ref)
     else:
-        ref = (a.float() @ bm).numpy()
+        ref = oracle.cpu_gemm(a.float().numpy(), bm.contiguous().numpy(), threads=0)
         assert oracle.rel_frobenius(first.float().numpy(), ref) <= 1e-2
         assert oracle.rel_frobenius(c.float().numpy(), 0.5 * ref) <= 1e-2
     assert not torch.isnan(c.float()).any()

@@ -5,11 +5,12 @@
 memory pool, start-up code that runs before an allocator exists); it keeps its scale scratch in a
 fixed array inside the library.  The array is shared by every call and keeps the previous call's
 contents, so the check runs two different problems back to back through the C ABI and compares
-each with the regular entry point.  This file sorts last on purpose: a run that stops at the first
-failure has then already executed every other test.
+each with the regular entry point and with the oracle's dequantised fp32 reference.  This file sorts
+last on purpose: a run that stops at the first failure has then already executed every other test.
 """
 import ctypes
 
+import numpy as np
 import pytest
 import torch
 
@@ -44,7 +45,7 @@ def _call(lib, static, prob, m, n, k, out):
     return z
 
 
-def test_static_scratch_entry_point_matches_workspace_entry_point(b200):
+def test_static_scratch_entry_point_matches_workspace_entry_point(b200, oracle):
     lib = b200
     # two calls in a row on different shapes: the second must not be disturbed by what the first
     # left behind in the shared array (the first is larger, so stale scales surround the second's)
@@ -59,8 +60,25 @@ def test_static_scratch_entry_point_matches_workspace_entry_point(b200):
         assert torch.equal(got, want)
         rel = (got.float() - want.float()).norm() / want.float().norm()
         assert rel <= 3e-2
+        # and against the CPU oracle: fp32 GEMM over the dequantised operands
+        xp, yp, xs, ys, alpha = prob
+        ref = oracle.cpu_gemm_nt(oracle.dequant_nvfp4(xp.cpu().numpy(), xs.cpu().numpy()),
+                                 oracle.dequant_nvfp4(yp.cpu().numpy(), ys.cpu().numpy()), alpha=alpha, threads=0)
+        assert oracle.rel_frobenius(got.float().cpu().numpy(), ref) <= (3e-2 if out == "bf16" else 1e-5)
+        # a further static call takes no device memory: the free-memory figure does not move
+        z = torch.empty_like(got)
+        stream = torch.cuda.current_stream().cuda_stream
+        common = (xp.data_ptr(), yp.data_ptr(), xs.data_ptr(), ys.data_ptr(), z.data_ptr(), out.encode(), m, n, k,
+                  k // 2, k // 2, n, k // 16, k // 16, alpha)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        _lib.check(lib.b200tile_linear_nvfp4_static(*common, -1, stream))
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] >= free_before
+        assert torch.equal(z, want)
     st = _lib.StatusC()
     _lib.check(lib.b200tile_status(torch.cuda.current_stream().cuda_stream, ctypes.byref(st)))
+    assert st.code == 0
 
 
 def test_static_scratch_entry_point_rejects_oversized_problems(b200):
