@@ -429,6 +429,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 namespace {
 struct SkScratch {
   unsigned long long stream_id;
+  cudaStream_t handle;   // the handle the id was read from; the only key usable while the stream is capturing
+  bool handle_live;      // false once another stream has been seen under the same handle
   float* partials;
   uint32_t* flags;
   int slots;
@@ -439,22 +441,30 @@ SkScratch g_sk[64][kSkPerDevice];
 std::mutex g_sk_mu;
 
 SkScratch* sk_scratch_for(int dev, int slots, cudaStream_t stream) {
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_sk_mu);
+  if (cs != cudaStreamCaptureStatusNone) {
+    // a capturing stream is alive, so its handle names it; only queries that are legal inside a capture
+    // are made, and nothing is allocated: without a set from an earlier eager launch, whole tiles
+    for (int i = 0; i < kSkPerDevice; ++i)
+      if (g_sk[dev][i].used && g_sk[dev][i].handle_live && g_sk[dev][i].handle == stream && g_sk[dev][i].slots >= slots)
+        return &g_sk[dev][i];
+    return nullptr;
+  }
   unsigned long long id = 0;
   if (cudaStreamGetId(stream, &id) != cudaSuccess) {
     cudaGetLastError();
     return nullptr;
   }
-  std::lock_guard<std::mutex> lk(g_sk_mu);
   for (int i = 0; i < kSkPerDevice; ++i)
     if (g_sk[dev][i].used && g_sk[dev][i].stream_id == id && g_sk[dev][i].slots >= slots) return &g_sk[dev][i];
   for (int i = 0; i < kSkPerDevice; ++i) {
     SkScratch& e = g_sk[dev][i];
     if (e.used) continue;
-    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) {
-      cudaGetLastError();
-      return nullptr;
-    }
     void *p = nullptr, *f = nullptr;
     if (cudaMalloc(&p, (size_t)slots * P_SLOT_FLOATS * sizeof(float)) != cudaSuccess) {
       cudaGetLastError();
@@ -467,10 +477,16 @@ SkScratch* sk_scratch_for(int dev, int slots, cudaStream_t stream) {
       return nullptr;
     }
     e.stream_id = id;
+    e.handle = stream;
+    e.handle_live = true;
     e.partials = static_cast<float*>(p);
     e.flags = static_cast<uint32_t*>(f);
     e.slots = slots;
     e.used = true;
+    // a set whose handle has been reused by this new stream belonged to a destroyed stream: it must not
+    // be found by handle any more
+    for (int j = 0; j < kSkPerDevice; ++j)
+      if (j != i && g_sk[dev][j].used && g_sk[dev][j].handle == stream) g_sk[dev][j].handle_live = false;
     return &e;
   }
   return nullptr;  // more streams than scratch sets: whole tiles only
