@@ -93,6 +93,8 @@ SIGNATURES = {
                                       c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                       c_void_p, c_uint64, c_int, c_void_p]),
     "b200tile_nvfp4_weight_scales_bytes": (c_uint64, [c_int, c_int, c_int]),
+    "b200tile_nvfp4_register_weight_scales": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_void_p]),
+    "b200tile_nvfp4_unregister_weight_scales": (c_int, [c_void_p]),
     "b200tile_nvfp4_prepare_weight_scales": (c_int, [c_void_p, c_int, c_int, c_int64, c_int, c_void_p, c_uint64,
                                                      c_void_p]),
     "b200tile_linear_nvfp4_prepared": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p, c_int,

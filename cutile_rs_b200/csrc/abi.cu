@@ -7,12 +7,18 @@
 #include <string.h>
 #include <cuda_fp16.h>
 
+#include <mutex>
+#include <vector>
+
 #include "host_common.h"
 
 // per-kernel launchers (defined next to their kernels)
 int b200_gemm_tc_dispatch(int dtype, int b_kmajor, int config, const void* A, const void* B,
                           void* C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
                           int group_m, int max_ctas, cudaStream_t stream);
+#ifdef B200TILE_TEST_HOOKS
+int b200_test_set_skip_stage(int on);
+#endif
 int b200_gemm_pair_reset_scratch(cudaStream_t stream);
 int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* B, void* C, int M,
                             int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int group_m,
@@ -180,6 +186,21 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
   if (!strcmp(kernel, "linear_tile_fp8_blk128")) {
     tab = kFp8Configs;
     n = 1;
+  }
+  // `linear_tile`: dtype names the OPERAND type, which is what separates the two reference kernels of that
+  // name (f4e2m1fnx2 = NVFP4, e4m3 scale per 16; f8e4m3fn = MXFP8, e8m0 scale per 32).  The launcher's tile
+  // generics only shape the launch grid; the kernel's own tile is the configuration listed here.
+  static const b200tile_config kNvfp4Configs[] = {{0, 128, 128, 256, 5, 1, 1}, {1, 128, 192, 256, 4, 1, 1},
+                                                  {2, 128, 256, 256, 3, 1, 1}};
+  static const b200tile_config kMxfp8Configs[] = {{0, 128, 224, 128, 4, 1, 1}};
+  if (!strcmp(kernel, "linear_tile")) {
+    if (!strcmp(dtype, "f4e2m1fnx2")) {
+      tab = kNvfp4Configs;
+      n = 3;
+    } else if (!strcmp(dtype, "f8e4m3fn")) {
+      tab = kMxfp8Configs;
+      n = 1;
+    }
   }
   for (int i = 0; i < n && i < cap && out; ++i) out[i] = tab[i];
   return n;
@@ -418,27 +439,9 @@ int b200tile_group_gemm(const char* dtype, const int64_t* a_ptrs, const int64_t*
   cudaStream_t stream = static_cast<cudaStream_t>(cu_stream);
   const size_t need = b200_grouped_workspace_bytes(num_groups);
   if (!workspace) {
-    // library-owned workspace, one per device, grown on demand (never inside a stream capture)
-    static void* pool[64] = {};
-    static size_t pool_bytes[64] = {};
-    const b200h::DeviceInfo* di = b200h::device_info();
-    if (!di) return B200TILE_ERR_CUDA;
-    if (pool_bytes[di->ordinal] < need) {
-      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-      B200_CUDA_CHECK(cudaStreamIsCapturing(stream, &cap));
-      if (cap != cudaStreamCaptureStatusNone)
-        return set_error(B200TILE_ERR_INVALID,
-                         "group_gemm: pass a workspace of %llu bytes when capturing (the library cannot allocate)",
-                         (unsigned long long)need);
-      B200_CUDA_CHECK(cudaDeviceSynchronize());  // earlier launches may still read the old block
-      if (pool[di->ordinal]) B200_CUDA_CHECK(cudaFree(pool[di->ordinal]));
-      pool[di->ordinal] = nullptr;
-      pool_bytes[di->ordinal] = 0;
-      const size_t grow = need < (64u << 10) ? (64u << 10) : need * 2;
-      B200_CUDA_CHECK(cudaMalloc(&pool[di->ordinal], grow));
-      pool_bytes[di->ordinal] = grow;
-    }
-    workspace = pool[di->ordinal];
+    // library-owned workspace, one per (device, stream), grown on demand (never inside a stream capture)
+    workspace = b200h::stream_scratch(stream, need, "group_gemm");
+    if (!workspace) return B200TILE_ERR_INVALID;
   } else if ((reinterpret_cast<uintptr_t>(workspace) & 127) != 0 || workspace_bytes < need) {
     return set_error(B200TILE_ERR_INVALID, "group_gemm: workspace of %llu bytes (128-byte aligned) required, got %llu",
                      (unsigned long long)need, (unsigned long long)workspace_bytes);
@@ -575,6 +578,67 @@ int b200tile_linear_nvfp4_prepared(const void* x, const void* y, const void* x_s
   return b200_gemm_nvfp4_dispatch(kNvfp4Bn[config], out_f32, x, y, x_scales, nullptr, z, m, n, k, ldx, ldy, ldz,
                                   ld_xs, 0, alpha, const_cast<void*>(y_scales_prepared),
                                   static_cast<cudaStream_t>(cu_stream), 1);
+}
+
+// Registry of prepared weight scales: the reference's `linear_tile` takes logically row-major scales on every
+// call, but inference weights do not change, so a serving loop can lay their scales out once
+// (b200tile_nvfp4_prepare_weight_scales) and register the result under the address of the row-major tensor.
+// `b200tile_launch("linear_tile", ...)` then finds decode-sized calls on that weight and skips the per-call
+// re-layout.  The caller owns both buffers and must unregister before freeing either.
+namespace {
+struct Nvfp4Registered {
+  int device;
+  const void* y_scales;
+  int n, k;
+  int64_t ld_ys;
+  const void* prepared;
+  int config;
+};
+std::vector<Nvfp4Registered> g_nvfp4_registry;
+std::mutex g_nvfp4_registry_mu;
+}  // namespace
+
+bool nvfp4_registry_find(const void* y_scales, int n, int k, int64_t ld_ys, const void** prepared, int* config) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  std::lock_guard<std::mutex> lk(g_nvfp4_registry_mu);
+  for (const Nvfp4Registered& e : g_nvfp4_registry)
+    if (e.device == dev && e.y_scales == y_scales && e.n == n && e.k == k && e.ld_ys == ld_ys) {
+      *prepared = e.prepared;
+      *config = e.config;
+      return true;
+    }
+  return false;
+}
+
+int b200tile_nvfp4_register_weight_scales(const void* y_scales, int n, int k, int64_t ld_ys, int config,
+                                          const void* prepared) {
+  if (!y_scales || !prepared || n <= 0 || k <= 0 || config < 0 || config > 2)
+    return set_error(B200TILE_ERR_INVALID, "nvfp4_register_weight_scales: bad argument");
+  if ((reinterpret_cast<uintptr_t>(prepared) & 15) != 0)
+    return set_error(B200TILE_ERR_ALIGN, "nvfp4_register_weight_scales: prepared buffer must be 16-byte aligned");
+  int dev = -1;
+  B200_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_nvfp4_registry_mu);
+  for (Nvfp4Registered& e : g_nvfp4_registry)
+    if (e.device == dev && e.y_scales == y_scales) {
+      e = Nvfp4Registered{dev, y_scales, n, k, ld_ys, prepared, config};
+      return B200TILE_OK;
+    }
+  g_nvfp4_registry.push_back(Nvfp4Registered{dev, y_scales, n, k, ld_ys, prepared, config});
+  return B200TILE_OK;
+}
+
+int b200tile_nvfp4_unregister_weight_scales(const void* y_scales) {
+  int dev = -1;
+  B200_CUDA_CHECK(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(g_nvfp4_registry_mu);
+  for (size_t i = 0; i < g_nvfp4_registry.size(); ++i)
+    if (g_nvfp4_registry[i].device == dev && g_nvfp4_registry[i].y_scales == y_scales) {
+      g_nvfp4_registry.erase(g_nvfp4_registry.begin() + (long)i);
+      return B200TILE_OK;
+    }
+  return set_error(B200TILE_ERR_INVALID, "nvfp4_unregister_weight_scales: %p is not registered on this device", y_scales);
 }
 
 // ---------------------------------------------------------------------------
@@ -1065,6 +1129,84 @@ int launch_linear_fp8_generic(const char* kernel, const char* const* generics, i
                                     z.stride[0], xs.stride[0], ys.stride[0], alpha, stream);
 }
 
+// "linear_tile": the block-scaled linear kernels of the reference, which share one name and one parameter list
+//   (z [M,N] f32 partition [BM,BN], x, y, x_scales, y_scales, alpha f32) and differ in the operand types:
+//   NVFP4  (cutile-examples/examples/nvfp4.rs:37-76): x [M,K/2], y [N,K/2] f4e2m1fnx2, scales [.,K/16] f8e4m3fn,
+//          generics [BM, BN, BK, BK_PACKED = BK/2, BK_SCALES = BK/16]
+//   MXFP8  (cutile-examples/examples/mxfp8.rs:34-64): x [M,K], y [N,K] f8e4m3fn, scales [.,K/32] f8e8m0fnu,
+//          generics [BM, BN, BK, BK_SCALES = BK/32]
+//   The element types are not generics in the reference, so the two are told apart by the generics themselves
+//   (five integers with BK = 16 BK_SCALES, or four with BK = 32 BK_SCALES); an optional leading type name
+//   selects a bf16 output instead of the reference's f32.  Any tile generics are accepted: they shape the
+//   launch grid, which is validated, and the kernel runs its own tile.  The scale re-layout scratch is a
+//   library-owned block per (device, stream).  Weight scales registered with
+//   b200tile_nvfp4_register_weight_scales are used in their prepared form for decode-sized M.
+int launch_linear_tile_generic(const char* kernel, const char* const* generics, int n_generics,
+                               const void* const* params, int n_params, const unsigned grid[3], void* stream,
+                               bool launch) {
+  const char* dtype;
+  long g[8];
+  int ng;
+  if (split_generics(generics, n_generics, "f32", &dtype, g, 8, &ng) || (ng != 4 && ng != 5))
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "%s: generics must be [BM, BN, BK, BK_PACKED, BK_SCALES] (NVFP4) or [BM, BN, BK, BK_SCALES] (MXFP8)",
+                     kernel);
+  const bool fp4 = ng == 5;
+  const long BM = g[0], BN = g[1], BK = g[2];
+  if (BM <= 0 || BN <= 0 || BK <= 0)
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: tile generics must be positive", kernel);
+  if (fp4 ? (g[3] * 2 != BK || g[4] * 16 != BK) : (g[3] * 32 != BK))
+    return set_error(B200TILE_ERR_UNSUPPORTED,
+                     "%s: generics do not describe a supported block-scaled format (NVFP4: BK_PACKED = BK/2 and "
+                     "BK_SCALES = BK/16; MXFP8: BK_SCALES = BK/32)", kernel);
+  if (strcmp(dtype, "f32") && strcmp(dtype, "bf16"))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported output type '%s'", kernel, dtype);
+  if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
+  ParamReader r{params, n_params, 0, true};
+  TensorArg z, x, y, xs, ys;
+  read_tensor(r, 2, true, z);
+  read_tensor(r, 2, false, x);
+  read_tensor(r, 2, false, y);
+  read_tensor(r, 2, false, xs);
+  read_tensor(r, 2, false, ys);
+  const float alpha = r.f32();
+  if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
+  const int M = z.dim[0], N = z.dim[1];
+  const int K = fp4 ? x.dim[1] * 2 : x.dim[1];
+  const int V = fp4 ? 16 : 32;
+  if (x.dim[0] != M || y.dim[0] != N || y.dim[1] != x.dim[1] || xs.dim[0] != M || ys.dim[0] != N ||
+      xs.dim[1] * V != K || ys.dim[1] * V != K)
+    return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
+  if (z.stride[1] != 1 || x.stride[1] != 1 || y.stride[1] != 1 || xs.stride[1] != 1 || ys.stride[1] != 1)
+    return set_error(B200TILE_ERR_INVALID, "%s: the last axis of every tensor must be contiguous", kernel);
+  if (z.pdim[0] != BM || z.pdim[1] != BN)
+    return set_error(B200TILE_ERR_INVALID, "%s: output partition does not match the tile generics", kernel);
+  if (grid[0] != (unsigned)((M + BM - 1) / BM) || grid[1] != (unsigned)((N + BN - 1) / BN) || grid[2] != 1)
+    return set_error(B200TILE_ERR_INVALID,
+                     "launch grid (%u, %u, %u) does not match the inferred partition grid", grid[0],
+                     grid[1], grid[2]);
+  const void* xp = reinterpret_cast<const void*>(x.ptr);
+  const void* yp = reinterpret_cast<const void*>(y.ptr);
+  const void* xsp = reinterpret_cast<const void*>(xs.ptr);
+  const void* ysp = reinterpret_cast<const void*>(ys.ptr);
+  void* zp = reinterpret_cast<void*>(z.ptr);
+  if (fp4 && M <= 128) {
+    const void* prepared = nullptr;
+    int config = 0;
+    if (nvfp4_registry_find(ysp, N, K, ys.stride[0], &prepared, &config))
+      return b200tile_linear_nvfp4_prepared(xp, yp, xsp, prepared, zp, dtype, M, N, K, x.stride[0], y.stride[0],
+                                            z.stride[0], xs.stride[0], alpha, config, stream);
+  }
+  const uint64_t need = fp4 ? b200tile_linear_nvfp4_workspace_bytes(M, N, K) : b200tile_linear_mxfp8_workspace_bytes(M, N, K);
+  void* ws = b200h::stream_scratch(static_cast<cudaStream_t>(stream), need, kernel);
+  if (!ws) return B200TILE_ERR_INVALID;
+  if (fp4)
+    return b200tile_linear_nvfp4(xp, yp, xsp, ysp, zp, dtype, M, N, K, x.stride[0], y.stride[0], z.stride[0],
+                                 xs.stride[0], ys.stride[0], alpha, ws, need, -1, stream);
+  return b200tile_linear_mxfp8(xp, yp, xsp, ysp, zp, dtype, M, N, K, x.stride[0], y.stride[0], z.stride[0],
+                               xs.stride[0], ys.stride[0], alpha, ws, need, stream);
+}
+
 // Serving attention kernels of cutile-kernels/src/attention.rs in their own parameter order.
 // "fmha_prefill_gqa" (:398-582): (q [q_len,q_heads,D], k, v [kv_heads,kv_len,D], out partition
 //    [BM,GROUP,D], qk_scale f32, query_group_size i32, kv_len i32, query_start i32), generics
@@ -1518,6 +1660,8 @@ int b200tile_launch(const char* kernel, const char* const* generics, int n_gener
                                cu_stream, true);
   if (!strcmp(kernel, "linear_tile_fp8_blk128"))
     return launch_linear_fp8_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
+  if (!strcmp(kernel, "linear_tile"))
+    return launch_linear_tile_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   if (!strcmp(kernel, "fmha_prefill_gqa") || !strcmp(kernel, "fmha_causal"))
     return launch_fmha_serving_generic(kernel, generics, n_generics, params, n_params, grid, cu_stream, true);
   if (!strcmp(kernel, "fmha_decode_gqa_split") || !strcmp(kernel, "splitk_reduce_merge"))
@@ -1549,6 +1693,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
                                false);
   if (!strcmp(kernel, "linear_tile_fp8_blk128"))
     return launch_linear_fp8_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
+  if (!strcmp(kernel, "linear_tile"))
+    return launch_linear_tile_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   if (!strcmp(kernel, "fmha_prefill_gqa") || !strcmp(kernel, "fmha_causal"))
     return launch_fmha_serving_generic(kernel, generics, n_generics, nullptr, 0, nullptr, nullptr, false);
   if (!strcmp(kernel, "fmha_decode_gqa_split") || !strcmp(kernel, "splitk_reduce_merge"))
@@ -1581,6 +1727,13 @@ B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!strcmp(which, "fmha_alt")) return b200_trace_read_fmha_alt(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "block_scaled")) return b200_trace_read_fp4(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   return B200TILE_ERR_UNSUPPORTED;
+}
+#endif
+
+#ifdef B200TILE_TEST_HOOKS
+// Test builds only: arms / disarms the producer hook of gemm_tc.cu that leaves one stage unloaded.
+B200TILE_API int b200tile_test_set_skip_stage(int on) {
+  return b200_test_set_skip_stage(on) ? B200TILE_ERR_CUDA : B200TILE_OK;
 }
 #endif
 

@@ -3,7 +3,13 @@
 set -euo pipefail
 here="$(cd "$(dirname "${BASH_SOURCE[0]}")" && pwd)"
 # B200_VARIANT=name builds a second library (libb200tile_name.so, objects _x.name.o) next to the
-# product one, e.g. the diagnostic build: B200_VARIANT=trace B200_NVCC_EXTRA=-DB200TILE_TRACE
+# product one:
+#   B200_VARIANT=waittest B200_NVCC_EXTRA="-DB200TILE_TEST_HOOKS -DB200_WAIT_LIMIT_CYCLES=(1ll<<20)"
+#       the library tests/test_wait_timeout_gpu.py loads: bounded waits give up after about half a
+#       millisecond and a producer hook can leave one stage unloaded (built by __graft_entry__.build())
+#   B200_VARIANT=trace B200_NVCC_EXTRA=-DB200TILE_TRACE
+#       diagnostic build with cycle counters in the MMA / softmax loops and b200tile_trace_read
+# The product library contains neither the hooks nor the counters.
 variant="${B200_VARIANT:-}"
 out="${here}/../libb200tile${variant:+_${variant}}.so"
 NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"

@@ -17,6 +17,13 @@
 
 namespace b200 {
 
+#ifdef B200TILE_TEST_HOOKS
+// Test builds only (libb200tile_waittest.so, never the product library): when set, CTA 0 leaves the second
+// k-slab of its first tile unloaded, so the MMA thread's wait for that stage runs out.  This is how the
+// bounded-wait path is exercised without faulting, trapping or hanging anything.
+__device__ int g_test_skip_stage;
+#endif
+
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;  // 64 x 2 bytes = one 128-byte swizzle row
 constexpr int GEMM_THREADS = 192;
@@ -140,6 +147,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         const int m0 = bm * GEMM_BM, n0 = bn * BN_OUT;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
+#ifdef B200TILE_TEST_HOOKS
+          if (g_test_skip_stage && blockIdx.x == 0 && tile == 0 && kb == 1) {
+            ok = false;   // the producer stops here: this stage's barrier is never armed, and the only
+            break;        // wait left to run out is the MMA thread's (one deterministic wait site)
+          }
+#endif
           const uint32_t full = bar_full + stage * 8;
           mbar_expect_tx(full, L::A_BYTES + L::B_BYTES);
           tma_load_2d(sA + stage * L::A_BYTES, &tmA, full, kb * GEMM_BK, m0);
@@ -381,3 +394,9 @@ int b200_gemm_swiglu_dispatch(int dtype, const void* X, const void* W, void* O, 
   return dtype ? launch_gemm_swiglu<true>(X, W, O, M, I, K, ldx, ldw, ldo, stream)
                : launch_gemm_swiglu<false>(X, W, O, M, I, K, ldx, ldw, ldo, stream);
 }
+
+#ifdef B200TILE_TEST_HOOKS
+int b200_test_set_skip_stage(int on) {
+  return cudaMemcpyToSymbol(b200::g_test_skip_stage, &on, sizeof(int)) != cudaSuccess;
+}
+#endif

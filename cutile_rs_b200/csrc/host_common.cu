@@ -138,4 +138,88 @@ const DeviceInfo* device_info() {
   return &d;
 }
 
+// ---------------------------------------------------------------------------
+// Per-(device, stream) scratch blocks.
+// ---------------------------------------------------------------------------
+namespace {
+struct ScratchBlock {
+  unsigned long long stream_id;
+  cudaStream_t handle;
+  bool handle_live;   // false once another stream has been seen under the same handle
+  void* ptr;
+  size_t bytes;
+  bool used;
+};
+constexpr int kScratchPerDevice = 16;
+ScratchBlock g_scratch[64][kScratchPerDevice];
+std::mutex g_scratch_mu;
+}  // namespace
+
+void* stream_scratch(cudaStream_t stream, size_t bytes, const char* who) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error(B200_ERR_CUDA, "%s: no usable CUDA device is current", who);
+    return nullptr;
+  }
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cs) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(B200_ERR_CUDA, "%s: cudaStreamIsCapturing failed", who);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_scratch_mu);
+  ScratchBlock* tab = g_scratch[dev];
+  if (cs != cudaStreamCaptureStatusNone) {
+    for (int i = 0; i < kScratchPerDevice; ++i)
+      if (tab[i].used && tab[i].handle_live && tab[i].handle == stream && tab[i].bytes >= bytes) return tab[i].ptr;
+    set_error(B200_ERR_INVALID,
+              "%s: needs %llu bytes of library scratch, which cannot be allocated inside a stream capture; run the "
+              "call once on this stream before capturing, or use the entry point that takes a workspace",
+              who, (unsigned long long)bytes);
+    return nullptr;
+  }
+  unsigned long long id = 0;
+  if (cudaStreamGetId(stream, &id) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(B200_ERR_CUDA, "%s: cudaStreamGetId failed", who);
+    return nullptr;
+  }
+  ScratchBlock* e = nullptr;
+  for (int i = 0; i < kScratchPerDevice && !e; ++i)
+    if (tab[i].used && tab[i].stream_id == id) e = &tab[i];
+  if (e && e->bytes >= bytes) return e->ptr;
+  if (!e)
+    for (int i = 0; i < kScratchPerDevice && !e; ++i)
+      if (!tab[i].used) e = &tab[i];
+  if (!e) {
+    set_error(B200_ERR_INVALID, "%s: all %d scratch blocks of this device belong to other streams; use the entry "
+              "point that takes a workspace", who, kScratchPerDevice);
+    return nullptr;
+  }
+  if (e->used) {
+    // grow: earlier launches of this stream may still read the old block
+    if (cudaStreamSynchronize(stream) != cudaSuccess || cudaFree(e->ptr) != cudaSuccess) {
+      set_error(B200_ERR_CUDA, "%s: could not release the old scratch block", who);
+      return nullptr;
+    }
+    e->used = false;
+  }
+  const size_t grow = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes + bytes / 2;
+  void* p = nullptr;
+  if (cudaMalloc(&p, grow) != cudaSuccess) {
+    cudaGetLastError();
+    set_error(B200_ERR_CUDA, "%s: cudaMalloc of %llu scratch bytes failed", who, (unsigned long long)grow);
+    return nullptr;
+  }
+  e->stream_id = id;
+  e->handle = stream;
+  e->handle_live = true;
+  e->ptr = p;
+  e->bytes = grow;
+  e->used = true;
+  for (int j = 0; j < kScratchPerDevice; ++j)
+    if (&tab[j] != e && tab[j].used && tab[j].handle == stream) tab[j].handle_live = false;
+  return p;
+}
+
 }  // namespace b200h

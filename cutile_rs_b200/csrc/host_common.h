@@ -52,6 +52,13 @@ struct DeviceInfo {
 // Returns nullptr (and sets the error) when the current device is unusable.
 const DeviceInfo* device_info();
 
+// Library-owned scratch, one block per (device, stream), grown on demand and kept until process exit.
+// Streams are told apart by cudaStreamGetId (never reused within a process); inside a stream capture,
+// where that query and every allocation are illegal, a block is found by the stream handle it was
+// created under, and a missing or too-small block is an error.  Returns nullptr with the error set.
+// Work enqueued on one stream is ordered, so consecutive launches may share the block.
+void* stream_scratch(cudaStream_t stream, size_t bytes, const char* who);
+
 #define B200_CUDA_CHECK(expr)                                                              \
   do {                                                                                     \
     cudaError_t _e = (expr);                                                               \

@@ -338,6 +338,50 @@ def linear_tile_fp8_blk128(z: Output, x: Tensor, y: Tensor, x_scales: Tensor, y_
     return LinearFp8Blk128([z, x, y, x_scales, y_scales, float(alpha)])
 
 
+class LinearTile(KernelLauncher):
+    """The reference's block-scaled `linear_tile` under its own name: z [M,N] partition [BM,BN] = alpha * x . y^T.
+    NVFP4 operands (``f4e2m1fnx2``) infer generics [BM, BN, BK, BK/2, BK/16], MXFP8 operands (``f8e4m3fn``)
+    [BM, BN, BK, BK/32]; a bf16 output prepends its type name (the reference's output is f32)."""
+    kernel_name = "linear_tile"
+
+    def infer_generics(self) -> List[str]:
+        z, x = self.args[0], self.args[1]
+        bm, bn = z.partition_shape[0], z.partition_shape[1]
+        head = [] if z.dtype_str() == "f32" else [z.dtype_str()]
+        if x.dtype == "f4e2m1fnx2":
+            return head + [str(bm), str(bn), "64", "32", "4"]
+        if x.dtype == "f8e4m3fn":
+            return head + [str(bm), str(bn), "64", "2"]
+        raise KernelLaunchError(f"linear_tile: operands of type {x.dtype} are not a block-scaled format "
+                                "(f4e2m1fnx2 or f8e4m3fn)")
+
+
+def linear_tile(z: Output, x: Tensor, y: Tensor, x_scales: Tensor, y_scales: Tensor, alpha: float = 1.0) -> LinearTile:
+    """`linear_tile` of cutile-examples/examples/nvfp4.rs:37-76 (x, y packed ``f4e2m1fnx2`` [., K/2], scales
+    ``f8e4m3fn`` [., K/16]) and of cutile-examples/examples/mxfp8.rs:34-64 (x, y ``f8e4m3fn`` [., K], scales
+    ``f8e8m0fnu`` [., K/32]); which of the two runs follows from the generics, as in the reference the operand
+    types are part of the kernel's signature.  The scale re-layout scratch belongs to the library (one block per
+    stream); weight scales registered with :func:`nvfp4_register_weight_scales` are used in their prepared form."""
+    return LinearTile([z, x, y, x_scales, y_scales, float(alpha)])
+
+
+def nvfp4_register_weight_scales(y_scales: Tensor, n: int, k: int, prepared: torch.Tensor, config: int = 0) -> None:
+    """Registers weight scales prepared by :func:`nvfp4_prepare_weight_scales` under the address of their row-major
+    original, for decode-sized calls of :func:`linear_tile`.  Keep both tensors alive until unregistered."""
+    lib = _lib.load()
+    rc = lib.b200tile_nvfp4_register_weight_scales(y_scales.cu_deviceptr(), n, k, y_scales.strides[0], config,
+                                                   prepared.data_ptr())
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+
+
+def nvfp4_unregister_weight_scales(y_scales: Tensor) -> None:
+    lib = _lib.load()
+    rc = lib.b200tile_nvfp4_unregister_weight_scales(y_scales.cu_deviceptr())
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+
+
 def linear_nvfp4(z: Tensor, x: Tensor, y: Tensor, x_scales: Tensor, y_scales: Tensor, alpha: float = 1.0,
                  stream: Optional[torch.cuda.Stream] = None, config: int = -1,
                  workspace: Optional[torch.Tensor] = None) -> Tensor:

@@ -387,6 +387,17 @@ B200TILE_API int b200tile_linear_nvfp4_prepared(const void* x, const void* y, co
                                                 int m, int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
                                                 int64_t ld_xs, float alpha, int config, void* cu_stream);
 
+/* Registry behind the generic `linear_tile` route.  The reference's kernel takes the weight scales in
+ * logical row-major order on every call (cutile-examples/examples/nvfp4.rs:37-76); weights of a served model
+ * do not change, so their scales can be laid out once (b200tile_nvfp4_prepare_weight_scales) and registered
+ * under the address of the row-major tensor.  b200tile_launch("linear_tile", ...) with M <= 128 on a registered
+ * y_scales (same n, k, row pitch, current device) then runs the prepared form: one kernel, no scale pre-pass.
+ * The caller keeps both buffers alive and unregisters before freeing either.  No counterpart in the
+ * reference, whose JIT re-reads the row-major scales in every launch. */
+B200TILE_API int b200tile_nvfp4_register_weight_scales(const void* y_scales, int n, int k, int64_t ld_ys,
+                                                       int config, const void* prepared);
+B200TILE_API int b200tile_nvfp4_unregister_weight_scales(const void* y_scales);
+
 /* Same computation as b200tile_linear_nvfp4, for callers that cannot provide device memory
  * (no counterpart in the reference, whose launchers always allocate through their own pool):
  * code that runs while a stream is being captured and must stay away from any allocator, plugins
