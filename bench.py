@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the dense-contraction hot path on N B200s of one node.
 
-Headline workload (BASELINE config 1): bf16 GEMM M=N=K=8192, A[M,K] and B[K,N] ~ N(0,1)/sqrt(K)
+Headline workload: bf16 GEMM M=N=K=8192, A[M,K] and B[K,N] ~ N(0,1)/sqrt(K)
 rounded to bf16, fp32 accumulation, bf16 output.  A "step" is one GEMM launch.  With N>1 GPUs the
 weight columns are split (rank r owns B[:, r*N/G:(r+1)*N/G] and the matching columns of C, A is
 replicated), so the total work is fixed ("strong" scaling) and no data-path collective runs.
@@ -10,8 +10,10 @@ replicated), so the total work is fixed ("strong" scaling) and no data-path coll
 the public launcher API with HOST buffers (pinned host -> device copies of A and B and a
 device -> host read of C inside the timed region).  `roofline` compares the kernel with the
 measured cuBLAS bf16 peak of this pool; `cpu_baseline` times the CPU oracle (a port of the
-reference's `cpu_gemm`) on a bounded slab.  `extra` reports FMHA forward (BASELINE config 2,
-8 x 32 x 4096 x 128, sharded by batch x head) measured the same way.
+reference's `cpu_gemm`) on a bounded slab.  The other workloads of the path (FMHA forward 8 x 32 x 4096 x
+128 non-causal and causal, the fp8 block-scaled GEMM 8192 x 28672 x 8192, the NVFP4 GEMM 4096 / 16 x 14336 x
+4096 and the f32 512^3 GEMM) are measured the same way and reported as `by_config` entries inside `roofline`,
+`cpu_baseline` and `e2e`; `extra` holds compact figures for the neighbouring kernels.
 
 `--impl reference` times the reference's own CPU implementation of the path (the oracle port of
 `cpu_gemm`; the reference's GPU path needs a Rust toolchain and NVIDIA's `tileiras`, neither of
@@ -231,7 +233,552 @@ def run_reference_arm(args):
 # ------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------
+NOMINAL_BF16, NOMINAL_FP8, NOMINAL_FP4 = 2250.0, 4500.0, 9000.0   # dense TFLOP/s per GPU (fp8 / fp4 = 2x / 4x bf16)
+
+
+class Ctx:
+    """What every workload of the GPU arm needs: the library, the stream, the ranks and a device timer."""
+
+    def __init__(self, lib, stream, dev, world, rank):
+        import torch
+        self.lib, self.stream, self.dev, self.world, self.rank = lib, stream, dev, world, rank
+        self.e0, self.e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.launches = 0
+
+    def barrier(self):
+        import torch
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(self, fn, iters, warm=3):
+        """ms per call: CUDA events on the launching stream, barrier + synchronize on both sides, max over ranks."""
+        from cutile_rs_b200 import sharding
+        for _ in range(warm):
+            fn()
+        self.barrier()
+        self.e0.record(self.stream)
+        for _ in range(iters):
+            fn()
+        self.e1.record(self.stream)
+        self.barrier()
+        return sharding.max_over_ranks(self.e0.elapsed_time(self.e1), self.dev) / iters
+
+
+def _roof(bound, achieved, peak, unit, ms, source, **more):
+    d = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+         "frac": (achieved / peak) if peak else None, "ms": ms, "peak_source": source}
+    d.update(more)
+    return d
+
+
+def _pin_like(t):
+    import torch
+    return torch.empty(t.shape, dtype=t.dtype).pin_memory()
+
+
+def bench_fmha(ctx, by, cpu_by, e2e_by, do_cpu):
+    """FMHA forward bf16 8 x 32 x 4096 x 128 (b x h split over the ranks), non-causal and causal."""
+    import ctypes
+    import torch
+    from cutile_rs_b200 import _lib, sharding, workloads
+    lib, stream, dev, world = ctx.lib, ctx.stream, ctx.dev, ctx.world
+    peak, _, src = measured_peaks()
+    B_, H_, S_, D_ = 8, 32, 4096, 128
+    p0, p1 = sharding.split_range(B_ * H_, world, ctx.rank, 1)
+    nb = p1 - p0
+    g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 2 + ctx.rank)
+    q = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
+    k = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
+    v = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
+    o = torch.empty_like(q)
+    st = (ctypes.c_int64 * 2)(S_ * D_, D_)
+    scale = 1.0 / math.sqrt(D_)
+    qh, kh, vh, oh = q.cpu().pin_memory(), k.cpu().pin_memory(), v.cpu().pin_memory(), _pin_like(o)
+    for causal in (False, True):
+        name = "fmha_causal" if causal else "fmha_noncausal"
+
+        def fstep():
+            _lib.check(lib.b200tile_fmha_fwd(b"bf16", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), 1, nb, nb,
+                                             S_, S_, D_, st, st, st, st, scale, int(causal), 0, stream.cuda_stream))
+        ms = ctx.timed(fstep, 10)
+        flops = workloads.fmha_flops(B_, H_, S_, D_, causal)
+        tf = flops / (ms * 1e-3) / 1e12 / world
+        by[name] = _roof("tensor", tf, peak, "TFLOP/s", ms, f"{src} cuBLAS bf16 burst", frac_of_nominal_2250=tf / NOMINAL_BF16)
+
+        def estep():
+            q.copy_(qh, non_blocking=True)
+            k.copy_(kh, non_blocking=True)
+            v.copy_(vh, non_blocking=True)
+            fstep()
+            oh.copy_(o, non_blocking=True)
+        ems = ctx.timed(estep, 3, warm=1)
+        e2e_by[name] = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ems,
+                        "h2d_bytes_per_step": 3 * B_ * H_ * S_ * D_ * 2, "d2h_bytes_per_step": B_ * H_ * S_ * D_ * 2}
+        ctx.launches += 13 + 4
+        if do_cpu:
+            from oracle import oracle
+            nbh, rows = 4, 256
+            qf = q[:nbh].float().cpu().numpy().reshape(1, nbh, S_, D_)
+            kf = k[:nbh].float().cpu().numpy().reshape(1, nbh, S_, D_)
+            vf = v[:nbh].float().cpu().numpy().reshape(1, nbh, S_, D_)
+            thr = oracle.max_threads()
+            t0 = time.perf_counter()
+            oracle.fmha_ref_cpu(qf, kf, vf, scale, causal=causal, bh=(0, nbh), rows=(S_ - rows, S_), threads=thr)
+            dt = time.perf_counter() - t0
+            rf = nbh * rows * 4.0 * S_ * D_ / (2.0 if causal else 1.0)
+            cpu_by[name] = {"value": rf / dt / 1e12, "unit": "TFLOP/s", "cores": thr, "kind": "port",
+                            "sample": f"fmha_ref_cpu port, {nbh} (b,h) x last {rows} query rows, {dt:.1f} s"}
+    # the CTA-pair configuration of the same non-causal shape, through the launcher mirror
+    from cutile_rs_b200 import api, launch
+    qd, kd, vd = (api.from_torch(t_.view(1, nb, S_, D_)) for t_ in (q, k, v))
+    od = [api.from_torch(o).partition([1, 128, D_])]
+    fopts = launch.CompileOptions(num_cta_in_cga=2)
+
+    def pstep():
+        (od[0], *_r) = launch.fmha(od[0], qd, kd, vd, scale, 0, 1, causal=False).compile_options(fopts).async_on(stream)
+    pms = ctx.timed(pstep, 10)
+    ctx.launches += 13
+    return {"fmha_noncausal_cta_pairs": {"tflops_per_gpu": workloads.fmha_flops(B_, H_, S_, D_, False) / (pms * 1e-3) / 1e12 / world,
+                                         "ms": pms}}
+
+
+def bench_fp8(ctx, by, cpu_by, e2e_by, do_cpu):
+    """fp8 e4m3 GEMM 8192 x 28672 x 8192 with fp32 scales per 1x128 / 128x128 block (weight rows split over the ranks),
+    and the same shape as MXFP8 (e8m0 scale per 32, applied by the tensor core)."""
+    import torch
+    from cutile_rs_b200 import _lib, quant, sharding, workloads
+    lib, stream, dev, world = ctx.lib, ctx.stream, ctx.dev, ctx.world
+    g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 3)
+    m8, n8, k8 = 8192, 28672, 8192
+    r0, r1 = sharding.split_range(n8, world, ctx.rank, 256)
+    nl = r1 - r0
+    xq, xs = quant.quant_fp8_block(torch.randn(m8, k8, device=dev, generator=g), 1, 128)
+    yq, ys = quant.quant_fp8_block(torch.randn(nl, k8, device=dev, generator=g), 128, 128)
+    z8 = torch.empty(m8, nl, dtype=torch.bfloat16, device=dev)
+
+    def f8step():
+        _lib.check(lib.b200tile_linear_fp8_blk128(xq.data_ptr(), yq.data_ptr(), xs.data_ptr(), ys.data_ptr(), z8.data_ptr(),
+                                                  b"bf16", m8, nl, k8, k8, k8, nl, k8 // 128, k8 // 128, 1.0,
+                                                  stream.cuda_stream))
+    ms = ctx.timed(f8step, 5)
+    flops = workloads.gemm_flops(m8, n8, k8)
+    tf = flops / (ms * 1e-3) / 1e12 / world
+    by["fp8_blk128"] = _roof("tensor", tf, NOMINAL_FP8, "TFLOP/s", ms, "nominal dense fp8 = 2 x 2250 (no measured fp8 peak)")
+    hx, hy, hxs, hys, hz = xq.cpu().pin_memory(), yq.cpu().pin_memory(), xs.cpu().pin_memory(), ys.cpu().pin_memory(), _pin_like(z8)
+
+    def estep():
+        xq.copy_(hx, non_blocking=True)
+        yq.copy_(hy, non_blocking=True)
+        xs.copy_(hxs, non_blocking=True)
+        ys.copy_(hys, non_blocking=True)
+        f8step()
+        hz.copy_(z8, non_blocking=True)
+    ems = ctx.timed(estep, 3, warm=1)
+    e2e_by["fp8_blk128"] = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ems,
+                            "h2d_bytes_per_step": world * (hx.numel() + hxs.numel() * 4) + n8 * k8 + (n8 // 128) * (k8 // 128) * 4,
+                            "d2h_bytes_per_step": m8 * n8 * 2}
+    ctx.launches += 8 + 4
+    if do_cpu:
+        from oracle import oracle
+        rows, cols = 16, 2048
+        thr = oracle.max_threads()
+        xqn, xsn = hx[:128].numpy().view("uint8"), hxs[:128].numpy()
+        yqn, ysn = hy[:cols].numpy().view("uint8"), hys[:cols // 128].numpy()
+        t0 = time.perf_counter()
+        xa = oracle.dequant_fp8_block(xqn, xsn, 1, 128)[:rows]
+        ya = oracle.dequant_fp8_block(yqn, ysn, 128, 128)
+        oracle.cpu_gemm_nt(xa, ya, threads=thr)
+        dt = time.perf_counter() - t0
+        cpu_by["fp8_blk128"] = {"value": 2.0 * rows * cols * k8 / dt / 1e12, "unit": "TFLOP/s", "cores": thr, "kind": "port",
+                                "sample": f"dequantise + cpu_gemm port on C[0:{rows}, 0:{cols}], K={k8}, {dt:.1f} s"}
+    del hx, hy, hxs, hys, hz
+    # MXFP8 on the same shape
+    xm, xms = quant.quant_mxfp8(torch.randn(m8, k8, device=dev, generator=g))
+    ym, yms = quant.quant_mxfp8(torch.randn(nl, k8, device=dev, generator=g))
+    wsm = lib.b200tile_linear_mxfp8_workspace_bytes(m8, nl, k8)
+    wsb8 = torch.empty(wsm, dtype=torch.uint8, device=dev)
+
+    def mx8step():
+        _lib.check(lib.b200tile_linear_mxfp8(xm.data_ptr(), ym.data_ptr(), xms.data_ptr(), yms.data_ptr(), z8.data_ptr(),
+                                             b"bf16", m8, nl, k8, k8, k8, nl, k8 // 32, k8 // 32, 1.0, wsb8.data_ptr(), wsm,
+                                             stream.cuda_stream))
+    msm = ctx.timed(mx8step, 5)
+    ctx.launches += 8 * 2
+    tfm = flops / (msm * 1e-3) / 1e12 / world
+    return {"gemm_mxfp8_8192x28672x8192": {"tflops_per_gpu": tfm, "ms": msm, "frac_of_nominal_4500": tfm / NOMINAL_FP8}}
+
+
+def bench_nvfp4(ctx, by, cpu_by, e2e_by, do_cpu):
+    """NVFP4 GEMM N=14336, K=4096 at M=4096 and the decode shape M=16 (weight rows split over the ranks), through the
+    reference's own kernel name: b200tile_launch("linear_tile", ...)."""
+    import torch
+    from cutile_rs_b200 import _lib, api, launch, quant, sharding, workloads
+    lib, stream, dev, world = ctx.lib, ctx.stream, ctx.dev, ctx.world
+    _, hbm_peak, src = measured_peaks()
+    g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 4)
+    n4, k4 = 14336, 4096
+    r0, r1 = sharding.split_range(n4, world, ctx.rank, 256)
+    nl = r1 - r0
+    yp, ysc, gy = quant.quant_nvfp4(torch.randn(nl, k4, device=dev, generator=g))
+    y, sy = api.from_torch(yp, "f4e2m1fnx2"), api.from_torch(ysc, "f8e4m3fn")
+    extra = {}
+    for m4 in (4096, 16):
+        name = f"nvfp4_m{m4}"
+        xp, xsc, gx = quant.quant_nvfp4(torch.randn(m4, k4, device=dev, generator=g))
+        x, sx = api.from_torch(xp, "f4e2m1fnx2"), api.from_torch(xsc, "f8e4m3fn")
+        z4 = torch.empty(m4, nl, dtype=torch.bfloat16, device=dev)
+        zp = [api.from_torch(z4).partition([16, 128])]
+        alpha = gx * gy
+
+        def f4step():
+            (zp[0], *_r) = launch.linear_tile(zp[0], x, y, sx, sy, alpha).async_on(stream)
+        if m4 <= 128:
+            # decode: launch-bound from Python, so the call is captured once and replayed (CUDA graph), which is how
+            # a serving loop issues it.  First with the per-call weight-scale pre-pass, then with the weight scales
+            # (constants of the model) laid out once and registered: the same generic call then runs one kernel.
+            cap = torch.cuda.Stream()
+            cap.wait_stream(stream)
+            (zp[0], *_r) = launch.linear_tile(zp[0], x, y, sx, sy, alpha).sync_on(cap)   # the capture stream's scratch
+            graph = launch.linear_tile(zp[0], x, y, sx, sy, alpha).graph_on(cap)
+            extra["nvfp4_m16_unregistered_weight_scales_us"] = ctx.timed(lambda: graph.launch(), 20) * 1e3
+            prep = launch.nvfp4_prepare_weight_scales(sy, nl, k4, 0)
+            launch.nvfp4_register_weight_scales(sy, nl, k4, prep, 0)
+            torch.cuda.synchronize()
+            graph = launch.linear_tile(zp[0], x, y, sx, sy, alpha).graph_on(cap)
+
+            def f4step():
+                graph.launch()
+            ctx.launches += 23 * 2 + 3
+        ms = ctx.timed(f4step, 20 if m4 <= 128 else 10)
+        ctx.launches += 23 if m4 <= 128 else 13 * 2
+        flops = workloads.gemm_flops(m4, n4, k4)
+        nbytes = (m4 * k4 // 2 + m4 * k4 // 16 + n4 * k4 // 2 + n4 * k4 // 16 + m4 * n4 * 2)
+        if m4 <= 128:
+            gbs = nbytes / (ms * 1e-3) / 1e9 / world
+            by[name] = _roof("hbm", gbs, hbm_peak, "GB/s", ms, f"{src} copy bandwidth", algorithmic_bytes=nbytes,
+                             tflops=flops / (ms * 1e-3) / 1e12 / world,
+                             how="generic linear_tile call, registered weight scales, CUDA-graph replay")
+        else:
+            tf = flops / (ms * 1e-3) / 1e12 / world
+            by[name] = _roof("tensor", tf, NOMINAL_FP4, "TFLOP/s", ms, "nominal dense fp4 = 4 x 2250 (no measured fp4 peak)")
+        hx, hxs, hy, hys, hz = xp.cpu().pin_memory(), xsc.cpu().pin_memory(), yp.cpu().pin_memory(), ysc.cpu().pin_memory(), _pin_like(z4)
+
+        def estep():
+            xp.copy_(hx, non_blocking=True)
+            xsc.copy_(hxs, non_blocking=True)
+            if m4 > 128:                 # decode: the weights stay resident, as they do in serving
+                yp.copy_(hy, non_blocking=True)
+                ysc.copy_(hys, non_blocking=True)
+            f4step()
+            hz.copy_(z4, non_blocking=True)
+        ems = ctx.timed(estep, 5, warm=1)
+        ctx.launches += 6 * 2
+        e2e_by[name] = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ems,
+                        "h2d_bytes_per_step": world * (hx.numel() + hxs.numel()) + (0 if m4 <= 128 else n4 * k4 // 2 + n4 * k4 // 16),
+                        "d2h_bytes_per_step": m4 * n4 * 2,
+                        "note": "weights resident, CUDA-graph replay" if m4 <= 128 else "all operands uploaded"}
+        if do_cpu:
+            from oracle import oracle
+            rows, cols = min(m4, 64), 2048
+            thr = oracle.max_threads()
+            t0 = time.perf_counter()
+            xa = oracle.dequant_nvfp4(hx[:rows].numpy(), hxs[:rows].numpy())
+            ya = oracle.dequant_nvfp4(hy[:cols].numpy(), hys[:cols].numpy())
+            oracle.cpu_gemm_nt(xa, ya, alpha=alpha, threads=thr)
+            dt = time.perf_counter() - t0
+            cpu_by[name] = {"value": 2.0 * rows * cols * k4 / dt / 1e12, "unit": "TFLOP/s", "cores": thr, "kind": "port",
+                            "sample": f"dequantise + cpu_gemm port on C[0:{rows}, 0:{cols}], K={k4}, {dt:.1f} s"}
+        if m4 <= 128:
+            launch.nvfp4_unregister_weight_scales(sy)
+    return extra
+
+
+def bench_f32(ctx, by, cpu_by, e2e_by, do_cpu):
+    """f32 GEMM 512^3, the reference's CPU-runnable configuration: exact fp32 arithmetic on the CUDA cores (replicas
+    only: every rank runs the whole problem)."""
+    import torch
+    from cutile_rs_b200 import api, launch, workloads
+    stream = ctx.stream
+    a, b = workloads.gemm_f32_inputs(512, 512, 512)
+    x, y = api.copy_host_to_device(a), api.copy_host_to_device(b)
+    z = [api.zeros([512, 512]).partition([64, 64])]
+    gen = ["f32", "64", "64", "16"]
+
+    def step():
+        (z[0], *_r) = launch.gemm(z[0], x, y).generics(gen).async_on(stream)
+    ms = ctx.timed(step, 20)
+    flops = workloads.gemm_flops(512, 512, 512)
+    by["f32_512"] = _roof("none", flops / (ms * 1e-3) / 1e9, None, "GFLOP/s", ms,
+                          "correctness configuration: bit-exact fp32, no tensor path, no roofline claim")
+    ap, bp = api.pin(a), api.pin(b)
+    cp = torch.empty(512, 512).pin_memory()
+
+    def estep():
+        xa = api.copy_host_to_device(ap, stream=stream)
+        yb = api.copy_host_to_device(bp, stream=stream)
+        (zz, _, _) = launch.gemm(z[0], xa, yb).generics(gen).async_on(stream)
+        cp.copy_(zz.unpartition().storage, non_blocking=True)
+    ems = ctx.timed(estep, 10, warm=2)
+    ctx.launches += 23 + 12
+    e2e_by["f32_512"] = {"value": flops / (ems * 1e-3) / 1e9, "unit": "GFLOP/s", "ms": ems,
+                         "h2d_bytes_per_step": 2 * 512 * 512 * 4, "d2h_bytes_per_step": 512 * 512 * 4}
+    if do_cpu:
+        from oracle import oracle
+        an, bn = a.numpy(), b.numpy()
+        t0 = time.perf_counter()
+        oracle.cpu_gemm(an, bn, threads=1)
+        t1 = time.perf_counter() - t0
+        thr = oracle.max_threads()
+        t0 = time.perf_counter()
+        oracle.cpu_gemm(an, bn, threads=thr)
+        tn = time.perf_counter() - t0
+        cpu_by["f32_512"] = {"value": flops / tn / 1e9, "unit": "GFLOP/s", "cores": thr, "kind": "port",
+                             "sample": f"cpu_gemm port on the whole 512^3 problem: {tn * 1e3:.1f} ms on {thr} threads, "
+                                       f"{t1 * 1e3:.1f} ms single-threaded as written"}
+
+
+def bench_neighbours(ctx):
+    """Compact figures for the other kernels on and around the path (numbers only; shapes in the names)."""
+    import ctypes
+    import torch
+    from cutile_rs_b200 import _lib, launch, sharding, workloads
+    lib, stream, dev, world, rank = ctx.lib, ctx.stream, ctx.dev, ctx.world, ctx.rank
+    hbm = measured_peaks()[1]
+    I2 = ctypes.c_int64 * 2
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 9)
+
+    # split-KV GQA decode attention + merge, K/V heads split over the ranks, K/V sets rotated (inputs > L2)
+    HKV, GRP, SKV, DD = 8, 4, 65536, 128
+    h0, h1 = sharding.split_range(HKV, world, rank, 1)
+    hl = h1 - h0
+    if hl > 0:
+        ns = max(1, lib.b200tile_num_sms() // hl)
+        nbuf = 4
+        qd = torch.randn(hl, GRP, DD, generator=g, device=dev).bfloat16()
+        kds = [torch.randn(hl, SKV, DD, generator=g, device=dev).bfloat16() for _ in range(nbuf)]
+        vds = [torch.randn(hl, SKV, DD, generator=g, device=dev).bfloat16() for _ in range(nbuf)]
+        attp = torch.empty(hl, ns * GRP, DD, dtype=torch.bfloat16, device=dev)
+        lsep = torch.empty(hl, ns * GRP, dtype=torch.float32, device=dev)
+        od = torch.empty_like(qd)
+        posd = torch.tensor([SKV - 1], dtype=torch.int32, device=dev)
+        turn = [0]
+
+        def dstep():
+            i = turn[0] = (turn[0] + 1) % nbuf
+            _lib.check(lib.b200tile_fmha_decode_gqa_split(
+                b"bf16", qd.data_ptr(), kds[i].data_ptr(), vds[i].data_ptr(), attp.data_ptr(), lsep.data_ptr(),
+                od.data_ptr(), posd.data_ptr(), hl, GRP, DD, SKV, 128, ns, 1.0 / math.sqrt(DD), I2(GRP * DD, DD),
+                I2(SKV * DD, DD), I2(SKV * DD, DD), I2(ns * GRP * DD, DD), ns * GRP, I2(GRP * DD, DD),
+                stream.cuda_stream))
+        msd = ctx.timed(dstep, 20)
+        del kds, vds
+    else:
+        ctx.barrier()
+        ctx.barrier()
+        msd = sharding.max_over_ranks(0.0, dev)
+    gbs = 2 * HKV * SKV * DD * 2 / (msd * 1e-3) / 1e9 / world
+    out["decode_attn_8kvh_x4_65536_d128"] = {"gbs_per_gpu": gbs, "us": msd * 1e3, "frac_of_measured_hbm": gbs / hbm}
+    ctx.launches += 23 * 2
+
+    # MoE grouped GEMM: 64 experts x 512 tokens x 4096 x 7168 bf16 (experts split over the ranks)
+    E, GM, GN, GK = 64, 512, 4096, 7168
+    e0_, e1_ = sharding.split_range(E, world, rank, 1)
+    ne = e1_ - e0_
+    ga = torch.randn(ne, GM, GK, device=dev, generator=g).bfloat16() / 8
+    gb = torch.randn(ne, GK, GN, device=dev, generator=g).bfloat16() / 8
+    gc = torch.empty(ne, GM, GN, device=dev, dtype=torch.bfloat16)
+    tabs = launch.group_gemm_tables(list(ga), list(gb), list(gc))
+    need = lib.b200tile_group_gemm_workspace_bytes(ne)
+    gws = torch.empty(need + 128, dtype=torch.uint8, device=dev)
+    gwp = (gws.data_ptr() + 127) // 128 * 128
+
+    def gstep():
+        _lib.check(lib.b200tile_group_gemm(b"bf16", *(t_.cu_deviceptr() for t_ in tabs), ne, 256, gwp, need,
+                                           stream.cuda_stream))
+    msg = ctx.timed(gstep, 5)
+    tfg = 2.0 * E * GM * GN * GK / (msg * 1e-3) / 1e12 / world
+    out["group_gemm_64x512x4096x7168"] = {"tflops_per_gpu": tfg, "ms": msg, "frac_of_nominal_2250": tfg / NOMINAL_BF16}
+    ctx.launches += 8 * 2
+    del ga, gb, gc
+
+    # residual add + RMSNorm, token rows split over the ranks, two tensor sets alternated (inputs > L2)
+    NT, NH = 16384, 8192
+    t0_, t1_ = sharding.split_range(NT, world, rank, 1)
+    nt = t1_ - t0_
+    sets = [(torch.randn(nt, NH, device=dev, generator=g).half(), torch.randn(nt, NH, device=dev, generator=g).half(),
+             torch.empty(nt, NH, device=dev, dtype=torch.float16), torch.empty(nt, NH, device=dev, dtype=torch.float16))
+            for _ in range(2)]
+    wn = torch.ones(NH, device=dev, dtype=torch.float16)
+    flip = [0]
+
+    def nstep():
+        r_, x_, o_, ro_ = sets[flip[0] & 1]
+        flip[0] += 1
+        _lib.check(lib.b200tile_add_rms_norm(b"f16", r_.data_ptr(), x_.data_ptr(), wn.data_ptr(), o_.data_ptr(),
+                                             ro_.data_ptr(), nt, NH, NH, NH, NH, NH, 1e-5, stream.cuda_stream))
+    msn = ctx.timed(nstep, 20)
+    gbn = 4.0 * NT * NH * 2 / (msn * 1e-3) / 1e9 / world
+    out["add_rms_norm_16384x8192"] = {"gbs_per_gpu": gbn, "us": msn * 1e3, "frac_of_measured_hbm": gbn / hbm}
+    ctx.launches += 23
+    del sets
+
+    # rotary embedding and the fused QK-norm + RoPE + KV-cache write, token rows split over the ranks
+    RT, RH, RD = 32768, 32, 128
+    t0_, t1_ = sharding.split_range(RT, world, rank, 1)
+    rt = t1_ - t0_
+    rsets = [(torch.randn(rt, RH, RD, device=dev).half(), torch.empty(rt, RH, RD, device=dev, dtype=torch.float16))
+             for _ in range(2)]
+    inv_f = (1.0 / 10000.0 ** (torch.arange(0, RD, 2, dtype=torch.float32, device=dev) / RD)).contiguous()
+    rst = I2(RH * RD, RD)
+    rflip = [0]
+
+    def rstep():
+        x_, o_ = rsets[rflip[0] & 1]
+        rflip[0] += 1
+        _lib.check(lib.b200tile_rope_seq(b"f16", x_.data_ptr(), inv_f.data_ptr(), o_.data_ptr(), rt, RH, RD, rst, rst,
+                                         t0_, None, stream.cuda_stream))
+    msr = ctx.timed(rstep, 20)
+    gbr = 2.0 * RT * RH * RD * 2 / (msr * 1e-3) / 1e9 / world
+    out["rope_seq_32768x32x128"] = {"gbs_per_gpu": gbr, "us": msr * 1e3, "frac_of_measured_hbm": gbr / hbm}
+    ctx.launches += 23
+    del rsets
+    QT, QH, KVH = 16384, 32, 8
+    t0_, t1_ = sharding.split_range(QT, world, rank, 1)
+    qt = t1_ - t0_
+    qq = torch.randn(qt, QH, RD, device=dev).half()
+    qk_ = torch.randn(qt, KVH, RD, device=dev).half()
+    qv = torch.randn(qt, KVH, RD, device=dev).half()
+    qo_ = torch.empty_like(qq)
+    kc_ = torch.empty(KVH, qt, RD, device=dev, dtype=torch.float16)
+    vc_ = torch.empty(KVH, qt, RD, device=dev, dtype=torch.float16)
+    wq_ = torch.ones(RD, device=dev, dtype=torch.float16)
+
+    def qstep():
+        _lib.check(lib.b200tile_qk_norm_rope_kv(b"f16", qq.data_ptr(), qk_.data_ptr(), qv.data_ptr(), wq_.data_ptr(),
+                                                wq_.data_ptr(), inv_f.data_ptr(), qo_.data_ptr(), kc_.data_ptr(),
+                                                vc_.data_ptr(), 1e-6, 0, None, qt, QH, KVH, RD, qt, QH * RD,
+                                                KVH * RD, KVH * RD, QH * RD, stream.cuda_stream))
+    msq = ctx.timed(qstep, 20)
+    gbq = 2.0 * QT * (QH + 2 * KVH) * RD * 2 / (msq * 1e-3) / 1e9 / world
+    out["qk_norm_rope_kv_16384tok"] = {"gbs_per_gpu": gbq, "us": msq * 1e3, "frac_of_measured_hbm": gbq / hbm}
+    ctx.launches += 23
+    del qq, qk_, qv, qo_, kc_, vc_
+
+    # LM head fused with the block argmax (vocabulary rows split over the ranks)
+    LV, LK = 128256, 4096
+    v0_, v1_ = sharding.split_range(LV, world, rank, 64)
+    lv = v1_ - v0_
+    lw = (torch.randn(lv, LK, device=dev) / 64).half()
+    lh = torch.randn(LK, device=dev).half()
+    lbm = torch.empty((lv + 63) // 64, device=dev, dtype=torch.float32)
+    lbi = torch.empty((lv + 63) // 64, device=dev, dtype=torch.int32)
+    ltok = torch.empty(1, device=dev, dtype=torch.int32)
+
+    def lstep():
+        _lib.check(lib.b200tile_lm_head_argmax_blocks(b"f16", lw.data_ptr(), lh.data_ptr(), lbm.data_ptr(),
+                                                      lbi.data_ptr(), lv, LK, LK, stream.cuda_stream))
+        _lib.check(lib.b200tile_argmax_reduce_blocks(lbm.data_ptr(), lbi.data_ptr(), ltok.data_ptr(),
+                                                     (lv + 63) // 64, stream.cuda_stream))
+    msl = ctx.timed(lstep, 20)
+    gbl = 2.0 * LV * LK / (msl * 1e-3) / 1e9 / world
+    out["lm_head_argmax_128256x4096"] = {"gbs_per_gpu": gbl, "us": msl * 1e3, "frac_of_measured_hbm": gbl / hbm}
+    ctx.launches += 23 * 2
+    del lw
+
+    # SiLU(gate) * up as a kernel of its own
+    ST, SI = 8192, 14336
+    t0_, t1_ = sharding.split_range(ST, world, rank, 1)
+    st_ = t1_ - t0_
+    sg = torch.randn(st_, SI, device=dev).half()
+    su = torch.randn(st_, SI, device=dev).half()
+    so = torch.empty_like(sg)
+
+    def sstep():
+        _lib.check(lib.b200tile_silu_mul_2d(b"f16", so.data_ptr(), sg.data_ptr(), su.data_ptr(), st_, SI, SI, SI, SI,
+                                            stream.cuda_stream))
+    mss = ctx.timed(sstep, 20)
+    gbs_ = 3.0 * ST * SI * 2 / (mss * 1e-3) / 1e9 / world
+    out["silu_mul_8192x14336"] = {"gbs_per_gpu": gbs_, "us": mss * 1e3, "frac_of_measured_hbm": gbs_ / hbm}
+    ctx.launches += 23
+    return out
+
+
+def bench_single_gpu_yardsticks(ctx, step, flops, x, y, n_local):
+    """1-GPU only: the reference's published timing protocol on all-ones f16 operands, and library kernels
+    (cuBLAS through torch.matmul, cuBLASLt fp8 through torch._scaled_mm) as yardsticks on the same box."""
+    import torch
+    from cutile_rs_b200 import _lib
+    lib, stream, dev = ctx.lib, ctx.stream, ctx.dev
+    out = {}
+    ones_a = torch.ones(M, K, dtype=torch.float16, device=dev)
+    ones_b = torch.ones(K, N, dtype=torch.float16, device=dev)
+    ones_c = torch.empty(M, N, dtype=torch.float16, device=dev)
+
+    def ones_step():
+        _lib.check(lib.b200tile_gemm(b"f16", 0, ones_a.data_ptr(), ones_b.data_ptr(), ones_c.data_ptr(), 1, M, N, K, K, N,
+                                     N, 0, 0, 0, 0, 2, 8, 0, stream.cuda_stream))
+    # 5 warm-up launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
+    # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322)
+    for _ in range(5):
+        ones_step()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(10):
+        t0 = time.perf_counter()
+        for _ in range(3):
+            ones_step()
+        torch.cuda.synchronize()
+        samples.append((time.perf_counter() - t0) / 3)
+    samples.sort()
+    med = 0.5 * (samples[4] + samples[5])
+    out["gemm_f16_ones_published_protocol"] = {
+        "tflops": flops / med / 1e12, "median_us": med * 1e6, "published_reference_tflops": 2068.88,
+        "result_is_k_everywhere": bool((ones_c[::997, ::991].float() == float(K)).all().item()),
+        "accumulator": "fp32 here, f16 in the published run"}
+    ctx.launches += 35
+    del ones_a, ones_b, ones_c
+    a_t, b_t, c_t = x.storage, y.storage, torch.empty((M, n_local), dtype=torch.bfloat16, device=dev)
+    for _ in range(3):          # library initialisation and heuristics stay outside the timing
+        torch.matmul(a_t, b_t, out=c_t)
+    torch.cuda.synchronize()
+    ours, theirs = [], []
+    for _ in range(6):
+        for lst, fn in ((ours, step), (theirs, lambda: torch.matmul(a_t, b_t, out=c_t))):
+            ctx.e0.record(stream)
+            for _ in range(16):
+                fn()
+            ctx.e1.record(stream)
+            torch.cuda.synchronize()
+            lst.append(flops / (ctx.e0.elapsed_time(ctx.e1) / 16 * 1e-3) / 1e12)
+    ctx.launches += 96
+    out["gemm_bf16_vs_cublas_interleaved_blocks_of_16"] = {"this_kernel_tflops": sum(ours) / len(ours),
+                                                           "cublas_tflops": sum(theirs) / len(theirs)}
+    try:
+        a8 = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
+        b8 = torch.randn(N, K, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+
+        def lib8():
+            return torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+        for _ in range(3):
+            lib8()
+        torch.cuda.synchronize()
+        ctx.e0.record(stream)
+        for _ in range(16):
+            lib8()
+        ctx.e1.record(stream)
+        torch.cuda.synchronize()
+        out["library_fp8_per_tensor_gemm_8192_yardstick_tflops"] = 2.0 * M * N * K / (ctx.e0.elapsed_time(ctx.e1) / 16 * 1e-3) / 1e12
+    except Exception as exc:  # the private API may differ between torch builds
+        out["library_fp8_per_tensor_gemm_8192_yardstick_tflops"] = f"unavailable: {str(exc)[:80]}"
+    return out
+
+
 def run_gpu_arm(args):
+    import ctypes
     import torch
     import torch.distributed as dist
 
@@ -249,11 +796,9 @@ def run_gpu_arm(args):
     lib = _lib.load()
     _lib.check(lib.b200tile_init(local_rank))
     stream = torch.cuda.current_stream()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    ctx = Ctx(lib, stream, dev, world, rank)
+    barrier = ctx.barrier
+    peak, hbm_peak, peak_src = measured_peaks()
 
     # ---- operands: A replicated, B and C column-sharded; generated once, outside timing ----
     n0, n1 = sharding.split_range(N, world, rank, 256)
@@ -271,7 +816,8 @@ def run_gpu_arm(args):
     def step():
         launch.gemm(z.partition([bm, bn]), x, y).generics(generics).compile_options(opts).async_on(stream)
 
-    for _ in range(max(args.warmup, 3)):
+    warmup = max(args.warmup, 3)
+    for _ in range(warmup):
         step()
     barrier()
     sampler = ClockSampler(local_rank)
@@ -280,483 +826,126 @@ def run_gpu_arm(args):
         time.sleep(0.25)
     barrier()
     t_begin = time.monotonic()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
+    ctx.e0.record(stream)
     for _ in range(args.steps):
         step()
-    e1.record(stream)
+    ctx.e1.record(stream)
     barrier()
     t_end = time.monotonic()
-    total_ms = sharding.max_over_ranks(e0.elapsed_time(e1), dev)
+    total_ms = sharding.max_over_ranks(ctx.e0.elapsed_time(ctx.e1), dev)
     clocks = sampler.stop(t_begin, t_end) if rank == 0 else None
     ms_per_step = total_ms / args.steps
     flops = workloads.gemm_flops(M, N, K)
     value = flops / (ms_per_step * 1e-3) / 1e12
-    _lib.check(lib.b200tile_status(stream.cuda_stream, __import__("ctypes").byref(_lib.StatusC())))
+    ctx.launches += warmup + args.steps
+    _lib.check(lib.b200tile_status(stream.cuda_stream, ctypes.byref(_lib.StatusC())))
+
+    # ---- the same launch repeated for about two seconds: the rate under the power cap (the timed region above
+    # is a burst of a few milliseconds) ----
+    n_sus = int(min(max(2000.0 / ms_per_step, 100), 20000))
+    sampler2 = ClockSampler(local_rank)
+    if rank == 0:
+        sampler2.start()
+    t_s0 = time.monotonic()
+    sus_ms = ctx.timed(step, n_sus, warm=0)
+    t_s1 = time.monotonic()
+    sus_clocks = sampler2.stop(t_s0, t_s1) if rank == 0 else None
+    ctx.launches += n_sus
+    sus_tf = flops / (sus_ms * 1e-3) / 1e12 / world
 
     # ---- end to end through the public API with host buffers ----
-    a_pin, b_pin = api.pin(a_host), api.pin(b_host)
-    c_pin = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
     e2e_steps = max(min(args.steps, 5), 1)
+    if world == 1:
+        a_pin, b_pin = api.pin(a_host), api.pin(b_host)
+        c_pin = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
+        # one call of the public API per step: B up, A up in 1024-row slabs, each slab multiplied on arrival and
+        # its C rows sent back while the next slab is in flight (uploads, MMA and downloads on three streams)
+        host_gemm = api.HostGemm(M, n_local, K, "bf16")
 
-    # one call of the public API per step: B up, A up in 1024-row slabs, each slab multiplied on arrival and
-    # its C rows sent back while the next slab is in flight (uploads, MMA and downloads on three streams)
-    host_gemm = api.HostGemm(M, n_local, K, "bf16")
+        def e2e_step():
+            host_gemm(a_pin, b_pin, c_pin, stream)
+        e2e_api = "api.HostGemm (b200tile_gemm_host): pinned host A, B, C; upload / multiply / download pipelined in 1024-row slabs"
+        e2e_launches = -(-M // 1024)
+    else:
+        # A crosses PCIe once per box: every rank uploads M/G rows and an NCCL all-gather over NVLink completes A
+        # in every rank's HBM; B and C stay column-sharded (no data-path collective in the GEMM itself)
+        rows0, rows1 = rank * (M // world), (rank + 1) * (M // world)
+        a_pin = api.pin(a_host[rows0:rows1].contiguous())
+        b_pin = api.pin(b_host)
+        c_pin = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
+        host_gemm = sharding.ShardedHostGemm(M, n_local, K, "bf16")
 
-    def e2e_step():
-        host_gemm(a_pin, b_pin, c_pin, stream)
-
-    def e2e_serial_step():
-        xa = api.copy_host_to_device(a_pin, stream=stream)
-        yb = api.copy_host_to_device(b_pin, stream=stream)
-        (zz, _, _) = launch.gemm(z.partition([bm, bn]), xa, yb).generics(generics) \
-            .compile_options(opts).async_on(stream)
-        c_pin.copy_(zz.unpartition().storage, non_blocking=True)
-
-    e2e_serial_step()
-    barrier()
-    e0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_serial_step()
-    e1.record(stream)
-    barrier()
-    e2e_serial_ms = sharding.max_over_ranks(e0.elapsed_time(e1), dev) / e2e_steps
-    e2e_step()
-    barrier()
-    e0.record(stream)
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record(stream)
-    barrier()
-    e2e_ms = sharding.max_over_ranks(e0.elapsed_time(e1), dev) / e2e_steps
+        def e2e_step():
+            host_gemm(a_pin, b_pin, c_pin, stream)
+        e2e_api = ("sharding.ShardedHostGemm: each rank uploads M/G rows of A and its B columns from pinned host memory, "
+                   "NCCL all-gather of A over NVLink, b200tile_gemm, download of its C columns")
+        e2e_launches = 1
+    e2e_ms = ctx.timed(e2e_step, e2e_steps, warm=1)
+    ctx.launches += (e2e_steps + 1) * e2e_launches
     e2e_value = flops / (e2e_ms * 1e-3) / 1e12
-    h2d = (a_pin.numel() + b_pin.numel()) * 2 * world
-    d2h = c_pin.numel() * 2 * world
+    h2d = M * K * 2 + K * N * 2
+    d2h = M * N * 2
+    del host_gemm
 
-    # ---- FMHA forward (config 2), sharded by batch x head, reported as `extra` ----
-    extra = {}
+    by = {"gemm_bf16_8192": _roof("tensor", value / world, peak, "TFLOP/s", ms_per_step, f"{peak_src} cuBLAS bf16 burst",
+                                  frac_of_nominal_2250=value / world / NOMINAL_BF16)}
+    cpu_by, e2e_by, extra = {}, {}, {}
+    e2e_by["gemm_bf16_8192"] = {"value": e2e_value, "unit": "TFLOP/s", "ms": e2e_ms, "h2d_bytes_per_step": h2d,
+                                "d2h_bytes_per_step": d2h}
+    do_cpu = world == 1 and rank == 0 and not args.no_cpu_baseline
     if not args.no_fmha:
-        import ctypes
-        B_, H_, S_, D_ = 8, 32, 4096, 128
-        p0, p1 = sharding.split_range(B_ * H_, world, rank, 1)
-        nb = p1 - p0
-        g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 2 + rank)
-        q = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
-        kk = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
-        v = torch.randn(nb, S_, D_, generator=g, device=dev).bfloat16()
-        o = torch.empty_like(q)
-        I2 = ctypes.c_int64 * 2
-        st = I2(S_ * D_, D_)
-        for causal in (False, True):
-            def fstep():
-                _lib.check(lib.b200tile_fmha_fwd(b"bf16", q.data_ptr(), kk.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                                 1, nb, nb, S_, S_, D_, st, st, st, st, 1.0 / math.sqrt(D_),
-                                                 int(causal), 0, stream.cuda_stream))
-            for _ in range(3):
-                fstep()
-            barrier()
-            e0.record(stream)
-            iters = 10
-            for _ in range(iters):
-                fstep()
-            e1.record(stream)
-            barrier()
-            fms = sharding.max_over_ranks(e0.elapsed_time(e1), dev) / iters
-            ftf = workloads.fmha_flops(B_, H_, S_, D_, causal) / (fms * 1e-3) / 1e12
-            extra["fmha_fwd_causal" if causal else "fmha_fwd_noncausal"] = {
-                "tflops": ftf, "tflops_per_gpu": ftf / world, "ms": fms,
-                "config": f"bf16 b{B_} h{H_} s{S_} d{D_}, (b*h) split over {world} GPU(s)"}
-        # the same non-causal shape through the generated-launcher mirror with the CTA-pair configuration
-        # (CompileOptions(num_cta_in_cga=2): persistent pairs, alternating softmax warpgroups)
-        qd, kd, vd = (api.from_torch(t_.view(1, nb, S_, D_)) for t_ in (q, kk, v))
-        od = api.from_torch(o).partition([1, 128, D_])
-        fopts = launch.CompileOptions(num_cta_in_cga=2)
-
-        def pstep():
-            nonlocal od
-            (od, *_r) = launch.fmha(od, qd, kd, vd, 1.0 / math.sqrt(D_), 0, 1, causal=False) \
-                .compile_options(fopts).async_on(stream)
-        for _ in range(3):
-            pstep()
-        barrier()
-        e0.record(stream)
-        for _ in range(10):
-            pstep()
-        e1.record(stream)
-        barrier()
-        fms = sharding.max_over_ranks(e0.elapsed_time(e1), dev) / 10
-        ftf = workloads.fmha_flops(B_, H_, S_, D_, False) / (fms * 1e-3) / 1e12
-        extra["fmha_fwd_noncausal_cta_pairs"] = {
-            "tflops": ftf, "tflops_per_gpu": ftf / world, "ms": fms,
-            "config": "same shape, CompileOptions(num_cta_in_cga=2), through the launcher"}
-        del q, kk, v, o, qd, kd, vd, od
-
-        # ---- block-scaled GEMMs (configs 3 and 4), weight rows (N) split over the ranks ----
-        from cutile_rs_b200 import quant
-
-        def timed(fn, iters=10):
-            for _ in range(3):
-                fn()
-            barrier()
-            e0.record(stream)
-            for _ in range(iters):
-                fn()
-            e1.record(stream)
-            barrier()
-            return sharding.max_over_ranks(e0.elapsed_time(e1), dev) / iters
-
-        g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 3)
-        m8, n8, k8 = 8192, 28672, 8192
-        r0, r1 = sharding.split_range(n8, world, rank, 256)
-        xq, xs = quant.quant_fp8_block(torch.randn(m8, k8, device=dev, generator=g), 1, 128)
-        yq, ys = quant.quant_fp8_block(torch.randn(r1 - r0, k8, device=dev, generator=g), 128, 128)
-        z8 = torch.empty(m8, r1 - r0, dtype=torch.bfloat16, device=dev)
-
-        def f8step():
-            _lib.check(lib.b200tile_linear_fp8_blk128(xq.data_ptr(), yq.data_ptr(), xs.data_ptr(), ys.data_ptr(),
-                                                      z8.data_ptr(), b"bf16", m8, r1 - r0, k8, k8, k8, r1 - r0,
-                                                      k8 // 128, k8 // 128, 1.0, stream.cuda_stream))
-        ms8 = timed(f8step, 5)
-        tf8 = workloads.gemm_flops(m8, n8, k8) / (ms8 * 1e-3) / 1e12
-        extra["gemm_fp8_blk128"] = {"tflops": tf8, "tflops_per_gpu": tf8 / world, "ms": ms8,
-                                    "pct_of_nominal_fp8_peak_4500": 100.0 * tf8 / world / 4500.0,
-                                    "config": f"e4m3 M{m8} N{n8} K{k8}, fp32 scales 1x128 / 128x128, bf16 out, "
-                                              f"N split over {world} GPU(s)"}
-        # the same shape with the hardware's own fp8 block scaling (MXFP8: e8m0 scale per 32 elements), the
-        # reference's fp8 path (cutile-examples/examples/mxfp8.rs:34-64): no promotion pass on CUDA cores
-        xm, xms = quant.quant_mxfp8(torch.randn(m8, k8, device=dev, generator=g))
-        ym, yms = quant.quant_mxfp8(torch.randn(r1 - r0, k8, device=dev, generator=g))
-        wsm = lib.b200tile_linear_mxfp8_workspace_bytes(m8, r1 - r0, k8)
-        wsb8 = torch.empty(wsm, dtype=torch.uint8, device=dev)
-
-        def mx8step():
-            _lib.check(lib.b200tile_linear_mxfp8(xm.data_ptr(), ym.data_ptr(), xms.data_ptr(), yms.data_ptr(),
-                                                 z8.data_ptr(), b"bf16", m8, r1 - r0, k8, k8, k8, r1 - r0, k8 // 32,
-                                                 k8 // 32, 1.0, wsb8.data_ptr(), wsm, stream.cuda_stream))
-        msm = timed(mx8step, 5)
-        tfm = workloads.gemm_flops(m8, n8, k8) / (msm * 1e-3) / 1e12
-        extra["gemm_mxfp8"] = {"tflops": tfm, "tflops_per_gpu": tfm / world, "ms": msm,
-                               "pct_of_nominal_fp8_peak_4500": 100.0 * tfm / world / 4500.0,
-                               "config": f"MXFP8 (e4m3, e8m0 scale per 32) M{m8} N{n8} K{k8}, bf16 out, N split over "
-                                         f"{world} GPU(s); includes the per-call scale re-layout"}
-        del xm, xms, ym, yms, wsb8
-        del xq, xs, yq, ys, z8
-        n4, k4 = 14336, 4096
-        r0, r1 = sharding.split_range(n4, world, rank, 256)
-        yp, ysc, gy = quant.quant_nvfp4(torch.randn(r1 - r0, k4, device=dev, generator=g))
-        for m4 in (4096, 16):
-            xp, xsc, gx = quant.quant_nvfp4(torch.randn(m4, k4, device=dev, generator=g))
-            z4 = torch.empty(m4, r1 - r0, dtype=torch.bfloat16, device=dev)
-            wsb = lib.b200tile_linear_nvfp4_workspace_bytes(m4, r1 - r0, k4)
-            ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
-
-            def f4step():
-                _lib.check(lib.b200tile_linear_nvfp4(xp.data_ptr(), yp.data_ptr(), xsc.data_ptr(), ysc.data_ptr(),
-                                                     z4.data_ptr(), b"bf16", m4, r1 - r0, k4, k4 // 2, k4 // 2,
-                                                     r1 - r0, k4 // 16, k4 // 16, gx * gy, ws.data_ptr(), wsb, -1,
-                                                     stream.cuda_stream))
-            ms4 = timed(f4step, 10)
-            tf4 = workloads.gemm_flops(m4, n4, k4) / (ms4 * 1e-3) / 1e12
-            nbytes = (m4 * k4 // 2 + m4 * k4 // 16 + n4 * k4 // 2 + n4 * k4 // 16 + m4 * n4 * 2)
-            entry = {"tflops": tf4, "tflops_per_gpu": tf4 / world, "ms": ms4,
-                     "pct_of_nominal_fp4_peak_9000": 100.0 * tf4 / world / 9000.0,
-                     "algorithmic_gbs": nbytes / (ms4 * 1e-3) / 1e9,
-                     "config": f"NVFP4 M{m4} N{n4} K{k4}, e4m3 scale per 16, bf16 out, N split over {world} "
-                               "GPU(s); includes the per-call re-layout of the weight scales"}
-            if m4 <= 128:
-                # decode: weight scales laid out once (they are constants of the model), then one kernel per call
-                cfg = 0
-                need = lib.b200tile_nvfp4_weight_scales_bytes(r1 - r0, k4, cfg)
-                prep = torch.empty(need, dtype=torch.uint8, device=dev)
-                _lib.check(lib.b200tile_nvfp4_prepare_weight_scales(ysc.data_ptr(), r1 - r0, k4, k4 // 16, cfg,
-                                                                    prep.data_ptr(), need, stream.cuda_stream))
-
-                def f4prep():
-                    _lib.check(lib.b200tile_linear_nvfp4_prepared(xp.data_ptr(), yp.data_ptr(), xsc.data_ptr(),
-                                                                  prep.data_ptr(), z4.data_ptr(), b"bf16", m4, r1 - r0,
-                                                                  k4, k4 // 2, k4 // 2, r1 - r0, k4 // 16, gx * gy, cfg,
-                                                                  stream.cuda_stream))
-                msp = timed(f4prep, 20)
-                entry["prepared_weight_scales"] = {
-                    "us": msp * 1e3, "algorithmic_gbs": nbytes / (msp * 1e-3) / 1e9,
-                    "frac_of_measured_hbm": nbytes / (msp * 1e-3) / 1e9 / world / measured_peaks()[1]}
-            extra[f"gemm_nvfp4_m{m4}"] = entry
-        del xp, xsc, yp, ysc, z4, ws
-
-        # ---- split-KV GQA decode attention + merge: K/V heads split over the ranks ----
-        HKV, GRP, SKV, DD = 8, 4, 65536, 128
-        h0, h1 = sharding.split_range(HKV, world, rank, 1)
-        hl = h1 - h0
-        if hl > 0:
-            ns = max(1, lib.b200tile_num_sms() // hl)
-            nbuf = 4   # rotate K/V sets (268 MB each at 8 heads) so that no launch finds its keys in L2
-            qd = torch.randn(hl, GRP, DD, generator=g, device=dev).bfloat16()
-            kds = [torch.randn(hl, SKV, DD, generator=g, device=dev).bfloat16() for _ in range(nbuf)]
-            vds = [torch.randn(hl, SKV, DD, generator=g, device=dev).bfloat16() for _ in range(nbuf)]
-            attp = torch.empty(hl, ns * GRP, DD, dtype=torch.bfloat16, device=dev)
-            lsep = torch.empty(hl, ns * GRP, dtype=torch.float32, device=dev)
-            od = torch.empty_like(qd)
-            posd = torch.tensor([SKV - 1], dtype=torch.int32, device=dev)
-            turn = [0]
-
-            def dstep():
-                i = turn[0] = (turn[0] + 1) % nbuf
-                _lib.check(lib.b200tile_fmha_decode_gqa_split(
-                    b"bf16", qd.data_ptr(), kds[i].data_ptr(), vds[i].data_ptr(), attp.data_ptr(), lsep.data_ptr(),
-                    od.data_ptr(), posd.data_ptr(), hl, GRP, DD, SKV, 128, ns, 1.0 / math.sqrt(DD), I2(GRP * DD, DD),
-                    I2(SKV * DD, DD), I2(SKV * DD, DD), I2(ns * GRP * DD, DD), ns * GRP, I2(GRP * DD, DD),
-                    stream.cuda_stream))
-            msd = timed(dstep, 20)
+        extra.update(bench_fmha(ctx, by, cpu_by, e2e_by, do_cpu))
+        extra.update(bench_fp8(ctx, by, cpu_by, e2e_by, do_cpu))
+        extra.update(bench_nvfp4(ctx, by, cpu_by, e2e_by, do_cpu) or {})
+        bench_f32(ctx, by, cpu_by, e2e_by, do_cpu)
+        extra.update(bench_neighbours(ctx))
+        if world == 1:
+            extra.update(bench_single_gpu_yardsticks(ctx, step, flops, x, y, n_local))
         else:
-            barrier(); barrier()
-            msd = sharding.max_over_ranks(0.0, dev)
-        kv_bytes = 2 * HKV * SKV * DD * 2
-        gbs = kv_bytes / (msd * 1e-3) / 1e9
-        extra["fmha_decode_gqa_split_merge"] = {
-            "gbs": gbs, "gbs_per_gpu": gbs / world, "us": msd * 1e3,
-            "frac_of_measured_hbm": gbs / world / measured_peaks()[1],
-            "config": f"bf16 kv_heads {HKV} group {GRP} D {DD} s_kv {SKV}, BN 128, splits = SMs / local heads, "
-                      f"split pass + merge per step, kv heads split over {world} GPU(s), K/V sets rotated (inputs > L2)"}
+            # the replicated-result option: NCCL all-gather of the C column shards (+ the local re-layout) and of
+            # the attention output slabs, timed by themselves
+            c_loc = z.storage
+            ag_ms = ctx.timed(lambda: sharding.all_gather_columns(c_loc), 5)
+            o_loc = torch.empty((256 // world, 4096, 128), dtype=torch.bfloat16, device=dev)
+            ao_ms = ctx.timed(lambda: sharding.all_gather_problems(o_loc), 5)
+            extra["all_gather_replicated_result"] = {
+                "gemm_c_columns_ms": ag_ms, "gemm_c_bytes_per_rank": c_loc.numel() * 2,
+                "gemm_step_plus_gather_ms": ms_per_step + ag_ms,
+                "fmha_o_problems_ms": ao_ms, "fmha_o_bytes_per_rank": o_loc.numel() * 2}
+    _lib.check(lib.b200tile_status(stream.cuda_stream, ctypes.byref(_lib.StatusC())))
 
-        # ---- residual add + RMSNorm (HBM-bound neighbour of the linear layers), token rows split over the ranks;
-        # two sets of tensors are alternated so that nothing is served from L2 (2 x 1.07 GB at one GPU)
-        NT, NH = 16384, 8192
-        t0_, t1_ = sharding.split_range(NT, world, rank, 1)
-        nt = t1_ - t0_
-        sets = []
-        for i_ in range(2):
-            g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 11 + i_)
-            sets.append((torch.randn(nt, NH, device=dev, generator=g).half(),
-                         torch.randn(nt, NH, device=dev, generator=g).half(),
-                         torch.empty(nt, NH, device=dev, dtype=torch.float16),
-                         torch.empty(nt, NH, device=dev, dtype=torch.float16)))
-        wn = torch.ones(NH, device=dev, dtype=torch.float16)
-        flip = [0]
-
-        def nstep():
-            r_, x_, o_, ro_ = sets[flip[0] & 1]
-            flip[0] += 1
-            _lib.check(lib.b200tile_add_rms_norm(b"f16", r_.data_ptr(), x_.data_ptr(), wn.data_ptr(), o_.data_ptr(),
-                                                 ro_.data_ptr(), nt, NH, NH, NH, NH, NH, 1e-5, stream.cuda_stream))
-        msn = timed(nstep, 20)
-        nbytes = 4.0 * NT * NH * 2
-        gbn = nbytes / (msn * 1e-3) / 1e9
-        extra["add_rms_norm_f16"] = {
-            "gbs": gbn, "gbs_per_gpu": gbn / world, "us": msn * 1e3,
-            "frac_of_measured_hbm": gbn / world / measured_peaks()[1],
-            "config": f"f16 {NT} tokens x {NH}, read residual + x, write out + residual_out (algorithmic bytes), "
-                      f"token rows split over {world} GPU(s), two tensor sets alternated (inputs > L2)"}
-        del sets
-
-        # ---- rotary position embedding over [tokens, heads, D]; token rows split over the ranks, two sets alternated
-        RT, RH, RD = 32768, 32, 128
-        t0_, t1_ = sharding.split_range(RT, world, rank, 1)
-        rt = t1_ - t0_
-        rsets = [(torch.randn(rt, RH, RD, device=dev).half(), torch.empty(rt, RH, RD, device=dev, dtype=torch.float16))
-                 for _ in range(2)]
-        inv_f = (1.0 / 10000.0 ** (torch.arange(0, RD, 2, dtype=torch.float32, device=dev) / RD)).contiguous()
-        I2r = ctypes.c_int64 * 2
-        rst = I2r(RH * RD, RD)
-        rflip = [0]
-
-        def rstep():
-            x_, o_ = rsets[rflip[0] & 1]
-            rflip[0] += 1
-            _lib.check(lib.b200tile_rope_seq(b"f16", x_.data_ptr(), inv_f.data_ptr(), o_.data_ptr(), rt, RH, RD, rst, rst,
-                                             t0_, None, stream.cuda_stream))
-        msr = timed(rstep, 20)
-        gbr = 2.0 * RT * RH * RD * 2 / (msr * 1e-3) / 1e9
-        extra["rope_seq_f16"] = {
-            "gbs": gbr, "gbs_per_gpu": gbr / world, "us": msr * 1e3,
-            "frac_of_measured_hbm": gbr / world / measured_peaks()[1],
-            "config": f"f16 {RT} tokens x {RH} heads x {RD}, one read + one write per element, token rows split over "
-                      f"{world} GPU(s), two tensor sets alternated (inputs > L2)"}
-        del rsets
-
-        # ---- QK norm + rotary embedding + KV-cache write in one pass (prefill block of 16384 tokens, 32 + 8 heads);
-        # token rows split over the ranks; 403 MB of reads and writes per launch at one GPU (> L2)
-        QT, QH, KVH = 16384, 32, 8
-        t0_, t1_ = sharding.split_range(QT, world, rank, 1)
-        qt = t1_ - t0_
-        qq = torch.randn(qt, QH, RD, device=dev).half()
-        qk_ = torch.randn(qt, KVH, RD, device=dev).half()
-        qv = torch.randn(qt, KVH, RD, device=dev).half()
-        qo_ = torch.empty_like(qq)
-        kc_ = torch.empty(KVH, qt, RD, device=dev, dtype=torch.float16)
-        vc_ = torch.empty(KVH, qt, RD, device=dev, dtype=torch.float16)
-        wq_ = torch.ones(RD, device=dev, dtype=torch.float16)
-
-        def qstep():
-            _lib.check(lib.b200tile_qk_norm_rope_kv(b"f16", qq.data_ptr(), qk_.data_ptr(), qv.data_ptr(), wq_.data_ptr(),
-                                                    wq_.data_ptr(), inv_f.data_ptr(), qo_.data_ptr(), kc_.data_ptr(),
-                                                    vc_.data_ptr(), 1e-6, 0, None, qt, QH, KVH, RD, qt, QH * RD,
-                                                    KVH * RD, KVH * RD, QH * RD, stream.cuda_stream))
-        msq = timed(qstep, 20)
-        gbq = 2.0 * QT * (QH + 2 * KVH) * RD * 2 / (msq * 1e-3) / 1e9
-        extra["qk_norm_rope_kv_prefill"] = {
-            "gbs": gbq, "gbs_per_gpu": gbq / world, "us": msq * 1e3,
-            "frac_of_measured_hbm": gbq / world / measured_peaks()[1],
-            "config": f"f16 {QT} tokens, {QH} q heads + {KVH} kv heads x {RD}: read q, k, v; write q_out, k_cache, v_cache; "
-                      f"token rows split over {world} GPU(s)"}
-        del qq, qk_, qv, qo_, kc_, vc_
-
-        # ---- LM head fused with the block argmax (decode: one hidden vector against the vocabulary matrix), the
-        # vocabulary rows split over the ranks; 1.05 GB of weights at one GPU (> L2), read once
-        LV, LK = 128256, 4096
-        v0_, v1_ = sharding.split_range(LV, world, rank, 64)
-        lv = v1_ - v0_
-        lw = (torch.randn(lv, LK, device=dev) / 64).half()
-        lh = torch.randn(LK, device=dev).half()
-        lbm = torch.empty((lv + 63) // 64, device=dev, dtype=torch.float32)
-        lbi = torch.empty((lv + 63) // 64, device=dev, dtype=torch.int32)
-        ltok = torch.empty(1, device=dev, dtype=torch.int32)
-
-        def lstep():
-            _lib.check(lib.b200tile_lm_head_argmax_blocks(b"f16", lw.data_ptr(), lh.data_ptr(), lbm.data_ptr(),
-                                                          lbi.data_ptr(), lv, LK, LK, stream.cuda_stream))
-            _lib.check(lib.b200tile_argmax_reduce_blocks(lbm.data_ptr(), lbi.data_ptr(), ltok.data_ptr(),
-                                                         (lv + 63) // 64, stream.cuda_stream))
-        msl = timed(lstep, 20)
-        gbl = 2.0 * LV * LK / (msl * 1e-3) / 1e9
-        extra["lm_head_argmax_f16"] = {
-            "gbs": gbl, "gbs_per_gpu": gbl / world, "us": msl * 1e3,
-            "frac_of_measured_hbm": gbl / world / measured_peaks()[1],
-            "config": f"f16 vocabulary {LV} x hidden {LK}: fused matrix-vector product + block argmax, then the reduction "
-                      f"over blocks (two launches per step); vocabulary rows split over {world} GPU(s)"}
-        del lw
-
-        # ---- SiLU(gate) * up as a kernel of its own (the unfused SwiGLU step), token rows split over the ranks;
-        # 3 x 235 MB per launch at one GPU (> L2)
-        ST, SI = 8192, 14336
-        t0_, t1_ = sharding.split_range(ST, world, rank, 1)
-        st_ = t1_ - t0_
-        sg = torch.randn(st_, SI, device=dev).half()
-        su = torch.randn(st_, SI, device=dev).half()
-        so = torch.empty_like(sg)
-
-        def sstep():
-            _lib.check(lib.b200tile_silu_mul_2d(b"f16", so.data_ptr(), sg.data_ptr(), su.data_ptr(), st_, SI, SI, SI, SI,
-                                                stream.cuda_stream))
-        mss = timed(sstep, 20)
-        gbs_ = 3.0 * ST * SI * 2 / (mss * 1e-3) / 1e9
-        extra["silu_mul_2d_f16"] = {
-            "gbs": gbs_, "gbs_per_gpu": gbs_ / world, "us": mss * 1e3,
-            "frac_of_measured_hbm": gbs_ / world / measured_peaks()[1],
-            "config": f"f16 {ST} x {SI}: two reads and one write per element, token rows split over {world} GPU(s)"}
-        del sg, su, so
-
-        # ---- the reference's published protocol, as far as this library goes: f16 all-ones operands, 5 warm-up
-        # launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
-        # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322).
-        # The accumulator here stays fp32 (the reference's run used f16 accumulation).
-        if world == 1:
-            ones_a = torch.ones(M, K, dtype=torch.float16, device=dev)
-            ones_b = torch.ones(K, N, dtype=torch.float16, device=dev)
-            ones_c = torch.empty(M, N, dtype=torch.float16, device=dev)
-
-            def ones_step():
-                _lib.check(lib.b200tile_gemm(b"f16", 0, ones_a.data_ptr(), ones_b.data_ptr(), ones_c.data_ptr(), 1, M,
-                                             N, K, K, N, N, 0, 0, 0, 0, 2, 8, 0, stream.cuda_stream))
-            for _ in range(5):
-                ones_step()
-            torch.cuda.synchronize()
-            samples = []
-            for _ in range(10):
-                t0 = time.perf_counter()
-                for _ in range(3):
-                    ones_step()
-                torch.cuda.synchronize()
-                samples.append((time.perf_counter() - t0) / 3)
-            samples.sort()
-            med = 0.5 * (samples[4] + samples[5])
-            ok_ones = bool((ones_c[::997, ::991].float() == float(K)).all().item())
-            extra["gemm_f16_ones_published_protocol"] = {
-                "tflops": flops / med / 1e12, "median_us": med * 1e6, "result_is_k_everywhere": ok_ones,
-                "published_reference_tflops": 2068.88,
-                "config": "f16 all-ones 8192^3, tile 256x256x64 on CTA pairs, grouped-M 8; fp32 accumulation here, "
-                          "f16 accumulation in the published run (other GPU, CUDA 13.2, locked 1830 MHz target)"}
-            del ones_a, ones_b, ones_c
-
-        # ---- this kernel and cuBLAS (torch.matmul, a library call used only as a yardstick) in alternating
-        # blocks of 16 launches on the same operands: under a sustained load both sit on the 1 kW cap, so a
-        # back-to-back comparison in one thermal state says more than two separate bursts
-        if world == 1:
-            a_t, b_t, c_t = x.storage, y.storage, torch.empty((M, n_local), dtype=torch.bfloat16, device=dev)
-            for _ in range(3):          # library initialisation and heuristics stay outside the timing
-                torch.matmul(a_t, b_t, out=c_t)
-            torch.cuda.synchronize()
-            ours, theirs = [], []
-            for _ in range(6):
-                for lst, fn in ((ours, step), (theirs, lambda: torch.matmul(a_t, b_t, out=c_t))):
-                    e0.record(stream)
-                    for _ in range(16):
-                        fn()
-                    e1.record(stream)
-                    torch.cuda.synchronize()
-                    lst.append(flops / (e0.elapsed_time(e1) / 16 * 1e-3) / 1e12)
-            extra["gemm_bf16_vs_cublas_interleaved"] = {
-                "this_kernel_tflops": sum(ours) / len(ours), "cublas_tflops": sum(theirs) / len(theirs),
-                "this_kernel_blocks": ours, "cublas_blocks": theirs,
-                "config": "8192^3 bf16, 6 alternating blocks of 16 launches each, CUDA events per block"}
-
-            # ---- the library's fp8 GEMM (cuBLASLt through torch._scaled_mm, one scale per tensor) as a
-            # yardstick for the block-scaled kernels above: it does less (no block scales) on the same
-            # power-capped part
-            try:
-                a8 = torch.randn(M, K, device=dev).to(torch.float8_e4m3fn)
-                b8 = torch.randn(N, K, device=dev).to(torch.float8_e4m3fn).t()
-                one = torch.ones((), device=dev)
-
-                def lib8():
-                    return torch._scaled_mm(a8, b8, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
-                for _ in range(3):
-                    lib8()
-                torch.cuda.synchronize()
-                e0.record(stream)
-                for _ in range(16):
-                    lib8()
-                e1.record(stream)
-                torch.cuda.synchronize()
-                extra["library_fp8_gemm_yardstick"] = {
-                    "tflops": 2.0 * M * N * K / (e0.elapsed_time(e1) / 16 * 1e-3) / 1e12,
-                    "config": "8192^3 e4m3 x e4m3 -> bf16, per-tensor scales, torch._scaled_mm, 16 launches"}
-                del a8, b8
-            except Exception as exc:  # the private API may differ between torch builds
-                extra["library_fp8_gemm_yardstick"] = {"unavailable": str(exc)[:200]}
-
-    peak, hbm_peak, peak_src = measured_peaks()
     if rank == 0:
         cpu = None
-        if world == 1 and not args.no_cpu_baseline:
+        if do_cpu:
             r = cpu_gemm_rate(12.0, 0)
             cpu = {"value": r["tflops"], "unit": "TFLOP/s", "cores": r["threads"], "kind": "port",
                    "sample": f"rows [0,{r['rows']}) of the same 8192^3 GEMM ({r['seconds']:.1f} s), "
-                             "oracle port of the reference's cpu_gemm"}
+                             "oracle port of the reference's cpu_gemm",
+                   "by_config": cpu_by}
         per_gpu = value / world
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "gemm_bf16_8192x8192x8192", "layout": "A[M,K] B[K,N] row-major, fp32 acc",
-                       "tile": f"{bm}x{bn}x64 per CTA pair (cta_group::2), 6-stage TMA ring, persistent, grouped-M 8",
+                       "tile": f"{bm}x{bn} per CTA pair (cta_group::2), 3 stages of 128-deep k slabs (TMA ring), persistent, grouped-M 8",
                        "parallelism": f"N-split x{world}" if world > 1 else "single GPU",
                        "l2": "operands 403 MB per step exceed the 126 MB L2; no flush between steps"},
             "per_gpu_tflops": per_gpu,
-            "pct_of_nominal_peak_2250": 100.0 * per_gpu / 2250.0,
+            "pct_of_nominal_peak_2250": 100.0 * per_gpu / NOMINAL_BF16,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
                          "frac": per_gpu / peak, "traffic": GEMM_DRAM_TRAFFIC_BYTES,
                          "peak_source": f"{peak_src} cuBLAS bf16 burst",
-                         "peak_sustained": SUSTAINED_BF16_TFLOPS,
-                         "frac_of_sustained": (per_gpu / SUSTAINED_BF16_TFLOPS) if SUSTAINED_BF16_TFLOPS else None,
-                         "note": "the MMA-issuing thread measures 1048 cycles per 1024 tensor-pipe cycles of work "
-                                 "(cycle accounting of the diagnostic trace build); the SM clock under the 1 kW cap sets the rest"},
+                         "sustained": {"achieved": sus_tf, "launches": n_sus, "seconds": sus_ms * n_sus * 1e-3,
+                                       "peak_sustained": SUSTAINED_BF16_TFLOPS,
+                                       "frac_of_sustained": (sus_tf / SUSTAINED_BF16_TFLOPS) if SUSTAINED_BF16_TFLOPS else None,
+                                       "sm_mhz": (sus_clocks or {}).get("sm_mhz"), "reasons": (sus_clocks or {}).get("reasons")},
+                         "by_config": by},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "api": "api.HostGemm (b200tile_gemm_host): pinned host A, B, C; pipelined in 1024-row slabs",
-                    "serial_copy_launch_copy_ms": e2e_serial_ms,
-                    "gpu_launches_per_step": -(-M // 1024)},
-            "gpu_launches": args.steps * world,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "api": e2e_api,
+                    "gpu_launches_per_step": e2e_launches * world, "by_config": e2e_by},
+            "gpu_launches": ctx.launches * world,
             "clocks": clocks,
             "extra": extra,
         }

@@ -75,6 +75,71 @@ def all_gather_problems(o_local: torch.Tensor, group: Optional[dist.ProcessGroup
     return out
 
 
+def all_gather_rows(a_full: torch.Tensor, rank_rows: torch.Tensor, group: Optional[dist.ProcessGroup] = None
+                    ) -> torch.Tensor:
+    """Completes ``a_full[M, K]`` on every rank from equal row slabs (rank r holds rows ``[r M/G, (r+1) M/G)``).
+    Row slabs of a row-major matrix are contiguous, so the gather writes ``a_full`` directly; ``rank_rows`` may be
+    the rank's own slab of ``a_full`` (gather in place)."""
+    world = dist.get_world_size(group)
+    if world == 1:
+        if rank_rows.data_ptr() != a_full.data_ptr():
+            a_full.copy_(rank_rows)
+        return a_full
+    if a_full.shape[0] != world * rank_rows.shape[0] or not a_full.is_contiguous():
+        raise ValueError("all_gather_rows: a_full must be contiguous with world x the rank's rows")
+    dist.all_gather_into_tensor(a_full, rank_rows, group=group)
+    return a_full
+
+
+class ShardedHostGemm:
+    """C[:, n0:n1] = A . B[:, n0:n1] for operands that live in HOST memory, on the ranks of one box.
+
+    The activation matrix A is needed whole by every rank, but it crosses PCIe only once: rank r uploads rows
+    ``[r M/G, (r+1) M/G)`` from its pinned host slab and an NCCL all-gather over NVLink completes A in every
+    rank's HBM while the rank's weight columns (B shard) are still arriving on a second stream.  The GEMM
+    (`b200tile_gemm`, weight-column split: no data-path collective) and the download of the rank's C columns
+    follow on the caller's stream."""
+
+    def __init__(self, m: int, n_local: int, k: int, dtype: str = "bf16", group: Optional[dist.ProcessGroup] = None):
+        from . import _lib
+        from .tensor import _NAME_TO_TORCH
+        self._lib = _lib.load()
+        self._check = _lib.check
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if m % self.world:
+            raise ValueError("ShardedHostGemm: M must be a multiple of the number of ranks")
+        self.m, self.n, self.k, self.dtype = m, n_local, k, dtype
+        td = _NAME_TO_TORCH[dtype]
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.a_dev = torch.empty((m, k), dtype=td, device=dev)
+        self.b_dev = torch.empty((k, n_local), dtype=td, device=dev)
+        self.c_dev = torch.empty((m, n_local), dtype=td, device=dev)
+        self.rows = (self.rank * (m // self.world), (self.rank + 1) * (m // self.world))
+        self.b_stream = torch.cuda.Stream()
+
+    def __call__(self, a_rows_host: torch.Tensor, b_host: torch.Tensor, c_host: torch.Tensor,
+                 stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
+        """``a_rows_host``: this rank's M/G rows of A (pinned); ``b_host``: its [K, N/G] weight columns (pinned);
+        ``c_host`` [M, N/G] is complete once ``stream`` has been synchronised."""
+        s = stream or torch.cuda.current_stream()
+        r0, r1 = self.rows
+        self.b_stream.wait_stream(s)                       # earlier work on s may still read b_dev
+        with torch.cuda.stream(self.b_stream):
+            self.b_dev.copy_(b_host, non_blocking=True)
+        with torch.cuda.stream(s):
+            mine = self.a_dev[r0:r1]
+            mine.copy_(a_rows_host, non_blocking=True)
+            all_gather_rows(self.a_dev, mine, self.group)
+            s.wait_stream(self.b_stream)
+            self._check(self._lib.b200tile_gemm(self.dtype.encode(), 0, self.a_dev.data_ptr(), self.b_dev.data_ptr(),
+                                                self.c_dev.data_ptr(), 1, self.m, self.n, self.k, self.k, self.n, self.n,
+                                                0, 0, 0, 0, -1, 0, 0, s.cuda_stream))
+            c_host.copy_(self.c_dev, non_blocking=True)
+        return c_host
+
+
 def max_over_ranks(ms: float, device: torch.device, group: Optional[dist.ProcessGroup] = None
                    ) -> float:
     """Device-timed duration reduced with MAX over ranks (the job time of a sharded step)."""

@@ -98,7 +98,7 @@ def test_properties(b200):
 
 @pytest.mark.parametrize("causal", [False, True])
 def test_full_size_slab(b200, oracle, causal):
-    # BASELINE config 2 at full size (8 x 32 x 4096 x 128); the oracle checks slabs
+    # the benchmark's attention workload at full size (8 x 32 x 4096 x 128); the oracle checks slabs
     b, h, s, d = 8, 32, 4096, 128
     q, k, v = workloads.fmha_inputs(b, h, s, d)
     o = _fmha(b200, q.cuda(), k.cuda(), v.cuda(), causal).float().cpu().numpy()

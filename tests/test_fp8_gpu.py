@@ -55,7 +55,7 @@ def test_known_answer_and_errors(b200):
 
 
 def test_full_size_slab_and_launcher(b200, oracle):
-    # BASELINE config 3 at full size: M=8192, N=28672, K=8192 (device-side generation, oracle slab)
+    # the benchmark's fp8 workload at full size: M=8192, N=28672, K=8192 (device-side generation, oracle slab)
     m, n, k = 8192, 28672, 8192
     g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 3)
     a = torch.randn(m, k, device="cuda", generator=g)

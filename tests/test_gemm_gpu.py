@@ -36,7 +36,7 @@ def _gemm(lib, dtype, a, b, layout=0, config=-1, accumulate=0, c=None, num_progr
 
 
 def test_f32_config0_is_bit_identical_to_oracle(b200, oracle):
-    # BASELINE config 0: f32 512^3, U[-1,1]
+    # the reference's CPU-runnable GEMM: f32 512^3, U[-1,1]
     a, b = workloads.gemm_f32_inputs(512, 512, 512)
     got = _gemm(b200, "f32", a.cuda(), b.cuda()).cpu().numpy()
     ref = oracle.cpu_gemm(a.numpy(), b.numpy(), threads=0)
@@ -117,7 +117,7 @@ def test_f16_and_known_answer(b200, oracle):
 
 
 def test_bf16_full_size_slab_and_properties(b200, oracle):
-    # BASELINE config 1 at full size: 8192^3; the oracle checks a 16-row slab, properties the rest
+    # the headline bf16 workload at full size: 8192^3; the oracle checks a 16-row slab, properties the rest
     m = n = k = 8192
     a, b = workloads.gemm_bf16_inputs(m, n, k)
     ad, bd = a.cuda(), b.cuda()

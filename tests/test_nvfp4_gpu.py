@@ -62,7 +62,7 @@ def test_scale_placement(b200, oracle):
 
 
 def test_full_size_slabs_and_errors(b200, oracle):
-    # BASELINE config 4: M=4096 (and the decode shape M=16), N=14336, K=4096
+    # the benchmark's NVFP4 workload: M=4096 (and the decode shape M=16), N=14336, K=4096
     n, k = 14336, 4096
     g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 4)
     b = torch.randn(n, k, device="cuda", generator=g)

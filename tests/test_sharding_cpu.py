@@ -44,8 +44,14 @@ def _worker(rank, world, port, q):
         o = torch.arange(6 * 4 * 2, dtype=torch.float32).reshape(6, 4, 2)
         o_r = sharding.shard_problems(o, world, rank) * 1.0
         ok3 = torch.equal(sharding.all_gather_problems(o_r), o)
+        # row slabs gathered in place into the full activation matrix (the upload path of ShardedHostGemm)
+        a_full = torch.full((32, 24), float("nan"))
+        r0, r1 = rank * 16, (rank + 1) * 16
+        a_full[r0:r1] = a[r0:r1]
+        sharding.all_gather_rows(a_full, a_full[r0:r1])
+        ok4 = torch.equal(a_full, a)
         t = sharding.max_over_ranks(1.0 + rank, torch.device("cpu"))
-        q.put((rank, bool(ok1 and ok2 and ok3), t))
+        q.put((rank, bool(ok1 and ok2 and ok3 and ok4), t))
     finally:
         dist.destroy_process_group()
 
