@@ -22,8 +22,9 @@
 // [m_g, n_g].  Every address the kernel touches is therefore ptr_g + (row < rows_g) * pitch_g +
 // (col < cols_g).
 //
-//   warps 0..3  producers: cp.async ring, completion handed to the MMA thread through the `full`
-//               barrier after cp.async.wait_group + fence.proxy.async (generic -> async proxy)
+//   warps 0..3  producers: cp.async ring; every thread lets the hardware arrive on the stage's `full`
+//               barrier when its copies have landed (cp.async.mbarrier.arrive.noinc), the MMA thread
+//               crosses from the generic to the async proxy with fence.proxy.async after its wait
 //   warp 4      MMA issuer: tcgen05.mma kind::f16 into two TMEM accumulator buffers
 //   warps 5..8  epilogue
 #include <atomic>
@@ -38,7 +39,6 @@ constexpr int GG_BK = 64;
 constexpr int GG_PRODUCERS = 128;
 constexpr int GG_THREADS = GG_PRODUCERS + 32 + 128;
 constexpr int GG_PREP_THREADS = 256;
-constexpr int GG_LAG = 2;   // a producer thread hands a stage over after issuing this many later ones
 
 enum : uint32_t { ST_BAD_GROUP = 3 };   // status code: a group's pointer or pitch breaks the 16-byte rule
 
@@ -141,7 +141,6 @@ struct GroupedSmem {
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
-  static_assert(GG_LAG < STAGES, "a stage must be handed over before the ring wraps onto it");
 };
 
 // 16-byte asynchronous copy global -> shared; bytes past `src_bytes` (0..16) are written as zeros and
@@ -149,11 +148,12 @@ struct GroupedSmem {
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+// Makes the mbarrier track the completion of all cp.async copies this thread has issued so far: one arrival
+// (counted in the barrier's expected arrivals, hence .noinc) is performed when they have completed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // B is [k, n] row-major (the N-major UMMA operand), as in the reference kernel's `b.partition([BK, BN])`.
 template <int BN, bool OUT_F16>
@@ -211,7 +211,7 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
     const uint16_t* pa = nullptr;
     const uint16_t* pb = nullptr;
     int64_t lda = 0, ldb = 0;
-    uint32_t issued = 0, arrived = 0;   // stages issued / handed over by this thread
+    uint32_t issued = 0;   // stages issued by this thread
     bool ok = true, first = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       if (cur.seek(tile) || first) {
@@ -267,23 +267,14 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
             }
           }
         }
-        cp_async_commit();
+        // hardware arrives on the stage's barrier once this thread's copies above have landed; the thread
+        // itself moves on to the next free slot (every slot of the ring can be in flight)
+        cp_async_arrive_noinc(bar_full + stage * 8);
         ++issued;
-        if (issued - arrived > (uint32_t)GG_LAG) {
-          cp_async_wait<GG_LAG>();
-          fence_proxy_async_smem();
-          mbar_arrive(bar_full + (arrived % STAGES) * 8);
-          ++arrived;
-        }
       }
     }
-    // hand over what is still in flight (also after a wait that gave up: nothing may stay in flight)
-    cp_async_wait<0>();
-    fence_proxy_async_smem();
-    while (arrived < issued) {
-      mbar_arrive(bar_full + (arrived % STAGES) * 8);
-      ++arrived;
-    }
+    // nothing of this thread may still be in flight when the CTA leaves (also after a wait that gave up)
+    cp_async_wait_all();
   } else if (warp == 4) {
     // ------------------------------- MMA issuer --------------------------------
     if (lane == 0) {
@@ -299,6 +290,8 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
+          // the operands were written by cp.async (generic proxy) and are read by the tensor core (async proxy)
+          fence_proxy_async_smem();
           tc_fence_after_sync();
           const uint64_t adesc = make_smem_desc(sA + stage * L::A_BYTES, 16, 1024, SWZ_128B);
           const uint64_t bdesc = make_smem_desc(sB + stage * L::B_BYTES, GG_BK * 128, 1024, SWZ_128B);
