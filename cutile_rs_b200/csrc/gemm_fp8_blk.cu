@@ -19,7 +19,10 @@ namespace b200 {
 constexpr int F8_BM = 128, F8_BN = 256, F8_BK = 128;
 constexpr int F8_THREADS = 384;
 constexpr int F8_STAGES = 4;
-constexpr int F8_PROMO_REGS = 216, F8_OTHER_REGS = 40;  // 128 x 40 + 256 x 216 = 60416
+// Register re-balancing (setmaxnreg).  The pool a CTA can re-balance is what it was GIVEN AT LAUNCH (threads x
+// the kernel's register count, 384 x 168 here), not the SM's 64 K registers: an increase that does not fit
+// into what the decrease released waits forever.
+constexpr int F8_PROMO_REGS = 216, F8_OTHER_REGS = 40;  // 128 x 40 + 256 x 216 = 60416 <= 384 x 168 = 64512
 
 struct Fp8Smem {
   static constexpr int A_BYTES = F8_BM * F8_BK;  // 16 KiB

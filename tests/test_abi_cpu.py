@@ -60,3 +60,21 @@ def test_query_configs_lists_the_fixed_table():
     assert (arr[0].num_cta_in_cga, arr[1].num_cta_in_cga) == (1, 2)
     assert lib.b200tile_query_configs(b"gemm", b"i4", arr, 8) == 0
     assert lib.b200tile_query_configs(b"unknown", b"bf16", arr, 8) == 0
+
+
+def test_rust_sys_crate_declares_every_header_symbol():
+    """rust/b200tile-sys/src/lib.rs is generated from the header: it must be up to date and name every export."""
+    import subprocess
+    import sys
+    gen = os.path.join(ROOT, "rust", "b200tile-sys", "gen_ffi.py")
+    assert subprocess.call([sys.executable, gen, "--check"]) == 0, "run rust/b200tile-sys/gen_ffi.py"
+    rs = open(os.path.join(ROOT, "rust", "b200tile-sys", "src", "lib.rs")).read()
+    assert sorted(set(re.findall(r"pub fn (b200tile_\w+)\(", rs))) == declared_symbols()
+    assert lib_query_linear_tile() == (3, 1)
+
+
+def lib_query_linear_tile():
+    lib = _lib.load()
+    arr = (_lib.ConfigC * 8)()
+    return (lib.b200tile_query_configs(b"linear_tile", b"f4e2m1fnx2", arr, 8),
+            lib.b200tile_query_configs(b"linear_tile", b"f8e4m3fn", arr, 8))
