@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Regenerates the `extern "C"` block of src/lib.rs from include/b200tile.h.
+"""Regenerates the `extern "C"` block of src/lib.rs (and its copy in INTEGRATION.md) from include/b200tile.h.
 
     python rust/b200tile-sys/gen_ffi.py            # rewrites src/lib.rs in place
     python rust/b200tile-sys/gen_ffi.py --check    # exit 1 when src/lib.rs is out of date (used by the tests)
@@ -11,6 +11,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 HEADER = os.path.join(HERE, "..", "..", "include", "b200tile.h")
 LIB_RS = os.path.join(HERE, "src", "lib.rs")
+INTEGRATION = os.path.join(HERE, "..", "..", "INTEGRATION.md")   # carries a copy of the block for readers
 BEGIN, END = "// --- generated: begin ---\n", "// --- generated: end ---\n"
 
 TYPES = {"int": "c_int", "unsigned": "c_uint", "float": "f32", "double": "f64", "uint64_t": "u64", "int64_t": "i64",
@@ -74,13 +75,16 @@ def render() -> str:
 
 
 def main() -> int:
-    src = open(LIB_RS).read()
-    a, b = src.index(BEGIN) + len(BEGIN), src.index(END)
-    new = src[:a] + render() + src[b:]
-    if "--check" in sys.argv:
-        return 0 if new == src else 1
-    open(LIB_RS, "w").write(new)
-    return 0
+    stale = 0
+    for path in (LIB_RS, INTEGRATION):
+        src = open(path).read()
+        a, b = src.index(BEGIN) + len(BEGIN), src.index(END)
+        new = src[:a] + render() + src[b:]
+        if "--check" in sys.argv:
+            stale |= int(new != src)
+        else:
+            open(path, "w").write(new)
+    return stale
 
 
 if __name__ == "__main__":

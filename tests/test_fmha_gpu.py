@@ -72,6 +72,28 @@ def test_golden_fixture_shape_family(b200, oracle):
     assert rc == _lib.ERR_UNSUPPORTED and b"head_dim" in b200.b200tile_last_error()
 
 
+def test_reference_causal_example_shape_against_the_golden_fixture(b200):
+    """The reference's asserted causal example (2 x 8 x 64 x 32, input_pos = 5, cutile-examples/examples/
+    flash_attention_causal.rs:216-285) on the GPU path: the kernels take head vectors of 64 or 128 16-bit elements,
+    so the fixture's f32 operands are rounded to f16 and their head vectors zero-padded from 32 to 64 (zero columns
+    change neither Q.K^T nor the first 32 output columns).  Tolerance: the attention contract (max-abs 2e-2); the
+    reference's own 2e-3 is for its f32 kernel."""
+    import os
+    import numpy as np
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "fmha_causal_pos5.npz"))
+    pad = lambda a: torch.nn.functional.pad(torch.from_numpy(a).half(), (0, 32)).cuda().contiguous()
+    q, k, v = pad(gold["q"]), pad(gold["k"]), pad(gold["v"])
+    b, h, s, d = q.shape
+    o = torch.full((b * h, s, d), float("nan"), dtype=torch.float16, device="cuda")
+    _lib.check(b200.b200tile_fmha_fwd(b"f16", q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), b, h, h, s, s, d,
+                                      I64x2(s * d, d), I64x2(s * d, d), I64x2(s * d, d), I64x2(s * d, d),
+                                      float(gold["scale"]), 1, 5, _stream().cuda_stream))
+    torch.cuda.synchronize()
+    got = o.float().cpu().numpy().reshape(b, h, s, d)
+    assert np.max(np.abs(got[..., :32] - gold["out"])) <= ATTN_TOL
+    assert not got[..., 32:].any()          # the padded value columns stay exactly zero
+
+
 def test_properties(b200):
     torch.manual_seed(1)
     b, h, s, d = 1, 4, 1024, 128
