@@ -68,6 +68,8 @@ SIGNATURES = {
                                 c_void_p]),
     "b200tile_silu_mul_2d": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64, c_int64,
                                      c_void_p]),
+    "b200tile_linear_bias_residual": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                              c_int, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "b200tile_group_gemm_workspace_bytes": (c_uint64, [c_int]),
     "b200tile_group_gemm": (c_int, [c_char_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                     c_int, c_void_p, c_uint64, c_void_p]),

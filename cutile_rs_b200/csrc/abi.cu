@@ -83,6 +83,9 @@ int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const vo
 int b200_fmha_decode_dispatch(int dtype, int head_dim, const void* q, const void* k, const void* v, void* att,
                               float* lse, void* out, const uint32_t* pos, int kv_heads, int group, int kv_cap,
                               int bn, int splits, float qk_scale, const int64_t* strides, cudaStream_t stream);
+int b200_gemm_epilogue_dispatch(int dtype, const void* X, const void* W, const void* bias, const void* residual,
+                                void* O, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ld_res, int64_t ldo,
+                                cudaStream_t stream);
 int b200_gemm_swiglu_dispatch(int dtype, const void* X, const void* W, void* O, int M, int I, int K, int64_t ldx,
                               int64_t ldw, int64_t ldo, cudaStream_t stream);
 size_t b200_grouped_workspace_bytes(int groups);
@@ -419,6 +422,24 @@ int b200tile_linear_swiglu(const char* dtype, const void* x, const void* w_gate_
     return set_error(B200TILE_ERR_ALIGN, "linear_swiglu: base pointers and row pitches must be 16-byte aligned");
   return b200_gemm_swiglu_dispatch(dt, x, w_gate_up, out, m, inter, k, ldx, ldw, ldo,
                                    static_cast<cudaStream_t>(cu_stream));
+}
+
+int b200tile_linear_bias_residual(const char* dtype, const void* x, const void* w, const void* bias,
+                                  const void* residual, void* out, int m, int n, int k, int64_t ldx, int64_t ldw,
+                                  int64_t ld_residual, int64_t ldo, void* cu_stream) {
+  int dt;
+  if (int rc = decode_dtype(dtype, "linear_bias_residual", &dt)) return rc;
+  if (!x || !w || !out) return set_error(B200TILE_ERR_INVALID, "linear_bias_residual: null tensor pointer");
+  if (m <= 0 || n <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_bias_residual: Shape dimensions must be positive");
+  if (ldx < k || ldw < k || ldo < n || (residual && ld_residual < n))
+    return set_error(B200TILE_ERR_INVALID, "linear_bias_residual: a leading dimension is smaller than its row");
+  const uintptr_t al = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out) |
+                       reinterpret_cast<uintptr_t>(bias) | reinterpret_cast<uintptr_t>(residual);
+  if ((al & 15) != 0 || (ldx % 8) || (ldw % 8) || (ldo % 8) || (residual && (ld_residual % 8)))
+    return set_error(B200TILE_ERR_ALIGN, "linear_bias_residual: base pointers and row pitches must be 16-byte aligned");
+  return b200_gemm_epilogue_dispatch(dt, x, w, bias, residual, out, m, n, k, ldx, ldw, ld_residual, ldo,
+                                     static_cast<cudaStream_t>(cu_stream));
 }
 
 // ---------------------------------------------------------------------------

@@ -12,6 +12,8 @@
 //   warps 2..5  epilogue: tcgen05.ld -> bf16/f16 -> swizzled smem -> TMA store
 // The epilogue of tile i overlaps the main loop of tile i+1 through the two accumulator buffers.
 // All waits are bounded; a wait that gives up records a status code and the CTA unwinds.
+#include <cuda_fp16.h>
+
 #include "host_common.h"
 #include "sm100_ptx.cuh"
 
@@ -80,11 +82,33 @@ __device__ __forceinline__ float swiglu_16bit(float gate, float up) {
 // x.up^T for the same 128 output columns, and the epilogue stores silu(gate) * up -- the GEMM and
 // `silu_mul_2d_f16` (cutile-kernels/src/pointwise.rs:50-77) in one pass, with gate and up rounded to
 // the 16-bit type in between exactly as the two-kernel sequence does.
-template <int BN, bool B_KMAJOR, bool OUT_F16, bool SWIGLU = false>
+// EPI (K-major B only): the linear layer's additive epilogue.  `bias` [N] (or null) is added to the fp32
+// accumulator before the result is rounded to the 16-bit type; `residual` [M, N] (or null) is then added the way
+// `add_2d_f16` (cutile-kernels/src/pointwise.rs:20-36) adds two 16-bit tensors: both operands in their 16-bit
+// form, one fp32 sum, one rounding -- so "linear, then add_2d_f16" and this epilogue give the same bits.
+struct EpiArgs {
+  const uint16_t* bias;
+  const uint16_t* residual;
+  int64_t ld_res;
+};
+
+template <bool OUT_F16>
+__device__ __forceinline__ float round_trip_16(float x) {
+  if (OUT_F16) return __half2float(__float2half_rn(x));
+  return __uint_as_float(pack_bf16x2(x, 0.0f) << 16);
+}
+template <bool OUT_F16>
+__device__ __forceinline__ float from_16(uint16_t h) {
+  if (OUT_F16) return __half2float(__ushort_as_half(h));
+  return __uint_as_float((uint32_t)h << 16);
+}
+
+template <int BN, bool B_KMAJOR, bool OUT_F16, bool SWIGLU = false, bool EPI = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int group_m,
-               uint32_t idesc, uint32_t* status) {
+               uint32_t idesc, uint32_t* status, EpiArgs epi) {
+  static_assert(!EPI || (B_KMAJOR && !SWIGLU), "the additive epilogue belongs to the NT linear layer");
   static_assert(!SWIGLU || (BN == 256 && B_KMAJOR), "the fused SwiGLU epilogue pairs two 128-row K-major B blocks");
   constexpr int BN_OUT = SWIGLU ? BN / 2 : BN;   // output columns per tile
   using L = GemmSmem<BN>;
@@ -241,6 +265,46 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) tma_store_wait_read<1>();
         __syncwarp();
         tmem_wait_ld();
+        if (EPI) {
+          const int col0 = n0 + c * 64;
+          const int row_g = m0 + q * 32 + lane;
+          if (epi.bias) {
+#pragma unroll
+            for (int i = 0; i < 64; i += 8) {
+              uint16_t b8[8];
+              if (col0 + i + 8 <= N) {
+                *reinterpret_cast<uint4*>(b8) = __ldg(reinterpret_cast<const uint4*>(epi.bias + col0 + i));
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) b8[e] = col0 + i + e < N ? __ldg(epi.bias + col0 + i + e) : (uint16_t)0;
+              }
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                uint32_t& dst = (i + e < 32) ? v0[(i + e) & 31] : v1[(i + e) & 31];
+                dst = __float_as_uint(__uint_as_float(dst) + from_16<OUT_F16>(b8[e]));
+              }
+            }
+          }
+          if (epi.residual && row_g < M) {
+            const uint16_t* rrow = epi.residual + (int64_t)row_g * epi.ld_res + col0;
+#pragma unroll
+            for (int i = 0; i < 64; i += 8) {
+              uint16_t r8[8];
+              // plain (coherent) loads: `out` may alias `residual`, so the data is not read-only for the kernel
+              if (col0 + i + 8 <= N) {
+                *reinterpret_cast<uint4*>(r8) = *reinterpret_cast<const uint4*>(rrow + i);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) r8[e] = col0 + i + e < N ? rrow[i + e] : (uint16_t)0;
+              }
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                uint32_t& dst = (i + e < 32) ? v0[(i + e) & 31] : v1[(i + e) & 31];
+                dst = __float_as_uint(round_trip_16<OUT_F16>(__uint_as_float(dst)) + from_16<OUT_F16>(r8[e]));
+              }
+            }
+          }
+        }
         const uint32_t sbuf = sCw + (c & 1) * L::C_WARP_BYTES;
         const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
@@ -321,7 +385,42 @@ static int launch_gemm_tc(const void* A, const void* B, void* C, int M, int N, i
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
   const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, GEMM_BM, BN);
   kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, group_m, idesc,
-                                                 di->status);
+                                                 di->status, EpiArgs{nullptr, nullptr, 0});
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// out[M, N] = x . w^T (+ bias[N]) (+ residual[M, N]); x [M,K], w [N,K]: the NT linear layer with its additive epilogue
+template <int BN, bool OUT_F16>
+static int launch_gemm_epi(const void* X, const void* W, const void* bias, const void* residual, void* O, int M, int N,
+                           int K, int64_t ldx, int64_t ldw, int64_t ld_res, int64_t ldo, cudaStream_t stream) {
+  using L = GemmSmem<BN>;
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200_ERR_CUDA;
+  const CUtensorMapDataType dt = OUT_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  if ((rc = b200h::encode_tmap_2d(&tmA, dt, 2, X, (uint64_t)K, (uint64_t)M, (uint64_t)ldx * 2, GEMM_BK, GEMM_BM,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_2d(&tmB, dt, 2, W, (uint64_t)K, (uint64_t)N, (uint64_t)ldw * 2, GEMM_BK, BN,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_2d(&tmC, dt, 2, O, (uint64_t)N, (uint64_t)M, (uint64_t)ldo * 2, 64, 32,
+                                  CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  auto kern = gemm_tc_kernel<BN, true, OUT_F16, false, true>;
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    attr_done.set(di->ordinal);
+  }
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < di->sm_count ? tiles : di->sm_count;
+  const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
+  const uint32_t idesc = make_idesc(fmt, fmt, 0, 0, GEMM_BM, BN);
+  EpiArgs epi{static_cast<const uint16_t*>(bias), static_cast<const uint16_t*>(residual), ld_res};
+  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, 8, idesc, di->status, epi);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -355,7 +454,8 @@ static int launch_gemm_swiglu(const void* X, const void* W, void* O, int M, int 
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
   const uint32_t idesc = make_idesc(fmt, fmt, 0, 0, GEMM_BM, 256);
-  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, I, K, 8, idesc, di->status);
+  kern<<<grid, GEMM_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, I, K, 8, idesc, di->status,
+                                                 EpiArgs{nullptr, nullptr, 0});
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }
@@ -393,6 +493,22 @@ int b200_gemm_swiglu_dispatch(int dtype, const void* X, const void* W, void* O, 
   using namespace b200;
   return dtype ? launch_gemm_swiglu<true>(X, W, O, M, I, K, ldx, ldw, ldo, stream)
                : launch_gemm_swiglu<false>(X, W, O, M, I, K, ldx, ldw, ldo, stream);
+}
+
+// dtype: 0 = bf16, 1 = f16.  Small problems take 128-column tiles (more CTAs), the rest 256-column ones.
+int b200_gemm_epilogue_dispatch(int dtype, const void* X, const void* W, const void* bias, const void* residual,
+                                void* O, int M, int N, int K, int64_t ldx, int64_t ldw, int64_t ld_res, int64_t ldo,
+                                cudaStream_t stream) {
+  using namespace b200;
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200_ERR_CUDA;
+  const long long tiles256 = (long long)((M + GEMM_BM - 1) / GEMM_BM) * ((N + 255) / 256);
+  const bool narrow = tiles256 < di->sm_count;
+  if (narrow)
+    return dtype ? launch_gemm_epi<128, true>(X, W, bias, residual, O, M, N, K, ldx, ldw, ld_res, ldo, stream)
+                 : launch_gemm_epi<128, false>(X, W, bias, residual, O, M, N, K, ldx, ldw, ld_res, ldo, stream);
+  return dtype ? launch_gemm_epi<256, true>(X, W, bias, residual, O, M, N, K, ldx, ldw, ld_res, ldo, stream)
+               : launch_gemm_epi<256, false>(X, W, bias, residual, O, M, N, K, ldx, ldw, ld_res, ldo, stream);
 }
 
 #ifdef B200TILE_TEST_HOOKS

@@ -765,6 +765,29 @@ def linear_swiglu(out: Tensor, x: Tensor, w_gate_up: Tensor, stream: Optional[to
     return out
 
 
+def linear_bias_residual(out: Tensor, x: Tensor, w: Tensor, bias: Optional[Tensor] = None,
+                         residual: Optional[Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> Tensor:
+    """out [M, N] = x . w^T (+ bias [N]) (+ residual [M, N]) in one kernel (``b200tile_linear_bias_residual``): the NT
+    linear layer with the residual add of `add_2d_f16` (cutile-kernels/src/pointwise.rs:20-36) in its epilogue;
+    x [M, K], w [N, K]; ``out`` may be ``residual``."""
+    lib = _lib.load()
+    s = stream or torch.cuda.current_stream()
+    m, n = out.shape
+    k = x.shape[1]
+    if tuple(w.shape) != (n, k) or x.shape[0] != m or (residual is not None and tuple(residual.shape) != (m, n)) or \
+            (bias is not None and bias.size() != n):
+        raise KernelLaunchError("linear_bias_residual: expected x [M,K], w [N,K], bias [N], residual / out [M,N]")
+    rc = lib.b200tile_linear_bias_residual(out.dtype_str().encode(), x.cu_deviceptr(), w.cu_deviceptr(),
+                                           bias.cu_deviceptr() if bias is not None else None,
+                                           residual.cu_deviceptr() if residual is not None else None, out.cu_deviceptr(),
+                                           m, n, k, x.strides[0], w.strides[0],
+                                           residual.strides[0] if residual is not None else 0, out.strides[0],
+                                           c_void_p(s.cuda_stream))
+    if rc:
+        raise KernelLaunchError(lib.b200tile_last_error().decode())
+    return out
+
+
 def nvfp4_prepare_weight_scales(y_scales: Tensor, n: int, k: int, config: int = 0,
                                 stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """Brings weight scales [N, K/16] into the kernel's tile layout once (``b200tile_nvfp4_prepare_weight_scales``);

@@ -228,6 +228,17 @@ B200TILE_API int b200tile_lm_head_argmax_blocks(const char* dtype, const void* w
 B200TILE_API int b200tile_argmax_reduce_blocks(const float* block_max, const uint32_t* block_idx, uint32_t* out,
                                                int num_blocks, void* cu_stream);
 
+/* out[m, n] = x . w^T (+ bias[n]) (+ residual[m, n]): the NT linear layer with its additive epilogue.  `bias` and
+ * `residual` may each be NULL.  The bias is added to the fp32 accumulator before the 16-bit rounding; the residual is
+ * added as `add_2d_f16` (cutile-kernels/src/pointwise.rs:20-36) adds two 16-bit tensors, so with a NULL bias the call
+ * replaces the sequence "NT linear layer, then add_2d_f16" (an attention or MLP output projection followed by the
+ * residual add) bit for bit, without the [m, n] intermediate going to memory and back.  `out` may alias `residual`.
+ *   dtype "bf16" or "f16"; x [m, k], w [n, k], residual / out [m, n]; pitches in elements, multiples of 8; pointers
+ *   16-byte aligned. */
+B200TILE_API int b200tile_linear_bias_residual(const char* dtype, const void* x, const void* w, const void* bias,
+                                               const void* residual, void* out, int m, int n, int k, int64_t ldx,
+                                               int64_t ldw, int64_t ld_residual, int64_t ldo, void* cu_stream);
+
 /* Element-wise kernels over [rows, cols] 16-bit tensors (pitches in elements; `out` may alias an input):
  * b200tile_add_2d:      out = lhs + rhs in the 16-bit type; replaces `add_2d_f16`
  *                       (cutile-kernels/src/pointwise.rs:20-36).

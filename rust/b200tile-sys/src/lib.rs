@@ -101,6 +101,9 @@ extern "C" {
         cu_stream: *mut c_void) -> c_int;
     pub fn b200tile_argmax_reduce_blocks(block_max: *const f32, block_idx: *const u32, out: *mut u32,
         num_blocks: c_int, cu_stream: *mut c_void) -> c_int;
+    pub fn b200tile_linear_bias_residual(dtype: *const c_char, x: *const c_void, w: *const c_void,
+        bias: *const c_void, residual: *const c_void, out: *mut c_void, m: c_int, n: c_int, k: c_int,
+        ldx: i64, ldw: i64, ld_residual: i64, ldo: i64, cu_stream: *mut c_void) -> c_int;
     pub fn b200tile_add_2d(dtype: *const c_char, out: *mut c_void, lhs: *const c_void, rhs: *const c_void,
         rows: c_int, cols: c_int, ld_out: i64, ld_lhs: i64, ld_rhs: i64, cu_stream: *mut c_void) -> c_int;
     pub fn b200tile_silu_mul_2d(dtype: *const c_char, out: *mut c_void, gate: *const c_void,

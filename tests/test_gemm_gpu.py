@@ -273,3 +273,44 @@ def test_linear_with_fused_swiglu(b200, oracle, dtype, m, inter, k):
     assert oracle.rel_frobenius(got, ref) <= 1e-2
     # element-wise: one rounding step of the output type plus the effect of a last-bit difference in gate/up
     assert np.max(np.abs(got - ref) / (np.abs(ref) + 1e-2)) <= 0.05
+
+
+@pytest.mark.parametrize("dtype,m,n,k", [(torch.bfloat16, 300, 392, 320), (torch.float16, 128, 200, 256),
+                                         (torch.bfloat16, 2048, 4096, 512)])
+def test_linear_with_bias_and_residual_epilogue(b200, oracle, dtype, m, n, k):
+    """x . w^T + bias + residual from one kernel.  Against the oracle (fp32 GEMM, bias added in fp32, rounded to the
+    16-bit type, residual added like `add_2d_f16`, pointwise.rs:20-36), and bit for bit against this library's own
+    unfused sequence (NT GEMM into memory, then b200tile_add_2d) when there is no bias."""
+    g = torch.Generator().manual_seed(n + k)
+    x = (torch.randn(m, k, generator=g) / 4).to(dtype)
+    w = (torch.randn(n, k, generator=g) / 4).to(dtype)
+    bias = torch.randn(n, generator=g).to(dtype)
+    res = torch.randn(m, n, generator=g).to(dtype)
+    name = "bf16" if dtype == torch.bfloat16 else "f16"
+    is_f16 = dtype == torch.float16
+    rnd = (lambda a: a.astype(np.float16).astype(np.float32)) if is_f16 else oracle.round_bf16
+    xd, wd, bd, rd = (api.copy_host_to_device(t) for t in (x, w, bias, res))
+    acc = oracle.cpu_gemm_nt(x.float().numpy(), w.float().numpy(), threads=0)
+    for use_bias, use_res in ((True, True), (True, False), (False, True)):
+        out = api.from_torch(torch.full((m, n), float("nan"), dtype=dtype, device="cuda"))
+        launch.linear_bias_residual(out, xd, wd, bd if use_bias else None, rd if use_res else None)
+        torch.cuda.synchronize()
+        ref = rnd(acc + (bias.float().numpy()[None, :] if use_bias else 0.0))
+        if use_res:
+            ref = rnd(ref + res.float().numpy())
+        got = out.storage.float().cpu().numpy()
+        assert not np.isnan(got).any()
+        assert oracle.rel_frobenius(got, ref) <= 1e-2
+        # element-wise: the fp32 sums are formed in another order, which can move a 16-bit rounding by one step
+        assert np.max(np.abs(got - ref) / (np.abs(ref) + 1.0)) <= (2.0 ** -9 if is_f16 else 2.0 ** -6)
+    # no bias: the same bits as GEMM -> memory -> add_2d
+    plain = _gemm(b200, name, xd.storage, wd.storage, layout=1, config=0)   # whole tiles: the same k order per output
+    unfused = torch.empty_like(plain)
+    _lib.check(b200.b200tile_add_2d(name.encode(), unfused.data_ptr(), plain.data_ptr(), rd.storage.data_ptr(), m, n, n, n,
+                                    n, _stream().cuda_stream))
+    fused = rd.storage.clone()           # in place: out aliases the residual
+    ft = api.from_torch(fused)
+    launch.linear_bias_residual(ft, xd, wd, None, ft)
+    torch.cuda.synchronize()
+    assert torch.equal(fused, unfused)
+    _status_ok(b200)
