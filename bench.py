@@ -722,7 +722,7 @@ def bench_single_gpu_yardsticks(ctx, step, flops, x, y, n_local):
 
     def ones_step():
         _lib.check(lib.b200tile_gemm(b"f16", 0, ones_a.data_ptr(), ones_b.data_ptr(), ones_c.data_ptr(), 1, M, N, K, K, N,
-                                     N, 0, 0, 0, 0, 2, 8, 0, stream.cuda_stream))
+                                     N, 0, 0, 0, 0, 3, 8, 0, stream.cuda_stream))
     # 5 warm-up launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
     # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322)
     for _ in range(5):
@@ -740,7 +740,7 @@ def bench_single_gpu_yardsticks(ctx, step, flops, x, y, n_local):
     out["gemm_f16_ones_published_protocol"] = {
         "tflops": flops / med / 1e12, "median_us": med * 1e6, "published_reference_tflops": 2068.88,
         "result_is_k_everywhere": bool((ones_c[::997, ::991].float() == float(K)).all().item()),
-        "accumulator": "fp32 here, f16 in the published run"}
+        "tile": "256x512 per CTA pair", "accumulator": "fp32 here, f16 in the published run"}
     ctx.launches += 35
     del ones_a, ones_b, ones_c
     a_t, b_t, c_t = x.storage, y.storage, torch.empty((M, n_local), dtype=torch.bfloat16, device=dev)
@@ -811,8 +811,11 @@ def run_gpu_arm(args):
     x = api.copy_host_to_device(a_host)
     y = api.copy_host_to_device(b_host)
     z = api.zeros([M, n_local], "bf16")
-    # the reference's published configuration: tile 256x256x64 on CTA pairs (num_cta_in_cga = 2)
-    bm, bn = 256, 256
+    # CTA pairs (num_cta_in_cga = 2, the reference's published cluster setting) on the 256 x 512 tile: two N = 256
+    # MMAs per k-step share the A operand, three quarters of the 256 x 256 tile's bytes per FLOP.  Shards too narrow
+    # to fill one wave of 512-wide tiles (8192 x 1024 at eight GPUs) take the 256 x 256 tile, which the pair kernel
+    # splits along K over all pairs (stream-K).
+    bm, bn = 256, (512 if (n_local // 512) * (M // 256) >= 74 else 256)
     generics = ["bf16", str(bm), str(bn), "64"]
     opts = launch.CompileOptions(num_cta_in_cga=2, occupancy=1)
 
@@ -931,7 +934,8 @@ def run_gpu_arm(args):
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "gemm_bf16_8192x8192x8192", "layout": "A[M,K] B[K,N] row-major, fp32 acc",
-                       "tile": f"{bm}x{bn} per CTA pair (cta_group::2), 3 stages of 128-deep k slabs (TMA ring), persistent, grouped-M 8",
+                       "tile": f"{bm}x{bn} per CTA pair (cta_group::2), " + ("4 stages of 64-deep" if bn == 512 else "3 stages of 128-deep") +
+                               " k slabs (TMA ring), persistent, grouped-M 8",
                        "parallelism": f"N-split x{world}" if world > 1 else "single GPU",
                        "l2": "operands 403 MB per step exceed the 126 MB L2; no flush between steps"},
             "per_gpu_tflops": per_gpu,
@@ -978,6 +982,7 @@ def run_case(argv) -> int:
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--config", type=int, default=-1)
     ap.add_argument("--layout", type=int, default=0)
+    ap.add_argument("--group-m", type=int, default=0, help="gemm: tile rows per band of the tile order (0 = the library's default, 8)")
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--seq", type=int, default=4096)
@@ -1011,7 +1016,7 @@ def run_case(argv) -> int:
 
         def run():
             _lib.check(lib.b200tile_gemm(b"bf16", args.layout, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n,
-                                         k, k, b.stride(0), n, 0, 0, 0, 0, args.config, 0, 0, stream.cuda_stream))
+                                         k, k, b.stride(0), n, 0, 0, 0, 0, args.config, args.group_m, 0, stream.cuda_stream))
         flops = 2.0 * m * n * k
     elif args.kernel == "nvfp4":
         m, n, k = args.m, args.n, args.k

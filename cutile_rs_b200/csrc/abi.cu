@@ -20,7 +20,7 @@ int b200_gemm_tc_dispatch(int dtype, int b_kmajor, int config, const void* A, co
 int b200_test_set_skip_stage(int on);
 #endif
 int b200_gemm_pair_reset_scratch(cudaStream_t stream);
-int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* B, void* C, int M,
+int b200_gemm_pair_dispatch(int dtype, int b_kmajor, int wide, const void* A, const void* B, void* C, int M,
                             int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int group_m,
                             int max_ctas, cudaStream_t stream);
 int b200_gemm_f32_dispatch(const float* A, const float* B, float* C, int batch, int M, int N,
@@ -155,6 +155,7 @@ static const b200tile_config kGemmTcConfigs[] = {
     {0, 128, 256, 64, 4, 1, 1},
     {1, 128, 128, 64, 6, 1, 1},
     {2, 256, 256, 64, 6, 2, 1},
+    {3, 256, 512, 64, 4, 2, 1},
 };
 static const b200tile_config kGemmF32Configs[] = {
     {0, 64, 64, 16, 1, 1, 1},
@@ -210,14 +211,24 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
 }
 
 // Default configuration: the one with the least (waves x per-SM tile work / relative speed).
-// Relative speeds are the measured ratios of the three kernels at 8192^3.
-static int default_gemm_config(int m, int n) {
+// Relative speeds are the measured ratios of the kernels at 8192^3 (the 256 x 512 pair tile moves three quarters
+// of the 256 x 256 tile's bytes per FLOP and is 3.6 % ahead there).  The pair kernels split a partial last wave
+// along K (stream-K) when K is deep enough, so their wave count is fractional above one wave.
+static int default_gemm_config(int m, int n, int k) {
   const b200h::DeviceInfo* di = b200h::device_info();
   const int64_t sms = di ? di->sm_count : 148;
   auto cdiv = [](int64_t a, int64_t b) { return (a + b - 1) / b; };
+  auto pair_waves = [&](int64_t tiles, int bk) {
+    const int64_t pairs = sms / 2;
+    if (tiles <= pairs) return 1.0;
+    if (cdiv(k, bk) >= 4) return 1.03 * (double)tiles / (double)pairs;
+    return (double)cdiv(tiles, pairs);
+  };
   const double cost0 = (double)cdiv(cdiv(m, 128) * cdiv(n, 256), sms) * 1.0 / 0.92;
   const double cost1 = (double)cdiv(cdiv(m, 128) * cdiv(n, 128), sms) * 0.5 / 0.72;
-  const double cost2 = (double)cdiv(cdiv(m, 256) * cdiv(n, 256), sms / 2) * 1.0 / 1.0;
+  const double cost2 = pair_waves(cdiv(m, 256) * cdiv(n, 256), 128) * 1.0 / 1.0;
+  const double cost3 = pair_waves(cdiv(m, 256) * cdiv(n, 512), 64) * 2.0 / 1.036;
+  if (cost3 <= cost2 && cost3 <= cost0 && cost3 <= cost1) return 3;
   if (cost2 <= cost0 && cost2 <= cost1) return 2;
   return cost0 <= cost1 ? 0 : 1;
 }
@@ -260,14 +271,14 @@ int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b,
   if (accumulate)
     return set_error(B200TILE_ERR_UNSUPPORTED,
                      "gemm(%s): accumulate-into-C is only provided for f32", dtype);
-  if (config < 0) config = default_gemm_config(m, n);
+  if (config < 0) config = default_gemm_config(m, n, k);
   for (int bi = 0; bi < batch; ++bi) {
     const char* ab = static_cast<const char*>(a) + (int64_t)bi * stride_a * 2;
     const char* bb = static_cast<const char*>(b) + (int64_t)bi * stride_b * 2;
     char* cb = static_cast<char*>(c) + (int64_t)bi * stride_c * 2;
-    int rc = config == 2
-                 ? b200_gemm_pair_dispatch(dt, b_layout ? 1 : 0, ab, bb, cb, m, n, k, lda, ldb, ldc,
-                                           group_size_m, num_programs, stream)
+    int rc = config >= 2
+                 ? b200_gemm_pair_dispatch(dt, b_layout ? 1 : 0, config == 3 ? 1 : 0, ab, bb, cb, m, n, k, lda, ldb,
+                                           ldc, group_size_m, num_programs, stream)
                  : b200_gemm_tc_dispatch(dt, b_layout ? 1 : 0, config, ab, bb, cb, m, n, k, lda,
                                          ldb, ldc, group_size_m, num_programs, stream);
     if (rc) return rc;
@@ -894,6 +905,7 @@ int select_gemm_config(const char* dtype, long bm, long bn, long bk,
     return B200TILE_OK;
   }
   if (bm == 256 && bn == 256 && bk == 64 && cga != 1) { *config = 2; return B200TILE_OK; }
+  if (bm == 256 && bn == 512 && bk == 64 && cga != 1) { *config = 3; return B200TILE_OK; }
   if (bm == 128 && bn == 256 && bk == 64 && cga != 2) { *config = 0; return B200TILE_OK; }
   if (bm == 128 && bn == 128 && bk == 64 && cga != 2) { *config = 1; return B200TILE_OK; }
   return set_error(B200TILE_ERR_UNSUPPORTED,

@@ -37,27 +37,37 @@ __device__ long long g_trace_gemm_pair[8];
 #endif
 
 constexpr int P_BM = 128;   // rows per CTA (256 per pair)
-constexpr int P_BN = 256;   // columns per pair (128 loaded per CTA)
-#ifndef B200_PAIR_BK
-#define B200_PAIR_BK 128
-#endif
-constexpr int P_BK = B200_PAIR_BK;  // 128: two 128-byte swizzle rows per stage, 8 MMAs per pair of commits
-constexpr int P_KH = P_BK / 64;  // 64-wide (128-byte) sub-blocks per stage
 constexpr int P_THREADS = 192;
-constexpr int P_STAGES = 384 / P_BK;  // 192 KiB of operand ring per CTA
 
-struct PairSmem {
-  static constexpr int A_BYTES = P_BM * P_BK * 2;        // 16 KiB
-  static constexpr int B_BYTES = (P_BN / 2) * P_BK * 2;  // 16 KiB
+// Two tile widths.  BN = 256: one 256x256 accumulator per tile, double-buffered (the epilogue of tile i overlaps
+// the main loop of tile i+1), 128-deep stages.  BN = 512: the pair's tile is 256 rows x 512 columns, i.e. two
+// N = 256 MMAs per k-step that share the A operand: each CTA loads 128 rows of A and 256 columns of B per
+// stage, three quarters of the bytes per FLOP of the 256-wide tile, which is what a kernel bound by the
+// L2 -> shared-memory stream at full clock needs; the accumulator then takes all 512 Tensor-Memory columns, so
+// there is one of it and the epilogue does not overlap the next tile's main loop (a few per cent at K = 8192).
+template <int BN>
+struct PairCfg {
+  static_assert(BN == 256 || BN == 512, "pair tiles are 256 or 512 columns wide");
+  static constexpr int NB = BN / 256;              // N = 256 MMAs per k-step
+  static constexpr int NACC = BN == 256 ? 2 : 1;   // accumulators in Tensor Memory
+  static constexpr int BK = BN == 256 ? 128 : 64;  // k depth of a stage
+  static constexpr int KH = BK / 64;               // 64-wide (128-byte) sub-blocks per stage
+  static constexpr int STAGES = BN == 256 ? 3 : 4; // 192 KiB of operand ring per CTA either way
+  static constexpr int A_BYTES = P_BM * BK * 2;
+  static constexpr int BJ_BYTES = 128 * BK * 2;    // the 128 columns (rows, for a K-major B) this CTA feeds to ONE MMA
+  static constexpr int B_BYTES = NB * BJ_BYTES;
   static constexpr int C_WARP_BYTES = 32 * 128;
   static constexpr int OFF_A = 0;
-  static constexpr int OFF_B = OFF_A + P_STAGES * A_BYTES;
-  static constexpr int OFF_C = OFF_B + P_STAGES * B_BYTES;
+  static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
+  static constexpr int OFF_C = OFF_B + STAGES * B_BYTES;
   static constexpr int OFF_BAR = OFF_C + 4 * 2 * C_WARP_BYTES;
-  static constexpr int NUM_BARS = 2 * P_STAGES + 4;
+  static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
+  static constexpr int SLOT_FLOATS = P_BM * BN;    // fp32 stream-K partial of one CTA
+  static_assert(TOTAL <= 232448, "exceeds the shared memory of a CTA");
 };
+constexpr int P_MAX_SLOT_FLOATS = P_BM * 512;
 
 __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int group_m,
                                                  int& bm, int& bn) {
@@ -144,15 +154,14 @@ __device__ __forceinline__ bool wait_flag(const WaitCtx& ctx, const uint32_t* fl
   return false;
 }
 
-constexpr int P_SLOT_FLOATS = P_BM * P_BN;  // fp32 partial of one CTA: 128 rows x 256 columns
-
-template <bool B_KMAJOR, bool OUT_F16>
+template <bool B_KMAJOR, bool OUT_F16, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int group_m,
                     uint32_t idesc, uint32_t* status, int sk_tiles, float* sk_partials,
                     uint32_t* sk_flags) {
-  using L = PairSmem;
+  using L = PairCfg<BN>;
+  constexpr int P_BK = L::BK, P_KH = L::KH, P_STAGES = L::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -197,7 +206,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t tmem_base = misc[0];
 
   const int tiles_m = (M + 2 * P_BM - 1) / (2 * P_BM);
-  const int tiles_n = (N + P_BN - 1) / P_BN;
+  const int tiles_n = (N + BN - 1) / BN;
   const int total_tiles = tiles_m * tiles_n;
   const int num_kb = (K + P_BK - 1) / P_BK;
   const int pair = blockIdx.x >> 1;
@@ -215,7 +224,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         int bm, bn;
         pair_tile_coords(tile, tiles_m, tiles_n, group_m, bm, bn);
         const int m0 = bm * (2 * P_BM) + (int)rank * P_BM;
-        const int n0 = bn * P_BN + (int)rank * (P_BN / 2);
+        // MMA j of a k-step covers tile columns [256 j, 256 j + 256); this CTA feeds its 128 of them
+        const int n0 = bn * BN + (int)rank * 128;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
           const uint32_t full_leader = mapa_u32(bar_full + stage * 8, 0);
@@ -225,17 +235,19 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int h = 0; h < P_KH; ++h)
             tma_load_2d_pair(sA + stage * L::A_BYTES + h * (P_BM * 128), &tmA, full_leader,
                              kb * P_BK + h * 64, m0);
-          if (B_KMAJOR) {
 #pragma unroll
-            for (int h = 0; h < P_KH; ++h)
-              tma_load_2d_pair(sB + stage * L::B_BYTES + h * ((P_BN / 2) * 128), &tmB, full_leader,
-                               kb * P_BK + h * 64, n0);
-          } else {
-            // N-major B: one [P_BK k-rows][64 columns] box per 64-column chunk
+          for (int jn = 0; jn < L::NB; ++jn) {
+            const uint32_t sBj = sB + stage * L::B_BYTES + jn * L::BJ_BYTES;
+            if (B_KMAJOR) {
 #pragma unroll
-            for (int j = 0; j < P_BN / 2 / 64; ++j)
-              tma_load_2d_pair(sB + stage * L::B_BYTES + j * (P_BK * 128), &tmB, full_leader,
-                               n0 + j * 64, kb * P_BK);
+              for (int h = 0; h < P_KH; ++h)
+                tma_load_2d_pair(sBj + h * (128 * 128), &tmB, full_leader, kb * P_BK + h * 64, n0 + jn * 256);
+            } else {
+              // N-major B: one [P_BK k-rows][64 columns] box per 64-column chunk
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                tma_load_2d_pair(sBj + j * (P_BK * 128), &tmB, full_leader, n0 + jn * 256 + j * 64, kb * P_BK);
+            }
           }
           if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
         }
@@ -251,13 +263,14 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int tile, kb0, kb1;
       B200_TR_DECL(6);
       for (; ok && sched.next(tile, kb0, kb1); ++it) {
-        const uint32_t buf = it & 1;
+        const uint32_t buf = L::NACC == 2 ? (it & 1) : 0;
+        const uint32_t tpar = L::NACC == 2 ? (((it >> 1) & 1) ^ 1) : ((it & 1) ^ 1);
         B200_TR_BEGIN();
-        if (!mbar_wait(wctx, bar_tempty + buf * 8, ((it >> 1) & 1) ^ 1, 2)) { ok = false; break; }
+        if (!mbar_wait(wctx, bar_tempty + buf * 8, tpar, 2)) { ok = false; break; }
         B200_TR_END(0);
         B200_TR_COUNT(5);
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * P_BN;
+        const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
           B200_TR_BEGIN();
           if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
@@ -266,18 +279,21 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           B200_TR_COUNT(4);
           B200_TR_BEGIN();
           const uint64_t adesc = make_smem_desc(sA + stage * L::A_BYTES, 16, 1024, SWZ_128B);
-          const uint64_t bdesc =
-              B_KMAJOR ? make_smem_desc(sB + stage * L::B_BYTES, 16, 1024, SWZ_128B)
-                       : make_smem_desc(sB + stage * L::B_BYTES, P_BK * 128, 1024, SWZ_128B);
 #pragma unroll
           for (int k = 0; k < P_BK / 16; ++k) {
             // K-major operands: 32 bytes per step inside a 64-wide sub-block, next sub-block one
             // [rows][128 B] slab further; N-major B: two 8-row groups (2 x 1024 bytes) per step
             const uint32_t kmaj_a = (uint32_t)((k & 3) * 2 + (k >> 2) * ((P_BM * 128) >> 4));
-            const uint32_t kmaj_b = (uint32_t)((k & 3) * 2 + (k >> 2) * (((P_BN / 2) * 128) >> 4));
+            const uint32_t kmaj_b = (uint32_t)((k & 3) * 2 + (k >> 2) * ((128 * 128) >> 4));
             const uint64_t a_k = adesc + (uint64_t)kmaj_a;
-            const uint64_t b_k = bdesc + (uint64_t)(B_KMAJOR ? kmaj_b : (uint32_t)(k * 128));
-            umma_f16_ss_2cta(d_tmem, a_k, b_k, idesc, (kb != kb0) || (k != 0));
+#pragma unroll
+            for (int jn = 0; jn < L::NB; ++jn) {
+              const uint32_t sBj = sB + stage * L::B_BYTES + jn * L::BJ_BYTES;
+              const uint64_t bdesc = B_KMAJOR ? make_smem_desc(sBj, 16, 1024, SWZ_128B)
+                                              : make_smem_desc(sBj, P_BK * 128, 1024, SWZ_128B);
+              const uint64_t b_k = bdesc + (uint64_t)(B_KMAJOR ? kmaj_b : (uint32_t)(k * 128));
+              umma_f16_ss_2cta(d_tmem + jn * 256, a_k, b_k, idesc, (kb != kb0) || (k != 0));
+            }
           }
           B200_TR_END(2);
           B200_TR_BEGIN();
@@ -308,18 +324,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     for (; ok && sched.next(tile, kb0, kb1); ++it) {
       int bm, bn;
       pair_tile_coords(tile, tiles_m, tiles_n, group_m, bm, bn);
-      const int m0 = bm * (2 * P_BM) + (int)rank * P_BM, n0 = bn * P_BN;
-      const uint32_t buf = it & 1;
-      if (!mbar_wait(wctx, bar_tfull + buf * 8, (it >> 1) & 1, 4)) { ok = false; break; }
+      const int m0 = bm * (2 * P_BM) + (int)rank * P_BM, n0 = bn * BN;
+      const uint32_t buf = L::NACC == 2 ? (it & 1) : 0;
+      if (!mbar_wait(wctx, bar_tfull + buf * 8, L::NACC == 2 ? ((it >> 1) & 1) : (it & 1), 4)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * P_BN;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       const int row = q * 32 + lane;
       if (kb1 < num_kb) {
         // ---- the share stops inside this tile: publish the fp32 partial, column-major so that the
         // 32 lanes of a warp write 128 contiguous bytes ----
-        float* slot = sk_partials + (size_t)blockIdx.x * P_SLOT_FLOATS;
+        float* slot = sk_partials + (size_t)blockIdx.x * L::SLOT_FLOATS;
 #pragma unroll 1
-        for (int c = 0; c < P_BN / 32; ++c) {
+        for (int c = 0; c < BN / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_row + c * 32, v);
           tmem_wait_ld();
@@ -350,7 +366,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!ok) break;
       }
 #pragma unroll 1
-      for (int c = 0; c < P_BN / 64; ++c) {
+      for (int c = 0; c < BN / 64; ++c) {
         uint32_t v0[32], v1[32];
         tmem_ld_32x32b_x32(t_row + c * 64, v0);
         tmem_ld_32x32b_x32(t_row + c * 64 + 32, v1);
@@ -359,7 +375,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_wait_ld();
         for (int qq = q_first; qq <= q_last; ++qq) {
           if (sched.first_unit(qq) == sched.first_unit(qq + 1)) continue;
-          const float* part = sk_partials + (size_t)(2 * qq + (int)rank) * P_SLOT_FLOATS + row;
+          const float* part = sk_partials + (size_t)(2 * qq + (int)rank) * L::SLOT_FLOATS + row;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             v0[i] = __float_as_uint(__uint_as_float(v0[i]) + __ldcg(part + (c * 64 + i) * P_BM));
@@ -369,7 +385,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         // staging buffer by chunk parity: valid because every tile stores an EVEN number of chunks (4), so
         // `wait_group.read 1` above has always drained the buffer chosen here; a variant that can store an
         // odd number of chunks per tile must count committed stores instead
-        static_assert((P_BN / 64) % 2 == 0, "chunk-parity staging needs an even number of chunks per tile");
+        static_assert((BN / 64) % 2 == 0, "chunk-parity staging needs an even number of chunks per tile");
         const uint32_t sbuf = sCw + (c & 1) * L::C_WARP_BYTES;
         const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
@@ -466,7 +482,7 @@ SkScratch* sk_scratch_for(int dev, int slots, cudaStream_t stream) {
     SkScratch& e = g_sk[dev][i];
     if (e.used) continue;
     void *p = nullptr, *f = nullptr;
-    if (cudaMalloc(&p, (size_t)slots * P_SLOT_FLOATS * sizeof(float)) != cudaSuccess) {
+    if (cudaMalloc(&p, (size_t)slots * P_MAX_SLOT_FLOATS * sizeof(float)) != cudaSuccess) {
       cudaGetLastError();
       return nullptr;
     }
@@ -501,11 +517,12 @@ bool streamk_enabled() {
 }
 }  // namespace
 
-template <bool B_KMAJOR, bool OUT_F16>
+template <bool B_KMAJOR, bool OUT_F16, int BN>
 static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
                             int64_t ldb, int64_t ldc, int group_m, int max_ctas,
                             cudaStream_t stream) {
-  using L = PairSmem;
+  using L = PairCfg<BN>;
+  constexpr int P_BK = L::BK;
   const b200h::DeviceInfo* di = b200h::device_info();
   if (!di) return B200_ERR_CUDA;
   const CUtensorMapDataType dt =
@@ -517,7 +534,7 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
     return rc;
   if (B_KMAJOR)
     rc = b200h::encode_tmap_2d(&tmB, dt, 2, B, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, 64,
-                               P_BN / 2, CU_TENSOR_MAP_SWIZZLE_128B);
+                               128, CU_TENSOR_MAP_SWIZZLE_128B);
   else
     rc = b200h::encode_tmap_2d(&tmB, dt, 2, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64,
                                P_BK, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -525,14 +542,14 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
   if ((rc = b200h::encode_tmap_2d(&tmC, dt, 2, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64,
                                   32, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  auto kern = gemm_tc_pair_kernel<B_KMAJOR, OUT_F16>;
+  auto kern = gemm_tc_pair_kernel<B_KMAJOR, OUT_F16, BN>;
   static b200h::DeviceOnce attr_done;
   if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(
         cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
     attr_done.set(di->ordinal);
   }
-  const int tiles = ((M + 2 * P_BM - 1) / (2 * P_BM)) * ((N + P_BN - 1) / P_BN);
+  const int tiles = ((M + 2 * P_BM - 1) / (2 * P_BM)) * ((N + BN - 1) / BN);
   const int all_pairs = di->sm_count / 2;
   int pairs = all_pairs;
   if (tiles < pairs) pairs = tiles;
@@ -554,7 +571,7 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
     }
   }
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
-  const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, 2 * P_BM, P_BN);
+  const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, 2 * P_BM, 256);
   kern<<<pairs * 2, P_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, group_m, idesc,
                                                    di->status, sk_tiles, sk ? sk->partials : nullptr,
                                                    sk ? sk->flags : nullptr);
@@ -564,17 +581,19 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
 
 }  // namespace b200
 
-int b200_gemm_pair_dispatch(int dtype, int b_kmajor, const void* A, const void* B, void* C, int M,
+// wide = 0: 256 x 256 tiles per CTA pair; wide = 1: 256 x 512 (two N = 256 MMAs per k-step sharing A)
+int b200_gemm_pair_dispatch(int dtype, int b_kmajor, int wide, const void* A, const void* B, void* C, int M,
                             int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int group_m,
                             int max_ctas, cudaStream_t stream) {
   using namespace b200;
-  if (!b_kmajor && dtype == 0)
-    return launch_gemm_pair<false, false>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
-  if (!b_kmajor && dtype == 1)
-    return launch_gemm_pair<false, true>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
-  if (b_kmajor && dtype == 0)
-    return launch_gemm_pair<true, false>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
-  return launch_gemm_pair<true, true>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
+#define B200_PAIR_CASE(KM_, F16_)                                                                          \
+  return wide ? launch_gemm_pair<KM_, F16_, 512>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream) \
+              : launch_gemm_pair<KM_, F16_, 256>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream)
+  if (!b_kmajor && dtype == 0) B200_PAIR_CASE(false, false);
+  if (!b_kmajor && dtype == 1) B200_PAIR_CASE(false, true);
+  if (b_kmajor && dtype == 0) B200_PAIR_CASE(true, false);
+  B200_PAIR_CASE(true, true);
+#undef B200_PAIR_CASE
 }
 
 // Clears the stream-K flags of every scratch set of the current device (ordered on `stream`).  A launch

@@ -132,7 +132,7 @@ def test_bf16_full_size_slab_and_properties(b200, oracle):
     c3 = _gemm(b200, "bf16", ad, bd, config=0, num_programs=37, group_m=3)
     assert torch.equal(c3, c)
     # different tile shapes (and the CTA-pair kernel) add the same k-slabs in the same order
-    for cfg in (1, 2):
+    for cfg in (1, 2, 3):
         assert torch.equal(_gemm(b200, "bf16", ad, bd, config=cfg), c)
     # checksum of checksums against the fp64 column/row sums: sum(C) = (1^T A)(B 1)
     lhs = c.double().sum().item()
@@ -313,4 +313,25 @@ def test_linear_with_bias_and_residual_epilogue(b200, oracle, dtype, m, n, k):
     launch.linear_bias_residual(ft, xd, wd, None, ft)
     torch.cuda.synchronize()
     assert torch.equal(fused, unfused)
+    _status_ok(b200)
+
+
+@pytest.mark.parametrize("m,n,k,layout", [(300, 520, 192, 0), (256, 512, 64, 1), (1000, 1104, 320, 1), (4096, 4096, 512, 0)])
+def test_wide_pair_tile_matches_oracle_and_the_other_configurations(b200, oracle, m, n, k, layout):
+    """The 256 x 512 CTA-pair tile (config 3): ragged edges in both layouts, and a shape whose partial last wave is split
+    along K (4096 x 4096: 128 tiles on 74 pairs)."""
+    a, b = workloads.gemm_bf16_inputs(m, n, k, config_index=50 + m % 7)
+    bd = (b.t().contiguous() if layout else b).cuda()
+    ad = a.cuda()
+    got = _gemm(b200, "bf16", ad, bd, layout=layout, config=3)
+    rows = slice(0, min(m, 48))
+    ref = oracle.cpu_gemm(a[rows].float().numpy(), b.float().numpy(), threads=0)
+    assert oracle.rel_frobenius(got[rows].float().cpu().numpy(), ref) <= BF16_TOL
+    assert not torch.isnan(got.float()).any()
+    other = _gemm(b200, "bf16", ad, bd, layout=layout, config=0)
+    if (m, n) == (4096, 4096):       # split-K partial sums: one bf16 rounding step at most
+        assert (got.float() - other.float()).abs().max().item() <= 2.0 ** -7 * other.float().abs().max().item()
+        assert torch.equal(got, _gemm(b200, "bf16", ad, bd, layout=layout, config=3))   # deterministic
+    else:
+        assert torch.equal(got, other)     # whole tiles add the same k slabs in the same order
     _status_ok(b200)
