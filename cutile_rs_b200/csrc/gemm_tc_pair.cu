@@ -19,7 +19,7 @@
 //
 //   warp 0      TMA producer (both CTAs); transaction bytes are counted on the leader's barrier
 //   warp 1      MMA issuer (leader CTA only) -- releases a stage in BOTH CTAs with two commits
-//   warps 2..5  epilogue of this CTA's 128 rows x 256 columns
+//   warps 2..   epilogue of this CTA's 128 rows: four warps per 256 columns (4 or 8 warps)
 #include <stdlib.h>
 
 #include <mutex>
@@ -37,7 +37,6 @@ __device__ long long g_trace_gemm_pair[8];
 #endif
 
 constexpr int P_BM = 128;   // rows per CTA (256 per pair)
-constexpr int P_THREADS = 192;
 
 // Two tile widths.  BN = 256: one 256x256 accumulator per tile, double-buffered (the epilogue of tile i overlaps
 // the main loop of tile i+1), 128-deep stages.  BN = 512: the pair's tile is 256 rows x 512 columns, i.e. two
@@ -53,6 +52,12 @@ struct PairCfg {
   static constexpr int BK = BN == 256 ? 128 : 64;  // k depth of a stage
   static constexpr int KH = BK / 64;               // 64-wide (128-byte) sub-blocks per stage
   static constexpr int STAGES = BN == 256 ? 3 : 4; // 192 KiB of operand ring per CTA either way
+  // Epilogue: every warp drains 256 columns of its Tensor-Memory lane quarter into packed 16-bit registers,
+  // hands the accumulator back, and only then stages and stores: EH warps per quarter (column halves).
+  static constexpr int EH = BN / 256;
+  static constexpr int EW = 4 * EH;                // epilogue warps
+  static constexpr int THREADS = 64 + 32 * EW;     // TMA warp, MMA warp, epilogue warps
+  static constexpr int NSB = 2 / EH;               // staging buffers per epilogue warp (32 KiB in total)
   static constexpr int A_BYTES = P_BM * BK * 2;
   static constexpr int BJ_BYTES = 128 * BK * 2;    // the 128 columns (rows, for a K-major B) this CTA feeds to ONE MMA
   static constexpr int B_BYTES = NB * BJ_BYTES;
@@ -60,7 +65,7 @@ struct PairCfg {
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + STAGES * A_BYTES;
   static constexpr int OFF_C = OFF_B + STAGES * B_BYTES;
-  static constexpr int OFF_BAR = OFF_C + 4 * 2 * C_WARP_BYTES;
+  static constexpr int OFF_BAR = OFF_C + EW * NSB * C_WARP_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 4;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
@@ -155,7 +160,7 @@ __device__ __forceinline__ bool wait_flag(const WaitCtx& ctx, const uint32_t* fl
 }
 
 template <bool B_KMAJOR, bool OUT_F16, int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(P_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int group_m,
                     uint32_t idesc, uint32_t* status, int sk_tiles, float* sk_partials,
@@ -187,7 +192,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + b * 8, 1);
-      mbar_init(bar_tempty + b * 8, 8);  // four epilogue warps from each CTA of the pair
+      mbar_init(bar_tempty + b * 8, 2 * L::EW);  // the epilogue warps of both CTAs of the pair
     }
     misc[1] = 0;
     fence_mbar_init();
@@ -312,30 +317,35 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // -------------------------------- epilogue ---------------------------------
+    // Warp w may read Tensor-Memory lanes 32 (w % 4) ..; with BN = 512 two warps share a lane quarter and take
+    // 256 columns each.
     const int q = warp & 3;
-    const uint32_t sCw = sC + q * (2 * L::C_WARP_BYTES);
+    const int ew = warp - 2;                 // 0 .. EW-1
+    const int half = ew >> 2;                // which 256 columns of the tile
+    constexpr int CW = 256;                  // columns per epilogue warp
+    const uint32_t sCw = sC + ew * (L::NSB * L::C_WARP_BYTES);
     const uint32_t tempty_leader = mapa_u32(bar_tempty, 0);
-    uint32_t it = 0;
+    uint32_t it = 0, nst = 0;
     bool ok = true;
     PairSched sched;
     sched.init(num_kb, sk_tiles, total_tiles, pair, num_pairs);
     int tile, kb0, kb1;
-    const int etid = threadIdx.x - 64;  // 0..127 inside the epilogue warps
+    const int etid = threadIdx.x - 64;  // 0 .. 32 EW - 1 inside the epilogue warps
     for (; ok && sched.next(tile, kb0, kb1); ++it) {
       int bm, bn;
       pair_tile_coords(tile, tiles_m, tiles_n, group_m, bm, bn);
-      const int m0 = bm * (2 * P_BM) + (int)rank * P_BM, n0 = bn * BN;
+      const int m0 = bm * (2 * P_BM) + (int)rank * P_BM, n0 = bn * BN + half * CW;
       const uint32_t buf = L::NACC == 2 ? (it & 1) : 0;
       if (!mbar_wait(wctx, bar_tfull + buf * 8, L::NACC == 2 ? ((it >> 1) & 1) : (it & 1), 4)) { ok = false; break; }
       tc_fence_after_sync();
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * CW;
       const int row = q * 32 + lane;
       if (kb1 < num_kb) {
         // ---- the share stops inside this tile: publish the fp32 partial, column-major so that the
         // 32 lanes of a warp write 128 contiguous bytes ----
-        float* slot = sk_partials + (size_t)blockIdx.x * L::SLOT_FLOATS;
+        float* slot = sk_partials + (size_t)blockIdx.x * L::SLOT_FLOATS + (size_t)(half * CW) * P_BM;
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = 0; c < CW / 32; ++c) {
           uint32_t v[32];
           tmem_ld_32x32b_x32(t_row + c * 32, v);
           tmem_wait_ld();
@@ -346,7 +356,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster_addr(tempty_leader + buf * 8);
         __threadfence();
-        named_bar_sync(1, 128);
+        named_bar_sync(1, 32 * L::EW);
         if (etid == 0) st_release_gpu(sk_flags + blockIdx.x, 1u);
         continue;
       }
@@ -365,41 +375,57 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         if (!ok) break;
       }
-#pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
+      // ---- pass 1: Tensor Memory -> packed 16-bit registers (fix-up partials added in fp32 first); then
+      // the accumulator goes back to the MMA thread, long before the stores below are done ----
+      uint32_t pk[CW / 2];
+#pragma unroll
+      for (int c = 0; c < CW / 64; ++c) {
         uint32_t v0[32], v1[32];
         tmem_ld_32x32b_x32(t_row + c * 64, v0);
         tmem_ld_32x32b_x32(t_row + c * 64 + 32, v1);
-        if (lane == 0) tma_store_wait_read<1>();
-        __syncwarp();
         tmem_wait_ld();
         for (int qq = q_first; qq <= q_last; ++qq) {
           if (sched.first_unit(qq) == sched.first_unit(qq + 1)) continue;
-          const float* part = sk_partials + (size_t)(2 * qq + (int)rank) * L::SLOT_FLOATS + row;
+          const float* part = sk_partials + (size_t)(2 * qq + (int)rank) * L::SLOT_FLOATS +
+                              (size_t)(half * CW) * P_BM + row;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             v0[i] = __float_as_uint(__uint_as_float(v0[i]) + __ldcg(part + (c * 64 + i) * P_BM));
             v1[i] = __float_as_uint(__uint_as_float(v1[i]) + __ldcg(part + (c * 64 + 32 + i) * P_BM));
           }
         }
-        // staging buffer by chunk parity: valid because every tile stores an EVEN number of chunks (4), so
-        // `wait_group.read 1` above has always drained the buffer chosen here; a variant that can store an
-        // odd number of chunks per tile must count committed stores instead
-        static_assert((BN / 64) % 2 == 0, "chunk-parity staging needs an even number of chunks per tile");
-        const uint32_t sbuf = sCw + (c & 1) * L::C_WARP_BYTES;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float a0 = __uint_as_float(v0[2 * i]), a1 = __uint_as_float(v0[2 * i + 1]);
+          const float b0 = __uint_as_float(v1[2 * i]), b1 = __uint_as_float(v1[2 * i + 1]);
+          pk[c * 32 + i] = OUT_F16 ? pack_f16x2(a0, a1) : pack_bf16x2(a0, a1);
+          pk[c * 32 + 16 + i] = OUT_F16 ? pack_f16x2(b0, b1) : pack_bf16x2(b0, b1);
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster_addr(tempty_leader + buf * 8);
+      if (q_last >= q_first) {
+        // every epilogue thread of this CTA has read the partials: clear their flags for the next launch
+        named_bar_sync(1, 32 * L::EW);
+        if (etid == 0)
+          for (int qq = q_first; qq <= q_last; ++qq)
+            if (sched.first_unit(qq) != sched.first_unit(qq + 1)) st_release_gpu(sk_flags + (2 * qq + (int)rank), 0u);
+      }
+      // ---- pass 2: registers -> swizzled staging -> TMA store, 64 columns at a time; the staging buffer is
+      // picked by a count of committed stores, so `wait_group.read NSB-1` has always drained it ----
+#pragma unroll
+      for (int c = 0; c < CW / 64; ++c) {
+        if (lane == 0) tma_store_wait_read<L::NSB - 1>();
+        __syncwarp();
+        const uint32_t sbuf = sCw + (nst % L::NSB) * L::C_WARP_BYTES;
+        ++nst;
         const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          const uint32_t* src = (j < 4) ? &v0[j * 8] : &v1[(j - 4) * 8];
-          uint32_t pk[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float lo = __uint_as_float(src[2 * e]), hi = __uint_as_float(src[2 * e + 1]);
-            pk[e] = OUT_F16 ? pack_f16x2(lo, hi) : pack_bf16x2(lo, hi);
-          }
           const uint32_t dst = row_addr + ((uint32_t)(j ^ (lane & 7)) << 4);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[0]),
-                       "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[c * 32 + j * 4]),
+                       "r"(pk[c * 32 + j * 4 + 1]), "r"(pk[c * 32 + j * 4 + 2]), "r"(pk[c * 32 + j * 4 + 3])
                        : "memory");
         }
         fence_proxy_async_smem();
@@ -408,16 +434,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tma_store_2d(&tmC, sbuf, n0 + c * 64, m0 + q * 32);
           tma_store_commit();
         }
-      }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_addr(tempty_leader + buf * 8);
-      if (q_last >= q_first) {
-        // every epilogue thread of this CTA has read the partials: clear their flags for the next launch
-        named_bar_sync(1, 128);
-        if (etid == 0)
-          for (int qq = q_first; qq <= q_last; ++qq)
-            if (sched.first_unit(qq) != sched.first_unit(qq + 1)) st_release_gpu(sk_flags + (2 * qq + (int)rank), 0u);
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
@@ -572,7 +588,7 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
   }
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
   const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, 2 * P_BM, 256);
-  kern<<<pairs * 2, P_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, group_m, idesc,
+  kern<<<pairs * 2, L::THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, group_m, idesc,
                                                    di->status, sk_tiles, sk ? sk->partials : nullptr,
                                                    sk ? sk->flags : nullptr);
   B200_CUDA_CHECK(cudaGetLastError());
