@@ -13,6 +13,8 @@
 #include "../../include/b200tile.h"
 #include <string.h>
 
+#include <mutex>
+
 #include "host_common.h"
 
 namespace {
@@ -27,6 +29,10 @@ struct HostPipe {
 };
 
 HostPipe g_pipes[64];
+// One pipe (two side streams, one set of events) per device, shared by every caller: the whole enqueue
+// sequence of a call holds the device's lock, so that two host threads cannot interleave their records
+// and waits on the same events.  The work itself is asynchronous; the lock is held for microseconds.
+std::mutex g_pipe_mu[64];
 
 int get_pipe(int ordinal, HostPipe** out) {
   HostPipe& p = g_pipes[ordinal];
@@ -73,35 +79,46 @@ extern "C" int b200tile_gemm_host(const char* dtype, int b_layout, const void* a
     slab_rows = ((m + kMaxSlabs - 1) / kMaxSlabs + 255) / 256 * 256;
     slabs = (m + slab_rows - 1) / slab_rows;
   }
+  std::lock_guard<std::mutex> lk(g_pipe_mu[di->ordinal]);
   HostPipe* p;
   if (int rc = get_pipe(di->ordinal, &p)) return rc;
 
-  // everything queued on the caller's stream so far comes first (it may still use the staging buffers)
-  B200_CUDA_CHECK(cudaEventRecord(p->start, s));
-  B200_CUDA_CHECK(cudaStreamWaitEvent(p->s_in, p->start, 0));
-  B200_CUDA_CHECK(cudaStreamWaitEvent(p->s_out, p->start, 0));
-  B200_CUDA_CHECK(cudaMemcpyAsync(b_dev, b_host, (size_t)n * k * es, cudaMemcpyHostToDevice, p->s_in));
-  B200_CUDA_CHECK(cudaEventRecord(p->b_up, p->s_in));
-  B200_CUDA_CHECK(cudaStreamWaitEvent(s, p->b_up, 0));
-  const int64_t ldb = b_layout ? k : n;
-  for (int i = 0; i < slabs; ++i) {
-    const int r0 = i * slab_rows;
-    const int rows = (m - r0) < slab_rows ? (m - r0) : slab_rows;
-    const size_t a_off = (size_t)r0 * k * es, c_off = (size_t)r0 * n * es;
-    B200_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(a_dev) + a_off, static_cast<const char*>(a_host) + a_off,
-                                    (size_t)rows * k * es, cudaMemcpyHostToDevice, p->s_in));
-    B200_CUDA_CHECK(cudaEventRecord(p->a_up[i], p->s_in));
-    B200_CUDA_CHECK(cudaStreamWaitEvent(s, p->a_up[i], 0));
-    if (int rc = b200tile_gemm(dtype, b_layout, static_cast<char*>(a_dev) + a_off, b_dev,
-                               static_cast<char*>(c_dev) + c_off, 1, rows, n, k, k, ldb, n, 0, 0, 0, 0, -1, 0, 0, s))
-      return rc;
-    B200_CUDA_CHECK(cudaEventRecord(p->c_ready[i], s));
-    B200_CUDA_CHECK(cudaStreamWaitEvent(p->s_out, p->c_ready[i], 0));
-    B200_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(c_host) + c_off, static_cast<char*>(c_dev) + c_off,
-                                    (size_t)rows * n * es, cudaMemcpyDeviceToHost, p->s_out));
-  }
+  // Whatever has been queued on the side streams when this function returns -- normally the whole pipeline,
+  // after an error a prefix of it -- is joined to the caller's stream, so that synchronising that stream always
+  // covers every copy that still touches the caller's buffers.
+  auto join = [&]() {
+    if (cudaEventRecord(p->b_up, p->s_in) == cudaSuccess) cudaStreamWaitEvent(s, p->b_up, 0);
+    if (cudaEventRecord(p->done, p->s_out) == cudaSuccess) cudaStreamWaitEvent(s, p->done, 0);
+  };
+  auto enqueue = [&]() -> int {
+    // everything queued on the caller's stream so far comes first (it may still use the staging buffers)
+    B200_CUDA_CHECK(cudaEventRecord(p->start, s));
+    B200_CUDA_CHECK(cudaStreamWaitEvent(p->s_in, p->start, 0));
+    B200_CUDA_CHECK(cudaStreamWaitEvent(p->s_out, p->start, 0));
+    B200_CUDA_CHECK(cudaMemcpyAsync(b_dev, b_host, (size_t)n * k * es, cudaMemcpyHostToDevice, p->s_in));
+    B200_CUDA_CHECK(cudaEventRecord(p->b_up, p->s_in));
+    B200_CUDA_CHECK(cudaStreamWaitEvent(s, p->b_up, 0));
+    const int64_t ldb = b_layout ? k : n;
+    for (int i = 0; i < slabs; ++i) {
+      const int r0 = i * slab_rows;
+      const int rows = (m - r0) < slab_rows ? (m - r0) : slab_rows;
+      const size_t a_off = (size_t)r0 * k * es, c_off = (size_t)r0 * n * es;
+      B200_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(a_dev) + a_off, static_cast<const char*>(a_host) + a_off,
+                                      (size_t)rows * k * es, cudaMemcpyHostToDevice, p->s_in));
+      B200_CUDA_CHECK(cudaEventRecord(p->a_up[i], p->s_in));
+      B200_CUDA_CHECK(cudaStreamWaitEvent(s, p->a_up[i], 0));
+      if (int rc = b200tile_gemm(dtype, b_layout, static_cast<char*>(a_dev) + a_off, b_dev,
+                                 static_cast<char*>(c_dev) + c_off, 1, rows, n, k, k, ldb, n, 0, 0, 0, 0, -1, 0, 0, s))
+        return rc;
+      B200_CUDA_CHECK(cudaEventRecord(p->c_ready[i], s));
+      B200_CUDA_CHECK(cudaStreamWaitEvent(p->s_out, p->c_ready[i], 0));
+      B200_CUDA_CHECK(cudaMemcpyAsync(static_cast<char*>(c_host) + c_off, static_cast<char*>(c_dev) + c_off,
+                                      (size_t)rows * n * es, cudaMemcpyDeviceToHost, p->s_out));
+    }
+    return B200_OK;
+  };
+  const int rc = enqueue();
   // the caller's stream ends after the last download: synchronising it covers the whole call
-  B200_CUDA_CHECK(cudaEventRecord(p->done, p->s_out));
-  B200_CUDA_CHECK(cudaStreamWaitEvent(s, p->done, 0));
-  return B200_OK;
+  join();
+  return rc;
 }

@@ -55,6 +55,9 @@ template <int BN, bool FP4 = true, bool A_DIRECT = false, int AROWS = 128>
 struct Fp4Cfg {
   static_assert(AROWS == 128 || (AROWS % 8 == 0 && AROWS * 128 + BN * 128 >= 128 * 128),
                 "a short A tile must be followed by enough of the B tile for the MMA's 128-row read");
+  // The rows past a short A tile are bytes of the B tile multiplied by zero scales: harmless for E2M1, which has
+  // no NaN or infinity encodings; an E4M3 operand (MXFP8) could turn 0 x NaN into NaN in those accumulator rows.
+  static_assert(AROWS == 128 || FP4, "the short A tile is only valid for operand types without NaN / Inf encodings");
   static constexpr int CHUNKS = (BN + 127) / 128;            // 128-row scale blocks per B tile
   static constexpr int KQ_PER_STAGE = FP4 ? 4 : 1;           // scale blocks along K per stage
   static constexpr int STAGES_ = AROWS < 128 ? ((BN <= 128) ? 9 : (BN <= 192 ? 6 : 5))

@@ -104,3 +104,25 @@ def test_prepared_weight_scales_give_the_same_bits(b200, config, m, n, k):
         assert torch.equal(z.storage, want)
     with pytest.raises(Exception, match="config"):
         launch.linear_nvfp4_prepared(z, xt, yt, api.from_torch(xs.cuda()), prepared, ga * gb, config=-1)
+
+
+@pytest.mark.parametrize("m", [1, 31, 32, 33])
+def test_decode_sized_m_never_stores_rows_past_m(b200, oracle, m):
+    """M <= 32 takes the short A tile (the tensor core still multiplies 128 rows; those past the tile are bytes of the
+    weight tile under zero scales): nothing of them may reach memory.  The output lives inside a larger NaN-filled
+    buffer whose rows past M must stay NaN."""
+    n, k = 384, 512
+    a, b = workloads.gemm_normal_inputs(m, n, k, config_index=12)
+    xp, xs, ga = quant.quant_nvfp4(a)
+    yp, ys, gb = quant.quant_nvfp4(b)
+    big = torch.full((m + 130, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    z = api.from_torch(big[:m])
+    launch.linear_nvfp4(z, api.from_torch(xp.cuda(), "f4e2m1fnx2"), api.from_torch(yp.cuda(), "f4e2m1fnx2"),
+                        api.from_torch(xs.cuda()), api.from_torch(ys.cuda()), ga * gb)
+    torch.cuda.synchronize()
+    ref = oracle.cpu_gemm_nt(oracle.dequant_nvfp4(xp.numpy(), xs.numpy()), oracle.dequant_nvfp4(yp.numpy(), ys.numpy()),
+                             alpha=ga * gb, threads=0)
+    got = big[:m].float().cpu().numpy()
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= FP4_TOL
+    assert torch.isnan(big[m:]).all()
