@@ -812,10 +812,11 @@ def run_gpu_arm(args):
     y = api.copy_host_to_device(b_host)
     z = api.zeros([M, n_local], "bf16")
     # CTA pairs (num_cta_in_cga = 2, the reference's published cluster setting) on the 256 x 512 tile: two N = 256
-    # MMAs per k-step share the A operand, three quarters of the 256 x 256 tile's bytes per FLOP.  Shards too narrow
-    # to fill one wave of 512-wide tiles (8192 x 1024 at eight GPUs) take the 256 x 256 tile, which the pair kernel
-    # splits along K over all pairs (stream-K).
-    bm, bn = 256, (512 if (n_local // 512) * (M // 256) >= 74 else 256)
+    # MMAs per k-step share the A operand, three quarters of the 256 x 256 tile's bytes per FLOP.  Shards whose
+    # 512-wide tiles do not fill whole waves of the 74 pairs (8192 x 4096 / 2048 / 1024 at 2 / 4 / 8 GPUs) take the
+    # 256 x 256 tile, whose partial last wave the pair kernel splits along K over all pairs (stream-K).
+    wide_tiles = (n_local // 512) * (M // 256)
+    bm, bn = 256, (512 if wide_tiles / (-(-wide_tiles // 74) * 74) >= 0.95 else 256)
     generics = ["bf16", str(bm), str(bn), "64"]
     opts = launch.CompileOptions(num_cta_in_cga=2, occupancy=1)
 

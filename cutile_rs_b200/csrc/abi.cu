@@ -227,7 +227,9 @@ static int default_gemm_config(int m, int n, int k) {
   const double cost0 = (double)cdiv(cdiv(m, 128) * cdiv(n, 256), sms) * 1.0 / 0.92;
   const double cost1 = (double)cdiv(cdiv(m, 128) * cdiv(n, 128), sms) * 0.5 / 0.72;
   const double cost2 = pair_waves(cdiv(m, 256) * cdiv(n, 256), 128) * 1.0 / 1.0;
-  const double cost3 = pair_waves(cdiv(m, 256) * cdiv(n, 512), 64) * 2.0 / 1.036;
+  // the 512-wide tile is only taken in whole waves: its K-split fix-up (256 KiB of partials per CTA) costs more
+  // than it recovers (8192 x 1024 x 8192: 1182 TFLOP/s against 1369 for the 256-wide tile with its K split)
+  const double cost3 = (double)cdiv(cdiv(m, 256) * cdiv(n, 512), sms / 2) * 2.0 / 1.036;
   if (cost3 <= cost2 && cost3 <= cost0 && cost3 <= cost1) return 3;
   if (cost2 <= cost0 && cost2 <= cost1) return 2;
   return cost0 <= cost1 ? 0 : 1;

@@ -576,12 +576,15 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
   int sk_tiles = 0;
   SkScratch* sk = nullptr;
   const int num_kb = (K + P_BK - 1) / P_BK;
-  if (max_ctas <= 0 && streamk_enabled() && tiles > all_pairs && tiles % all_pairs != 0 && num_kb >= 4) {
+  // Also when the tiles do not even fill one wave (at least half of it): all of them are then split along K.
+  const bool partial_last = tiles > all_pairs && tiles % all_pairs != 0;
+  const bool under_one = tiles < all_pairs && 2 * tiles >= all_pairs;
+  if (max_ctas <= 0 && streamk_enabled() && (partial_last || under_one) && num_kb >= 4) {
     const int waves = (tiles + all_pairs - 1) / all_pairs;
     if ((double)tiles / ((double)waves * all_pairs) < 0.95) {
       sk = sk_scratch_for(di->ordinal, 2 * all_pairs, stream);
       if (sk) {
-        sk_tiles = tiles % all_pairs;
+        sk_tiles = tiles % all_pairs;   // == tiles when they fill less than one wave
         pairs = all_pairs;
       }
     }
