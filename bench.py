@@ -41,10 +41,11 @@ if ROOT not in sys.path:
 METRIC = "TFLOP/s (GEMM 8192^3 bf16, fp32 accumulate)"
 M = N = K = 8192
 FALLBACK_BF16_TFLOPS = 1590.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tc_pair_kernel: 316.7 MB measured
-# by ncu on a 4096x4096x8192 case (256 tiles), scaled by tiles processed to the 1024 tiles of
-# 8192^3 (profiles/gemm_bf16_pair.md).  The full-size launch is not captured under ncu.
-GEMM_DRAM_TRAFFIC_BYTES = int(316.7e6 * 4)
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of gemm_tc_pair_kernel<., ., 512> on the full-size 8192^3
+# problem: 984.2 MB + 146.2 MB, a one-pass ncu capture of two launches of `bench.py --case gemm --m 8192 --n 8192
+# --k 8192 --config 3` (profiles/gemm_bf16_pair.md); the 256-wide tile's figure, scaled from a quarter-size capture,
+# was 1.27 GB.
+GEMM_DRAM_TRAFFIC_BYTES = 984_226_816 + 146_217_728
 
 
 SUSTAINED_BF16_TFLOPS = None
@@ -856,7 +857,7 @@ def run_gpu_arm(args):
 
     # ---- the same launch repeated for about two seconds: the rate under the power cap (the timed region above
     # is a burst of a few milliseconds) ----
-    n_sus = int(min(max(2000.0 / ms_per_step, 100), 20000))
+    n_sus = 20 if args.no_sustained else int(min(max(2000.0 / ms_per_step, 100), 20000))
     sampler2 = ClockSampler(local_rank)
     if rank == 0:
         sampler2.start()
@@ -1200,6 +1201,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-fmha", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true",
+                    help="shorten the two-second repetition of the headline launch to 20 launches (launch-list captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
