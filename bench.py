@@ -436,25 +436,24 @@ def bench_nvfp4(ctx, by, cpu_by, e2e_by, do_cpu):
         zp = [api.from_torch(z4).partition([16, 128])]
         alpha = gx * gy
 
-        def f4step():
-            (zp[0], *_r) = launch.linear_tile(zp[0], x, y, sx, sy, alpha).async_on(stream)
+        # The generic call is captured once and replayed (CUDA graph): the launcher mirror's Python costs ~100 us per
+        # call, more than the kernel at decode sizes and on the shards of a multi-GPU run.
+        cap = torch.cuda.Stream()
+        cap.wait_stream(stream)
+        (zp[0], *_r) = launch.linear_tile(zp[0], x, y, sx, sy, alpha).sync_on(cap)   # the capture stream's scratch
+        graph = [launch.linear_tile(zp[0], x, y, sx, sy, alpha).graph_on(cap)]
         if m4 <= 128:
-            # decode: launch-bound from Python, so the call is captured once and replayed (CUDA graph), which is how
-            # a serving loop issues it.  First with the per-call weight-scale pre-pass, then with the weight scales
-            # (constants of the model) laid out once and registered: the same generic call then runs one kernel.
-            cap = torch.cuda.Stream()
-            cap.wait_stream(stream)
-            (zp[0], *_r) = launch.linear_tile(zp[0], x, y, sx, sy, alpha).sync_on(cap)   # the capture stream's scratch
-            graph = launch.linear_tile(zp[0], x, y, sx, sy, alpha).graph_on(cap)
-            extra["nvfp4_m16_unregistered_weight_scales_us"] = ctx.timed(lambda: graph.launch(), 20) * 1e3
+            # decode: first with the per-call weight-scale pre-pass, then with the weight scales (constants of the
+            # model) laid out once and registered: the same generic call then runs one kernel.
+            extra["nvfp4_m16_unregistered_weight_scales_us"] = ctx.timed(lambda: graph[0].launch(), 20) * 1e3
             prep = launch.nvfp4_prepare_weight_scales(sy, nl, k4, 0)
             launch.nvfp4_register_weight_scales(sy, nl, k4, prep, 0)
             torch.cuda.synchronize()
-            graph = launch.linear_tile(zp[0], x, y, sx, sy, alpha).graph_on(cap)
-
-            def f4step():
-                graph.launch()
+            graph[0] = launch.linear_tile(zp[0], x, y, sx, sy, alpha).graph_on(cap)
             ctx.launches += 23 * 2 + 3
+
+        def f4step():
+            graph[0].launch()
         ms = ctx.timed(f4step, 20 if m4 <= 128 else 10)
         ctx.launches += 23 if m4 <= 128 else 13 * 2
         flops = workloads.gemm_flops(m4, n4, k4)
@@ -466,7 +465,8 @@ def bench_nvfp4(ctx, by, cpu_by, e2e_by, do_cpu):
                              how="generic linear_tile call, registered weight scales, CUDA-graph replay")
         else:
             tf = flops / (ms * 1e-3) / 1e12 / world
-            by[name] = _roof("tensor", tf, NOMINAL_FP4, "TFLOP/s", ms, "nominal dense fp4 = 4 x 2250 (no measured fp4 peak)")
+            by[name] = _roof("tensor", tf, NOMINAL_FP4, "TFLOP/s", ms, "nominal dense fp4 = 4 x 2250 (no measured fp4 peak)",
+                             how="generic linear_tile call (scale pre-pass + GEMM), CUDA-graph replay")
         hx, hxs, hy, hys, hz = xp.cpu().pin_memory(), xsc.cpu().pin_memory(), yp.cpu().pin_memory(), ysc.cpu().pin_memory(), _pin_like(z4)
 
         def estep():
@@ -482,7 +482,7 @@ def bench_nvfp4(ctx, by, cpu_by, e2e_by, do_cpu):
         e2e_by[name] = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ems,
                         "h2d_bytes_per_step": world * (hx.numel() + hxs.numel()) + (0 if m4 <= 128 else n4 * k4 // 2 + n4 * k4 // 16),
                         "d2h_bytes_per_step": m4 * n4 * 2,
-                        "note": "weights resident, CUDA-graph replay" if m4 <= 128 else "all operands uploaded"}
+                        "note": "weights resident, CUDA-graph replay" if m4 <= 128 else "all operands uploaded, CUDA-graph replay"}
         if do_cpu:
             from oracle import oracle
             rows, cols = min(m4, 64), 2048
