@@ -721,28 +721,32 @@ def bench_single_gpu_yardsticks(ctx, step, flops, x, y, n_local):
     ones_b = torch.ones(K, N, dtype=torch.float16, device=dev)
     ones_c = torch.empty(M, N, dtype=torch.float16, device=dev)
 
-    def ones_step():
-        _lib.check(lib.b200tile_gemm(b"f16", 0, ones_a.data_ptr(), ones_b.data_ptr(), ones_c.data_ptr(), 1, M, N, K, K, N,
-                                     N, 0, 0, 0, 0, 3, 8, 0, stream.cuda_stream))
     # 5 warm-up launches, median over 10 samples of 3 back-to-back launches between stream syncs, host clock
-    # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322)
-    for _ in range(5):
-        ones_step()
-    torch.cuda.synchronize()
-    samples = []
-    for _ in range(10):
-        t0 = time.perf_counter()
-        for _ in range(3):
+    # (cutile-benchmarks/paper/sec5_exp1_safety_overhead/rust/gemm/src/main.rs:629-631,1289-1322); once with
+    # fp32 accumulators and once with the f16 accumulators of the published kernel (benches/gemm.rs:20-41)
+    for key, cfg, acc in (("gemm_f16_ones_published_protocol", 3, "fp32"),
+                          ("gemm_f16_ones_published_protocol_f16_accumulators", 4, "f16, as in the published run")):
+        def ones_step():
+            _lib.check(lib.b200tile_gemm(b"f16", 0, ones_a.data_ptr(), ones_b.data_ptr(), ones_c.data_ptr(), 1, M, N, K,
+                                         K, N, N, 0, 0, 0, 0, cfg, 8, 0, stream.cuda_stream))
+        ones_c.fill_(float("nan"))
+        for _ in range(5):
             ones_step()
         torch.cuda.synchronize()
-        samples.append((time.perf_counter() - t0) / 3)
-    samples.sort()
-    med = 0.5 * (samples[4] + samples[5])
-    out["gemm_f16_ones_published_protocol"] = {
-        "tflops": flops / med / 1e12, "median_us": med * 1e6, "published_reference_tflops": 2068.88,
-        "result_is_k_everywhere": bool((ones_c[::997, ::991].float() == float(K)).all().item()),
-        "tile": "256x512 per CTA pair", "accumulator": "fp32 here, f16 in the published run"}
-    ctx.launches += 35
+        samples = []
+        for _ in range(10):
+            t0 = time.perf_counter()
+            for _ in range(3):
+                ones_step()
+            torch.cuda.synchronize()
+            samples.append((time.perf_counter() - t0) / 3)
+        samples.sort()
+        med = 0.5 * (samples[4] + samples[5])
+        out[key] = {
+            "tflops": flops / med / 1e12, "median_us": med * 1e6, "published_reference_tflops": 2068.88,
+            "result_is_k_everywhere": bool((ones_c[::997, ::991].float() == float(K)).all().item()),
+            "tile": "256x512 per CTA pair", "accumulator": acc}
+        ctx.launches += 35
     del ones_a, ones_b, ones_c
     a_t, b_t, c_t = x.storage, y.storage, torch.empty((M, n_local), dtype=torch.bfloat16, device=dev)
     for _ in range(3):          # library initialisation and heuristics stay outside the timing
@@ -1016,15 +1020,16 @@ def run_case(argv) -> int:
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if args.kernel == "gemm":
         m, n, k = args.m, args.n, args.k
-        a = (torch.randn(m, k, device="cuda", generator=g) / math.sqrt(k)).bfloat16()
-        b = (torch.randn((n, k) if args.layout else (k, n), device="cuda", generator=g) / math.sqrt(k)).bfloat16()
+        tdt, name = (torch.float16, b"f16") if args.config == 4 else (torch.bfloat16, b"bf16")   # config 4: f16 accumulators
+        a = (torch.randn(m, k, device="cuda", generator=g) / math.sqrt(k)).to(tdt)
+        b = (torch.randn((n, k) if args.layout else (k, n), device="cuda", generator=g) / math.sqrt(k)).to(tdt)
         if args.ones:   # the published benchmark's inputs: far fewer bit flips, so less power and higher clocks
             a.fill_(1.0)
             b.fill_(1.0)
-        c = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
+        c = torch.empty(m, n, dtype=tdt, device="cuda")
 
         def run():
-            _lib.check(lib.b200tile_gemm(b"bf16", args.layout, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n,
+            _lib.check(lib.b200tile_gemm(name, args.layout, a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, m, n,
                                          k, k, b.stride(0), n, 0, 0, 0, 0, args.config, args.group_m, 0, stream.cuda_stream))
         flops = 2.0 * m * n * k
     elif args.kernel == "nvfp4":

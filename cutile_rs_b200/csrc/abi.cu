@@ -157,6 +157,12 @@ static const b200tile_config kGemmTcConfigs[] = {
     {2, 256, 256, 64, 6, 2, 1},
     {3, 256, 512, 64, 4, 2, 1},
 };
+// f16 adds id 4: the 256 x 512 pair tile with f16 accumulators, the accumulator type of the reference's
+// benchmark kernel (cutile-benchmarks/benches/gemm.rs:20-41: `mma(x, y, z)` with z a Tile<T>)
+static const b200tile_config kGemmTcConfigsF16[] = {
+    {0, 128, 256, 64, 4, 1, 1}, {1, 128, 128, 64, 6, 1, 1}, {2, 256, 256, 64, 6, 2, 1},
+    {3, 256, 512, 64, 4, 2, 1}, {4, 256, 512, 64, 4, 2, 1},
+};
 static const b200tile_config kGemmF32Configs[] = {
     {0, 64, 64, 16, 1, 1, 1},
 };
@@ -174,9 +180,12 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
     if (!strcmp(dtype, "f32")) {
       tab = kGemmF32Configs;
       n = (int)(sizeof(kGemmF32Configs) / sizeof(kGemmF32Configs[0]));
-    } else if (!strcmp(dtype, "bf16") || !strcmp(dtype, "f16")) {
+    } else if (!strcmp(dtype, "bf16")) {
       tab = kGemmTcConfigs;
       n = (int)(sizeof(kGemmTcConfigs) / sizeof(kGemmTcConfigs[0]));
+    } else if (!strcmp(dtype, "f16")) {
+      tab = kGemmTcConfigsF16;
+      n = (int)(sizeof(kGemmTcConfigsF16) / sizeof(kGemmTcConfigsF16[0]));
     }
   }
   static const b200tile_config kFmhaConfigs[] = {{0, 128, 128, 0, 2, 1, 1}, {1, 128, 128, 0, 4, 2, 1}};
@@ -274,12 +283,14 @@ int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b,
     return set_error(B200TILE_ERR_UNSUPPORTED,
                      "gemm(%s): accumulate-into-C is only provided for f32", dtype);
   if (config < 0) config = default_gemm_config(m, n, k);
+  if (config > 4 || (config == 4 && dt != 1))
+    return set_error(B200TILE_ERR_UNSUPPORTED, "gemm(%s): unknown config %d", dtype, config);
   for (int bi = 0; bi < batch; ++bi) {
     const char* ab = static_cast<const char*>(a) + (int64_t)bi * stride_a * 2;
     const char* bb = static_cast<const char*>(b) + (int64_t)bi * stride_b * 2;
     char* cb = static_cast<char*>(c) + (int64_t)bi * stride_c * 2;
     int rc = config >= 2
-                 ? b200_gemm_pair_dispatch(dt, b_layout ? 1 : 0, config == 3 ? 1 : 0, ab, bb, cb, m, n, k, lda, ldb,
+                 ? b200_gemm_pair_dispatch(dt, b_layout ? 1 : 0, config - 2, ab, bb, cb, m, n, k, lda, ldb,
                                            ldc, group_size_m, num_programs, stream)
                  : b200_gemm_tc_dispatch(dt, b_layout ? 1 : 0, config, ab, bb, cb, m, n, k, lda,
                                          ldb, ldc, group_size_m, num_programs, stream);

@@ -159,7 +159,7 @@ __device__ __forceinline__ bool wait_flag(const WaitCtx& ctx, const uint32_t* fl
   return false;
 }
 
-template <bool B_KMAJOR, bool OUT_F16, int BN>
+template <bool B_KMAJOR, bool OUT_F16, int BN, bool ACC16>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, int M, int N, int K, int group_m,
@@ -340,7 +340,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after_sync();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + half * CW;
       const int row = q * 32 + lane;
-      if (kb1 < num_kb) {
+      if (!ACC16 && kb1 < num_kb) {
         // ---- the share stops inside this tile: publish the fp32 partial, column-major so that the
         // 32 lanes of a warp write 128 contiguous bytes ----
         float* slot = sk_partials + (size_t)blockIdx.x * L::SLOT_FLOATS + (size_t)(half * CW) * P_BM;
@@ -378,6 +378,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // ---- pass 1: Tensor Memory -> packed 16-bit registers (fix-up partials added in fp32 first); then
       // the accumulator goes back to the MMA thread, long before the stores below are done ----
       uint32_t pk[CW / 2];
+      if constexpr (ACC16) {
+        // 16-bit accumulators: one value per Tensor-Memory column; the packing load delivers two adjacent
+        // columns per register, which is already the output format
+#pragma unroll
+        for (int c = 0; c < CW / 64; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32_pack16(t_row + c * 64, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[c * 32 + i] = v[i];
+        }
+      } else {
 #pragma unroll
       for (int c = 0; c < CW / 64; ++c) {
         uint32_t v0[32], v1[32];
@@ -401,6 +413,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           pk[c * 32 + i] = OUT_F16 ? pack_f16x2(a0, a1) : pack_bf16x2(a0, a1);
           pk[c * 32 + 16 + i] = OUT_F16 ? pack_f16x2(b0, b1) : pack_bf16x2(b0, b1);
         }
+      }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -533,7 +546,7 @@ bool streamk_enabled() {
 }
 }  // namespace
 
-template <bool B_KMAJOR, bool OUT_F16, int BN>
+template <bool B_KMAJOR, bool OUT_F16, int BN, bool ACC16 = false>
 static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N, int K, int64_t lda,
                             int64_t ldb, int64_t ldc, int group_m, int max_ctas,
                             cudaStream_t stream) {
@@ -558,7 +571,8 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
   if ((rc = b200h::encode_tmap_2d(&tmC, dt, 2, C, (uint64_t)N, (uint64_t)M, (uint64_t)ldc * 2, 64,
                                   32, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  auto kern = gemm_tc_pair_kernel<B_KMAJOR, OUT_F16, BN>;
+  static_assert(!ACC16 || OUT_F16, "16-bit accumulators exist for f16 only");
+  auto kern = gemm_tc_pair_kernel<B_KMAJOR, OUT_F16, BN, ACC16>;
   static b200h::DeviceOnce attr_done;
   if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(
@@ -579,7 +593,8 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
   // Also when the tiles do not even fill one wave (at least half of it): all of them are then split along K.
   const bool partial_last = tiles > all_pairs && tiles % all_pairs != 0;
   const bool under_one = tiles < all_pairs && 2 * tiles >= all_pairs;
-  if (max_ctas <= 0 && streamk_enabled() && (partial_last || under_one) && num_kb >= 4) {
+  // (f16 accumulators: whole tiles only, the stream-K partials are fp32)
+  if (!ACC16 && max_ctas <= 0 && streamk_enabled() && (partial_last || under_one) && num_kb >= 4) {
     const int waves = (tiles + all_pairs - 1) / all_pairs;
     if ((double)tiles / ((double)waves * all_pairs) < 0.95) {
       sk = sk_scratch_for(di->ordinal, 2 * all_pairs, stream);
@@ -590,7 +605,7 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
     }
   }
   const uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
-  const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, 2 * P_BM, 256);
+  const uint32_t idesc = make_idesc(fmt, fmt, 0, B_KMAJOR ? 0 : 1, 2 * P_BM, 256, ACC16 ? 0 : 1);
   kern<<<pairs * 2, L::THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, M, N, K, group_m, idesc,
                                                    di->status, sk_tiles, sk ? sk->partials : nullptr,
                                                    sk ? sk->flags : nullptr);
@@ -600,11 +615,17 @@ static int launch_gemm_pair(const void* A, const void* B, void* C, int M, int N,
 
 }  // namespace b200
 
-// wide = 0: 256 x 256 tiles per CTA pair; wide = 1: 256 x 512 (two N = 256 MMAs per k-step sharing A)
+// wide = 0: 256 x 256 tiles per CTA pair; wide = 1: 256 x 512 (two N = 256 MMAs per k-step sharing A);
+// wide = 2: the 256 x 512 tile with f16 accumulators (f16 operands only)
 int b200_gemm_pair_dispatch(int dtype, int b_kmajor, int wide, const void* A, const void* B, void* C, int M,
                             int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int group_m,
                             int max_ctas, cudaStream_t stream) {
   using namespace b200;
+  if (wide == 2) {
+    if (dtype != 1) return b200h::set_error(B200_ERR_UNSUPPORTED, "gemm: f16 accumulators need f16 operands");
+    return b_kmajor ? launch_gemm_pair<true, true, 512, true>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream)
+                    : launch_gemm_pair<false, true, 512, true>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream);
+  }
 #define B200_PAIR_CASE(KM_, F16_)                                                                          \
   return wide ? launch_gemm_pair<KM_, F16_, 512>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream) \
               : launch_gemm_pair<KM_, F16_, 256>(A, B, C, M, N, K, lda, ldb, ldc, group_m, max_ctas, stream)

@@ -124,7 +124,10 @@ B200TILE_API int b200tile_prepare(const char* kernel, const char* const* generic
  *               (tensor cores, fp32 accumulation, output rounded to the input type)
  *   b_layout    0: B is [K,N] (reference GEMM), 1: B is [N,K] (reference linear_tile, "NT")
  *   accumulate  0: C = A*B, 1: C = C + A*B (the `load_tile_mut` form; f32 only)
- *   config      id from b200tile_query_configs, or -1 for the default
+ *   config      id from b200tile_query_configs, or -1 for the default.  Accumulation is fp32 except for
+ *               id 4 (f16 only): f16 accumulators, the arithmetic of the reference's benchmark kernel,
+ *               whose `mma(x, y, z)` accumulates in a Tile<T> (cutile-benchmarks/benches/gemm.rs:20-41);
+ *               never chosen by default
  *   group_size_m  grouped-M tile order (main.rs:53-66); <=0 selects 8
  *   num_programs  persistent grid size; <=0 selects min(SMs, tiles) */
 B200TILE_API int b200tile_gemm(const char* dtype, int b_layout, const void* a, const void* b, void* c,

@@ -335,3 +335,43 @@ def test_wide_pair_tile_matches_oracle_and_the_other_configurations(b200, oracle
     else:
         assert torch.equal(got, other)     # whole tiles add the same k slabs in the same order
     _status_ok(b200)
+
+
+@pytest.mark.parametrize("layout", [0, 1])
+def test_f16_accumulators_config4(b200, oracle, layout):
+    """Config 4 accumulates in f16 like the reference's benchmark kernel (cutile-benchmarks/benches/gemm.rs:20-41:
+    `mma(tile_x, tile_y, tile_z)` with `tile_z: Tile<T>`).  Integer data whose partial sums all fit f16's 11-bit
+    significand make the result independent of the order of accumulation: bit-exact against the oracle."""
+    m, n, k = 520, 1304, 512
+    # (1) position pattern: C[i, j] = (i % 4 + 1) * (j % 512), every row and column of the tile told apart
+    a = torch.zeros((m, k), dtype=torch.float16)
+    a[:, 0] = (torch.arange(m) % 4 + 1).to(torch.float16)
+    b = torch.zeros((k, n), dtype=torch.float16)
+    b[0] = (torch.arange(n) % 512).to(torch.float16)
+    bd = (b.t().contiguous() if layout else b).cuda()
+    got = _gemm(b200, "f16", a.cuda(), bd, layout=layout, config=4).cpu()
+    want = ((torch.arange(m) % 4 + 1)[:, None] * (torch.arange(n) % 512)[None, :]).to(torch.float16)
+    assert torch.equal(got, want)
+    # (2) random small integers over the whole K: |partial sums| <= 4 * 512 = 2048, all exact in f16
+    g = torch.Generator().manual_seed(workloads.SEED_BASE + 77)
+    a = torch.randint(-2, 3, (m, k), generator=g).to(torch.float16)
+    b = torch.randint(-2, 3, (k, n), generator=g).to(torch.float16)
+    bd = (b.t().contiguous() if layout else b).cuda()
+    got = _gemm(b200, "f16", a.cuda(), bd, layout=layout, config=4).cpu()
+    ref = oracle.cpu_gemm(a.float().numpy(), b.float().numpy(), threads=0)
+    assert np.array_equal(got.float().numpy(), ref)
+    # (3) normal data: f16 rounding of the running sums stays far inside the 16-bit tolerance
+    a, bt = workloads.gemm_normal_inputs(m, n, k, config_index=9)
+    a, b = a.to(torch.float16), bt.t().contiguous().to(torch.float16)
+    bd = (b.t().contiguous() if layout else b).cuda()
+    got = _gemm(b200, "f16", a.cuda(), bd, layout=layout, config=4)
+    ref = oracle.cpu_gemm(a[:48].float().numpy(), b.float().numpy(), threads=0)
+    assert oracle.rel_frobenius(got[:48].float().cpu().numpy(), ref) <= BF16_TOL
+    assert not torch.isnan(got.float()).any()
+    # only f16 has them
+    with pytest.raises(_lib.B200TileError, match="unknown config 4"):
+        _gemm(b200, "bf16", a.bfloat16().cuda(), bd.bfloat16(), layout=layout, config=4)
+    cfgs = (_lib.ConfigC * 8)()
+    assert b200.b200tile_query_configs(b"gemm", b"f16", cfgs, 8) == 5 and cfgs[4].id == 4
+    assert b200.b200tile_query_configs(b"gemm", b"bf16", cfgs, 8) == 4
+    _status_ok(b200)
