@@ -496,6 +496,22 @@ def bench_nvfp4(ctx, by, cpu_by, e2e_by, do_cpu):
                             "sample": f"dequantise + cpu_gemm port on C[0:{rows}, 0:{cols}], K={k4}, {dt:.1f} s"}
         if m4 <= 128:
             launch.nvfp4_unregister_weight_scales(sy)
+    # MXFP4 (the same packed operands with power-of-two scales per 32 elements) at M = 4096, typed entry point
+    m4 = 4096
+    xq, xqs = quant.quant_mxfp4(torch.randn(m4, k4, device=dev, generator=g))
+    yq, yqs = quant.quant_mxfp4(torch.randn(nl, k4, device=dev, generator=g))
+    zq = torch.empty(m4, nl, dtype=torch.bfloat16, device=dev)
+    need = lib.b200tile_linear_mxfp4_workspace_bytes(m4, nl, k4)
+    wsq = torch.empty(need, dtype=torch.uint8, device=dev)
+
+    def mx4step():
+        _lib.check(lib.b200tile_linear_mxfp4(xq.data_ptr(), yq.data_ptr(), xqs.data_ptr(), yqs.data_ptr(), zq.data_ptr(),
+                                             b"bf16", m4, nl, k4, k4 // 2, k4 // 2, nl, k4 // 32, k4 // 32, 1.0,
+                                             wsq.data_ptr(), need, stream.cuda_stream))
+    msq = ctx.timed(mx4step, 10)
+    ctx.launches += 13 * 3
+    tfq = workloads.gemm_flops(m4, n4, k4) / (msq * 1e-3) / 1e12 / world
+    extra["gemm_mxfp4_4096x14336x4096"] = {"tflops_per_gpu": tfq, "ms": msq, "frac_of_nominal_9000": tfq / NOMINAL_FP4}
     return extra
 
 

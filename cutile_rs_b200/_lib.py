@@ -106,6 +106,10 @@ SIGNATURES = {
     "b200tile_linear_mxfp8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p, c_int,
                                       c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                       c_void_p, c_uint64, c_void_p]),
+    "b200tile_linear_mxfp4_workspace_bytes": (c_uint64, [c_int, c_int, c_int]),
+    "b200tile_linear_mxfp4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p, c_int,
+                                      c_int, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
+                                      c_void_p, c_uint64, c_void_p]),
     "b200tile_linear_nvfp4_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_char_p,
                                              c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64,
                                              c_int64, c_float, c_int, c_void_p]),

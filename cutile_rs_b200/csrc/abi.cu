@@ -79,6 +79,10 @@ size_t b200_mxfp8_scratch_bytes(int M, int N, int K);
 int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
                              int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                              int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
+size_t b200_mxf4_scratch_bytes(int M, int N, int K);
+int b200_gemm_mxf4_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
+                            int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                            int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
 
 int b200_fmha_decode_dispatch(int dtype, int head_dim, const void* q, const void* k, const void* v, void* att,
                               float* lse, void* out, const uint32_t* pos, int kv_heads, int group, int kv_cap,
@@ -725,6 +729,47 @@ int b200tile_linear_mxfp8(const void* x, const void* y, const void* x_scales, co
 }
 
 // ---------------------------------------------------------------------------
+// Typed MXFP4 entry point: E2M1 operands (packed, as for NVFP4) with UE8M0 scales per 32 elements
+// ---------------------------------------------------------------------------
+uint64_t b200tile_linear_mxfp4_workspace_bytes(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  return (uint64_t)b200_mxf4_scratch_bytes(m, n, k);
+}
+
+int b200tile_linear_mxfp4(const void* x, const void* y, const void* x_scales, const void* y_scales,
+                          void* z, const char* out_dtype, int m, int n, int k, int64_t ldx, int64_t ldy,
+                          int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
+                          uint64_t workspace_bytes, void* cu_stream) {
+  if (!x || !y || !x_scales || !y_scales || !z || !out_dtype)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp4: null argument");
+  if (m <= 0 || n <= 0 || k <= 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp4: Shape dimensions must be positive");
+  if (k % 128 != 0)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp4: K (%d) must be a multiple of 128", k);
+  if (ldx < k / 2 || ldy < k / 2 || ldz < n || ld_xs < k / 32 || ld_ys < k / 32)
+    return set_error(B200TILE_ERR_INVALID, "linear_mxfp4: leading dimension too small");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(y) & 15) != 0 || ldx % 16 != 0 ||
+      ldy % 16 != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_mxfp4: operand rows must be 16-byte aligned");
+  if (ld_xs % 4 != 0 || ld_ys % 4 != 0 || (reinterpret_cast<uintptr_t>(x_scales) & 3) != 0 ||
+      (reinterpret_cast<uintptr_t>(y_scales) & 3) != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_mxfp4: scale rows must be 4-byte aligned");
+  int out_f32;
+  if (!strcmp(out_dtype, "f32")) out_f32 = 1;
+  else if (!strcmp(out_dtype, "bf16")) out_f32 = 0;
+  else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_mxfp4: unsupported output type '%s'", out_dtype);
+  if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
+    return set_error(B200TILE_ERR_ALIGN, "linear_mxfp4: output must be 16-byte aligned with a 16-byte pitch");
+  const size_t need = b200_mxf4_scratch_bytes(m, n, k);
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
+    return set_error(B200TILE_ERR_INVALID,
+                     "linear_mxfp4: workspace of %llu bytes (16-byte aligned) required, got %llu",
+                     (unsigned long long)need, (unsigned long long)workspace_bytes);
+  return b200_gemm_mxf4_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs, ld_ys,
+                                 alpha, workspace, static_cast<cudaStream_t>(cu_stream));
+}
+
+// ---------------------------------------------------------------------------
 // Typed normalisation entry points
 // ---------------------------------------------------------------------------
 int b200tile_add_rms_norm(const char* dtype, const void* residual, const void* x, const void* w, void* out,
@@ -1181,8 +1226,10 @@ int launch_linear_fp8_generic(const char* kernel, const char* const* generics, i
 //          generics [BM, BN, BK, BK_PACKED = BK/2, BK_SCALES = BK/16]
 //   MXFP8  (cutile-examples/examples/mxfp8.rs:34-64): x [M,K], y [N,K] f8e4m3fn, scales [.,K/32] f8e8m0fnu,
 //          generics [BM, BN, BK, BK_SCALES = BK/32]
-//   The element types are not generics in the reference, so the two are told apart by the generics themselves
-//   (five integers with BK = 16 BK_SCALES, or four with BK = 32 BK_SCALES); an optional leading type name
+//   MXFP4  (the operand / scale pairing of cutile/tests/tensor_and_matrix_ops.rs:224-244): NVFP4's operands with
+//          [.,K/32] f8e8m0fnu scales, generics [BM, BN, BK, BK_PACKED = BK/2, BK_SCALES = BK/32]
+//   The element types are not generics in the reference, so the formats are told apart by the generics themselves
+//   (five integers with BK = 16 or 32 BK_SCALES, or four with BK = 32 BK_SCALES); an optional leading type name
 //   selects a bf16 output instead of the reference's f32.  Any tile generics are accepted: they shape the
 //   launch grid, which is validated, and the kernel runs its own tile.  The scale re-layout scratch is a
 //   library-owned block per (device, stream).  Weight scales registered with
@@ -1198,13 +1245,14 @@ int launch_linear_tile_generic(const char* kernel, const char* const* generics, 
                      "%s: generics must be [BM, BN, BK, BK_PACKED, BK_SCALES] (NVFP4) or [BM, BN, BK, BK_SCALES] (MXFP8)",
                      kernel);
   const bool fp4 = ng == 5;
+  const bool mxf4 = fp4 && g[4] * 32 == g[2];
   const long BM = g[0], BN = g[1], BK = g[2];
   if (BM <= 0 || BN <= 0 || BK <= 0)
     return set_error(B200TILE_ERR_UNSUPPORTED, "%s: tile generics must be positive", kernel);
-  if (fp4 ? (g[3] * 2 != BK || g[4] * 16 != BK) : (g[3] * 32 != BK))
+  if (fp4 ? (g[3] * 2 != BK || (g[4] * 16 != BK && !mxf4)) : (g[3] * 32 != BK))
     return set_error(B200TILE_ERR_UNSUPPORTED,
                      "%s: generics do not describe a supported block-scaled format (NVFP4: BK_PACKED = BK/2 and "
-                     "BK_SCALES = BK/16; MXFP8: BK_SCALES = BK/32)", kernel);
+                     "BK_SCALES = BK/16, or BK/32 for UE8M0 scales; MXFP8: BK_SCALES = BK/32)", kernel);
   if (strcmp(dtype, "f32") && strcmp(dtype, "bf16"))
     return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported output type '%s'", kernel, dtype);
   if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
@@ -1219,7 +1267,7 @@ int launch_linear_tile_generic(const char* kernel, const char* const* generics, 
   if (!r.ok) return set_error(B200TILE_ERR_INVALID, "%s: parameter array too short", kernel);
   const int M = z.dim[0], N = z.dim[1];
   const int K = fp4 ? x.dim[1] * 2 : x.dim[1];
-  const int V = fp4 ? 16 : 32;
+  const int V = (fp4 && !mxf4) ? 16 : 32;
   if (x.dim[0] != M || y.dim[0] != N || y.dim[1] != x.dim[1] || xs.dim[0] != M || ys.dim[0] != N ||
       xs.dim[1] * V != K || ys.dim[1] * V != K)
     return set_error(B200TILE_ERR_INVALID, "%s: tensor shapes do not compose", kernel);
@@ -1236,6 +1284,13 @@ int launch_linear_tile_generic(const char* kernel, const char* const* generics, 
   const void* xsp = reinterpret_cast<const void*>(xs.ptr);
   const void* ysp = reinterpret_cast<const void*>(ys.ptr);
   void* zp = reinterpret_cast<void*>(z.ptr);
+  if (mxf4) {
+    const uint64_t need = b200tile_linear_mxfp4_workspace_bytes(M, N, K);
+    void* ws = b200h::stream_scratch(static_cast<cudaStream_t>(stream), need, kernel);
+    if (!ws) return B200TILE_ERR_INVALID;
+    return b200tile_linear_mxfp4(xp, yp, xsp, ysp, zp, dtype, M, N, K, x.stride[0], y.stride[0], z.stride[0],
+                                 xs.stride[0], ys.stride[0], alpha, ws, need, stream);
+  }
   if (fp4 && M <= 128) {
     const void* prepared = nullptr;
     int config = 0;

@@ -41,32 +41,36 @@ __device__ long long g_trace_fp4_producer[8];
 constexpr int F4_BM = 128;
 constexpr int F4_THREADS = 448;  // TMA, MMA, 4 epilogue warps, two sets of 4 scale-writer warps
 
-// FP4 = true : NVFP4 (packed e2m1, UE4M3 scale per 16, K = 64 per MMA, 256 elements per stage)
-// FP4 = false: MXFP8 (e4m3, UE8M0 scale per 32, K = 32 per MMA, 128 elements per stage)
+// FMT = 1: NVFP4 (packed e2m1, UE4M3 scale per 16, K = 64 per MMA, 256 elements per stage)
+// FMT = 0: MXFP8 (e4m3, UE8M0 scale per 32, K = 32 per MMA, 128 elements per stage)
+// FMT = 2: MXFP4 (packed e2m1, UE8M0 scale per 32, K = 64 per MMA, 256 elements per stage; the operand /
+//          scale pairing of cutile/tests/tensor_and_matrix_ops.rs:224-244)
 // Either way a stage is 128 bytes per row and 4 MMAs; a 512-byte scale block holds 128 rows x 4
-// scale bytes: one MMA's scales for NVFP4, the whole stage's (one byte per MMA) for MXFP8.
+// scale bytes: one MMA's scales for NVFP4, two MMAs' (a byte pair each) for MXFP4, the whole stage's
+// (one byte per MMA) for MXFP8.
 // A_DIRECT: A's scales are read in place by the writer warps (no pre-pass, no scratch: decode-sized M
 // and the prepared-weights entry); otherwise they come re-laid-out from scratch with the stage's TMA.
 // AROWS: rows of the A tile that are loaded (the TMA box).  The MMA always reads 128 rows; with AROWS < 128
 // (decode-sized M) the rows past the box are whatever follows in the stage (the B tile), their scales are
 // zero and their results are never stored, and the shared memory saved buys a ring nearly twice as deep,
 // which is what a call bound by the latency of the weight stream needs.
-template <int BN, bool FP4 = true, bool A_DIRECT = false, int AROWS = 128>
+template <int BN, int FMT = 1, bool A_DIRECT = false, int AROWS = 128>
 struct Fp4Cfg {
+  static constexpr bool FP4 = FMT != 0;                      // packed 4-bit operands
   static_assert(AROWS == 128 || (AROWS % 8 == 0 && AROWS * 128 + BN * 128 >= 128 * 128),
                 "a short A tile must be followed by enough of the B tile for the MMA's 128-row read");
   // The rows past a short A tile are bytes of the B tile multiplied by zero scales: harmless for E2M1, which has
   // no NaN or infinity encodings; an E4M3 operand (MXFP8) could turn 0 x NaN into NaN in those accumulator rows.
   static_assert(AROWS == 128 || FP4, "the short A tile is only valid for operand types without NaN / Inf encodings");
   static constexpr int CHUNKS = (BN + 127) / 128;            // 128-row scale blocks per B tile
-  static constexpr int KQ_PER_STAGE = FP4 ? 4 : 1;           // scale blocks along K per stage
+  static constexpr int KQ_PER_STAGE = FMT == 1 ? 4 : (FMT == 2 ? 2 : 1);   // scale blocks along K per stage
   static constexpr int STAGES_ = AROWS < 128 ? ((BN <= 128) ? 9 : (BN <= 192 ? 6 : 5))
                                              : ((BN <= 128) ? 5 : 4);   // 3 instead of 4 measured 9 % slower at BN = 192
   // Scales travel to Tensor Memory in REGIONS of RK scale blocks along K (half a stage for NVFP4, a
   // whole one for MXFP8); the columns left beside the accumulators form a ring of NREG regions so
   // that the writers run ahead of the MMAs.  NREG < STAGES * HALVES keeps a writer's wait on a
   // stage's `empty` barrier within one phase of that barrier.
-  static constexpr int RK = FP4 ? 2 : 1;
+  static constexpr int RK = FMT == 1 ? 2 : 1;
   static constexpr int HALVES = KQ_PER_STAGE / RK;           // regions per stage
   static constexpr int MMAS_PER_REGION = 4 / HALVES;
   static constexpr int REGION_COLS = 4 * RK * (1 + CHUNKS);
@@ -166,13 +170,29 @@ __host__ __device__ constexpr uint32_t make_idesc_nvfp4(uint32_t M, uint32_t N) 
   return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (0u << 23) | ((M >> 4) << 24);
 }
 
-template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT, int AROWS>
+// MXFP4: E2M1 operands, UE8M0 scales, K = 64 per instruction, two scale bytes per row and instruction;
+// `sf_half` (0 or 2) picks the byte pair of the TMEM word.
+__device__ __forceinline__ void umma_mxf4_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_mxf4(uint32_t M, uint32_t N, uint32_t sf_half) {
+  return (sf_half << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (sf_half << 29);
+}
+
+template <int BN, bool OUT_F32, int FMT, bool A_DIRECT, int AROWS>
 __global__ void __launch_bounds__(F4_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const uint8_t* __restrict__ xs, int64_t ld_xs, int kq_valid, const uint8_t* __restrict__ sfa,
                   const uint8_t* __restrict__ sfb, void* __restrict__ Z,
                   int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
-  using C = Fp4Cfg<BN, FP4, A_DIRECT, AROWS>;
+  using C = Fp4Cfg<BN, FMT, A_DIRECT, AROWS>;
+  constexpr bool FP4 = C::FP4;
   constexpr int STAGES = C::STAGES;
   constexpr int STAGE_ELEMS = FP4 ? 256 : 128;  // K elements per 128-byte row
   extern __shared__ uint8_t smem_raw[];
@@ -289,7 +309,10 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 #pragma unroll
             for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
               const int k = h * C::MMAS_PER_REGION + kk;
-              if (FP4)
+              if (FMT == 2)
+                umma_mxf4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
+                             make_idesc_mxf4(F4_BM, BN, (uint32_t)(kk * 2)), sf_t, sf_t + C::SFB_COL0, (kb | k) != 0);
+              else if (FMT == 1)
                 umma_nvfp4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
                               make_idesc_nvfp4(F4_BM, BN), sf_t + kk * 4, sf_t + C::SFB_COL0 + kk * C::CHUNKS * 4,
                               (kb | k) != 0);
@@ -514,8 +537,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 }
 
 // Bytes of scratch needed for the re-laid-out B (weight) scales of an (M, N, K) problem with B tiles of BN rows.
-static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offset, bool fp4 = true) {
-  const size_t kq = fp4 ? (size_t)((K + 255) / 256) * 4 : (size_t)((K + 127) / 128);
+static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offset, int fmt = 1) {
+  const size_t kq = fmt == 1 ? (size_t)((K + 255) / 256) * 4
+                             : (fmt == 2 ? (size_t)((K + 255) / 256) * 2 : (size_t)((K + 127) / 128));
   const size_t tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
   const size_t chunks = (BN + 127) / 128;
   // decode-sized M reads A's scales in place (no scratch for them)
@@ -526,11 +550,12 @@ static size_t nvfp4_scratch_layout(int M, int N, int K, int BN, size_t* sfb_offs
 
 // b_scales_prepared: `scratch` IS the tile layout of the B scales (written once by the caller); A's
 // scales are then read in place whatever M is, so that the call needs no workspace at all.
-template <int BN, bool OUT_F32, bool FP4, bool A_DIRECT, int AROWS = 128>
+template <int BN, bool OUT_F32, int FMT, bool A_DIRECT, int AROWS = 128>
 static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
                              int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys,
                              float alpha, uint8_t* scratch, cudaStream_t stream, bool b_scales_prepared) {
-  using C = Fp4Cfg<BN, FP4, A_DIRECT, AROWS>;
+  using C = Fp4Cfg<BN, FMT, A_DIRECT, AROWS>;
+  constexpr bool FP4 = C::FP4;
   const b200h::DeviceInfo* di = b200h::device_info();
   const uint64_t row_bytes = FP4 ? (uint64_t)K / 2 : (uint64_t)K;
   if (!di) return B200_ERR_CUDA;
@@ -542,8 +567,9 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
   if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, row_bytes, (uint64_t)N,
                                   (uint64_t)ldy, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  const int kq = FP4 ? ((K + 255) / 256) * 4 : (K + 127) / 128;
-  const int kq_valid = FP4 ? K / 64 : K / 128;
+  // scale blocks (4 scale bytes per row) along K: padded to whole stages / those the tensors hold
+  const int kq = FP4 ? ((K + 255) / 256) * C::KQ_PER_STAGE : (K + 127) / 128;
+  const int kq_valid = FMT == 1 ? K / 64 : K / 128;
   const int tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
   const size_t sfb_off = A_DIRECT ? 0 : (size_t)tiles_m * kq * 512;
   if (!A_DIRECT) {
@@ -560,7 +586,7 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
         reinterpret_cast<uint32_t*>(scratch + sfb_off));
   }
   B200_CUDA_CHECK(cudaGetLastError());
-  auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FP4, A_DIRECT, AROWS>;
+  auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FMT, A_DIRECT, AROWS>;
   static b200h::DeviceOnce attr_done;
   if (!attr_done.test(di->ordinal)) {
     B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
@@ -574,20 +600,20 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
   return B200_OK;
 }
 
-template <int BN, bool OUT_F32, bool FP4 = true>
+template <int BN, bool OUT_F32, int FMT = 1>
 static int launch_nvfp4(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N,
                         int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha,
                         uint8_t* scratch, cudaStream_t stream, bool b_scales_prepared = false) {
   // same rule as nvfp4_scratch_layout: one tile row of A, or prepared weights => A's scales in place
-  if constexpr (FP4 && BN == 128) {
+  if constexpr (FMT == 1 && BN == 128) {
     if (M <= 32)   // decode: short A tile, deep ring
-      return launch_nvfp4_impl<BN, OUT_F32, FP4, true, 32>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys,
+      return launch_nvfp4_impl<BN, OUT_F32, FMT, true, 32>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys,
                                                            alpha, scratch, stream, b_scales_prepared);
   }
   if (M <= F4_BM || b_scales_prepared)
-    return launch_nvfp4_impl<BN, OUT_F32, FP4, true>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha,
+    return launch_nvfp4_impl<BN, OUT_F32, FMT, true>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha,
                                                      scratch, stream, b_scales_prepared);
-  return launch_nvfp4_impl<BN, OUT_F32, FP4, false>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha,
+  return launch_nvfp4_impl<BN, OUT_F32, FMT, false>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha,
                                                     scratch, stream, false);
 }
 
@@ -611,7 +637,22 @@ size_t b200_nvfp4_scratch_bytes(int M, int N, int K, int bn) {
 }
 
 size_t b200_mxfp8_scratch_bytes(int M, int N, int K) {
-  return b200::nvfp4_scratch_layout(M, N, K, 224, nullptr, false);
+  return b200::nvfp4_scratch_layout(M, N, K, 224, nullptr, 0);
+}
+
+size_t b200_mxf4_scratch_bytes(int M, int N, int K) {
+  return b200::nvfp4_scratch_layout(M, N, K, 192, nullptr, 2);
+}
+
+// MXFP4 (E2M1 operands with UE8M0 scales per 32 elements): B tiles of 192 rows, as for NVFP4
+int b200_gemm_mxf4_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
+                            int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                            int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream) {
+  using namespace b200;
+  uint8_t* s = static_cast<uint8_t*>(scratch);
+  if (out_f32)
+    return launch_nvfp4<192, true, 2>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
+  return launch_nvfp4<192, false, 2>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
 }
 
 // MXFP8: B tiles of 224 rows -- the widest that keeps two accumulators plus the scales in TMEM
@@ -621,8 +662,8 @@ int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const vo
   using namespace b200;
   uint8_t* s = static_cast<uint8_t*>(scratch);
   if (out_f32)
-    return launch_nvfp4<224, true, false>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
-  return launch_nvfp4<224, false, false>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
+    return launch_nvfp4<224, true, 0>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
+  return launch_nvfp4<224, false, 0>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, s, stream);
 }
 
 int b200_gemm_nvfp4_dispatch(int bn, int out_f32, const void* x, const void* y, const void* xs, const void* ys,

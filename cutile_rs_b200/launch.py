@@ -340,8 +340,9 @@ def linear_tile_fp8_blk128(z: Output, x: Tensor, y: Tensor, x_scales: Tensor, y_
 
 class LinearTile(KernelLauncher):
     """The reference's block-scaled `linear_tile` under its own name: z [M,N] partition [BM,BN] = alpha * x . y^T.
-    NVFP4 operands (``f4e2m1fnx2``) infer generics [BM, BN, BK, BK/2, BK/16], MXFP8 operands (``f8e4m3fn``)
-    [BM, BN, BK, BK/32]; a bf16 output prepends its type name (the reference's output is f32)."""
+    NVFP4 operands (``f4e2m1fnx2``) infer generics [BM, BN, BK, BK/2, BK/16] (BK/32 when the scales are
+    ``f8e8m0fnu``: MXFP4), MXFP8 operands (``f8e4m3fn``) [BM, BN, BK, BK/32]; a bf16 output prepends its type name
+    (the reference's output is f32)."""
     kernel_name = "linear_tile"
 
     def infer_generics(self) -> List[str]:
@@ -349,7 +350,8 @@ class LinearTile(KernelLauncher):
         bm, bn = z.partition_shape[0], z.partition_shape[1]
         head = [] if z.dtype_str() == "f32" else [z.dtype_str()]
         if x.dtype == "f4e2m1fnx2":
-            return head + [str(bm), str(bn), "64", "32", "4"]
+            # UE8M0 scales per 32 elements (MXFP4) or UE4M3 scales per 16 (NVFP4)
+            return head + [str(bm), str(bn), "64", "32", "2" if self.args[3].dtype == "f8e8m0fnu" else "4"]
         if x.dtype == "f8e4m3fn":
             return head + [str(bm), str(bn), "64", "2"]
         raise KernelLaunchError(f"linear_tile: operands of type {x.dtype} are not a block-scaled format "

@@ -69,3 +69,22 @@ def quant_mxfp8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     scale = torch.ldexp(torch.ones_like(amax), e)
     q = (xb / scale[:, :, None]).reshape(r, c).to(torch.float8_e4m3fn)
     return q.view(torch.uint8), (e + 127).to(torch.uint8).contiguous()
+
+
+def quant_mxfp4(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """MXFP4: e2m1 values with one e8m0 (power-of-two) scale per 32 contiguous K elements; the scale is the
+    smallest power of two with blockmax/scale <= 6.  Returns (packed [R, C/2] uint8, low nibble first; scales
+    uint8 [R, C/32] holding the biased exponent)."""
+    r, c = x.shape
+    assert c % 32 == 0
+    xb = x.float().reshape(r, c // 32, 32)
+    amax = xb.abs().amax(dim=2)
+    mant, exp = torch.frexp(amax / 6.0)             # amax/6 = mant * 2^exp, mant in [0.5, 1)
+    e = torch.where(mant == 0.5, exp - 1, exp)
+    e = torch.where(amax > 0, e, torch.zeros_like(e)).clamp(-127, 127)
+    scale = torch.ldexp(torch.ones_like(amax), e)
+    y = xb / scale[:, :, None]
+    code = _to_e2m1_codes(y.abs()) | ((y < 0) | ((y == 0) & torch.signbit(y))).to(torch.uint8) * 8
+    code = code.reshape(r, c)
+    packed = (code[:, 0::2] & 0xF) | ((code[:, 1::2] & 0xF) << 4)
+    return packed.contiguous(), (e + 127).to(torch.uint8).contiguous()

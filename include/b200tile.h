@@ -385,6 +385,19 @@ B200TILE_API int b200tile_linear_mxfp8(const void* x, const void* y, const void*
                                        int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
                                        uint64_t workspace_bytes, void* cu_stream);
 
+/* z[M,N] = alpha * sum_k x[m,k]*xs[m,k/32] * y[n,k]*ys[n,k/32]  (MXFP4: NVFP4's packed E2M1 operands with
+ * power-of-two f8e8m0fnu scales per 32 elements).  The operand / scale pairing of `mmaf_scaled` in
+ * cutile/tests/tensor_and_matrix_ops.rs:224-244 (`raw_mmaf_scaled_nvfp4_kernel`): x [M,K/2], y [N,K/2]
+ * f4e2m1fnx2 bytes (low nibble first); xs [M,K/32], ys [N,K/32] in logical row-major order.
+ *   out_dtype  "bf16" or "f32";  K must be a multiple of 128; leading dimensions in BYTES
+ *   workspace  at least b200tile_linear_mxfp4_workspace_bytes(m, n, k) bytes, 16-byte aligned */
+B200TILE_API uint64_t b200tile_linear_mxfp4_workspace_bytes(int m, int n, int k);
+B200TILE_API int b200tile_linear_mxfp4(const void* x, const void* y, const void* x_scales,
+                                       const void* y_scales, void* z, const char* out_dtype, int m,
+                                       int n, int k, int64_t ldx, int64_t ldy, int64_t ldz,
+                                       int64_t ld_xs, int64_t ld_ys, float alpha, void* workspace,
+                                       uint64_t workspace_bytes, void* cu_stream);
+
 /* NVFP4 linear layer with the weight scales laid out ahead of time.  Inference weights do not
  * change, so their scales can be brought into the kernel's tile layout once
  * (b200tile_nvfp4_prepare_weight_scales, for one `config` = B tile of 128 / 192 / 256 rows); every

@@ -218,6 +218,24 @@ def dequant_nvfp4(packed, scales) -> np.ndarray:
     return out
 
 
+_E2M1_VALUES = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=np.float32)
+
+
+def dequant_mxfp4(packed, scales) -> np.ndarray:
+    """Packed f4e2m1fnx2 bytes (low nibble = even element, cuda-core/src/dtype.rs:60-110) times one f8e8m0fnu
+    scale 2^(e - 127) per 32 elements: the operand / scale pairing of `mmaf_scaled` in
+    cutile/tests/tensor_and_matrix_ops.rs:224-244.  numpy; every product is exact in fp32."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint8)
+    scales = np.ascontiguousarray(scales, dtype=np.uint8)
+    r, c2 = packed.shape
+    codes = np.empty((r, c2 * 2), dtype=np.uint8)
+    codes[:, 0::2] = packed & 0xF
+    codes[:, 1::2] = packed >> 4
+    vals = _E2M1_VALUES[codes & 7] * np.where(codes & 8, np.float32(-1.0), np.float32(1.0))
+    sc = np.ldexp(np.float32(1.0), scales.astype(np.int32) - 127).astype(np.float32)
+    return (vals.reshape(r, c2 * 2 // 32, 32) * sc[:, :, None]).reshape(r, c2 * 2).astype(np.float32)
+
+
 def quant_mxfp8(x):
     """-> (q [R, C] u8 e4m3 bits, scales [R, C/32] u8 e8m0 bits)."""
     x = _f32(x)

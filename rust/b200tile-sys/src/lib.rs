@@ -145,6 +145,11 @@ extern "C" {
         y_scales: *const c_void, z: *mut c_void, out_dtype: *const c_char, m: c_int, n: c_int, k: c_int,
         ldx: i64, ldy: i64, ldz: i64, ld_xs: i64, ld_ys: i64, alpha: f32, workspace: *mut c_void,
         workspace_bytes: u64, cu_stream: *mut c_void) -> c_int;
+    pub fn b200tile_linear_mxfp4_workspace_bytes(m: c_int, n: c_int, k: c_int) -> u64;
+    pub fn b200tile_linear_mxfp4(x: *const c_void, y: *const c_void, x_scales: *const c_void,
+        y_scales: *const c_void, z: *mut c_void, out_dtype: *const c_char, m: c_int, n: c_int, k: c_int,
+        ldx: i64, ldy: i64, ldz: i64, ld_xs: i64, ld_ys: i64, alpha: f32, workspace: *mut c_void,
+        workspace_bytes: u64, cu_stream: *mut c_void) -> c_int;
     pub fn b200tile_nvfp4_weight_scales_bytes(n: c_int, k: c_int, config: c_int) -> u64;
     pub fn b200tile_nvfp4_prepare_weight_scales(y_scales: *const c_void, n: c_int, k: c_int, ld_ys: i64,
         config: c_int, prepared: *mut c_void, prepared_bytes: u64, cu_stream: *mut c_void) -> c_int;
