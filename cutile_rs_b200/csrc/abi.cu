@@ -84,6 +84,10 @@ int b200_gemm_mxf4_dispatch(int out_f32, const void* x, const void* y, const voi
                             int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
 
+int b200_fmha_f32_dispatch(int head_dim, const void* q, const void* k, const void* v, void* out, int batch, int heads,
+                           int heads_kv, int q_len, int kv_len, const int64_t* qs, const int64_t* ks,
+                           const int64_t* vs, const int64_t* os, float qk_scale, int causal, int input_pos,
+                           const uint32_t* pos_ptr, cudaStream_t stream);
 int b200_fmha_decode_dispatch(int dtype, int head_dim, const void* q, const void* k, const void* v, void* att,
                               float* lse, void* out, const uint32_t* pos, int kv_heads, int group, int kv_cap,
                               int bn, int splits, float qk_scale, const int64_t* strides, cudaStream_t stream);
@@ -323,6 +327,10 @@ static int fmha_fwd_common(const char* dtype, const void* q, const void* k, cons
     return set_error(B200TILE_ERR_INVALID, "fmha: heads (%d) must be a multiple of heads_kv (%d)",
                      heads, heads_kv);
   if (input_pos < 0) return set_error(B200TILE_ERR_INVALID, "fmha: input_pos must be >= 0");
+  if (!strcmp(dtype, "f32"))   // exact fp32 on the CUDA cores: the element type of the reference's asserted examples
+    return b200_fmha_f32_dispatch(head_dim, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, q_strides, k_strides,
+                                  v_strides, o_strides, qk_scale, causal ? 1 : 0, input_pos, pos_ptr,
+                                  static_cast<cudaStream_t>(cu_stream));
   int dt;
   if (!strcmp(dtype, "bf16"))
     dt = 0;
@@ -1093,12 +1101,14 @@ int launch_fmha_generic(const char* kernel, const char* const* generics, int n_g
     return set_error(B200TILE_ERR_UNSUPPORTED, "%s: malformed generics", kernel);
   const long BM = g[0], BN = g[1], D = g[2];
   const long causal = prefill ? g[3] : g[4];
-  if (strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
+  const bool f32 = !strcmp(dtype, "f32");
+  if (!f32 && strcmp(dtype, "bf16") && strcmp(dtype, "f16"))
     return set_error(B200TILE_ERR_UNSUPPORTED, "%s: unsupported element type '%s'", kernel, dtype);
-  if (BM != 128 || BN != 128 || (D != 64 && D != 128))
+  // f32 (CUDA cores): any tile generics, they only shape the launch grid; 16-bit types: the tensor-core tile
+  if (f32 ? (BM <= 0 || BN <= 0 || (D != 32 && D != 64 && D != 128)) : (BM != 128 || BN != 128 || (D != 64 && D != 128)))
     return set_error(B200TILE_ERR_UNSUPPORTED,
                      "%s: tile (BM %ld, BN %ld, D %ld) has no precompiled configuration "
-                     "(BM=BN=128, D in {64,128})",
+                     "(16-bit types: BM=BN=128, D in {64,128}; f32: D in {32,64,128})",
                      kernel, BM, BN, D);
   if (!launch) return b200h::device_info() ? B200TILE_OK : B200TILE_ERR_CUDA;
   ParamReader r{params, n_params, 0, true};

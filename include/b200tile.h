@@ -282,7 +282,10 @@ B200TILE_API int b200tile_group_gemm(const char* dtype, const int64_t* a_ptrs, c
  * Replaces `fmha_prefill_causal` (cutile-kernels/src/attention.rs:232-392), the benchmark kernels
  * `fmha` (cutile-benchmarks/benches/fmha.rs:20-146, fmha_causal.rs:20-136) and the example
  * kernels (cutile-examples/examples/flash_attention.rs:20-136, flash_attention_causal.rs:19-134).
- *   dtype      "bf16" or "f16" (tensor cores; head_dim 64 or 128)
+ *   dtype      "bf16" or "f16" (tensor cores; head_dim 64 or 128), or "f32": every product and sum in IEEE
+ *              fp32 on the CUDA cores, head_dim 32, 64 or 128 -- the element type of the reference's two
+ *              asserted examples (flash_attention.rs:199-264, flash_attention_causal.rs:216-285); like the
+ *              exact fp32 GEMM a correctness configuration, with fp32 probabilities
  *   q          query tensor; element (b, h, i, d) at q + (b*heads + h)*q_strides[0] +
  *              i*q_strides[1] + d  -- covers both (b,h,s,d) and [q_len, heads, D] layouts
  *   k, v       same addressing with heads_kv; kv head = h / (heads / heads_kv) (GQA)
