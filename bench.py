@@ -1170,18 +1170,31 @@ def _print_trace(lib, args) -> None:
         raise SystemExit("--trace needs the diagnostic build (see the module docstring)")
     out = (ctypes.c_longlong * 20)()
     which = {"gemm": b"gemm_pair", "fmha": b"fmha_alt" if args.pair else b"fmha",
-             "nvfp4": b"block_scaled"}.get(args.kernel)
+             "nvfp4": b"block_scaled_pair" if args.config == 3 else b"block_scaled"}.get(args.kernel)
     if which is None or lib.b200tile_trace_read(which, out):
         raise SystemExit("no trace for this kernel")
     v = list(out)
     if args.kernel == "nvfp4":
         n = max(v[5], 1)
         print(f"MMA thread of one CTA per stage (4 block-scaled MMAs): stage + scale waits {v[2] / n:.0f}, "
-              f"MMA issue {v[3] / n:.0f}, commit {v[4] / n:.0f}; total {v[6] / n:.0f} cycles per stage ({n} stages); "
+              f"MMA issue {v[3] / n:.0f}, commit {v[4] / n:.0f}, accumulator waits {v[0] / n:.0f}; "
+              f"total {v[6] / n:.0f} cycles per stage ({n} stages); "
               f"SM clock inside the kernel {1e3 * v[6] / max(v[7], 1):.0f} MHz")
         w = max(v[14], 1)
-        print(f"scale-writer warp per stage: stage-full wait {v[10] / w:.0f}, region wait + loads + store issue "
-              f"{v[11] / w:.0f}, store completion {v[12] / w:.0f}, hand-off {v[13] / w:.0f}; total {v[15] / w:.0f}")
+        if args.config == 3:
+            print(f"scale-writer warp per stage: stage-full wait {v[10] / w:.0f}, loads + store issue {v[11] / w:.0f}, "
+                  f"store completion {v[12] / w:.0f}, region wait {v[13] / w:.0f}; total {v[15] / w:.0f}")
+        else:
+            print(f"scale-writer warp per stage: stage-full wait {v[10] / w:.0f}, region wait + loads + store issue "
+                  f"{v[11] / w:.0f}, store completion {v[12] / w:.0f}, hand-off {v[13] / w:.0f}; total {v[15] / w:.0f}")
+        if args.config == 3:
+            tl = (ctypes.c_longlong * 20)()
+            if lib.b200tile_trace_read(b"block_scaled_pair_timeline", tl) == 0:
+                t0 = tl[0]
+                names = ["slot free seen by producer", "copies issued", "landed seen by writer", "region 0 free", "region 1 free",
+                         "scale stores complete", "writer arrived", "scales 0 ready seen by MMA thread", "MMAs 0 issued",
+                         "scales 1 ready seen", "MMAs 1 issued", "committed", "slot free again"]
+                print("time line of one stage (cycles): " + ", ".join(f"{n} {tl[i] - t0}" for i, n in enumerate(names)))
         pn = max(v[19], 1)
         print(f"TMA producer per stage: stage-empty wait {v[17] / pn:.0f}, issue of the copies {v[18] / pn:.0f}")
         return

@@ -63,6 +63,8 @@ int b200_trace_read_fmha_alt_t(long long* out);
 int b200_trace_read_gemm_pair(long long* out);
 int b200_trace_read_fmha(long long* out);
 int b200_trace_read_fp4(long long* out);
+int b200_trace_read_fp4_pair(long long* out);
+int b200_trace_read_fp4_pair_tl(long long* out);
 #endif
 
 int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const float* xs,
@@ -80,6 +82,10 @@ int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const vo
                              int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                              int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
 size_t b200_mxf4_scratch_bytes(int M, int N, int K);
+size_t b200_nvfp4_pair_scratch_bytes(int M, int N, int K);
+int b200_gemm_nvfp4_pair_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
+                                  int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                                  int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
 int b200_gemm_mxf4_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
                             int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
@@ -212,12 +218,12 @@ int b200tile_query_configs(const char* kernel, const char* dtype, b200tile_confi
   // name (f4e2m1fnx2 = NVFP4, e4m3 scale per 16; f8e4m3fn = MXFP8, e8m0 scale per 32).  The launcher's tile
   // generics only shape the launch grid; the kernel's own tile is the configuration listed here.
   static const b200tile_config kNvfp4Configs[] = {{0, 128, 128, 256, 5, 1, 1}, {1, 128, 192, 256, 4, 1, 1},
-                                                  {2, 128, 256, 256, 3, 1, 1}};
+                                                  {2, 128, 256, 256, 3, 1, 1}, {3, 256, 256, 256, 5, 2, 1}};
   static const b200tile_config kMxfp8Configs[] = {{0, 128, 224, 128, 4, 1, 1}};
   if (!strcmp(kernel, "linear_tile")) {
     if (!strcmp(dtype, "f4e2m1fnx2")) {
       tab = kNvfp4Configs;
-      n = 3;
+      n = 4;
     } else if (!strcmp(dtype, "f8e4m3fn")) {
       tab = kMxfp8Configs;
       n = 1;
@@ -545,6 +551,8 @@ uint64_t b200tile_linear_nvfp4_workspace_bytes(int m, int n, int k) {
     const size_t b = b200_nvfp4_scratch_bytes(m, n, k, kNvfp4Bn[i]);
     if (b > best) best = b;
   }
+  const size_t pair = b200_nvfp4_pair_scratch_bytes(m, n, k);
+  if (pair > best) best = pair;
   return (uint64_t)best;
 }
 
@@ -569,11 +577,24 @@ int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales, co
   else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_nvfp4: unsupported output type '%s'", out_dtype);
   if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
     return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4: output must be 16-byte aligned with a 16-byte pitch");
-  if (config < -1 || config > 2)
+  if (config < -1 || config > 3)
     return set_error(B200TILE_ERR_UNSUPPORTED, "linear_nvfp4: unknown config %d", config);
-  // default: 192-row B tiles; decode-sized M takes 128-row tiles (more CTAs for the weight stream, and the
-  // short-A-tile configuration of the kernel exists for that tile only)
-  if (config < 0) config = m <= 32 ? 0 : 1;
+  // default: CTA pairs (256 x 256 tiles) from 512 rows on (measured ahead of the single-CTA tiles at every such
+  // shape: 8 % at 4096 x 14336 x 4096, 24 % at 8192 x 28672 x 8192); below that 192-row B tiles, and decode-sized M
+  // takes 128-row tiles (more CTAs for the weight stream, and the short-A-tile configuration exists for that tile only)
+  if (config < 0) config = m <= 32 ? 0 : (m >= 512 ? 3 : 1);
+  if (config == 3) {   // CTA pairs, 256 x 256 tiles
+    const size_t need = b200_nvfp4_pair_scratch_bytes(m, n, k);
+    if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
+      return set_error(B200TILE_ERR_INVALID,
+                       "linear_nvfp4: workspace of %llu bytes (16-byte aligned) required, got %llu",
+                       (unsigned long long)need, (unsigned long long)workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(y) & 15) != 0 || ldx % 16 != 0 ||
+        ldy % 16 != 0)
+      return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4: operand rows must be 16-byte aligned");
+    return b200_gemm_nvfp4_pair_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs, ld_ys,
+                                         alpha, workspace, static_cast<cudaStream_t>(cu_stream));
+  }
   const int bn = kNvfp4Bn[config];
   const size_t need = b200_nvfp4_scratch_bytes(m, n, k, bn);
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
@@ -1828,7 +1849,7 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
 
 #ifdef B200TILE_TRACE
 // Diagnostic builds only: copies the cycle counters of one traced kernel ("gemm_pair", "fmha",
-// "fmha_alt", "fmha_alt_t", "block_scaled") into out[20]; see csrc/trace.cuh.
+// "fmha_alt", "fmha_alt_t", "block_scaled", "block_scaled_pair") into out[20]; see csrc/trace.cuh.
 B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!which || !out) return B200TILE_ERR_INVALID;
   for (int i = 0; i < 20; ++i) out[i] = 0;
@@ -1837,6 +1858,9 @@ B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!strcmp(which, "fmha_alt_t")) return b200_trace_read_fmha_alt_t(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "fmha_alt")) return b200_trace_read_fmha_alt(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "block_scaled")) return b200_trace_read_fp4(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "block_scaled_pair")) return b200_trace_read_fp4_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "block_scaled_pair_timeline"))
+    return b200_trace_read_fp4_pair_tl(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   return B200TILE_ERR_UNSUPPORTED;
 }
 #endif

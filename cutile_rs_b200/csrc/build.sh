@@ -16,7 +16,7 @@ NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"
 FLAGS=(-std=c++17 -O3 -lineinfo -gencode arch=compute_100a,code=sm_100a
        -Xcompiler -fPIC -Xcompiler -fvisibility=hidden ${B200_NVCC_EXTRA:-})
 objs=()
-for src in host_common gemm_tc gemm_tc_pair gemm_f32 gemm_fp8_blk gemm_nvfp4 fmha_fwd fmha_fwd_alt fmha_f32 fmha_decode gemm_host gemm_grouped norms positional argmax pointwise abi; do
+for src in host_common gemm_tc gemm_tc_pair gemm_f32 gemm_fp8_blk gemm_nvfp4 gemm_nvfp4_pair fmha_fwd fmha_fwd_alt fmha_f32 fmha_decode gemm_host gemm_grouped norms positional argmax pointwise abi; do
   obj="${here}/_${src}${variant:+.${variant}}.o"
   if [[ ! -f "${obj}" || "${here}/${src}.cu" -nt "${obj}" || "${here}/sm100_ptx.cuh" -nt "${obj}" \
         || "${here}/host_common.h" -nt "${obj}" || "${here}/fmha_common.cuh" -nt "${obj}" || "${here}/trace.cuh" -nt "${obj}" || "${here}/../../include/b200tile.h" -nt "${obj}" ]]; then

@@ -280,7 +280,11 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       B200_TR_FLUSH(g_trace_fp4_producer, 3, blockIdx.x == 5);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
+      // The whole warp runs the control flow and the address arithmetic (which then stays in uniform registers) and
+      // one elected lane issues the tcgen05 instructions: under `if (lane == 0)` the thread spent ~75 cycles per MMA
+      // and ~60 per commit, 626 cycles per stage against the 384 the tensor pipe needs for the stage's MMAs.
+      const bool me = elect_one() != 0;
       uint32_t stage = 0, phase = 0, it = 0, g = 0, reg = 0, reg_par = 0;
       bool ok = true;
       B200_TR_DECL(6);
@@ -288,7 +292,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const uint32_t buf = (C::NACC == 2) ? (it & 1) : 0;
         const uint32_t par = (C::NACC == 2) ? (((it >> 1) & 1) ^ 1) : ((it & 1) ^ 1);
         B200_TR_BEGIN();
-        if (!mbar_wait(wctx, bar_tempty + buf * 8, par, 2)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_tempty + buf * 8, par, 2))) { ok = false; break; }
         B200_TR_END(0);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
@@ -302,13 +306,14 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             // the scale writers arrive only after the stage's TMA bytes have landed, so this wait
             // covers the operands in shared memory and the region's scales in Tensor Memory
             const uint32_t sf_t = tmem_base + C::SF_BASE + reg * C::REGION_COLS;
-            if (!mbar_wait(wctx, bar_sf_ready + reg * 8, reg_par, 6)) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_sf_ready + reg * 8, reg_par, 6))) { ok = false; break; }
             tc_fence_after_sync();
             B200_TR_END(2);
             B200_TR_BEGIN();
 #pragma unroll
             for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
               const int k = h * C::MMAS_PER_REGION + kk;
+              if (!me) continue;
               if (FMT == 2)
                 umma_mxf4_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2),
                              make_idesc_mxf4(F4_BM, BN, (uint32_t)(kk * 2)), sf_t, sf_t + C::SFB_COL0, (kb | k) != 0);
@@ -325,13 +330,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           }
           if (!ok) break;
           B200_TR_BEGIN();
-          umma_commit(bar_empty + stage * 8);   // frees the smem stage and, later, the TMEM scale regions it used
+          if (me) umma_commit(bar_empty + stage * 8);   // frees the smem stage and, later, the TMEM scale regions it used
+          __syncwarp();
           B200_TR_END(4);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(bar_tfull + buf * 8);
+        if (ok && me) umma_commit(bar_tfull + buf * 8);
+        __syncwarp();
       }
-      B200_TR_FLUSH(g_trace_fp4, 6, blockIdx.x == 5);
+      B200_TR_FLUSH(g_trace_fp4, 6, blockIdx.x == 5 && lane == 0);
     }
   } else if (warp >= 6) {
     // ---- scale writers: four warps, one per 32-lane quadrant of Tensor Memory ----
@@ -735,7 +742,8 @@ extern "C" int b200tile_linear_nvfp4_static(const void* x, const void* y, const 
   if (config < -1 || config > 2)
     return b200h::set_error(B200_ERR_UNSUPPORTED, "linear_nvfp4_static: unknown config %d", config);
   static const int kBn[3] = {128, 192, 256};
-  const int bn = kBn[config < 0 ? (m <= 32 ? 0 : 1) : config];   // the default of b200tile_linear_nvfp4
+  if (config < 0) config = m <= 32 ? 0 : 1;   // this entry's own default: single-CTA tiles (its scratch is sized for them)
+  const int bn = kBn[config];
   const size_t need = b200::nvfp4_scratch_layout(m, n, k, bn, nullptr);
   if (need > (size_t)B200TILE_NVFP4_STATIC_SCRATCH_BYTES)
     return b200h::set_error(B200_ERR_INVALID,

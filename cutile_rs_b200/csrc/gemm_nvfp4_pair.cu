@@ -1,0 +1,486 @@
+// NVFP4 block-scaled GEMM on CTA pairs: one 256 x 256 output tile per pair of SMs
+// (tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale, M = 256, N = 256, K = 64 per instruction).
+//
+// Why pairs: the single-CTA kernel (gemm_nvfp4.cu) moves 46 KB of operands into shared memory per 384
+// tensor-pipe cycles of a 128 x 192 tile, 120 bytes per clock and SM, about twice what L2 delivers when all
+// SMs pull at once, so its tensor pipe idles 60 % of the time.  In a pair each CTA loads its own 128 rows of A
+// and only HALF of the tile's B rows (the instruction reads the other half from the partner's shared
+// memory): 32 KB + 6 KB of scales per 512 tensor-pipe cycles, 74 bytes per clock.
+//
+// Same operand formats, scale arrangement in Tensor Memory and scratch layout of the re-laid-out scales as
+// gemm_nvfp4.cu (Z = alpha * sum_k x*xs * y*ys; cutile-examples/examples/nvfp4.rs:37-76).  Per CTA:
+//   warp 0        TMA producer: own A rows, own half of B, own A-scale blocks, the tile's B-scale blocks
+//   warp 1        leader CTA only: issues the pair's MMAs; both: Tensor-Memory allocation
+//   warps 2, 3    idle (roles are aligned to warpgroups so that registers can be re-balanced with setmaxnreg)
+//   warps 4..11   epilogue: two warps per 32-lane quarter (128 columns each); the accumulator is drained
+//                 into packed registers first and handed back, then stored
+//   warps 12..19  scale writers: shared memory -> Tensor Memory (tcgen05.st), two sets taking alternate
+//                 stages; each CTA writes its own Tensor Memory and arrives on the LEADER's region barrier
+// Every CTA holds the scales of its own 128 A rows and of all 256 B rows of the tile.
+#include "../../include/b200tile.h"
+#include "host_common.h"
+#include "sm100_ptx.cuh"
+#include "trace.cuh"
+
+namespace b200 {
+
+#ifdef B200TILE_TRACE
+// leader CTA of pair 5 -- MMA thread: [0] accumulator waits, [2] scale-region waits, [3] MMA issue, [4] commits,
+// [5] stages, [6] total cycles, [7] the same span in ns; writer warp 12: [0] stage-full waits, [1] loads +
+// store issue, [2] store completion, [3] region waits, [4] stages, [5] total; producer: [0] stage-empty waits,
+// [1] issue of the copies, [2] stages, [3] total
+__device__ long long g_trace_fp4p[8];
+__device__ long long g_trace_fp4p_writer[8];
+__device__ long long g_trace_fp4p_producer[8];
+// time line (clock64 of one SM) of global stage 100 of the leader CTA of pair 5: see b200_trace_read_fp4_pair_tl
+__device__ long long g_trace_fp4p_tl[16];
+#define B200_TL(i, cond) if ((cond) && blockIdx.x == 10) g_trace_fp4p_tl[i] = clock64()
+#else
+#define B200_TL(i, cond)
+#endif
+
+struct F4P {
+  static constexpr int BM = 128;                 // rows per CTA (256 per pair)
+  static constexpr int BN = 256;                 // tile columns
+#ifndef B200_F4P_STAGES
+#define B200_F4P_STAGES 5
+#endif
+  static constexpr int STAGES = B200_F4P_STAGES;
+  static constexpr int EW = 8;                   // epilogue warps
+  static constexpr int THREADS = 128 + 32 * EW + 256;   // 640: the kernel is compiled for 96 registers per thread
+  // setmaxnreg pool = what the CTA was given at launch, 640 x 96 = 61440: 384 x 56 + 256 x 152 = 60416
+  static constexpr int OTHER_REGS = 56, EPI_REGS = 152;
+  static constexpr int CHUNKS = 2;               // 128-row scale blocks per B tile
+  static constexpr int KQ_PER_STAGE = 4;         // scale blocks along K per stage (one per K = 64 instruction)
+  static constexpr int RK = 2, HALVES = 2, MMAS_PER_REGION = 2;
+  // 24 columns of scales per region, padded to 32 so that ONE tcgen05.st writes a region: the instruction costs
+  // ~170 cycles whatever its width, and the x16 + x8 pair made the writers the slowest stage of the pipeline
+  static constexpr int REGION_USED = 4 * RK * (1 + CHUNKS);
+  static constexpr int REGION_COLS = 32;
+  static constexpr int SF_BASE = BN;             // one accumulator, the scale regions follow it
+  static constexpr int NREG_FIT = (512 - SF_BASE) / REGION_COLS;  // 8
+  static constexpr int NREG = NREG_FIT < STAGES * HALVES - 1 ? NREG_FIT : STAGES * HALVES - 1;
+  static_assert(SF_BASE + NREG * REGION_COLS <= 512, "scale regions must fit beside the accumulator");
+  static constexpr int A_BYTES = BM * 128;
+  static constexpr int B_BYTES = (BN / 2) * 128;
+  static constexpr int SFA_BYTES = KQ_PER_STAGE * 512;
+  static constexpr int SFB_BYTES = KQ_PER_STAGE * CHUNKS * 512;
+  static constexpr int SFB_COL0 = 4 * RK;
+  static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+  static constexpr int STAGE_BYTES = (STAGE_TX + 1023) / 1024 * 1024;
+  static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
+  static constexpr int NUM_BARS = 2 * STAGES + 2 + NREG;
+  static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
+  static constexpr int TOTAL = OFF_MISC + 16 + 1024;
+};
+
+__device__ __forceinline__ void bulk_load_1d_p(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void umma_nvfp4_ss_2cta(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                   uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// E2M1 operands (code 1), UE4M3 scales, K = 64
+__host__ __device__ constexpr uint32_t make_idesc_nvfp4_p(uint32_t M, uint32_t N) {
+  return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+template <bool OUT_F32>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(F4P::THREADS, 1)
+gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z, int M,
+                       int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
+  using C = F4P;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_full = base + C::OFF_BAR;            // per CTA: its own TMA bytes
+  const uint32_t bar_empty = bar_full + STAGES * 8;       // per CTA: the leader commits to both
+  const uint32_t bar_tfull = bar_empty + STAGES * 8;      // per CTA
+  const uint32_t bar_tempty = bar_tfull + 8;              // meaningful in the leader only
+  const uint32_t bar_sf_ready = bar_tempty + 8;           // [NREG], meaningful in the leader only
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + C::OFF_MISC);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  WaitCtx wctx{misc + 1, status};
+  auto stage_a = [&](uint32_t s) { return base + s * C::STAGE_BYTES; };
+  auto stage_b = [&](uint32_t s) { return base + s * C::STAGE_BYTES + C::A_BYTES; };
+  auto stage_sfa = [&](uint32_t s) { return base + s * C::STAGE_BYTES + C::A_BYTES + C::B_BYTES; };
+  auto stage_sfb = [&](uint32_t s) { return stage_sfa(s) + C::SFA_BYTES; };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + s * 8, 1);
+      mbar_init(bar_empty + s * 8, 1);
+    }
+    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tempty, 2 * C::EW);                                    // the epilogue warps of both CTAs
+    for (int r = 0; r < C::NREG; ++r) mbar_init(bar_sf_ready + r * 8, 8);   // four writer warps of each CTA
+    misc[1] = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(misc)), 512);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // the partner's barriers exist before anything signals them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = misc[0];
+
+  const int tiles_m = (M + 2 * C::BM - 1) / (2 * C::BM);
+  const int tiles_n = (N + C::BN - 1) / C::BN;
+  const int total_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + 255) / 256;
+  const int kq_count = num_kb * C::KQ_PER_STAGE;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  auto tile_coords = [&](int tile, int& bm, int& bn) {
+    const int in_group = group_m * tiles_n;
+    const int group = tile / in_group;
+    const int first_m = group * group_m;
+    const int rem = tiles_m - first_m;
+    const int gsz = rem < group_m ? rem : group_m;
+    bm = first_m + (tile % gsz);
+    bn = (tile % in_group) / gsz;
+  };
+
+  if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::OTHER_REGS));
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      [[maybe_unused]] uint32_t gs = 0;
+      B200_TR_DECL(3);
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        int bm, bn;
+        tile_coords(tile, bm, bn);
+        const int m0 = bm * (2 * C::BM) + (int)rank * C::BM;
+        const int n0 = bn * C::BN + (int)rank * (C::BN / 2);
+        const uint8_t* sfa_tile = sfa + (int64_t)(bm * 2 + (int)rank) * kq_count * 512;
+        const uint8_t* sfb_tile = sfb + (int64_t)bn * kq_count * (C::CHUNKS * 512);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          B200_TR_COUNT(2);
+          B200_TR_BEGIN();
+          if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
+          B200_TR_END(0);
+          B200_TL(0, gs == 100);
+          B200_TL(12, gs == 100 + STAGES);
+          B200_TR_BEGIN();
+          const uint32_t full = bar_full + stage * 8;
+          mbar_expect_tx(full, C::STAGE_TX);
+          tma_load_2d(stage_a(stage), &tmA, full, kb * 128, m0);
+          tma_load_2d(stage_b(stage), &tmB, full, kb * 128, n0);
+          bulk_load_1d_p(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
+          bulk_load_1d_p(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+          B200_TR_END(1);
+          B200_TL(1, gs == 100);
+          ++gs;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      B200_TR_FLUSH(g_trace_fp4p_producer, 3, blockIdx.x == 10);
+    }
+  } else if (warp == 1) {
+    if (leader) {
+      // The whole warp runs the control flow and the address arithmetic (so that it stays in uniform registers)
+      // and one elected lane issues the tcgen05 instructions: a loop under `if (lane == 0)` costs ~80 cycles per
+      // MMA and per commit, more per stage than the stage's 540 cycles of tensor work leave room for.
+      const bool me = elect_one() != 0;
+      uint32_t stage = 0, it = 0, reg = 0, reg_par = 0;
+      bool ok = true;
+      [[maybe_unused]] uint32_t gs = 0;
+      const uint32_t idesc = make_idesc_nvfp4_p(2 * C::BM, C::BN);
+      B200_TR_DECL(6);
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+        B200_TR_BEGIN();
+        if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_tempty, (it & 1) ^ 1, 2))) { ok = false; break; }
+        B200_TR_END(0);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          B200_TR_COUNT(5);
+          const uint64_t adesc = make_smem_desc(stage_a(stage), 16, 1024, SWZ_128B);
+          const uint64_t bdesc = make_smem_desc(stage_b(stage), 16, 1024, SWZ_128B);
+#pragma unroll
+          for (int h = 0; h < C::HALVES; ++h) {
+            // both CTAs' writers arrive only after their stage's TMA bytes have landed, so this wait covers the
+            // operands in both shared memories and the region's scales in both Tensor Memories
+            const uint32_t sf_t = tmem_base + C::SF_BASE + reg * C::REGION_COLS;
+            B200_TR_BEGIN();
+            if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_sf_ready + reg * 8, reg_par, 6))) { ok = false; break; }
+            tc_fence_after_sync();
+            B200_TR_END(2);
+            B200_TL(7 + 2 * h, gs == 100);
+            B200_TR_BEGIN();
+#pragma unroll
+            for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
+              const int k = h * C::MMAS_PER_REGION + kk;
+              if (me)
+                umma_nvfp4_ss_2cta(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, sf_t + kk * 4,
+                                   sf_t + C::SFB_COL0 + kk * C::CHUNKS * 4, (kb | k) != 0);
+            }
+            B200_TR_END(3);
+            B200_TL(8 + 2 * h, gs == 100);
+            if (++reg == C::NREG) { reg = 0; reg_par ^= 1; }
+          }
+          if (!ok) break;
+          // frees the stage (and, later, the scale regions it used) in both CTAs
+          B200_TR_BEGIN();
+          if (me) {
+            umma_commit_2cta(bar_empty + stage * 8);
+            umma_commit_2cta(mapa_u32(bar_empty + stage * 8, 1));
+          }
+          __syncwarp();
+          B200_TR_END(4);
+          B200_TL(11, gs == 100);
+          ++gs;
+          if (++stage == STAGES) stage = 0;
+        }
+        if (ok && me) {
+          umma_commit_2cta(bar_tfull);
+          umma_commit_2cta(mapa_u32(bar_tfull, 1));
+        }
+        __syncwarp();
+      }
+      B200_TR_FLUSH(g_trace_fp4p, 6, blockIdx.x == 10 && lane == 0);
+    }
+  } else if (warp >= 4 + C::EW) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::OTHER_REGS));
+    // ---- scale writers: one warp per 32-lane quadrant of this CTA's Tensor Memory, two sets ----
+    const int q = warp & 3;
+    constexpr int NBLK = C::RK * (1 + C::CHUNKS);   // 512-byte blocks per region, A's first
+    const uint32_t set = (uint32_t)(warp - (4 + C::EW)) >> 2;
+    int tile = pair, kb = 0;
+    uint32_t stage = 0, phase = 0, u = 0, reg = 0;
+    auto advance = [&]() {
+      if (++kb == num_kb) { kb = 0; tile += num_pairs; }
+      if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      u += C::HALVES;
+      reg = (reg + C::HALVES) % C::NREG;
+    };
+    if (set == 1) advance();
+    bool ok = true;
+    [[maybe_unused]] uint32_t gs = set;
+    [[maybe_unused]] const bool tl = warp == 4 + C::EW && lane == 0;
+    B200_TR_DECL(5);
+    while (tile < total_tiles && ok) {
+      B200_TR_COUNT(4);
+      B200_TR_BEGIN();
+      if (!mbar_wait(wctx, bar_full + stage * 8, phase, 5)) { ok = false; break; }
+      B200_TR_END(0);
+      B200_TL(2, tl && gs == 100);
+      B200_TR_BEGIN();
+#pragma unroll
+      for (int h = 0; h < C::HALVES; ++h) {
+        const uint32_t uu = u + h, rr = (reg + h) % C::NREG;
+        // region rr was last read by the MMAs of unit uu - NREG; their stage's commit is `empty`
+        if (uu >= (uint32_t)C::NREG) {
+          const uint32_t gp = (uu - C::NREG) / C::HALVES;
+          B200_TR_END(1);
+          B200_TR_BEGIN();
+          if (!mbar_wait(wctx, bar_empty + (gp % STAGES) * 8, (gp / STAGES) & 1, 7)) { ok = false; break; }
+          B200_TR_END(3);
+          B200_TR_BEGIN();
+        }
+        B200_TL(3 + h, tl && gs == 100);
+        tc_fence_after_sync();
+        const uint32_t dst = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_BASE + rr * C::REGION_COLS;
+        const uint32_t src_a = stage_sfa(stage) + (h * C::RK) * 512 + lane * 16;
+        const uint32_t src_b = stage_sfb(stage) + (h * C::RK) * C::CHUNKS * 512 + lane * 16;
+        uint32_t regs[C::REGION_COLS];
+#pragma unroll
+        for (int i = NBLK * 4; i < C::REGION_COLS; ++i) regs[i] = 0u;
+#pragma unroll
+        for (int b = 0; b < C::RK; ++b)
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(regs[4 * b]), "=r"(regs[4 * b + 1]), "=r"(regs[4 * b + 2]), "=r"(regs[4 * b + 3])
+                       : "r"(src_a + b * 512));
+#pragma unroll
+        for (int b = C::RK; b < NBLK; ++b)
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(regs[4 * b]), "=r"(regs[4 * b + 1]), "=r"(regs[4 * b + 2]), "=r"(regs[4 * b + 3])
+                       : "r"(src_b + (b - C::RK) * 512));
+        tmem_st_cols<C::REGION_COLS>(dst, regs);
+      }
+      if (!ok) break;
+      B200_TR_END(1);
+      B200_TR_BEGIN();
+      tmem_wait_st();
+      B200_TR_END(2);
+      B200_TL(5, tl && gs == 100);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        // the stores have completed (wait::st), so a CTA-scope release is enough for the arrive on the leader's
+        // barrier; a cluster-scope release costs ~500 cycles per call
+#pragma unroll
+        for (int h = 0; h < C::HALVES; ++h)
+          mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_sf_ready + ((reg + h) % C::NREG) * 8, 0));
+      }
+      B200_TL(6, tl && gs == 100);
+      gs += 2;
+      advance();
+      advance();
+    }
+    B200_TR_FLUSH(g_trace_fp4p_writer, 5, blockIdx.x == 10 && warp == 4 + C::EW && lane == 0);
+  } else if (warp >= 4) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::EPI_REGS));
+    // ---- epilogue ----
+    const int q = warp & 3;
+    const int half = (warp - 4) >> 2;     // which 128 columns of the tile
+    const int row = q * 32 + lane;
+    const uint32_t tempty_leader = mapa_u32(bar_tempty, 0);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
+      int bm, bn;
+      tile_coords(tile, bm, bn);
+      if (!mbar_wait(wctx, bar_tfull, it & 1, 4)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + half * 128;
+      const int row_g = bm * (2 * C::BM) + (int)rank * C::BM + row;
+      const int col0 = bn * C::BN + half * 128;
+      if (OUT_F32) {
+        float* zrow = static_cast<float*>(Z) + (int64_t)row_g * ldz;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, v);
+          tmem_wait_ld();
+          const int cc = col0 + c * 32;
+          if (row_g < M && cc < N) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              if (cc + i + 3 < N)
+                *reinterpret_cast<float4*>(zrow + cc + i) =
+                    make_float4(__uint_as_float(v[i]) * alpha, __uint_as_float(v[i + 1]) * alpha,
+                                __uint_as_float(v[i + 2]) * alpha, __uint_as_float(v[i + 3]) * alpha);
+              else
+                for (int e = 0; e < 4; ++e)
+                  if (cc + i + e < N) zrow[cc + i + e] = __uint_as_float(v[i + e]) * alpha;
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_addr_cta_release(tempty_leader);   // the loads have completed (wait::ld)
+      } else {
+        // pass 1: Tensor Memory -> packed bf16 registers, then the accumulator goes back to the MMA thread
+        uint32_t pk[64];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_row + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[c * 16 + i] = pack_bf16x2(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster_addr_cta_release(tempty_leader);   // the loads have completed (wait::ld)
+        // pass 2: the thread's 128 columns of its row
+        if (row_g < M) {
+          uint16_t* zrow = static_cast<uint16_t*>(Z) + (int64_t)row_g * ldz;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int cc = col0 + i * 8;
+            if (cc + 7 < N) {
+              *reinterpret_cast<uint4*>(zrow + cc) = make_uint4(pk[i * 4], pk[i * 4 + 1], pk[i * 4 + 2], pk[i * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (cc + e < N) zrow[cc + e] = (uint16_t)((pk[i * 4 + (e >> 1)] >> ((e & 1) * 16)) & 0xFFFF);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // neither CTA leaves while its partner may still touch its memory
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_2cta(tmem_base, 512);
+  }
+}
+
+}  // namespace b200
+
+int b200_nvfp4_prepare_b_scales(const void* ys, int N, int K, int64_t ld_ys, int bn, void* out, cudaStream_t stream);
+
+// Scratch: [2 ceil(M/256)] blocks of A scales (128-row tiles), then [ceil(N/256)] tiles of B scales (2 chunks).
+size_t b200_nvfp4_pair_scratch_bytes(int M, int N, int K) {
+  const size_t kq = (size_t)((K + 255) / 256) * 4;
+  return ((size_t)2 * ((M + 255) / 256) + (size_t)2 * ((N + 255) / 256)) * kq * 512;
+}
+
+int b200_gemm_nvfp4_pair_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
+                                  int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
+                                  int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream) {
+  using namespace b200;
+  using C = F4P;
+  const b200h::DeviceInfo* di = b200h::device_info();
+  if (!di) return B200_ERR_CUDA;
+  CUtensorMap tmA, tmB;
+  int rc;
+  const uint64_t row_bytes = (uint64_t)K / 2;
+  if ((rc = b200h::encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, row_bytes, (uint64_t)M, (uint64_t)ldx, 128,
+                                  C::BM, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, row_bytes, (uint64_t)N, (uint64_t)ldy, 128,
+                                  C::BN / 2, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
+  const int kq = ((K + 255) / 256) * 4;
+  const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
+  uint8_t* s = static_cast<uint8_t*>(scratch);
+  const size_t sfb_off = (size_t)2 * tiles_m * kq * 512;
+  // A scales as 128-row tiles: 2 tiles_m of them (rows past M are written as zeros); B scales as 256-row tiles
+  if ((rc = b200_nvfp4_prepare_b_scales(xs, M, K, ld_xs, 128, s, stream))) return rc;
+  if (2 * tiles_m > (M + 127) / 128)   // the last pair's second CTA has no rows: its blocks must still read as zero
+    B200_CUDA_CHECK(cudaMemsetAsync(s + (size_t)((M + 127) / 128) * kq * 512, 0, (size_t)kq * 512, stream));
+  if ((rc = b200_nvfp4_prepare_b_scales(ys, N, K, ld_ys, 256, s + sfb_off, stream))) return rc;
+  static b200h::DeviceOnce attr_done[2];
+  auto launch = [&](auto kern, int which) -> int {
+    if (!attr_done[which].test(di->ordinal)) {
+      B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+      attr_done[which].set(di->ordinal);
+    }
+    const int tiles = tiles_m * tiles_n;
+    const int all_pairs = di->sm_count / 2;
+    const int pairs = tiles < all_pairs ? tiles : all_pairs;
+    kern<<<pairs * 2, C::THREADS, C::TOTAL, stream>>>(tmA, tmB, s, s + sfb_off, z, M, N, K, ldz, alpha, 8, di->status);
+    B200_CUDA_CHECK(cudaGetLastError());
+    return B200_OK;
+  };
+  return out_f32 ? launch(gemm_nvfp4_pair_kernel<true>, 0) : launch(gemm_nvfp4_pair_kernel<false>, 1);
+}
+
+#ifdef B200TILE_TRACE
+int b200_trace_read_fp4_pair(long long* out) {
+  if (cudaMemcpyFromSymbol(out, b200::g_trace_fp4p, 8 * sizeof(long long)) != cudaSuccess) return 1;
+  if (cudaMemcpyFromSymbol(out + 10, b200::g_trace_fp4p_writer, 7 * sizeof(long long)) != cudaSuccess) return 1;
+  return cudaMemcpyFromSymbol(out + 17, b200::g_trace_fp4p_producer, 3 * sizeof(long long)) != cudaSuccess;
+}
+// out[0..12]: clock64 of the events of global stage 100 in the leader CTA of pair 5 -- producer: 0 stage free seen,
+// 1 copies issued; writer warp 12: 2 stage landed seen, 3 / 4 region free for half 0 / 1, 5 stores complete,
+// 6 arrived; MMA thread: 7 / 9 scales ready seen (half 0 / 1), 8 / 10 MMAs of the half issued, 11 committed;
+// producer: 12 the same slot seen free again (its MMAs have completed)
+int b200_trace_read_fp4_pair_tl(long long* out) {
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fp4p_tl, 13 * sizeof(long long)) != cudaSuccess;
+}
+#endif

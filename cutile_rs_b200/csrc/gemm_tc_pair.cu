@@ -417,7 +417,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster_addr(tempty_leader + buf * 8);
+      if (lane == 0) mbar_arrive_cluster_addr_cta_release(tempty_leader + buf * 8);   // the loads have completed (wait::ld): no cluster-scope release, which costs ~500 cycles
       if (q_last >= q_first) {
         // every epilogue thread of this CTA has read the partials: clear their flags for the next launch
         named_bar_sync(1, 32 * L::EW);

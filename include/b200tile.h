@@ -366,7 +366,8 @@ B200TILE_API int b200tile_linear_fp8_blk128(const void* x, const void* y, const 
  *   workspace  device scratch of at least b200tile_linear_nvfp4_workspace_bytes(m, n, k) bytes,
  *              16-byte aligned: the scales are re-laid out into it on every call (stream-ordered);
  *              calls that overlap on the device must not share a workspace
- *   config     -1 = default (1; 0 when m <= 32), 0/1/2 = B tiles of 128/192/256 rows */
+ *   config     -1 = default (0 when m <= 32, 3 when m >= 512, else 1), 0/1/2 = single-CTA kernel with B tiles of
+ *              128/192/256 rows, 3 = CTA pairs (cta_group::2) with 256 x 256 tiles */
 B200TILE_API uint64_t b200tile_linear_nvfp4_workspace_bytes(int m, int n, int k);
 B200TILE_API int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales,
                                        const void* y_scales, void* z, const char* out_dtype, int m,

@@ -70,7 +70,7 @@ def test_rust_sys_crate_declares_every_header_symbol():
     assert subprocess.call([sys.executable, gen, "--check"]) == 0, "run rust/b200tile-sys/gen_ffi.py"
     rs = open(os.path.join(ROOT, "rust", "b200tile-sys", "src", "lib.rs")).read()
     assert sorted(set(re.findall(r"pub fn (b200tile_\w+)\(", rs))) == declared_symbols()
-    assert lib_query_linear_tile() == (3, 1)
+    assert lib_query_linear_tile() == (4, 1)   # NVFP4: three single-CTA tiles and the CTA-pair tile
 
 
 def lib_query_linear_tile():

@@ -47,6 +47,29 @@ def test_matches_oracle(b200, oracle, config, m, n, k, out):
     assert oracle.rel_frobenius(got, ref) <= (FP4_TOL if out == "bf16" else 1e-5)
 
 
+@pytest.mark.parametrize("m,n,k,out", [(256, 256, 256, "f32"), (300, 520, 320, "f32"), (512, 768, 1024, "f32"),
+                                       (1000, 1000, 512, "bf16"), (130, 200, 64, "bf16")])
+def test_cta_pair_kernel_matches_oracle(b200, oracle, m, n, k, out):
+    """Config 3 (CTA pairs, 256 x 256 tiles): scales that differ per row and per 16-block, ragged edges in M and N
+    (a pair whose second CTA has no rows at all included); with an f32 output every product and sum is exact."""
+    g = torch.Generator().manual_seed(9 + m)
+    xp = torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8)
+    yp = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+    xs = (0x30 + torch.randint(0, 24, (m, k // 16), generator=g)).to(torch.uint8)   # 0.5 .. 3.5
+    ys = (0x30 + torch.randint(0, 24, (n, k // 16), generator=g)).to(torch.uint8)
+    got = _run(xp.cuda(), yp.cuda(), xs.cuda(), ys.cuda(), m, n, k, out, 0.5, config=3).float().cpu().numpy()
+    ref = oracle.cpu_gemm_nt(oracle.dequant_nvfp4(xp.numpy(), xs.numpy()), oracle.dequant_nvfp4(yp.numpy(), ys.numpy()),
+                             alpha=0.5, threads=0)
+    assert not np.isnan(got).any()
+    assert oracle.rel_frobenius(got, ref) <= (FP4_TOL if out == "bf16" else 1e-6)
+    if out == "f32":
+        single = _run(xp.cuda(), yp.cuda(), xs.cuda(), ys.cuda(), m, n, k, out, 0.5, config=1).cpu().numpy()
+        assert np.array_equal(got, single)      # same products, same order of accumulation along K
+    st = _lib.StatusC()
+    _lib.check(b200.b200tile_status(torch.cuda.current_stream().cuda_stream, st))
+    assert st.code == 0
+
+
 def test_scale_placement(b200, oracle):
     # scales that differ per row and per 16-block expose any mistake in the Tensor-Memory scale layout
     m, n, k = 256, 384, 256
