@@ -1188,13 +1188,12 @@ def _print_trace(lib, args) -> None:
             print(f"scale-writer warp per stage: stage-full wait {v[10] / w:.0f}, region wait + loads + store issue "
                   f"{v[11] / w:.0f}, store completion {v[12] / w:.0f}, hand-off {v[13] / w:.0f}; total {v[15] / w:.0f}")
         if args.config == 3:
-            tl = (ctypes.c_longlong * 20)()
+            tl = (ctypes.c_longlong * 40)()
             if lib.b200tile_trace_read(b"block_scaled_pair_timeline", tl) == 0:
-                t0 = tl[0]
-                names = ["slot free seen by producer", "copies issued", "landed seen by writer", "region 0 free", "region 1 free",
-                         "scale stores complete", "writer arrived", "scales 0 ready seen by MMA thread", "MMAs 0 issued",
-                         "scales 1 ready seen", "MMAs 1 issued", "committed", "slot free again"]
-                print("time line of one stage (cycles): " + ", ".join(f"{n} {tl[i] - t0}" for i, n in enumerate(names)))
+                print("time lines of 8 consecutive stages (cycles after the producer saw the first slot free): "
+                      "slot free / copies issued / landed / scales ready seen by the MMA warp / committed")
+                for g in range(8):
+                    print("   " + " ".join(f"{tl[5 * g + e] - tl[0]:6d}" for e in range(5)))
         pn = max(v[19], 1)
         print(f"TMA producer per stage: stage-empty wait {v[17] / pn:.0f}, issue of the copies {v[18] / pn:.0f}")
         return

@@ -1849,7 +1849,8 @@ int b200tile_prepare(const char* kernel, const char* const* generics, int n_gene
 
 #ifdef B200TILE_TRACE
 // Diagnostic builds only: copies the cycle counters of one traced kernel ("gemm_pair", "fmha",
-// "fmha_alt", "fmha_alt_t", "block_scaled", "block_scaled_pair") into out[20]; see csrc/trace.cuh.
+// "fmha_alt", "fmha_alt_t", "block_scaled", "block_scaled_pair") into out[20]
+// ("block_scaled_pair_timeline": out[40]); see csrc/trace.cuh.
 B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!which || !out) return B200TILE_ERR_INVALID;
   for (int i = 0; i < 20; ++i) out[i] = 0;

@@ -32,9 +32,10 @@ namespace b200 {
 __device__ long long g_trace_fp4p[8];
 __device__ long long g_trace_fp4p_writer[8];
 __device__ long long g_trace_fp4p_producer[8];
-// time line (clock64 of one SM) of global stage 100 of the leader CTA of pair 5: see b200_trace_read_fp4_pair_tl
-__device__ long long g_trace_fp4p_tl[16];
-#define B200_TL(i, cond) if ((cond) && blockIdx.x == 10) g_trace_fp4p_tl[i] = clock64()
+// time lines (clock64 of one SM) of global stages 96..103 of the leader CTA of pair 5, five events per stage:
+// see b200_trace_read_fp4_pair_tl
+__device__ long long g_trace_fp4p_tl[40];
+#define B200_TL(e, g) if ((g) >= 96u && (g) < 104u && blockIdx.x == 10) g_trace_fp4p_tl[((g) - 96u) * 5 + (e)] = clock64()
 #else
 #define B200_TL(i, cond)
 #endif
@@ -68,7 +69,13 @@ struct F4P {
   static constexpr int SFB_COL0 = 4 * RK;
   static constexpr int STAGE_TX = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
   static constexpr int STAGE_BYTES = (STAGE_TX + 1023) / 1024 * 1024;
-  static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
+  // bf16 output staging: one [32 rows][128 B] swizzled buffer per epilogue warp, stored with TMA.  (Storing rows
+  // straight from registers -- 16 bytes per lane, 32 different rows per instruction -- made every tile boundary a
+  // burst of half-filled sectors from all 148 CTAs at once, behind which the next tile's loads waited up to 6000
+  // cycles.)
+  static constexpr int OFF_C = STAGES * STAGE_BYTES;
+  static constexpr int C_WARP_BYTES = 32 * 128;
+  static constexpr int OFF_BAR = OFF_C + EW * C_WARP_BYTES;
   static constexpr int NUM_BARS = 2 * STAGES + 2 + NREG;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
@@ -95,7 +102,7 @@ __host__ __device__ constexpr uint32_t make_idesc_nvfp4_p(uint32_t M, uint32_t N
 template <bool OUT_F32>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(F4P::THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                       const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z, int M,
+                       const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z, int M,
                        int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
   using C = F4P;
   constexpr int STAGES = C::STAGES;
@@ -129,6 +136,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (!OUT_F32) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(misc)), 512);
@@ -175,8 +183,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           B200_TR_BEGIN();
           if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
           B200_TR_END(0);
-          B200_TL(0, gs == 100);
-          B200_TL(12, gs == 100 + STAGES);
+          B200_TL(0, gs);
           B200_TR_BEGIN();
           const uint32_t full = bar_full + stage * 8;
           mbar_expect_tx(full, C::STAGE_TX);
@@ -185,7 +192,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           bulk_load_1d_p(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
           bulk_load_1d_p(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
           B200_TR_END(1);
-          B200_TL(1, gs == 100);
+          B200_TL(1, gs);
           ++gs;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -222,7 +229,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_sf_ready + reg * 8, reg_par, 6))) { ok = false; break; }
             tc_fence_after_sync();
             B200_TR_END(2);
-            B200_TL(7 + 2 * h, gs == 100);
+            if (h == 0) { B200_TL(3, gs); }
             B200_TR_BEGIN();
 #pragma unroll
             for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
@@ -232,7 +239,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                                    sf_t + C::SFB_COL0 + kk * C::CHUNKS * 4, (kb | k) != 0);
             }
             B200_TR_END(3);
-            B200_TL(8 + 2 * h, gs == 100);
             if (++reg == C::NREG) { reg = 0; reg_par ^= 1; }
           }
           if (!ok) break;
@@ -244,7 +250,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           }
           __syncwarp();
           B200_TR_END(4);
-          B200_TL(11, gs == 100);
+          B200_TL(4, gs);
           ++gs;
           if (++stage == STAGES) stage = 0;
         }
@@ -273,14 +279,14 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     if (set == 1) advance();
     bool ok = true;
     [[maybe_unused]] uint32_t gs = set;
-    [[maybe_unused]] const bool tl = warp == 4 + C::EW && lane == 0;
+    [[maybe_unused]] const bool tl = q == 0 && lane == 0;   // first warp of either set
     B200_TR_DECL(5);
     while (tile < total_tiles && ok) {
       B200_TR_COUNT(4);
       B200_TR_BEGIN();
       if (!mbar_wait(wctx, bar_full + stage * 8, phase, 5)) { ok = false; break; }
       B200_TR_END(0);
-      B200_TL(2, tl && gs == 100);
+      if (tl) { B200_TL(2, gs); }
       B200_TR_BEGIN();
 #pragma unroll
       for (int h = 0; h < C::HALVES; ++h) {
@@ -294,7 +300,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           B200_TR_END(3);
           B200_TR_BEGIN();
         }
-        B200_TL(3 + h, tl && gs == 100);
         tc_fence_after_sync();
         const uint32_t dst = tmem_base + ((uint32_t)(q * 32) << 16) + C::SF_BASE + rr * C::REGION_COLS;
         const uint32_t src_a = stage_sfa(stage) + (h * C::RK) * 512 + lane * 16;
@@ -319,7 +324,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       B200_TR_BEGIN();
       tmem_wait_st();
       B200_TR_END(2);
-      B200_TL(5, tl && gs == 100);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -329,7 +333,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int h = 0; h < C::HALVES; ++h)
           mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_sf_ready + ((reg + h) % C::NREG) * 8, 0));
       }
-      B200_TL(6, tl && gs == 100);
       gs += 2;
       advance();
       advance();
@@ -391,23 +394,30 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster_addr_cta_release(tempty_leader);   // the loads have completed (wait::ld)
-        // pass 2: the thread's 128 columns of its row
-        if (row_g < M) {
-          uint16_t* zrow = static_cast<uint16_t*>(Z) + (int64_t)row_g * ldz;
+        // pass 2: registers -> swizzled staging -> TMA store (which clips at M and N), 64 columns at a time
+        const uint32_t sbuf = base + C::OFF_C + (uint32_t)(warp - 4) * C::C_WARP_BYTES;
+        const uint32_t row_addr = sbuf + lane * 128;
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const int cc = col0 + i * 8;
-            if (cc + 7 < N) {
-              *reinterpret_cast<uint4*>(zrow + cc) = make_uint4(pk[i * 4], pk[i * 4 + 1], pk[i * 4 + 2], pk[i * 4 + 3]);
-            } else {
+        for (int c = 0; c < 2; ++c) {
+          if (lane == 0) tma_store_wait_read<0>();   // the previous store has read the buffer
+          __syncwarp();
 #pragma unroll
-              for (int e = 0; e < 8; ++e)
-                if (cc + e < N) zrow[cc + e] = (uint16_t)((pk[i * 4 + (e >> 1)] >> ((e & 1) * 16)) & 0xFFFF);
-            }
+          for (int j = 0; j < 8; ++j) {
+            const uint32_t dst = row_addr + ((uint32_t)(j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[c * 32 + j * 4]),
+                         "r"(pk[c * 32 + j * 4 + 1]), "r"(pk[c * 32 + j * 4 + 2]), "r"(pk[c * 32 + j * 4 + 3])
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, sbuf, col0 + c * 64, bm * (2 * C::BM) + (int)rank * C::BM + q * 32);
+            tma_store_commit();
           }
         }
       }
     }
+    if (!OUT_F32 && lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
@@ -445,6 +455,10 @@ int b200_gemm_nvfp4_pair_dispatch(int out_f32, const void* x, const void* y, con
   if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, row_bytes, (uint64_t)N, (uint64_t)ldy, 128,
                                   C::BN / 2, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
+  CUtensorMap tmC = tmA;   // only the bf16 instantiation reads it
+  if (!out_f32 && (rc = b200h::encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, z, (uint64_t)N, (uint64_t)M,
+                                              (uint64_t)ldz * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
   const int kq = ((K + 255) / 256) * 4;
   const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
   uint8_t* s = static_cast<uint8_t*>(scratch);
@@ -463,7 +477,8 @@ int b200_gemm_nvfp4_pair_dispatch(int out_f32, const void* x, const void* y, con
     const int tiles = tiles_m * tiles_n;
     const int all_pairs = di->sm_count / 2;
     const int pairs = tiles < all_pairs ? tiles : all_pairs;
-    kern<<<pairs * 2, C::THREADS, C::TOTAL, stream>>>(tmA, tmB, s, s + sfb_off, z, M, N, K, ldz, alpha, 8, di->status);
+    kern<<<pairs * 2, C::THREADS, C::TOTAL, stream>>>(tmA, tmB, tmC, s, s + sfb_off, z, M, N, K, ldz, alpha, 8,
+                                                     di->status);
     B200_CUDA_CHECK(cudaGetLastError());
     return B200_OK;
   };
@@ -476,11 +491,10 @@ int b200_trace_read_fp4_pair(long long* out) {
   if (cudaMemcpyFromSymbol(out + 10, b200::g_trace_fp4p_writer, 7 * sizeof(long long)) != cudaSuccess) return 1;
   return cudaMemcpyFromSymbol(out + 17, b200::g_trace_fp4p_producer, 3 * sizeof(long long)) != cudaSuccess;
 }
-// out[0..12]: clock64 of the events of global stage 100 in the leader CTA of pair 5 -- producer: 0 stage free seen,
-// 1 copies issued; writer warp 12: 2 stage landed seen, 3 / 4 region free for half 0 / 1, 5 stores complete,
-// 6 arrived; MMA thread: 7 / 9 scales ready seen (half 0 / 1), 8 / 10 MMAs of the half issued, 11 committed;
-// producer: 12 the same slot seen free again (its MMAs have completed)
+// out[5 g + e], g = 0..7 (global stages 96..103 of the leader CTA of pair 5), clock64 of event e -- 0: the producer
+// sees the slot free, 1: it has issued the stage's copies, 2: a writer warp sees the stage landed, 3: the MMA warp
+// sees the stage's first scale region ready, 4: it has committed the stage
 int b200_trace_read_fp4_pair_tl(long long* out) {
-  return cudaMemcpyFromSymbol(out, b200::g_trace_fp4p_tl, 13 * sizeof(long long)) != cudaSuccess;
+  return cudaMemcpyFromSymbol(out, b200::g_trace_fp4p_tl, 40 * sizeof(long long)) != cudaSuccess;
 }
 #endif
