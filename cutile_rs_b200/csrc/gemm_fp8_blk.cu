@@ -29,7 +29,11 @@ struct Fp8Smem {
   static constexpr int B_BYTES = F8_BN * F8_BK;  // 32 KiB
   static constexpr int OFF_A = 0;
   static constexpr int OFF_B = OFF_A + F8_STAGES * A_BYTES;
-  static constexpr int OFF_BAR = OFF_B + F8_STAGES * B_BYTES;
+  // bf16 output staging for TMA stores: one [32 rows][128 B] swizzled buffer per promotion warp (rows stored
+  // straight from registers reach L2 as half-filled sectors from all CTAs at once and hold up the next tile's loads)
+  static constexpr int OFF_C = OFF_B + F8_STAGES * B_BYTES;
+  static constexpr int C_WARP_BYTES = 32 * 128;
+  static constexpr int OFF_BAR = OFF_C + 8 * C_WARP_BYTES;
   static constexpr int NUM_BARS = 2 * F8_STAGES + 4;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
@@ -38,7 +42,7 @@ struct Fp8Smem {
 template <bool OUT_F32>
 __global__ void __launch_bounds__(F8_THREADS, 1)
 gemm_fp8_blk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const float* __restrict__ sa, const float* __restrict__ sb, void* __restrict__ Z,
+                    const __grid_constant__ CUtensorMap tmC, const float* __restrict__ sa, const float* __restrict__ sb, void* __restrict__ Z,
                     int M, int N, int K, int64_t ldz, int ld_sa, int ld_sb, float alpha, int group_m,
                     uint32_t idesc, uint32_t* status) {
   using L = Fp8Smem;
@@ -67,6 +71,7 @@ gemm_fp8_blk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (!OUT_F32) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(misc)), 512);
@@ -184,7 +189,33 @@ gemm_fp8_blk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(s, __uint_as_float(v1[i]), acc[96 + i]);
       }
       if (!ok) break;
-      // epilogue: one output row (128 contiguous columns) per thread, written straight to global
+      if constexpr (!OUT_F32) {
+        // epilogue: registers -> bf16 -> swizzled staging -> TMA store (which clips at M and N), 64 columns at a time
+        const uint32_t sbuf = base + L::OFF_C + (uint32_t)(warp - 4) * L::C_WARP_BYTES;
+        const uint32_t row_addr = sbuf + lane * 128;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          if (lane == 0) tma_store_wait_read<0>();   // the previous store has read the buffer
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float* a = acc + c * 64 + j * 8;
+            const uint32_t dst = row_addr + ((uint32_t)(j ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst),
+                         "r"(pack_bf16x2(a[0] * alpha, a[1] * alpha)), "r"(pack_bf16x2(a[2] * alpha, a[3] * alpha)),
+                         "r"(pack_bf16x2(a[4] * alpha, a[5] * alpha)), "r"(pack_bf16x2(a[6] * alpha, a[7] * alpha))
+                         : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, sbuf, col0 + c * 64, bm * F8_BM + q * 32);
+            tma_store_commit();
+          }
+        }
+        continue;
+      }
+      // f32 output: one output row (128 contiguous columns) per thread, written straight to global
       if (row_ok && col_ok) {
         if (OUT_F32) {
           float* zrow = static_cast<float*>(Z) + (int64_t)row_g * ldz + col0;
@@ -217,6 +248,7 @@ gemm_fp8_blk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
     }
+    if (!OUT_F32 && lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
@@ -242,6 +274,10 @@ static int launch_fp8(const void* x, const void* y, const float* xs, const float
   if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, (uint64_t)K, (uint64_t)N,
                                   (uint64_t)ldy, F8_BK, F8_BN, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
+  CUtensorMap tmC = tmA;   // read only by the bf16 instantiation
+  if (!OUT_F32 && (rc = b200h::encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, z, (uint64_t)N, (uint64_t)M,
+                                              (uint64_t)ldz * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)))
+    return rc;
   auto kern = gemm_fp8_blk_kernel<OUT_F32>;
   static b200h::DeviceOnce attr_done;
   if (!attr_done.test(di->ordinal)) {
@@ -251,7 +287,7 @@ static int launch_fp8(const void* x, const void* y, const float* xs, const float
   const int tiles = ((M + F8_BM - 1) / F8_BM) * ((N + F8_BN - 1) / F8_BN);
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;
   const uint32_t idesc = make_idesc(FMT_E4M3, FMT_E4M3, 0, 0, F8_BM, F8_BN);
-  kern<<<grid, F8_THREADS, L::TOTAL, stream>>>(tmA, tmB, xs, ys, z, M, N, K, ldz, ld_xs, ld_ys, alpha, 8,
+  kern<<<grid, F8_THREADS, L::TOTAL, stream>>>(tmA, tmB, tmC, xs, ys, z, M, N, K, ldz, ld_xs, ld_ys, alpha, 8,
                                                idesc, di->status);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;

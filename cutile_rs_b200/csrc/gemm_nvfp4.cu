@@ -93,6 +93,15 @@ struct Fp4Cfg {
   static constexpr int XROW_BYTES = 4 * KQ_PER_STAGE;          // one row's A scales for one stage
   static constexpr int OFF_XBUF = (OFF_MISC + 16 + 15) / 16 * 16;   // [2][128 rows][XROW_BYTES]
   static constexpr int TOTAL = OFF_XBUF + 4 * F4_BM * XROW_BYTES + 1024;   // two buffers per writer set
+  // bf16 output staging for TMA stores, one [32 rows][CW columns] swizzled buffer per epilogue warp, where shared
+  // memory has room for it (every configuration but the short-A-tile one and 256-row B tiles).  Rows stored
+  // straight from registers (16 bytes per lane, 32 rows per instruction) reach L2 as half-filled sectors from all
+  // CTAs at once, and the next tile's loads queue behind them.
+  static constexpr int CW = BN % 64 == 0 ? 64 : 32;                 // columns per store: 128- or 64-byte rows
+  static constexpr int C_WARP_BYTES = 32 * CW * 2;
+  static constexpr int OFF_CSTG = (OFF_XBUF + 4 * F4_BM * XROW_BYTES + 1023) / 1024 * 1024;
+  static constexpr int TOTAL_STG = OFF_CSTG + 4 * C_WARP_BYTES + 1024;
+  static constexpr bool STG_FITS = AROWS == 128 && TOTAL_STG <= 232448;
 };
 
 // ---------------------------------------------------------------------------
@@ -188,7 +197,7 @@ __host__ __device__ constexpr uint32_t make_idesc_mxf4(uint32_t M, uint32_t N, u
 template <int BN, bool OUT_F32, int FMT, bool A_DIRECT, int AROWS>
 __global__ void __launch_bounds__(F4_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                  const uint8_t* __restrict__ xs, int64_t ld_xs, int kq_valid, const uint8_t* __restrict__ sfa,
+                  const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ xs, int64_t ld_xs, int kq_valid, const uint8_t* __restrict__ sfa,
                   const uint8_t* __restrict__ sfb, void* __restrict__ Z,
                   int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
   using C = Fp4Cfg<BN, FMT, A_DIRECT, AROWS>;
@@ -225,6 +234,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if (!OUT_F32 && C::STG_FITS) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(misc)), 512);
@@ -490,6 +500,47 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
       const int row_g = bm * F4_BM + row;
       const int col0 = bn * BN;
+      if constexpr (!OUT_F32 && C::STG_FITS) {
+        // Tensor Memory -> bf16 -> swizzled staging -> TMA store (which clips at M and N), CW columns at a time
+        constexpr int CW = C::CW;
+        const uint32_t sbuf = base + C::OFF_CSTG + (uint32_t)q * C::C_WARP_BYTES;
+        const uint32_t row_addr = sbuf + lane * (CW * 2);
+#pragma unroll 1
+        for (int c = 0; c < BN / CW; ++c) {
+          uint32_t pk[CW / 2];
+#pragma unroll
+          for (int h = 0; h < CW / 32; ++h) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(t_row + c * CW + h * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              pk[h * 16 + i] = pack_bf16x2(__uint_as_float(v[2 * i]) * alpha, __uint_as_float(v[2 * i + 1]) * alpha);
+          }
+          if (c == BN / CW - 1) {   // the accumulator has been read: hand it back before the last store
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + buf * 8);
+          }
+          if (lane == 0) tma_store_wait_read<0>();   // the previous store has read the buffer
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < CW / 8; ++j) {
+            // 16-byte chunk j of the row: 128-byte rows swizzle with row % 8, 64-byte rows with (row / 2) % 4
+            const uint32_t sw = CW == 64 ? (uint32_t)(lane & 7) : (uint32_t)((lane >> 1) & 3);
+            const uint32_t dst = row_addr + (((uint32_t)j ^ sw) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(pk[j * 4]), "r"(pk[j * 4 + 1]),
+                         "r"(pk[j * 4 + 2]), "r"(pk[j * 4 + 3]) : "memory");
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, sbuf, col0 + c * CW, bm * F4_BM + q * 32);
+            tma_store_commit();
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -533,6 +584,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + buf * 8);
     }
+    if (!OUT_F32 && C::STG_FITS && lane == 0) tma_store_wait_all<0>();
   }
 
   tc_fence_before_sync();
@@ -575,6 +627,13 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
                                   (uint64_t)ldy, 128, BN, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   // scale blocks (4 scale bytes per row) along K: padded to whole stages / those the tensors hold
+  constexpr bool STG = !OUT_F32 && C::STG_FITS;
+  constexpr int SMEM = STG ? C::TOTAL_STG : C::TOTAL;
+  CUtensorMap tmC = tmA;   // read only by the instantiations that stage their bf16 output
+  if (STG && (rc = b200h::encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, z, (uint64_t)N, (uint64_t)M,
+                                         (uint64_t)ldz * 2, C::CW, 32,
+                                         C::CW == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)))
+    return rc;
   const int kq = FP4 ? ((K + 255) / 256) * C::KQ_PER_STAGE : (K + 127) / 128;
   const int kq_valid = FMT == 1 ? K / 64 : K / 128;
   const int tiles_m = (M + F4_BM - 1) / F4_BM, tiles_n = (N + BN - 1) / BN;
@@ -596,12 +655,12 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
   auto kern = gemm_nvfp4_kernel<BN, OUT_F32, FMT, A_DIRECT, AROWS>;
   static b200h::DeviceOnce attr_done;
   if (!attr_done.test(di->ordinal)) {
-    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
     attr_done.set(di->ordinal);
   }
   const int tiles = tiles_m * tiles_n;
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;
-  kern<<<grid, F4_THREADS, C::TOTAL, stream>>>(tmA, tmB, static_cast<const uint8_t*>(xs), ld_xs, kq_valid, scratch,
+  kern<<<grid, F4_THREADS, SMEM, stream>>>(tmA, tmB, tmC, static_cast<const uint8_t*>(xs), ld_xs, kq_valid, scratch,
                                                scratch + sfb_off, z, M, N, K, ldz, alpha, 8, di->status);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
