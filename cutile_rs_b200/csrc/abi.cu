@@ -82,10 +82,14 @@ int b200_gemm_mxfp8_dispatch(int out_f32, const void* x, const void* y, const vo
                              int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                              int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
 size_t b200_mxf4_scratch_bytes(int M, int N, int K);
-size_t b200_nvfp4_pair_scratch_bytes(int M, int N, int K);
-int b200_gemm_nvfp4_pair_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
-                                  int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
-                                  int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
+// CTA-pair kernels of the block-scaled formats (fmt 1 = NVFP4, 2 = MXFP4, 0 = MXFP8)
+size_t b200_blockscaled_pair_scratch_bytes(int fmt, int M, int N, int K);
+int b200_gemm_blockscaled_pair_dispatch(int fmt, int out_f32, const void* x, const void* y, const void* xs,
+                                        const void* ys, void* z, int M, int N, int K, int64_t ldx, int64_t ldy,
+                                        int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha, void* scratch,
+                                        cudaStream_t stream);
+// from this many rows on the CTA-pair kernels are ahead of the single-CTA ones (measured)
+static const int kPairMinRows = 512;
 int b200_gemm_mxf4_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
                             int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
                             int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream);
@@ -551,7 +555,7 @@ uint64_t b200tile_linear_nvfp4_workspace_bytes(int m, int n, int k) {
     const size_t b = b200_nvfp4_scratch_bytes(m, n, k, kNvfp4Bn[i]);
     if (b > best) best = b;
   }
-  const size_t pair = b200_nvfp4_pair_scratch_bytes(m, n, k);
+  const size_t pair = b200_blockscaled_pair_scratch_bytes(1, m, n, k);
   if (pair > best) best = pair;
   return (uint64_t)best;
 }
@@ -582,9 +586,9 @@ int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales, co
   // default: CTA pairs (256 x 256 tiles) from 512 rows on (measured ahead of the single-CTA tiles at every such
   // shape: 8 % at 4096 x 14336 x 4096, 24 % at 8192 x 28672 x 8192); below that 192-row B tiles, and decode-sized M
   // takes 128-row tiles (more CTAs for the weight stream, and the short-A-tile configuration exists for that tile only)
-  if (config < 0) config = m <= 32 ? 0 : (m >= 512 ? 3 : 1);
+  if (config < 0) config = m <= 32 ? 0 : (m >= kPairMinRows ? 3 : 1);
   if (config == 3) {   // CTA pairs, 256 x 256 tiles
-    const size_t need = b200_nvfp4_pair_scratch_bytes(m, n, k);
+    const size_t need = b200_blockscaled_pair_scratch_bytes(1, m, n, k);
     if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
       return set_error(B200TILE_ERR_INVALID,
                        "linear_nvfp4: workspace of %llu bytes (16-byte aligned) required, got %llu",
@@ -592,8 +596,8 @@ int b200tile_linear_nvfp4(const void* x, const void* y, const void* x_scales, co
     if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(y) & 15) != 0 || ldx % 16 != 0 ||
         ldy % 16 != 0)
       return set_error(B200TILE_ERR_ALIGN, "linear_nvfp4: operand rows must be 16-byte aligned");
-    return b200_gemm_nvfp4_pair_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs, ld_ys,
-                                         alpha, workspace, static_cast<cudaStream_t>(cu_stream));
+    return b200_gemm_blockscaled_pair_dispatch(1, out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs,
+                                               ld_ys, alpha, workspace, static_cast<cudaStream_t>(cu_stream));
   }
   const int bn = kNvfp4Bn[config];
   const size_t need = b200_nvfp4_scratch_bytes(m, n, k, bn);
@@ -724,7 +728,8 @@ int b200tile_nvfp4_unregister_weight_scales(const void* y_scales) {
 // ---------------------------------------------------------------------------
 uint64_t b200tile_linear_mxfp8_workspace_bytes(int m, int n, int k) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  return (uint64_t)b200_mxfp8_scratch_bytes(m, n, k);
+  const size_t a = b200_mxfp8_scratch_bytes(m, n, k), b = b200_blockscaled_pair_scratch_bytes(0, m, n, k);
+  return (uint64_t)(a > b ? a : b);
 }
 
 int b200tile_linear_mxfp8(const void* x, const void* y, const void* x_scales, const void* y_scales,
@@ -748,11 +753,15 @@ int b200tile_linear_mxfp8(const void* x, const void* y, const void* x_scales, co
   else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_mxfp8: unsupported output type '%s'", out_dtype);
   if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
     return set_error(B200TILE_ERR_ALIGN, "linear_mxfp8: output must be 16-byte aligned with a 16-byte pitch");
-  const size_t need = b200_mxfp8_scratch_bytes(m, n, k);
+  const bool pair = m >= kPairMinRows;   // CTA pairs with 256 x 256 tiles, else single CTAs with 224-row B tiles
+  const size_t need = pair ? b200_blockscaled_pair_scratch_bytes(0, m, n, k) : b200_mxfp8_scratch_bytes(m, n, k);
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
     return set_error(B200TILE_ERR_INVALID,
                      "linear_mxfp8: workspace of %llu bytes (16-byte aligned) required, got %llu",
                      (unsigned long long)need, (unsigned long long)workspace_bytes);
+  if (pair)
+    return b200_gemm_blockscaled_pair_dispatch(0, out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs,
+                                               ld_ys, alpha, workspace, static_cast<cudaStream_t>(cu_stream));
   return b200_gemm_mxfp8_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs, ld_ys,
                                   alpha, workspace, static_cast<cudaStream_t>(cu_stream));
 }
@@ -762,7 +771,8 @@ int b200tile_linear_mxfp8(const void* x, const void* y, const void* x_scales, co
 // ---------------------------------------------------------------------------
 uint64_t b200tile_linear_mxfp4_workspace_bytes(int m, int n, int k) {
   if (m <= 0 || n <= 0 || k <= 0) return 0;
-  return (uint64_t)b200_mxf4_scratch_bytes(m, n, k);
+  const size_t a = b200_mxf4_scratch_bytes(m, n, k), b = b200_blockscaled_pair_scratch_bytes(2, m, n, k);
+  return (uint64_t)(a > b ? a : b);
 }
 
 int b200tile_linear_mxfp4(const void* x, const void* y, const void* x_scales, const void* y_scales,
@@ -789,11 +799,15 @@ int b200tile_linear_mxfp4(const void* x, const void* y, const void* x_scales, co
   else return set_error(B200TILE_ERR_UNSUPPORTED, "linear_mxfp4: unsupported output type '%s'", out_dtype);
   if ((reinterpret_cast<uintptr_t>(z) & 15) != 0 || (ldz * (out_f32 ? 4 : 2)) % 16 != 0)
     return set_error(B200TILE_ERR_ALIGN, "linear_mxfp4: output must be 16-byte aligned with a 16-byte pitch");
-  const size_t need = b200_mxf4_scratch_bytes(m, n, k);
+  const bool pair = m >= kPairMinRows;   // CTA pairs with 256 x 256 tiles, else single CTAs with 192-row B tiles
+  const size_t need = pair ? b200_blockscaled_pair_scratch_bytes(2, m, n, k) : b200_mxf4_scratch_bytes(m, n, k);
   if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15) != 0 || workspace_bytes < need)
     return set_error(B200TILE_ERR_INVALID,
                      "linear_mxfp4: workspace of %llu bytes (16-byte aligned) required, got %llu",
                      (unsigned long long)need, (unsigned long long)workspace_bytes);
+  if (pair)
+    return b200_gemm_blockscaled_pair_dispatch(2, out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs,
+                                               ld_ys, alpha, workspace, static_cast<cudaStream_t>(cu_stream));
   return b200_gemm_mxf4_dispatch(out_f32, x, y, x_scales, y_scales, z, m, n, k, ldx, ldy, ldz, ld_xs, ld_ys,
                                  alpha, workspace, static_cast<cudaStream_t>(cu_stream));
 }

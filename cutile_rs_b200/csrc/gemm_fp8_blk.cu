@@ -213,10 +213,8 @@ gemm_fp8_blk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             tma_store_commit();
           }
         }
-        continue;
-      }
-      // f32 output: one output row (128 contiguous columns) per thread, written straight to global
-      if (row_ok && col_ok) {
+      } else if (row_ok && col_ok) {
+        // f32 output: one output row (128 contiguous columns) per thread, written straight to global
         if (OUT_F32) {
           float* zrow = static_cast<float*>(Z) + (int64_t)row_g * ldz + col0;
 #pragma unroll

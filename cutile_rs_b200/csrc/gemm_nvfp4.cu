@@ -539,8 +539,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tma_store_commit();
           }
         }
-        continue;
-      }
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
@@ -583,6 +582,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_tempty + buf * 8);
+      }
     }
     if (!OUT_F32 && C::STG_FITS && lane == 0) tma_store_wait_all<0>();
   }
@@ -694,6 +694,20 @@ int b200_nvfp4_prepare_b_scales(const void* ys, int N, int K, int64_t ld_ys, int
     return b200h::set_error(B200_ERR_UNSUPPORTED, "nvfp4_prepare_weight_scales: scale tensor too large for the pre-pass");
   nvfp4_relayout_scales_kernel<<<nvfp4_relayout_grid(tiles_n, kq, chunks), 1024, 0, stream>>>(
       static_cast<const uint8_t*>(ys), N, kq, kq_valid, ld_ys, bn, chunks, tiles_n, static_cast<uint32_t*>(out));
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// Row-major scales [rows][4 kq_valid bytes] -> [tile of tile_rows][kq][128-row chunk][512 B] blocks (the pre-pass of
+// every block-scaled kernel, for any format: a block is 128 rows x 4 scale bytes).
+int b200_blockscale_relayout(const void* src, int rows, int kq, int kq_valid, int64_t ld, int tile_rows, void* out,
+                             cudaStream_t stream) {
+  using namespace b200;
+  const int tiles = (rows + tile_rows - 1) / tile_rows, chunks = (tile_rows + 127) / 128;
+  if (!nvfp4_relayout_fits(tiles, kq, chunks))
+    return b200h::set_error(B200_ERR_UNSUPPORTED, "block-scaled GEMM: scale tensor too large for the pre-pass");
+  nvfp4_relayout_scales_kernel<<<nvfp4_relayout_grid(tiles, kq, chunks), 1024, 0, stream>>>(
+      static_cast<const uint8_t*>(src), rows, kq, kq_valid, ld, tile_rows, chunks, tiles, static_cast<uint32_t*>(out));
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

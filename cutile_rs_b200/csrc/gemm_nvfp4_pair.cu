@@ -1,5 +1,7 @@
-// NVFP4 block-scaled GEMM on CTA pairs: one 256 x 256 output tile per pair of SMs
-// (tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale, M = 256, N = 256, K = 64 per instruction).
+// Block-scaled GEMMs on CTA pairs: one 256 x 256 output tile per pair of SMs (tcgen05.mma.cta_group::2 with
+// .block_scale, M = 256, N = 256), for the three formats of gemm_nvfp4.cu: NVFP4 (kind::mxf4nvf4, K = 64 per
+// instruction, UE4M3 scale per 16), MXFP4 (kind::mxf4, K = 64, UE8M0 scale per 32) and MXFP8 (kind::mxf8f6f4,
+// K = 32, UE8M0 scale per 32).
 //
 // Why pairs: the single-CTA kernel (gemm_nvfp4.cu) moves 46 KB of operands into shared memory per 384
 // tensor-pipe cycles of a 128 x 192 tile, 120 bytes per clock and SM, about twice what L2 delivers when all
@@ -40,7 +42,11 @@ __device__ long long g_trace_fp4p_tl[40];
 #define B200_TL(i, cond)
 #endif
 
+// FMT = 1: NVFP4, 2: MXFP4, 0: MXFP8 (as in gemm_nvfp4.cu)
+template <int FMT>
 struct F4P {
+  static constexpr bool FP4 = FMT != 0;
+  static constexpr int STAGE_ELEMS = FP4 ? 256 : 128;   // K elements per 128-byte row
   static constexpr int BM = 128;                 // rows per CTA (256 per pair)
   static constexpr int BN = 256;                 // tile columns
 #ifndef B200_F4P_STAGES
@@ -52,15 +58,19 @@ struct F4P {
   // setmaxnreg pool = what the CTA was given at launch, 640 x 96 = 61440: 384 x 56 + 256 x 152 = 60416
   static constexpr int OTHER_REGS = 56, EPI_REGS = 152;
   static constexpr int CHUNKS = 2;               // 128-row scale blocks per B tile
-  static constexpr int KQ_PER_STAGE = 4;         // scale blocks along K per stage (one per K = 64 instruction)
-  static constexpr int RK = 2, HALVES = 2, MMAS_PER_REGION = 2;
-  // 24 columns of scales per region, padded to 32 so that ONE tcgen05.st writes a region: the instruction costs
-  // ~170 cycles whatever its width, and the x16 + x8 pair made the writers the slowest stage of the pipeline
+  // 512-byte scale blocks (128 rows x 4 scale bytes) along K per stage: one per instruction for NVFP4, one per two
+  // instructions for MXFP4 (a byte pair each), one per stage for MXFP8 (a byte per instruction)
+  static constexpr int KQ_PER_STAGE = FMT == 1 ? 4 : (FMT == 2 ? 2 : 1);
+  static constexpr int RK = FMT == 1 ? 2 : 1;    // blocks along K per scale region
+  static constexpr int HALVES = KQ_PER_STAGE / RK, MMAS_PER_REGION = 4 / HALVES;
+  // a region's columns (24 or 12) are padded to 32 / 16 so that ONE tcgen05.st writes it
   static constexpr int REGION_USED = 4 * RK * (1 + CHUNKS);
-  static constexpr int REGION_COLS = 32;
+  static constexpr int REGION_COLS = REGION_USED <= 16 ? 16 : 32;
   static constexpr int SF_BASE = BN;             // one accumulator, the scale regions follow it
-  static constexpr int NREG_FIT = (512 - SF_BASE) / REGION_COLS;  // 8
-  static constexpr int NREG = NREG_FIT < STAGES * HALVES - 1 ? NREG_FIT : STAGES * HALVES - 1;
+  static constexpr int NREG_FIT = (512 - SF_BASE) / REGION_COLS;
+  static constexpr int NREG_CAP = STAGES * HALVES - 1;   // a writer's wait on `empty` stays within one phase
+  static constexpr int NREG = NREG_FIT < NREG_CAP ? NREG_FIT : NREG_CAP;
+  static_assert(NREG >= 2, "at least two scale regions");
   static_assert(SF_BASE + NREG * REGION_COLS <= 512, "scale regions must fit beside the accumulator");
   static constexpr int A_BYTES = BM * 128;
   static constexpr int B_BYTES = (BN / 2) * 128;
@@ -94,17 +104,39 @@ __device__ __forceinline__ void umma_nvfp4_ss_2cta(uint32_t d_tmem, uint64_t ade
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
       : "memory");
 }
-// E2M1 operands (code 1), UE4M3 scales, K = 64
-__host__ __device__ constexpr uint32_t make_idesc_nvfp4_p(uint32_t M, uint32_t N) {
-  return (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+__device__ __forceinline__ void umma_mxf4_ss_2cta(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                  uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_mxfp8_ss_2cta(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                   uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+      : "memory");
+}
+// Instruction descriptors: E2M1 operands have code 1 (NVFP4, MXFP4), E4M3 code 0 (MXFP8); bit 23 selects UE8M0
+// scales; `sf` picks the scale byte (MXFP8: 0..3) or byte pair (MXFP4: 0 or 2) of the Tensor-Memory word, for A in
+// bits [29,31) and for B in bits [4,6)
+template <int FMT>
+__host__ __device__ constexpr uint32_t make_idesc_bs_pair(uint32_t M, uint32_t N, uint32_t sf) {
+  return (FMT != 0 ? ((1u << 7) | (1u << 10)) : 0u) | (FMT != 1 ? (1u << 23) : 0u) | ((N >> 3) << 17) |
+         ((M >> 4) << 24) | (sf << 4) | (sf << 29);
 }
 
-template <bool OUT_F32>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(F4P::THREADS, 1)
+template <bool OUT_F32, int FMT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(F4P<FMT>::THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z, int M,
                        int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
-  using C = F4P;
+  using C = F4P<FMT>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -151,7 +183,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const int tiles_m = (M + 2 * C::BM - 1) / (2 * C::BM);
   const int tiles_n = (N + C::BN - 1) / C::BN;
   const int total_tiles = tiles_m * tiles_n;
-  const int num_kb = (K + 255) / 256;
+  const int num_kb = (K + C::STAGE_ELEMS - 1) / C::STAGE_ELEMS;
   const int kq_count = num_kb * C::KQ_PER_STAGE;
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   auto tile_coords = [&](int tile, int& bm, int& bn) {
@@ -208,7 +240,6 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t stage = 0, it = 0, reg = 0, reg_par = 0;
       bool ok = true;
       [[maybe_unused]] uint32_t gs = 0;
-      const uint32_t idesc = make_idesc_nvfp4_p(2 * C::BM, C::BN);
       B200_TR_DECL(6);
       for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++it) {
         B200_TR_BEGIN();
@@ -234,9 +265,17 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 #pragma unroll
             for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
               const int k = h * C::MMAS_PER_REGION + kk;
-              if (me)
-                umma_nvfp4_ss_2cta(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 2), idesc, sf_t + kk * 4,
+              if (!me) continue;
+              const uint64_t a_k = adesc + (uint64_t)(k * 2), b_k = bdesc + (uint64_t)(k * 2);
+              if (FMT == 1)
+                umma_nvfp4_ss_2cta(d_tmem, a_k, b_k, make_idesc_bs_pair<1>(2 * C::BM, C::BN, 0), sf_t + kk * 4,
                                    sf_t + C::SFB_COL0 + kk * C::CHUNKS * 4, (kb | k) != 0);
+              else if (FMT == 2)
+                umma_mxf4_ss_2cta(d_tmem, a_k, b_k, make_idesc_bs_pair<2>(2 * C::BM, C::BN, (uint32_t)(kk * 2)), sf_t,
+                                  sf_t + C::SFB_COL0, (kb | k) != 0);
+              else
+                umma_mxfp8_ss_2cta(d_tmem, a_k, b_k, make_idesc_bs_pair<0>(2 * C::BM, C::BN, (uint32_t)k), sf_t,
+                                   sf_t + C::SFB_COL0, (kb | k) != 0);
             }
             B200_TR_END(3);
             if (++reg == C::NREG) { reg = 0; reg_par ^= 1; }
@@ -431,58 +470,86 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
 }  // namespace b200
 
-int b200_nvfp4_prepare_b_scales(const void* ys, int N, int K, int64_t ld_ys, int bn, void* out, cudaStream_t stream);
+// gemm_nvfp4.cu: re-lays out row-major scales [rows][4 kq_valid bytes] as [tile][kq][chunk][512 B] blocks
+int b200_blockscale_relayout(const void* src, int rows, int kq, int kq_valid, int64_t ld, int tile_rows, void* out,
+                             cudaStream_t stream);
 
-// Scratch: [2 ceil(M/256)] blocks of A scales (128-row tiles), then [ceil(N/256)] tiles of B scales (2 chunks).
-size_t b200_nvfp4_pair_scratch_bytes(int M, int N, int K) {
-  const size_t kq = (size_t)((K + 255) / 256) * 4;
-  return ((size_t)2 * ((M + 255) / 256) + (size_t)2 * ((N + 255) / 256)) * kq * 512;
+namespace {
+// scale blocks along K: padded to whole stages / those the row-major tensors hold
+inline void pair_kq(int fmt, int K, int* kq, int* kq_valid) {
+  *kq = fmt == 1 ? ((K + 255) / 256) * 4 : (fmt == 2 ? ((K + 255) / 256) * 2 : (K + 127) / 128);
+  *kq_valid = fmt == 1 ? K / 64 : K / 128;
 }
 
-int b200_gemm_nvfp4_pair_dispatch(int out_f32, const void* x, const void* y, const void* xs, const void* ys, void* z,
-                                  int M, int N, int K, int64_t ldx, int64_t ldy, int64_t ldz, int64_t ld_xs,
-                                  int64_t ld_ys, float alpha, void* scratch, cudaStream_t stream) {
+template <bool OUT_F32, int FMT>
+int launch_pair(const void* x, const void* y, const void* xs, const void* ys, void* z, int M, int N, int K, int64_t ldx,
+                int64_t ldy, int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha, void* scratch,
+                cudaStream_t stream) {
   using namespace b200;
-  using C = F4P;
+  using C = F4P<FMT>;
   const b200h::DeviceInfo* di = b200h::device_info();
   if (!di) return B200_ERR_CUDA;
   CUtensorMap tmA, tmB;
   int rc;
-  const uint64_t row_bytes = (uint64_t)K / 2;
+  const uint64_t row_bytes = C::FP4 ? (uint64_t)K / 2 : (uint64_t)K;
   if ((rc = b200h::encode_tmap_2d(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, row_bytes, (uint64_t)M, (uint64_t)ldx, 128,
                                   C::BM, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
   if ((rc = b200h::encode_tmap_2d(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, y, row_bytes, (uint64_t)N, (uint64_t)ldy, 128,
                                   C::BN / 2, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  CUtensorMap tmC = tmA;   // only the bf16 instantiation reads it
-  if (!out_f32 && (rc = b200h::encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, z, (uint64_t)N, (uint64_t)M,
+  CUtensorMap tmC = tmA;   // only the bf16 instantiations read it
+  if (!OUT_F32 && (rc = b200h::encode_tmap_2d(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, z, (uint64_t)N, (uint64_t)M,
                                               (uint64_t)ldz * 2, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B)))
     return rc;
-  const int kq = ((K + 255) / 256) * 4;
+  int kq, kq_valid;
+  pair_kq(FMT, K, &kq, &kq_valid);
   const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
   uint8_t* s = static_cast<uint8_t*>(scratch);
   const size_t sfb_off = (size_t)2 * tiles_m * kq * 512;
   // A scales as 128-row tiles: 2 tiles_m of them (rows past M are written as zeros); B scales as 256-row tiles
-  if ((rc = b200_nvfp4_prepare_b_scales(xs, M, K, ld_xs, 128, s, stream))) return rc;
+  if ((rc = b200_blockscale_relayout(xs, M, kq, kq_valid, ld_xs, 128, s, stream))) return rc;
   if (2 * tiles_m > (M + 127) / 128)   // the last pair's second CTA has no rows: its blocks must still read as zero
     B200_CUDA_CHECK(cudaMemsetAsync(s + (size_t)((M + 127) / 128) * kq * 512, 0, (size_t)kq * 512, stream));
-  if ((rc = b200_nvfp4_prepare_b_scales(ys, N, K, ld_ys, 256, s + sfb_off, stream))) return rc;
-  static b200h::DeviceOnce attr_done[2];
-  auto launch = [&](auto kern, int which) -> int {
-    if (!attr_done[which].test(di->ordinal)) {
-      B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
-      attr_done[which].set(di->ordinal);
-    }
-    const int tiles = tiles_m * tiles_n;
-    const int all_pairs = di->sm_count / 2;
-    const int pairs = tiles < all_pairs ? tiles : all_pairs;
-    kern<<<pairs * 2, C::THREADS, C::TOTAL, stream>>>(tmA, tmB, tmC, s, s + sfb_off, z, M, N, K, ldz, alpha, 8,
-                                                     di->status);
-    B200_CUDA_CHECK(cudaGetLastError());
-    return B200_OK;
-  };
-  return out_f32 ? launch(gemm_nvfp4_pair_kernel<true>, 0) : launch(gemm_nvfp4_pair_kernel<false>, 1);
+  if ((rc = b200_blockscale_relayout(ys, N, kq, kq_valid, ld_ys, 256, s + sfb_off, stream))) return rc;
+  auto kern = gemm_nvfp4_pair_kernel<OUT_F32, FMT>;
+  static b200h::DeviceOnce attr_done;
+  if (!attr_done.test(di->ordinal)) {
+    B200_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
+    attr_done.set(di->ordinal);
+  }
+  const int tiles = tiles_m * tiles_n;
+  const int all_pairs = di->sm_count / 2;
+  const int pairs = tiles < all_pairs ? tiles : all_pairs;
+  kern<<<pairs * 2, C::THREADS, C::TOTAL, stream>>>(tmA, tmB, tmC, s, s + sfb_off, z, M, N, K, ldz, alpha, 8,
+                                                   di->status);
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+}  // namespace
+
+// Scratch: [2 ceil(M/256)] blocks of A scales (128-row tiles), then [ceil(N/256)] tiles of B scales (2 chunks).
+// fmt = 1: NVFP4, 2: MXFP4, 0: MXFP8
+size_t b200_blockscaled_pair_scratch_bytes(int fmt, int M, int N, int K) {
+  int kq, kq_valid;
+  pair_kq(fmt, K, &kq, &kq_valid);
+  return ((size_t)2 * ((M + 255) / 256) + (size_t)2 * ((N + 255) / 256)) * (size_t)kq * 512;
+}
+
+int b200_gemm_blockscaled_pair_dispatch(int fmt, int out_f32, const void* x, const void* y, const void* xs,
+                                        const void* ys, void* z, int M, int N, int K, int64_t ldx, int64_t ldy,
+                                        int64_t ldz, int64_t ld_xs, int64_t ld_ys, float alpha, void* scratch,
+                                        cudaStream_t stream) {
+#define B200_PAIR_BS(F32_, FMT_) \
+  return launch_pair<F32_, FMT_>(x, y, xs, ys, z, M, N, K, ldx, ldy, ldz, ld_xs, ld_ys, alpha, scratch, stream)
+  if (fmt == 1 && out_f32) B200_PAIR_BS(true, 1);
+  if (fmt == 1) B200_PAIR_BS(false, 1);
+  if (fmt == 2 && out_f32) B200_PAIR_BS(true, 2);
+  if (fmt == 2) B200_PAIR_BS(false, 2);
+  if (fmt == 0 && out_f32) B200_PAIR_BS(true, 0);
+  if (fmt == 0) B200_PAIR_BS(false, 0);
+#undef B200_PAIR_BS
+  return b200h::set_error(B200_ERR_UNSUPPORTED, "block-scaled pair GEMM: unknown format %d", fmt);
 }
 
 #ifdef B200TILE_TRACE

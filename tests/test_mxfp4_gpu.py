@@ -49,9 +49,10 @@ def test_matches_oracle(b200, oracle, m, n, k, out):
     assert oracle.rel_frobenius(got, ref) <= (3e-2 if out == "bf16" else 1e-5)
 
 
-def test_scale_byte_pair_selection(b200, oracle):
+@pytest.mark.parametrize("m", [256, 640])     # single-CTA kernel / CTA-pair kernel (from 512 rows)
+def test_scale_byte_pair_selection(b200, oracle, m):
     # different power-of-two scales in every 32-block and row: checks the byte pair each K = 64 instruction picks
-    m, n, k = 256, 448, 512
+    n, k = 448, 512
     g = torch.Generator().manual_seed(4)
     xq = torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8)
     yq = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)

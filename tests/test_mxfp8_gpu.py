@@ -46,9 +46,10 @@ def test_matches_oracle(b200, oracle, m, n, k, out):
     assert oracle.rel_frobenius(got, full) <= 6e-2
 
 
-def test_scale_byte_selection(b200, oracle):
+@pytest.mark.parametrize("m", [256, 640])     # single-CTA kernel / CTA-pair kernel (from 512 rows)
+def test_scale_byte_selection(b200, oracle, m):
     # different power-of-two scales in every 32-block and row: checks the per-MMA scale-byte select
-    m, n, k = 256, 448, 256
+    n, k = 448, 256
     g = torch.Generator().manual_seed(3)
     xq = torch.randint(0, 0x78, (m, k), generator=g, dtype=torch.uint8)
     yq = torch.randint(0, 0x78, (n, k), generator=g, dtype=torch.uint8)
