@@ -86,7 +86,7 @@ struct F4P {
   static constexpr int OFF_C = STAGES * STAGE_BYTES;
   static constexpr int C_WARP_BYTES = 32 * 128;
   static constexpr int OFF_BAR = OFF_C + EW * C_WARP_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 2 + NREG;
+  static constexpr int NUM_BARS = 3 * STAGES + 2;
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int TOTAL = OFF_MISC + 16 + 1024;
 };
@@ -145,7 +145,10 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   const uint32_t bar_empty = bar_full + STAGES * 8;       // per CTA: the leader commits to both
   const uint32_t bar_tfull = bar_empty + STAGES * 8;      // per CTA
   const uint32_t bar_tempty = bar_tfull + 8;              // meaningful in the leader only
-  const uint32_t bar_sf_ready = bar_tempty + 8;           // [NREG], meaningful in the leader only
+  // [STAGES], meaningful in the leader only: a stage's scales are in both Tensor Memories (which implies that its
+  // operands are in both shared memories); ONE barrier per stage, not per scale region, because every wait costs
+  // the MMA warp ~90 cycles
+  const uint32_t bar_sf_ready = bar_tempty + 8;
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + C::OFF_MISC);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -163,7 +166,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
     mbar_init(bar_tfull, 1);
     mbar_init(bar_tempty, 2 * C::EW);                                    // the epilogue warps of both CTAs
-    for (int r = 0; r < C::NREG; ++r) mbar_init(bar_sf_ready + r * 8, 8);   // four writer warps of each CTA
+    for (int r = 0; r < STAGES; ++r) mbar_init(bar_sf_ready + r * 8, 8);   // four writer warps of each CTA
     misc[1] = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -198,7 +201,9 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
   if (warp < 4) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::OTHER_REGS));
   if (warp == 0) {
-    if (lane == 0) {
+    {
+      // converged warp, one elected lane issues the copies (as for the MMA warp below)
+      const bool me = elect_one() != 0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       [[maybe_unused]] uint32_t gs = 0;
@@ -213,23 +218,28 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int kb = 0; kb < num_kb; ++kb) {
           B200_TR_COUNT(2);
           B200_TR_BEGIN();
-          if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1))) { ok = false; break; }
           B200_TR_END(0);
           B200_TL(0, gs);
           B200_TR_BEGIN();
           const uint32_t full = bar_full + stage * 8;
-          mbar_expect_tx(full, C::STAGE_TX);
-          tma_load_2d(stage_a(stage), &tmA, full, kb * 128, m0);
-          tma_load_2d(stage_b(stage), &tmB, full, kb * 128, n0);
-          bulk_load_1d_p(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
-          bulk_load_1d_p(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+          if (me) {
+            // (a barrier of their own for the scale blocks, so that the writers start while the operands are still
+            // in flight, was measured 4 % slower: one more wait per stage for the MMA warp)
+            mbar_expect_tx(full, C::STAGE_TX);
+            bulk_load_1d_p(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
+            bulk_load_1d_p(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+            tma_load_2d(stage_a(stage), &tmA, full, kb * 128, m0);
+            tma_load_2d(stage_b(stage), &tmB, full, kb * 128, n0);
+          }
+          __syncwarp();
           B200_TR_END(1);
           B200_TL(1, gs);
           ++gs;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
-      B200_TR_FLUSH(g_trace_fp4p_producer, 3, blockIdx.x == 10);
+      B200_TR_FLUSH(g_trace_fp4p_producer, 3, blockIdx.x == 10 && lane == 0);
     }
   } else if (warp == 1) {
     if (leader) {
@@ -237,7 +247,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       // and one elected lane issues the tcgen05 instructions: a loop under `if (lane == 0)` costs ~80 cycles per
       // MMA and per commit, more per stage than the stage's 540 cycles of tensor work leave room for.
       const bool me = elect_one() != 0;
-      uint32_t stage = 0, it = 0, reg = 0, reg_par = 0;
+      uint32_t stage = 0, phase = 0, it = 0, reg = 0;
       bool ok = true;
       [[maybe_unused]] uint32_t gs = 0;
       B200_TR_DECL(6);
@@ -251,16 +261,16 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           B200_TR_COUNT(5);
           const uint64_t adesc = make_smem_desc(stage_a(stage), 16, 1024, SWZ_128B);
           const uint64_t bdesc = make_smem_desc(stage_b(stage), 16, 1024, SWZ_128B);
+          // both CTAs' writers arrive only after their stage's TMA bytes have landed, so this wait covers the
+          // operands in both shared memories and the stage's scales in both Tensor Memories
+          B200_TR_BEGIN();
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_sf_ready + stage * 8, phase, 6))) { ok = false; break; }
+          tc_fence_after_sync();
+          B200_TR_END(2);
+          B200_TL(3, gs);
 #pragma unroll
           for (int h = 0; h < C::HALVES; ++h) {
-            // both CTAs' writers arrive only after their stage's TMA bytes have landed, so this wait covers the
-            // operands in both shared memories and the region's scales in both Tensor Memories
             const uint32_t sf_t = tmem_base + C::SF_BASE + reg * C::REGION_COLS;
-            B200_TR_BEGIN();
-            if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_sf_ready + reg * 8, reg_par, 6))) { ok = false; break; }
-            tc_fence_after_sync();
-            B200_TR_END(2);
-            if (h == 0) { B200_TL(3, gs); }
             B200_TR_BEGIN();
 #pragma unroll
             for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
@@ -278,9 +288,8 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                                    sf_t + C::SFB_COL0, (kb | k) != 0);
             }
             B200_TR_END(3);
-            if (++reg == C::NREG) { reg = 0; reg_par ^= 1; }
+            if (++reg == C::NREG) reg = 0;
           }
-          if (!ok) break;
           // frees the stage (and, later, the scale regions it used) in both CTAs
           B200_TR_BEGIN();
           if (me) {
@@ -291,7 +300,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           B200_TR_END(4);
           B200_TL(4, gs);
           ++gs;
-          if (++stage == STAGES) stage = 0;
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok && me) {
           umma_commit_2cta(bar_tfull);
@@ -368,9 +377,7 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       if (lane == 0) {
         // the stores have completed (wait::st), so a CTA-scope release is enough for the arrive on the leader's
         // barrier; a cluster-scope release costs ~500 cycles per call
-#pragma unroll
-        for (int h = 0; h < C::HALVES; ++h)
-          mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_sf_ready + ((reg + h) % C::NREG) * 8, 0));
+        mbar_arrive_cluster_addr_cta_release(mapa_u32(bar_sf_ready + stage * 8, 0));
       }
       gs += 2;
       advance();
