@@ -88,7 +88,7 @@ struct Fp4Cfg {
   static constexpr int STAGE_BYTES = (STAGE_TX + 1023) / 1024 * 1024;         // 1024-aligned stride
   static constexpr int STAGES = STAGES_;
   static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
-  static constexpr int NUM_BARS = 2 * STAGES + 4 + NREG;   // + one `ready` barrier per scale region
+  static constexpr int NUM_BARS = 3 * STAGES + 4;   // + one `ready` barrier per stage
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int XROW_BYTES = 4 * KQ_PER_STAGE;          // one row's A scales for one stage
   static constexpr int OFF_XBUF = (OFF_MISC + 16 + 15) / 16 * 16;   // [2][128 rows][XROW_BYTES]
@@ -211,7 +211,9 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t bar_empty = bar_full + STAGES * 8;
   const uint32_t bar_tfull = bar_empty + STAGES * 8;
   const uint32_t bar_tempty = bar_tfull + 2 * 8;
-  const uint32_t bar_sf_ready = bar_tempty + 2 * 8;   // [NREG]: stage landed in shared memory AND the region's scales in TMEM
+  // [STAGES]: the stage has landed in shared memory AND its scales are in Tensor Memory.  One barrier per stage, not
+  // per scale region: every wait costs the MMA warp ~90 cycles.
+  const uint32_t bar_sf_ready = bar_tempty + 2 * 8;
   volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gen_base + C::OFF_MISC);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wctx{misc + 1, status};
@@ -229,7 +231,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       mbar_init(bar_tfull + b * 8, 1);
       mbar_init(bar_tempty + b * 8, 4);
     }
-    for (int r = 0; r < C::NREG; ++r) mbar_init(bar_sf_ready + r * 8, 4);   // one arrival per scale-writer warp
+    for (int r = 0; r < STAGES; ++r) mbar_init(bar_sf_ready + r * 8, 4);   // one arrival per scale-writer warp
     misc[1] = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmA);
@@ -295,7 +297,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
       // one elected lane issues the tcgen05 instructions: under `if (lane == 0)` the thread spent ~75 cycles per MMA
       // and ~60 per commit, 626 cycles per stage against the 384 the tensor pipe needs for the stage's MMAs.
       const bool me = elect_one() != 0;
-      uint32_t stage = 0, phase = 0, it = 0, g = 0, reg = 0, reg_par = 0;
+      uint32_t stage = 0, phase = 0, it = 0, g = 0, reg = 0;
       bool ok = true;
       B200_TR_DECL(6);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
@@ -310,15 +312,15 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
           B200_TR_COUNT(5);
           const uint64_t adesc = make_smem_desc(stage_a(stage), 16, 1024, SWZ_128B);
           const uint64_t bdesc = make_smem_desc(stage_b(stage), 16, 1024, SWZ_128B);
+          // the scale writers arrive only after the stage's TMA bytes have landed, so this wait covers the
+          // operands in shared memory and the stage's scales in Tensor Memory
+          B200_TR_BEGIN();
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_sf_ready + stage * 8, phase, 6))) { ok = false; break; }
+          tc_fence_after_sync();
+          B200_TR_END(2);
 #pragma unroll
           for (int h = 0; h < C::HALVES; ++h) {
-            B200_TR_BEGIN();
-            // the scale writers arrive only after the stage's TMA bytes have landed, so this wait
-            // covers the operands in shared memory and the region's scales in Tensor Memory
             const uint32_t sf_t = tmem_base + C::SF_BASE + reg * C::REGION_COLS;
-            if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_sf_ready + reg * 8, reg_par, 6))) { ok = false; break; }
-            tc_fence_after_sync();
-            B200_TR_END(2);
             B200_TR_BEGIN();
 #pragma unroll
             for (int kk = 0; kk < C::MMAS_PER_REGION; ++kk) {
@@ -336,9 +338,8 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                               make_idesc_mxfp8(F4_BM, BN, (uint32_t)k), sf_t, sf_t + C::SFB_COL0, (kb | k) != 0);
             }
             B200_TR_END(3);
-            if (++reg == C::NREG) { reg = 0; reg_par ^= 1; }
+            if (++reg == C::NREG) reg = 0;
           }
-          if (!ok) break;
           B200_TR_BEGIN();
           if (me) umma_commit(bar_empty + stage * 8);   // frees the smem stage and, later, the TMEM scale regions it used
           __syncwarp();
@@ -475,10 +476,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         B200_TR_BEGIN();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-          for (int h = 0; h < C::HALVES; ++h) mbar_arrive(bar_sf_ready + ((reg + h) % C::NREG) * 8);
-        }
+        if (lane == 0) mbar_arrive(bar_sf_ready + stage * 8);
         B200_TR_END(3);
       }
       advance();
