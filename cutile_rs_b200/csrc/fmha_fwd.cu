@@ -180,7 +180,11 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer --------------------------------
-    if (lane == 0 && n_max > 0) {
+    // The whole warp runs the control flow and the descriptor arithmetic (which then stays in uniform registers);
+    // one elected lane issues the tcgen05 instructions.  Under `if (lane == 0)` every MMA and commit costs the
+    // issuing thread ~80 cycles, more than the 64 a 128 x 128 x 16 MMA occupies the tensor pipe.
+    if (n_max > 0) {
+      const bool me = elect_one() != 0;
       constexpr uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
       constexpr uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, FA_BM, FA_BN);
       constexpr uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, FA_BM, D);
@@ -190,7 +194,7 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const uint32_t off = (kk / 4) * HALF + (kk % 4) * 32;
           const uint64_t a = make_smem_desc(sQ + t * TILE + off, 16, 1024, SWZ_128B);
           const uint64_t b = make_smem_desc(k_addr + off, 16, 1024, SWZ_128B);
-          umma_f16_ss(tmem_base + S_COL(t), a, b, idesc_qk, kk != 0);
+          if (me) umma_f16_ss(tmem_base + S_COL(t), a, b, idesc_qk, kk != 0);
         }
       };
       auto issue_pv = [&](int t, uint32_t v_addr, bool acc) {
@@ -199,61 +203,60 @@ fmha_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           // V is the N-major B operand: 16 key rows per step = two 8-row groups of 1024 bytes;
           // the second 64-wide half of the head vector lies HALF bytes further (leading offset).
           const uint64_t b = make_smem_desc(v_addr + kk * 2048, HALF, 1024, SWZ_128B);
-          umma_f16_ts(tmem_base + O_COL(t), tmem_base + S_COL(t) + kk * 8, b, idesc_pv,
-                      acc || kk != 0);
+          if (me) umma_f16_ts(tmem_base + O_COL(t), tmem_base + S_COL(t) + kk * 8, b, idesc_pv, acc || kk != 0);
         }
       };
       bool ok = true;
       B200_TR_DECL(7);
       // prologue: S_t(0) = Q_t K(0)^T
-      ok = mbar_wait(wctx, bar_k_full + 0, 0, 20);
+      ok = __all_sync(0xffffffffu, mbar_wait(wctx, bar_k_full + 0, 0, 20));
 #pragma unroll
       for (int t = 0; t < 2 && ok; ++t) {
         if (n_kv[t] == 0) continue;
-        if (!mbar_wait(wctx, bar_q_full + t * 8, 0, 21)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_q_full + t * 8, 0, 21))) { ok = false; break; }
         tc_fence_after_sync();
         issue_qk(t, sK);
-        umma_commit(bar_s_full + t * 8);
+        if (me) umma_commit(bar_s_full + t * 8);
       }
-      if (ok) umma_commit(bar_k_empty + 0);
+      if (ok && me) umma_commit(bar_k_empty + 0);
       for (int j = 0; j < n_max && ok; ++j) {
         const uint32_t vs = j % STAGES, vph = (j / STAGES) & 1;
         const uint32_t ks = (j + 1) % STAGES, kph = ((j + 1) / STAGES) & 1;
         const bool have_next = j + 1 < n_max;
         B200_TR_COUNT(6);
         B200_TR_BEGIN();
-        if (!mbar_wait(wctx, bar_v_full + vs * 8, vph, 22)) { ok = false; break; }
-        if (have_next && !mbar_wait(wctx, bar_k_full + ks * 8, kph, 23)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_v_full + vs * 8, vph, 22))) { ok = false; break; }
+        if (have_next && !__all_sync(0xffffffffu, mbar_wait(wctx, bar_k_full + ks * 8, kph, 23))) { ok = false; break; }
         tc_fence_after_sync();
         B200_TR_END(0);
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (j < n_kv[t]) {
             B200_TR_BEGIN();
-            if (!mbar_wait(wctx, bar_p_full + t * 8, j & 1, 24)) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_p_full + t * 8, j & 1, 24))) { ok = false; break; }
             tc_fence_after_sync();
             B200_TR_END(1);
             B200_TR_BEGIN();
             issue_pv(t, sV + vs * TILE, j > 0);
             B200_TR_END(2);
-            if (j == n_kv[t] - 1) umma_commit(bar_o_done + t * 8);
+            if (j == n_kv[t] - 1 && me) umma_commit(bar_o_done + t * 8);
           }
           if (j + 1 < n_kv[t]) {
             B200_TR_BEGIN();
             issue_qk(t, sK + ks * TILE);
             B200_TR_END(3);
             B200_TR_BEGIN();
-            umma_commit(bar_s_full + t * 8);
+            if (me) umma_commit(bar_s_full + t * 8);
             B200_TR_END(4);
           }
         }
         if (!ok) break;
         B200_TR_BEGIN();
-        umma_commit(bar_v_empty + vs * 8);
-        if (have_next) umma_commit(bar_k_empty + ks * 8);
+        if (me) umma_commit(bar_v_empty + vs * 8);
+        if (have_next && me) umma_commit(bar_k_empty + ks * 8);
         B200_TR_END(5);
       }
-      B200_TR_FLUSH(g_trace_fmha, 7, blockIdx.x == 7);
+      B200_TR_FLUSH(g_trace_fmha, 7, blockIdx.x == 7 && lane == 0);
     }
   } else if (warp >= 4) {
     // -------------------------------- softmax ----------------------------------
