@@ -108,32 +108,48 @@ struct Fp4Cfg {
 // Pre-pass: row-major scales -> per-tile tcgen05 scale blocks in scratch memory.
 // One thread per 4-byte word of the output.
 // ---------------------------------------------------------------------------
-__global__ void nvfp4_relayout_scales_kernel(const uint8_t* __restrict__ src, int rows, int kq_count,
-                                             int kq_valid, int64_t ld, int tile_rows, int chunks,
-                                             int num_tiles, uint32_t* __restrict__ dst) {
-  // Work item = (tile, group of 8 scale blocks along K, chunk, block of the group, word): the 1024 threads of
-  // a CTA read 32 consecutive bytes of each of 128 rows (whole sectors, shared through L1) and every warp
-  // writes 128 consecutive bytes.  32-bit index arithmetic: the 64-bit divisions of a first version cost
-  // more than the copy itself.
-  const uint32_t kq_groups = (uint32_t)(kq_count + 7) / 8;
-  const uint32_t total = (uint32_t)num_tiles * kq_groups * (uint32_t)chunks * 1024u;   // checked on the host
-  for (uint32_t w = blockIdx.x * blockDim.x + threadIdx.x; w < total; w += gridDim.x * blockDim.x) {
+struct RelayoutJob {
+  const uint8_t* src;
+  uint32_t* dst;
+  int64_t ld;
+  int rows, kq_count, kq_valid, tile_rows, chunks, num_tiles;
+  int grid;   // CTAs that work on this job
+};
+// Work item = (tile, group of 8 scale blocks along K, chunk, block of the group, word): the 1024 threads of
+// a CTA read 32 consecutive bytes of each of 128 rows (whole sectors, shared through L1) and every warp
+// writes 128 consecutive bytes.  32-bit index arithmetic: the 64-bit divisions of a first version cost
+// more than the copy itself.  Rows past `rows` and blocks past `kq_valid` are written as zeros.
+__device__ __forceinline__ void relayout_scales(const RelayoutJob& j, uint32_t block, uint32_t nblocks) {
+  const uint32_t kq_groups = (uint32_t)(j.kq_count + 7) / 8;
+  const uint32_t total = (uint32_t)j.num_tiles * kq_groups * (uint32_t)j.chunks * 1024u;   // checked on the host
+  for (uint32_t w = block * blockDim.x + threadIdx.x; w < total; w += nblocks * blockDim.x) {
     const uint32_t word = w & 127u;              // word inside the 512-byte block
     const uint32_t kq_lo = (w >> 7) & 7u;
     const uint32_t rest = w >> 10;
-    const uint32_t c = rest % (uint32_t)chunks;
-    const uint32_t t_kg = rest / (uint32_t)chunks;
+    const uint32_t c = rest % (uint32_t)j.chunks;
+    const uint32_t t_kg = rest / (uint32_t)j.chunks;
     const uint32_t kq = (t_kg % kq_groups) * 8u + kq_lo;
     const uint32_t tile = t_kg / kq_groups;
-    if (kq >= (uint32_t)kq_count) continue;
+    if (kq >= (uint32_t)j.kq_count) continue;
     const int r32 = (int)(word >> 2), g = (int)(word & 3u);
     const int local = (int)c * 128 + g * 32 + r32;
-    const int row = (int)tile * tile_rows + local;
+    const int row = (int)tile * j.tile_rows + local;
     uint32_t v = 0;
-    if (local < tile_rows && row < rows && (int)kq < kq_valid)
-      v = *reinterpret_cast<const uint32_t*>(src + (int64_t)row * ld + (int64_t)kq * 4);
-    dst[((size_t)(tile * (uint32_t)kq_count + kq) * (uint32_t)chunks + c) * 128u + word] = v;
+    if (local < j.tile_rows && row < j.rows && (int)kq < j.kq_valid)
+      v = *reinterpret_cast<const uint32_t*>(j.src + (int64_t)row * j.ld + (int64_t)kq * 4);
+    j.dst[((size_t)(tile * (uint32_t)j.kq_count + kq) * (uint32_t)j.chunks + c) * 128u + word] = v;
   }
+}
+__global__ void nvfp4_relayout_scales_kernel(const uint8_t* __restrict__ src, int rows, int kq_count,
+                                             int kq_valid, int64_t ld, int tile_rows, int chunks,
+                                             int num_tiles, uint32_t* __restrict__ dst) {
+  const RelayoutJob j{src, dst, ld, rows, kq_count, kq_valid, tile_rows, chunks, num_tiles, (int)gridDim.x};
+  relayout_scales(j, blockIdx.x, gridDim.x);
+}
+// Both operands' scales in one launch (a launch costs more than either copy)
+__global__ void nvfp4_relayout_scales2_kernel(const RelayoutJob a, const RelayoutJob b) {
+  if ((int)blockIdx.x < a.grid) relayout_scales(a, blockIdx.x, (uint32_t)a.grid);
+  else relayout_scales(b, blockIdx.x - (uint32_t)a.grid, (uint32_t)b.grid);
 }
 
 // Launch shape of the pre-pass: 1024-thread CTAs, one per 8 scale blocks along K of a 128-row chunk.
@@ -706,6 +722,24 @@ int b200_blockscale_relayout(const void* src, int rows, int kq, int kq_valid, in
     return b200h::set_error(B200_ERR_UNSUPPORTED, "block-scaled GEMM: scale tensor too large for the pre-pass");
   nvfp4_relayout_scales_kernel<<<nvfp4_relayout_grid(tiles, kq, chunks), 1024, 0, stream>>>(
       static_cast<const uint8_t*>(src), rows, kq, kq_valid, ld, tile_rows, chunks, tiles, static_cast<uint32_t*>(out));
+  B200_CUDA_CHECK(cudaGetLastError());
+  return B200_OK;
+}
+
+// The same for both operands of a GEMM in one launch; `tiles_a` / `tiles_b` may exceed what the rows need (the
+// extra tiles are written as zeros).
+int b200_blockscale_relayout2(const void* src_a, int rows_a, int64_t ld_a, int tile_rows_a, int tiles_a, void* out_a,
+                              const void* src_b, int rows_b, int64_t ld_b, int tile_rows_b, int tiles_b, void* out_b,
+                              int kq, int kq_valid, cudaStream_t stream) {
+  using namespace b200;
+  const int ca = (tile_rows_a + 127) / 128, cb = (tile_rows_b + 127) / 128;
+  if (!nvfp4_relayout_fits(tiles_a, kq, ca) || !nvfp4_relayout_fits(tiles_b, kq, cb))
+    return b200h::set_error(B200_ERR_UNSUPPORTED, "block-scaled GEMM: scale tensor too large for the pre-pass");
+  const RelayoutJob a{static_cast<const uint8_t*>(src_a), static_cast<uint32_t*>(out_a), ld_a, rows_a, kq, kq_valid,
+                      tile_rows_a, ca, tiles_a, nvfp4_relayout_grid(tiles_a, kq, ca)};
+  const RelayoutJob b{static_cast<const uint8_t*>(src_b), static_cast<uint32_t*>(out_b), ld_b, rows_b, kq, kq_valid,
+                      tile_rows_b, cb, tiles_b, nvfp4_relayout_grid(tiles_b, kq, cb)};
+  nvfp4_relayout_scales2_kernel<<<a.grid + b.grid, 1024, 0, stream>>>(a, b);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

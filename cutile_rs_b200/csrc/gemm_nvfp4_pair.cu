@@ -477,9 +477,11 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
 }  // namespace b200
 
-// gemm_nvfp4.cu: re-lays out row-major scales [rows][4 kq_valid bytes] as [tile][kq][chunk][512 B] blocks
-int b200_blockscale_relayout(const void* src, int rows, int kq, int kq_valid, int64_t ld, int tile_rows, void* out,
-                             cudaStream_t stream);
+// gemm_nvfp4.cu: re-lays out the row-major scales [rows][4 kq_valid bytes] of both operands as
+// [tile][kq][chunk][512 B] blocks, in one launch
+int b200_blockscale_relayout2(const void* src_a, int rows_a, int64_t ld_a, int tile_rows_a, int tiles_a, void* out_a,
+                              const void* src_b, int rows_b, int64_t ld_b, int tile_rows_b, int tiles_b, void* out_b,
+                              int kq, int kq_valid, cudaStream_t stream);
 
 namespace {
 // scale blocks along K: padded to whole stages / those the row-major tensors hold
@@ -514,11 +516,11 @@ int launch_pair(const void* x, const void* y, const void* xs, const void* ys, vo
   const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
   uint8_t* s = static_cast<uint8_t*>(scratch);
   const size_t sfb_off = (size_t)2 * tiles_m * kq * 512;
-  // A scales as 128-row tiles: 2 tiles_m of them (rows past M are written as zeros); B scales as 256-row tiles
-  if ((rc = b200_blockscale_relayout(xs, M, kq, kq_valid, ld_xs, 128, s, stream))) return rc;
-  if (2 * tiles_m > (M + 127) / 128)   // the last pair's second CTA has no rows: its blocks must still read as zero
-    B200_CUDA_CHECK(cudaMemsetAsync(s + (size_t)((M + 127) / 128) * kq * 512, 0, (size_t)kq * 512, stream));
-  if ((rc = b200_blockscale_relayout(ys, N, kq, kq_valid, ld_ys, 256, s + sfb_off, stream))) return rc;
+  // A scales as 128-row tiles: 2 tiles_m of them (a last pair whose second CTA has no rows reads zeros); B scales
+  // as 256-row tiles
+  if ((rc = b200_blockscale_relayout2(xs, M, ld_xs, 128, 2 * tiles_m, s, ys, N, ld_ys, 256, tiles_n, s + sfb_off, kq,
+                                      kq_valid, stream)))
+    return rc;
   auto kern = gemm_nvfp4_pair_kernel<OUT_F32, FMT>;
   static b200h::DeviceOnce attr_done;
   if (!attr_done.test(di->ordinal)) {
