@@ -148,6 +148,10 @@ __global__ void nvfp4_relayout_scales_kernel(const uint8_t* __restrict__ src, in
 }
 // Both operands' scales in one launch (a launch costs more than either copy)
 __global__ void nvfp4_relayout_scales2_kernel(const RelayoutJob a, const RelayoutJob b) {
+  // the GEMM that follows is launched with programmatic stream serialisation: let its CTAs set themselves up
+  // (barriers, Tensor Memory, descriptor prefetch) while this grid runs; its producer warp waits for this grid's
+  // completion (griddepcontrol.wait) before it reads the first scale block
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if ((int)blockIdx.x < a.grid) relayout_scales(a, blockIdx.x, (uint32_t)a.grid);
   else relayout_scales(b, blockIdx.x - (uint32_t)a.grid, (uint32_t)b.grid);
 }

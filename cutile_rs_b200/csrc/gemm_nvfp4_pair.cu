@@ -204,6 +204,9 @@ gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     {
       // converged warp, one elected lane issues the copies (as for the MMA warp below)
       const bool me = elect_one() != 0;
+      // the scale blocks come from the pre-pass launched just before this kernel (programmatic dependent launch:
+      // everything above overlapped its tail); nothing else in this kernel reads what that grid writes
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       [[maybe_unused]] uint32_t gs = 0;
@@ -530,9 +533,18 @@ int launch_pair(const void* x, const void* y, const void* xs, const void* ys, vo
   const int tiles = tiles_m * tiles_n;
   const int all_pairs = di->sm_count / 2;
   const int pairs = tiles < all_pairs ? tiles : all_pairs;
-  kern<<<pairs * 2, C::THREADS, C::TOTAL, stream>>>(tmA, tmB, tmC, s, s + sfb_off, z, M, N, K, ldz, alpha, 8,
-                                                   di->status);
-  B200_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pairs * 2);
+  cfg.blockDim = dim3(C::THREADS);
+  cfg.dynamicSmemBytes = C::TOTAL;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start while the pre-pass drains
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, static_cast<const uint8_t*>(s),
+                                     static_cast<const uint8_t*>(s + sfb_off), z, M, N, K, ldz, alpha, 8, di->status));
   return B200_OK;
 }
 }  // namespace
