@@ -413,6 +413,32 @@ def bench_fp8(ctx, by, cpu_by, e2e_by, do_cpu):
     tfm = flops / (msm * 1e-3) / 1e12 / world
     by["mxfp8"] = _roof("tensor", tfm, NOMINAL_FP8, "TFLOP/s", msm, "nominal dense fp8 = 2 x 2250 (no measured fp8 peak)",
                         how="typed entry point (scale pre-pass + CTA-pair GEMM), e8m0 scale per 32")
+    hx, hy, hxs, hys, hz = xm.cpu().pin_memory(), ym.cpu().pin_memory(), xms.cpu().pin_memory(), yms.cpu().pin_memory(), _pin_like(z8)
+
+    def emstep():
+        xm.copy_(hx, non_blocking=True)
+        ym.copy_(hy, non_blocking=True)
+        xms.copy_(hxs, non_blocking=True)
+        yms.copy_(hys, non_blocking=True)
+        mx8step()
+        hz.copy_(z8, non_blocking=True)
+    emm = ctx.timed(emstep, 3, warm=1)
+    ctx.launches += 4 * 2
+    e2e_by["mxfp8"] = {"value": flops / (emm * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": emm,
+                       "h2d_bytes_per_step": world * (hx.numel() + hxs.numel()) + n8 * k8 + n8 * k8 // 32,
+                       "d2h_bytes_per_step": m8 * n8 * 2}
+    if do_cpu:
+        from oracle import oracle
+        rows, cols = 16, 2048
+        thr = oracle.max_threads()
+        t0 = time.perf_counter()
+        xa = oracle.dequant_mxfp8(hx[:rows].numpy(), hxs[:rows].numpy())
+        ya = oracle.dequant_mxfp8(hy[:cols].numpy(), hys[:cols].numpy())
+        oracle.cpu_gemm_nt(xa, ya, threads=thr)
+        dt = time.perf_counter() - t0
+        cpu_by["mxfp8"] = {"value": 2.0 * rows * cols * k8 / dt / 1e12, "unit": "TFLOP/s", "cores": thr, "kind": "port",
+                           "sample": f"dequantise + cpu_gemm port on C[0:{rows}, 0:{cols}], K={k8}, {dt:.1f} s"}
+    del hx, hy, hxs, hys, hz
     return {"gemm_mxfp8_8192x28672x8192": {"tflops_per_gpu": tfm, "ms": msm, "frac_of_nominal_4500": tfm / NOMINAL_FP8}}
 
 
@@ -511,7 +537,7 @@ def bench_nvfp4(ctx, by, cpu_by, e2e_by, do_cpu):
                                              b"bf16", m4, nl, k4, k4 // 2, k4 // 2, nl, k4 // 32, k4 // 32, 1.0,
                                              wsq.data_ptr(), need, stream.cuda_stream))
     msq = ctx.timed(mx4step, 10)
-    ctx.launches += 13 * 3
+    ctx.launches += 13 * 2        # scale pre-pass + CTA-pair GEMM per call
     tfq = workloads.gemm_flops(m4, n4, k4) / (msq * 1e-3) / 1e12 / world
     extra["gemm_mxfp4_4096x14336x4096"] = {"tflops_per_gpu": tfq, "ms": msq, "frac_of_nominal_9000": tfq / NOMINAL_FP4}
     return extra
