@@ -716,22 +716,9 @@ int b200_nvfp4_prepare_b_scales(const void* ys, int N, int K, int64_t ld_ys, int
   return B200_OK;
 }
 
-// Row-major scales [rows][4 kq_valid bytes] -> [tile of tile_rows][kq][128-row chunk][512 B] blocks (the pre-pass of
-// every block-scaled kernel, for any format: a block is 128 rows x 4 scale bytes).
-int b200_blockscale_relayout(const void* src, int rows, int kq, int kq_valid, int64_t ld, int tile_rows, void* out,
-                             cudaStream_t stream) {
-  using namespace b200;
-  const int tiles = (rows + tile_rows - 1) / tile_rows, chunks = (tile_rows + 127) / 128;
-  if (!nvfp4_relayout_fits(tiles, kq, chunks))
-    return b200h::set_error(B200_ERR_UNSUPPORTED, "block-scaled GEMM: scale tensor too large for the pre-pass");
-  nvfp4_relayout_scales_kernel<<<nvfp4_relayout_grid(tiles, kq, chunks), 1024, 0, stream>>>(
-      static_cast<const uint8_t*>(src), rows, kq, kq_valid, ld, tile_rows, chunks, tiles, static_cast<uint32_t*>(out));
-  B200_CUDA_CHECK(cudaGetLastError());
-  return B200_OK;
-}
-
-// The same for both operands of a GEMM in one launch; `tiles_a` / `tiles_b` may exceed what the rows need (the
-// extra tiles are written as zeros).
+// Row-major scales [rows][4 kq_valid bytes] -> [tile of tile_rows][kq][128-row chunk][512 B] blocks (a block is
+// 128 rows x 4 scale bytes, whatever the format), for both operands of a GEMM in one launch; `tiles_a` / `tiles_b`
+// may exceed what the rows need (the extra tiles are written as zeros).
 int b200_blockscale_relayout2(const void* src_a, int rows_a, int64_t ld_a, int tile_rows_a, int tiles_a, void* out_a,
                               const void* src_b, int rows_b, int64_t ld_b, int tile_rows_b, int tiles_b, void* out_b,
                               int kq, int kq_valid, cudaStream_t stream) {

@@ -49,10 +49,7 @@ struct F4P {
   static constexpr int STAGE_ELEMS = FP4 ? 256 : 128;   // K elements per 128-byte row
   static constexpr int BM = 128;                 // rows per CTA (256 per pair)
   static constexpr int BN = 256;                 // tile columns
-#ifndef B200_F4P_STAGES
-#define B200_F4P_STAGES 5
-#endif
-  static constexpr int STAGES = B200_F4P_STAGES;
+  static constexpr int STAGES = 5;               // 3 / 4 stages measured 16 % / 4 % slower
   static constexpr int EW = 8;                   // epilogue warps
   static constexpr int THREADS = 128 + 32 * EW + 256;   // 640: the kernel is compiled for 96 registers per thread
   // setmaxnreg pool = what the CTA was given at launch, 640 x 96 = 61440: 384 x 56 + 256 x 152 = 60416
