@@ -3,11 +3,12 @@
 // instruction, UE4M3 scale per 16), MXFP4 (kind::mxf4, K = 64, UE8M0 scale per 32) and MXFP8 (kind::mxf8f6f4,
 // K = 32, UE8M0 scale per 32).
 //
-// Why pairs: the single-CTA kernel (gemm_nvfp4.cu) moves 46 KB of operands into shared memory per 384
-// tensor-pipe cycles of a 128 x 192 tile, 120 bytes per clock and SM, about twice what L2 delivers when all
-// SMs pull at once, so its tensor pipe idles 60 % of the time.  In a pair each CTA loads its own 128 rows of A
-// and only HALF of the tile's B rows (the instruction reads the other half from the partner's shared
-// memory): 32 KB + 6 KB of scales per 512 tensor-pipe cycles, 74 bytes per clock.
+// Why pairs: a block-scaled stage is only 384-540 tensor-pipe cycles long, so what limits these kernels is not a
+// memory level (L2 -> SM runs at a third of its peak) but the chain of hand-offs around every stage: copies issued,
+// bytes landed, scales moved to Tensor Memory, MMAs issued, stage released.  A pair puts twice the tensor work
+// (256 x 256 x 256 elements per stage) behind one such chain, with each CTA loading its own 128 rows of A and only
+// HALF of the tile's B rows (the instruction reads the other half from the partner's shared memory): 32 KB + 6 KB of
+// scales per CTA and stage.
 //
 // Same operand formats, scale arrangement in Tensor Memory and scratch layout of the re-laid-out scales as
 // gemm_nvfp4.cu (Z = alpha * sum_k x*xs * y*ys; cutile-examples/examples/nvfp4.rs:37-76).  Per CTA:
@@ -15,9 +16,9 @@
 //   warp 1        leader CTA only: issues the pair's MMAs; both: Tensor-Memory allocation
 //   warps 2, 3    idle (roles are aligned to warpgroups so that registers can be re-balanced with setmaxnreg)
 //   warps 4..11   epilogue: two warps per 32-lane quarter (128 columns each); the accumulator is drained
-//                 into packed registers first and handed back, then stored
+//                 into packed registers first and handed back, then staged and stored with TMA
 //   warps 12..19  scale writers: shared memory -> Tensor Memory (tcgen05.st), two sets taking alternate
-//                 stages; each CTA writes its own Tensor Memory and arrives on the LEADER's region barrier
+//                 stages; each CTA writes its own Tensor Memory and arrives on the LEADER's per-stage barrier
 // Every CTA holds the scales of its own 128 A rows and of all 256 B rows of the tile.
 #include "../../include/b200tile.h"
 #include "host_common.h"
@@ -131,8 +132,9 @@ __host__ __device__ constexpr uint32_t make_idesc_bs_pair(uint32_t M, uint32_t N
 template <bool OUT_F32, int FMT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(F4P<FMT>::THREADS, 1)
 gemm_nvfp4_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                       const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb, void* __restrict__ Z, int M,
-                       int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
+                       const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ sfa,
+                       const uint8_t* __restrict__ sfb, void* __restrict__ Z, int M, int N, int K, int64_t ldz,
+                       float alpha, int group_m, uint32_t* status) {
   using C = F4P<FMT>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
