@@ -60,7 +60,7 @@ struct FmhaAltSmem {
   static constexpr int OFF_BAR = OFF_V + V_STAGES * V_BYTES;
   // q_full[2], q_empty[2], k_full[KS], k_empty[KS], v_full[VS], v_empty[VS], s_full[2], s_free[2],
   // p_full[2], o_free, m_pub[2][4]
-  static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 6 + 1 + 8;
+  static constexpr int NUM_BARS = 4 + 2 * K_STAGES + 2 * V_STAGES + 6 + 1 + 8 + 2;
   static constexpr int OFF_MREF = OFF_BAR + NUM_BARS * 8;       // float[128] shared reference maximum
   static constexpr int OFF_LSUM = OFF_MREF + 128 * 4;           // float[2][128] partial sums, float[2][128] their references
   static constexpr int OFF_MISC = OFF_LSUM + 4 * 128 * 4;
@@ -121,6 +121,11 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t bar_p_full = bar_s_free + 2 * 8;           // leader [2], 8 arrivals
   const uint32_t bar_o_free = bar_p_full + 2 * 8;           // leader, 16 arrivals: O read out of Tensor Memory
   const uint32_t bar_m_pub = bar_o_free + 8;                // each CTA: [warpgroup][quadrant]
+  // each CTA [2], 4 arrivals: warpgroup w may start the exponentials of its next key tile, the other warpgroup has
+  // finished its own.  The two warpgroups share the special-function unit; taking turns makes each exp2 loop ~1.5 k
+  // cycles instead of ~1.75 k and measured 2-3 % on the whole kernel.
+  const uint32_t bar_turn = bar_m_pub + 8 * 8;
+
   float* m_ref = reinterpret_cast<float*>(gen_base + L::OFF_MREF);
   float* l_part_sm = reinterpret_cast<float*>(gen_base + L::OFF_LSUM);
   float* m_part_sm = l_part_sm + 256;
@@ -156,6 +161,7 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     mbar_init(bar_o_free, 16);            // eight softmax warps from each CTA
     for (int i = 0; i < 8; ++i) mbar_init(bar_m_pub + i * 8, 1);
+    for (int i = 0; i < 2; ++i) mbar_init(bar_turn + i * 8, 4);
     misc[1] = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmQ);
@@ -224,7 +230,10 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------- S = Q K^T issuer (leader CTA only), runs ahead of the softmax -------------
-    if (leader && lane == 0) {
+    if (leader) {
+      // whole warp runs the loop, one elected lane issues (an issue loop under `if (lane == 0)` costs ~80 cycles
+      // per MMA and per commit)
+      const bool me = elect_one() != 0;
       constexpr uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
       constexpr uint32_t idesc_qk = make_idesc(fmt, fmt, 0, 0, 2 * FA_BM, FA_BN);
       const uint32_t s_full_peer = mapa_u32(bar_s_full, 1);
@@ -240,21 +249,21 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (it.n_kv <= 0) continue;
         const uint32_t qb = n_item & 1, qph = (n_item >> 1) & 1;
         ++n_item;
-        if (!mbar_wait(wctx, bar_q_full + qb * 8, qph, 21)) break;
+        if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_q_full + qb * 8, qph, 21))) break;
         const uint32_t q_addr = sQ + qb * L::TILE_BYTES;
         for (int j = 0; j < it.n_kv; ++j, ++g) {
           const uint32_t sb = g & 1;
 #ifdef B200TILE_TRACE
           const long long c0 = clock64();
 #endif
-          if (!mbar_wait(wctx, bar_k_full + ks * 8, kph, 20)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_k_full + ks * 8, kph, 20))) { ok = false; break; }
 #ifdef B200TILE_TRACE
           const long long c1 = clock64();
           qk_wait_k += c1 - c0;
 #endif
           if (g >= 2) {
             // the softmax warps of both CTAs have read S(g - 2) out of buffer sb
-            if (!mbar_wait(wctx, bar_s_free + sb * 8, ((g >> 1) - 1) & 1u, 23)) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_s_free + sb * 8, ((g >> 1) - 1) & 1u, 23))) { ok = false; break; }
           }
 #ifdef B200TILE_TRACE
           qk_wait_s += clock64() - c1;
@@ -265,26 +274,29 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int kk = 0; kk < D / 16; ++kk) {
             const uint64_t a = make_smem_desc(q_addr + (kk / 4) * HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
             const uint64_t bd = make_smem_desc(k_addr + (kk / 4) * L::K_HALF + (kk % 4) * 32, 16, 1024, SWZ_128B);
-            umma_f16_ss_2cta(tmem_base + S_COL(sb), a, bd, idesc_qk, kk != 0);
+            if (me) umma_f16_ss_2cta(tmem_base + S_COL(sb), a, bd, idesc_qk, kk != 0);
           }
-          umma_commit_2cta(bar_s_full + sb * 8);
-          umma_commit_2cta(s_full_peer + sb * 8);
-          umma_commit_2cta(bar_k_empty + ks * 8);
-          umma_commit_2cta(k_empty_peer + ks * 8);
+          if (me) umma_commit_2cta(bar_s_full + sb * 8);
+          if (me) umma_commit_2cta(s_full_peer + sb * 8);
+          if (me) umma_commit_2cta(bar_k_empty + ks * 8);
+          if (me) umma_commit_2cta(k_empty_peer + ks * 8);
           if (++ks == KST) { ks = 0; kph ^= 1; }
         }
         // every Q.K^T of the item has been issued: its Q tile is free once they retire
-        umma_commit_2cta(bar_q_empty + qb * 8);
-        umma_commit_2cta(q_empty_peer + qb * 8);
+        if (me) umma_commit_2cta(bar_q_empty + qb * 8);
+        if (me) umma_commit_2cta(q_empty_peer + qb * 8);
       }
 #ifdef B200TILE_TRACE
-      misc[2] = (uint32_t)qk_wait_k;   // read by the P.V thread, which finishes later
-      misc[3] = (uint32_t)qk_wait_s;
+      if (lane == 0) {
+        misc[2] = (uint32_t)qk_wait_k;   // read by the P.V thread, which finishes later
+        misc[3] = (uint32_t)qk_wait_s;
+      }
 #endif
     }
   } else if (warp == 2) {
     // ------------------------- O += P V issuer (leader CTA only) -------------------------
-    if (leader && lane == 0) {
+    if (leader) {
+      const bool me = elect_one() != 0;
       constexpr uint32_t fmt = OUT_F16 ? FMT_F16 : FMT_BF16;
       constexpr uint32_t idesc_pv = make_idesc(fmt, fmt, 0, 1, 2 * FA_BM, D);
       const uint32_t v_empty_peer = mapa_u32(bar_v_empty, 1);
@@ -295,16 +307,16 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const AltItem it = alt_item(p, idx, 0, input_pos, n_total);
         if (it.n_kv <= 0) continue;
         // the previous item's accumulator has been read out by all softmax warps of both CTAs
-        if (n_item > 0 && !mbar_wait(wctx, bar_o_free, (n_item - 1) & 1u, 25)) break;
+        if (n_item > 0 && !__all_sync(0xffffffffu, mbar_wait(wctx, bar_o_free, (n_item - 1) & 1u, 25))) break;
         ++n_item;
         for (int j = 0; j < it.n_kv; ++j, ++g) {
           const uint32_t pb = g & 1, pph = (g >> 1) & 1;
           B200_TR_COUNT(6);
           B200_TR_BEGIN();
-          if (!mbar_wait(wctx, bar_v_full + vs * 8, vph, 22)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_v_full + vs * 8, vph, 22))) { ok = false; break; }
           B200_TR_END(0);
           B200_TR_BEGIN();
-          if (!mbar_wait(wctx, bar_p_full + pb * 8, pph, 24)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_p_full + pb * 8, pph, 24))) { ok = false; break; }
           tc_fence_after_sync();
           B200_TR_END(1);
           B200_TR_BEGIN();
@@ -313,13 +325,13 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           for (int kk = 0; kk < FA_BN / 16; ++kk) {
             // V is the N-major B operand; each CTA holds one 64-column block, 16 key rows per step
             const uint64_t bd = make_smem_desc(v_addr + kk * 2048, HALF, 1024, SWZ_128B);
-            umma_f16_ts_2cta(tmem_base + O_COL, tmem_base + P_COL(pb) + kk * 8, bd, idesc_pv, j > 0 || kk != 0);
+            if (me) umma_f16_ts_2cta(tmem_base + O_COL, tmem_base + P_COL(pb) + kk * 8, bd, idesc_pv, j > 0 || kk != 0);
           }
           B200_TR_END(2);
           // V(g) is free in both CTAs; the same signal tells the softmax warps that O holds key tile g
           B200_TR_BEGIN();
-          umma_commit_2cta(bar_v_empty + vs * 8);
-          umma_commit_2cta(v_empty_peer + vs * 8);
+          if (me) umma_commit_2cta(bar_v_empty + vs * 8);
+          if (me) umma_commit_2cta(v_empty_peer + vs * 8);
           B200_TR_END(5);
           if (++vs == VST) { vs = 0; vph ^= 1; }
         }
@@ -328,7 +340,7 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       tr_[3] = misc[2];
       tr_[4] = misc[3];
 #endif
-      B200_TR_FLUSH(g_trace_fmha_alt, 7, blockIdx.x == 14);
+      B200_TR_FLUSH(g_trace_fmha_alt, 7, blockIdx.x == 14 && lane == 0);
     }
   } else if (warp >= 4) {
     // -------------------------------- softmax ----------------------------------
@@ -445,6 +457,8 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           if (!mbar_wait(wctx, bar_v_empty + (gp % VST) * 8, (gp / VST) & 1u, 34)) { ok = false; break; }
           tc_fence_after_sync();
         }
+        // the exponentials of key tile g - 1 (the other warpgroup's) are done: the special-function unit is ours
+        if (g >= 1 && !mbar_wait(wctx, bar_turn + w * 8, ((g - 1) >> 1) & 1u, 35)) { ok = false; break; }
         // probabilities: exp2(s*scale - m); masked entries are exp2(-inf) = 0
         const float neg_m = -m_new;
         const uint64_t scale2 = pack2(scale, scale), negm2 = pack2(neg_m, neg_m);
@@ -464,6 +478,8 @@ fmha_fwd_alt_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
           tmem_st_32x32b_x16(tP + c * 16, pk);
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_turn + (1 - w) * 8);
         float ls[4];
         {
           const uint64_t s01 = add2(ls2[0], ls2[1]), s23 = add2(ls2[2], ls2[3]);
