@@ -149,3 +149,32 @@ def test_decode_sized_m_never_stores_rows_past_m(b200, oracle, m):
     assert not np.isnan(got).any()
     assert oracle.rel_frobenius(got, ref) <= FP4_TOL
     assert torch.isnan(big[m:]).all()
+
+
+def test_cta_pair_kernel_back_to_back_calls_share_one_workspace(b200):
+    """The pair GEMM is launched behind its scale pre-pass with programmatic stream serialisation and starts while the
+    pre-pass drains; only its producer warp waits for it.  Twenty calls in a row on one stream and one workspace, the
+    scales changed between calls without any host synchronisation: every result must equal the single-CTA kernel's,
+    which would not be the case if a GEMM ever read the previous call's scale blocks."""
+    m, n, k = 640, 768, 512
+    g = torch.Generator(device="cuda").manual_seed(21)
+    xp = torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8, device="cuda")
+    yp = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    need = b200.b200tile_linear_nvfp4_workspace_bytes(m, n, k)
+    ws = torch.empty(need, dtype=torch.uint8, device="cuda")
+    xs_all = (0x30 + torch.randint(0, 24, (20, m, k // 16), generator=g, device="cuda")).to(torch.uint8)
+    ys_all = (0x30 + torch.randint(0, 24, (20, n, k // 16), generator=g, device="cuda")).to(torch.uint8)
+    outs = torch.full((20, m, n), float("nan"), device="cuda")
+    refs = torch.full((20, m, n), float("nan"), device="cuda")
+
+    def call(cfg, xs, ys, z):
+        _lib.check(b200.b200tile_linear_nvfp4(xp.data_ptr(), yp.data_ptr(), xs.data_ptr(), ys.data_ptr(), z.data_ptr(), b"f32",
+                                              m, n, k, k // 2, k // 2, n, k // 16, k // 16, 1.0, ws.data_ptr(), need, cfg, s))
+    for i in range(20):
+        call(3, xs_all[i], ys_all[i], outs[i])
+    for i in range(20):
+        call(1, xs_all[i], ys_all[i], refs[i])
+    torch.cuda.synchronize()
+    assert not torch.isnan(outs).any()
+    assert torch.equal(outs, refs)
