@@ -277,7 +277,10 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
     cp_async_wait_all();
   } else if (warp == 4) {
     // ------------------------------- MMA issuer --------------------------------
-    if (lane == 0) {
+    {
+      // the whole warp runs the loop, one elected lane issues (an issue loop under `if (lane == 0)` costs ~80 cycles
+      // per MMA and per commit)
+      const bool me = elect_one() != 0;
       GroupCursor cur(ws.info, groups);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
@@ -285,11 +288,11 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
         cur.seek(tile);
         const int num_kb = (cur.cur.z + GG_BK - 1) / GG_BK;
         const uint32_t buf = it & 1;
-        if (!mbar_wait(wctx, bar_tempty + buf * 8, ((it >> 1) & 1) ^ 1, 2)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_tempty + buf * 8, ((it >> 1) & 1) ^ 1, 2))) { ok = false; break; }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_full + stage * 8, phase, 3))) { ok = false; break; }
           // the operands were written by cp.async (generic proxy) and are read by the tensor core (async proxy)
           fence_proxy_async_smem();
           tc_fence_after_sync();
@@ -297,11 +300,11 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
           const uint64_t bdesc = make_smem_desc(sB + stage * L::B_BYTES, GG_BK * 128, 1024, SWZ_128B);
 #pragma unroll
           for (int k = 0; k < GG_BK / 16; ++k)
-            umma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc, (kb | k) != 0);
-          umma_commit(bar_empty + stage * 8);
+            if (me) umma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc, (kb | k) != 0);
+          if (me) umma_commit(bar_empty + stage * 8);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) umma_commit(bar_tfull + buf * 8);  // with k = 0 nothing was issued: completes at once
+        if (ok && me) umma_commit(bar_tfull + buf * 8);  // with k = 0 nothing was issued: completes at once
       }
     }
   } else {
