@@ -1198,10 +1198,16 @@ def _print_trace(lib, args) -> None:
         raise SystemExit("--trace needs the diagnostic build (see the module docstring)")
     out = (ctypes.c_longlong * 20)()
     which = {"gemm": b"gemm_pair", "fmha": b"fmha_alt" if args.pair else b"fmha",
-             "nvfp4": b"block_scaled_pair" if args.config == 3 else b"block_scaled"}.get(args.kernel)
+             "nvfp4": b"block_scaled_pair" if args.config == 3 else b"block_scaled", "group": b"grouped"}.get(args.kernel)
     if which is None or lib.b200tile_trace_read(which, out):
         raise SystemExit("no trace for this kernel")
     v = list(out)
+    if args.kernel == "group":
+        n = max(v[4], 1)
+        print(f"MMA warp of one CTA per 64-deep stage (4 MMAs = 540 tensor cycles): stage-full waits {v[1] / n:.0f}, fence + issue "
+              f"+ commit {v[2] / n:.0f}, accumulator waits {v[0] / n:.0f}; total {v[5] / n:.0f} cycles per stage ({n} stages); "
+              f"SM clock inside the kernel {1e3 * v[5] / max(v[6], 1):.0f} MHz")
+        return
     if args.kernel == "nvfp4":
         n = max(v[5], 1)
         print(f"MMA thread of one CTA per stage (4 block-scaled MMAs): stage + scale waits {v[2] / n:.0f}, "

@@ -65,6 +65,7 @@ int b200_trace_read_fmha(long long* out);
 int b200_trace_read_fp4(long long* out);
 int b200_trace_read_fp4_pair(long long* out);
 int b200_trace_read_fp4_pair_tl(long long* out);
+int b200_trace_read_grouped(long long* out);
 #endif
 
 int b200_gemm_fp8_blk_dispatch(int out_f32, const void* x, const void* y, const float* xs,
@@ -1874,6 +1875,7 @@ B200TILE_API int b200tile_trace_read(const char* which, long long* out) {
   if (!strcmp(which, "fmha_alt")) return b200_trace_read_fmha_alt(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "block_scaled")) return b200_trace_read_fp4(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "block_scaled_pair")) return b200_trace_read_fp4_pair(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
+  if (!strcmp(which, "grouped")) return b200_trace_read_grouped(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   if (!strcmp(which, "block_scaled_pair_timeline"))
     return b200_trace_read_fp4_pair_tl(out) ? B200TILE_ERR_CUDA : B200TILE_OK;
   return B200TILE_ERR_UNSUPPORTED;

@@ -31,8 +31,15 @@
 
 #include "host_common.h"
 #include "sm100_ptx.cuh"
+#include "trace.cuh"
 
 namespace b200 {
+
+#ifdef B200TILE_TRACE
+// MMA warp of CTA 5: [0] accumulator waits, [1] stage-full waits, [2] fence + MMA issue + commit, [4] stages,
+// [5] total cycles, [6] the same span in ns
+__device__ long long g_trace_grouped[8];
+#endif
 
 constexpr int GG_BM = 128;
 constexpr int GG_BK = 64;
@@ -284,15 +291,22 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
       GroupCursor cur(ws.info, groups);
       uint32_t stage = 0, phase = 0, it = 0;
       bool ok = true;
+      B200_TR_DECL(5);
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
         cur.seek(tile);
         const int num_kb = (cur.cur.z + GG_BK - 1) / GG_BK;
         const uint32_t buf = it & 1;
+        B200_TR_BEGIN();
         if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_tempty + buf * 8, ((it >> 1) & 1) ^ 1, 2))) { ok = false; break; }
+        B200_TR_END(0);
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          B200_TR_COUNT(4);
+          B200_TR_BEGIN();
           if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_full + stage * 8, phase, 3))) { ok = false; break; }
+          B200_TR_END(1);
+          B200_TR_BEGIN();
           // the operands were written by cp.async (generic proxy) and are read by the tensor core (async proxy)
           fence_proxy_async_smem();
           tc_fence_after_sync();
@@ -302,10 +316,12 @@ gemm_grouped_kernel(GroupedWs ws, const int64_t* a_ptrs, const int64_t* b_ptrs, 
           for (int k = 0; k < GG_BK / 16; ++k)
             if (me) umma_f16_ss(d_tmem, adesc + (uint64_t)(k * 2), bdesc + (uint64_t)(k * 128), idesc, (kb | k) != 0);
           if (me) umma_commit(bar_empty + stage * 8);
+          B200_TR_END(2);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (ok && me) umma_commit(bar_tfull + buf * 8);  // with k = 0 nothing was issued: completes at once
       }
+      B200_TR_FLUSH(g_trace_grouped, 5, blockIdx.x == 5 && lane == 0);
     }
   } else {
     // -------------------------------- epilogue ---------------------------------
@@ -449,3 +465,9 @@ int b200_gemm_grouped_dispatch(int dtype, int bn, const int64_t* a_ptrs, const i
                  : launch_grouped<128, false>(a_ptrs, b_ptrs, c_ptrs, a_metas, b_metas, c_metas, groups, workspace, stream);
   return b200h::set_error(B200_ERR_UNSUPPORTED, "group_gemm: BN=%d has no precompiled configuration (128, 256)", bn);
 }
+
+#ifdef B200TILE_TRACE
+int b200_trace_read_grouped(long long* out) {
+  return cudaMemcpyFromSymbol(out, b200::g_trace_grouped, 8 * sizeof(long long)) != cudaSuccess;
+}
+#endif
