@@ -59,3 +59,24 @@ def test_scale_byte_selection(b200, oracle, m):
     ref = oracle.cpu_gemm_nt(oracle.dequant_mxfp8(xq.numpy(), xs.numpy()), oracle.dequant_mxfp8(yq.numpy(), ys.numpy()),
                              threads=0)
     assert oracle.rel_frobenius(got, ref) <= 1e-5
+
+
+def test_full_size_slab_and_scale_linearity(b200, oracle):
+    """The benchmark's MXFP8 shape at full size (8192 x 28672 x 8192, CTA-pair kernel): device-side generation, an
+    oracle slab that straddles tile and CTA boundaries, and a size-independent property: adding 1 to every E8M0 scale
+    byte of x doubles the result bit for bit."""
+    m, n, k = 8192, 28672, 8192
+    g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 13)
+    xq, xs = quant.quant_mxfp8(torch.randn(m, k, device="cuda", generator=g))
+    yq, ys = quant.quant_mxfp8(torch.randn(n, k, device="cuda", generator=g))
+    out = _run(b200, xq, yq, xs, ys, m, n, k, "bf16", 1.0)
+    rows, cols = slice(4090, 4102), slice(14300, 14428)
+    ref = oracle.cpu_gemm_nt(oracle.dequant_mxfp8(xq[rows].cpu().numpy(), xs[rows].cpu().numpy()),
+                             oracle.dequant_mxfp8(yq[cols].cpu().numpy(), ys[cols].cpu().numpy()), threads=0)
+    assert oracle.rel_frobenius(out[rows, cols].float().cpu().numpy(), ref) <= 3e-2
+    assert not torch.isnan(out.float()).any()
+    out2 = _run(b200, xq, yq, xs + 1, ys, m, n, k, "bf16", 1.0)
+    assert torch.equal(out2, out * 2)
+    st = _lib.StatusC()
+    _lib.check(b200.b200tile_status(torch.cuda.current_stream().cuda_stream, st))
+    assert st.code == 0
