@@ -92,14 +92,15 @@ struct Fp4Cfg {
   static constexpr int OFF_MISC = OFF_BAR + NUM_BARS * 8;
   static constexpr int XROW_BYTES = 4 * KQ_PER_STAGE;          // one row's A scales for one stage
   static constexpr int OFF_XBUF = (OFF_MISC + 16 + 15) / 16 * 16;   // [2][128 rows][XROW_BYTES]
-  static constexpr int TOTAL = OFF_XBUF + 4 * F4_BM * XROW_BYTES + 1024;   // two buffers per writer set
+  static constexpr int XBUF_BYTES = (A_DIRECT && AROWS <= 32) ? 0 : 4 * F4_BM * XROW_BYTES;   // two buffers per writer set
+  static constexpr int TOTAL = OFF_XBUF + XBUF_BYTES + 1024;
   // bf16 output staging for TMA stores, one [32 rows][CW columns] swizzled buffer per epilogue warp, where shared
   // memory has room for it (every configuration but the short-A-tile one and 256-row B tiles).  Rows stored
   // straight from registers (16 bytes per lane, 32 rows per instruction) reach L2 as half-filled sectors from all
   // CTAs at once, and the next tile's loads queue behind them.
   static constexpr int CW = BN % 64 == 0 ? 64 : 32;                 // columns per store: 128- or 64-byte rows
   static constexpr int C_WARP_BYTES = 32 * CW * 2;
-  static constexpr int OFF_CSTG = (OFF_XBUF + 4 * F4_BM * XROW_BYTES + 1023) / 1024 * 1024;
+  static constexpr int OFF_CSTG = (OFF_XBUF + XBUF_BYTES + 1023) / 1024 * 1024;
   static constexpr int TOTAL_STG = OFF_CSTG + 4 * C_WARP_BYTES + 1024;
   static constexpr bool STG_FITS = AROWS == 128 && TOTAL_STG <= 232448;
 };
@@ -219,8 +220,14 @@ __global__ void __launch_bounds__(F4_THREADS, 1)
 gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                   const __grid_constant__ CUtensorMap tmC, const uint8_t* __restrict__ xs, int64_t ld_xs, int kq_valid, const uint8_t* __restrict__ sfa,
                   const uint8_t* __restrict__ sfb, void* __restrict__ Z,
-                  int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status) {
+                  int M, int N, int K, int64_t ldz, float alpha, int group_m, uint32_t* status, int weights_first) {
   using C = Fp4Cfg<BN, FMT, A_DIRECT, AROWS>;
+  // Decode-sized calls (the short A tile) are chained back to back in a serving step, and ~4 us of each call are
+  // fixed: launch, set-up, the first copies' latency, the drain.  So this instantiation takes part in programmatic
+  // dependent launch: it lets its successor start early, and when ITS launch carries the attribute it sets itself up
+  // and (weights_first: the weights and their scales are constants of the model) fills its ring with the weight tiles
+  // before it waits for the predecessor, whose output it only needs for the activations.
+  constexpr bool CHAINED = A_DIRECT && AROWS <= 32;
   constexpr bool FP4 = C::FP4;
   constexpr int STAGES = C::STAGES;
   constexpr int STAGE_ELEMS = FP4 ? 256 : 128;  // K elements per 128-byte row
@@ -266,6 +273,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = misc[0];
+  if constexpr (CHAINED) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int tiles_m = (M + F4_BM - 1) / F4_BM;
   const int tiles_n = (N + BN - 1) / BN;
@@ -283,10 +291,33 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   };
 
   if (warp == 0) {
-    if (lane == 0) {
+    {
+      // converged warp, one elected lane issues the copies (as for the MMA warp below): 124 instead of 251 cycles per
+      // stage
+      const bool me = elect_one() != 0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       B200_TR_DECL(3);
+      // stages of the first tile whose weight tile and weight scales are already on their way
+      int prefetched = 0;
+      if constexpr (CHAINED) {
+        if (weights_first && (int)blockIdx.x < total_tiles) {
+          int bm, bn;
+          tile_coords(blockIdx.x, bm, bn);
+          const uint8_t* sfb_tile = sfb + (int64_t)bn * kq_count * (C::CHUNKS * 512);
+          prefetched = num_kb < STAGES ? num_kb : STAGES;
+          if (me) {
+            for (int kb = 0; kb < prefetched; ++kb) {
+              const uint32_t full = bar_full + kb * 8;
+              mbar_expect_tx(full, C::STAGE_TX);
+              tma_load_2d(stage_b(kb), &tmB, full, kb * 128, bn * BN);
+              bulk_load_1d(stage_sfb(kb), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+            }
+          }
+          __syncwarp();
+        }
+        asm volatile("griddepcontrol.wait;" ::: "memory");   // the activations are the predecessor's output
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int bm, bn;
         tile_coords(tile, bm, bn);
@@ -295,21 +326,27 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         for (int kb = 0; kb < num_kb; ++kb) {
           B200_TR_COUNT(2);
           B200_TR_BEGIN();
-          if (!mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait(wctx, bar_empty + stage * 8, phase ^ 1, 1))) { ok = false; break; }
           B200_TR_END(0);
           B200_TR_BEGIN();
           const uint32_t full = bar_full + stage * 8;
-          mbar_expect_tx(full, C::STAGE_TX);
-          tma_load_2d(stage_a(stage), &tmA, full, kb * 128, bm * F4_BM);
-          tma_load_2d(stage_b(stage), &tmB, full, kb * 128, bn * BN);
-          if (!A_DIRECT)
-            bulk_load_1d(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
-          bulk_load_1d(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+          const bool half_done = CHAINED && tile == (int)blockIdx.x && kb < prefetched;
+          if (me) {
+            if (!half_done) mbar_expect_tx(full, C::STAGE_TX);
+            tma_load_2d(stage_a(stage), &tmA, full, kb * 128, bm * F4_BM);
+            if (!half_done) {
+              tma_load_2d(stage_b(stage), &tmB, full, kb * 128, bn * BN);
+              if (!A_DIRECT)
+                bulk_load_1d(stage_sfa(stage), sfa_tile + (int64_t)kb * C::SFA_BYTES, C::SFA_BYTES, full);
+              bulk_load_1d(stage_sfb(stage), sfb_tile + (int64_t)kb * C::SFB_BYTES, C::SFB_BYTES, full);
+            }
+          }
+          __syncwarp();
           B200_TR_END(1);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
-      B200_TR_FLUSH(g_trace_fp4_producer, 3, blockIdx.x == 5);
+      B200_TR_FLUSH(g_trace_fp4_producer, 3, blockIdx.x == 5 && lane == 0);
     }
   } else if (warp == 1) {
     {
@@ -386,10 +423,18 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     constexpr int AW = C::KQ_PER_STAGE * 4;     // A-scale words per lane and stage
     constexpr int XW = C::KQ_PER_STAGE;         // words per row and stage
     const uint32_t xbuf = base + C::OFF_XBUF;
+    // Short A tile (AROWS <= 32, a single row of tiles): only rows 0..31 exist, every quadrant's lane l needs row l's
+    // words and zeros for rows l+32, l+64, l+96, so each writer thread loads row `lane` itself and nothing is
+    // swapped through shared memory (the swap, with its barrier over the four warps and the tile arithmetic, was 870
+    // of the 1350 cycles a writer set spent per stage at M = 16).
+    constexpr bool SHORT_A = A_DIRECT && AROWS <= 32;
     auto load_row_scales = [&](int tile, int kb, uint32_t (&dst)[XW]) {
-      int bm, bn;
-      tile_coords(tile, bm, bn);
-      const int row = bm * F4_BM + q * 32 + lane;
+      int row = lane;
+      if constexpr (!SHORT_A) {
+        int bm, bn;
+        tile_coords(tile, bm, bn);
+        row = bm * F4_BM + q * 32 + lane;
+      }
       const int kq0 = kb * C::KQ_PER_STAGE;
 #pragma unroll
       for (int k = 0; k < XW; ++k) dst[k] = 0u;
@@ -425,11 +470,22 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     bool ok = true;
     B200_TR_DECL(5);
     uint32_t x_next[XW];
+    if constexpr (CHAINED) asm volatile("griddepcontrol.wait;" ::: "memory");   // the activation scales are the predecessor's output
     if (A_DIRECT && tile < total_tiles) load_row_scales(tile, kb, x_next);
     while (tile < total_tiles && ok) {
       {
         uint32_t a_cur[AW];
-        if (A_DIRECT) {
+        if constexpr (SHORT_A) {
+#pragma unroll
+          for (int k = 0; k < XW; ++k) {
+            a_cur[k * 4] = x_next[k];
+            a_cur[k * 4 + 1] = a_cur[k * 4 + 2] = a_cur[k * 4 + 3] = 0u;
+          }
+          int nt = tile, nkb = kb;
+          next_stage(nt, nkb);
+          next_stage(nt, nkb);
+          if (nt < total_tiles) load_row_scales(nt, nkb, x_next);
+        } else if (A_DIRECT) {
           // publish this stage's row words, fetch those of the set's next stage, then gather the four
           // rows of the lane; two buffers per set so that a fast warp cannot overwrite a slow one's rows
           const uint32_t xb = xbuf + (set * 2 + ((g >> 1) & 1)) * (F4_BM * C::XROW_BYTES);
@@ -508,6 +564,7 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const int row = q * 32 + lane;
     uint32_t it = 0;
     bool ok = true;
+    if constexpr (CHAINED) asm volatile("griddepcontrol.wait;" ::: "memory");   // the output may be the predecessor's too
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
       int bm, bn;
       tile_coords(tile, bm, bn);
@@ -678,8 +735,26 @@ static int launch_nvfp4_impl(const void* x, const void* y, const void* xs, const
   }
   const int tiles = tiles_m * tiles_n;
   const int grid = tiles < di->sm_count ? tiles : di->sm_count;
+  if constexpr (A_DIRECT && AROWS <= 32) {
+    // decode-sized call: programmatic stream serialisation (see CHAINED in the kernel); the weight tiles go first only
+    // when their scales were prepared ahead of the call, i.e. when nothing of the weights is written on this stream
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(F4_THREADS);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, static_cast<const uint8_t*>(xs), ld_xs, kq_valid,
+                                       static_cast<const uint8_t*>(scratch), static_cast<const uint8_t*>(scratch + sfb_off), z,
+                                       M, N, K, ldz, alpha, 8, di->status, b_scales_prepared ? 1 : 0));
+    return B200_OK;
+  }
   kern<<<grid, F4_THREADS, SMEM, stream>>>(tmA, tmB, tmC, static_cast<const uint8_t*>(xs), ld_xs, kq_valid, scratch,
-                                               scratch + sfb_off, z, M, N, K, ldz, alpha, 8, di->status);
+                                               scratch + sfb_off, z, M, N, K, ldz, alpha, 8, di->status, 0);
   B200_CUDA_CHECK(cudaGetLastError());
   return B200_OK;
 }

@@ -408,7 +408,11 @@ B200TILE_API int b200tile_linear_mxfp4(const void* x, const void* y, const void*
  * later call then runs a single kernel and needs no workspace (the activation scales are read in
  * place).  Same operands and semantics as b200tile_linear_nvfp4 otherwise; config 0 suits decode
  * (m <= 128: most tile-blocks), config 1 large m.  No reference counterpart: the reference passes
- * logically row-major scales on every call (cutile-examples/examples/nvfp4.rs:37-76). */
+ * logically row-major scales on every call (cutile-examples/examples/nvfp4.rs:37-76).
+ * The weights `y` and their prepared scales are treated as CONSTANTS: with m <= 32 the kernel is launched with
+ * programmatic stream serialisation and begins to fetch them while the preceding kernel of the stream is still
+ * running (it waits for that kernel before it reads x, x_scales or writes z).  Do not use this entry, or
+ * registered scales, for weights that earlier work on the same stream is still writing. */
 B200TILE_API uint64_t b200tile_nvfp4_weight_scales_bytes(int n, int k, int config);
 B200TILE_API int b200tile_nvfp4_prepare_weight_scales(const void* y_scales, int n, int k, int64_t ld_ys,
                                                       int config, void* prepared, uint64_t prepared_bytes,

@@ -178,3 +178,57 @@ def test_cta_pair_kernel_back_to_back_calls_share_one_workspace(b200):
     torch.cuda.synchronize()
     assert not torch.isnan(outs).any()
     assert torch.equal(outs, refs)
+
+
+def test_decode_calls_chained_back_to_back_see_their_predecessors_output(b200, oracle):
+    """Decode-sized calls on prepared weights start under programmatic stream serialisation: a call fetches its weight
+    tiles while its predecessor still runs and must wait for it before it touches the activations.  Here every call's
+    activations (packed codes AND scales) are rewritten on the same stream right before it, and every output is written
+    twice by two calls in a row; twelve steps deep, eagerly and from a captured graph; each output is compared with the
+    oracle for the activations and the alpha the last call should have used."""
+    m, n, k, calls = 16, 1024, 2048, 12
+    g = torch.Generator().manual_seed(404)
+    yp = torch.randint(0, 256, (n, k // 2), generator=g, dtype=torch.uint8)
+    ys = (0x30 + torch.randint(0, 24, (n, k // 16), generator=g)).to(torch.uint8)
+    xps = [torch.randint(0, 256, (m, k // 2), generator=g, dtype=torch.uint8) for _ in range(calls)]
+    xss = [(0x30 + torch.randint(0, 24, (m, k // 16), generator=g)).to(torch.uint8) for _ in range(calls)]
+    yd, ysd = api.from_torch(yp.cuda(), "f4e2m1fnx2"), api.from_torch(ys.cuda())
+    prepared = launch.nvfp4_prepare_weight_scales(ysd, n, k, 0)
+    xp_all, xs_all = torch.stack(xps).cuda(), torch.stack(xss).cuda()
+    xp_cur, xs_cur = torch.zeros_like(xp_all[0]), torch.zeros_like(xs_all[0])
+    xd, xsd = api.from_torch(xp_cur, "f4e2m1fnx2"), api.from_torch(xs_cur)
+    outs = [torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32) for _ in range(calls)]
+    yref = oracle.dequant_nvfp4(yp.numpy(), ys.numpy())
+    refs = [oracle.cpu_gemm_nt(oracle.dequant_nvfp4(xps[i].numpy(), xss[i].numpy()), yref, alpha=0.5, threads=0)
+            for i in range(calls)]
+
+    def step():
+        for i in range(calls):
+            xp_cur.copy_(xp_all[i])          # device-to-device copies on the same stream: the predecessor of call i
+            xs_cur.copy_(xs_all[i])
+            launch.linear_nvfp4_prepared(api.from_torch(outs[i]), xd, yd, xsd, prepared, 0.25, config=0)
+            # a second call straight behind the first (it overlaps the first one's tail) into the same output with
+            # another alpha: its stores must land after the first call's
+            launch.linear_nvfp4_prepared(api.from_torch(outs[i]), xd, yd, xsd, prepared, 0.5, config=0)
+
+    def check():
+        torch.cuda.synchronize()
+        for i in range(calls):
+            got = outs[i].cpu().numpy()
+            assert not np.isnan(got).any()
+            assert oracle.rel_frobenius(got, refs[i]) <= 1e-6, i
+            outs[i].fill_(float("nan"))
+
+    step()
+    check()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=s, capture_error_mode="relaxed"):
+        step()
+    for _ in range(3):
+        graph.replay()
+        check()
+    st = _lib.StatusC()
+    _lib.check(b200.b200tile_status(torch.cuda.current_stream().cuda_stream, st))
+    assert st.code == 0
