@@ -286,7 +286,7 @@ def bench_fmha(ctx, by, cpu_by, e2e_by, do_cpu):
     """FMHA forward bf16 8 x 32 x 4096 x 128 (b x h split over the ranks), non-causal and causal."""
     import ctypes
     import torch
-    from cutile_rs_b200 import _lib, sharding, workloads
+    from cutile_rs_b200 import _lib, api, sharding, workloads
     lib, stream, dev, world = ctx.lib, ctx.stream, ctx.dev, ctx.world
     peak, _, src = measured_peaks()
     B_, H_, S_, D_ = 8, 32, 4096, 128
@@ -311,16 +311,17 @@ def bench_fmha(ctx, by, cpu_by, e2e_by, do_cpu):
         tf = flops / (ms * 1e-3) / 1e12 / world
         by[name] = _roof("tensor", tf, peak, "TFLOP/s", ms, f"{src} cuBLAS bf16 burst", frac_of_nominal_2250=tf / NOMINAL_BF16)
 
+        # end to end: api.HostFmha, eight groups of (batch, head) problems uploaded / attended / downloaded on three streams
+        plan = api.HostFmha(nb, S_, D_, "bf16", causal=causal, group=max(1, nb // 8))
+
         def estep():
-            q.copy_(qh, non_blocking=True)
-            k.copy_(kh, non_blocking=True)
-            v.copy_(vh, non_blocking=True)
-            fstep()
-            oh.copy_(o, non_blocking=True)
+            plan(qh, kh, vh, oh, scale, stream)
         ems = ctx.timed(estep, 3, warm=1)
+        del plan
         e2e_by[name] = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ems,
-                        "h2d_bytes_per_step": 3 * B_ * H_ * S_ * D_ * 2, "d2h_bytes_per_step": B_ * H_ * S_ * D_ * 2}
-        ctx.launches += 13 + 4
+                        "h2d_bytes_per_step": 3 * B_ * H_ * S_ * D_ * 2, "d2h_bytes_per_step": B_ * H_ * S_ * D_ * 2,
+                        "note": "api.HostFmha: pinned host Q, K, V, O; pipelined in eight groups of problems"}
+        ctx.launches += 13 + 4 * 8
         if do_cpu:
             from oracle import oracle
             nbh, rows = 4, 256
@@ -352,7 +353,7 @@ def bench_fp8(ctx, by, cpu_by, e2e_by, do_cpu):
     """fp8 e4m3 GEMM 8192 x 28672 x 8192 with fp32 scales per 1x128 / 128x128 block (weight rows split over the ranks),
     and the same shape as MXFP8 (e8m0 scale per 32, applied by the tensor core)."""
     import torch
-    from cutile_rs_b200 import _lib, quant, sharding, workloads
+    from cutile_rs_b200 import _lib, api, quant, sharding, workloads
     lib, stream, dev, world = ctx.lib, ctx.stream, ctx.dev, ctx.world
     g = torch.Generator(device="cuda").manual_seed(workloads.SEED_BASE + 3)
     m8, n8, k8 = 8192, 28672, 8192
@@ -372,18 +373,22 @@ def bench_fp8(ctx, by, cpu_by, e2e_by, do_cpu):
     by["fp8_blk128"] = _roof("tensor", tf, NOMINAL_FP8, "TFLOP/s", ms, "nominal dense fp8 = 2 x 2250 (no measured fp8 peak)")
     hx, hy, hxs, hys, hz = xq.cpu().pin_memory(), yq.cpu().pin_memory(), xs.cpu().pin_memory(), ys.cpu().pin_memory(), _pin_like(z8)
 
+    # end to end: api.HostRowPipeline, weights first, then 1024-row slabs uploaded / multiplied / downloaded on three streams
+    pipe = api.HostRowPipeline(m8, 1024)
+
+    def f8rows(a0, a1, s_):
+        _lib.check(lib.b200tile_linear_fp8_blk128(xq[a0:].data_ptr(), yq.data_ptr(), xs[a0:].data_ptr(), ys.data_ptr(),
+                                                  z8[a0:].data_ptr(), b"bf16", a1 - a0, nl, k8, k8, k8, nl, k8 // 128,
+                                                  k8 // 128, 1.0, s_.cuda_stream))
+
     def estep():
-        xq.copy_(hx, non_blocking=True)
-        yq.copy_(hy, non_blocking=True)
-        xs.copy_(hxs, non_blocking=True)
-        ys.copy_(hys, non_blocking=True)
-        f8step()
-        hz.copy_(z8, non_blocking=True)
+        pipe([(hy, yq), (hys, ys)], [(hx, xq), (hxs, xs)], [(z8, hz)], f8rows, stream)
     ems = ctx.timed(estep, 3, warm=1)
     e2e_by["fp8_blk128"] = {"value": flops / (ems * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": ems,
                             "h2d_bytes_per_step": world * (hx.numel() + hxs.numel() * 4) + n8 * k8 + (n8 // 128) * (k8 // 128) * 4,
-                            "d2h_bytes_per_step": m8 * n8 * 2}
-    ctx.launches += 8 + 4
+                            "d2h_bytes_per_step": m8 * n8 * 2,
+                            "note": "api.HostRowPipeline: all operands uploaded, pipelined in 1024-row slabs"}
+    ctx.launches += 8 + 4 * 8
     if do_cpu:
         from oracle import oracle
         rows, cols = 16, 2048
@@ -415,18 +420,19 @@ def bench_fp8(ctx, by, cpu_by, e2e_by, do_cpu):
                         how="typed entry point (scale pre-pass + CTA-pair GEMM), e8m0 scale per 32")
     hx, hy, hxs, hys, hz = xm.cpu().pin_memory(), ym.cpu().pin_memory(), xms.cpu().pin_memory(), yms.cpu().pin_memory(), _pin_like(z8)
 
+    def mx8rows(a0, a1, s_):
+        _lib.check(lib.b200tile_linear_mxfp8(xm[a0:].data_ptr(), ym.data_ptr(), xms[a0:].data_ptr(), yms.data_ptr(),
+                                             z8[a0:].data_ptr(), b"bf16", a1 - a0, nl, k8, k8, k8, nl, k8 // 32, k8 // 32,
+                                             1.0, wsb8.data_ptr(), wsm, s_.cuda_stream))
+
     def emstep():
-        xm.copy_(hx, non_blocking=True)
-        ym.copy_(hy, non_blocking=True)
-        xms.copy_(hxs, non_blocking=True)
-        yms.copy_(hys, non_blocking=True)
-        mx8step()
-        hz.copy_(z8, non_blocking=True)
+        pipe([(hy, ym), (hys, yms)], [(hx, xm), (hxs, xms)], [(z8, hz)], mx8rows, stream)
     emm = ctx.timed(emstep, 3, warm=1)
-    ctx.launches += 4 * 2
+    ctx.launches += 4 * 2 * 8
     e2e_by["mxfp8"] = {"value": flops / (emm * 1e-3) / 1e12, "unit": "TFLOP/s", "ms": emm,
                        "h2d_bytes_per_step": world * (hx.numel() + hxs.numel()) + n8 * k8 + n8 * k8 // 32,
-                       "d2h_bytes_per_step": m8 * n8 * 2}
+                       "d2h_bytes_per_step": m8 * n8 * 2,
+                       "note": "api.HostRowPipeline: all operands uploaded, pipelined in 1024-row slabs"}
     if do_cpu:
         from oracle import oracle
         rows, cols = 16, 2048

@@ -49,6 +49,30 @@ def test_bf16_matches_oracle(b200, oracle, b, h, hkv, s, d, causal):
     assert oracle.max_abs(got, ref.reshape(b * h, s, d)) <= ATTN_TOL
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_host_operand_pipeline(b200, oracle, causal):
+    """`api.HostFmha`: Q, K, V in pinned host memory, groups of problems uploaded / attended / downloaded on three
+    streams (a ragged last group included); two calls in a row on one plan, against the oracle and bit-identical to
+    the one-launch device path."""
+    b, h, s, d = 1, 7, 256, 128
+    q, k, v = workloads.fmha_inputs(b, h, s, d, config_index=311)
+    qh, kh, vh = (api.pin(t.reshape(b * h, s, d).contiguous()) for t in (q, k, v))
+    oh = torch.full((b * h, s, d), float("nan"), dtype=torch.bfloat16).pin_memory()
+    plan = api.HostFmha(b * h, s, d, "bf16", causal=causal, group=3)
+    scale = 1.0 / math.sqrt(d)
+    direct = _fmha(b200, q.cuda(), k.cuda(), v.cuda(), causal).cpu()
+    ref = oracle.fmha_ref_cpu(q.float().numpy(), k.float().numpy(), v.float().numpy(), scale, causal=causal,
+                              threads=0).reshape(b * h, s, d)
+    for _ in range(2):
+        plan(qh, kh, vh, oh, scale)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(oh, direct)
+        assert oracle.max_abs(oh.float().numpy(), ref) <= ATTN_TOL
+        oh.fill_(float("nan"))
+    with pytest.raises(ValueError, match="planned shape"):
+        plan(qh[:3], kh, vh, oh, scale)
+
+
 def test_f16_and_input_pos(b200, oracle):
     q, k, v = workloads.fmha_inputs(1, 2, 256, 64, config_index=77)
     q, k, v = q.half(), k.half(), v.half()

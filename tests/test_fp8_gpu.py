@@ -78,3 +78,32 @@ def test_full_size_slab_and_launcher(b200, oracle):
     res2 = launch.linear_tile_fp8_blk128(api.zeros([m, n], "bf16").partition([128, 256]), x, y, api.from_torch(sa * 2),
                                          api.from_torch(sb), 1.0).sync_on(torch.cuda.current_stream())
     assert torch.equal(res2[0].unpartition().storage, out * 2)
+
+
+def test_host_row_pipeline_gives_the_bits_of_one_call(b200):
+    """`api.HostRowPipeline` over the fp8 linear layer: weights first, then ragged row slabs uploaded / multiplied /
+    downloaded on three streams; twice on one plan; bit-identical to one call over device-resident operands."""
+    m, n, k = 1100, 640, 512
+    a, b = workloads.gemm_normal_inputs(m, n, k, config_index=31)
+    aq, sa = quant.quant_fp8_block(a, 1, 128)
+    bq, sb = quant.quant_fp8_block(b, 128, 128)
+    want = _run(b200, aq.cuda(), bq.cuda(), sa.cuda(), sb.cuda(), m, n, k).cpu()
+    host = [t.pin_memory() for t in (aq, sa, bq, sb)]
+    dev = [torch.empty_like(t, device="cuda") for t in (aq, sa, bq, sb)]
+    z = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
+    zh = torch.full((m, n), float("nan"), dtype=torch.bfloat16).pin_memory()
+
+    def rows(r0, r1, s):
+        _lib.check(b200.b200tile_linear_fp8_blk128(dev[0][r0:].data_ptr(), dev[2].data_ptr(), dev[1][r0:].data_ptr(),
+                                                   dev[3].data_ptr(), z[r0:].data_ptr(), b"bf16", r1 - r0, n, k, k, k, n,
+                                                   k // 128, k // 128, 1.0, s.cuda_stream))
+    pipe = api.HostRowPipeline(m, 256)
+    for _ in range(2):
+        pipe([(host[2], dev[2]), (host[3], dev[3])], [(host[0], dev[0]), (host[1], dev[1])], [(z, zh)], rows)
+        torch.cuda.current_stream().synchronize()
+        assert torch.equal(zh, want)
+        zh.fill_(float("nan"))
+        for d in dev:
+            d.zero_()
+    with pytest.raises(ValueError, match="one entry per row"):
+        pipe([], [(host[2], dev[2])], [(z, zh)], rows)
