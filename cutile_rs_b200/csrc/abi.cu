@@ -357,7 +357,19 @@ static int fmha_fwd_common(const char* dtype, const void* q, const void* k, cons
     const char* e = getenv("B200TILE_FMHA_PAIR");
     return e && e[0] != '0';
   }();
-  if (head_dim == 128 && (cluster == 2 || (cluster == 0 && env_pair)))
+  // Unspecified (cluster == 0): the default kernel, except where its 256-row CTAs would leave the last wave mostly
+  // empty -- non-causal problems whose CTA count is a few waves with less than 0.9 of the last one used (the shard
+  // of 8 x 32 heads x 4096 on one of eight GPUs: 512 CTAs = 3.46 waves, 1060 TFLOP/s against 1140 for the
+  // persistent pair kernel, which deals out 128-row items).
+  bool auto_pair = false;
+  if (cluster == 0 && !env_pair && head_dim == 128 && !causal && heads == heads_kv && q_len % 256 == 0 && kv_len >= 2048) {
+    const b200h::DeviceInfo* di = b200h::device_info();
+    const int64_t sms = di ? di->sm_count : 148;
+    const int64_t ctas = (int64_t)batch * heads * (q_len / 256);
+    const int64_t waves = (ctas + sms - 1) / sms;
+    auto_pair = waves >= 2 && waves <= 5 && (double)ctas / (double)(waves * sms) < 0.9;
+  }
+  if (head_dim == 128 && (cluster == 2 || (cluster == 0 && (env_pair || auto_pair))))
     return b200_fmha_fwd_alt_dispatch(dt, q, k, v, out, batch, heads, heads_kv, q_len, kv_len, q_strides,
                                       k_strides, v_strides, o_strides, qk_scale, causal ? 1 : 0, input_pos,
                                       pos_ptr, static_cast<cudaStream_t>(cu_stream));

@@ -238,3 +238,22 @@ def test_every_case_under_the_cta_pair_configuration(b200):
                        cwd=os.path.dirname(os.path.dirname(here)))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert " passed" in r.stdout
+
+
+def test_partial_last_wave_takes_the_persistent_pair_kernel(b200, oracle):
+    """With no configuration asked for, a non-causal problem whose 256-row CTAs would fill only part of their last wave
+    (here 20 heads x 2048 rows = 160 CTAs on 148 SMs) runs on the persistent CTA-pair kernel: the typed entry point's
+    output is bit-identical to the one `num_cta_in_cga = 2` gives, and right against the oracle on three slabs."""
+    b, h, s, d = 1, 20, 2048, 128
+    q, k, v = workloads.fmha_inputs(b, h, s, d, config_index=520)
+    auto = _fmha(b200, q.cuda(), k.cuda(), v.cuda(), False)
+    qd, kd, vd = (api.copy_host_to_device(t) for t in (q, k, v))
+    out = api.zeros([b * h, s, d], "bf16").partition([1, 128, d])
+    (out, *_rest) = launch.fmha(out, qd, kd, vd, 1 / math.sqrt(d), 0, 1, causal=False) \
+        .compile_options(launch.CompileOptions(num_cta_in_cga=2)).sync_on(_stream())
+    assert torch.equal(auto, out.unpartition().storage.reshape(b * h, s, d))
+    got = auto.float().cpu().numpy()
+    for hh, rows in [(0, (0, 8)), (11, (1000, 1016)), (19, (2040, 2048))]:
+        ref = oracle.fmha_ref_cpu(q[:, hh:hh + 1].float().numpy(), k[:, hh:hh + 1].float().numpy(),
+                                  v[:, hh:hh + 1].float().numpy(), 1 / math.sqrt(d), causal=False, rows=rows, threads=0)
+        assert oracle.max_abs(got[hh, rows[0]:rows[1]], ref[0, 0, rows[0]:rows[1]]) <= ATTN_TOL
