@@ -1242,6 +1242,11 @@ def _print_trace(lib, args) -> None:
               f"+ commit {v[2] / n:.0f}, accumulator waits {v[0] / n:.0f}; total {v[5] / n:.0f} cycles per stage ({n} stages); "
               f"SM clock inside the kernel {1e3 * v[5] / max(v[6], 1):.0f} MHz")
         return
+    if args.kernel == "gemm" and v[13] > v[8] > 0:
+        t0 = v[8]
+        print("time line of that CTA, us after its entry: set-up done %.2f, first operands landed %.2f, last commit "
+              "issued %.2f, first epilogue warp done %.2f, about to leave %.2f"
+              % tuple((v[i] - t0) / 1e3 for i in (9, 10, 11, 12, 13)))
     if args.kernel == "nvfp4":
         n = max(v[5], 1)
         print(f"MMA thread of one CTA per stage (4 block-scaled MMAs): stage + scale waits {v[2] / n:.0f}, "

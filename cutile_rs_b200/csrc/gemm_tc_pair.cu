@@ -33,7 +33,7 @@ namespace b200 {
 #ifdef B200TILE_TRACE
 // MMA thread of pair 10: [0] accumulator-buffer waits, [1] stage-full waits, [2] MMA issue,
 // [3] commits, [4] stages, [5] tiles, [6] total cycles, [7] the same span in ns
-__device__ long long g_trace_gemm_pair[8];
+__device__ long long g_trace_gemm_pair[16];   // [8..13]: time line of CTA 20 in ns of the global timer
 #endif
 
 constexpr int P_BM = 128;   // rows per CTA (256 per pair)
@@ -184,6 +184,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   WaitCtx wctx{misc + 1, status};
+#ifdef B200TILE_TRACE
+  if (blockIdx.x == 20 && threadIdx.x == 0) g_trace_gemm_pair[8] = b200_globaltimer_ns();    // kernel entry
+#endif
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < P_STAGES; ++s) {
@@ -209,6 +212,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   cluster_sync_all();  // the partner's barriers exist before anything signals them
   tc_fence_after_sync();
   const uint32_t tmem_base = misc[0];
+#ifdef B200TILE_TRACE
+  if (blockIdx.x == 20 && threadIdx.x == 0) g_trace_gemm_pair[9] = b200_globaltimer_ns();    // set-up done
+#endif
 
   const int tiles_m = (M + 2 * P_BM - 1) / (2 * P_BM);
   const int tiles_n = (N + BN - 1) / BN;
@@ -281,6 +287,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (!mbar_wait(wctx, bar_full + stage * 8, phase, 3)) { ok = false; break; }
           tc_fence_after_sync();
           B200_TR_END(1);
+#ifdef B200TILE_TRACE
+          if (blockIdx.x == 20 && it == 0 && kb == kb0) g_trace_gemm_pair[10] = b200_globaltimer_ns();   // first operands landed
+#endif
           B200_TR_COUNT(4);
           B200_TR_BEGIN();
           const uint64_t adesc = make_smem_desc(sA + stage * L::A_BYTES, 16, 1024, SWZ_128B);
@@ -314,6 +323,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       B200_TR_FLUSH(g_trace_gemm_pair, 6, blockIdx.x == 20);
+#ifdef B200TILE_TRACE
+      if (blockIdx.x == 20) g_trace_gemm_pair[11] = b200_globaltimer_ns();   // last commit issued
+#endif
     }
   } else {
     // -------------------------------- epilogue ---------------------------------
@@ -450,11 +462,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     if (lane == 0) tma_store_wait_all<0>();
+#ifdef B200TILE_TRACE
+    if (blockIdx.x == 20 && threadIdx.x == 64) g_trace_gemm_pair[12] = b200_globaltimer_ns();   // epilogue warp 0 done
+#endif
   }
 
   tc_fence_before_sync();
   __syncthreads();
   cluster_sync_all();  // neither CTA leaves while its partner may still touch its memory
+#ifdef B200TILE_TRACE
+  if (blockIdx.x == 20 && threadIdx.x == 0) g_trace_gemm_pair[13] = b200_globaltimer_ns();    // about to leave
+#endif
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc_2cta(tmem_base, 512);
@@ -653,6 +671,6 @@ int b200_gemm_pair_reset_scratch(cudaStream_t stream) {
 
 #ifdef B200TILE_TRACE
 int b200_trace_read_gemm_pair(long long* out) {
-  return cudaMemcpyFromSymbol(out, b200::g_trace_gemm_pair, 8 * sizeof(long long)) != cudaSuccess;
+  return cudaMemcpyFromSymbol(out, b200::g_trace_gemm_pair, 16 * sizeof(long long)) != cudaSuccess;
 }
 #endif
