@@ -982,8 +982,9 @@ def run_gpu_arm(args):
         def e2e_step():
             host_gemm(a_pin, b_pin, c_pin, stream)
         e2e_api = ("sharding.ShardedHostGemm: each rank uploads M/G rows of A and its B columns from pinned host memory, "
-                   "NCCL all-gather of A over NVLink, b200tile_gemm, download of its C columns")
-        e2e_launches = 1
+                   "NCCL all-gather of A over NVLink, b200tile_gemm, download of its C columns; pipelined over "
+                   f"{host_gemm.chunks} row chunks")
+        e2e_launches = host_gemm.chunks
     e2e_ms = ctx.timed(e2e_step, e2e_steps, warm=1)
     ctx.launches += (e2e_steps + 1) * e2e_launches
     e2e_value = flops / (e2e_ms * 1e-3) / 1e12
