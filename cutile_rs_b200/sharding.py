@@ -91,6 +91,14 @@ def all_gather_rows(a_full: torch.Tensor, rank_rows: torch.Tensor, group: Option
     return a_full
 
 
+def chunk_block_rows(rank: int, world: int, m: int, chunks: int, j: int) -> Tuple[int, int]:
+    """Global rows ``[start, stop)`` of A (and C) that block ``rank`` of row chunk ``j`` holds when every rank's M/G
+    rows are cut into ``chunks`` equal parts: the chunk-major layout of :class:`ShardedHostGemm`."""
+    slab = m // world
+    sub = slab // chunks
+    return rank * slab + j * sub, rank * slab + (j + 1) * sub
+
+
 class ShardedHostGemm:
     """C[:, n0:n1] = A . B[:, n0:n1] for operands that live in HOST memory, on the ranks of one box.
 
@@ -136,7 +144,7 @@ class ShardedHostGemm:
         """``a_rows_host``: this rank's M/G rows of A (pinned); ``b_host``: its [K, N/G] weight columns (pinned);
         ``c_host`` [M, N/G] is complete once ``stream`` has been synchronised."""
         s = stream or torch.cuda.current_stream()
-        g, sub, slab = self.world, self.sub, self.m // self.world
+        g, sub = self.world, self.sub
         s_in, s_out = self.in_stream, self.out_stream
         s_in.wait_stream(s)                                # earlier work on s may still read the device buffers
         s_out.wait_stream(s)
@@ -163,8 +171,8 @@ class ShardedHostGemm:
                 s_out.wait_event(done)
                 with torch.cuda.stream(s_out):
                     for r in range(g):
-                        c_host[r * slab + j * sub:r * slab + (j + 1) * sub].copy_(self.c_dev[j, r * sub:(r + 1) * sub],
-                                                                                  non_blocking=True)
+                        g0, g1 = chunk_block_rows(r, g, self.m, self.chunks, j)
+                        c_host[g0:g1].copy_(self.c_dev[j, r * sub:(r + 1) * sub], non_blocking=True)
             s.wait_stream(s_in)                            # synchronising s covers every copy of the call
             s.wait_stream(s_out)
         return c_host

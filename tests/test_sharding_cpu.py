@@ -50,8 +50,21 @@ def _worker(rank, world, port, q):
         a_full[r0:r1] = a[r0:r1]
         sharding.all_gather_rows(a_full, a_full[r0:r1])
         ok4 = torch.equal(a_full, a)
+        # the chunked pipeline of ShardedHostGemm with the kernel and the copies replaced by torch on CPU: chunk j of
+        # the rank's rows into its block of the chunk-major matrix, gather in place, multiply, rows back by the map
+        chunks, sub = 2, 8
+        a_cm = torch.full((chunks, world * sub, 24), float("nan"))
+        c_out = torch.full((32, b_r.shape[1]), float("nan"))
+        for j in range(chunks):
+            a_cm[j, rank * sub:(rank + 1) * sub] = a[r0 + j * sub:r0 + (j + 1) * sub]
+            dist.all_gather_into_tensor(a_cm[j], a_cm[j, rank * sub:(rank + 1) * sub].clone())
+            c_j = a_cm[j] @ b_r
+            for r in range(world):
+                g0, g1 = sharding.chunk_block_rows(r, world, 32, chunks, j)
+                c_out[g0:g1] = c_j[r * sub:(r + 1) * sub]
+        ok5 = torch.allclose(c_out, a @ b_r, atol=1e-5)
         t = sharding.max_over_ranks(1.0 + rank, torch.device("cpu"))
-        q.put((rank, bool(ok1 and ok2 and ok3 and ok4), t))
+        q.put((rank, bool(ok1 and ok2 and ok3 and ok4 and ok5), t))
     finally:
         dist.destroy_process_group()
 
@@ -72,3 +85,14 @@ def test_two_rank_gloo_split_and_gather():
         assert p.exitcode == 0
     assert all(ok for _, ok, _ in res)
     assert all(t == 2.0 for _, _, t in res)          # MAX over ranks
+
+
+def test_chunk_block_rows_cover_every_row_once():
+    for world, m, chunks in [(1, 256, 2), (2, 512, 2), (4, 8192, 4), (8, 8192, 4)]:
+        seen = []
+        for j in range(chunks):
+            for r in range(world):
+                g0, g1 = sharding.chunk_block_rows(r, world, m, chunks, j)
+                assert g1 - g0 == m // world // chunks and r * (m // world) <= g0 < g1 <= (r + 1) * (m // world)
+                seen.extend(range(g0, g1))
+        assert sorted(seen) == list(range(m))
